@@ -1,0 +1,72 @@
+// Shared device helpers for the sm_100a kernels of this package.
+//
+// Every launcher is an extern "C" function that takes raw device pointers, sizes
+// and a stream, validates what it can on the host, launches, and returns 0 or a
+// negative code (see dib_status below); the Python wrappers turn codes into
+// exceptions.  dtype codes: 0 = float32, 1 = bfloat16.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+enum dib_status : int {
+  DIB_OK = 0,
+  DIB_BAD_DTYPE = -1,
+  DIB_BAD_SIZE = -2,      // a size this kernel refuses (message printed by the wrapper)
+  DIB_BAD_ALIGN = -3,
+  DIB_LAUNCH_FAILED = -4,
+};
+
+#define DIB_CHECK_LAUNCH()                                   \
+  do {                                                       \
+    cudaError_t e__ = cudaGetLastError();                    \
+    if (e__ != cudaSuccess) return DIB_LAUNCH_FAILED;        \
+  } while (0)
+
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+  static __device__ __forceinline__ float load(const float* p) { return *p; }
+  static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+// Round a float32 value to the storage type and back (what a store followed by
+// a load would give).
+template <typename T> __device__ __forceinline__ float round_to(float v);
+template <> __device__ __forceinline__ float round_to<float>(float v) { return v; }
+template <> __device__ __forceinline__ float round_to<__nv_bfloat16>(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+// Fixed-order butterfly reductions: the same lanes always combine in the same
+// order, so a row's result never depends on what else is in the launch.
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum with a fixed order: warp butterflies, then warp 0 adds the
+// per-warp partials in index order.  `scratch` holds at least 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from a previous call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float total = 0.f;
+  for (int w = 0; w < nwarps; ++w) total += scratch[w];
+  return total;
+}
+
+static inline int ceil_div_host(long long a, long long b) { return (int)((a + b - 1) / b); }

@@ -1,0 +1,317 @@
+// Row-wise and element-wise kernels: embedding gather, RMSNorm, fused
+// residual-add + RMSNorm, per-head q/k RMSNorm fused with rotary position
+// encoding and the write into the paged cache, SiLU-gate, row gather.
+//
+// All arithmetic is float32; storage is float32 or bfloat16 (template T).  Norm
+// weights and the rotary table are always float32.
+//
+// Paged cache layout of one layer: [num_pages, 2 (key,value), num_kv_heads,
+// page_size, head_dim], so the keys (or values) of one head inside one page are
+// contiguous.
+#include "common.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                 T* __restrict__ out, int H, int V) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  const bool ok = id >= 0 && id < V;
+  const T* src = table + (size_t)(ok ? id : 0) * H;
+  T* dst = out + (size_t)t * H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    if (ok) dst[i] = src[i];
+    else Elem<T>::store(dst + i, 0.f);
+  }
+}
+
+// ---------------------------------------------------------------- RMSNorm
+// y = x * 1/sqrt(mean(x^2) + eps) * w; one block per row; the row is staged in
+// shared memory as float32.  With ADD: residual += x first (stored rounded to T),
+// and the norm reads the unrounded float32 sum; y overwrites x.
+template <typename T, bool ADD>
+__global__ void rms_norm_kernel(T* __restrict__ x, T* __restrict__ residual,
+                                const float* __restrict__ w, T* __restrict__ out,
+                                int H, float eps) {
+  extern __shared__ float row[];
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = Elem<T>::load(x + base + i);
+    if (ADD) {
+      v += Elem<T>::load(residual + base + i);
+      Elem<T>::store(residual + base + i, v);
+    }
+    row[i] = v;
+    ss += v * v;
+  }
+  const float total = block_sum(ss, scratch);
+  const float rstd = 1.0f / sqrtf(total / (float)H + eps);
+  T* dst = ADD ? x : out;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    Elem<T>::store(dst + base + i, row[i] * rstd * w[i]);
+  }
+}
+
+// ------------------------------------------- q/k norm + rotary + cache write
+// One warp per (token, head) of the fused qkv row.  Heads 0..Hq-1 are queries
+// (written to q_out), then Hkv key heads, then Hkv value heads (written to the
+// cache page slot of the token).  Norm is applied when its weight pointer is
+// non-null, the rotation when the table pointer is non-null; the rotation is
+// rotate-half over the first rotary_dim dims: (x[d], x[d+r/2]) rotated by
+// angle(pos, d) with the table row [cos(r/2) | sin(r/2)].
+template <typename T>
+__global__ void qk_norm_rope_cache_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ kv_cache,
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+    const float* __restrict__ cos_sin, int rotary_dim, int max_pos,
+    const int* __restrict__ positions, const int* __restrict__ slot_mapping,
+    int T_tokens, int Hq, int Hkv, int D, int page_size, long long num_pages) {
+  extern __shared__ float smem[];
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = Hq + 2 * Hkv;
+  const long long item = (long long)blockIdx.x * warps_per_block + warp;
+  if (item >= (long long)T_tokens * heads) return;
+  const int t = (int)(item / heads);
+  const int head = (int)(item % heads);
+  float* s = smem + (size_t)warp * D;
+
+  const T* src = qkv + ((size_t)t * heads + head) * D;
+  const bool is_q = head < Hq;
+  const bool is_k = !is_q && head < Hq + Hkv;
+  const float* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+
+  // destination
+  T* dst = nullptr;
+  if (is_q) {
+    dst = q_out + ((size_t)t * Hq + head) * D;
+  } else {
+    if (kv_cache == nullptr) return;
+    const int slot = slot_mapping[t];
+    if (slot < 0) return;
+    const long long page = slot / page_size;
+    if (page >= num_pages) return;
+    const int off = slot % page_size;
+    const int kv = is_k ? 0 : 1;
+    const int h = is_k ? head - Hq : head - Hq - Hkv;
+    dst = kv_cache + ((((size_t)page * 2 + kv) * Hkv + h) * page_size + off) * D;
+  }
+
+  float ss = 0.f;
+  for (int d = lane; d < D; d += 32) {
+    const float v = Elem<T>::load(src + d);
+    s[d] = v;
+    ss += v * v;
+  }
+  if (nw != nullptr) {
+    ss = warp_sum(ss);
+    const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+    __syncwarp();
+    for (int d = lane; d < D; d += 32) s[d] = s[d] * rstd * nw[d];
+  }
+  __syncwarp();
+
+  const bool rotate = (cos_sin != nullptr) && (is_q || is_k);
+  if (rotate) {
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* tab = cos_sin + (size_t)pos * rotary_dim;
+    const int half = rotary_dim >> 1;
+    for (int d = lane; d < half; d += 32) {
+      const float c = tab[d], sn = tab[half + d];
+      const float x1 = s[d], x2 = s[d + half];
+      Elem<T>::store(dst + d, x1 * c - x2 * sn);
+      Elem<T>::store(dst + d + half, x2 * c + x1 * sn);
+    }
+    for (int d = rotary_dim + lane; d < D; d += 32) Elem<T>::store(dst + d, s[d]);
+  } else {
+    for (int d = lane; d < D; d += 32) Elem<T>::store(dst + d, s[d]);
+  }
+}
+
+// ------------------------------------------------ standalone cache write
+// k, v: [T, Hkv, D] -> the page slot of each token (slot < 0: skipped).
+template <typename T>
+__global__ void reshape_and_cache_kernel(const T* __restrict__ k, const T* __restrict__ v,
+                                         T* __restrict__ kv_cache,
+                                         const int* __restrict__ slot_mapping, int Hkv, int D,
+                                         int page_size, long long num_pages) {
+  const int t = blockIdx.x;
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;
+  const long long page = slot / page_size;
+  if (page >= num_pages) return;
+  const int off = slot % page_size;
+  for (int i = threadIdx.x; i < Hkv * D; i += blockDim.x) {
+    const int h = i / D, d = i % D;
+    const size_t kd = ((((size_t)page * 2 + 0) * Hkv + h) * page_size + off) * D + d;
+    const size_t vd = ((((size_t)page * 2 + 1) * Hkv + h) * page_size + off) * D + d;
+    kv_cache[kd] = k[(size_t)t * Hkv * D + i];
+    kv_cache[vd] = v[(size_t)t * Hkv * D + i];
+  }
+}
+
+// ---------------------------------------------------------------- SiLU gate
+// out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(z) = z / (1 + exp(-z)).
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total,
+                                int I) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long t = idx / I;
+  const int i = (int)(idx % I);
+  const float g = Elem<T>::load(gu + t * 2 * I + i);
+  const float u = Elem<T>::load(gu + t * 2 * I + I + i);
+  const float sg = g / (1.0f + expf(-g));
+  Elem<T>::store(out + idx, sg * u);
+}
+
+// ---------------------------------------------------------------- row gather
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ idx,
+                                   T* __restrict__ out, int H, int T_rows) {
+  const int r = blockIdx.x;
+  int src = idx[r];
+  src = src < 0 ? 0 : (src >= T_rows ? T_rows - 1 : src);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[(size_t)r * H + i] = x[(size_t)src * H + i];
+}
+
+int pick_threads(int n) {
+  int t = 32;
+  while (t < n && t < 1024) t <<= 1;
+  return t;
+}
+
+template <typename T, bool ADD>
+int launch_rms(void* x, void* res, const float* w, void* out, int rows, int H, float eps,
+                      cudaStream_t st) {
+  const size_t smem = (size_t)H * sizeof(float);
+  if (smem > 200 * 1024) return DIB_BAD_SIZE;
+  auto kern = rms_norm_kernel<T, ADD>;
+  if (smem > 48 * 1024) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return DIB_LAUNCH_FAILED;
+  }
+  int th = pick_threads(H);
+  if (th > 512) th = 512;
+  kern<<<rows, th, smem, st>>>((T*)x, (T*)res, w, (T*)out, H, eps);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dib_embedding(const void* table, const int* ids, void* out, int T, int H, int V, int dtype,
+                  cudaStream_t st) {
+  if (T == 0) return DIB_OK;
+  const int th = pick_threads(H) > 256 ? 256 : pick_threads(H);
+  if (dtype == 0)
+    embedding_kernel<float><<<T, th, 0, st>>>((const float*)table, ids, (float*)out, H, V);
+  else if (dtype == 1)
+    embedding_kernel<__nv_bfloat16><<<T, th, 0, st>>>((const __nv_bfloat16*)table, ids,
+                                                      (__nv_bfloat16*)out, H, V);
+  else return DIB_BAD_DTYPE;
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+int dib_rms_norm(const void* x, const float* w, void* out, int rows, int H, float eps, int dtype,
+                 cudaStream_t st) {
+  if (rows == 0) return DIB_OK;
+  if (dtype == 0) return launch_rms<float, false>((void*)x, nullptr, w, out, rows, H, eps, st);
+  if (dtype == 1)
+    return launch_rms<__nv_bfloat16, false>((void*)x, nullptr, w, out, rows, H, eps, st);
+  return DIB_BAD_DTYPE;
+}
+
+int dib_add_rms_norm(void* x, void* residual, const float* w, int rows, int H, float eps,
+                     int dtype, cudaStream_t st) {
+  if (rows == 0) return DIB_OK;
+  if (dtype == 0) return launch_rms<float, true>(x, residual, w, nullptr, rows, H, eps, st);
+  if (dtype == 1) return launch_rms<__nv_bfloat16, true>(x, residual, w, nullptr, rows, H, eps, st);
+  return DIB_BAD_DTYPE;
+}
+
+int dib_qk_norm_rope_cache(const void* qkv, void* q_out, void* kv_cache, const float* q_norm_w,
+                           const float* k_norm_w, float eps, const float* cos_sin, int rotary_dim,
+                           int max_pos, const int* positions, const int* slot_mapping, int T,
+                           int Hq, int Hkv, int D, int page_size, long long num_pages, int dtype,
+                           cudaStream_t st) {
+  if (T == 0) return DIB_OK;
+  if (D < 2 || D > 1024 || (rotary_dim & 1) || rotary_dim > D) return DIB_BAD_SIZE;
+  const int warps = 4;
+  const long long items = (long long)T * (Hq + 2 * Hkv);
+  const int blocks = ceil_div_host(items, warps);
+  const size_t smem = (size_t)warps * D * sizeof(float);
+  if (dtype == 0)
+    qk_norm_rope_cache_kernel<float><<<blocks, warps * 32, smem, st>>>(
+        (const float*)qkv, (float*)q_out, (float*)kv_cache, q_norm_w, k_norm_w, eps, cos_sin,
+        rotary_dim, max_pos, positions, slot_mapping, T, Hq, Hkv, D, page_size, num_pages);
+  else if (dtype == 1)
+    qk_norm_rope_cache_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, st>>>(
+        (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_cache, q_norm_w,
+        k_norm_w, eps, cos_sin, rotary_dim, max_pos, positions, slot_mapping, T, Hq, Hkv, D,
+        page_size, num_pages);
+  else return DIB_BAD_DTYPE;
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+int dib_reshape_and_cache(const void* k, const void* v, void* kv_cache, const int* slot_mapping,
+                          int T, int Hkv, int D, int page_size, long long num_pages, int dtype,
+                          cudaStream_t st) {
+  if (T == 0) return DIB_OK;
+  int th = pick_threads(Hkv * D);
+  if (th > 256) th = 256;
+  if (dtype == 0)
+    reshape_and_cache_kernel<float><<<T, th, 0, st>>>((const float*)k, (const float*)v,
+                                                      (float*)kv_cache, slot_mapping, Hkv, D,
+                                                      page_size, num_pages);
+  else if (dtype == 1)
+    reshape_and_cache_kernel<__nv_bfloat16><<<T, th, 0, st>>>(
+        (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)kv_cache, slot_mapping,
+        Hkv, D, page_size, num_pages);
+  else return DIB_BAD_DTYPE;
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+int dib_silu_mul(const void* gu, void* out, int T, int I, int dtype, cudaStream_t st) {
+  const long long total = (long long)T * I;
+  if (total == 0) return DIB_OK;
+  const int th = 256;
+  const int blocks = ceil_div_host(total, th);
+  if (dtype == 0)
+    silu_mul_kernel<float><<<blocks, th, 0, st>>>((const float*)gu, (float*)out, total, I);
+  else if (dtype == 1)
+    silu_mul_kernel<__nv_bfloat16><<<blocks, th, 0, st>>>((const __nv_bfloat16*)gu,
+                                                          (__nv_bfloat16*)out, total, I);
+  else return DIB_BAD_DTYPE;
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+int dib_gather_rows(const void* x, const int* idx, void* out, int R, int H, int T_rows, int dtype,
+                    cudaStream_t st) {
+  if (R == 0) return DIB_OK;
+  int th = pick_threads(H);
+  if (th > 256) th = 256;
+  if (dtype == 0)
+    gather_rows_kernel<float><<<R, th, 0, st>>>((const float*)x, idx, (float*)out, H, T_rows);
+  else if (dtype == 1)
+    gather_rows_kernel<__nv_bfloat16><<<R, th, 0, st>>>((const __nv_bfloat16*)x, idx,
+                                                        (__nv_bfloat16*)out, H, T_rows);
+  else return DIB_BAD_DTYPE;
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+}  // extern "C"

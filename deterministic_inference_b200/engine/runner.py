@@ -1,0 +1,72 @@
+"""The step function and what it owns: the model, its weights and the cache.
+
+``ModelRunner.step(entries)`` runs exactly the tokens it is given, as one batch,
+from the cache that earlier steps left, and returns float32 logits at the wanted
+places.  The reference's counterpart is ``ModelRunner.forward`` over a
+``ForwardBatch`` built for one mode (sid/engine/model_runner.py:36-96); its
+numerics pinning (TF32 and reduced-precision reductions off, :28-33) is kept for
+the library matrix products.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.engine_config import EngineConfig
+from ..models.registry import build_model, config_from_dir
+from ..weights.loader import load_weights
+from ..weights.random_init import random_tensors_on_device
+from .batch import SequenceInput, StepBatch, build_step_batch
+
+_TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+def pin_numerics() -> None:
+    torch.backends.cuda.matmul.allow_tf32 = False
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    torch.backends.cuda.matmul.allow_fp16_reduced_precision_reduction = False
+
+
+class ModelRunner:
+    def __init__(self, cfg: EngineConfig):
+        pin_numerics()
+        self.cfg = cfg
+        self.device = torch.device(cfg.device)
+        self.dtype = _TORCH_DTYPES[cfg.dtype]
+        # every kernel wrapper refuses tensors that are not on a CUDA device, so a
+        # CPU device fails at the first operation with that message
+        self.model_config = (config_from_dir(cfg.model_path) if cfg.model_path is not None
+                             else cfg.model_config)
+        self.model = build_model(self.model_config, self.dtype, self.device)
+        specs = self.model.tensor_specs()
+        with torch.inference_mode():
+            if cfg.model_path is not None:
+                tensors = load_weights(cfg.model_path, specs, self.model.plan, self.dtype, self.device)
+            else:
+                tensors = random_tensors_on_device(specs, cfg.random_seed, self.dtype, self.device)
+            self.model.load(tensors)
+        self.max_positions = self.model.plan.max_positions
+        self.cache = CacheManager(self.model.cache_specs(), num_pages=cfg.num_pages + 1,
+                                  page_size=cfg.page_size, max_reqs=cfg.max_reqs + 1,
+                                  max_seq_len=min(cfg.max_seq_len, self.max_positions),
+                                  dtype=self.dtype, device=self.device)
+        self.steps_run = 0
+        self.tokens_run = 0
+
+    @torch.inference_mode()
+    def step(self, entries: list[SequenceInput]):
+        """Returns (logits float32 [R, V], the StepBatch).  Row order: the wanted
+        places of the batch's sequences in batch order; ``batch.logit_rows[i]``
+        are the rows of the caller's i-th entry."""
+        for e in entries:
+            self.cache.allocate(e.slot, e.num_computed + len(e.tokens))
+        self.cache.reset_fresh_state()
+        batch = build_step_batch(entries, self.cache, self.device)
+        logits = self.model.forward(batch, self.cache)
+        for e in entries:
+            self.cache.release_passed(e.slot, e.num_computed + len(e.tokens))
+        self.steps_run += 1
+        self.tokens_run += batch.num_tokens
+        return logits, batch

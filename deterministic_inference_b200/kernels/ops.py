@@ -1,0 +1,316 @@
+"""Python side of the CUDA kernels: argument checks and launches.
+
+Every function takes CUDA tensors, checks dtype, shape and contiguity on the
+host, and launches the hand-written kernel on the current stream.  There is no
+CPU path and no library fallback: a tensor that is not on a CUDA device raises
+``KernelError``, and a missing or unbuildable library raises
+``KernelBuildError``.  The one library call is the bfloat16 matrix product of
+``linear`` (cuBLAS through ``torch.mm``) for shapes the package's own tcgen05
+kernel does not take; the reference uses the library for every matrix product
+(sid/model/qwen3.py:38).
+
+The parts call these functions through the module (``ops.rms_norm(...)``), so a
+test can substitute plain PyTorch restatements to exercise the engine's host
+logic on a machine without a GPU; the package itself never does.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from . import build
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_STATUS = {
+    -1: "unsupported dtype",
+    -2: "a size this kernel refuses",
+    -3: "misaligned pointer",
+    -4: "kernel launch failed",
+    -5: "a bounded wait inside the kernel ran out",
+}
+
+_DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+def _ptr(t):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _check(status: int, what: str, detail: str = ""):
+    if status != 0:
+        raise KernelError(f"{what}: {_STATUS.get(status, status)}{(' — ' + detail) if detail else ''}")
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, ndim=None):
+    if not isinstance(t, torch.Tensor):
+        raise KernelError(f"{name} must be a tensor")
+    if not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor: this package has no CPU path")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous (shape {tuple(t.shape)}, stride {t.stride()})")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if ndim is not None and t.dim() != ndim:
+        raise KernelError(f"{name} must have {ndim} dims, got shape {tuple(t.shape)}")
+
+
+def _dt(t: torch.Tensor, name: str) -> int:
+    if t.dtype not in _DT:
+        raise KernelError(f"{name}: dtype {t.dtype} is not supported (float32 or bfloat16)")
+    return _DT[t.dtype]
+
+
+_libs: dict[str, ctypes.CDLL] = {}
+
+
+def _lib(name: str) -> ctypes.CDLL:
+    lib = _libs.get(name)
+    if lib is None:
+        lib = build.load_library(name)
+        _libs[name] = lib
+    return lib
+
+
+# ---------------------------------------------------------------- embedding
+
+def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    """out[t] = table[ids[t]]; ids int32 [T], table [V, H]."""
+    _need(ids, "ids", torch.int32, 1)
+    _need(table, "table", None, 2)
+    out = torch.empty(ids.shape[0], table.shape[1], dtype=table.dtype, device=table.device)
+    st = _lib("elementwise").dib_embedding(
+        _ptr(table), _ptr(ids), _ptr(out), c_int(ids.shape[0]), c_int(table.shape[1]),
+        c_int(table.shape[0]), c_int(_dt(table, "table")), _stream())
+    _check(st, "embedding")
+    return out
+
+
+# ---------------------------------------------------------------- norms
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """y = x / sqrt(mean(x^2) + eps) * weight over the last dim; weight float32."""
+    _need(x, "x")
+    _need(weight, "weight", torch.float32, 1)
+    h = x.shape[-1]
+    if weight.shape[0] != h:
+        raise KernelError(f"rms_norm: weight has {weight.shape[0]} elements, rows have {h}")
+    out = torch.empty_like(x)
+    rows = x.numel() // h if h else 0
+    st = _lib("elementwise").dib_rms_norm(_ptr(x), _ptr(weight), _ptr(out), c_int(rows), c_int(h),
+                                          c_float(eps), c_int(_dt(x, "x")), _stream())
+    _check(st, "rms_norm", f"row width {h}")
+    return out
+
+
+def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float):
+    """In place: residual += x (stored rounded); x = rms_norm(unrounded sum).
+    Returns (x, residual)."""
+    _need(x, "x")
+    _need(residual, "residual", x.dtype)
+    _need(weight, "weight", torch.float32, 1)
+    if x.shape != residual.shape:
+        raise KernelError(f"add_rms_norm: x {tuple(x.shape)} vs residual {tuple(residual.shape)}")
+    h = x.shape[-1]
+    if weight.shape[0] != h:
+        raise KernelError(f"add_rms_norm: weight has {weight.shape[0]} elements, rows have {h}")
+    rows = x.numel() // h if h else 0
+    st = _lib("elementwise").dib_add_rms_norm(_ptr(x), _ptr(residual), _ptr(weight), c_int(rows),
+                                              c_int(h), c_float(eps), c_int(_dt(x, "x")), _stream())
+    _check(st, "add_rms_norm", f"row width {h}")
+    return x, residual
+
+
+# ------------------------------------------------ q/k norm + rotary + cache
+
+def qk_norm_rope_cache(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                       q_norm_weight, k_norm_weight, eps: float, cos_sin, positions: torch.Tensor,
+                       kv_cache, slot_mapping, page_size: int) -> torch.Tensor:
+    """From the fused projection row [q heads | k heads | v heads] of each token:
+    per-head RMSNorm of q and k (when a weight is given), rotate-half rotation by
+    the token's position (when a table [max_pos, rotary_dim] = [cos | sin] is
+    given), q to the returned tensor [T, Hq, D], k and v into the token's slot of
+    the paged cache [pages, 2, Hkv, page_size, D] (when a cache is given;
+    slot = page * page_size + offset, negative = skip)."""
+    _need(qkv, "qkv", None, 2)
+    t = qkv.shape[0]
+    width = (num_heads + 2 * num_kv_heads) * head_dim
+    if qkv.shape[1] != width:
+        raise KernelError(f"qkv has width {qkv.shape[1]}, expected {width}")
+    _need(positions, "positions", torch.int32, 1)
+    for w, n in ((q_norm_weight, "q_norm_weight"), (k_norm_weight, "k_norm_weight")):
+        if w is not None:
+            _need(w, n, torch.float32, 1)
+            if w.shape[0] != head_dim:
+                raise KernelError(f"{n} has {w.shape[0]} elements, head_dim is {head_dim}")
+    rotary_dim, max_pos = 0, 0
+    if cos_sin is not None:
+        _need(cos_sin, "cos_sin", torch.float32, 2)
+        max_pos, rotary_dim = cos_sin.shape
+    num_pages = 0
+    if kv_cache is not None:
+        _need(kv_cache, "kv_cache", qkv.dtype, 5)
+        _need(slot_mapping, "slot_mapping", torch.int32, 1)
+        if tuple(kv_cache.shape[1:]) != (2, num_kv_heads, page_size, head_dim):
+            raise KernelError(f"kv_cache shape {tuple(kv_cache.shape)} does not match "
+                              f"[pages, 2, {num_kv_heads}, {page_size}, {head_dim}]")
+        num_pages = kv_cache.shape[0]
+    q = torch.empty(t, num_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
+    st = _lib("elementwise").dib_qk_norm_rope_cache(
+        _ptr(qkv), _ptr(q), _ptr(kv_cache), _ptr(q_norm_weight), _ptr(k_norm_weight), c_float(eps),
+        _ptr(cos_sin), c_int(rotary_dim), c_int(max_pos), _ptr(positions), _ptr(slot_mapping),
+        c_int(t), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
+        c_longlong(num_pages), c_int(_dt(qkv, "qkv")), _stream())
+    _check(st, "qk_norm_rope_cache", f"head_dim {head_dim}, rotary_dim {rotary_dim}")
+    return q
+
+
+def reshape_and_cache(k: torch.Tensor, v: torch.Tensor, kv_cache: torch.Tensor,
+                      slot_mapping: torch.Tensor) -> None:
+    """k, v [T, Hkv, D] into their slots of the paged cache (negative slot: skip)."""
+    _need(k, "k", None, 3)
+    _need(v, "v", k.dtype, 3)
+    _need(kv_cache, "kv_cache", k.dtype, 5)
+    _need(slot_mapping, "slot_mapping", torch.int32, 1)
+    t, hkv, d = k.shape
+    if v.shape != k.shape or kv_cache.shape[1] != 2 or kv_cache.shape[2] != hkv or kv_cache.shape[4] != d:
+        raise KernelError(f"reshape_and_cache: k {tuple(k.shape)}, v {tuple(v.shape)}, "
+                          f"cache {tuple(kv_cache.shape)}")
+    st = _lib("elementwise").dib_reshape_and_cache(
+        _ptr(k), _ptr(v), _ptr(kv_cache), _ptr(slot_mapping), c_int(t), c_int(hkv), c_int(d),
+        c_int(kv_cache.shape[3]), c_longlong(kv_cache.shape[0]), c_int(_dt(k, "k")), _stream())
+    _check(st, "reshape_and_cache")
+
+
+# ---------------------------------------------------------------- attention
+
+def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float,
+                    window=None) -> torch.Tensor:
+    """Causal attention of every token of the step over its sequence's keys in the
+    paged cache.  q [T, Hq, D]; kv_cache [pages, 2, Hkv, page_size, D]; ``meta``
+    is the step's attention metadata for this cache's group (``AttentionMeta``:
+    block_table [B, max_blocks], token_seq [T], positions [T], cu_q_lens [B+1],
+    seq_lens [B], host copies of the lengths, number of leading decode
+    sequences).  A query at position p sees keys max(0, p-window+1) .. p."""
+    _need(q, "q", None, 3)
+    _need(kv_cache, "kv_cache", q.dtype, 5)
+    t, hq, d = q.shape
+    _, two, hkv, page_size, d2 = kv_cache.shape
+    if two != 2 or d2 != d or hq % hkv:
+        raise KernelError(f"paged_attention: q {tuple(q.shape)} vs cache {tuple(kv_cache.shape)}")
+    _need(meta.block_table, "block_table", torch.int32, 2)
+    _need(meta.token_seq, "token_seq", torch.int32, 1)
+    _need(meta.positions, "positions", torch.int32, 1)
+    out = torch.empty_like(q)
+    win = int(window) if window else 0
+    if q.dtype == torch.bfloat16:
+        from . import attention_bf16
+        if attention_bf16.supports(hq, hkv, d, page_size):
+            attention_bf16.run(q, out, kv_cache, meta, scale, win)
+            return out
+    st = _lib("attention_generic").dib_paged_attention_generic(
+        _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(meta.block_table), c_int(meta.block_table.shape[1]),
+        _ptr(meta.token_seq), _ptr(meta.positions), c_int(t), c_int(hq), c_int(hkv), c_int(d),
+        c_int(page_size), c_float(scale), c_int(win), c_int(_dt(q, "q")), _stream())
+    _check(st, "paged_attention", f"head_dim {d} (at most 256), heads {hq}/{hkv}")
+    return out
+
+
+# ---------------------------------------------------------------- feed-forward
+
+def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
+    """[T, 2I] = [gate | up] -> silu(gate) * up, [T, I]."""
+    _need(gate_up, "gate_up", None, 2)
+    t, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError(f"silu_mul: width {two_i} is odd")
+    out = torch.empty(t, two_i // 2, dtype=gate_up.dtype, device=gate_up.device)
+    st = _lib("elementwise").dib_silu_mul(_ptr(gate_up), _ptr(out), c_int(t), c_int(two_i // 2),
+                                          c_int(_dt(gate_up, "gate_up")), _stream())
+    _check(st, "silu_mul")
+    return out
+
+
+def gather_rows(x: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    """out[r] = x[index[r]]; index int32."""
+    _need(x, "x", None, 2)
+    _need(index, "index", torch.int32, 1)
+    out = torch.empty(index.shape[0], x.shape[1], dtype=x.dtype, device=x.device)
+    st = _lib("elementwise").dib_gather_rows(_ptr(x), _ptr(index), _ptr(out), c_int(index.shape[0]),
+                                             c_int(x.shape[1]), c_int(x.shape[0]),
+                                             c_int(_dt(x, "x")), _stream())
+    _check(st, "gather_rows")
+    return out
+
+
+# ---------------------------------------------------------------- matrix product
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    """y = x @ weight^T; x [M, K], weight [N, K] (checkpoint layout), no bias.
+
+    float32: the package's own CUDA-core kernel (plain FMA, no TF32, fixed k
+    order, so a row's bits do not depend on the batch).  bfloat16: float32
+    accumulation on the tensor cores; ``out_dtype=torch.float32`` returns the
+    accumulator unrounded (used for the logits)."""
+    _need(x, "x", None, 2)
+    _need(weight, "weight", x.dtype, 2)
+    m, k = x.shape
+    n, k2 = weight.shape
+    if k != k2:
+        raise KernelError(f"linear: x [{m}, {k}] against weight [{n}, {k2}]")
+    if x.dtype == torch.float32:
+        out = torch.empty(m, n, dtype=torch.float32, device=x.device)
+        st = _lib("gemm_fp32").dib_gemm_fp32(_ptr(x), _ptr(weight), _ptr(out), c_int(m), c_int(n),
+                                             c_int(k), _stream())
+        _check(st, "linear(float32)", f"M={m} N={n} K={k}")
+        return out
+    if x.dtype != torch.bfloat16:
+        raise KernelError(f"linear: dtype {x.dtype} is not supported")
+    from . import gemm_bf16
+    return gemm_bf16.linear(x, weight, out_dtype or torch.bfloat16)
+
+
+# ---------------------------------------------------------------- sampling
+
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """int32 [R]: index of the largest logit of each row, lowest index on ties."""
+    _need(logits, "logits", torch.float32, 2)
+    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    st = _lib("sampling").dib_argmax(_ptr(logits), _ptr(out), c_int(logits.shape[0]),
+                                     c_int(logits.shape[1]), _stream())
+    _check(st, "argmax")
+    return out
+
+
+def gumbel_sample(logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor,
+                  sample_positions: torch.Tensor, keep=None) -> torch.Tensor:
+    """int32 [R]: rows with temperature <= 0 take the argmax; the others the
+    position-seeded Gumbel-max draw from softmax(logits / temperature), restricted
+    to ids with keep != 0 when a mask (uint8 [R, V]) is given."""
+    _need(logits, "logits", torch.float32, 2)
+    r, v = logits.shape
+    _need(temperatures, "temperatures", torch.float32, 1)
+    _need(seeds, "seeds", torch.int64, 1)
+    _need(sample_positions, "sample_positions", torch.int64, 1)
+    if not (temperatures.shape[0] == seeds.shape[0] == sample_positions.shape[0] == r):
+        raise KernelError("gumbel_sample: per-row parameter lengths differ from the number of rows")
+    if keep is not None:
+        _need(keep, "keep", torch.uint8, 2)
+        if tuple(keep.shape) != (r, v):
+            raise KernelError(f"gumbel_sample: keep {tuple(keep.shape)} vs logits {(r, v)}")
+    out = torch.empty(r, dtype=torch.int32, device=logits.device)
+    st = _lib("sampling").dib_gumbel_sample(_ptr(logits), _ptr(temperatures), _ptr(seeds),
+                                            _ptr(sample_positions), _ptr(keep), _ptr(out),
+                                            c_int(r), c_int(v), _stream())
+    _check(st, "gumbel_sample")
+    return out

@@ -1,0 +1,110 @@
+"""The generic decoder: embedding, a schedule of blocks, final norm, head.
+
+It is built from a ``ModelPlan`` alone and runs one step: the tokens of the
+batch through every schedule entry, each entry's mixer working on the cache the
+entry names, then the head on the requested rows only
+(sid/model/qwen3.py:88-115).  Which architecture the plan came from is not
+known here.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildContext, ModelPlan, TensorSpec
+
+
+class DecoderModel:
+    def __init__(self, plan: ModelPlan, dtype: torch.dtype, device):
+        plan.validate()
+        self.plan = plan
+        self.dtype = dtype
+        self.device = torch.device(device)
+        self.ctx = BuildContext(dtype=dtype, device=self.device)
+        self.blocks = []
+        self.mixers = []
+        for spec in plan.layers:
+            mixer = MIXERS.build(spec.mixer, self.ctx)
+            ff = FEED_FORWARDS.build(spec.feed_forward, self.ctx)
+            n1 = NORMS.build(spec.mixer_norm, self.ctx)
+            n2 = NORMS.build(spec.feed_forward_norm, self.ctx)
+            self.blocks.append(BLOCKS.create(spec.block, self.ctx, mixer=mixer, feed_forward=ff,
+                                             mixer_norm=n1, feed_forward_norm=n2))
+            self.mixers.append(mixer)
+        self.final_norm = NORMS.build(plan.final_norm, self.ctx)
+        self.embedding = None
+        self.head = None
+
+    # ---- weights ------------------------------------------------------------
+
+    def parts(self):
+        for b in self.blocks:
+            yield b.mixer
+            yield b.feed_forward
+            yield b.mixer_norm
+            yield b.feed_forward_norm
+        yield self.final_norm
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        """Every checkpoint tensor the model needs, in a fixed order (the order
+        the random-weights mode draws them in)."""
+        p = self.plan
+        specs = [TensorSpec(p.embedding_name, (p.vocab_size, p.hidden_size), role="table")]
+        for part in self.parts():
+            specs.extend(part.tensor_specs())
+        if p.head_name is not None:
+            specs.append(TensorSpec(p.head_name, (p.vocab_size, p.hidden_size)))
+        seen = set()
+        for s in specs:
+            if s.name in seen:
+                raise ValueError(f"tensor {s.name!r} is claimed by two parts")
+            seen.add(s.name)
+        return specs
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        p = self.plan
+        self.embedding = tensors[p.embedding_name]
+        self.head = self.embedding if p.head_name is None else tensors[p.head_name]
+        for part in self.parts():
+            part.load(tensors)
+
+    # ---- caches ---------------------------------------------------------------
+
+    def cache_specs(self) -> dict[int, object]:
+        """cache id -> the need of the mixer that writes it."""
+        out = {}
+        for e in self.plan.schedule:
+            spec = self.mixers[e.layer].cache_spec()
+            if spec is None:
+                continue
+            if e.writes_cache:
+                out[e.cache] = spec
+        for e in self.plan.schedule:
+            spec = self.mixers[e.layer].cache_spec()
+            if spec is not None and not e.writes_cache:
+                if out[e.cache].group_key() != spec.group_key():
+                    raise ValueError(f"layer {e.layer} reads cache {e.cache} of another kind: "
+                                     f"{spec} vs {out[e.cache]}")
+        return out
+
+    # ---- one step ---------------------------------------------------------------
+
+    def forward(self, step, cache_manager) -> torch.Tensor:
+        """float32 logits [R, V] at ``step.logit_indices``."""
+        hidden = ops.embedding(step.input_ids, self.embedding)
+        residual = None
+        for e in self.plan.schedule:
+            cache = cache_manager.view(e.cache, step, writes=e.writes_cache)
+            hidden, residual = self.blocks[e.layer].forward(hidden, residual, step, cache)
+        # the head is applied to the requested rows only: gather first, then the
+        # last residual add and the final norm on those rows
+        if step.num_logits == 0:
+            return torch.empty(0, self.plan.vocab_size, dtype=torch.float32, device=hidden.device)
+        rows = ops.gather_rows(hidden, step.logit_indices)
+        if residual is None:
+            rows = self.final_norm.forward(rows)
+        else:
+            res_rows = ops.gather_rows(residual, step.logit_indices)
+            rows, _ = self.final_norm.add_forward(rows, res_rows)
+        return ops.linear(rows, self.head, out_dtype=torch.float32)

@@ -1,0 +1,73 @@
+"""Interfaces of the parts.
+
+Part                 tensor_specs() -> [TensorSpec]; load(tensors: {name: Tensor})
+Norm(Part)           forward(x) -> y;  add_forward(x, residual) -> (y, residual)
+PositionEncoding     prepare(); rotary_table() -> Tensor | None; apply(q, k, positions)
+Mixer(Part)          cache_spec() -> PagedKVSpec | StateSpec | None
+                     forward(x [T, H], step, cache) -> [T, H]
+FeedForward(Part)    forward(x [T, H]) -> [T, H]
+Block                forward(hidden, residual, step, cache) -> (hidden, residual)
+
+``step`` is the step's ``StepBatch`` (tokens, positions, sequence boundaries,
+state slots); ``cache`` is the view of the one cache the schedule entry names
+(``CacheView``: the layer's page pool with its group's block table and slot
+mapping, or the state array).  No part sees the model, the schedule, the
+scheduler or another part's weights.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .spec import TensorSpec
+
+
+class Part:
+    kind = "?"
+
+    def tensor_specs(self) -> list[TensorSpec]:
+        return []
+
+    def load(self, tensors: dict[str, torch.Tensor]) -> None:
+        pass
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_forward(self, x: torch.Tensor, residual: torch.Tensor):
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def prepare(self) -> None:
+        pass
+
+    def rotary_table(self) -> Optional[torch.Tensor]:
+        """float32 [max_positions, rotary_dim] = [cos | sin] for mixers that fuse
+        the rotation into their own kernel, or None if this encoding is not a
+        rotation."""
+        return None
+
+
+class Mixer(Part):
+    def cache_spec(self):
+        return None
+
+    def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block:
+    kind = "?"
+
+    def forward(self, hidden, residual, step, cache):
+        raise NotImplementedError

@@ -1,0 +1,60 @@
+"""Sampling from float32 logits rows.
+
+Greedy (temperature 0): argmax, lowest index on ties.  Otherwise softmax of
+logits / temperature, optional top-k / top-p filtering, and a Gumbel-max draw
+whose noise is a pure function of (seed, position of the generated token,
+vocabulary id), so a request's draw does not depend on the batch
+(sid/engine/sampler.py:22-69).  The position convention is the reference's:
+the token generated after n tokens of the sequence has position n
+(sid/engine/batch.py:3-10).
+
+argmax and the Gumbel draw are this package's kernels; the top-k / top-p mask is
+built with a sort on the device, as in the reference, and only when some row
+asks for it.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+
+
+def keep_mask(logits: torch.Tensor, temperatures: torch.Tensor, top_ks: torch.Tensor,
+              top_ps: torch.Tensor) -> torch.Tensor:
+    """uint8 [R, V]: 1 for ids that survive top-k / top-p
+    (sid/engine/sampler.py:44-62): sort the probabilities descending; drop a token
+    when the mass before it exceeds top_p or its rank >= top_k; rank 0 stays."""
+    stochastic = temperatures > 0
+    temps = torch.where(stochastic, temperatures, torch.ones_like(temperatures))
+    probs = torch.softmax(logits / temps.unsqueeze(-1), dim=-1)
+    probs_sort, probs_idx = probs.sort(dim=-1, descending=True)
+    cum = torch.cumsum(probs_sort, dim=-1)
+    dropped = (cum - probs_sort) > top_ps.unsqueeze(-1)
+    ranks = torch.arange(probs.shape[-1], device=probs.device).expand_as(probs_sort)
+    k = torch.where(top_ks > 0, top_ks, torch.full_like(top_ks, probs.shape[-1]))
+    dropped |= ranks >= k.unsqueeze(-1)
+    dropped[:, 0] = False
+    keep = torch.zeros_like(dropped)
+    keep.scatter_(-1, probs_idx, ~dropped)
+    return keep.to(torch.uint8).contiguous()
+
+
+def sample(logits: torch.Tensor, params: list, sample_positions: list) -> torch.Tensor:
+    """int32 [R] token ids.  ``params[i]`` is the ``SamplingParams`` of row i and
+    ``sample_positions[i]`` the absolute position of the token it generates."""
+    r = logits.shape[0]
+    if r == 0:
+        return torch.empty(0, dtype=torch.int32, device=logits.device)
+    if all(p.temperature <= 0 for p in params):
+        return ops.argmax(logits)
+    dev = logits.device
+    temps = torch.tensor([p.temperature for p in params], dtype=torch.float32, device=dev)
+    seeds = torch.tensor([p.seed for p in params], dtype=torch.int64, device=dev)
+    pos = torch.tensor(list(sample_positions), dtype=torch.int64, device=dev)
+    keep = None
+    if any(p.temperature > 0 and (p.top_k > 0 or p.top_p < 1.0) for p in params):
+        top_ks = torch.tensor([p.top_k if p.top_k > 0 else -1 for p in params], dtype=torch.int64, device=dev)
+        top_ps = torch.tensor([p.top_p for p in params], dtype=torch.float32, device=dev)
+        keep = keep_mask(logits, temps, top_ks, top_ps)
+    return ops.gumbel_sample(logits, temps, seeds, pos, keep)

@@ -1,0 +1,321 @@
+"""Each CUDA kernel alone against its plain PyTorch reference (tests/torch_kernels.py),
+at sizes other than the engine's: odd widths, head sizes in steps of 16, group
+ratios 1..8, shuffled pages, page and tile edges, window edges.  Patterned after
+the reference's kernel tests (tests/test_01_triton_ops.py, test_02_flash_decode.py,
+test_03_extend_attention.py, test_04_reshape_and_cache.py, test_07_sampler.py)."""
+
+import pytest
+import torch
+
+from tests import torch_kernels as ref
+from tests.attn_util import PagedCase, dense_reference
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    # bfloat16: the reference's kernel tolerance (tests/conftest.py:35-37)
+    return dict(atol=2e-2, rtol=2e-2) if dtype == torch.bfloat16 else dict(atol=2e-6, rtol=2e-6)
+
+
+def ops():
+    from deterministic_inference_b200.kernels import ops as o
+    return o
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(dtype):
+    torch.manual_seed(0)
+    table = torch.randn(1000, 200, device="cuda").to(dtype)
+    ids = torch.tensor([0, 999, 5, 5, 123, 998, 1], dtype=torch.int32, device="cuda")
+    assert torch.equal(ops().embedding(ids, table), ref.embedding(ids, table))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,h", [(1, 1024), (7, 5120), (33, 200), (128, 96), (3, 12288)])
+def test_rms_norm(dtype, rows, h):
+    torch.manual_seed(1)
+    x = torch.randn(rows, h, device="cuda").to(dtype)
+    w = torch.randn(h, device="cuda")
+    got = ops().rms_norm(x, w, 1e-5)
+    want = ref._rms(x.float(), w, 1e-5)
+    torch.testing.assert_close(got.float(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,h", [(1, 1024), (9, 4096), (33, 200)])
+def test_add_rms_norm(dtype, rows, h):
+    torch.manual_seed(2)
+    x = torch.randn(rows, h, device="cuda").to(dtype)
+    r = torch.randn(rows, h, device="cuda").to(dtype)
+    w = torch.randn(h, device="cuda")
+    s = x.float() + r.float()
+    gx, gr = ops().add_rms_norm(x.clone(), r.clone(), w, 1e-6)
+    torch.testing.assert_close(gr.float(), s.to(dtype).float(), atol=0, rtol=0)   # stored rounded
+    torch.testing.assert_close(gx.float(), ref._rms(s, w, 1e-6), **tol(dtype))    # norm of unrounded sum
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,rot,norm", [
+    (16, 8, 128, 128, True), (6, 2, 32, 32, True), (5, 5, 48, 48, True), (4, 1, 80, 32, False),
+    (8, 1, 16, 16, True), (3, 3, 64, 0, True), (7, 7, 256, 256, True)])
+def test_qk_norm_rope_cache(dtype, hq, hkv, d, rot, norm):
+    torch.manual_seed(3)
+    t, page, pages, max_pos = 37, 16, 11, 300
+    qkv = torch.randn(t, (hq + 2 * hkv) * d, device="cuda").to(dtype)
+    qw = torch.randn(d, device="cuda") if norm else None
+    kw = torch.randn(d, device="cuda") if norm else None
+    table = None
+    if rot:
+        half = rot // 2
+        inv = 1.0 / (1e4 ** (torch.arange(half, dtype=torch.float32, device="cuda") / half))
+        f = torch.outer(torch.arange(max_pos, dtype=torch.float32, device="cuda"), inv)
+        table = torch.cat([f.cos(), f.sin()], -1).contiguous()
+    pos = torch.randint(0, max_pos, (t,), device="cuda", dtype=torch.int32)
+    slots = (torch.randperm((pages - 1) * page, device="cuda")[:t] + page).to(torch.int32)
+    slots[5] = -1                                   # skipped token
+    c1 = torch.zeros(pages, 2, hkv, page, d, device="cuda", dtype=dtype)
+    c2 = c1.clone()
+    q1 = ops().qk_norm_rope_cache(qkv, hq, hkv, d, qw, kw, 1e-6, table, pos, c1, slots, page)
+    q2 = ref.qk_norm_rope_cache(qkv, hq, hkv, d, qw, kw, 1e-6, table, pos, c2, slots, page)
+    torch.testing.assert_close(q1.float(), q2.float(), **tol(dtype))
+    torch.testing.assert_close(c1.float(), c2.float(), **tol(dtype))
+    assert torch.equal(c1[0], torch.zeros_like(c1[0]))      # page 0 untouched
+    # without a cache nothing is written and q is the same
+    q3 = ops().qk_norm_rope_cache(qkv, hq, hkv, d, qw, kw, 1e-6, table, pos, None, None, page)
+    assert torch.equal(q1, q3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_reshape_and_cache_round_trip(dtype):
+    torch.manual_seed(4)
+    t, hkv, d, page, pages = 50, 3, 48, 8, 20
+    k = torch.randn(t, hkv, d, device="cuda").to(dtype)
+    v = torch.randn(t, hkv, d, device="cuda").to(dtype)
+    slots = (torch.randperm((pages - 1) * page, device="cuda")[:t] + page).to(torch.int32)
+    slots[0] = -1
+    cache = torch.zeros(pages, 2, hkv, page, d, device="cuda", dtype=dtype)
+    ops().reshape_and_cache(k, v, cache, slots)
+    for i in range(1, t):
+        p, o = int(slots[i]) // page, int(slots[i]) % page
+        assert torch.equal(cache[p, 0, :, o], k[i]) and torch.equal(cache[p, 1, :, o], v[i])
+    assert cache.float().abs().sum() == (k[1:].float().abs().sum() + v[1:].float().abs().sum())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("t,i", [(1, 3072), (5, 160), (64, 25600), (3, 7)])
+def test_silu_mul(dtype, t, i):
+    torch.manual_seed(5)
+    gu = (3 * torch.randn(t, 2 * i, device="cuda")).to(dtype)
+    g, u = gu[:, :i].float(), gu[:, i:].float()
+    torch.testing.assert_close(ops().silu_mul(gu).float(), g * torch.sigmoid(g) * u, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gather_rows(dtype):
+    x = torch.randn(40, 200, device="cuda").to(dtype)
+    idx = torch.tensor([39, 0, 7, 7], dtype=torch.int32, device="cuda")
+    assert torch.equal(ops().gather_rows(x, idx), x[idx.long()])
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 151, 97), (33, 200, 130), (70, 64, 64), (2, 1000, 1024),
+                                   (257, 96, 160)])
+def test_linear_fp32_is_true_fp32(m, n, k):
+    torch.manual_seed(6)
+    x = torch.randn(m, k, device="cuda")
+    w = torch.randn(n, k, device="cuda")
+    got = ops().linear(x, w)
+    want = (x.double() @ w.double().T)
+    # float32 FMA accumulation: error ~ k * 2^-24 * |terms|; TF32 would be ~1e-3
+    torch.testing.assert_close(got.double(), want, atol=2e-5 * (k ** 0.5), rtol=1e-5)
+
+
+def test_linear_fp32_row_does_not_depend_on_batch():
+    """A row gives the same bits alone and among 333 rows (the reference checks its
+    batch-invariant product the same way, tests/test_10_batch_invariant.py:32-43)."""
+    torch.manual_seed(7)
+    x = torch.randn(333, 200, device="cuda")
+    w = torch.randn(150, 200, device="cuda")
+    full = ops().linear(x, w)
+    for r in (0, 63, 64, 332):
+        assert torch.equal(ops().linear(x[r:r + 1].contiguous(), w)[0], full[r])
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 4096, 1024), (8, 1024, 3072), (64, 200, 136), (300, 152, 96),
+                                   (2048, 512, 256)])
+def test_linear_bf16(m, n, k):
+    torch.manual_seed(8)
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = (0.05 * torch.randn(n, k, device="cuda")).to(torch.bfloat16)
+    want = x.float() @ w.float().T
+    torch.testing.assert_close(ops().linear(x, w).float(), want, atol=2e-2, rtol=2e-2)
+    got32 = ops().linear(x, w, out_dtype=torch.float32)
+    assert got32.dtype == torch.float32
+    torch.testing.assert_close(got32, want, atol=1e-3, rtol=1e-3)
+
+
+# ------------------------------------------------------------------ attention
+
+ATTN_SHAPES = [(16, 8, 128, 16), (6, 2, 32, 32), (5, 5, 48, 16), (8, 1, 64, 8), (4, 4, 16, 64),
+               (64, 8, 128, 16), (2, 2, 256, 16)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hq,hkv,d,page", ATTN_SHAPES)
+def test_paged_attention_mixed_batch(dtype, hq, hkv, d, page):
+    """Decode tokens beside prompt portions with cached prefixes, shuffled pages;
+    lengths at page and tile edges (tests/test_02_flash_decode.py:61-71,
+    tests/test_03_extend_attention.py:56-72 of the reference)."""
+    lens = [1, 33, 257, 64, 100, 31]
+    case = PagedCase(lens, hkv, d, page, dtype, seed=11)
+    # seq: (first new position, new tokens)
+    cuts = [(0, 1), (32, 1), (256, 1), (0, 64), (37, 63), (29, 2)]
+    seqs = list(range(len(lens)))
+    meta = case.meta(seqs, cuts)
+    g = torch.Generator().manual_seed(12)
+    t = sum(n for _, n in cuts)
+    q = torch.randn(t, hq, d, generator=g).to(device="cuda", dtype=dtype)
+    got = ops().paged_attention(q, case.cache, meta, d ** -0.5)
+    off = 0
+    for s, (start, n) in zip(seqs, cuts):
+        want = dense_reference(q[off:off + n], case.k[s], case.v[s], d ** -0.5,
+                               list(range(start, start + n)))
+        torch.testing.assert_close(got[off:off + n].float(), want, **tol(dtype))
+        off += n
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 7, 16, 24, 33, 500])
+def test_paged_attention_window_edge(dtype, window):
+    """One key far outside and one just inside the window carry huge values: the
+    output shows at once whether the edge is off by one."""
+    hq, hkv, d, page = 4, 2, 32, 16
+    n = 90
+    g = torch.Generator().manual_seed(13)
+    k = [torch.randn(n, hkv, d, generator=g).to(device="cuda", dtype=dtype)]
+    v = [torch.randn(n, hkv, d, generator=g).to(device="cuda", dtype=dtype)]
+    case = PagedCase([n], hkv, d, page, dtype, seed=14, k=k, v=v)
+    q = torch.randn(n - 40, hq, d, generator=g).to(device="cuda", dtype=dtype)
+    meta = case.meta([0], [(40, n - 40)])
+    got = ops().paged_attention(q, case.cache, meta, d ** -0.5, window)
+    want = dense_reference(q, k[0], v[0], d ** -0.5, list(range(40, n)), window)
+    torch.testing.assert_close(got.float(), want, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_far_key_stands_out(dtype):
+    """Among 700 keys one early key matches the query strongly: the output must be
+    that key's value (a kernel that skips a page or a tile would miss it)."""
+    hq, hkv, d, page, n = 4, 2, 64, 16, 700
+    g = torch.Generator().manual_seed(15)
+    for far in (0, 15, 16, 255, 256, 300, 698):
+        k = 0.1 * torch.randn(n, hkv, d, generator=g)
+        v = torch.randn(n, hkv, d, generator=g)
+        q = 0.1 * torch.randn(1, hq, d, generator=g)
+        direction = torch.randn(d, generator=g)
+        direction /= direction.norm()
+        k[far] += 30 * direction
+        q += 30 * direction
+        case = PagedCase([n], hkv, d, page, dtype, seed=16,
+                         k=[k.to(device="cuda", dtype=dtype)], v=[v.to(device="cuda", dtype=dtype)])
+        qd = q.to(device="cuda", dtype=dtype)
+        got = ops().paged_attention(qd, case.cache, case.meta([0], [(n - 1, 1)]), 1.0)
+        for h in range(hq):
+            torch.testing.assert_close(got[0, h].float(), case.v[0][far, h // 2].float(),
+                                       atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_paged_attention_cut_and_batch_invariance(dtype):
+    """The same query position gives close results (float32: the same bits)
+    whatever the cut of the prompt and whatever else is in the batch
+    (tests/test_03_extend_attention.py:75-152 of the reference)."""
+    hq, hkv, d, page = 6, 2, 32, 16
+    lens = [150, 97, 40]
+    case = PagedCase(lens, hkv, d, page, dtype, seed=17)
+    g = torch.Generator().manual_seed(18)
+    qfull = torch.randn(150, hq, d, generator=g).to(device="cuda", dtype=dtype)
+    whole = ops().paged_attention(qfull, case.cache, case.meta([0], [(0, 150)]), d ** -0.5)
+    # cut at 70, and as one of three sequences
+    other = torch.randn(97 - 10 + 40, hq, d, generator=g).to(device="cuda", dtype=dtype)
+    part = ops().paged_attention(qfull[70:], case.cache, case.meta([0], [(70, 80)]), d ** -0.5)
+    mixed_q = torch.cat([other[:87], qfull[70:], other[87:]])
+    mixed = ops().paged_attention(mixed_q, case.cache,
+                                  case.meta([1, 0, 2], [(10, 87), (70, 80), (0, 40)]), d ** -0.5)
+    one = ops().paged_attention(qfull[149:150], case.cache, case.meta([0], [(149, 1)]), d ** -0.5)
+    if dtype == torch.float32:
+        assert torch.equal(part, whole[70:])
+        assert torch.equal(mixed[87:167], whole[70:])
+        assert torch.equal(one[0], whole[149])
+    else:
+        torch.testing.assert_close(part.float(), whole[70:].float(), **tol(dtype))
+        torch.testing.assert_close(mixed[87:167].float(), whole[70:].float(), **tol(dtype))
+        torch.testing.assert_close(one[0].float(), whole[149].float(), **tol(dtype))
+    # running it again gives the same bits in either dtype
+    again = ops().paged_attention(qfull, case.cache, case.meta([0], [(0, 150)]), d ** -0.5)
+    assert torch.equal(again, whole)
+
+
+# ------------------------------------------------------------------ sampling
+
+def test_argmax_lowest_index_on_ties():
+    logits = torch.zeros(3, 151936, device="cuda")
+    logits[0, 7] = 5.0
+    logits[1, 3] = 2.0
+    logits[1, 151935] = 2.0
+    logits[2, 151935] = 1.0
+    assert ops().argmax(logits).tolist() == [7, 3, 151935]
+    x = torch.randn(9, 1000, device="cuda")
+    assert ops().argmax(x).tolist() == torch.argmax(x, -1).tolist()
+
+
+def test_gumbel_sample_matches_formula():
+    torch.manual_seed(20)
+    r, v = 16, 5003
+    logits = 3 * torch.randn(r, v, device="cuda")
+    temps = torch.tensor([0.0, 0.8, 1.5, 0.3] * 4, device="cuda")
+    seeds = torch.arange(r, device="cuda", dtype=torch.int64) * 977 - 5
+    pos = torch.arange(100, 100 + r, device="cuda", dtype=torch.int64)
+    got = ops().gumbel_sample(logits, temps, seeds, pos)
+    scores = ref.gumbel_scores(logits, temps, seeds, pos)
+    want = ref.gumbel_sample(logits, temps, seeds, pos)
+    for i in range(r):
+        if got[i] != want[i]:      # only a near tie of the two scores may differ
+            assert abs(float(scores[i, got[i]] - scores[i, want[i]])) < 1e-4, (i, got[i], want[i])
+    assert (got == want).float().mean() > 0.9
+
+
+def test_gumbel_draw_independent_of_batch_and_depends_on_position():
+    torch.manual_seed(21)
+    row = torch.randn(1, 5000, device="cuda")
+    one = lambda lg, seeds, pos: ops().gumbel_sample(
+        lg, torch.full((lg.shape[0],), 0.8, device="cuda"),
+        torch.tensor(seeds, dtype=torch.int64, device="cuda"),
+        torch.tensor(pos, dtype=torch.int64, device="cuda"))
+    alone = one(row, [1234], [17])
+    for batch in (2, 7, 33):
+        lg = torch.cat([torch.randn(batch - 1, 5000, device="cuda"), row])
+        toks = one(lg, [1234] * batch, list(range(100, 100 + batch - 1)) + [17])
+        assert toks[-1] == alone[0]
+    same = torch.randn(1, 1000, device="cuda").repeat(64, 1)
+    assert len(set(one(same, [42] * 64, list(range(64))).tolist())) > 1
+
+
+def test_top_k_top_p_respected():
+    from deterministic_inference_b200.config import SamplingParams
+    from deterministic_inference_b200.sampling import sample
+    logits = torch.tensor([[10.0, 9.0, 8.0, -20.0, -20.0]], device="cuda")
+    for pos in range(100):
+        tok = sample(logits, [SamplingParams(temperature=2.0, seed=5, top_k=3)], [pos]).item()
+        assert tok in (0, 1, 2)
+    peaked = torch.tensor([[10.0, 0.0, 0.0, 0.0, 0.0]], device="cuda")
+    for pos in range(50):
+        assert sample(peaked, [SamplingParams(temperature=1.0, seed=5, top_p=0.5)], [pos]).item() == 0
+
+
+def test_no_cpu_path():
+    from deterministic_inference_b200.kernels.ops import KernelError
+    with pytest.raises(KernelError, match="CUDA"):
+        ops().rms_norm(torch.randn(2, 8), torch.ones(8), 1e-6)
