@@ -193,7 +193,7 @@ int launch_rms(void* x, void* res, const float* w, void* out, int rows, int H, f
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 200 * 1024) return DIB_BAD_SIZE;
   auto kern = rms_norm_kernel<T, ADD>;
-  if (smem > 48 * 1024) {
+  if (smem > 40 * 1024) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return DIB_LAUNCH_FAILED;

@@ -1,13 +1,68 @@
-"""bfloat16 tensor-core attention over the paged cache (prefill/extend and
-split-KV decode).  ``supports`` says whether the kernels take a shape; shapes
-they refuse run on the generic kernel."""
+"""bfloat16 tensor-core attention over the paged cache: the split-KV decode
+kernels for the batch's leading one-token sequences and the extend kernel for
+sequences that bring a portion of a prompt.  ``supports`` says whether the
+kernels take a shape; shapes they refuse run on the generic kernel.
+
+The decode kernel writes per-split partial outputs to scratch memory
+(``part_o`` float32 [sequences, heads, splits, head_dim] and ``part_lse``
+[sequences, heads, splits]) which its second stage merges in split order.
+"""
 
 from __future__ import annotations
 
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+SPLIT = 128        # keys per split of the decode kernel (fixed: the order of a
+                   # sequence's reduction depends on its own length only)
+TILE_ROWS = 64     # rows (token, head-of-group pairs) per tile of the extend kernel
+
 
 def supports(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
-    return False
+    group = num_heads // num_kv_heads
+    return head_dim % 16 == 0 and 16 <= head_dim <= 128 and group <= 16 and num_kv_heads <= 65535
+
+
+def extend_tiles(q_lens: list, first_seq: int, tokens_per_tile: int):
+    seqs, starts = [], []
+    for s in range(first_seq, len(q_lens)):
+        for t0 in range(0, q_lens[s], tokens_per_tile):
+            seqs.append(s)
+            starts.append(t0)
+    return seqs, starts
 
 
 def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
-    raise NotImplementedError
+    from .ops import _check, _lib, _ptr, _stream
+
+    lib = _lib("attention_bf16")
+    t, hq, d = q.shape
+    _, _, hkv, page_size, _ = kv_cache.shape
+    nd, b = meta.num_decode, len(meta.q_lens)
+    bt = meta.block_table
+    if nd > 0:
+        max_splits = max(1, -(-max(meta.kv_lens[:nd]) // SPLIT))
+        ws = meta.scratch.get(("decode_ws", hq, d, max_splits))
+        if ws is None:
+            ws = (torch.empty(nd, hq, max_splits, d, dtype=torch.float32, device=q.device),
+                  torch.empty(nd, hq, max_splits, dtype=torch.float32, device=q.device))
+            meta.scratch[("decode_ws", hq, d, max_splits)] = ws
+        st = lib.dib_decode_attention_bf16(
+            _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(bt), c_int(bt.shape[1]), _ptr(meta.seq_lens),
+            _ptr(ws[0]), _ptr(ws[1]), c_int(nd), c_int(max_splits), c_int(hq), c_int(hkv), c_int(d),
+            c_int(page_size), c_float(scale), c_int(window), _stream())
+        _check(st, "decode_attention_bf16", f"heads {hq}/{hkv}, head_dim {d}")
+    if b > nd:
+        tpt = TILE_ROWS // (hq // hkv)
+        tiles = meta.scratch.get(("extend_tiles", tpt))
+        if tiles is None:
+            seqs, starts = extend_tiles(meta.q_lens, nd, tpt)
+            both = torch.tensor([seqs, starts], dtype=torch.int32).to(q.device, non_blocking=True)
+            tiles = (both[0], both[1], len(seqs))
+            meta.scratch[("extend_tiles", tpt)] = tiles
+        st = lib.dib_extend_attention_bf16(
+            _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(bt), c_int(bt.shape[1]), _ptr(meta.cu_q_lens),
+            _ptr(meta.seq_lens), _ptr(tiles[0]), _ptr(tiles[1]), c_int(tiles[2]), c_int(hq),
+            c_int(hkv), c_int(d), c_int(page_size), c_float(scale), c_int(window), _stream())
+        _check(st, "extend_attention_bf16", f"heads {hq}/{hkv}, head_dim {d}")

@@ -56,15 +56,16 @@ def read_safetensors(path: Path) -> dict[str, torch.Tensor]:
     return out
 
 
-def read_model_dir(model_dir) -> tuple[dict, dict[str, torch.Tensor]]:
-    """config.json as a dict and all tensors upcast to float32
+def read_model_dir(model_dir, dtype=torch.float32) -> tuple[dict, dict[str, torch.Tensor]]:
+    """config.json as a dict and all tensors upcast to ``dtype`` (float32; float64
+    gives the reference value that float32 implementations are measured against)
     (sid/model/loader.py:30-55 for the keys, :64-68 for the files)."""
     model_dir = Path(model_dir)
     cfg = json.loads((model_dir / "config.json").read_text())
     tensors: dict[str, torch.Tensor] = {}
     for f in sorted(model_dir.glob("*.safetensors")):
         tensors.update(read_safetensors(f))
-    return cfg, {k: v.float() for k, v in tensors.items()}
+    return cfg, {k: v.to(dtype) for k, v in tensors.items()}
 
 
 # --------------------------------------------------------------------------
@@ -91,6 +92,7 @@ def apply_rope(x: torch.Tensor, angles: torch.Tensor) -> torch.Tensor:
     out = [x1 cos - x2 sin, x2 cos + x1 sin] (sid/kernels/rope.py:15-37).
     x: [T, heads, D]; angles: [T, D/2]."""
     half = x.shape[-1] // 2
+    angles = angles.to(x.dtype)          # the angle itself is always formed in float32
     cos = angles.cos()[:, None, :]
     sin = angles.sin()[:, None, :]
     x1, x2 = x[..., :half], x[..., half:]
@@ -98,13 +100,16 @@ def apply_rope(x: torch.Tensor, angles: torch.Tensor) -> torch.Tensor:
 
 
 def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
-              window: int | None = None) -> torch.Tensor:
+              window: int | None = None, rnd=None) -> torch.Tensor:
     """Causal grouped-query attention of one whole sequence.
     q: [T, Hq, D], k/v: [T, Hkv, D]; q head h reads kv head h // (Hq/Hkv);
     s = (q.k) * scale with the scale applied after the dot product; a query at
     position p sees keys 0..p; softmax and P.V in float32
     (sid/kernels/extend_attention.py:55,80-109; tests/conftest.py:11-32).
-    ``window`` (not in the reference): keys older than p-window+1 are masked."""
+    ``window`` (not in the reference): keys older than p-window+1 are masked.
+    ``rnd`` (bfloat16 storage emulation): the reference's prefill kernel rounds
+    the unnormalised probabilities exp(s - max) to bfloat16 before P.V and divides
+    by the float32 sum (sid/kernels/extend_attention.py:100-109)."""
     t, hq, d = q.shape
     hkv = k.shape[1]
     group = hq // hkv
@@ -117,17 +122,22 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
         kh = h // group
         s = (q[:, h] @ k[:, kh].T) * scale
         s = s.masked_fill(~visible, float("-inf"))
-        out[:, h] = torch.softmax(s, dim=-1) @ v[:, kh]
+        if rnd is None:
+            out[:, h] = torch.softmax(s, dim=-1) @ v[:, kh]
+        else:
+            e = torch.exp(s - s.max(dim=-1, keepdim=True).values)
+            out[:, h] = (rnd(e) @ v[:, kh]) / e.sum(dim=-1, keepdim=True)
     return out
 
 
 def swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor,
-           w_down: torch.Tensor) -> torch.Tensor:
+           w_down: torch.Tensor, rnd=None) -> torch.Tensor:
     """down( silu(gate(x)) * up(x) ), silu(z) = z * sigmoid(z), no biases
     (sid/model/qwen3.py:82-86)."""
-    g = x @ w_gate.T
-    u = x @ w_up.T
-    return ((g * torch.sigmoid(g)) * u) @ w_down.T
+    rnd = rnd or (lambda z: z)
+    g = rnd(x @ w_gate.T)
+    u = rnd(x @ w_up.T)
+    return rnd(rnd((g * torch.sigmoid(g)) * u) @ w_down.T)
 
 
 def layer_window(cfg: dict, layer: int) -> int | None:
@@ -141,7 +151,16 @@ def layer_window(cfg: dict, layer: int) -> int | None:
     return int(cfg["sliding_window"])
 
 
-def attention_block(h: torch.Tensor, cfg: dict, w: dict, layer: int) -> torch.Tensor:
+def _identity(x):
+    return x
+
+
+def round_bf16(x: torch.Tensor) -> torch.Tensor:
+    """What storing a float32 value as bfloat16 and reading it back gives."""
+    return x.to(torch.bfloat16).to(x.dtype)
+
+
+def attention_block(h: torch.Tensor, cfg: dict, w: dict, layer: int, rnd=_identity) -> torch.Tensor:
     """q/k/v projections without bias, per-head RMSNorm of q and k with one
     weight [D] shared by the heads and the layer norms' eps, then RoPE, then
     attention with scale D^-0.5, then the output projection
@@ -150,34 +169,47 @@ def attention_block(h: torch.Tensor, cfg: dict, w: dict, layer: int) -> torch.Te
     t = h.shape[0]
     hq, hkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     eps = cfg["rms_norm_eps"]
-    q = (h @ w[p + "q_proj.weight"].T).view(t, hq, d)
-    k = (h @ w[p + "k_proj.weight"].T).view(t, hkv, d)
-    v = (h @ w[p + "v_proj.weight"].T).view(t, hkv, d)
+    q = rnd(h @ w[p + "q_proj.weight"].T).view(t, hq, d)
+    k = rnd(h @ w[p + "k_proj.weight"].T).view(t, hkv, d)
+    v = rnd(h @ w[p + "v_proj.weight"].T).view(t, hkv, d)
     q = rms_norm(q, w[p + "q_norm.weight"], eps)
     k = rms_norm(k, w[p + "k_norm.weight"], eps)
     ang = rope_angles(torch.arange(t), d, cfg["rope_theta"])
-    q, k = apply_rope(q, ang), apply_rope(k, ang)
-    o = attention(q, k, v, d ** -0.5, layer_window(cfg, layer))
-    return o.reshape(t, hq * d) @ w[p + "o_proj.weight"].T
+    q, k = rnd(apply_rope(q, ang)), rnd(apply_rope(k, ang))
+    o = rnd(attention(q, k, v, d ** -0.5, layer_window(cfg, layer),
+                      None if rnd is _identity else rnd))
+    return rnd(o.reshape(t, hq * d) @ w[p + "o_proj.weight"].T)
 
 
-def forward(cfg: dict, w: dict, token_ids) -> torch.Tensor:
+def forward(cfg: dict, w: dict, token_ids, store_bf16: bool = False) -> torch.Tensor:
     """Logits [T, V] of one whole sequence.  Pre-norm residual stream: at each
     norm site the residual takes the block's output first and the norm reads
     the sum (sid/model/qwen3.py:88-115, sid/kernels/rmsnorm.py:27-42); final
     norm, then the head, which is the embedding when tie_word_embeddings
-    (sid/model/loader.py:74-82)."""
+    (sid/model/loader.py:74-82).
+
+    ``store_bf16``: all arithmetic stays float32, but every tensor the reference
+    stores in bfloat16 between two kernels (projection outputs, q and k after
+    norm and rotation, attention output, the gated product, norm outputs, the
+    residual: sid/model/qwen3.py:49-115, sid/kernels/rmsnorm.py:34-42) is rounded
+    to bfloat16 there.  The difference between the two modes is what rounding
+    alone does to this model; tests use it to tell rounding from faults."""
+    rnd = round_bf16 if store_bf16 else _identity
     ids = torch.as_tensor(token_ids, dtype=torch.long)
     eps = cfg["rms_norm_eps"]
     res = w["model.embed_tokens.weight"][ids]
+    h = rnd(rms_norm(res, w["model.layers.0.input_layernorm.weight"], eps))
     for i in range(cfg["num_hidden_layers"]):
         p = f"model.layers.{i}."
-        h = rms_norm(res, w[p + "input_layernorm.weight"], eps)
-        res = res + attention_block(h, cfg, w, i)
-        h = rms_norm(res, w[p + "post_attention_layernorm.weight"], eps)
-        res = res + swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
-                           w[p + "mlp.down_proj.weight"])
-    h = rms_norm(res, w["model.norm.weight"], eps)
+        s = res + attention_block(h, cfg, w, i, rnd)
+        h = rnd(rms_norm(s, w[p + "post_attention_layernorm.weight"], eps))   # reads the unrounded sum
+        res = rnd(s)                                                           # stored rounded
+        s = res + swiglu(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
+                         w[p + "mlp.down_proj.weight"], rnd)
+        nxt = (f"model.layers.{i + 1}.input_layernorm.weight"
+               if i + 1 < cfg["num_hidden_layers"] else "model.norm.weight")
+        h = rnd(rms_norm(s, w[nxt], eps))
+        res = rnd(s)
     head = (w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False)
             else w["lm_head.weight"])
     return h @ head.T
