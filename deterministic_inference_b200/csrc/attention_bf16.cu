@@ -461,10 +461,13 @@ int launch_extend(const void* q, void* out, const void* cache, const int* bt, in
                   int window, cudaStream_t st) {
   const size_t smem = (size_t)(EXT_M + 4 * EXT_N) * (D + PAD) * sizeof(__nv_bfloat16);
   auto kern = extend_attention_kernel<D>;
-  if (smem > 40 * 1024 &&
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-          cudaSuccess)
-    return DIB_LAUNCH_FAILED;
+  static bool attr_set = false;  // once per instantiation; never during a stream capture
+  if (!attr_set && smem > 40 * 1024) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return DIB_LAUNCH_FAILED;
+    attr_set = true;
+  }
   dim3 grid(num_tiles, Hkv);
   kern<<<grid, EXT_THREADS, smem, st>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,
                                         (const __nv_bfloat16*)cache, bt, max_blocks, cu_q_lens,
@@ -482,10 +485,13 @@ int launch_decode(const void* q, void* out, const void* cache, const int* bt, in
   const size_t merge = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
   if (merge > smem) smem = merge;
   auto kern = decode_attention_stage1_kernel<D>;
-  if (smem > 40 * 1024 &&
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-          cudaSuccess)
-    return DIB_LAUNCH_FAILED;
+  static bool attr_set = false;
+  if (!attr_set && smem > 40 * 1024) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return DIB_LAUNCH_FAILED;
+    attr_set = true;
+  }
   dim3 grid(Hkv, num_seqs, max_splits);
   kern<<<grid, DEC_THREADS, smem, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt,
                                         max_blocks, seq_lens, part_o, part_lse, max_splits, Hq, Hkv,

@@ -193,10 +193,12 @@ int launch_rms(void* x, void* res, const float* w, void* out, int rows, int H, f
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 200 * 1024) return DIB_BAD_SIZE;
   auto kern = rms_norm_kernel<T, ADD>;
-  if (smem > 40 * 1024) {
+  static size_t attr_smem = 0;  // raised when a wider row comes; never shrinks
+  if (smem > 40 * 1024 && smem > attr_smem) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return DIB_LAUNCH_FAILED;
+    attr_smem = smem;
   }
   int th = pick_threads(H);
   if (th > 512) th = 512;

@@ -74,6 +74,51 @@ def _align(n: int, a: int = 4) -> int:
     return (n + a - 1) // a * a
 
 
+class PackedLayout:
+    """Where each piece of a step's integer metadata lies in the one packed int32
+    array, for ``t`` tokens, ``b`` sequences, ``r`` logit rows and block tables
+    ``width`` pages wide in each of ``num_groups`` cache groups."""
+
+    def __init__(self, t: int, b: int, r: int, width: int, num_groups: int):
+        self.t, self.b, self.r, self.width, self.num_groups = t, b, r, width, num_groups
+        self.off = {}
+        cur = 0
+        for name, n in (("input_ids", t), ("positions", t), ("token_seq", t), ("cu_q_lens", b + 1),
+                        ("seq_lens", b), ("state_slots", b), ("logit_indices", r)):
+            self.off[name] = (cur, n)
+            cur = _align(cur + n)
+        for gi in range(num_groups):
+            self.off[("bt", gi)] = (cur, b * width)
+            cur = _align(cur + b * width)
+            self.off[("sm", gi)] = (cur, t)
+            cur = _align(cur + t)
+        self.size = max(cur, 1)
+
+    def seg(self, array, name):
+        s, n = self.off[name]
+        return array[s:s + n]
+
+
+def step_views(td: torch.Tensor, lay: PackedLayout, group_list: list, q_lens: list, kv_lens: list,
+               slots: list, num_decode: int, logit_rows: list, order: list) -> "StepBatch":
+    """A ``StepBatch`` whose tensors are views of the packed device array ``td``."""
+    b = lay.b
+    groups = {}
+    for gi, g in enumerate(group_list):
+        groups[g.key] = AttentionMeta(
+            block_table=lay.seg(td, ("bt", gi)).view(b, lay.width),
+            slot_mapping=lay.seg(td, ("sm", gi)), token_seq=lay.seg(td, "token_seq"),
+            positions=lay.seg(td, "positions"), cu_q_lens=lay.seg(td, "cu_q_lens"),
+            seq_lens=lay.seg(td, "seq_lens"), q_lens=q_lens, kv_lens=kv_lens, num_decode=num_decode)
+    return StepBatch(
+        num_tokens=lay.t, num_seqs=b, num_decode=num_decode, num_logits=lay.r,
+        input_ids=lay.seg(td, "input_ids"), positions=lay.seg(td, "positions"),
+        token_seq=lay.seg(td, "token_seq"), cu_q_lens=lay.seg(td, "cu_q_lens"),
+        seq_lens=lay.seg(td, "seq_lens"), state_slots=lay.seg(td, "state_slots"),
+        logit_indices=lay.seg(td, "logit_indices"), q_lens=q_lens, kv_lens=kv_lens, slots=slots,
+        groups=groups, logit_rows=logit_rows, order=order)
+
+
 def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatch:
     """Pack ``entries`` (``SequenceInput``; pages already allocated) into a
     ``StepBatch`` on ``device``."""
@@ -107,27 +152,11 @@ def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatc
 
     group_list = list(cache.page_groups.values())
     width = max(1, max(-(-kv // cache.page_size) for kv in kv_lens))
+    lay = PackedLayout(t, b, r, width, len(group_list))
+    host = np.zeros(lay.size, dtype=np.int32)
 
-    # layout of the packed int32 array
-    off = {}
-    cur = 0
-    for name, n in (("input_ids", t), ("positions", t), ("token_seq", t), ("cu_q_lens", b + 1),
-                    ("seq_lens", b), ("state_slots", b), ("logit_indices", r)):
-        off[name] = (cur, n)
-        cur = _align(cur + n)
-    for gi, g in enumerate(group_list):
-        off[("bt", gi)] = (cur, b * width)
-        cur = _align(cur + b * width)
-        off[("sm", gi)] = (cur, t)
-        cur = _align(cur + t)
-    host = np.zeros(max(cur, 1), dtype=np.int32)
-
-    def seg(name):
-        s, n = off[name]
-        return host[s:s + n]
-
-    ids, pos, tseq = seg("input_ids"), seg("positions"), seg("token_seq")
-    cu = seg("cu_q_lens")
+    ids, pos, tseq = lay.seg(host, "input_ids"), lay.seg(host, "positions"), lay.seg(host, "token_seq")
+    cu = lay.seg(host, "cu_q_lens")
     start = 0
     for bi, e in enumerate(seqs):
         q = q_lens[bi]
@@ -136,13 +165,13 @@ def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatc
         tseq[start:start + q] = bi
         cu[bi + 1] = start + q
         start += q
-    seg("seq_lens")[:] = kv_lens
+    lay.seg(host, "seq_lens")[:] = kv_lens
     slots = [e.slot for e in seqs]
-    seg("state_slots")[:] = slots
-    seg("logit_indices")[:] = logit_index
+    lay.seg(host, "state_slots")[:] = slots
+    lay.seg(host, "logit_indices")[:] = logit_index
     for gi, g in enumerate(group_list):
-        seg(("bt", gi))[:] = cache.block_table(g, slots, width).reshape(-1)
-        sm = seg(("sm", gi))
+        lay.seg(host, ("bt", gi))[:] = cache.block_table(g, slots, width).reshape(-1)
+        sm = lay.seg(host, ("sm", gi))
         start = 0
         for bi, e in enumerate(seqs):
             q = q_lens[bi]
@@ -157,20 +186,4 @@ def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatc
         td = th.to(dev, non_blocking=True)
     else:
         td = th
-
-    def dseg(name):
-        s, n = off[name]
-        return td[s:s + n]
-
-    groups = {}
-    for gi, g in enumerate(group_list):
-        groups[g.key] = AttentionMeta(
-            block_table=dseg(("bt", gi)).view(b, width), slot_mapping=dseg(("sm", gi)),
-            token_seq=dseg("token_seq"), positions=dseg("positions"), cu_q_lens=dseg("cu_q_lens"),
-            seq_lens=dseg("seq_lens"), q_lens=q_lens, kv_lens=kv_lens, num_decode=num_decode)
-    return StepBatch(
-        num_tokens=t, num_seqs=b, num_decode=num_decode, num_logits=r,
-        input_ids=dseg("input_ids"), positions=dseg("positions"), token_seq=dseg("token_seq"),
-        cu_q_lens=dseg("cu_q_lens"), seq_lens=dseg("seq_lens"), state_slots=dseg("state_slots"),
-        logit_indices=dseg("logit_indices"), q_lens=q_lens, kv_lens=kv_lens, slots=slots,
-        groups=groups, logit_rows=logit_rows, order=order)
+    return step_views(td, lay, group_list, q_lens, kv_lens, slots, num_decode, logit_rows, order)

@@ -1,19 +1,135 @@
-"""CUDA-graph replay of pure-decode steps (every sequence brings one token).
+"""CUDA-graph replay of pure-decode steps (every sequence brings one token and
+wants its logits).
 
-A decode step of a small model is bound by launch latency, not by the GPU; the
-step function's kernels for a batch-size bucket are captured once and replayed
-with the step's metadata copied into the captured buffers.
+A decode step of a small model is bound by launch latency, not by the GPU.  For
+a bucket of batch size and block-table width the step function is captured once:
+its kernels read the step's integer metadata from ONE static device array, so a
+later step only copies its packed metadata into that array (one host-to-device
+copy from pinned memory) and replays the graph.  Batches are padded to the
+bucket with sequences that live on the cache's page 0 and state slot 0, which no
+request owns.  Grid sizes that depend on sequence lengths are captured for the
+longest sequence the block-table width allows; blocks beyond a sequence's real
+length exit at once.
 """
 
 from __future__ import annotations
 
+import numpy as np
+import torch
+
+from .batch import PackedLayout, step_views
+
+
+def _bucket(n: int, smallest: int = 1) -> int:
+    b = smallest
+    while b < n:
+        b *= 2
+    return b
+
+
+class _Captured:
+    def __init__(self, graph, static_meta, host_meta, layout, logits):
+        self.graph, self.static_meta, self.host_meta = graph, static_meta, host_meta
+        self.layout, self.logits = layout, logits
+
 
 class DecodeGraphs:
-    def __init__(self, runner):
+    def __init__(self, runner, max_batch: int = 256, min_width: int = 8):
         self.runner = runner
+        self.cache = runner.cache
+        self.max_batch = max_batch
+        self.min_width = min_width
+        self.graphs: dict[tuple, _Captured] = {}
+        self.group_list = list(self.cache.page_groups.values())
+        self.replays = 0
+        self.kernels_per_graph: dict[tuple, int] = {}
 
     def usable(self, entries) -> bool:
-        return False
+        return (0 < len(entries) <= self.max_batch
+                and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
 
+    # ---- capture ---------------------------------------------------------------
+
+    def _key(self, entries) -> tuple:
+        ps = self.cache.page_size
+        width = max(-(-(e.num_computed + 1) // ps) for e in entries)
+        return (_bucket(len(entries)), min(_bucket(width, self.min_width), self.cache.max_blocks))
+
+    def _fill(self, host: np.ndarray, lay: PackedLayout, entries) -> None:
+        """Packed metadata of a pure-decode step, padded to the bucket."""
+        n, bb, w = len(entries), lay.b, lay.width
+        host[:] = 0
+        ids, pos = lay.seg(host, "input_ids"), lay.seg(host, "positions")
+        lay.seg(host, "token_seq")[:] = np.arange(bb)
+        lay.seg(host, "cu_q_lens")[:] = np.arange(bb + 1)
+        lay.seg(host, "logit_indices")[:] = np.arange(bb)
+        seq_lens = lay.seg(host, "seq_lens")
+        seq_lens[:] = 1
+        slots = lay.seg(host, "state_slots")
+        for i, e in enumerate(entries):
+            ids[i] = e.tokens[0]
+            pos[i] = e.num_computed
+            seq_lens[i] = e.num_computed + 1
+            slots[i] = e.slot
+        for gi, g in enumerate(self.group_list):
+            bt = lay.seg(host, ("bt", gi)).reshape(bb, w)
+            sm = lay.seg(host, ("sm", gi))
+            for i, e in enumerate(entries):
+                pl = g.pages[e.slot]
+                m = min(len(pl), w)
+                bt[i, :m] = pl[:m]
+                sm[i] = pl[e.num_computed // g.page_size] * g.page_size + e.num_computed % g.page_size
+
+    def _capture(self, key: tuple, entries) -> _Captured:
+        bb, w = key
+        dev = self.runner.device
+        lay = PackedLayout(bb, bb, bb, w, len(self.group_list))
+        host = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
+        static = torch.zeros(lay.size, dtype=torch.int32, device=dev)
+        upper = w * self.cache.page_size
+        batch = step_views(static, lay, self.group_list, [1] * bb, [upper] * bb, [0] * bb, bb,
+                           [[i] for i in range(bb)], list(range(bb)))
+        self._fill(host.numpy(), lay, entries)
+        static.copy_(host, non_blocking=True)
+        # warm up on a side stream (library handles, lazy module loading), then capture
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.runner.model.forward(batch, self.cache)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        from ..kernels import ops
+        n0 = ops.launch_count
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.runner.model.forward(batch, self.cache)
+        self.kernels_per_graph[key] = ops.launch_count - n0
+        cap = _Captured(graph, static, host, lay, logits)
+        self.graphs[key] = cap
+        return cap
+
+    # ---- replay -------------------------------------------------------------------
+
+    @torch.inference_mode()
     def run(self, entries):
-        raise NotImplementedError
+        """Same contract as ``ModelRunner.step`` for a pure-decode batch: returns
+        (logits [B, V], rows per entry)."""
+        cache = self.cache
+        for e in entries:
+            cache.allocate(e.slot, e.num_computed + 1)
+        cache.reset_fresh_state()
+        key = self._key(entries)
+        cap = self.graphs.get(key)
+        if cap is None:
+            cap = self._capture(key, entries)
+        self._fill(cap.host_meta.numpy(), cap.layout, entries)
+        cap.static_meta.copy_(cap.host_meta, non_blocking=True)
+        cap.graph.replay()
+        for e in entries:
+            cache.release_passed(e.slot, e.num_computed + 1)
+        self.replays += 1
+        self.runner.steps_run += 1
+        self.runner.tokens_run += len(entries)
+        n = len(entries)
+        return cap.logits[:n], [[i] for i in range(n)]

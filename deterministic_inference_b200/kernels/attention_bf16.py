@@ -52,7 +52,7 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
             _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(bt), c_int(bt.shape[1]), _ptr(meta.seq_lens),
             _ptr(ws[0]), _ptr(ws[1]), c_int(nd), c_int(max_splits), c_int(hq), c_int(hkv), c_int(d),
             c_int(page_size), c_float(scale), c_int(window), _stream())
-        _check(st, "decode_attention_bf16", f"heads {hq}/{hkv}, head_dim {d}")
+        _check(st, "decode_attention_bf16", f"heads {hq}/{hkv}, head_dim {d}", kernels=2)
     if b > nd:
         tpt = TILE_ROWS // (hq // hkv)
         tiles = meta.scratch.get(("extend_tiles", tpt))

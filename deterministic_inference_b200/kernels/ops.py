@@ -47,7 +47,9 @@ def _stream():
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
-def _check(status: int, what: str, detail: str = ""):
+def _check(status: int, what: str, detail: str = "", kernels: int = 1):
+    global launch_count
+    launch_count += kernels
     if status != 0:
         raise KernelError(f"{what}: {_STATUS.get(status, status)}{(' — ' + detail) if detail else ''}")
 
@@ -72,6 +74,15 @@ def _dt(t: torch.Tensor, name: str) -> int:
 
 
 _libs: dict[str, ctypes.CDLL] = {}
+
+# Kernels launched by this module since import (this package's own kernels plus
+# the library matrix products it calls); benchmarks read differences of it.
+launch_count = 0
+
+
+def _launched(n: int = 1) -> None:
+    global launch_count
+    launch_count += n
 
 
 def _lib(name: str) -> ctypes.CDLL:
