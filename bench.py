@@ -141,6 +141,10 @@ def main() -> int:
     ap.add_argument("--points", default="1,64", help="extra decode batch sizes")
     ap.add_argument("--point-steps", type=int, default=64)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
+                    help="bracket this region with cudaProfilerStart/Stop (for ncu "
+                         "--profile-from-start off); the numbers of such a run are not a result")
     a = ap.parse_args()
 
     if a.impl == "reference":
@@ -193,14 +197,20 @@ def main() -> int:
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > L2
     prompt = random_prompt(a.prefill_tokens)
     prefill_ms = []
-    for it in range(3 + 3):
+    reps = (0 if a.no_prefill else 3 + 3) if a.profile != "prefill" else 3 + 1
+    for it in range(reps):
         slot = cache.allocate_slot()
         flush.zero_()
+        if a.profile == "prefill" and it == reps - 1:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
         ms = timed(lambda: runner.step([SequenceInput(slot, prompt, 0, [len(prompt) - 1])]))
+        if a.profile == "prefill" and it == reps - 1:
+            torch.cuda.profiler.stop()
         cache.release_slot(slot)
         if it >= 3:
             prefill_ms.append(ms)
-    prefill_ms = sorted(prefill_ms)[len(prefill_ms) // 2]
+    prefill_ms = sorted(prefill_ms)[len(prefill_ms) // 2] if prefill_ms else float("nan")
     _, prefill_flops = model_bytes_and_flops(cfg, layers, 1, 0, a.prefill_tokens)
     prefill = {"value": a.prefill_tokens / (prefill_ms / 1e3), "tokens": a.prefill_tokens,
                "ms": prefill_ms,
@@ -243,7 +253,12 @@ def main() -> int:
         if sample_clocks:
             sampler.start()
         n0 = ops.launch_count
+        if a.profile == "decode" and sample_clocks:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
         ms = timed(lambda: [one(k) for k in range(warmup, total)])
+        if a.profile == "decode" and sample_clocks:
+            torch.cuda.profiler.stop()
         per_graph = graphs.kernels_per_graph.get(key, 0)
         launches = steps * (per_graph + 2) + (ops.launch_count - n0)
         clocks = sampler.stop() if sample_clocks else None

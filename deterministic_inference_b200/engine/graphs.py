@@ -28,9 +28,13 @@ def _bucket(n: int, smallest: int = 1) -> int:
 
 
 class _Captured:
-    def __init__(self, graph, static_meta, host_meta, layout, logits):
+    """A captured step.  ``batch`` is kept because the captured kernels use what it
+    holds: the views of ``static_meta`` and the scratch memory kernels attached to
+    it during the warm-up runs (the decode attention's split workspace)."""
+
+    def __init__(self, graph, static_meta, host_meta, layout, logits, batch):
         self.graph, self.static_meta, self.host_meta = graph, static_meta, host_meta
-        self.layout, self.logits = layout, logits
+        self.layout, self.logits, self.batch = layout, logits, batch
 
 
 class DecodeGraphs:
@@ -105,7 +109,7 @@ class DecodeGraphs:
         with torch.cuda.graph(graph):
             logits = self.runner.model.forward(batch, self.cache)
         self.kernels_per_graph[key] = ops.launch_count - n0
-        cap = _Captured(graph, static, host, lay, logits)
+        cap = _Captured(graph, static, host, lay, logits, batch)
         self.graphs[key] = cap
         return cap
 
