@@ -38,6 +38,10 @@ SOURCES = {
     "gemm_bf16": "gemm_bf16.cu",
 }
 HEADERS = ("common.cuh",)
+# further headers a library includes
+EXTRA_HEADERS = {
+    "attention_bf16": ("attention_bf16_kernels.cuh",),
+}
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -95,7 +99,7 @@ def _pick_build_dir() -> Path:
 
 def _digest(name: str) -> str:
     h = hashlib.sha256()
-    for f in (SOURCES[name],) + HEADERS:
+    for f in (SOURCES[name],) + HEADERS + EXTRA_HEADERS.get(name, ()):
         h.update((CSRC / f).read_bytes())
     h.update(" ".join(NVCC_FLAGS + EXTRA_FLAGS.get(name, [])).encode())
     return h.hexdigest()[:16]
