@@ -36,11 +36,13 @@ SOURCES = {
     "attention_generic": "attention_generic.cu",
     "attention_bf16": "attention_bf16.cu",
     "gemm_bf16": "gemm_bf16.cu",
+    "decode_attention_noalloc": "decode_attention_noalloc.cu",
 }
 HEADERS = ("common.cuh",)
 # further headers a library includes
 EXTRA_HEADERS = {
     "attention_bf16": ("attention_bf16_kernels.cuh",),
+    "decode_attention_noalloc": ("attention_bf16_kernels.cuh", "decode_attention_noalloc.h"),
 }
 
 NVCC_FLAGS = [
