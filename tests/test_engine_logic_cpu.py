@@ -1,0 +1,110 @@
+"""The engine's host logic (cache manager, batch packing, step function, scheduler,
+entry point) on a machine without a GPU: the kernel wrappers are replaced by their
+plain PyTorch restatements (fixture ``torch_ops``), everything else is the product
+code.  Logits and tokens are compared with the plain implementation under every
+cutting.  The GPU tests repeat this with the real kernels."""
+
+import pytest
+import torch
+
+from deterministic_inference_b200.config import EngineConfig, SamplingParams
+from deterministic_inference_b200.engine import Engine, ModelRunner, SequenceInput
+from tests import plain_qwen3
+from tests.conftest import TINY
+
+
+def runner_for(model_dir, page, pool=512, **kw):
+    return ModelRunner(EngineConfig(model_path=str(model_dir), dtype="float32", device="cpu",
+                                    kv_pool_tokens=pool, page_size=page, max_reqs=8,
+                                    max_seq_len=512, **kw))
+
+
+@pytest.mark.parametrize("name", ["a", "bw", "c"])
+def test_cuttings_on_cpu(name, tiny_model_dirs, torch_ops):
+    d = tiny_model_dirs[name]
+    cfg, w = plain_qwen3.read_model_dir(d)
+    g = torch.Generator().manual_seed(2)
+    toks = torch.randint(0, cfg["vocab_size"], (75,), generator=g).tolist()
+    other = torch.randint(0, cfg["vocab_size"], (40,), generator=g).tolist()
+    ref, ref_other = plain_qwen3.forward(cfg, w, toks), plain_qwen3.forward(cfg, w, other)
+    r = runner_for(d, TINY[name]["page_size"], pool=192)
+    tol = dict(atol=2e-5, rtol=1e-4)
+
+    # whole, wanting a subset of places
+    s = r.cache.allocate_slot()
+    logits, _ = r.step([SequenceInput(s, toks, 0, [0, 5, 74])])
+    torch.testing.assert_close(logits, ref[[0, 5, 74]], **tol)
+    r.cache.release_slot(s)
+
+    # portions of changing size beside another request that decodes token by token
+    s, o = r.cache.allocate_slot(), r.cache.allocate_slot()
+    r.step([SequenceInput(o, other[:20], 0, [])])
+    c, oc = 0, 20
+    for n in (13, 2, 7, 2, 30, 5, 16):
+        entries = [SequenceInput(s, toks[c:c + n], c, list(range(n)))]
+        if oc < len(other):
+            entries.insert(0, SequenceInput(o, other[oc:oc + 1], oc, [0]))
+        logits, batch = r.step(entries)
+        rows = batch.logit_rows
+        torch.testing.assert_close(logits[rows[-1]], ref[c:c + n], **tol)
+        if len(entries) == 2:
+            torch.testing.assert_close(logits[rows[0]], ref_other[oc:oc + 1], **tol)
+            oc += 1
+        c += n
+    assert c == 75
+    r.cache.release_slot(s)
+    r.cache.release_slot(o)
+    r.cache.check_invariants()
+
+
+def test_entry_point_matches_plain_generation(tiny_model_dirs, torch_ops):
+    d = tiny_model_dirs["a"]
+    cfg, w = plain_qwen3.read_model_dir(d)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 255, (n,), generator=g).tolist() for n in (5, 17, 33)]
+    for temp, kw in ((0.0, {}), (0.8, dict(top_k=20, top_p=0.9))):
+        sp = SamplingParams(temperature=temp, seed=7, max_new_tokens=8, ignore_eos=True, **kw)
+        want = [plain_qwen3.generate(cfg, w, p, 8, temp, 7, **kw) for p in prompts]
+        for ekw in (dict(kv_pool_tokens=1024), dict(kv_pool_tokens=1024, max_prefill_tokens=8),
+                    dict(kv_pool_tokens=64, max_prefill_tokens=16)):
+            eng = Engine(EngineConfig(model_path=str(d), dtype="float32", device="cpu", page_size=16,
+                                      max_reqs=8, max_seq_len=256, **ekw))
+            outs = eng.generate(prompts, sp)
+            assert [o.token_ids for o in outs] == want, (temp, ekw)
+            assert [o.finish_reason for o in outs] == ["length"] * 3
+            eng.cache.check_invariants()
+            assert eng.cache.num_free_pages() == eng.cache.usable_pages()
+
+
+def test_eos_ends_a_request(tiny_model_dirs, torch_ops):
+    d = tiny_model_dirs["a"]
+    cfg, w = plain_qwen3.read_model_dir(d)
+    prompt = [3, 1, 4, 1, 5]
+    free = plain_qwen3.generate(cfg, w, prompt, 6)
+    eng = Engine(EngineConfig(model_path=str(d), dtype="float32", device="cpu", kv_pool_tokens=256,
+                              max_reqs=4, max_seq_len=256))
+    out = eng.generate([prompt], SamplingParams(max_new_tokens=6, stop_token_ids=[free[2]]))[0]
+    assert out.token_ids == free[:3] and out.finish_reason == "stop"
+
+
+def test_add_request_refuses_what_can_never_run(tiny_model_dirs, torch_ops):
+    eng = Engine(EngineConfig(model_path=str(tiny_model_dirs["a"]), dtype="float32", device="cpu",
+                              kv_pool_tokens=64, max_reqs=4, max_seq_len=128))
+    with pytest.raises(ValueError, match="cache pool"):
+        eng.add_request(prompt_ids=[1] * 60, params=SamplingParams(max_new_tokens=10))
+    with pytest.raises(ValueError, match="position limit"):
+        eng.add_request(prompt_ids=[1] * 10, params=SamplingParams(max_new_tokens=200))
+    with pytest.raises(ValueError, match="vocabulary"):
+        eng.add_request(prompt_ids=[1, 999])
+    with pytest.raises(ValueError, match="empty"):
+        eng.add_request(prompt_ids=[])
+
+
+def test_no_cpu_path_in_the_product():
+    """Without the test's stand-ins the engine refuses CPU tensors loudly."""
+    from deterministic_inference_b200.kernels import ops
+    from deterministic_inference_b200.kernels.ops import KernelError
+    with pytest.raises(KernelError, match="no CPU path"):
+        ops.rms_norm(torch.randn(2, 8), torch.ones(8), 1e-6)
+    with pytest.raises(KernelError, match="no CPU path"):
+        ops.linear(torch.randn(2, 8), torch.randn(4, 8))
