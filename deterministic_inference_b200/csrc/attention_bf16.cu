@@ -5,6 +5,14 @@
 extern "C" {
 
 int dib_attention_bf16_split_size() { return DEC_SPLIT; }
+
+// 0, or 1 if a bounded wait inside a kernel of this library ever ran out (the
+// results of that launch are then not valid).  Synchronises with the device.
+int dib_attention_bf16_status() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, dib_attention_error_word, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
 int dib_attention_bf16_tile_rows() { return EXT_M; }
 
 // Sequences with more than one new token.  q/out are the step's full [T, Hq, D]

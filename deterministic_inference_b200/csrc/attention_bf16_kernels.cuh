@@ -36,6 +36,53 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
 }
 
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ---- mbarrier + bulk copy (global -> shared, completion counted in bytes)
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes,
+                                         unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+// Wait for a phase of the barrier with a bound: after ~2^20 polls (each poll may
+// itself block for a while in hardware) the wait gives up and reports false.
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+  for (int i = 0; i < (1 << 20); ++i) {
+    unsigned ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; "
+        "selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+// Set when a bounded wait ran out; read by dib_attention_bf16_status().
+__device__ int dib_attention_error_word = 0;
+
 __device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(p);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -164,7 +211,7 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NK / 8][4], float (&o)[D
     mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
     const float mnew = fmaxf(mrow[rr], mx[rr]);
     msafe[rr] = mnew <= -1e29f ? 0.f : mnew;  // nothing visible yet: exponentials become 0
-    alpha[rr] = exp2f(mrow[rr] - msafe[rr]);
+    alpha[rr] = fast_exp2(mrow[rr] - msafe[rr]);
     mrow[rr] = mnew;
   }
   float sum[2] = {0.f, 0.f};
@@ -172,7 +219,7 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NK / 8][4], float (&o)[D
   for (int nt = 0; nt < NK / 8; ++nt)
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float e = exp2f(s[nt][i] - msafe[i >> 1]);
+      const float e = fast_exp2(s[nt][i] - msafe[i >> 1]);
       s[nt][i] = e;
       sum[i >> 1] += e;
     }
@@ -208,7 +255,8 @@ extend_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
   constexpr int TILE_ELEMS = EXT_N * (D + PAD);
   // stage s: K at sK0 + s*2*TILE_ELEMS, V right behind it
 
-  const int tile = blockIdx.x, kvh = blockIdx.y;
+  // tiles are listed in order of position; the ones with the most keys run first
+  const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
   const int G = Hq / Hkv;
   const int tokens_per_tile = EXT_M / G;
   const int seq = tile_seq[tile];
@@ -336,26 +384,44 @@ decode_attention_stage1_kernel(const __nv_bfloat16* __restrict__ q,
   const int* bt = block_table + (size_t)b * max_blocks;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // K and V of the split as two groups, so the scores can start while V arrives
+  // K and V rows of the split by bulk copies: thread r owns key k0 + r and issues
+  // one copy for its K row and one for its V row (the keys of a head inside a page
+  // are contiguous, so a row is D*2 contiguous bytes).  Two barriers count the
+  // bytes, so the scores can start while V is still arriving.  Rows at or beyond
+  // the sequence's length are zero-filled by their thread.
+  static_assert(DEC_THREADS == DEC_SPLIT, "one thread per key row");
+  unsigned long long* bars =
+      reinterpret_cast<unsigned long long*>(smem_raw + (size_t)2 * DEC_SPLIT * (D + PAD) * 2);
+  if (threadIdx.x == 0) {
+    mbar_init(&bars[0], 1);
+    mbar_init(&bars[1], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
   {
-    constexpr int CH = D / 8;
-    const size_t head_stride = (size_t)page_size * D;
-    const size_t kv_stride = (size_t)Hkv * head_stride;
-    for (int pass = 0; pass < 2; ++pass) {
-      __nv_bfloat16* dstbase = pass == 0 ? sK : sV;
-      for (int c = threadIdx.x; c < DEC_SPLIT * CH; c += DEC_THREADS) {
-        const int r = c / CH, ch = c % CH;
-        const int key = k0 + r;
-        const bool valid = key < kv_len;
-        const __nv_bfloat16* src = cache;
-        if (valid) {
-          const int page = bt[key / page_size];
-          src = cache + (size_t)page * 2 * kv_stride + (size_t)pass * kv_stride +
-                (size_t)kvh * head_stride + (size_t)(key % page_size) * D + ch * 8;
-        }
-        cp_async16(dstbase + r * (D + PAD) + ch * 8, src, valid);
+    const int nvalid = min(DEC_SPLIT, kv_len - k0);
+    if (threadIdx.x == 0) {
+      mbar_expect_tx(&bars[0], (unsigned)nvalid * D * 2);
+      mbar_expect_tx(&bars[1], (unsigned)nvalid * D * 2);
+    }
+    const int r = threadIdx.x;
+    __nv_bfloat16* dk = sK + r * (D + PAD);
+    __nv_bfloat16* dv = sV + r * (D + PAD);
+    if (r < nvalid) {
+      const int key = k0 + r;
+      const size_t head_stride = (size_t)page_size * D;
+      const size_t kv_stride = (size_t)Hkv * head_stride;
+      const int page = bt[key / page_size];
+      const __nv_bfloat16* src = cache + (size_t)page * 2 * kv_stride + (size_t)kvh * head_stride +
+                                 (size_t)(key % page_size) * D;
+      bulk_g2s(dk, src, D * 2, &bars[0]);
+      bulk_g2s(dv, src + kv_stride, D * 2, &bars[1]);
+    } else {
+#pragma unroll
+      for (int c = 0; c < D / 8; ++c) {
+        *reinterpret_cast<uint4*>(dk + c * 8) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dv + c * 8) = make_uint4(0, 0, 0, 0);
       }
-      cp_async_commit();
     }
   }
 
@@ -382,14 +448,13 @@ decode_attention_stage1_kernel(const __nv_bfloat16* __restrict__ q,
     for (int i = 0; i < 4; ++i) o[dt][i] = 0.f;
   float mrow[2] = {NEG_BIG, NEG_BIG}, lrow[2] = {0.f, 0.f};
 
-  cp_async_wait<1>();
-  __syncthreads();
+  __syncthreads();  // zero-filled rows are visible
+  if (!mbar_wait(&bars[0], 0)) atomicExch(&dib_attention_error_word, 1);
   float s[DEC_WARP_KEYS / 8][4];
   qk_tile<D, DEC_WARP_KEYS>(s, qf, sK, warp * DEC_WARP_KEYS, lane);
   softmax_tile<D, DEC_WARP_KEYS>(s, o, mrow, lrow, k0 + warp * DEC_WARP_KEYS, lo, hi,
                                  scale * LOG2E, lane);
-  cp_async_wait<0>();
-  __syncthreads();
+  if (!mbar_wait(&bars[1], 0)) atomicExch(&dib_attention_error_word, 1);
   pv_tile<D, DEC_WARP_KEYS>(o, s, sV, warp * DEC_WARP_KEYS, lane);
   __syncthreads();  // sK is reused for the merge
 
@@ -412,21 +477,31 @@ decode_attention_stage1_kernel(const __nv_bfloat16* __restrict__ q,
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += DEC_THREADS) {
-    const int r = idx / D, d = idx % D;
+  // per row: the common maximum, each warp's factor (kept in sM) and 1/L (in sL[0])
+  if (threadIdx.x < G) {
+    const int r = threadIdx.x;
     float M = NEG_BIG;
 #pragma unroll
     for (int w = 0; w < 4; ++w) M = fmaxf(M, sM[w * 16 + r]);
-    float L = 0.f, acc = 0.f;
+    float L = 0.f;
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
-      const float f = exp2f(sM[w * 16 + r] - M);
+      const float f = fast_exp2(sM[w * 16 + r] - M);
       L += sL[w * 16 + r] * f;
-      acc += sO[(w * 16 + r) * D + d] * f;
+      sM[w * 16 + r] = f;
     }
+    sL[r] = 1.0f / L;
     const size_t row = ((size_t)b * Hq + (size_t)kvh * G + r) * max_splits + split;
-    part_o[row * D + d] = acc / L;
-    if (d == 0) part_lse[row] = (M + log2f(L)) / LOG2E;  // natural-log domain
+    part_lse[row] = (M + log2f(L)) / LOG2E;  // natural-log domain
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += DEC_THREADS) {
+    const int r = idx / D, d = idx % D;
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) acc += sO[(w * 16 + r) * D + d] * sM[w * 16 + r];
+    const size_t row = ((size_t)b * Hq + (size_t)kvh * G + r) * max_splits + split;
+    part_o[row * D + d] = acc * sL[r];
   }
 }
 
@@ -482,7 +557,7 @@ template <int D>
 int launch_decode(const void* q, void* out, const void* cache, const int* bt, int max_blocks,
                   const int* seq_lens, float* part_o, float* part_lse, int num_seqs, int max_splits,
                   int Hq, int Hkv, int page_size, float scale, int window, cudaStream_t st) {
-  size_t smem = (size_t)2 * DEC_SPLIT * (D + PAD) * sizeof(__nv_bfloat16);
+  size_t smem = (size_t)2 * DEC_SPLIT * (D + PAD) * sizeof(__nv_bfloat16) + 16;  // + 2 barriers
   const size_t merge = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
   if (merge > smem) smem = merge;
   auto kern = decode_attention_stage1_kernel<D>;

@@ -56,6 +56,85 @@ __global__ void rms_norm_kernel(T* __restrict__ x, T* __restrict__ residual,
   }
 }
 
+// Vector path of the same kernel: 16-byte loads, the row kept in registers.  Used
+// when the row width is a multiple of the vector width and fits ITERS passes.
+template <typename T> struct Vec;
+template <> struct Vec<float> {
+  static constexpr int N = 4;
+  static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+    const float4 x = *reinterpret_cast<const float4*>(p);
+    v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct Vec<__nv_bfloat16> {
+  static constexpr int N = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 x = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 x;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&x);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = x;
+  }
+};
+
+template <typename T, bool ADD, int ITERS>
+__global__ void rms_norm_vec_kernel(T* __restrict__ x, T* __restrict__ residual,
+                                    const float* __restrict__ w, T* __restrict__ out, int H,
+                                    float eps) {
+  constexpr int N = Vec<T>::N;
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * H;
+  float v[ITERS][N];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = (it * blockDim.x + threadIdx.x) * N;
+    if (i < H) {
+      Vec<T>::load(x + base + i, v[it]);
+      if (ADD) {
+        float r[N];
+        Vec<T>::load(residual + base + i, r);
+#pragma unroll
+        for (int k = 0; k < N; ++k) v[it][k] += r[k];
+        Vec<T>::store(residual + base + i, v[it]);
+      }
+#pragma unroll
+      for (int k = 0; k < N; ++k) ss += v[it][k] * v[it][k];
+    }
+  }
+  const float total = block_sum(ss, scratch);
+  const float rstd = 1.0f / sqrtf(total / (float)H + eps);
+  T* dst = ADD ? x : out;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = (it * blockDim.x + threadIdx.x) * N;
+    if (i < H) {
+      float y[N];
+#pragma unroll
+      for (int k = 0; k < N; k += 4) {
+        const float4 ww = *reinterpret_cast<const float4*>(w + i + k);
+        y[k] = v[it][k] * rstd * ww.x;
+        y[k + 1] = v[it][k + 1] * rstd * ww.y;
+        y[k + 2] = v[it][k + 2] * rstd * ww.z;
+        y[k + 3] = v[it][k + 3] * rstd * ww.w;
+      }
+      Vec<T>::store(dst + base + i, y);
+    }
+  }
+}
+
 // ------------------------------------------- q/k norm + rotary + cache write
 // One warp per (token, head) of the fused qkv row.  Heads 0..Hq-1 are queries
 // (written to q_out), then Hkv key heads, then Hkv value heads (written to the
@@ -133,6 +212,82 @@ __global__ void qk_norm_rope_cache_kernel(
   }
 }
 
+// Vector path of the kernel above for head sizes that are multiples of 64 with a
+// rotation over the whole head (or none): each lane owns EPL = D/32 contiguous
+// elements, so the partner of a rotation pair (d, d + D/2) sits in lane ^ 16 and
+// nothing goes through shared memory.
+template <typename T, int EPL>
+struct alignas((sizeof(T) * EPL) <= 16 ? (sizeof(T) * EPL) : 16) Pack {
+  T e[EPL];
+};
+
+template <typename T, int EPL>
+__global__ void qk_norm_rope_cache_vec_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ kv_cache,
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+    const float* __restrict__ cos_sin, int max_pos, const int* __restrict__ positions,
+    const int* __restrict__ slot_mapping, int T_tokens, int Hq, int Hkv, int page_size,
+    long long num_pages) {
+  constexpr int D = EPL * 32;
+  const int warps_per_block = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = Hq + 2 * Hkv;
+  const long long item = (long long)blockIdx.x * warps_per_block + warp;
+  if (item >= (long long)T_tokens * heads) return;
+  const int t = (int)(item / heads);
+  const int head = (int)(item % heads);
+  const bool is_q = head < Hq;
+  const bool is_k = !is_q && head < Hq + Hkv;
+  const float* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+
+  T* dst = nullptr;
+  if (is_q) {
+    dst = q_out + ((size_t)t * Hq + head) * D;
+  } else {
+    if (kv_cache == nullptr) return;
+    const int slot = slot_mapping[t];
+    if (slot < 0) return;
+    const long long page = slot / page_size;
+    if (page >= num_pages) return;
+    const int off = slot % page_size;
+    const int kv = is_k ? 0 : 1;
+    const int h = is_k ? head - Hq : head - Hq - Hkv;
+    dst = kv_cache + ((((size_t)page * 2 + kv) * Hkv + h) * page_size + off) * D;
+  }
+  const T* src = qkv + ((size_t)t * heads + head) * D + lane * EPL;
+  const Pack<T, EPL> in = *reinterpret_cast<const Pack<T, EPL>*>(src);
+  float v[EPL];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < EPL; ++k) {
+    v[k] = Elem<T>::load(&in.e[k]);
+    ss += v[k] * v[k];
+  }
+  if (nw != nullptr) {
+    ss = warp_sum(ss);
+    const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) v[k] = v[k] * rstd * nw[lane * EPL + k];
+  }
+  if (cos_sin != nullptr && (is_q || is_k)) {
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* tab = cos_sin + (size_t)pos * D;
+    const int j0 = (lane & 15) * EPL;
+    const bool upper = lane >= 16;
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) {
+      const float partner = __shfl_xor_sync(0xffffffffu, v[k], 16);
+      const float c = tab[j0 + k], sn = tab[D / 2 + j0 + k];
+      v[k] = upper ? (v[k] * c + partner * sn) : (v[k] * c - partner * sn);
+    }
+  }
+  Pack<T, EPL> o;
+#pragma unroll
+  for (int k = 0; k < EPL; ++k) Elem<T>::store(&o.e[k], v[k]);
+  *reinterpret_cast<Pack<T, EPL>*>(dst + lane * EPL) = o;
+}
+
 // ------------------------------------------------ standalone cache write
 // k, v: [T, Hkv, D] -> the page slot of each token (slot < 0: skipped).
 template <typename T>
@@ -170,6 +325,23 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
   Elem<T>::store(out + idx, sg * u);
 }
 
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, long long vecs,
+                                    int I) {
+  constexpr int N = Vec<T>::N;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= vecs) return;
+  const int per_row = I / N;
+  const long long t = idx / per_row;
+  const int i = (int)(idx % per_row) * N;
+  float g[N], u[N], y[N];
+  Vec<T>::load(gu + t * 2 * I + i, g);
+  Vec<T>::load(gu + t * 2 * I + I + i, u);
+#pragma unroll
+  for (int k = 0; k < N; ++k) y[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
+  Vec<T>::store(out + t * I + i, y);
+}
+
 // ---------------------------------------------------------------- row gather
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ idx,
@@ -190,6 +362,25 @@ int pick_threads(int n) {
 template <typename T, bool ADD>
 int launch_rms(void* x, void* res, const float* w, void* out, int rows, int H, float eps,
                       cudaStream_t st) {
+  constexpr int N = Vec<T>::N;
+  const bool aligned = (reinterpret_cast<uintptr_t>(x) % 16 == 0) &&
+                       (res == nullptr || reinterpret_cast<uintptr_t>(res) % 16 == 0) &&
+                       (out == nullptr || reinterpret_cast<uintptr_t>(out) % 16 == 0) &&
+                       (reinterpret_cast<uintptr_t>(w) % 16 == 0);
+  if (H % N == 0 && aligned && H / N <= 4 * 256) {
+    const int vecs = H / N;
+    int th = 32;
+    while (th < vecs && th < 256) th <<= 1;
+    const int iters = (vecs + th - 1) / th;
+    if (iters == 1)
+      rms_norm_vec_kernel<T, ADD, 1><<<rows, th, 0, st>>>((T*)x, (T*)res, w, (T*)out, H, eps);
+    else if (iters == 2)
+      rms_norm_vec_kernel<T, ADD, 2><<<rows, th, 0, st>>>((T*)x, (T*)res, w, (T*)out, H, eps);
+    else
+      rms_norm_vec_kernel<T, ADD, 4><<<rows, th, 0, st>>>((T*)x, (T*)res, w, (T*)out, H, eps);
+    DIB_CHECK_LAUNCH();
+    return DIB_OK;
+  }
   const size_t smem = (size_t)H * sizeof(float);
   if (smem > 200 * 1024) return DIB_BAD_SIZE;
   auto kern = rms_norm_kernel<T, ADD>;
@@ -252,6 +443,28 @@ int dib_qk_norm_rope_cache(const void* qkv, void* q_out, void* kv_cache, const f
   const int warps = 4;
   const long long items = (long long)T * (Hq + 2 * Hkv);
   const int blocks = ceil_div_host(items, warps);
+  const bool aligned = reinterpret_cast<uintptr_t>(qkv) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(q_out) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(kv_cache) % 16 == 0;
+  if (aligned && (D == 64 || D == 128 || D == 256) && (cos_sin == nullptr || rotary_dim == D) &&
+      (dtype == 0 || dtype == 1)) {
+#define DIB_QK_VEC(TT, EPL)                                                                      \
+  qk_norm_rope_cache_vec_kernel<TT, EPL><<<blocks, warps * 32, 0, st>>>(                        \
+      (const TT*)qkv, (TT*)q_out, (TT*)kv_cache, q_norm_w, k_norm_w, eps, cos_sin, max_pos,    \
+      positions, slot_mapping, T, Hq, Hkv, page_size, num_pages)
+    if (dtype == 0) {
+      if (D == 64) DIB_QK_VEC(float, 2);
+      else if (D == 128) DIB_QK_VEC(float, 4);
+      else DIB_QK_VEC(float, 8);
+    } else {
+      if (D == 64) DIB_QK_VEC(__nv_bfloat16, 2);
+      else if (D == 128) DIB_QK_VEC(__nv_bfloat16, 4);
+      else DIB_QK_VEC(__nv_bfloat16, 8);
+    }
+#undef DIB_QK_VEC
+    DIB_CHECK_LAUNCH();
+    return DIB_OK;
+  }
   const size_t smem = (size_t)warps * D * sizeof(float);
   if (dtype == 0)
     qk_norm_rope_cache_kernel<float><<<blocks, warps * 32, smem, st>>>(
@@ -290,6 +503,21 @@ int dib_silu_mul(const void* gu, void* out, int T, int I, int dtype, cudaStream_
   const long long total = (long long)T * I;
   if (total == 0) return DIB_OK;
   const int th = 256;
+  const bool aligned = reinterpret_cast<uintptr_t>(gu) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
+  if (aligned && dtype == 1 && I % 8 == 0) {
+    const long long vecs = total / 8;
+    silu_mul_vec_kernel<__nv_bfloat16><<<ceil_div_host(vecs, th), th, 0, st>>>(
+        (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, vecs, I);
+    DIB_CHECK_LAUNCH();
+    return DIB_OK;
+  }
+  if (aligned && dtype == 0 && I % 4 == 0) {
+    const long long vecs = total / 4;
+    silu_mul_vec_kernel<float><<<ceil_div_host(vecs, th), th, 0, st>>>((const float*)gu,
+                                                                      (float*)out, vecs, I);
+    DIB_CHECK_LAUNCH();
+    return DIB_OK;
+  }
   const int blocks = ceil_div_host(total, th);
   if (dtype == 0)
     silu_mul_kernel<float><<<blocks, th, 0, st>>>((const float*)gu, (float*)out, total, I);

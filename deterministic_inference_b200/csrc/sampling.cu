@@ -67,6 +67,37 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict_
   if (threadIdx.x == 0) out[blockIdx.x] = b.i == INT_MAX_ ? 0 : b.i;
 }
 
+// Two-stage argmax for wide rows: a row is cut into chunks of ARGMAX_CHUNK ids,
+// one block per (row, chunk) writes its best (value, index); a second kernel picks
+// the best chunk.  Ties go to the lowest index in both stages.
+constexpr int ARGMAX_CHUNK = 4096;
+
+__global__ void argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ pv,
+                                      int* __restrict__ pi, int V, int chunks) {
+  __shared__ Best scratch[32];
+  const int r = blockIdx.y, c = blockIdx.x;
+  const float* row = logits + (size_t)r * V;
+  const int lo = c * ARGMAX_CHUNK, hi = min(V, lo + ARGMAX_CHUNK);
+  Best b{-INFINITY, INT_MAX_};
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) b = better(b, Best{row[i], i});
+  b = block_best(b, scratch);
+  if (threadIdx.x == 0) {
+    pv[(size_t)r * chunks + c] = b.v;
+    pi[(size_t)r * chunks + c] = b.i;
+  }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi,
+                                    int* __restrict__ out, int chunks) {
+  __shared__ Best scratch[32];
+  const int r = blockIdx.x;
+  Best b{-INFINITY, INT_MAX_};
+  for (int c = threadIdx.x; c < chunks; c += blockDim.x)
+    b = better(b, Best{pv[(size_t)r * chunks + c], pi[(size_t)r * chunks + c]});
+  b = block_best(b, scratch);
+  if (threadIdx.x == 0) out[r] = b.i == INT_MAX_ ? 0 : b.i;
+}
+
 __device__ __forceinline__ float seeded_gumbel(long long seed, long long pos, int col) {
   const unsigned long long step =
       ((unsigned long long)seed * 19349663ull) ^ ((unsigned long long)pos * 73856093ull);
@@ -121,6 +152,21 @@ int dib_argmax(const float* logits, int* out, int R, int V, cudaStream_t st) {
   if (R == 0) return DIB_OK;
   if (V < 1) return DIB_BAD_SIZE;
   argmax_kernel<<<R, 1024, 0, st>>>(logits, out, V);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+int dib_argmax_chunks(int V) { return (V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK; }
+
+// scratch_v / scratch_i: [R, dib_argmax_chunks(V)]
+int dib_argmax_two_stage(const float* logits, float* scratch_v, int* scratch_i, int* out, int R,
+                         int V, cudaStream_t st) {
+  if (R == 0) return DIB_OK;
+  if (V < 1 || R > 65535) return DIB_BAD_SIZE;
+  const int chunks = (V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+  argmax_partial_kernel<<<dim3(chunks, R), 256, 0, st>>>(logits, scratch_v, scratch_i, V, chunks);
+  DIB_CHECK_LAUNCH();
+  argmax_final_kernel<<<R, 64, 0, st>>>(scratch_v, scratch_i, out, chunks);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }

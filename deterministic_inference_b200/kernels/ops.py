@@ -296,9 +296,19 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tenso
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     """int32 [R]: index of the largest logit of each row, lowest index on ties."""
     _need(logits, "logits", torch.float32, 2)
-    out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-    st = _lib("sampling").dib_argmax(_ptr(logits), _ptr(out), c_int(logits.shape[0]),
-                                     c_int(logits.shape[1]), _stream())
+    r, v = logits.shape
+    out = torch.empty(r, dtype=torch.int32, device=logits.device)
+    lib = _lib("sampling")
+    if v > 8192 and r <= 65535:
+        # wide rows: one block per chunk of the row, then a second tiny kernel
+        chunks = -(-v // 4096)
+        sv = torch.empty(r, chunks, dtype=torch.float32, device=logits.device)
+        si = torch.empty(r, chunks, dtype=torch.int32, device=logits.device)
+        st = lib.dib_argmax_two_stage(_ptr(logits), _ptr(sv), _ptr(si), _ptr(out), c_int(r), c_int(v),
+                                      _stream())
+        _check(st, "argmax", kernels=2)
+        return out
+    st = lib.dib_argmax(_ptr(logits), _ptr(out), c_int(r), c_int(v), _stream())
     _check(st, "argmax")
     return out
 
