@@ -1,0 +1,367 @@
+// bfloat16 matrix product out[M, N] = X[M, K] * W[N, K]^T on the 5th-generation
+// tensor cores: tcgen05.mma with the accumulator in tensor memory, operands staged
+// in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle) through a ring of
+// mbarrier-guarded stages, float32 accumulation.
+//
+// "Swap-AB" form for few tokens (decode and the head): the 128 rows of the MMA are
+// rows of W (output features), its N is the token count padded to 16..128, so a
+// handful of tokens fills the tensor core and the kernel streams W once.  A CTA owns
+// one (128 output features) x (BN tokens) tile and a contiguous range of k-blocks;
+// when there are fewer tiles than SMs the k range is split across CTAs: every CTA
+// writes its float32 partial tile, and the CTA that finishes last adds the partials
+// IN SPLIT ORDER, so the result does not depend on which CTA came last.  Neither the
+// k order nor the split depends on M.
+//
+// Roles inside a CTA of 128 threads: warp 0 allocates tensor memory and one of its
+// lanes issues the TMA loads; one lane of warp 1 issues the MMAs; all four warps read
+// the accumulator back (tcgen05.ld: warp w owns lanes 32w..32w+31) and store it.
+// Every mbarrier wait is bounded; a wait that runs out sets an error word that the
+// host reads with dib_gemm_bf16_status(), tensor memory is still freed, and the kernel
+// returns.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;      // W rows per tile = MMA M
+constexpr int BK = 64;       // k per stage: 64 bf16 = 128 bytes = one swizzle atom
+constexpr int UMMA_K = 16;   // k per tcgen05.mma for 16-bit inputs
+constexpr int STAGES = 4;
+constexpr int THREADS = 128;
+
+__device__ int dib_gemm_error_word = 0;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+  for (int i = 0; i < (1 << 20); ++i) {
+    unsigned ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; "
+        "selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1,
+                                            unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(smem_u32(bar)),
+      "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, both operands K-major.
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long desc_a,
+                                       unsigned long long desc_b, unsigned idesc, unsigned accum) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accum), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld16(unsigned taddr, unsigned (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, "
+      "%12, %13, %14, %15}, [%16];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes
+// (one 128-byte swizzle atom wide): 8-row groups lie 1024 bytes apart.
+__device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);   // start address
+  d |= (unsigned long long)(1024u >> 4) << 32;         // stride between 8-row groups
+  d |= 1ull << 46;                                     // descriptor version of sm_100
+  d |= 2ull << 61;                                     // layout: 128-byte swizzle
+  return d;
+}
+
+// kind::f16 instruction descriptor: float32 accumulator, bf16 A and B, both K-major.
+constexpr unsigned make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+
+template <int BN, typename OutT>
+__global__ void __launch_bounds__(THREADS)
+gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                 OutT* __restrict__ out, float* __restrict__ partial, int* __restrict__ counters,
+                 int M, int N, int num_kb, int kb_per_split, int splits) {
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
+  unsigned long long* empty = full + STAGES;
+  unsigned long long* accum = empty + STAGES;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(accum + 1);
+  __shared__ int s_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN, split = blockIdx.z;
+  const int kb_begin = split * kb_per_split;
+  const int nkb = min(kb_per_split, num_kb - kb_begin);
+
+  if (warp == 1 && lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(accum, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((unsigned)TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 0 && lane == 0) {
+    // ---- TMA producer
+    for (int i = 0; i < nkb && ok; ++i) {
+      const int s = i % STAGES;
+      if (i >= STAGES) ok = mbar_wait(&empty[s], ((i / STAGES) - 1) & 1);
+      if (!ok) break;
+      mbar_expect_tx(&full[s], STAGE_BYTES);
+      unsigned char* a = smem + s * STAGE_BYTES;
+      const int k = (kb_begin + i) * BK;
+      tma_load_2d(a, &map_w, k, n0, &full[s]);
+      tma_load_2d(a + A_BYTES, &map_x, k, m0, &full[s]);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer
+    constexpr unsigned idesc = make_idesc(BM, BN);
+    for (int i = 0; i < nkb && ok; ++i) {
+      const int s = i % STAGES;
+      ok = mbar_wait(&full[s], (i / STAGES) & 1);
+      if (!ok) break;
+      tc_fence_after();
+      const unsigned a = smem_u32(smem + s * STAGE_BYTES), b = a + A_BYTES;
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k)
+        tc_mma(tmem, smem_desc_sw128(a + k * UMMA_K * 2), smem_desc_sw128(b + k * UMMA_K * 2), idesc,
+               (i > 0 || k > 0) ? 1u : 0u);
+      tc_commit(&empty[s]);   // the stage is free once these MMAs have read it
+    }
+    if (ok) tc_commit(accum);  // the accumulator is complete once all MMAs are done
+  }
+  if (!ok) atomicExch(&dib_gemm_error_word, 1);
+  __syncwarp();
+
+  // ---- epilogue: accumulator D[n (lane), token (column)] -> out[token][n]
+  bool acc_ok = mbar_wait(accum, 0);
+  acc_ok = __all_sync(0xffffffffu, acc_ok);   // tcgen05.ld below is warp-wide
+  if (!acc_ok) atomicExch(&dib_gemm_error_word, 1);
+  tc_fence_after();
+  const int n = n0 + warp * 32 + lane;
+  const int m_pad = gridDim.y * BN;
+  if (acc_ok) {
+#pragma unroll
+    for (int c = 0; c < BN / 16; ++c) {
+      unsigned r[16];
+      tc_ld16(tmem + ((unsigned)(warp * 32) << 16) + c * 16, r);
+      tc_wait_ld();
+      if (n < N) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + c * 16 + j;
+          const float v = __uint_as_float(r[j]);
+          if (splits == 1) {
+            if (m < M) Elem<OutT>::store(out + (size_t)m * N + n, v);
+          } else {
+            partial[((size_t)split * m_pad + m) * N + n] = v;
+          }
+        }
+      }
+    }
+  }
+  if (splits > 1) {
+    // the CTA that finishes last adds the partial tiles in split order
+    __threadfence();
+    __syncthreads();
+    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+    if (threadIdx.x == 0) s_last = (atomicAdd(&counters[tile], 1) == splits - 1);
+    __syncthreads();
+    if (s_last) {
+      __threadfence();
+      if (n < N) {
+        for (int j = 0; j < BN; ++j) {
+          const int m = m0 + j;
+          if (m >= M) break;
+          float acc = 0.f;
+          for (int s = 0; s < splits; ++s) acc += partial[((size_t)s * m_pad + m) * N + n];
+          Elem<OutT>::store(out + (size_t)m * N + n, acc);
+        }
+      }
+      if (threadIdx.x == 0) counters[tile] = 0;   // ready for the next launch
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem),
+                 "r"((unsigned)TMEM_COLS));
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Tensor map of a row-major bf16 matrix [rows, K] with boxes of box_rows x 64
+// elements, 128-byte swizzle; out-of-range elements read as zero.
+bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, int box_rows) {
+  EncodeTiledFn enc = encode_tiled();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, typename OutT>
+int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, void* out, float* partial,
+                int* counters, int M, int N, int num_kb, int kb_per_split, int splits, dim3 grid,
+                cudaStream_t st) {
+  constexpr size_t smem =
+      (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
+  auto kern = gemm_swap_kernel<BN, OutT>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return DIB_LAUNCH_FAILED;
+    attr_set = true;
+  }
+  kern<<<grid, THREADS, smem, st>>>(mw, mx, (OutT*)out, partial, counters, M, N, num_kb,
+                                    kb_per_split, splits);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dib_gemm_bf16_status() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, dib_gemm_error_word, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+// How the product of these sizes is cut: tokens per tile, k-blocks per split, number
+// of splits.  A function of (M, N, K, number of SMs) only; the split of k depends on
+// N and K, never on M.
+void dib_gemm_bf16_plan(int M, int N, int K, int sm_count, int* bn, int* kb_per_split,
+                        int* splits) {
+  int b = 16;
+  while (b < M && b < 128) b <<= 1;
+  const int n_tiles = (N + BM - 1) / BM;
+  const int num_kb = (K + BK - 1) / BK;
+  int want = sm_count / n_tiles;          // CTAs per weight tile that would fill the GPU
+  if (want < 1) want = 1;
+  int per = (num_kb + want - 1) / want;
+  if (per < 2) per = num_kb < 2 ? num_kb : 2;
+  *bn = b;
+  *kb_per_split = per;
+  *splits = (num_kb + per - 1) / per;
+}
+
+// out[M, N] = x[M, K] * w[N, K]^T, bf16 inputs, float32 accumulation.  out is bf16
+// (out_fp32 = 0) or float32.  partial: float32 scratch for split-k, at least
+// splits * ceil(M / bn) * bn * N floats; counters: int32, one per output tile, zero
+// before the first call (the kernel leaves them zero).  K must be a multiple of 8
+// (TMA wants 16-byte row strides); x, w must be 16-byte aligned.
+int dib_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K, int out_fp32,
+                  float* partial, long long partial_floats, int* counters, int num_counters,
+                  int sm_count, cudaStream_t st) {
+  if (M == 0 || N == 0) return DIB_OK;
+  if (K < 8 || K % 8 != 0) return DIB_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16 != 0) return DIB_BAD_ALIGN;
+  int bn, per, splits;
+  dib_gemm_bf16_plan(M, N, K, sm_count, &bn, &per, &splits);
+  const int n_tiles = (N + BM - 1) / BM, m_tiles = (M + bn - 1) / bn;
+  const int num_kb = (K + BK - 1) / BK;
+  if (splits > 1 && ((long long)splits * m_tiles * bn * N > partial_floats ||
+                     n_tiles * m_tiles > num_counters)) {
+    splits = 1;            // no room for partial tiles: one CTA walks all of k
+    per = num_kb;
+  }
+  if (m_tiles > 65535 || splits > 65535) return DIB_BAD_SIZE;
+  CUtensorMap mw, mx;
+  if (!make_map(&mw, w, N, K, BM) || !make_map(&mx, x, M, K, bn)) return DIB_LAUNCH_FAILED;
+  dim3 grid(n_tiles, m_tiles, splits);
+#define CALL(BNV)                                                                                \
+  (out_fp32 ? launch_swap<BNV, float>(mw, mx, out, partial, counters, M, N, num_kb, per, splits, \
+                                      grid, st)                                                  \
+            : launch_swap<BNV, __nv_bfloat16>(mw, mx, out, partial, counters, M, N, num_kb, per, \
+                                              splits, grid, st))
+  switch (bn) {
+    case 16: return CALL(16);
+    case 32: return CALL(32);
+    case 64: return CALL(64);
+    default: return CALL(128);
+  }
+#undef CALL
+}
+
+}  // extern "C"

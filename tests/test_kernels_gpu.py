@@ -143,9 +143,14 @@ def test_linear_fp32_row_does_not_depend_on_batch():
         assert torch.equal(ops().linear(x[r:r + 1].contiguous(), w)[0], full[r])
 
 
-@pytest.mark.parametrize("m,n,k", [(1, 4096, 1024), (8, 1024, 3072), (64, 200, 136), (300, 152, 96),
-                                   (2048, 512, 256)])
+@pytest.mark.parametrize("m,n,k", [
+    (1, 4096, 1024), (8, 1024, 3072), (8, 1024, 2048), (8, 6144, 1024), (64, 200, 136),
+    (17, 130, 72), (128, 256, 64), (33, 100, 8), (5, 151936, 1024), (100, 3000, 520),
+    (129, 152, 96), (300, 152, 96), (2048, 512, 256)])
 def test_linear_bf16(m, n, k):
+    """Rows up to 128 run the package's tcgen05 kernel (tails in N and K, split k,
+    one to four token tiles), more rows the library."""
+    from deterministic_inference_b200.kernels import gemm_bf16
     torch.manual_seed(8)
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (0.05 * torch.randn(n, k, device="cuda")).to(torch.bfloat16)
@@ -154,6 +159,19 @@ def test_linear_bf16(m, n, k):
     got32 = ops().linear(x, w, out_dtype=torch.float32)
     assert got32.dtype == torch.float32
     torch.testing.assert_close(got32, want, atol=1e-3, rtol=1e-3)
+    assert gemm_bf16.status() == 0
+
+
+def test_linear_bf16_row_does_not_depend_on_batch():
+    """The k order and the split of k depend on N and K only: a row alone and among
+    100 rows gives the same bits; and a second launch finds its counters reset."""
+    torch.manual_seed(9)
+    x = torch.randn(100, 2048, device="cuda").to(torch.bfloat16)
+    w = (0.05 * torch.randn(1024, 2048, device="cuda")).to(torch.bfloat16)
+    full = ops().linear(x, w)
+    for r in (0, 15, 16, 99):
+        assert torch.equal(ops().linear(x[r:r + 1].contiguous(), w)[0], full[r])
+    assert torch.equal(ops().linear(x, w), full)
 
 
 # ------------------------------------------------------------------ attention
