@@ -249,6 +249,7 @@ extend_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
                         const int* __restrict__ cu_q_lens, const int* __restrict__ seq_lens,
                         const int* __restrict__ tile_seq, const int* __restrict__ tile_start,
                         int Hq, int Hkv, int page_size, float scale, int window) {
+  pdl_prologue();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* sK0 = sQ + EXT_M * (D + PAD);
@@ -370,6 +371,7 @@ decode_attention_stage1_kernel(const __nv_bfloat16* __restrict__ q,
                                const int* __restrict__ seq_lens, float* __restrict__ part_o,
                                float* __restrict__ part_lse, int max_splits, int Hq, int Hkv,
                                int page_size, float scale, int window) {
+  pdl_prologue();
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* sV = sK + DEC_SPLIT * (D + PAD);
@@ -511,6 +513,7 @@ __global__ void decode_attention_stage2_kernel(const float* __restrict__ part_o,
                                                const int* __restrict__ seq_lens,
                                                __nv_bfloat16* __restrict__ out, int max_splits,
                                                int Hq, int D, int window) {
+  pdl_prologue();
   const int b = blockIdx.x, h = blockIdx.y;
   const int kv_len = seq_lens[b];
   const int pos = kv_len - 1;
@@ -545,7 +548,7 @@ int launch_extend(const void* q, void* out, const void* cache, const int* bt, in
     attr_set = true;
   }
   dim3 grid(num_tiles, Hkv);
-  kern<<<grid, EXT_THREADS, smem, st>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out,
+  dib_launch(kern, dim3(grid), dim3(EXT_THREADS), smem, st, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,
                                         (const __nv_bfloat16*)cache, bt, max_blocks, cu_q_lens,
                                         seq_lens, tile_seq, tile_start, Hq, Hkv, page_size, scale,
                                         window);
@@ -569,13 +572,13 @@ int launch_decode(const void* q, void* out, const void* cache, const int* bt, in
     attr_set = true;
   }
   dim3 grid(Hkv, num_seqs, max_splits);
-  kern<<<grid, DEC_THREADS, smem, st>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt,
+  dib_launch(kern, dim3(grid), dim3(DEC_THREADS), smem, st, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt,
                                         max_blocks, seq_lens, part_o, part_lse, max_splits, Hq, Hkv,
                                         page_size, scale, window);
   DIB_CHECK_LAUNCH();
   dim3 grid2(num_seqs, Hq);
   const int th = D < 32 ? 32 : (D + 31) / 32 * 32;
-  decode_attention_stage2_kernel<<<grid2, th, 0, st>>>(part_o, part_lse, seq_lens,
+  dib_launch(decode_attention_stage2_kernel, dim3(grid2), dim3(th), 0, st, part_o, part_lse, seq_lens,
                                                        (__nv_bfloat16*)out, max_splits, Hq, D,
                                                        window);
   DIB_CHECK_LAUNCH();

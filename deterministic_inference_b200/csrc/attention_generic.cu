@@ -30,6 +30,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out,
                                const int* __restrict__ token_seq,
                                const int* __restrict__ positions, int T_tokens, int Hq, int Hkv,
                                int D, int page_size, float scale, int window) {
+  pdl_prologue();
   __shared__ float sq[WARPS][MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -112,11 +113,11 @@ extern "C" int dib_paged_attention_generic(const void* q, void* out, const void*
   const long long items = (long long)T * Hq;
   const int blocks = ceil_div_host(items, WARPS);
   if (dtype == 0)
-    paged_attention_generic_kernel<float><<<blocks, WARPS * 32, 0, st>>>(
+    dib_launch(paged_attention_generic_kernel<float>, dim3(blocks), dim3(WARPS * 32), 0, st, 
         (const float*)q, (float*)out, (const float*)kv_cache, block_table, max_blocks, token_seq,
         positions, T, Hq, Hkv, D, page_size, scale, window);
   else if (dtype == 1)
-    paged_attention_generic_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, st>>>(
+    dib_launch(paged_attention_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(WARPS * 32), 0, st, 
         (const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)kv_cache, block_table,
         max_blocks, token_seq, positions, T, Hq, Hkv, D, page_size, scale, window);
   else return DIB_BAD_DTYPE;

@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 enum dib_status : int {
   DIB_OK = 0,
@@ -70,3 +71,44 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int ceil_div_host(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// ---- programmatic dependent launch
+// Every kernel of this package is launched with the attribute that lets it start
+// while the kernel before it on the stream is still draining (its blocks are
+// scheduled, its prologue runs), and every kernel waits with griddepcontrol.wait for
+// that predecessor to have finished and flushed its memory before it reads or writes
+// anything the predecessor may touch.  Only constants (weights, tables, tensor maps)
+// are read before the wait.  In a chain A, B, C each kernel waits for the one before
+// it, which itself only finished after its own wait, so C also sees A complete.  Set
+// DIB200_PDL=0 to launch the plain way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::); }
+__device__ __forceinline__ void pdl_prologue() {
+  pdl_trigger();
+  pdl_wait();
+}
+
+static inline bool dib_pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("DIB200_PDL");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline void dib_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dib_pdl_enabled() ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

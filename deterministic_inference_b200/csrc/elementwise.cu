@@ -16,6 +16,7 @@ namespace {
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  T* __restrict__ out, int H, int V) {
+  pdl_prologue();
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < V;
@@ -35,6 +36,7 @@ template <typename T, bool ADD>
 __global__ void rms_norm_kernel(T* __restrict__ x, T* __restrict__ residual,
                                 const float* __restrict__ w, T* __restrict__ out,
                                 int H, float eps) {
+  pdl_prologue();
   extern __shared__ float row[];
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * H;
@@ -93,6 +95,7 @@ template <typename T, bool ADD, int ITERS>
 __global__ void rms_norm_vec_kernel(T* __restrict__ x, T* __restrict__ residual,
                                     const float* __restrict__ w, T* __restrict__ out, int H,
                                     float eps) {
+  pdl_prologue();
   constexpr int N = Vec<T>::N;
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * H;
@@ -149,6 +152,7 @@ __global__ void qk_norm_rope_cache_kernel(
     const float* __restrict__ cos_sin, int rotary_dim, int max_pos,
     const int* __restrict__ positions, const int* __restrict__ slot_mapping,
     int T_tokens, int Hq, int Hkv, int D, int page_size, long long num_pages) {
+  pdl_prologue();
   extern __shared__ float smem[];
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -223,11 +227,13 @@ struct alignas((sizeof(T) * EPL) <= 16 ? (sizeof(T) * EPL) : 16) Pack {
 
 template <typename T, int EPL>
 __global__ void qk_norm_rope_cache_vec_kernel(
-    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ kv_cache,
+    const T* __restrict__ qkv, const float* __restrict__ parts, int S, long long split_stride,
+    T* __restrict__ q_out, T* __restrict__ kv_cache,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
     const float* __restrict__ cos_sin, int max_pos, const int* __restrict__ positions,
     const int* __restrict__ slot_mapping, int T_tokens, int Hq, int Hkv, int page_size,
     long long num_pages) {
+  pdl_prologue();
   constexpr int D = EPL * 32;
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -254,15 +260,30 @@ __global__ void qk_norm_rope_cache_vec_kernel(
     const int h = is_k ? head - Hq : head - Hq - Hkv;
     dst = kv_cache + ((((size_t)page * 2 + kv) * Hkv + h) * page_size + off) * D;
   }
-  const T* src = qkv + ((size_t)t * heads + head) * D + lane * EPL;
-  const Pack<T, EPL> in = *reinterpret_cast<const Pack<T, EPL>*>(src);
   float v[EPL];
   float ss = 0.f;
+  if (parts == nullptr) {
+    const T* src = qkv + ((size_t)t * heads + head) * D + lane * EPL;
+    const Pack<T, EPL> in = *reinterpret_cast<const Pack<T, EPL>*>(src);
 #pragma unroll
-  for (int k = 0; k < EPL; ++k) {
-    v[k] = Elem<T>::load(&in.e[k]);
-    ss += v[k] * v[k];
+    for (int k = 0; k < EPL; ++k) v[k] = Elem<T>::load(&in.e[k]);
+  } else {
+    // the row is a sum of split-k partial products, added in split order and rounded
+    // to T as a stored projection output would be
+    const float* src = parts + ((size_t)t * heads + head) * D + lane * EPL;
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) v[k] = 0.f;
+#pragma unroll 4
+    for (int sp = 0; sp < S; ++sp) {
+      const Pack<float, EPL> in = *reinterpret_cast<const Pack<float, EPL>*>(src + sp * split_stride);
+#pragma unroll
+      for (int k = 0; k < EPL; ++k) v[k] += in.e[k];
+    }
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) v[k] = round_to<T>(v[k]);
   }
+#pragma unroll
+  for (int k = 0; k < EPL; ++k) ss += v[k] * v[k];
   if (nw != nullptr) {
     ss = warp_sum(ss);
     const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
@@ -295,6 +316,7 @@ __global__ void reshape_and_cache_kernel(const T* __restrict__ k, const T* __res
                                          T* __restrict__ kv_cache,
                                          const int* __restrict__ slot_mapping, int Hkv, int D,
                                          int page_size, long long num_pages) {
+  pdl_prologue();
   const int t = blockIdx.x;
   const int slot = slot_mapping[t];
   if (slot < 0) return;
@@ -315,6 +337,7 @@ __global__ void reshape_and_cache_kernel(const T* __restrict__ k, const T* __res
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total,
                                 int I) {
+  pdl_prologue();
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const long long t = idx / I;
@@ -328,6 +351,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, long long vecs,
                                     int I) {
+  pdl_prologue();
   constexpr int N = Vec<T>::N;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= vecs) return;
@@ -342,10 +366,113 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ ou
   Vec<T>::store(out + t * I + i, y);
 }
 
+// ------------------------------------------------ readers of split-k partials
+// A matrix product with split k leaves `S` float32 partial products
+// parts[s][row][col]; its readers add them in split order and round the sum to T,
+// which is what reading a stored product would give.
+
+template <typename T>
+__global__ void sum_split_kernel(const float* __restrict__ parts, T* __restrict__ out,
+                                 long long total4, long long split_stride, int S) {
+  pdl_prologue();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total4) return;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int sp = 0; sp < S; ++sp) {
+    const float4 p = *reinterpret_cast<const float4*>(parts + sp * split_stride + i * 4);
+    a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w;
+  }
+  Pack<T, 4> o;
+  Elem<T>::store(&o.e[0], a.x);
+  Elem<T>::store(&o.e[1], a.y);
+  Elem<T>::store(&o.e[2], a.z);
+  Elem<T>::store(&o.e[3], a.w);
+  *reinterpret_cast<Pack<T, 4>*>(out + i * 4) = o;
+}
+
+// residual += x (stored rounded), out = rms_norm(unrounded sum), x given as partials.
+template <typename T, int ITERS>
+__global__ void add_rms_norm_split_kernel(const float* __restrict__ parts, int S,
+                                          long long split_stride, T* __restrict__ residual,
+                                          const float* __restrict__ w, T* __restrict__ out, int H,
+                                          float eps) {
+  pdl_prologue();
+  __shared__ float scratch[32];
+  const size_t base = (size_t)blockIdx.x * H;
+  float v[ITERS][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = (it * blockDim.x + threadIdx.x) * 4;
+    if (i < H) {
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+      for (int sp = 0; sp < S; ++sp) {
+        const float4 p = *reinterpret_cast<const float4*>(parts + sp * split_stride + base + i);
+        a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w;
+      }
+      const Pack<T, 4> r = *reinterpret_cast<const Pack<T, 4>*>(residual + base + i);
+      v[it][0] = round_to<T>(a.x) + Elem<T>::load(&r.e[0]);
+      v[it][1] = round_to<T>(a.y) + Elem<T>::load(&r.e[1]);
+      v[it][2] = round_to<T>(a.z) + Elem<T>::load(&r.e[2]);
+      v[it][3] = round_to<T>(a.w) + Elem<T>::load(&r.e[3]);
+      Pack<T, 4> o;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        Elem<T>::store(&o.e[k], v[it][k]);
+        ss += v[it][k] * v[it][k];
+      }
+      *reinterpret_cast<Pack<T, 4>*>(residual + base + i) = o;
+    }
+  }
+  const float total = block_sum(ss, scratch);
+  const float rstd = 1.0f / sqrtf(total / (float)H + eps);
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = (it * blockDim.x + threadIdx.x) * 4;
+    if (i < H) {
+      const float4 ww = *reinterpret_cast<const float4*>(w + i);
+      Pack<T, 4> o;
+      Elem<T>::store(&o.e[0], v[it][0] * rstd * ww.x);
+      Elem<T>::store(&o.e[1], v[it][1] * rstd * ww.y);
+      Elem<T>::store(&o.e[2], v[it][2] * rstd * ww.z);
+      Elem<T>::store(&o.e[3], v[it][3] * rstd * ww.w);
+      *reinterpret_cast<Pack<T, 4>*>(out + base + i) = o;
+    }
+  }
+}
+
+template <typename T>
+__global__ void silu_mul_split_kernel(const float* __restrict__ parts, int S, long long split_stride,
+                                      T* __restrict__ out, long long vecs, int I) {
+  pdl_prologue();
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= vecs) return;
+  const int per_row = I / 4;
+  const long long t = idx / per_row;
+  const int i = (int)(idx % per_row) * 4;
+  float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+#pragma unroll 4
+  for (int sp = 0; sp < S; ++sp) {
+    const float* row = parts + sp * split_stride + t * 2 * I;
+    const float4 a = *reinterpret_cast<const float4*>(row + i);
+    const float4 b = *reinterpret_cast<const float4*>(row + I + i);
+    g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+    u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+  }
+  const float gg[4] = {round_to<T>(g.x), round_to<T>(g.y), round_to<T>(g.z), round_to<T>(g.w)};
+  const float uu[4] = {round_to<T>(u.x), round_to<T>(u.y), round_to<T>(u.z), round_to<T>(u.w)};
+  Pack<T, 4> o;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) Elem<T>::store(&o.e[k], gg[k] / (1.0f + expf(-gg[k])) * uu[k]);
+  *reinterpret_cast<Pack<T, 4>*>(out + t * I + i) = o;
+}
+
 // ---------------------------------------------------------------- row gather
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ idx,
                                    T* __restrict__ out, int H, int T_rows) {
+  pdl_prologue();
   const int r = blockIdx.x;
   int src = idx[r];
   src = src < 0 ? 0 : (src >= T_rows ? T_rows - 1 : src);
@@ -373,11 +500,11 @@ int launch_rms(void* x, void* res, const float* w, void* out, int rows, int H, f
     while (th < vecs && th < 256) th <<= 1;
     const int iters = (vecs + th - 1) / th;
     if (iters == 1)
-      rms_norm_vec_kernel<T, ADD, 1><<<rows, th, 0, st>>>((T*)x, (T*)res, w, (T*)out, H, eps);
+      dib_launch(rms_norm_vec_kernel<T, ADD, 1>, dim3(rows), dim3(th), 0, st, (T*)x, (T*)res, w, (T*)out, H, eps);
     else if (iters == 2)
-      rms_norm_vec_kernel<T, ADD, 2><<<rows, th, 0, st>>>((T*)x, (T*)res, w, (T*)out, H, eps);
+      dib_launch(rms_norm_vec_kernel<T, ADD, 2>, dim3(rows), dim3(th), 0, st, (T*)x, (T*)res, w, (T*)out, H, eps);
     else
-      rms_norm_vec_kernel<T, ADD, 4><<<rows, th, 0, st>>>((T*)x, (T*)res, w, (T*)out, H, eps);
+      dib_launch(rms_norm_vec_kernel<T, ADD, 4>, dim3(rows), dim3(th), 0, st, (T*)x, (T*)res, w, (T*)out, H, eps);
     DIB_CHECK_LAUNCH();
     return DIB_OK;
   }
@@ -393,7 +520,7 @@ int launch_rms(void* x, void* res, const float* w, void* out, int rows, int H, f
   }
   int th = pick_threads(H);
   if (th > 512) th = 512;
-  kern<<<rows, th, smem, st>>>((T*)x, (T*)res, w, (T*)out, H, eps);
+  dib_launch(kern, dim3(rows), dim3(th), smem, st, (T*)x, (T*)res, w, (T*)out, H, eps);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -407,9 +534,9 @@ int dib_embedding(const void* table, const int* ids, void* out, int T, int H, in
   if (T == 0) return DIB_OK;
   const int th = pick_threads(H) > 256 ? 256 : pick_threads(H);
   if (dtype == 0)
-    embedding_kernel<float><<<T, th, 0, st>>>((const float*)table, ids, (float*)out, H, V);
+    dib_launch(embedding_kernel<float>, dim3(T), dim3(th), 0, st, (const float*)table, ids, (float*)out, H, V);
   else if (dtype == 1)
-    embedding_kernel<__nv_bfloat16><<<T, th, 0, st>>>((const __nv_bfloat16*)table, ids,
+    dib_launch(embedding_kernel<__nv_bfloat16>, dim3(T), dim3(th), 0, st, (const __nv_bfloat16*)table, ids,
                                                       (__nv_bfloat16*)out, H, V);
   else return DIB_BAD_DTYPE;
   DIB_CHECK_LAUNCH();
@@ -433,7 +560,28 @@ int dib_add_rms_norm(void* x, void* residual, const float* w, int rows, int H, f
   return DIB_BAD_DTYPE;
 }
 
+int dib_qk_norm_rope_cache_split(const void* qkv, const float* parts, int S, long long split_stride,
+                                 void* q_out, void* kv_cache, const float* q_norm_w,
+                                 const float* k_norm_w, float eps, const float* cos_sin,
+                                 int rotary_dim, int max_pos, const int* positions,
+                                 const int* slot_mapping, int T, int Hq, int Hkv, int D,
+                                 int page_size, long long num_pages, int dtype, cudaStream_t st);
+
 int dib_qk_norm_rope_cache(const void* qkv, void* q_out, void* kv_cache, const float* q_norm_w,
+                           const float* k_norm_w, float eps, const float* cos_sin, int rotary_dim,
+                           int max_pos, const int* positions, const int* slot_mapping, int T,
+                           int Hq, int Hkv, int D, int page_size, long long num_pages, int dtype,
+                           cudaStream_t st) {
+  return dib_qk_norm_rope_cache_split(qkv, nullptr, 0, 0, q_out, kv_cache, q_norm_w, k_norm_w, eps,
+                                      cos_sin, rotary_dim, max_pos, positions, slot_mapping, T, Hq,
+                                      Hkv, D, page_size, num_pages, dtype, st);
+}
+
+// With parts != nullptr the fused projection rows are sums of S split-k partials
+// (float32 [S, T, (Hq+2Hkv)*D]); only head sizes 64, 128, 256 with a full rotation
+// take that form (-2 otherwise: the caller sums the partials first).
+int dib_qk_norm_rope_cache_split(const void* qkv, const float* parts, int S, long long split_stride,
+                                 void* q_out, void* kv_cache, const float* q_norm_w,
                            const float* k_norm_w, float eps, const float* cos_sin, int rotary_dim,
                            int max_pos, const int* positions, const int* slot_mapping, int T,
                            int Hq, int Hkv, int D, int page_size, long long num_pages, int dtype,
@@ -444,13 +592,15 @@ int dib_qk_norm_rope_cache(const void* qkv, void* q_out, void* kv_cache, const f
   const long long items = (long long)T * (Hq + 2 * Hkv);
   const int blocks = ceil_div_host(items, warps);
   const bool aligned = reinterpret_cast<uintptr_t>(qkv) % 16 == 0 &&
+                       reinterpret_cast<uintptr_t>(parts) % 16 == 0 &&
                        reinterpret_cast<uintptr_t>(q_out) % 16 == 0 &&
                        reinterpret_cast<uintptr_t>(kv_cache) % 16 == 0;
   if (aligned && (D == 64 || D == 128 || D == 256) && (cos_sin == nullptr || rotary_dim == D) &&
       (dtype == 0 || dtype == 1)) {
 #define DIB_QK_VEC(TT, EPL)                                                                      \
-  qk_norm_rope_cache_vec_kernel<TT, EPL><<<blocks, warps * 32, 0, st>>>(                        \
-      (const TT*)qkv, (TT*)q_out, (TT*)kv_cache, q_norm_w, k_norm_w, eps, cos_sin, max_pos,    \
+  dib_launch(qk_norm_rope_cache_vec_kernel<TT, EPL>, dim3(blocks), dim3(warps * 32), 0, st,                         \
+      (const TT*)qkv, parts, S, split_stride, (TT*)q_out, (TT*)kv_cache, q_norm_w, k_norm_w,   \
+      eps, cos_sin, max_pos,                                                                    \
       positions, slot_mapping, T, Hq, Hkv, page_size, num_pages)
     if (dtype == 0) {
       if (D == 64) DIB_QK_VEC(float, 2);
@@ -465,13 +615,14 @@ int dib_qk_norm_rope_cache(const void* qkv, void* q_out, void* kv_cache, const f
     DIB_CHECK_LAUNCH();
     return DIB_OK;
   }
+  if (parts != nullptr) return DIB_BAD_SIZE;
   const size_t smem = (size_t)warps * D * sizeof(float);
   if (dtype == 0)
-    qk_norm_rope_cache_kernel<float><<<blocks, warps * 32, smem, st>>>(
+    dib_launch(qk_norm_rope_cache_kernel<float>, dim3(blocks), dim3(warps * 32), smem, st, 
         (const float*)qkv, (float*)q_out, (float*)kv_cache, q_norm_w, k_norm_w, eps, cos_sin,
         rotary_dim, max_pos, positions, slot_mapping, T, Hq, Hkv, D, page_size, num_pages);
   else if (dtype == 1)
-    qk_norm_rope_cache_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, st>>>(
+    dib_launch(qk_norm_rope_cache_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, st, 
         (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_cache, q_norm_w,
         k_norm_w, eps, cos_sin, rotary_dim, max_pos, positions, slot_mapping, T, Hq, Hkv, D,
         page_size, num_pages);
@@ -487,11 +638,11 @@ int dib_reshape_and_cache(const void* k, const void* v, void* kv_cache, const in
   int th = pick_threads(Hkv * D);
   if (th > 256) th = 256;
   if (dtype == 0)
-    reshape_and_cache_kernel<float><<<T, th, 0, st>>>((const float*)k, (const float*)v,
+    dib_launch(reshape_and_cache_kernel<float>, dim3(T), dim3(th), 0, st, (const float*)k, (const float*)v,
                                                       (float*)kv_cache, slot_mapping, Hkv, D,
                                                       page_size, num_pages);
   else if (dtype == 1)
-    reshape_and_cache_kernel<__nv_bfloat16><<<T, th, 0, st>>>(
+    dib_launch(reshape_and_cache_kernel<__nv_bfloat16>, dim3(T), dim3(th), 0, st, 
         (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)kv_cache, slot_mapping,
         Hkv, D, page_size, num_pages);
   else return DIB_BAD_DTYPE;
@@ -506,23 +657,23 @@ int dib_silu_mul(const void* gu, void* out, int T, int I, int dtype, cudaStream_
   const bool aligned = reinterpret_cast<uintptr_t>(gu) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
   if (aligned && dtype == 1 && I % 8 == 0) {
     const long long vecs = total / 8;
-    silu_mul_vec_kernel<__nv_bfloat16><<<ceil_div_host(vecs, th), th, 0, st>>>(
+    dib_launch(silu_mul_vec_kernel<__nv_bfloat16>, dim3(ceil_div_host(vecs, th)), dim3(th), 0, st, 
         (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, vecs, I);
     DIB_CHECK_LAUNCH();
     return DIB_OK;
   }
   if (aligned && dtype == 0 && I % 4 == 0) {
     const long long vecs = total / 4;
-    silu_mul_vec_kernel<float><<<ceil_div_host(vecs, th), th, 0, st>>>((const float*)gu,
+    dib_launch(silu_mul_vec_kernel<float>, dim3(ceil_div_host(vecs, th)), dim3(th), 0, st, (const float*)gu,
                                                                       (float*)out, vecs, I);
     DIB_CHECK_LAUNCH();
     return DIB_OK;
   }
   const int blocks = ceil_div_host(total, th);
   if (dtype == 0)
-    silu_mul_kernel<float><<<blocks, th, 0, st>>>((const float*)gu, (float*)out, total, I);
+    dib_launch(silu_mul_kernel<float>, dim3(blocks), dim3(th), 0, st, (const float*)gu, (float*)out, total, I);
   else if (dtype == 1)
-    silu_mul_kernel<__nv_bfloat16><<<blocks, th, 0, st>>>((const __nv_bfloat16*)gu,
+    dib_launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(th), 0, st, (const __nv_bfloat16*)gu,
                                                           (__nv_bfloat16*)out, total, I);
   else return DIB_BAD_DTYPE;
   DIB_CHECK_LAUNCH();
@@ -535,10 +686,71 @@ int dib_gather_rows(const void* x, const int* idx, void* out, int R, int H, int 
   int th = pick_threads(H);
   if (th > 256) th = 256;
   if (dtype == 0)
-    gather_rows_kernel<float><<<R, th, 0, st>>>((const float*)x, idx, (float*)out, H, T_rows);
+    dib_launch(gather_rows_kernel<float>, dim3(R), dim3(th), 0, st, (const float*)x, idx, (float*)out, H, T_rows);
   else if (dtype == 1)
-    gather_rows_kernel<__nv_bfloat16><<<R, th, 0, st>>>((const __nv_bfloat16*)x, idx,
+    dib_launch(gather_rows_kernel<__nv_bfloat16>, dim3(R), dim3(th), 0, st, (const __nv_bfloat16*)x, idx,
                                                         (__nv_bfloat16*)out, H, T_rows);
+  else return DIB_BAD_DTYPE;
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+// out[i] = round(sum over s of parts[s][i]); total elements a multiple of 4.
+int dib_sum_split(const float* parts, int S, long long split_stride, void* out, long long total,
+                  int dtype, cudaStream_t st) {
+  if (total == 0) return DIB_OK;
+  if (total % 4 != 0 || S < 1) return DIB_BAD_SIZE;
+  const long long v = total / 4;
+  const int th = 256;
+  if (dtype == 0)
+    dib_launch(sum_split_kernel<float>, dim3(ceil_div_host(v, th)), dim3(th), 0, st, parts, (float*)out, v, split_stride, S);
+  else if (dtype == 1)
+    dib_launch(sum_split_kernel<__nv_bfloat16>, dim3(ceil_div_host(v, th)), dim3(th), 0, st, parts, (__nv_bfloat16*)out, v,
+                                                                      split_stride, S);
+  else return DIB_BAD_DTYPE;
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+// add_rms_norm with x given as split-k partials [S, rows, H]; out [rows, H] is new.
+int dib_add_rms_norm_split(const float* parts, int S, long long split_stride, void* residual,
+                           const float* w, void* out, int rows, int H, float eps, int dtype,
+                           cudaStream_t st) {
+  if (rows == 0) return DIB_OK;
+  if (H % 4 != 0 || H / 4 > 4 * 256 || S < 1) return DIB_BAD_SIZE;
+  const int vecs = H / 4;
+  int th = 32;
+  while (th < vecs && th < 256) th <<= 1;
+  const int iters = (vecs + th - 1) / th;
+#define DIB_ARS(TT, IT)                                                                         \
+  dib_launch(add_rms_norm_split_kernel<TT, IT>, dim3(rows), dim3(th), 0, st, parts, S, split_stride, (TT*)residual, w, \
+                                                         (TT*)out, H, eps)
+  if (dtype == 0) {
+    if (iters == 1) DIB_ARS(float, 1); else if (iters == 2) DIB_ARS(float, 2); else DIB_ARS(float, 4);
+  } else if (dtype == 1) {
+    if (iters == 1) DIB_ARS(__nv_bfloat16, 1);
+    else if (iters == 2) DIB_ARS(__nv_bfloat16, 2);
+    else DIB_ARS(__nv_bfloat16, 4);
+  } else return DIB_BAD_DTYPE;
+#undef DIB_ARS
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+// silu_mul with [gate | up] given as split-k partials [S, T, 2I].
+int dib_silu_mul_split(const float* parts, int S, long long split_stride, void* out, int T, int I,
+                       int dtype, cudaStream_t st) {
+  const long long total = (long long)T * I;
+  if (total == 0) return DIB_OK;
+  if (I % 4 != 0 || S < 1) return DIB_BAD_SIZE;
+  const long long v = total / 4;
+  const int th = 256;
+  if (dtype == 0)
+    dib_launch(silu_mul_split_kernel<float>, dim3(ceil_div_host(v, th)), dim3(th), 0, st, parts, S, split_stride,
+                                                                    (float*)out, v, I);
+  else if (dtype == 1)
+    dib_launch(silu_mul_split_kernel<__nv_bfloat16>, dim3(ceil_div_host(v, th)), dim3(th), 0, st, 
+        parts, S, split_stride, (__nv_bfloat16*)out, v, I);
   else return DIB_BAD_DTYPE;
   DIB_CHECK_LAUNCH();
   return DIB_OK;

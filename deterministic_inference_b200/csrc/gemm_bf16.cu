@@ -7,10 +7,12 @@
 // rows of W (output features), its N is the token count padded to 16..128, so a
 // handful of tokens fills the tensor core and the kernel streams W once.  A CTA owns
 // one (128 output features) x (BN tokens) tile and a contiguous range of k-blocks;
-// when there are fewer tiles than SMs the k range is split across CTAs: every CTA
-// writes its float32 partial tile, and the CTA that finishes last adds the partials
-// IN SPLIT ORDER, so the result does not depend on which CTA came last.  Neither the
-// k order nor the split depends on M.
+// when there are fewer tiles than SMs the k range is split across CTAs and every CTA
+// writes its float32 partial tile to partial[split][token][feature].  The partials
+// are added IN SPLIT ORDER by whoever reads them: the next kernel of the layer
+// (residual-add + norm, q/k norm, SiLU gate) or a plain sum kernel, so no CTA waits
+// for another and the result does not depend on their timing.  Neither the k order
+// nor the split depends on M.
 //
 // Roles inside a CTA of 128 threads: warp 0 allocates tensor memory and one of its
 // lanes issues the TMA loads; one lane of warp 1 issues the MMAs; all four warps read
@@ -120,8 +122,8 @@ constexpr unsigned make_idesc(int m, int n) {
 template <int BN, typename OutT>
 __global__ void __launch_bounds__(THREADS)
 gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                 OutT* __restrict__ out, float* __restrict__ partial, int* __restrict__ counters,
-                 int M, int N, int num_kb, int kb_per_split, int splits) {
+                 OutT* __restrict__ out, float* __restrict__ partial, int M, int N, int num_kb,
+                 int kb_per_split, int splits) {
   constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   extern __shared__ unsigned char smem_raw[];
@@ -131,7 +133,6 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   unsigned long long* empty = full + STAGES;
   unsigned long long* accum = empty + STAGES;
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(accum + 1);
-  __shared__ int s_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN, split = blockIdx.z;
@@ -158,11 +159,22 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const unsigned tmem = *tmem_slot;
   bool ok = true;
 
+  pdl_trigger();
   if (warp == 0 && lane == 0) {
-    // ---- TMA producer
-    for (int i = 0; i < nkb && ok; ++i) {
+    // ---- TMA producer.  The weights do not depend on the kernel before this one, so
+    // their loads for the first stages start before the wait for that kernel; the
+    // activations follow after it.
+    const int pre = nkb < STAGES ? nkb : STAGES;
+    for (int i = 0; i < pre; ++i) {
+      mbar_expect_tx(&full[i], STAGE_BYTES);
+      tma_load_2d(smem + i * STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full[i]);
+    }
+    pdl_wait();
+    for (int i = 0; i < pre; ++i)
+      tma_load_2d(smem + i * STAGE_BYTES + A_BYTES, &map_x, (kb_begin + i) * BK, m0, &full[i]);
+    for (int i = pre; i < nkb && ok; ++i) {
       const int s = i % STAGES;
-      if (i >= STAGES) ok = mbar_wait(&empty[s], ((i / STAGES) - 1) & 1);
+      ok = mbar_wait(&empty[s], ((i / STAGES) - 1) & 1);
       if (!ok) break;
       mbar_expect_tx(&full[s], STAGE_BYTES);
       unsigned char* a = smem + s * STAGE_BYTES;
@@ -189,6 +201,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   }
   if (!ok) atomicExch(&dib_gemm_error_word, 1);
   __syncwarp();
+  pdl_wait();   // nothing is stored before the kernel before this one has finished
 
   // ---- epilogue: accumulator D[n (lane), token (column)] -> out[token][n]
   bool acc_ok = mbar_wait(accum, 0);
@@ -196,7 +209,6 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (!acc_ok) atomicExch(&dib_gemm_error_word, 1);
   tc_fence_after();
   const int n = n0 + warp * 32 + lane;
-  const int m_pad = gridDim.y * BN;
   if (acc_ok) {
 #pragma unroll
     for (int c = 0; c < BN / 16; ++c) {
@@ -207,35 +219,12 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           const int m = m0 + c * 16 + j;
-          const float v = __uint_as_float(r[j]);
-          if (splits == 1) {
-            if (m < M) Elem<OutT>::store(out + (size_t)m * N + n, v);
-          } else {
-            partial[((size_t)split * m_pad + m) * N + n] = v;
-          }
-        }
-      }
-    }
-  }
-  if (splits > 1) {
-    // the CTA that finishes last adds the partial tiles in split order
-    __threadfence();
-    __syncthreads();
-    const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-    if (threadIdx.x == 0) s_last = (atomicAdd(&counters[tile], 1) == splits - 1);
-    __syncthreads();
-    if (s_last) {
-      __threadfence();
-      if (n < N) {
-        for (int j = 0; j < BN; ++j) {
-          const int m = m0 + j;
           if (m >= M) break;
-          float acc = 0.f;
-          for (int s = 0; s < splits; ++s) acc += partial[((size_t)s * m_pad + m) * N + n];
-          Elem<OutT>::store(out + (size_t)m * N + n, acc);
+          const float v = __uint_as_float(r[j]);
+          if (splits == 1) Elem<OutT>::store(out + (size_t)m * N + n, v);
+          else partial[((size_t)split * M + m) * N + n] = v;
         }
       }
-      if (threadIdx.x == 0) counters[tile] = 0;   // ready for the next launch
     }
   }
   tc_fence_before();
@@ -279,9 +268,8 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, in
 }
 
 template <int BN, typename OutT>
-int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, void* out, float* partial,
-                int* counters, int M, int N, int num_kb, int kb_per_split, int splits, dim3 grid,
-                cudaStream_t st) {
+int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, void* out, float* partial, int M,
+                int N, int num_kb, int kb_per_split, int splits, dim3 grid, cudaStream_t st) {
   constexpr size_t smem =
       (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
   auto kern = gemm_swap_kernel<BN, OutT>;
@@ -292,8 +280,8 @@ int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, void* out, float* 
       return DIB_LAUNCH_FAILED;
     attr_set = true;
   }
-  kern<<<grid, THREADS, smem, st>>>(mw, mx, (OutT*)out, partial, counters, M, N, num_kb,
-                                    kb_per_split, splits);
+  dib_launch(kern, dim3(grid), dim3(THREADS), smem, st, mw, mx, (OutT*)out, partial, M, N, num_kb, kb_per_split,
+                                    splits);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -326,14 +314,14 @@ void dib_gemm_bf16_plan(int M, int N, int K, int sm_count, int* bn, int* kb_per_
   *splits = (num_kb + per - 1) / per;
 }
 
-// out[M, N] = x[M, K] * w[N, K]^T, bf16 inputs, float32 accumulation.  out is bf16
-// (out_fp32 = 0) or float32.  partial: float32 scratch for split-k, at least
-// splits * ceil(M / bn) * bn * N floats; counters: int32, one per output tile, zero
-// before the first call (the kernel leaves them zero).  K must be a multiple of 8
-// (TMA wants 16-byte row strides); x, w must be 16-byte aligned.
+// x[M, K] * w[N, K]^T, bf16 inputs, float32 accumulation.  With `splits` == 1 (as
+// dib_gemm_bf16_plan says, or forced by passing partial == nullptr) the product goes to
+// out [M, N], bf16 (out_fp32 = 0) or float32.  Otherwise out is not touched and
+// partial [splits, M, N] float32 receives the partial products, to be added in split
+// order by the reader.  K must be a multiple of 8 (TMA wants 16-byte row strides); x
+// and w must be 16-byte aligned.
 int dib_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K, int out_fp32,
-                  float* partial, long long partial_floats, int* counters, int num_counters,
-                  int sm_count, cudaStream_t st) {
+                  float* partial, int sm_count, cudaStream_t st) {
   if (M == 0 || N == 0) return DIB_OK;
   if (K < 8 || K % 8 != 0) return DIB_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16 != 0) return DIB_BAD_ALIGN;
@@ -341,20 +329,18 @@ int dib_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K, 
   dib_gemm_bf16_plan(M, N, K, sm_count, &bn, &per, &splits);
   const int n_tiles = (N + BM - 1) / BM, m_tiles = (M + bn - 1) / bn;
   const int num_kb = (K + BK - 1) / BK;
-  if (splits > 1 && ((long long)splits * m_tiles * bn * N > partial_floats ||
-                     n_tiles * m_tiles > num_counters)) {
-    splits = 1;            // no room for partial tiles: one CTA walks all of k
+  if (partial == nullptr) {   // the caller wants the finished product: one CTA walks all of k
+    splits = 1;
     per = num_kb;
   }
   if (m_tiles > 65535 || splits > 65535) return DIB_BAD_SIZE;
   CUtensorMap mw, mx;
   if (!make_map(&mw, w, N, K, BM) || !make_map(&mx, x, M, K, bn)) return DIB_LAUNCH_FAILED;
   dim3 grid(n_tiles, m_tiles, splits);
-#define CALL(BNV)                                                                                \
-  (out_fp32 ? launch_swap<BNV, float>(mw, mx, out, partial, counters, M, N, num_kb, per, splits, \
-                                      grid, st)                                                  \
-            : launch_swap<BNV, __nv_bfloat16>(mw, mx, out, partial, counters, M, N, num_kb, per, \
-                                              splits, grid, st))
+#define CALL(BNV)                                                                              \
+  (out_fp32 ? launch_swap<BNV, float>(mw, mx, out, partial, M, N, num_kb, per, splits, grid, st) \
+            : launch_swap<BNV, __nv_bfloat16>(mw, mx, out, partial, M, N, num_kb, per, splits,  \
+                                              grid, st))
   switch (bn) {
     case 16: return CALL(16);
     case 32: return CALL(32);

@@ -15,6 +15,7 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 __global__ void __launch_bounds__(256)
 gemm_fp32_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C,
                  int M, int N, int K) {
+  pdl_prologue();
   __shared__ float sA[BK][BM + 4];
   __shared__ float sW[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -72,7 +73,7 @@ extern "C" int dib_gemm_fp32(const float* A, const float* W, float* C, int M, in
   if (K <= 0) return DIB_BAD_SIZE;
   dim3 grid(ceil_div_host(N, BN), ceil_div_host(M, BM));
   if (grid.y > 65535) return DIB_BAD_SIZE;
-  gemm_fp32_kernel<<<grid, 256, 0, st>>>(A, W, C, M, N, K);
+  dib_launch(gemm_fp32_kernel, dim3(grid), dim3(256), 0, st, A, W, C, M, N, K);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }

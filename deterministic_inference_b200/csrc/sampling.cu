@@ -56,6 +56,7 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 constexpr int INT_MAX_ = 0x7fffffff;
 
 __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
+  pdl_prologue();
   __shared__ Best scratch[32];
   const float* row = logits + (size_t)blockIdx.x * V;
   Best b{-INFINITY, INT_MAX_};
@@ -74,6 +75,7 @@ constexpr int ARGMAX_CHUNK = 4096;
 
 __global__ void argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ pv,
                                       int* __restrict__ pi, int V, int chunks) {
+  pdl_prologue();
   __shared__ Best scratch[32];
   const int r = blockIdx.y, c = blockIdx.x;
   const float* row = logits + (size_t)r * V;
@@ -89,6 +91,7 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, float* _
 
 __global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi,
                                     int* __restrict__ out, int chunks) {
+  pdl_prologue();
   __shared__ Best scratch[32];
   const int r = blockIdx.x;
   Best b{-INFINITY, INT_MAX_};
@@ -113,6 +116,7 @@ __global__ void gumbel_sample_kernel(const float* __restrict__ logits,
                                      const long long* __restrict__ sample_pos,
                                      const unsigned char* __restrict__ keep,
                                      int* __restrict__ out, int V) {
+  pdl_prologue();
   __shared__ Best bscratch[32];
   __shared__ float fscratch[32];
   const int r = blockIdx.x;
@@ -151,7 +155,7 @@ extern "C" {
 int dib_argmax(const float* logits, int* out, int R, int V, cudaStream_t st) {
   if (R == 0) return DIB_OK;
   if (V < 1) return DIB_BAD_SIZE;
-  argmax_kernel<<<R, 1024, 0, st>>>(logits, out, V);
+  dib_launch(argmax_kernel, dim3(R), dim3(1024), 0, st, logits, out, V);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -164,9 +168,9 @@ int dib_argmax_two_stage(const float* logits, float* scratch_v, int* scratch_i, 
   if (R == 0) return DIB_OK;
   if (V < 1 || R > 65535) return DIB_BAD_SIZE;
   const int chunks = (V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
-  argmax_partial_kernel<<<dim3(chunks, R), 256, 0, st>>>(logits, scratch_v, scratch_i, V, chunks);
+  dib_launch(argmax_partial_kernel, dim3(dim3(chunks, R)), dim3(256), 0, st, logits, scratch_v, scratch_i, V, chunks);
   DIB_CHECK_LAUNCH();
-  argmax_final_kernel<<<R, 64, 0, st>>>(scratch_v, scratch_i, out, chunks);
+  dib_launch(argmax_final_kernel, dim3(R), dim3(64), 0, st, scratch_v, scratch_i, out, chunks);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -176,7 +180,7 @@ int dib_gumbel_sample(const float* logits, const float* temperatures, const long
                       int V, cudaStream_t st) {
   if (R == 0) return DIB_OK;
   if (V < 1) return DIB_BAD_SIZE;
-  gumbel_sample_kernel<<<R, 1024, 0, st>>>(logits, temperatures, seeds, sample_pos, keep, out, V);
+  dib_launch(gumbel_sample_kernel, dim3(R), dim3(1024), 0, st, logits, temperatures, seeds, sample_pos, keep, out, V);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }

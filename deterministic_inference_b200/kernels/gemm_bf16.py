@@ -11,26 +11,22 @@ sid/model/qwen3.py:38).
 from __future__ import annotations
 
 import os
-from ctypes import c_int, c_longlong, c_void_p
+from ctypes import byref, c_int, c_void_p
 
 import torch
 
 # rows up to which the package's own kernel is used
 MAX_ROWS = int(os.environ.get("DIB200_GEMM_MAX_ROWS", "128"))
-_PARTIAL_FLOATS = 8 * 1024 * 1024      # split-k scratch per device (32 MiB)
-_NUM_COUNTERS = 16384
 
-_workspace: dict = {}
+_sm_count: dict = {}
 
 
-def _ws(device):
-    ws = _workspace.get(device)
-    if ws is None:
-        ws = (torch.empty(_PARTIAL_FLOATS, dtype=torch.float32, device=device),
-              torch.zeros(_NUM_COUNTERS, dtype=torch.int32, device=device),
-              torch.cuda.get_device_properties(device).multi_processor_count)
-        _workspace[device] = ws
-    return ws
+def _sms(device) -> int:
+    n = _sm_count.get(device)
+    if n is None:
+        n = torch.cuda.get_device_properties(device).multi_processor_count
+        _sm_count[device] = n
+    return n
 
 
 def status() -> int:
@@ -39,19 +35,36 @@ def status() -> int:
     return int(_lib("gemm_bf16").dib_gemm_bf16_status())
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+def plan(m: int, n: int, k: int, device) -> tuple:
+    """(tokens per tile, k-blocks per split, splits) the kernel uses for these sizes."""
+    from .ops import _lib
+    bn, per, splits = c_int(), c_int(), c_int()
+    _lib("gemm_bf16").dib_gemm_bf16_plan(c_int(m), c_int(n), c_int(k), c_int(_sms(device)),
+                                         byref(bn), byref(per), byref(splits))
+    return bn.value, per.value, splits.value
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, allow_split: bool = True):
+    """x [M, K] @ weight[N, K]^T.  Returns a tensor, or, when the kernel splits k and
+    ``allow_split``, an ``ops.SplitSum`` of its float32 partial products."""
     from . import ops
     m, k = x.shape
     n = weight.shape[0]
     if m <= MAX_ROWS and k % 8 == 0 and k >= 8 and out_dtype in (torch.bfloat16, torch.float32) \
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
-        partial, counters, sms = _ws(x.device)
+        lib = ops._lib("gemm_bf16")
+        splits = plan(m, n, k, x.device)[2] if allow_split else 1
+        fp32 = c_int(1 if out_dtype == torch.float32 else 0)
+        if splits > 1:
+            parts = torch.empty(splits, m, n, dtype=torch.float32, device=x.device)
+            st = lib.dib_gemm_bf16(ops._ptr(x), ops._ptr(weight), c_void_p(0), c_int(m), c_int(n),
+                                   c_int(k), fp32, ops._ptr(parts), c_int(_sms(x.device)),
+                                   ops._stream())
+            ops._check(st, "linear(bfloat16)", f"M={m} N={n} K={k}")
+            return ops.SplitSum(parts, out_dtype)
         out = torch.empty(m, n, dtype=out_dtype, device=x.device)
-        st = ops._lib("gemm_bf16").dib_gemm_bf16(
-            ops._ptr(x), ops._ptr(weight), ops._ptr(out), c_int(m), c_int(n), c_int(k),
-            c_int(1 if out_dtype == torch.float32 else 0), ops._ptr(partial),
-            c_longlong(partial.numel()), ops._ptr(counters), c_int(counters.numel()), c_int(sms),
-            ops._stream())
+        st = lib.dib_gemm_bf16(ops._ptr(x), ops._ptr(weight), ops._ptr(out), c_int(m), c_int(n),
+                               c_int(k), fp32, c_void_p(0), c_int(_sms(x.device)), ops._stream())
         ops._check(st, "linear(bfloat16)", f"M={m} N={n} K={k}")
         return out
     ops._launched(1)

@@ -93,6 +93,52 @@ def _lib(name: str) -> ctypes.CDLL:
     return lib
 
 
+# ---------------------------------------------------------------- deferred sums
+
+class SplitSum:
+    """A matrix that exists as ``S`` float32 partial products of a split-k matrix
+    product, ``parts[s]`` of shape [rows, cols], not yet added.  The kernels that
+    read a projection output (residual-add + norm, q/k norm, SiLU gate) take it as
+    it is and add the partials in split order while they load, rounding the sum to
+    ``dtype`` as a stored product would be; anything else gets a plain tensor from
+    ``as_tensor``.  ``hidden`` handed from a block to the next may be one."""
+
+    def __init__(self, parts: torch.Tensor, dtype: torch.dtype):
+        self.parts, self.dtype = parts, dtype
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+    @property
+    def device(self):
+        return self.parts.device
+
+    @property
+    def splits(self) -> int:
+        return self.parts.shape[0]
+
+    def tensor(self) -> torch.Tensor:
+        s, m, n = self.parts.shape
+        out = torch.empty(m, n, dtype=self.dtype, device=self.parts.device)
+        if (m * n) % 4 == 0:
+            st = _lib("elementwise").dib_sum_split(_ptr(self.parts), c_int(s), c_longlong(m * n),
+                                                   _ptr(out), c_longlong(m * n),
+                                                   c_int(_DT[self.dtype]), _stream())
+            _check(st, "sum_split")
+            return out
+        _launched(1)
+        acc = self.parts[0].clone()
+        for i in range(1, s):          # split order
+            acc += self.parts[i]
+        return acc.to(self.dtype)
+
+
+def as_tensor(x):
+    """A plain tensor, whatever ``x`` is."""
+    return x.tensor() if isinstance(x, SplitSum) else x
+
+
 # ---------------------------------------------------------------- embedding
 
 def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
@@ -111,6 +157,7 @@ def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
     """y = x / sqrt(mean(x^2) + eps) * weight over the last dim; weight float32."""
+    x = as_tensor(x)
     _need(x, "x")
     _need(weight, "weight", torch.float32, 1)
     h = x.shape[-1]
@@ -126,7 +173,23 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
 
 def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, eps: float):
     """In place: residual += x (stored rounded); x = rms_norm(unrounded sum).
-    Returns (x, residual)."""
+    Returns (x, residual).  ``x`` may be a ``SplitSum``; the norm is then written to
+    a new tensor."""
+    if isinstance(x, SplitSum):
+        _need(residual, "residual", x.dtype, 2)
+        _need(weight, "weight", torch.float32, 1)
+        s_, rows, h = x.parts.shape
+        if tuple(residual.shape) != (rows, h) or weight.shape[0] != h:
+            raise KernelError(f"add_rms_norm: x {(rows, h)} vs residual {tuple(residual.shape)}, "
+                              f"weight {weight.shape[0]}")
+        if h % 4 == 0 and h <= 4096:
+            out = torch.empty(rows, h, dtype=x.dtype, device=x.device)
+            st = _lib("elementwise").dib_add_rms_norm_split(
+                _ptr(x.parts), c_int(s_), c_longlong(rows * h), _ptr(residual), _ptr(weight),
+                _ptr(out), c_int(rows), c_int(h), c_float(eps), c_int(_DT[x.dtype]), _stream())
+            _check(st, "add_rms_norm(split)", f"row width {h}")
+            return out, residual
+        x = x.tensor()
     _need(x, "x")
     _need(residual, "residual", x.dtype)
     _need(weight, "weight", torch.float32, 1)
@@ -153,11 +216,19 @@ def qk_norm_rope_cache(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, hea
     given), q to the returned tensor [T, Hq, D], k and v into the token's slot of
     the paged cache [pages, 2, Hkv, page_size, D] (when a cache is given;
     slot = page * page_size + offset, negative = skip)."""
-    _need(qkv, "qkv", None, 2)
-    t = qkv.shape[0]
+    parts = None
+    if isinstance(qkv, SplitSum):
+        if head_dim in (64, 128, 256) and (cos_sin is None or cos_sin.shape[1] == head_dim):
+            parts = qkv
+        else:
+            qkv = qkv.tensor()
+    if parts is None:
+        _need(qkv, "qkv", None, 2)
+    t, got_width = qkv.shape
+    act_dtype, device = qkv.dtype, qkv.device
     width = (num_heads + 2 * num_kv_heads) * head_dim
-    if qkv.shape[1] != width:
-        raise KernelError(f"qkv has width {qkv.shape[1]}, expected {width}")
+    if got_width != width:
+        raise KernelError(f"qkv has width {got_width}, expected {width}")
     _need(positions, "positions", torch.int32, 1)
     for w, n in ((q_norm_weight, "q_norm_weight"), (k_norm_weight, "k_norm_weight")):
         if w is not None:
@@ -170,13 +241,22 @@ def qk_norm_rope_cache(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, hea
         max_pos, rotary_dim = cos_sin.shape
     num_pages = 0
     if kv_cache is not None:
-        _need(kv_cache, "kv_cache", qkv.dtype, 5)
+        _need(kv_cache, "kv_cache", act_dtype, 5)
         _need(slot_mapping, "slot_mapping", torch.int32, 1)
         if tuple(kv_cache.shape[1:]) != (2, num_kv_heads, page_size, head_dim):
             raise KernelError(f"kv_cache shape {tuple(kv_cache.shape)} does not match "
                               f"[pages, 2, {num_kv_heads}, {page_size}, {head_dim}]")
         num_pages = kv_cache.shape[0]
-    q = torch.empty(t, num_heads, head_dim, dtype=qkv.dtype, device=qkv.device)
+    q = torch.empty(t, num_heads, head_dim, dtype=act_dtype, device=device)
+    if parts is not None:
+        st = _lib("elementwise").dib_qk_norm_rope_cache_split(
+            c_void_p(0), _ptr(parts.parts), c_int(parts.splits), c_longlong(t * width), _ptr(q),
+            _ptr(kv_cache), _ptr(q_norm_weight), _ptr(k_norm_weight), c_float(eps), _ptr(cos_sin),
+            c_int(rotary_dim), c_int(max_pos), _ptr(positions), _ptr(slot_mapping), c_int(t),
+            c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
+            c_longlong(num_pages), c_int(_DT[parts.dtype]), _stream())
+        _check(st, "qk_norm_rope_cache(split)", f"head_dim {head_dim}")
+        return q
     st = _lib("elementwise").dib_qk_norm_rope_cache(
         _ptr(qkv), _ptr(q), _ptr(kv_cache), _ptr(q_norm_weight), _ptr(k_norm_weight), c_float(eps),
         _ptr(cos_sin), c_int(rotary_dim), c_int(max_pos), _ptr(positions), _ptr(slot_mapping),
@@ -241,6 +321,16 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float,
 
 def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
     """[T, 2I] = [gate | up] -> silu(gate) * up, [T, I]."""
+    if isinstance(gate_up, SplitSum):
+        s_, t, two_i = gate_up.parts.shape
+        if two_i % 8 == 0:
+            out = torch.empty(t, two_i // 2, dtype=gate_up.dtype, device=gate_up.device)
+            st = _lib("elementwise").dib_silu_mul_split(
+                _ptr(gate_up.parts), c_int(s_), c_longlong(t * two_i), _ptr(out), c_int(t),
+                c_int(two_i // 2), c_int(_DT[gate_up.dtype]), _stream())
+            _check(st, "silu_mul(split)")
+            return out
+        gate_up = gate_up.tensor()
     _need(gate_up, "gate_up", None, 2)
     t, two_i = gate_up.shape
     if two_i % 2:
@@ -254,6 +344,7 @@ def silu_mul(gate_up: torch.Tensor) -> torch.Tensor:
 
 def gather_rows(x: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
     """out[r] = x[index[r]]; index int32."""
+    x = as_tensor(x)
     _need(x, "x", None, 2)
     _need(index, "index", torch.int32, 1)
     out = torch.empty(index.shape[0], x.shape[1], dtype=x.dtype, device=x.device)
@@ -272,7 +363,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tenso
     float32: the package's own CUDA-core kernel (plain FMA, no TF32, fixed k
     order, so a row's bits do not depend on the batch).  bfloat16: float32
     accumulation on the tensor cores; ``out_dtype=torch.float32`` returns the
-    accumulator unrounded (used for the logits)."""
+    accumulator unrounded (used for the logits).  With few rows and a split of k the
+    bfloat16 product comes back as a ``SplitSum`` (see there)."""
+    x = as_tensor(x)
     _need(x, "x", None, 2)
     _need(weight, "weight", x.dtype, 2)
     m, k = x.shape

@@ -8,6 +8,12 @@ Mixer(Part)          cache_spec() -> PagedKVSpec | StateSpec | None
 FeedForward(Part)    forward(x [T, H]) -> [T, H]
 Block                forward(hidden, residual, step, cache) -> (hidden, residual)
 
+What a mixer or feed-forward returns, and what a block hands on as ``hidden``, is a
+tensor or an ``ops.SplitSum`` (the float32 partial products of a matrix product
+whose k was split, which the next norm adds while it loads them); the package's
+kernels take either, and ``ops.as_tensor`` gives a plain tensor to code that needs
+one.  The INPUT of a mixer or feed-forward is always a plain tensor (a norm's output).
+
 ``step`` is the step's ``StepBatch`` (tokens, positions, sequence boundaries,
 state slots); ``cache`` is the view of the one cache the schedule entry names
 (``CacheView``: the layer's page pool with its group's block table and slot

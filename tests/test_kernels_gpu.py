@@ -155,8 +155,10 @@ def test_linear_bf16(m, n, k):
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (0.05 * torch.randn(n, k, device="cuda")).to(torch.bfloat16)
     want = x.float() @ w.float().T
-    torch.testing.assert_close(ops().linear(x, w).float(), want, atol=2e-2, rtol=2e-2)
-    got32 = ops().linear(x, w, out_dtype=torch.float32)
+    got = ops().linear(x, w)
+    assert isinstance(got, ops().SplitSum) == (m <= 128 and gemm_bf16.plan(m, n, k, x.device)[2] > 1)
+    torch.testing.assert_close(ops().as_tensor(got).float(), want, atol=2e-2, rtol=2e-2)
+    got32 = ops().as_tensor(ops().linear(x, w, out_dtype=torch.float32))
     assert got32.dtype == torch.float32
     torch.testing.assert_close(got32, want, atol=1e-3, rtol=1e-3)
     assert gemm_bf16.status() == 0
@@ -168,10 +170,51 @@ def test_linear_bf16_row_does_not_depend_on_batch():
     torch.manual_seed(9)
     x = torch.randn(100, 2048, device="cuda").to(torch.bfloat16)
     w = (0.05 * torch.randn(1024, 2048, device="cuda")).to(torch.bfloat16)
-    full = ops().linear(x, w)
+    lin = lambda a: ops().as_tensor(ops().linear(a, w))
+    full = lin(x)
     for r in (0, 15, 16, 99):
-        assert torch.equal(ops().linear(x[r:r + 1].contiguous(), w)[0], full[r])
-    assert torch.equal(ops().linear(x, w), full)
+        assert torch.equal(lin(x[r:r + 1].contiguous())[0], full[r])
+    assert torch.equal(lin(x), full)
+
+
+@pytest.mark.parametrize("m", [1, 8, 50])
+def test_readers_of_split_k_partials(m):
+    """The kernels that take a projection output as split-k partials give what they
+    give on the summed tensor."""
+    o = ops()
+    torch.manual_seed(10)
+    h, i, hq, hkv, d = 1024, 3072, 16, 8, 128
+    x = torch.randn(m, h, device="cuda").to(torch.bfloat16)
+    res = torch.randn(m, h, device="cuda").to(torch.bfloat16)
+    wn = torch.randn(h, device="cuda")
+    mk = lambda n, k: (0.05 * torch.randn(n, k, device="cuda")).to(torch.bfloat16)
+    # residual-add + norm reading the output projection
+    a = torch.randn(m, 2048, device="cuda").to(torch.bfloat16)
+    wo = mk(h, 2048)
+    y = o.linear(a, wo)
+    assert isinstance(y, o.SplitSum)
+    got, r1 = o.add_rms_norm(y, res.clone(), wn, 1e-6)
+    want, r2 = o.add_rms_norm(y.tensor(), res.clone(), wn, 1e-6)
+    assert torch.equal(got, want) and torch.equal(r1, r2)
+    # SiLU gate reading gate_up
+    gu = o.linear(x, mk(2 * i, h))
+    assert isinstance(gu, o.SplitSum)
+    assert torch.equal(o.silu_mul(gu), o.silu_mul(gu.tensor()))
+    # q/k norm + rotation + cache write reading qkv
+    qkv = o.linear(x, mk((hq + 2 * hkv) * d, h))
+    assert isinstance(qkv, o.SplitSum)
+    half = d // 2
+    inv = 1.0 / (1e6 ** (torch.arange(half, dtype=torch.float32, device="cuda") / half))
+    f = torch.outer(torch.arange(64, dtype=torch.float32, device="cuda"), inv)
+    table = torch.cat([f.cos(), f.sin()], -1).contiguous()
+    pos = torch.randint(0, 64, (m,), device="cuda", dtype=torch.int32)
+    slots = (torch.randperm(5 * 16, device="cuda")[:m] + 16).to(torch.int32)
+    c1 = torch.zeros(7, 2, hkv, 16, d, device="cuda", dtype=torch.bfloat16)
+    c2 = c1.clone()
+    qn, kn = torch.randn(d, device="cuda"), torch.randn(d, device="cuda")
+    q1 = o.qk_norm_rope_cache(qkv, hq, hkv, d, qn, kn, 1e-6, table, pos, c1, slots, 16)
+    q2 = o.qk_norm_rope_cache(qkv.tensor(), hq, hkv, d, qn, kn, 1e-6, table, pos, c2, slots, 16)
+    assert torch.equal(q1, q2) and torch.equal(c1, c2)
 
 
 # ------------------------------------------------------------------ attention
