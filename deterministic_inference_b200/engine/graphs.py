@@ -57,7 +57,10 @@ class DecodeGraphs:
     def _key(self, entries) -> tuple:
         ps = self.cache.page_size
         width = max(-(-(e.num_computed + 1) // ps) for e in entries)
-        return (_bucket(len(entries)), min(_bucket(width, self.min_width), self.cache.max_blocks))
+        # block-table width: powers of two up to 32 pages, then multiples of 32 (grids
+        # sized for the width's longest sequence should not be mostly empty)
+        wb = _bucket(width, self.min_width) if width <= 32 else -(-width // 32) * 32
+        return (_bucket(len(entries)), min(wb, self.cache.max_blocks))
 
     def _fill(self, host: np.ndarray, lay: PackedLayout, entries) -> None:
         """Packed metadata of a pure-decode step, padded to the bucket."""

@@ -10,7 +10,8 @@ The decode kernel writes per-split partial outputs to scratch memory
 
 from __future__ import annotations
 
-from ctypes import c_float, c_int, c_void_p
+import os
+from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
@@ -48,8 +49,10 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
             ws = (torch.empty(nd, hq, max_splits, d, dtype=torch.float32, device=q.device),
                   torch.empty(nd, hq, max_splits, dtype=torch.float32, device=q.device))
             meta.scratch[("decode_ws", hq, d, max_splits)] = ws
+        use_tma = os.environ.get("DIB200_DECODE_TMA", "1") != "0"
         st = lib.dib_decode_attention_bf16(
-            _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(bt), c_int(bt.shape[1]), _ptr(meta.seq_lens),
+            _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0] if use_tma else 0),
+            _ptr(bt), c_int(bt.shape[1]), _ptr(meta.seq_lens),
             _ptr(ws[0]), _ptr(ws[1]), c_int(nd), c_int(max_splits), c_int(hq), c_int(hkv), c_int(d),
             c_int(page_size), c_float(scale), c_int(window), _stream())
         _check(st, "decode_attention_bf16", f"heads {hq}/{hkv}, head_dim {d}", kernels=2)
