@@ -40,7 +40,11 @@ decode_attention_stage1_tma_kernel(const __grid_constant__ CUtensorMap map,
                                    const int* __restrict__ seq_lens, float* __restrict__ part_o,
                                    float* __restrict__ part_lse, int max_splits, int Hq, int Hkv,
                                    int page_size, float scale, int window) {
-  pdl_prologue();
+  // Keys and values of earlier steps do not depend on the kernel before this one
+  // (which only writes the new token's slot), nor do the block table and the
+  // lengths: their loads start at once; only the page that holds the new token, and
+  // the query, wait for that kernel.
+  pdl_trigger();
   constexpr int HALVES = D / 64;
   constexpr int TILE = DEC_SPLIT * D;   // elements of the K (or V) tile
   extern __shared__ unsigned char smem_dyn[];
@@ -81,14 +85,17 @@ decode_attention_stage1_tma_kernel(const __grid_constant__ CUtensorMap map,
     mbar_expect_tx(&bars[0], (unsigned)valid_pages * page_size * D * 2);
     mbar_expect_tx(&bars[1], (unsigned)valid_pages * page_size * D * 2);
   }
-  // thread t issues the copy of (page t / (2*HALVES), key-or-value, 64-column half)
-  if (threadIdx.x < pages * 2 * HALVES && pi < valid_pages) {
-    const int kv = (threadIdx.x / HALVES) & 1;
-    const int half = threadIdx.x % HALVES;
-    const int row0 = (((page * 2 + kv) * Hkv) + kvh) * page_size;
-    __nv_bfloat16* dst = (kv ? sV : sK) + half * (DEC_SPLIT * 64) + pi * page_size * 64;
-    tma_load_2d(dst, &map, half * 64, row0, &bars[kv]);
-  }
+  // thread t issues the copy of (page t / (2*HALVES), key-or-value, 64-column half):
+  // before the wait if the page lies wholly before the new token's position
+  const bool issuer = threadIdx.x < pages * 2 * HALVES && pi < valid_pages;
+  const bool early = (k0 / page_size + pi) < pos / page_size;
+  const int kv = (threadIdx.x / HALVES) & 1;
+  const int half = threadIdx.x % HALVES;
+  const int row0 = (((page * 2 + kv) * Hkv) + kvh) * page_size;
+  __nv_bfloat16* dst = (kv ? sV : sK) + half * (DEC_SPLIT * 64) + pi * page_size * 64;
+  if (issuer && early) tma_load_2d(dst, &map, half * 64, row0, &bars[kv]);
+  pdl_wait();
+  if (issuer && !early) tma_load_2d(dst, &map, half * 64, row0, &bars[kv]);
 
   unsigned qf[D / 16][4];
   {
