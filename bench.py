@@ -292,10 +292,10 @@ def main() -> int:
         for _ in range(a.warmup):
             engine.step()
         e2e_ms = timed(lambda: [engine.step() for _ in range(a.steps)])
-        assert all(r.num_output >= a.steps for r in engine.scheduler.running)
+        assert all(r.num_output + r.num_pending >= a.steps for r in engine.scheduler.running)
         e2e = {"value": a.batch * a.steps / (e2e_ms / 1e3), "unit": "tokens/s",
                "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": a.batch * 4}
-        while engine.scheduler.has_work():
+        while engine.has_work():
             engine.step()
 
     line = {

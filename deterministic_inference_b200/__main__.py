@@ -28,7 +28,8 @@ def _cmd_generate(a) -> int:
     kw = dict(dtype=a.dtype, kv_pool_tokens=a.kv_pool_tokens, page_size=a.page_size,
               max_reqs=a.max_reqs, max_seq_len=a.max_seq_len,
               max_prefill_tokens=a.max_prefill_tokens, max_decode_batch=a.max_decode_batch,
-              cuda_graphs=not a.no_cuda_graphs, device=a.device)
+              cuda_graphs=not a.no_cuda_graphs, async_scheduling=not a.no_async_scheduling,
+              device=a.device)
     if a.model is not None:
         cfg = EngineConfig(model_path=a.model, **kw)
     else:
@@ -99,6 +100,7 @@ def main(argv=None) -> int:
     g.add_argument("--max-prefill-tokens", type=int, default=8192)
     g.add_argument("--max-decode-batch", type=int, default=256)
     g.add_argument("--no-cuda-graphs", action="store_true")
+    g.add_argument("--no-async-scheduling", action="store_true")
     g.add_argument("--device", default="cuda")
     g.set_defaults(fn=_cmd_generate)
 

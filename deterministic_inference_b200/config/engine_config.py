@@ -35,6 +35,8 @@ class EngineConfig:
     max_decode_batch: int = 256          # sequences running at a time
 
     cuda_graphs: bool = True             # replay pure-decode steps as CUDA graphs
+    async_scheduling: bool = True        # sampled tokens stay on the device for the next step;
+                                         # the host reads them one step late
     device: str = "cuda"
 
     def __post_init__(self):

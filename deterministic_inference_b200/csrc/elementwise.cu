@@ -468,6 +468,19 @@ __global__ void silu_mul_split_kernel(const float* __restrict__ parts, int S, lo
   *reinterpret_cast<Pack<T, 4>*>(out + t * I + i) = o;
 }
 
+// ------------------------------------------------ token hand-over on the device
+// ids[dst[i]] = prev[src[i]] for every i with dst[i] >= 0: the tokens a step sampled
+// become the next step's inputs without a trip to the host.
+__global__ void patch_ids_kernel(int* __restrict__ ids, const int* __restrict__ dst,
+                                 const int* __restrict__ src, const int* __restrict__ prev, int n,
+                                 int num_ids, int num_prev) {
+  pdl_prologue();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int d = dst[i], sidx = src[i];
+  if (d >= 0 && d < num_ids && sidx >= 0 && sidx < num_prev) ids[d] = prev[sidx];
+}
+
 // ---------------------------------------------------------------- row gather
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ idx,
@@ -752,6 +765,15 @@ int dib_silu_mul_split(const float* parts, int S, long long split_stride, void* 
     dib_launch(silu_mul_split_kernel<__nv_bfloat16>, dim3(ceil_div_host(v, th)), dim3(th), 0, st, 
         parts, S, split_stride, (__nv_bfloat16*)out, v, I);
   else return DIB_BAD_DTYPE;
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+int dib_patch_ids(int* ids, const int* dst, const int* src, const int* prev, int n, int num_ids,
+                  int num_prev, cudaStream_t st) {
+  if (n == 0) return DIB_OK;
+  dib_launch(patch_ids_kernel, dim3(ceil_div_host(n, 128)), dim3(128), 0, st, ids, dst, src, prev, n,
+             num_ids, num_prev);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }

@@ -30,6 +30,8 @@ class SequenceInput:
     tokens: list              # its next tokens
     num_computed: int         # tokens of it already in the cache
     want: list = field(default_factory=list)   # places among ``tokens`` whose logits are wanted
+    pending_row: int = -1     # >= 0: the LAST of ``tokens`` is not known on the host; it is row
+                              # ``pending_row`` of the tokens the previous step sampled
 
 
 @dataclass
@@ -68,6 +70,9 @@ class StepBatch:
     groups: dict                     # group key -> AttentionMeta
     logit_rows: list                 # per input entry (caller's order): its rows of the logits
     order: list                      # batch order -> index of the caller's entry
+    patch_dst: Optional[torch.Tensor] = None   # int32 [B]: place in input_ids, or -1
+    patch_src: Optional[torch.Tensor] = None   # int32 [B]: row of the previous step's tokens
+    num_patches: int = 0
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -84,7 +89,8 @@ class PackedLayout:
         self.off = {}
         cur = 0
         for name, n in (("input_ids", t), ("positions", t), ("token_seq", t), ("cu_q_lens", b + 1),
-                        ("seq_lens", b), ("state_slots", b), ("logit_indices", r)):
+                        ("seq_lens", b), ("state_slots", b), ("logit_indices", r),
+                        ("patch_dst", b), ("patch_src", b)):
             self.off[name] = (cur, n)
             cur = _align(cur + n)
         for gi in range(num_groups):
@@ -116,7 +122,8 @@ def step_views(td: torch.Tensor, lay: PackedLayout, group_list: list, q_lens: li
         token_seq=lay.seg(td, "token_seq"), cu_q_lens=lay.seg(td, "cu_q_lens"),
         seq_lens=lay.seg(td, "seq_lens"), state_slots=lay.seg(td, "state_slots"),
         logit_indices=lay.seg(td, "logit_indices"), q_lens=q_lens, kv_lens=kv_lens, slots=slots,
-        groups=groups, logit_rows=logit_rows, order=order)
+        groups=groups, logit_rows=logit_rows, order=order,
+        patch_dst=lay.seg(td, "patch_dst"), patch_src=lay.seg(td, "patch_src"))
 
 
 def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatch:
@@ -169,6 +176,14 @@ def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatc
     slots = [e.slot for e in seqs]
     lay.seg(host, "state_slots")[:] = slots
     lay.seg(host, "logit_indices")[:] = logit_index
+    pdst, psrc = lay.seg(host, "patch_dst"), lay.seg(host, "patch_src")
+    pdst[:] = -1
+    num_patches = 0
+    for bi, e in enumerate(seqs):
+        if e.pending_row >= 0:
+            pdst[bi] = int(cu[bi + 1]) - 1       # the sequence's last token
+            psrc[bi] = e.pending_row
+            num_patches += 1
     for gi, g in enumerate(group_list):
         lay.seg(host, ("bt", gi))[:] = cache.block_table(g, slots, width).reshape(-1)
         sm = lay.seg(host, ("sm", gi))
@@ -186,4 +201,6 @@ def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatc
         td = th.to(dev, non_blocking=True)
     else:
         td = th
-    return step_views(td, lay, group_list, q_lens, kv_lens, slots, num_decode, logit_rows, order)
+    batch = step_views(td, lay, group_list, q_lens, kv_lens, slots, num_decode, logit_rows, order)
+    batch.num_patches = num_patches
+    return batch

@@ -34,6 +34,27 @@ class RequestOutput:
     num_preemptions: int = 0
 
 
+class _InFlight:
+    """The tokens a step sampled, on their way to the host."""
+
+    def __init__(self, tokens_dev: torch.Tensor, row_req: list):
+        self.tokens_dev, self.row_req = tokens_dev, row_req
+        self.row_of = {r.rid: i for i, r in enumerate(row_req)}
+        self.host = None
+        self.event = None
+        if tokens_dev.is_cuda:
+            self.host = torch.empty(tokens_dev.shape, dtype=tokens_dev.dtype, pin_memory=True)
+            self.host.copy_(tokens_dev, non_blocking=True)
+            self.event = torch.cuda.Event()
+            self.event.record()
+
+    def read(self) -> list:
+        if self.host is None:
+            return self.tokens_dev.tolist()
+        self.event.synchronize()
+        return self.host.tolist()
+
+
 class Engine:
     def __init__(self, cfg: EngineConfig):
         self.cfg = cfg
@@ -46,6 +67,8 @@ class Engine:
         self._next_rid = 0
         self._done: dict[int, Request] = {}
         self._pool_capacity = self.cache.usable_pages() * cfg.page_size
+        self._inflight = None
+        self.async_scheduling = cfg.async_scheduling
         self.decode_graphs = None
         if cfg.cuda_graphs and self.runner.device.type == "cuda":
             from .graphs import DecodeGraphs
@@ -110,7 +133,7 @@ class Engine:
                 rids.append(self.add_request(prompt=p, params=sp, chat=chat))
             else:
                 rids.append(self.add_request(prompt_ids=p, params=sp))
-        while self.scheduler.has_work():
+        while self.has_work():
             self.step()
         return [self._output(self._done.pop(rid)) for rid in rids]
 
@@ -121,8 +144,17 @@ class Engine:
     # ---- one step ----------------------------------------------------------------
 
     def step(self) -> None:
+        """Schedule, run the batch, sample; read the tokens of the step BEFORE this
+        one.  With ``async_scheduling`` the tokens a step samples stay on the device:
+        the next step takes them as inputs there (``pending_row``), and the host reads
+        them one step late, while the GPU already runs that next step.  A request
+        that turns out to have stopped on an end-of-sequence token has then been fed
+        one token too many; that result is dropped."""
         sched = self.scheduler.schedule()
         if not sched:
+            if self._inflight is not None:
+                self._collect()
+                return
             if self.scheduler.waiting and not self.scheduler.running:
                 head = self.scheduler.waiting[0]
                 raise RuntimeError(
@@ -130,33 +162,52 @@ class Engine:
                     f"{min(head.remaining, self.scheduler.token_budget)} tokens and the pool has "
                     f"{self.cache.num_free_pages()} free pages of {self.cfg.page_size}")
             return
-        reqs = [s.request for s in sched]
+        prev = self._inflight
         entries = []
-        sampling = []           # (request, row order) of entries that sample
         for s in sched:
             r, n = s.request, s.num_tokens
             last = r.num_computed + n == r.total_len
+            pending_row = prev.row_of[r.rid] if (last and r.num_pending and prev is not None) else -1
             entries.append(SequenceInput(r.slot, r.next_tokens(n), r.num_computed,
-                                         [n - 1] if last else []))
+                                         [n - 1] if last else [], pending_row))
+        prev_tokens = prev.tokens_dev if prev is not None else None
         if self.decode_graphs is not None and self.decode_graphs.usable(entries):
-            logits, rows = self.decode_graphs.run(entries)
+            logits, rows = self.decode_graphs.run(entries, prev_tokens)
         else:
-            logits, batch = self.runner.step(entries)
+            logits, batch = self.runner.step(entries, prev_tokens)
             rows = batch.logit_rows
-        # rows of the logits in batch order -> requests
         row_req: list = [None] * logits.shape[0]
         for i, s in enumerate(sched):
             s.request.num_computed += s.num_tokens
             for row in rows[i]:
                 row_req[row] = s.request
+        flight = None
         if row_req:
-            tokens = sample(logits, [r.params for r in row_req],
-                            [r.total_len for r in row_req]).tolist()
-            for r, tok in zip(row_req, tokens):
-                r.output_ids.append(int(tok))
-                r.check_finished()
+            # the generated token's position is the sequence's length so far
+            tokens_dev = sample(logits, [r.params for r in row_req], [r.total_len for r in row_req])
+            for r in row_req:
+                r.num_pending += 1
+            flight = _InFlight(tokens_dev, row_req)
+        if prev is not None:
+            self._collect()                  # the step before this one
+        self._inflight = flight
+        if flight is not None and not self.async_scheduling:
+            self._collect()
+
+    def _collect(self) -> None:
+        """Read the in-flight step's tokens, give them to their requests, retire."""
+        flight, self._inflight = self._inflight, None
+        for r, tok in zip(flight.row_req, flight.read()):
+            r.num_pending -= 1
+            if r.finished_reason is not None:
+                continue                     # it had stopped already: this token is dropped
+            r.output_ids.append(int(tok))
+            r.check_finished()
         for req in self.scheduler.release_finished():
             self._done[req.rid] = req
+
+    def has_work(self) -> bool:
+        return self.scheduler.has_work() or self._inflight is not None
 
     def _output(self, req: Request) -> RequestOutput:
         text = ""

@@ -73,7 +73,11 @@ class DecodeGraphs:
         seq_lens = lay.seg(host, "seq_lens")
         seq_lens[:] = 1
         slots = lay.seg(host, "state_slots")
+        pdst, psrc = lay.seg(host, "patch_dst"), lay.seg(host, "patch_src")
+        pdst[:] = -1
         for i, e in enumerate(entries):
+            if e.pending_row >= 0:
+                pdst[i], psrc[i] = i, e.pending_row
             ids[i] = e.tokens[0]
             pos[i] = e.num_computed
             seq_lens[i] = e.num_computed + 1
@@ -119,7 +123,7 @@ class DecodeGraphs:
     # ---- replay -------------------------------------------------------------------
 
     @torch.inference_mode()
-    def run(self, entries):
+    def run(self, entries, prev_tokens=None):
         """Same contract as ``ModelRunner.step`` for a pure-decode batch: returns
         (logits [B, V], rows per entry)."""
         cache = self.cache
@@ -132,6 +136,10 @@ class DecodeGraphs:
             cap = self._capture(key, entries)
         self._fill(cap.host_meta.numpy(), cap.layout, entries)
         cap.static_meta.copy_(cap.host_meta, non_blocking=True)
+        if any(e.pending_row >= 0 for e in entries):
+            from ..kernels import ops
+            ops.patch_token_ids(cap.batch.input_ids, cap.batch.patch_dst, cap.batch.patch_src,
+                                prev_tokens)
         cap.graph.replay()
         for e in entries:
             cache.release_passed(e.slot, e.num_computed + 1)

@@ -37,6 +37,7 @@ class Request:
         self.finished_reason: Optional[str] = None
         self.slot: int = -1
         self.num_computed = 0
+        self.num_pending = 0          # tokens sampled on the device, not yet read by the host
         self.num_preemptions = 0
         self.admit_order = -1
 
@@ -50,7 +51,13 @@ class Request:
 
     @property
     def total_len(self) -> int:
-        return len(self.prompt_ids) + len(self.output_ids)
+        return len(self.prompt_ids) + len(self.output_ids) + self.num_pending
+
+    @property
+    def done_generating(self) -> bool:
+        """All the tokens it may generate are sampled (some perhaps not yet read)."""
+        return self.finished_reason is not None or \
+            len(self.output_ids) + self.num_pending >= self.params.max_new_tokens
 
     @property
     def remaining(self) -> int:
@@ -59,11 +66,13 @@ class Request:
         return self.total_len - self.num_computed
 
     def next_tokens(self, n: int) -> list:
+        """The next n token ids; a token not yet read from the device is given as 0
+        (the step patches it in on the device)."""
         c = self.num_computed
         p = self.prompt_len
         if c + n <= p:
             return self.prompt_ids[c:c + n]
-        return (self.prompt_ids + self.output_ids)[c:c + n]
+        return (self.prompt_ids + self.output_ids + [0] * self.num_pending)[c:c + n]
 
     def check_finished(self) -> None:
         """sid/engine/request.py:84-95: EOS (unless ignore_eos) -> "stop";

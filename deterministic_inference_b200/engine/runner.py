@@ -56,14 +56,19 @@ class ModelRunner:
         self.tokens_run = 0
 
     @torch.inference_mode()
-    def step(self, entries: list[SequenceInput]):
+    def step(self, entries: list[SequenceInput], prev_tokens=None):
         """Returns (logits float32 [R, V], the StepBatch).  Row order: the wanted
         places of the batch's sequences in batch order; ``batch.logit_rows[i]``
-        are the rows of the caller's i-th entry."""
+        are the rows of the caller's i-th entry.  ``prev_tokens`` (int32, on the
+        device): the tokens the previous step sampled, for entries whose last token
+        is still there (``pending_row``)."""
         for e in entries:
             self.cache.allocate(e.slot, e.num_computed + len(e.tokens))
         self.cache.reset_fresh_state()
         batch = build_step_batch(entries, self.cache, self.device)
+        if batch.num_patches:
+            from ..kernels import ops
+            ops.patch_token_ids(batch.input_ids, batch.patch_dst, batch.patch_src, prev_tokens)
         logits = self.model.forward(batch, self.cache)
         for e in entries:
             self.cache.release_passed(e.slot, e.num_computed + len(e.tokens))

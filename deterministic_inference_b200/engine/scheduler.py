@@ -72,7 +72,7 @@ class Scheduler:
         # 1. running requests, decoding ones first, each group in admission order
         order = sorted(self.running, key=lambda r: (r.remaining != 1, r.admit_order))
         for req in order:
-            if req.state != RequestState.RUNNING or budget <= 0:
+            if req.state != RequestState.RUNNING or budget <= 0 or req.done_generating:
                 continue
             n = min(req.remaining, budget)
             while not self.cache.can_allocate(req.slot, req.num_computed + n):

@@ -153,6 +153,20 @@ def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def patch_token_ids(input_ids: torch.Tensor, patch_dst: torch.Tensor, patch_src: torch.Tensor,
+                    prev_tokens: torch.Tensor) -> None:
+    """input_ids[patch_dst[i]] = prev_tokens[patch_src[i]] where patch_dst[i] >= 0 (all
+    int32): the tokens the previous step sampled become inputs on the device."""
+    for t, n in ((input_ids, "input_ids"), (patch_dst, "patch_dst"), (patch_src, "patch_src"),
+                 (prev_tokens, "prev_tokens")):
+        _need(t, n, torch.int32, 1)
+    st = _lib("elementwise").dib_patch_ids(_ptr(input_ids), _ptr(patch_dst), _ptr(patch_src),
+                                           _ptr(prev_tokens), c_int(patch_dst.shape[0]),
+                                           c_int(input_ids.shape[0]), c_int(prev_tokens.shape[0]),
+                                           _stream())
+    _check(st, "patch_token_ids")
+
+
 # ---------------------------------------------------------------- norms
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:

@@ -66,7 +66,9 @@ def test_entry_point_matches_plain_generation(tiny_model_dirs, torch_ops):
         sp = SamplingParams(temperature=temp, seed=7, max_new_tokens=8, ignore_eos=True, **kw)
         want = [plain_qwen3.generate(cfg, w, p, 8, temp, 7, **kw) for p in prompts]
         for ekw in (dict(kv_pool_tokens=1024), dict(kv_pool_tokens=1024, max_prefill_tokens=8),
-                    dict(kv_pool_tokens=64, max_prefill_tokens=16)):
+                    dict(kv_pool_tokens=64, max_prefill_tokens=16),
+                    dict(kv_pool_tokens=1024, async_scheduling=False),
+                    dict(kv_pool_tokens=64, max_prefill_tokens=16, async_scheduling=False)):
             eng = Engine(EngineConfig(model_path=str(d), dtype="float32", device="cpu", page_size=16,
                                       max_reqs=8, max_seq_len=256, **ekw))
             outs = eng.generate(prompts, sp)
@@ -76,15 +78,23 @@ def test_entry_point_matches_plain_generation(tiny_model_dirs, torch_ops):
             assert eng.cache.num_free_pages() == eng.cache.usable_pages()
 
 
-def test_eos_ends_a_request(tiny_model_dirs, torch_ops):
+@pytest.mark.parametrize("async_scheduling", [True, False])
+def test_eos_ends_a_request(tiny_model_dirs, torch_ops, async_scheduling):
+    """With tokens read one step late a request that stops on a token has been fed one
+    token too many; nothing of that shows in its output or in the cache's books."""
     d = tiny_model_dirs["a"]
     cfg, w = plain_qwen3.read_model_dir(d)
-    prompt = [3, 1, 4, 1, 5]
-    free = plain_qwen3.generate(cfg, w, prompt, 6)
+    prompts = [[3, 1, 4, 1, 5], [9, 2, 6, 5, 3, 5, 8]]
+    free = [plain_qwen3.generate(cfg, w, p, 6) for p in prompts]
     eng = Engine(EngineConfig(model_path=str(d), dtype="float32", device="cpu", kv_pool_tokens=256,
-                              max_reqs=4, max_seq_len=256))
-    out = eng.generate([prompt], SamplingParams(max_new_tokens=6, stop_token_ids=[free[2]]))[0]
-    assert out.token_ids == free[:3] and out.finish_reason == "stop"
+                              max_reqs=4, max_seq_len=256, async_scheduling=async_scheduling))
+    outs = eng.generate(prompts, [SamplingParams(max_new_tokens=6, stop_token_ids=[free[0][2]]),
+                                  SamplingParams(max_new_tokens=6, ignore_eos=True)])
+    cut = free[0].index(free[0][2]) + 1
+    assert outs[0].token_ids == free[0][:cut] and outs[0].finish_reason == "stop"
+    assert outs[1].token_ids == free[1] and outs[1].finish_reason == "length"
+    eng.cache.check_invariants()
+    assert eng.cache.num_free_pages() == eng.cache.usable_pages() and not eng.has_work()
 
 
 def test_add_request_refuses_what_can_never_run(tiny_model_dirs, torch_ops):

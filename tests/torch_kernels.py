@@ -21,6 +21,11 @@ def embedding(ids, table):
     return table[ids.long()]
 
 
+def patch_token_ids(input_ids, patch_dst, patch_src, prev_tokens):
+    ok = patch_dst >= 0
+    input_ids[patch_dst[ok].long()] = prev_tokens[patch_src[ok].long()]
+
+
 def _rms(x32, w, eps):
     """sid/kernels/rmsnorm.py:14-24"""
     var = (x32 * x32).mean(dim=-1, keepdim=True)
@@ -159,5 +164,5 @@ def gumbel_sample(logits, temperatures, seeds, sample_positions, keep=None):
     return torch.where(temperatures > 0, sampled, greedy).to(torch.int32)
 
 
-ALL = ("embedding", "rms_norm", "add_rms_norm", "qk_norm_rope_cache", "reshape_and_cache",
+ALL = ("patch_token_ids", "embedding", "rms_norm", "add_rms_norm", "qk_norm_rope_cache", "reshape_and_cache",
        "paged_attention", "silu_mul", "gather_rows", "linear", "argmax", "gumbel_sample")
