@@ -1,0 +1,431 @@
+// Prefill / extend attention over the paged cache on the 5th-generation tensor
+// cores: S = Q K^T and O_j = P V by tcgen05.mma with accumulators in tensor memory,
+// K and V pages fetched by TMA into 128-byte-swizzled tiles, softmax in float32 by
+// one thread per query row.
+//
+// A CTA owns 128 rows = (token, query head of one kv group) pairs of one sequence and
+// walks the key tiles of 128 keys from position 0 (or the window's start) to its last
+// token, so the order of a row's reduction depends on its position alone.  Six warps:
+//   warps 0-3  softmax: thread i owns row i (tensor-memory lane i): reads S, masks,
+//              keeps the running max and sum, writes P (bf16) to shared memory as the
+//              A operand of the second product, then adds O_j into its float32 row
+//              accumulator (rescaled by exp(m_old - m_new)).
+//   warp 4     TMA: one copy per (page, key-or-value, 64-column half) of a tile, two
+//              stages.
+//   warp 5     MMA issue: S_j = Q K_j^T, then (after the P of the tile is in shared
+//              memory) O_j = P_j V_j, then at once S_{j+1}, which overlaps the
+//              accumulation of O_j.
+// Operand layouts (all 128-byte swizzle): Q, K, P K-major [halves][rows][64]; V is
+// read as the MN-major B operand straight from its [key][dim] tile.  head_dim 128,
+// group ratio dividing 128, page_size dividing 128 (at least 8).  Every mbarrier wait
+// is bounded; a wait that runs out sets the error word and the kernel unwinds.
+#include <cuda.h>
+
+#include <map>
+#include <tuple>
+
+#include "attention_bf16_kernels.cuh"
+
+namespace {
+
+constexpr int TC_M = 128, TC_N = 128, TC_D = 128, TC_THREADS = 192;
+constexpr int TILE_BYTES = 128 * 128 * 2;   // a [128 x 128] bf16 tile (two 64-column halves)
+constexpr int HALF_BYTES = 128 * 64 * 2;
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1,
+                                            unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(smem_u32(bar)),
+      "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long desc_a,
+                                       unsigned long long desc_b, unsigned idesc, unsigned accum) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accum), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(unsigned taddr, float (&v)[32]) {
+  unsigned r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, "
+      "%12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, "
+      "%30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// K-major operand, rows of 128 bytes, 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ unsigned long long desc_k_major(unsigned addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
+  d |= (unsigned long long)(1024u >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+// MN-major operand (V as [key][dim] rows of 128 bytes per 64-dim half): 64 dims are
+// contiguous, the next 64 dims lie `half_stride` bytes on (leading byte offset), 8-key
+// groups are 1024 bytes apart (stride byte offset).
+__device__ __forceinline__ unsigned long long desc_mn_major(unsigned addr, unsigned half_stride) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
+  d |= (unsigned long long)((half_stride >> 4) & 0x3FFFu) << 16;
+  d |= (unsigned long long)(1024u >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+constexpr unsigned idesc_f16(int m, int n, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)b_mn_major << 16) |
+         ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+
+// byte offset of (row, 16-byte chunk c of the row's 128 elements) in a [2][128][64] bf16 tile
+__device__ __forceinline__ int sw_chunk_off(int row, int c) {
+  return (c >> 3) * HALF_BYTES + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
+                           const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                           const int* __restrict__ block_table, int max_blocks,
+                           const int* __restrict__ cu_q_lens, const int* __restrict__ seq_lens,
+                           const int* __restrict__ tile_seq, const int* __restrict__ tile_start,
+                           int Hq, int Hkv, int page_size, float scale, int window) {
+  pdl_prologue();
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  unsigned char* sQ = smem;                       // 32 KB
+  unsigned char* sP = smem + TILE_BYTES;          // 32 KB
+  unsigned char* sKV = smem + 2 * TILE_BYTES;     // 2 stages x (K 32 KB + V 32 KB)
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + 6 * TILE_BYTES);
+  unsigned long long* kv_full = bars;             // [2]
+  unsigned long long* kv_empty = bars + 2;        // [2]
+  unsigned long long* bar_s = bars + 4;           // S_j is in tensor memory
+  unsigned long long* bar_p = bars + 5;           // P_j is in shared memory (128 arrivals)
+  unsigned long long* bar_o = bars + 6;           // O_j is in tensor memory
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 7);
+
+  const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;   // longest tiles first
+  const int G = Hq / Hkv;
+  const int tokens_per_tile = TC_M / G;
+  const int seq = tile_seq[tile];
+  const int tok0 = tile_start[tile];
+  const int q_begin = cu_q_lens[seq];
+  const int q_len = cu_q_lens[seq + 1] - q_begin;
+  const int kv_len = seq_lens[seq];
+  const int prefix = kv_len - q_len;
+  const int ntok = min(tokens_per_tile, q_len - tok0);
+  const int* bt = block_table + (size_t)seq * max_blocks;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  const int first_pos = prefix + tok0, last_pos = prefix + tok0 + ntok - 1;
+  const int first_key = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+  const int j0 = first_key / TC_N, j1 = last_pos / TC_N;
+  const int ntiles = j1 - j0 + 1;
+
+  if (warp == 5 && lane == 0) {
+    mbar_init(&kv_full[0], 1);
+    mbar_init(&kv_full[1], 1);
+    mbar_init(&kv_empty[0], 1);
+    mbar_init(&kv_empty[1], 1);
+    mbar_init(bar_s, 1);
+    mbar_init(bar_p, 128);
+    mbar_init(bar_o, 1);
+    mbar_fence_init();
+  }
+  if (warp == 4) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(256u));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  // Q tile -> shared memory, swizzled; rows beyond the tile's tokens are zero
+  for (int c = threadIdx.x; c < TC_M * 16; c += TC_THREADS) {
+    const int r = c >> 4, ch = c & 15;
+    const int tl = r / G, g = r % G;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tl < ntok) {
+      const size_t t = (size_t)(q_begin + tok0 + tl);
+      v = *reinterpret_cast<const uint4*>(q + (t * Hq + (size_t)kvh * G + g) * TC_D + ch * 8);
+    }
+    *reinterpret_cast<uint4*>(sQ + sw_chunk_off(r, ch)) = v;
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // Q is read by the MMA unit
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem = *tmem_slot;
+  const unsigned tmem_s = tmem, tmem_o = tmem + 128;   // columns 0..127: S, 128..255: O_j
+  bool ok = true;
+
+  if (warp == 4) {
+    // ---- TMA: one copy per (page, K or V, half); lanes share the copies of a tile
+    const int pages = TC_N / page_size;
+    const int ops = pages * 4;
+    for (int i = 0; i < ntiles && ok; ++i) {
+      const int st = i & 1;
+      if (i >= 2) ok = mbar_wait(&kv_empty[st], ((i >> 1) - 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      if (lane == 0) mbar_expect_tx(&kv_full[st], 2 * TILE_BYTES);
+      __syncwarp();
+      const int k0 = (j0 + i) * TC_N;
+      for (int op = lane; op < ops; op += 32) {
+        const int pi = op >> 2, kv = (op >> 1) & 1, half = op & 1;
+        const int idx = k0 / page_size + pi;
+        const int page = idx < max_blocks ? bt[idx] : 0;
+        const int row0 = (((page * 2 + kv) * Hkv) + kvh) * page_size;
+        unsigned char* dst = sKV + st * 2 * TILE_BYTES + kv * TILE_BYTES + half * HALF_BYTES +
+                             pi * page_size * 128;
+        tma_load_2d(dst, &map, half * 64, row0, &kv_full[st]);
+      }
+    }
+  } else if (warp == 5) {
+    // ---- MMA issue (one lane)
+    if (lane == 0) {
+      constexpr unsigned idesc_s = idesc_f16(TC_M, TC_N, 0);
+      constexpr unsigned idesc_o = idesc_f16(TC_M, TC_D, 1);
+      const unsigned q_addr = smem_u32(sQ), p_addr = smem_u32(sP);
+      auto issue_s = [&](int i) {
+        const unsigned k_addr = smem_u32(sKV + (i & 1) * 2 * TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < TC_D / 16; ++ks) {
+          const unsigned off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+          tc_mma(tmem_s, desc_k_major(q_addr + off), desc_k_major(k_addr + off), idesc_s,
+                 ks > 0 ? 1u : 0u);
+        }
+        tc_commit(bar_s);
+      };
+      ok = mbar_wait(&kv_full[0], 0);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int i = 0; i < ntiles && ok; ++i) {
+        const int st = i & 1;
+        ok = mbar_wait(bar_p, i & 1);   // P_i is in shared memory, S_i has been read
+        if (!ok) break;
+        tc_fence_after();
+        const unsigned v_addr = smem_u32(sKV + st * 2 * TILE_BYTES + TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < TC_N / 16; ++ks) {
+          const unsigned a_off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;   // 16 keys of P
+          const unsigned b_off = ks * 16 * 128;                            // 16 key rows of V
+          tc_mma(tmem_o, desc_k_major(p_addr + a_off), desc_mn_major(v_addr + b_off, HALF_BYTES),
+                 idesc_o, ks > 0 ? 1u : 0u);
+        }
+        tc_commit(bar_o);
+        tc_commit(&kv_empty[st]);
+        if (i + 1 < ntiles) {
+          ok = mbar_wait(&kv_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(i + 1);
+        }
+      }
+    }
+  } else {
+    // ---- softmax: thread = row
+    const int r = threadIdx.x;
+    const int tl = r / G, g = r % G;
+    const bool valid = tl < ntok;
+    const int hi = valid ? prefix + tok0 + tl : -1;
+    const int lo = (valid && window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
+    const float scale_log2 = scale * LOG2E;
+    const unsigned lane_base = (unsigned)(warp * 32) << 16;
+    float acc[TC_D];
+#pragma unroll
+    for (int d = 0; d < TC_D; ++d) acc[d] = 0.f;
+    float m = NEG_BIG, l = 0.f;
+    for (int i = 0; i < ntiles && ok; ++i) {
+      ok = mbar_wait(bar_s, i & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int kbase = (j0 + i) * TC_N;
+      // pass 1: the row's maximum over the tile
+      float mx = NEG_BIG;
+#pragma unroll
+      for (int c = 0; c < TC_N / 32; ++c) {
+        float v[32];
+        tc_ld32(tmem_s + lane_base + c * 32, v);
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int key = kbase + c * 32 + k;
+          if (key >= lo && key <= hi) mx = fmaxf(mx, v[k] * scale_log2);
+        }
+      }
+      const float m_new = fmaxf(m, mx);
+      const float m_safe = m_new <= -1e29f ? 0.f : m_new;
+      const float alpha = fast_exp2(m - m_safe);
+      // pass 2: probabilities -> bf16 -> shared memory (A operand of P V)
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < TC_N / 32; ++c) {
+        float v[32];
+        tc_ld32(tmem_s + lane_base + c * 32, v);
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const int key = kbase + c * 32 + k;
+          const bool vis = key >= lo && key <= hi;
+          v[k] = vis ? fast_exp2(v[k] * scale_log2 - m_safe) : 0.f;
+          sum += v[k];
+        }
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint4 pk;
+          pk.x = pack_bf16(v[ch * 8 + 0], v[ch * 8 + 1]);
+          pk.y = pack_bf16(v[ch * 8 + 2], v[ch * 8 + 3]);
+          pk.z = pack_bf16(v[ch * 8 + 4], v[ch * 8 + 5]);
+          pk.w = pack_bf16(v[ch * 8 + 6], v[ch * 8 + 7]);
+          *reinterpret_cast<uint4*>(sP + sw_chunk_off(r, c * 4 + ch)) = pk;
+        }
+      }
+      l = l * alpha + sum;
+      m = m_new;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      tc_fence_before();
+      mbar_arrive(bar_p);
+      // O_j -> row accumulator
+      ok = mbar_wait(bar_o, i & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < TC_D / 32; ++c) {
+        float v[32];
+        tc_ld32(tmem_o + lane_base + c * 32, v);
+#pragma unroll
+        for (int k = 0; k < 32; ++k) acc[c * 32 + k] = acc[c * 32 + k] * alpha + v[k];
+      }
+      tc_fence_before();
+    }
+    if (ok && valid) {
+      const float inv = 1.0f / l;
+      const size_t t = (size_t)(q_begin + tok0 + tl);
+      __nv_bfloat16* dst = out + (t * Hq + (size_t)kvh * G + g) * TC_D;
+#pragma unroll
+      for (int ch = 0; ch < TC_D / 8; ++ch) {
+        uint4 pk;
+        pk.x = pack_bf16(acc[ch * 8 + 0] * inv, acc[ch * 8 + 1] * inv);
+        pk.y = pack_bf16(acc[ch * 8 + 2] * inv, acc[ch * 8 + 3] * inv);
+        pk.z = pack_bf16(acc[ch * 8 + 4] * inv, acc[ch * 8 + 5] * inv);
+        pk.w = pack_bf16(acc[ch * 8 + 6] * inv, acc[ch * 8 + 7] * inv);
+        *reinterpret_cast<uint4*>(dst + ch * 8) = pk;
+      }
+    }
+  }
+  if (!ok) atomicExch(&dib_attention_error_word, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u));
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+const CUtensorMap* cache_map(const void* cache, long long num_pages, int Hkv, int page_size, int D) {
+  static EncodeTiledFn enc = nullptr;
+  static std::map<std::tuple<const void*, long long, int, int, int>, CUtensorMap> maps;
+  if (enc == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) != cudaSuccess ||
+        qr != cudaDriverEntryPointSuccess)
+      return nullptr;
+    enc = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  const auto key = std::make_tuple(cache, num_pages, Hkv, page_size, D);
+  auto it = maps.find(key);
+  if (it != maps.end()) return &it->second;
+  CUtensorMap m;
+  const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)num_pages * 2 * Hkv * page_size};
+  const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+  const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+  const cuuint32_t estr[2] = {1, 1};
+  if (enc(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
+          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return nullptr;
+  return &maps.emplace(key, m).first->second;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dib_attention_prefill_tc_tile_rows() { return TC_M; }
+
+int dib_attention_prefill_tc_status() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, dib_attention_error_word, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+
+// Sequences with more than one new token; tiles name (sequence, first token of the
+// tile among its new tokens) with 128 / (Hq/Hkv) tokens per tile.  Returns -2 for
+// shapes this kernel does not take (the caller then uses the mma.sync kernel).
+int dib_extend_attention_tc(const void* q, void* out, const void* cache, long long num_pages,
+                            const int* block_table, int max_blocks, const int* cu_q_lens,
+                            const int* seq_lens, const int* tile_seq, const int* tile_start,
+                            int num_tiles, int Hq, int Hkv, int D, int page_size, float scale,
+                            int window, cudaStream_t st) {
+  if (num_tiles == 0) return DIB_OK;
+  if (D != TC_D || Hkv < 1 || Hq % Hkv != 0 || TC_M % (Hq / Hkv) != 0 || page_size < 8 ||
+      page_size > TC_N || TC_N % page_size != 0 || Hkv > 65535 ||
+      (long long)num_pages * 2 * Hkv * page_size >= (1ll << 31) ||
+      reinterpret_cast<uintptr_t>(cache) % 16 != 0 || reinterpret_cast<uintptr_t>(q) % 16 != 0)
+    return DIB_BAD_SIZE;
+  const CUtensorMap* map = cache_map(cache, num_pages, Hkv, page_size, D);
+  if (map == nullptr) return DIB_LAUNCH_FAILED;
+  const size_t smem = 6 * TILE_BYTES + 8 * 8 + 16 + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(extend_attention_tc_kernel,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return DIB_LAUNCH_FAILED;
+    attr_set = true;
+  }
+  dib_launch(extend_attention_tc_kernel, dim3(num_tiles, Hkv), dim3(TC_THREADS), smem, st, *map,
+             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, max_blocks, cu_q_lens,
+             seq_lens, tile_seq, tile_start, Hq, Hkv, page_size, scale, window);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+}  // extern "C"

@@ -17,7 +17,8 @@ import torch
 
 SPLIT = 128        # keys per split of the decode kernel (fixed: the order of a
                    # sequence's reduction depends on its own length only)
-TILE_ROWS = 64     # rows (token, head-of-group pairs) per tile of the extend kernel
+TILE_ROWS = 64     # rows (token, head-of-group pairs) per tile of the mma.sync extend kernel
+TC_TILE_ROWS = 128  # ... of the tcgen05 extend kernel (head_dim 128)
 
 
 def supports(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -> bool:
@@ -56,6 +57,24 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
             _ptr(ws[0]), _ptr(ws[1]), c_int(nd), c_int(max_splits), c_int(hq), c_int(hkv), c_int(d),
             c_int(page_size), c_float(scale), c_int(window), _stream())
         _check(st, "decode_attention_bf16", f"heads {hq}/{hkv}, head_dim {d}", kernels=2)
+    group = hq // hkv
+    if b > nd and d == 128 and TC_TILE_ROWS % group == 0 and page_size in (8, 16, 32, 64, 128) \
+            and os.environ.get("DIB200_PREFILL_TC", "1") != "0":
+        # tcgen05 kernel: 128 rows per tile
+        tpt = TC_TILE_ROWS // group
+        tiles = meta.scratch.get(("extend_tiles", tpt))
+        if tiles is None:
+            seqs, starts = extend_tiles(meta.q_lens, nd, tpt)
+            both = torch.tensor([seqs, starts], dtype=torch.int32).to(q.device, non_blocking=True)
+            tiles = (both[0], both[1], len(seqs))
+            meta.scratch[("extend_tiles", tpt)] = tiles
+        st = _lib("attention_prefill_tc").dib_extend_attention_tc(
+            _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0]), _ptr(bt),
+            c_int(bt.shape[1]), _ptr(meta.cu_q_lens), _ptr(meta.seq_lens), _ptr(tiles[0]),
+            _ptr(tiles[1]), c_int(tiles[2]), c_int(hq), c_int(hkv), c_int(d), c_int(page_size),
+            c_float(scale), c_int(window), _stream())
+        _check(st, "extend_attention_tc", f"heads {hq}/{hkv}, head_dim {d}")
+        return
     if b > nd:
         tpt = TILE_ROWS // (hq // hkv)
         tiles = meta.scratch.get(("extend_tiles", tpt))

@@ -37,12 +37,14 @@ SOURCES = {
     "attention_bf16": "attention_bf16.cu",
     "gemm_bf16": "gemm_bf16.cu",
     "decode_attention_noalloc": "decode_attention_noalloc.cu",
+    "attention_prefill_tc": "attention_prefill_tc.cu",
 }
 HEADERS = ("common.cuh",)
 # further headers a library includes
 EXTRA_HEADERS = {
     "attention_bf16": ("attention_bf16_kernels.cuh",),
     "decode_attention_noalloc": ("attention_bf16_kernels.cuh", "decode_attention_noalloc.h"),
+    "attention_prefill_tc": ("attention_bf16_kernels.cuh",),
 }
 
 NVCC_FLAGS = [
