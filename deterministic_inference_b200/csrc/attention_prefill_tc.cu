@@ -5,14 +5,16 @@
 //
 // A CTA owns 128 rows = (token, query head of one kv group) pairs of one sequence and
 // walks the key tiles of 128 keys from position 0 (or the window's start) to its last
-// token, so the order of a row's reduction depends on its position alone.  Six warps:
-//   warps 0-3  softmax: thread i owns row i (tensor-memory lane i): reads S, masks,
-//              keeps the running max and sum, writes P (bf16) to shared memory as the
-//              A operand of the second product, then adds O_j into its float32 row
+// token, so the order of a row's reduction depends on its position alone.  Ten warps:
+//   warps 0-7  softmax: two threads share a row (tensor-memory lane = row; warp w reads
+//              lanes 32(w%4).., and half w/4 of the columns).  Both read all of S_j for
+//              the row's maximum; each computes the probabilities of its 64 keys, writes
+//              them (bf16) to shared memory as the A operand of the second product, keeps
+//              the sum of its half, and adds its 64 dims of O_j into a float32
 //              accumulator (rescaled by exp(m_old - m_new)).
-//   warp 4     TMA: one copy per (page, key-or-value, 64-column half) of a tile, two
+//   warp 8     TMA: one copy per (page, key-or-value, 64-column half) of a tile, two
 //              stages.
-//   warp 5     MMA issue: S_j = Q K_j^T, then (after the P of the tile is in shared
+//   warp 9     MMA issue: S_j = Q K_j^T, then (after the P of the tile is in shared
 //              memory) O_j = P_j V_j, then at once S_{j+1}, which overlaps the
 //              accumulation of O_j.
 // Operand layouts (all 128-byte swizzle): Q, K, P K-major [halves][rows][64]; V is
@@ -28,7 +30,8 @@
 
 namespace {
 
-constexpr int TC_M = 128, TC_N = 128, TC_D = 128, TC_THREADS = 192;
+constexpr int TC_M = 128, TC_N = 128, TC_D = 128, TC_THREADS = 320;
+constexpr int TMA_WARP = 8, MMA_WARP = 9;
 constexpr int TILE_BYTES = 128 * 128 * 2;   // a [128 x 128] bf16 tile (two 64-column halves)
 constexpr int HALF_BYTES = 128 * 64 * 2;
 
@@ -66,8 +69,11 @@ __device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long desc_
       "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accum), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
       : "memory");
 }
-__device__ __forceinline__ void tc_ld32(unsigned taddr, float (&v)[32]) {
-  unsigned r[32];
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// 32 consecutive columns of this thread's lane; the values are valid after tc_wait_ld().
+__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, "
       "%12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, "
@@ -78,9 +84,6 @@ __device__ __forceinline__ void tc_ld32(unsigned taddr, float (&v)[32]) {
         "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
 // K-major operand, rows of 128 bytes, 128-byte swizzle: 8-row groups 1024 bytes apart.
@@ -154,17 +157,17 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
   const int j0 = first_key / TC_N, j1 = last_pos / TC_N;
   const int ntiles = j1 - j0 + 1;
 
-  if (warp == 5 && lane == 0) {
+  if (warp == MMA_WARP && lane == 0) {
     mbar_init(&kv_full[0], 1);
     mbar_init(&kv_full[1], 1);
     mbar_init(&kv_empty[0], 1);
     mbar_init(&kv_empty[1], 1);
     mbar_init(bar_s, 1);
-    mbar_init(bar_p, 128);
+    mbar_init(bar_p, 256);
     mbar_init(bar_o, 1);
     mbar_fence_init();
   }
-  if (warp == 4) {
+  if (warp == TMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
                  "r"(256u));
@@ -189,7 +192,7 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
   const unsigned tmem_s = tmem, tmem_o = tmem + 128;   // columns 0..127: S, 128..255: O_j
   bool ok = true;
 
-  if (warp == 4) {
+  if (warp == TMA_WARP) {
     // ---- TMA: one copy per (page, K or V, half); lanes share the copies of a tile
     const int pages = TC_N / page_size;
     const int ops = pages * 4;
@@ -211,7 +214,7 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
         tma_load_2d(dst, &map, half * 64, row0, &kv_full[st]);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == MMA_WARP) {
     // ---- MMA issue (one lane)
     if (lane == 0) {
       constexpr unsigned idesc_s = idesc_f16(TC_M, TC_N, 0);
@@ -256,17 +259,18 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
       }
     }
   } else {
-    // ---- softmax: thread = row
-    const int r = threadIdx.x;
+    // ---- softmax: two threads per row, each with half of the keys and of the dims
+    const int r = threadIdx.x & 127;
+    const int hf = threadIdx.x >> 7;                 // 0: keys/dims 0..63, 1: 64..127
     const int tl = r / G, g = r % G;
     const bool valid = tl < ntok;
     const int hi = valid ? prefix + tok0 + tl : -1;
     const int lo = (valid && window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
     const float scale_log2 = scale * LOG2E;
-    const unsigned lane_base = (unsigned)(warp * 32) << 16;
-    float acc[TC_D];
+    const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;
+    float acc[TC_D / 2];
 #pragma unroll
-    for (int d = 0; d < TC_D; ++d) acc[d] = 0.f;
+    for (int d = 0; d < TC_D / 2; ++d) acc[d] = 0.f;
     float m = NEG_BIG, l = 0.f;
     for (int i = 0; i < ntiles && ok; ++i) {
       ok = mbar_wait(bar_s, i & 1);
@@ -274,42 +278,62 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
       if (!ok) break;
       tc_fence_after();
       const int kbase = (j0 + i) * TC_N;
-      // pass 1: the row's maximum over the tile
+      const bool full = kbase >= lo && kbase + TC_N - 1 <= hi;   // no key of the tile is masked
+      // pass 1: the row's maximum over all 128 keys (both threads of the row)
       float mx = NEG_BIG;
 #pragma unroll
-      for (int c = 0; c < TC_N / 32; ++c) {
-        float v[32];
-        tc_ld32(tmem_s + lane_base + c * 32, v);
+      for (int c = 0; c < TC_N / 64; ++c) {
+        unsigned v0[32], v1[32];
+        tc_ld32(tmem_s + lane_base + c * 64, v0);
+        tc_ld32(tmem_s + lane_base + c * 64 + 32, v1);
+        tc_wait_ld();
+        if (full) {
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int key = kbase + c * 32 + k;
-          if (key >= lo && key <= hi) mx = fmaxf(mx, v[k] * scale_log2);
+          for (int k = 0; k < 32; ++k)
+            mx = fmaxf(mx, fmaxf(__uint_as_float(v0[k]), __uint_as_float(v1[k])));
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const int key = kbase + c * 64 + k;
+            if (key >= lo && key <= hi) mx = fmaxf(mx, __uint_as_float(v0[k]));
+            if (key + 32 >= lo && key + 32 <= hi) mx = fmaxf(mx, __uint_as_float(v1[k]));
+          }
         }
       }
+      mx = mx <= -1e29f ? NEG_BIG : mx * scale_log2;   // scale is positive
       const float m_new = fmaxf(m, mx);
       const float m_safe = m_new <= -1e29f ? 0.f : m_new;
       const float alpha = fast_exp2(m - m_safe);
-      // pass 2: probabilities -> bf16 -> shared memory (A operand of P V)
+      // pass 2: probabilities of this thread's 64 keys -> bf16 -> shared memory
       float sum = 0.f;
-#pragma unroll
-      for (int c = 0; c < TC_N / 32; ++c) {
-        float v[32];
-        tc_ld32(tmem_s + lane_base + c * 32, v);
+      {
+        unsigned v0[32], v1[32];
+        tc_ld32(tmem_s + lane_base + hf * 64, v0);
+        tc_ld32(tmem_s + lane_base + hf * 64 + 32, v1);
+        tc_wait_ld();
+        float p0[32], p1[32];
 #pragma unroll
         for (int k = 0; k < 32; ++k) {
-          const int key = kbase + c * 32 + k;
-          const bool vis = key >= lo && key <= hi;
-          v[k] = vis ? fast_exp2(v[k] * scale_log2 - m_safe) : 0.f;
-          sum += v[k];
+          const int key = kbase + hf * 64 + k;
+          const bool vis0 = full || (key >= lo && key <= hi);
+          const bool vis1 = full || (key + 32 >= lo && key + 32 <= hi);
+          p0[k] = vis0 ? fast_exp2(__uint_as_float(v0[k]) * scale_log2 - m_safe) : 0.f;
+          p1[k] = vis1 ? fast_exp2(__uint_as_float(v1[k]) * scale_log2 - m_safe) : 0.f;
+          sum += p0[k] + p1[k];
         }
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {
           uint4 pk;
-          pk.x = pack_bf16(v[ch * 8 + 0], v[ch * 8 + 1]);
-          pk.y = pack_bf16(v[ch * 8 + 2], v[ch * 8 + 3]);
-          pk.z = pack_bf16(v[ch * 8 + 4], v[ch * 8 + 5]);
-          pk.w = pack_bf16(v[ch * 8 + 6], v[ch * 8 + 7]);
-          *reinterpret_cast<uint4*>(sP + sw_chunk_off(r, c * 4 + ch)) = pk;
+          pk.x = pack_bf16(p0[ch * 8 + 0], p0[ch * 8 + 1]);
+          pk.y = pack_bf16(p0[ch * 8 + 2], p0[ch * 8 + 3]);
+          pk.z = pack_bf16(p0[ch * 8 + 4], p0[ch * 8 + 5]);
+          pk.w = pack_bf16(p0[ch * 8 + 6], p0[ch * 8 + 7]);
+          *reinterpret_cast<uint4*>(sP + sw_chunk_off(r, hf * 8 + ch)) = pk;
+          pk.x = pack_bf16(p1[ch * 8 + 0], p1[ch * 8 + 1]);
+          pk.y = pack_bf16(p1[ch * 8 + 2], p1[ch * 8 + 3]);
+          pk.z = pack_bf16(p1[ch * 8 + 4], p1[ch * 8 + 5]);
+          pk.w = pack_bf16(p1[ch * 8 + 6], p1[ch * 8 + 7]);
+          *reinterpret_cast<uint4*>(sP + sw_chunk_off(r, hf * 8 + 4 + ch)) = pk;
         }
       }
       l = l * alpha + sum;
@@ -317,26 +341,35 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
       mbar_arrive(bar_p);
-      // O_j -> row accumulator
+      // this thread's 64 dims of O_j -> accumulator
       ok = mbar_wait(bar_o, i & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      {
+        unsigned v0[32], v1[32];
+        tc_ld32(tmem_o + lane_base + hf * 64, v0);
+        tc_ld32(tmem_o + lane_base + hf * 64 + 32, v1);
+        tc_wait_ld();
 #pragma unroll
-      for (int c = 0; c < TC_D / 32; ++c) {
-        float v[32];
-        tc_ld32(tmem_o + lane_base + c * 32, v);
-#pragma unroll
-        for (int k = 0; k < 32; ++k) acc[c * 32 + k] = acc[c * 32 + k] * alpha + v[k];
+        for (int k = 0; k < 32; ++k) {
+          acc[k] = acc[k] * alpha + __uint_as_float(v0[k]);
+          acc[32 + k] = acc[32 + k] * alpha + __uint_as_float(v1[k]);
+        }
       }
       tc_fence_before();
     }
+    // the row's sum is the sum of its two halves (sP is free now: reuse it)
+    float* sL = reinterpret_cast<float*>(sP);
+    sL[hf * 128 + r] = l;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    const float l_row = sL[r] + sL[128 + r];
     if (ok && valid) {
-      const float inv = 1.0f / l;
+      const float inv = 1.0f / l_row;
       const size_t t = (size_t)(q_begin + tok0 + tl);
-      __nv_bfloat16* dst = out + (t * Hq + (size_t)kvh * G + g) * TC_D;
+      __nv_bfloat16* dst = out + (t * Hq + (size_t)kvh * G + g) * TC_D + hf * 64;
 #pragma unroll
-      for (int ch = 0; ch < TC_D / 8; ++ch) {
+      for (int ch = 0; ch < TC_D / 16; ++ch) {
         uint4 pk;
         pk.x = pack_bf16(acc[ch * 8 + 0] * inv, acc[ch * 8 + 1] * inv);
         pk.y = pack_bf16(acc[ch * 8 + 2] * inv, acc[ch * 8 + 3] * inv);
@@ -349,7 +382,7 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
   if (!ok) atomicExch(&dib_attention_error_word, 1);
   tc_fence_before();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == TMA_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u));
   }
 }
