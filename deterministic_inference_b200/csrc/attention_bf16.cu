@@ -298,7 +298,7 @@ int dib_extend_attention_bf16(const void* q, void* out, const void* cache, const
                               int Hkv, int D, int page_size, float scale, int window,
                               cudaStream_t st) {
   if (num_tiles == 0) return DIB_OK;
-  if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > EXT_M || Hkv > 65535) return DIB_BAD_SIZE;
+  if (Hkv < 1 || Hq % Hkv != 0 || Hq / Hkv > EXT_M || num_tiles > 65535) return DIB_BAD_SIZE;
 #define CALL(DD)                                                                              \
   launch_extend<DD>(q, out, cache, block_table, max_blocks, cu_q_lens, seq_lens, tile_seq,   \
                     tile_start, num_tiles, Hq, Hkv, page_size, scale, window, st)

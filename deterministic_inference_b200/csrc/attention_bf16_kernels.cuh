@@ -257,7 +257,7 @@ extend_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
   // stage s: K at sK0 + s*2*TILE_ELEMS, V right behind it
 
   // tiles are listed in order of position; the ones with the most keys run first
-  const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;
+  const int tile = gridDim.y - 1 - blockIdx.y, kvh = blockIdx.x;
   const int G = Hq / Hkv;
   const int tokens_per_tile = EXT_M / G;
   const int seq = tile_seq[tile];
@@ -547,7 +547,7 @@ int launch_extend(const void* q, void* out, const void* cache, const int* bt, in
       return DIB_LAUNCH_FAILED;
     attr_set = true;
   }
-  dim3 grid(num_tiles, Hkv);
+  dim3 grid(Hkv, num_tiles);   // x-then-y order: all kv heads of the longest tile first
   dib_launch(kern, dim3(grid), dim3(EXT_THREADS), smem, st, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,
                                         (const __nv_bfloat16*)cache, bt, max_blocks, cu_q_lens,
                                         seq_lens, tile_seq, tile_start, Hq, Hkv, page_size, scale,

@@ -139,7 +139,8 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
   unsigned long long* bar_o = bars + 6;           // O_j is in tensor memory
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 7);
 
-  const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y;   // longest tiles first
+  // blocks are handed out in x-then-y order: y counts the tiles from the longest down
+  const int tile = gridDim.y - 1 - blockIdx.y, kvh = blockIdx.x;
   const int G = Hq / Hkv;
   const int tokens_per_tile = TC_M / G;
   const int seq = tile_seq[tile];
@@ -440,7 +441,7 @@ int dib_extend_attention_tc(const void* q, void* out, const void* cache, long lo
                             int window, cudaStream_t st) {
   if (num_tiles == 0) return DIB_OK;
   if (D != TC_D || Hkv < 1 || Hq % Hkv != 0 || TC_M % (Hq / Hkv) != 0 || page_size < 8 ||
-      page_size > TC_N || TC_N % page_size != 0 || Hkv > 65535 ||
+      page_size > TC_N || TC_N % page_size != 0 || num_tiles > 65535 ||
       (long long)num_pages * 2 * Hkv * page_size >= (1ll << 31) ||
       reinterpret_cast<uintptr_t>(cache) % 16 != 0 || reinterpret_cast<uintptr_t>(q) % 16 != 0)
     return DIB_BAD_SIZE;
@@ -454,7 +455,7 @@ int dib_extend_attention_tc(const void* q, void* out, const void* cache, long lo
       return DIB_LAUNCH_FAILED;
     attr_set = true;
   }
-  dib_launch(extend_attention_tc_kernel, dim3(num_tiles, Hkv), dim3(TC_THREADS), smem, st, *map,
+  dib_launch(extend_attention_tc_kernel, dim3(Hkv, num_tiles), dim3(TC_THREADS), smem, st, *map,
              (const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, max_blocks, cu_q_lens,
              seq_lens, tile_seq, tile_start, Hq, Hkv, page_size, scale, window);
   DIB_CHECK_LAUNCH();

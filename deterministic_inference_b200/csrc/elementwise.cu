@@ -225,7 +225,7 @@ struct alignas((sizeof(T) * EPL) <= 16 ? (sizeof(T) * EPL) : 16) Pack {
   T e[EPL];
 };
 
-template <typename T, int EPL>
+template <typename T, int EPL, int ITEMS>
 __global__ void qk_norm_rope_cache_vec_kernel(
     const T* __restrict__ qkv, const float* __restrict__ parts, int S, long long split_stride,
     T* __restrict__ q_out, T* __restrict__ kv_cache,
@@ -238,75 +238,94 @@ __global__ void qk_norm_rope_cache_vec_kernel(
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = Hq + 2 * Hkv;
-  const long long item = (long long)blockIdx.x * warps_per_block + warp;
-  if (item >= (long long)T_tokens * heads) return;
-  const int t = (int)(item / heads);
-  const int head = (int)(item % heads);
-  const bool is_q = head < Hq;
-  const bool is_k = !is_q && head < Hq + Hkv;
-  const float* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+  const long long total = (long long)T_tokens * heads;
+  const long long item0 = ((long long)blockIdx.x * warps_per_block + warp) * ITEMS;
+  if (item0 >= total) return;
 
-  T* dst = nullptr;
-  if (is_q) {
-    dst = q_out + ((size_t)t * Hq + head) * D;
-  } else {
-    if (kv_cache == nullptr) return;
-    const int slot = slot_mapping[t];
-    if (slot < 0) return;
-    const long long page = slot / page_size;
-    if (page >= num_pages) return;
-    const int off = slot % page_size;
-    const int kv = is_k ? 0 : 1;
-    const int h = is_k ? head - Hq : head - Hq - Hkv;
-    dst = kv_cache + ((((size_t)page * 2 + kv) * Hkv + h) * page_size + off) * D;
-  }
-  float v[EPL];
-  float ss = 0.f;
-  if (parts == nullptr) {
-    const T* src = qkv + ((size_t)t * heads + head) * D + lane * EPL;
-    const Pack<T, EPL> in = *reinterpret_cast<const Pack<T, EPL>*>(src);
+  // A warp takes ITEMS consecutive (token, head) items and issues the loads of all of
+  // them before it works on any, so their memory round-trips overlap.
+  float v[ITEMS][EPL];
+  int tok[ITEMS], head[ITEMS], pos[ITEMS], slot[ITEMS];
+  bool act[ITEMS];
 #pragma unroll
-    for (int k = 0; k < EPL; ++k) v[k] = Elem<T>::load(&in.e[k]);
-  } else {
-    // the row is a sum of split-k partial products, added in split order and rounded
-    // to T as a stored projection output would be
-    const float* src = parts + ((size_t)t * heads + head) * D + lane * EPL;
+  for (int it = 0; it < ITEMS; ++it) {
+    const long long item = item0 + it;
+    act[it] = item < total;
+    tok[it] = act[it] ? (int)(item / heads) : 0;
+    head[it] = act[it] ? (int)(item % heads) : 0;
+    pos[it] = 0;
+    slot[it] = -1;
+    if (!act[it]) continue;
+    if (parts == nullptr) {
+      const T* src = qkv + ((size_t)tok[it] * heads + head[it]) * D + lane * EPL;
+      const Pack<T, EPL> in = *reinterpret_cast<const Pack<T, EPL>*>(src);
 #pragma unroll
-    for (int k = 0; k < EPL; ++k) v[k] = 0.f;
+      for (int k = 0; k < EPL; ++k) v[it][k] = Elem<T>::load(&in.e[k]);
+    } else {
+      // the row is a sum of split-k partial products, added in split order and rounded
+      // to T as a stored projection output would be
+      const float* src = parts + ((size_t)tok[it] * heads + head[it]) * D + lane * EPL;
+#pragma unroll
+      for (int k = 0; k < EPL; ++k) v[it][k] = 0.f;
 #pragma unroll 4
-    for (int sp = 0; sp < S; ++sp) {
-      const Pack<float, EPL> in = *reinterpret_cast<const Pack<float, EPL>*>(src + sp * split_stride);
+      for (int sp = 0; sp < S; ++sp) {
+        const Pack<float, EPL> in = *reinterpret_cast<const Pack<float, EPL>*>(src + sp * split_stride);
 #pragma unroll
-      for (int k = 0; k < EPL; ++k) v[k] += in.e[k];
+        for (int k = 0; k < EPL; ++k) v[it][k] += in.e[k];
+      }
+#pragma unroll
+      for (int k = 0; k < EPL; ++k) v[it][k] = round_to<T>(v[it][k]);
     }
-#pragma unroll
-    for (int k = 0; k < EPL; ++k) v[k] = round_to<T>(v[k]);
-  }
-#pragma unroll
-  for (int k = 0; k < EPL; ++k) ss += v[k] * v[k];
-  if (nw != nullptr) {
-    ss = warp_sum(ss);
-    const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
-#pragma unroll
-    for (int k = 0; k < EPL; ++k) v[k] = v[k] * rstd * nw[lane * EPL + k];
-  }
-  if (cos_sin != nullptr && (is_q || is_k)) {
-    int pos = positions[t];
-    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
-    const float* tab = cos_sin + (size_t)pos * D;
-    const int j0 = (lane & 15) * EPL;
-    const bool upper = lane >= 16;
-#pragma unroll
-    for (int k = 0; k < EPL; ++k) {
-      const float partner = __shfl_xor_sync(0xffffffffu, v[k], 16);
-      const float c = tab[j0 + k], sn = tab[D / 2 + j0 + k];
-      v[k] = upper ? (v[k] * c + partner * sn) : (v[k] * c - partner * sn);
+    if (cos_sin != nullptr && head[it] < Hq + Hkv) {
+      const int p = positions[tok[it]];
+      pos[it] = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
     }
+    if (head[it] >= Hq && kv_cache != nullptr) slot[it] = slot_mapping[tok[it]];
   }
-  Pack<T, EPL> o;
+
 #pragma unroll
-  for (int k = 0; k < EPL; ++k) Elem<T>::store(&o.e[k], v[k]);
-  *reinterpret_cast<Pack<T, EPL>*>(dst + lane * EPL) = o;
+  for (int it = 0; it < ITEMS; ++it) {
+    if (!act[it]) continue;
+    const bool is_q = head[it] < Hq;
+    const bool is_k = !is_q && head[it] < Hq + Hkv;
+    const float* nw = is_q ? q_norm_w : (is_k ? k_norm_w : nullptr);
+    T* dst = nullptr;
+    if (is_q) {
+      dst = q_out + ((size_t)tok[it] * Hq + head[it]) * D;
+    } else {
+      if (slot[it] < 0) continue;
+      const long long page = slot[it] / page_size;
+      if (page >= num_pages) continue;
+      const int off = slot[it] % page_size;
+      const int kv = is_k ? 0 : 1;
+      const int h = is_k ? head[it] - Hq : head[it] - Hq - Hkv;
+      dst = kv_cache + ((((size_t)page * 2 + kv) * Hkv + h) * page_size + off) * D;
+    }
+    if (nw != nullptr) {
+      float ss = 0.f;
+#pragma unroll
+      for (int k = 0; k < EPL; ++k) ss += v[it][k] * v[it][k];
+      ss = warp_sum(ss);
+      const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+#pragma unroll
+      for (int k = 0; k < EPL; ++k) v[it][k] = v[it][k] * rstd * nw[lane * EPL + k];
+    }
+    if (cos_sin != nullptr && (is_q || is_k)) {
+      const float* tab = cos_sin + (size_t)pos[it] * D;
+      const int j0 = (lane & 15) * EPL;
+      const bool upper = lane >= 16;
+#pragma unroll
+      for (int k = 0; k < EPL; ++k) {
+        const float partner = __shfl_xor_sync(0xffffffffu, v[it][k], 16);
+        const float c = tab[j0 + k], sn = tab[D / 2 + j0 + k];
+        v[it][k] = upper ? (v[it][k] * c + partner * sn) : (v[it][k] * c - partner * sn);
+      }
+    }
+    Pack<T, EPL> o;
+#pragma unroll
+    for (int k = 0; k < EPL; ++k) Elem<T>::store(&o.e[k], v[it][k]);
+    *reinterpret_cast<Pack<T, EPL>*>(dst + lane * EPL) = o;
+  }
 }
 
 // ------------------------------------------------ standalone cache write
@@ -610,8 +629,17 @@ int dib_qk_norm_rope_cache_split(const void* qkv, const float* parts, int S, lon
                        reinterpret_cast<uintptr_t>(kv_cache) % 16 == 0;
   if (aligned && (D == 64 || D == 128 || D == 256) && (cos_sin == nullptr || rotary_dim == D) &&
       (dtype == 0 || dtype == 1)) {
+    // many items: 4 per warp (their loads overlap); few items: one per warp
+    const bool many = parts == nullptr && items >= 8192;
+    const int vblocks = many ? ceil_div_host(items, warps * 4) : blocks;
 #define DIB_QK_VEC(TT, EPL)                                                                      \
-  dib_launch(qk_norm_rope_cache_vec_kernel<TT, EPL>, dim3(blocks), dim3(warps * 32), 0, st,                         \
+  if (many)                                                                                      \
+    dib_launch(qk_norm_rope_cache_vec_kernel<TT, EPL, 4>, dim3(vblocks), dim3(warps * 32), 0, st, \
+      (const TT*)qkv, parts, S, split_stride, (TT*)q_out, (TT*)kv_cache, q_norm_w, k_norm_w,   \
+      eps, cos_sin, max_pos,                                                                    \
+      positions, slot_mapping, T, Hq, Hkv, page_size, num_pages);                              \
+  else                                                                                           \
+  dib_launch(qk_norm_rope_cache_vec_kernel<TT, EPL, 1>, dim3(blocks), dim3(warps * 32), 0, st,                         \
       (const TT*)qkv, parts, S, split_stride, (TT*)q_out, (TT*)kv_cache, q_norm_w, k_norm_w,   \
       eps, cos_sin, max_pos,                                                                    \
       positions, slot_mapping, T, Hq, Hkv, page_size, num_pages)
