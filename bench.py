@@ -172,7 +172,7 @@ def main() -> int:
 
     sizes = sorted({a.batch, *[int(x) for x in a.points.split(",") if x.strip()]})
     max_b = max(sizes)
-    per_req = a.context + max(a.steps + a.warmup, a.point_steps + a.warmup) + 64
+    per_req = a.context + max(a.steps + a.warmup, a.point_steps + a.warmup) + 96
     pool = max_b * (-(-per_req // 16) * 16) + a.prefill_tokens + 1024
     ecfg = EngineConfig(model_config=cfg, random_seed=0, dtype="bfloat16", kv_pool_tokens=pool,
                         page_size=16, max_reqs=max(256, max_b + 8), max_seq_len=8192,
@@ -284,7 +284,7 @@ def main() -> int:
     # ---------------- decode end to end through Engine.step() ----------------
     e2e = None
     if not a.no_e2e:
-        sp = SamplingParams(max_new_tokens=a.steps + a.warmup + 2, ignore_eos=True)
+        sp = SamplingParams(max_new_tokens=a.steps + a.warmup + 32, ignore_eos=True)   # nobody finishes inside the timed steps
         for _ in range(a.batch):
             engine.add_request(prompt_ids=random_prompt(a.context), params=sp)
         while any(r.num_output == 0 for r in list(engine.scheduler.running) + list(engine.scheduler.waiting)):

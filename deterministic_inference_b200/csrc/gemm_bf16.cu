@@ -119,7 +119,10 @@ constexpr unsigned make_idesc(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
 
-template <int BN, typename OutT>
+// GATED: w is [gate rows ; up rows] of a gated feed-forward ([2N, K]); a tile holds 64
+// gate rows and the 64 up rows of the same features, and the epilogue writes
+// silu(gate) * up, [M, N], so the gate/up product never goes to memory.  k is not split.
+template <int BN, typename OutT, bool GATED>
 __global__ void __launch_bounds__(THREADS)
 gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  OutT* __restrict__ out, float* __restrict__ partial, int M, int N, int num_kb,
@@ -135,7 +138,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(accum + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BM, m0 = blockIdx.y * BN, split = blockIdx.z;
+  const int n0 = blockIdx.x * (GATED ? BM / 2 : BM), m0 = blockIdx.y * BN, split = blockIdx.z;
   const int kb_begin = split * kb_per_split;
   const int nkb = min(kb_per_split, num_kb - kb_begin);
 
@@ -167,7 +170,13 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     const int pre = nkb < STAGES ? nkb : STAGES;
     for (int i = 0; i < pre; ++i) {
       mbar_expect_tx(&full[i], STAGE_BYTES);
-      tma_load_2d(smem + i * STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full[i]);
+      if (GATED) {
+        tma_load_2d(smem + i * STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full[i]);
+        tma_load_2d(smem + i * STAGE_BYTES + A_BYTES / 2, &map_w, (kb_begin + i) * BK, N + n0,
+                    &full[i]);
+      } else {
+        tma_load_2d(smem + i * STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full[i]);
+      }
     }
     pdl_wait();
     for (int i = 0; i < pre; ++i)
@@ -180,6 +189,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       unsigned char* a = smem + s * STAGE_BYTES;
       const int k = (kb_begin + i) * BK;
       tma_load_2d(a, &map_w, k, n0, &full[s]);
+      if (GATED) tma_load_2d(a + A_BYTES / 2, &map_w, k, N + n0, &full[s]);
       tma_load_2d(a + A_BYTES, &map_x, k, m0, &full[s]);
     }
   } else if (warp == 1 && lane == 0) {
@@ -209,7 +219,37 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (!acc_ok) atomicExch(&dib_gemm_error_word, 1);
   tc_fence_after();
   const int n = n0 + warp * 32 + lane;
-  if (acc_ok) {
+  if (GATED) {
+    // rows 0..63 of the tile are gate rows (warps 0, 1), rows 64..127 the up rows of
+    // the same features (warps 2, 3): the up values go through shared memory (the
+    // pipeline stages are free: every MMA has completed)
+    float* ex = reinterpret_cast<float*>(smem);   // [64][17]
+    const int pr = (warp & 1) * 32 + lane;         // pair index inside the tile
+#pragma unroll 1
+    for (int c = 0; c < BN / 16; ++c) {
+      unsigned r[16];
+      if (acc_ok) {
+        tc_ld16(tmem + ((unsigned)(warp * 32) << 16) + c * 16, r);
+        tc_wait_ld();
+      }
+      if (warp >= 2) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) ex[pr * 17 + j] = __uint_as_float(r[j]);
+      }
+      __syncthreads();
+      if (warp < 2 && acc_ok && n0 + pr < N) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int m = m0 + c * 16 + j;
+          if (m >= M) break;
+          const float g = round_to<__nv_bfloat16>(__uint_as_float(r[j]));
+          const float u = round_to<__nv_bfloat16>(ex[pr * 17 + j]);
+          Elem<OutT>::store(out + (size_t)m * N + n0 + pr, g / (1.0f + expf(-g)) * u);
+        }
+      }
+      __syncthreads();
+    }
+  } else if (acc_ok) {
 #pragma unroll
     for (int c = 0; c < BN / 16; ++c) {
       unsigned r[16];
@@ -267,12 +307,12 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, in
              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, typename OutT>
+template <int BN, typename OutT, bool GATED = false>
 int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, void* out, float* partial, int M,
                 int N, int num_kb, int kb_per_split, int splits, dim3 grid, cudaStream_t st) {
   constexpr size_t smem =
       (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
-  auto kern = gemm_swap_kernel<BN, OutT>;
+  auto kern = gemm_swap_kernel<BN, OutT, GATED>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
@@ -341,6 +381,32 @@ int dib_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K, 
   (out_fp32 ? launch_swap<BNV, float>(mw, mx, out, partial, M, N, num_kb, per, splits, grid, st) \
             : launch_swap<BNV, __nv_bfloat16>(mw, mx, out, partial, M, N, num_kb, per, splits,  \
                                               grid, st))
+  switch (bn) {
+    case 16: return CALL(16);
+    case 32: return CALL(32);
+    case 64: return CALL(64);
+    default: return CALL(128);
+  }
+#undef CALL
+}
+
+// out[M, I] = silu(x w_gate^T) * (x w_up^T) with w = [w_gate ; w_up] of shape [2I, K]
+// (bf16 in, bf16 out; the two products are rounded to bf16 before the gate, as stored
+// products would be).  I must be a multiple of 64, K of 8.
+int dib_gemm_bf16_gated(const void* x, const void* w, void* out, int M, int I, int K,
+                        cudaStream_t st) {
+  if (M == 0 || I == 0) return DIB_OK;
+  if (K < 8 || K % 8 != 0 || I % 64 != 0) return DIB_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16 != 0) return DIB_BAD_ALIGN;
+  int bn = 16;
+  while (bn < M && bn < 128) bn <<= 1;
+  const int m_tiles = (M + bn - 1) / bn, num_kb = (K + BK - 1) / BK;
+  if (m_tiles > 65535) return DIB_BAD_SIZE;
+  CUtensorMap mw, mx;
+  if (!make_map(&mw, w, 2ll * I, K, BM / 2) || !make_map(&mx, x, M, K, bn)) return DIB_LAUNCH_FAILED;
+  dim3 grid(I / 64, m_tiles, 1);
+#define CALL(BNV) \
+  launch_swap<BNV, __nv_bfloat16, true>(mw, mx, out, nullptr, M, I, num_kb, num_kb, 1, grid, st)
   switch (bn) {
     case 16: return CALL(16);
     case 32: return CALL(32);

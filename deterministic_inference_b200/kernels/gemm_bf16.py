@@ -71,3 +71,25 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, allow_
     if out_dtype == torch.bfloat16:
         return torch.mm(x, weight.t())
     return torch.mm(x, weight.t(), out_dtype=out_dtype)
+
+
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor):
+    """silu(x @ w_gate^T) * (x @ w_up^T) for w_gate_up = [w_gate ; w_up] ([2I, K]) in one
+    kernel (the gate happens in the product's epilogue), or None if the shape does not
+    allow it (the caller then runs the product and the gate separately)."""
+    from . import ops
+    m, k = x.shape
+    i = w_gate_up.shape[0] // 2
+    # one CTA per 64 features and no split of k: worth it when that alone fills the GPU
+    # (measured on the 0.6B shape, 48 tiles: 1.458 ms per step against 1.435 ms with the
+    # split product and the separate gate)
+    if i // 64 < int(os.environ.get("DIB200_GATED_MIN_TILES", "96")):
+        return None
+    if not (m <= MAX_ROWS and k % 8 == 0 and k >= 8 and i % 64 == 0 and w_gate_up.shape[0] == 2 * i
+            and x.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0):
+        return None
+    out = torch.empty(m, i, dtype=torch.bfloat16, device=x.device)
+    st = ops._lib("gemm_bf16").dib_gemm_bf16_gated(ops._ptr(x), ops._ptr(w_gate_up), ops._ptr(out),
+                                                   c_int(m), c_int(i), c_int(k), ops._stream())
+    ops._check(st, "gated_linear(bfloat16)", f"M={m} I={i} K={k}")
+    return out

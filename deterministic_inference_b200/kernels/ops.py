@@ -398,6 +398,23 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tenso
     return gemm_bf16.linear(x, weight, out_dtype or torch.bfloat16)
 
 
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(x w_gate^T) * (x w_up^T), [M, I], for the concatenated weight
+    [w_gate ; w_up] ([2I, K]).  With few bfloat16 rows the gate is applied in the matrix
+    product's epilogue; otherwise this is ``silu_mul(linear(x, w_gate_up))``."""
+    x = as_tensor(x)
+    if x.dtype == torch.bfloat16 and x.is_cuda:
+        _need(x, "x", None, 2)
+        _need(w_gate_up, "w_gate_up", x.dtype, 2)
+        if x.shape[1] != w_gate_up.shape[1]:
+            raise KernelError(f"gated_linear: x {tuple(x.shape)} against weight {tuple(w_gate_up.shape)}")
+        from . import gemm_bf16
+        out = gemm_bf16.gated_linear(x, w_gate_up)
+        if out is not None:
+            return out
+    return silu_mul(linear(x, w_gate_up))
+
+
 # ---------------------------------------------------------------- sampling
 
 def argmax(logits: torch.Tensor) -> torch.Tensor:

@@ -34,5 +34,4 @@ class GatedMLP(FeedForward):
         self.w_down = tensors[p + "down_proj.weight"]
 
     def forward(self, x):
-        gate_up = ops.linear(x, self.w_gate_up)
-        return ops.linear(ops.silu_mul(gate_up), self.w_down)
+        return ops.linear(ops.gated_linear(x, self.w_gate_up), self.w_down)

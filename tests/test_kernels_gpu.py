@@ -177,6 +177,24 @@ def test_linear_bf16_row_does_not_depend_on_batch():
     assert torch.equal(lin(x), full)
 
 
+@pytest.mark.parametrize("m,i,k", [(1, 3072, 1024), (8, 128, 72), (40, 192, 520), (100, 64, 64),
+                                   (200, 128, 96), (8, 100, 64)])
+def test_gated_linear(m, i, k, monkeypatch):
+    """silu(x Wg^T) * (x Wu^T) with the gate in the product's epilogue (few rows, I a
+    multiple of 64) or as two kernels; both against the formula with the two products
+    rounded to bfloat16 as stored."""
+    monkeypatch.setenv("DIB200_GATED_MIN_TILES", "1")      # also the small shapes take the epilogue
+    torch.manual_seed(12)
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = (0.08 * torch.randn(2 * i, k, device="cuda")).to(torch.bfloat16)
+    y = (x.float() @ w.float().T).to(torch.bfloat16).float()
+    g, u = y[:, :i], y[:, i:]
+    want = g * torch.sigmoid(g) * u
+    got = ops().gated_linear(x, w)
+    assert got.shape == (m, i) and got.dtype == torch.bfloat16
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("m", [1, 8, 50])
 def test_readers_of_split_k_partials(m):
     """The kernels that take a projection output as split-k partials give what they

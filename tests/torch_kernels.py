@@ -122,6 +122,11 @@ def silu_mul(gate_up):
     return (g * torch.sigmoid(g) * u).to(gate_up.dtype)
 
 
+def gated_linear(x, w_gate_up):
+    """sid/model/qwen3.py:84-86"""
+    return silu_mul(linear(x, w_gate_up))
+
+
 def gather_rows(x, index):
     """sid/model/qwen3.py:113"""
     return x[index.long()].contiguous()
@@ -165,4 +170,4 @@ def gumbel_sample(logits, temperatures, seeds, sample_positions, keep=None):
 
 
 ALL = ("patch_token_ids", "embedding", "rms_norm", "add_rms_norm", "qk_norm_rope_cache", "reshape_and_cache",
-       "paged_attention", "silu_mul", "gather_rows", "linear", "argmax", "gumbel_sample")
+       "paged_attention", "silu_mul", "gated_linear", "gather_rows", "linear", "argmax", "gumbel_sample")
