@@ -526,10 +526,12 @@ int launch_rms(void* x, void* res, const float* w, void* out, int rows, int H, f
                        (res == nullptr || reinterpret_cast<uintptr_t>(res) % 16 == 0) &&
                        (out == nullptr || reinterpret_cast<uintptr_t>(out) % 16 == 0) &&
                        (reinterpret_cast<uintptr_t>(w) % 16 == 0);
-  if (H % N == 0 && aligned && H / N <= 4 * 256) {
+  if (H % N == 0 && aligned && H / N <= 4 * 1024) {
     const int vecs = H / N;
     int th = 32;
-    while (th < vecs && th < 256) th <<= 1;
+    // few rows: a wide block (more loads in flight per row); many rows: 256 threads
+    const int th_max = rows <= 64 ? 1024 : 256;
+    while (th < vecs && th < th_max) th <<= 1;
     const int iters = (vecs + th - 1) / th;
     if (iters == 1)
       dib_launch(rms_norm_vec_kernel<T, ADD, 1>, dim3(rows), dim3(th), 0, st, (T*)x, (T*)res, w, (T*)out, H, eps);
@@ -758,10 +760,11 @@ int dib_add_rms_norm_split(const float* parts, int S, long long split_stride, vo
                            const float* w, void* out, int rows, int H, float eps, int dtype,
                            cudaStream_t st) {
   if (rows == 0) return DIB_OK;
-  if (H % 4 != 0 || H / 4 > 4 * 256 || S < 1) return DIB_BAD_SIZE;
+  if (H % 4 != 0 || H / 4 > 4 * 1024 || S < 1) return DIB_BAD_SIZE;
   const int vecs = H / 4;
   int th = 32;
-  while (th < vecs && th < 256) th <<= 1;
+  const int th_max = rows <= 64 ? 1024 : 256;
+  while (th < vecs && th < th_max) th <<= 1;
   const int iters = (vecs + th - 1) / th;
 #define DIB_ARS(TT, IT)                                                                         \
   dib_launch(add_rms_norm_split_kernel<TT, IT>, dim3(rows), dim3(th), 0, st, parts, S, split_stride, (TT*)residual, w, \

@@ -29,7 +29,6 @@ namespace {
 constexpr int BM = 128;      // W rows per tile = MMA M
 constexpr int BK = 64;       // k per stage: 64 bf16 = 128 bytes = one swizzle atom
 constexpr int UMMA_K = 16;   // k per tcgen05.mma for 16-bit inputs
-constexpr int STAGES = 4;
 constexpr int THREADS = 128;
 
 __device__ int dib_gemm_error_word = 0;
@@ -122,7 +121,7 @@ constexpr unsigned make_idesc(int m, int n) {
 // GATED: w is [gate rows ; up rows] of a gated feed-forward ([2N, K]); a tile holds 64
 // gate rows and the 64 up rows of the same features, and the epilogue writes
 // silu(gate) * up, [M, N], so the gate/up product never goes to memory.  k is not split.
-template <int BN, typename OutT, bool GATED>
+template <int BN, typename OutT, bool GATED, int STAGES>
 __global__ void __launch_bounds__(THREADS)
 gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  OutT* __restrict__ out, float* __restrict__ partial, int M, int N, int num_kb,
@@ -307,12 +306,16 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, in
              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BN, typename OutT, bool GATED = false>
-int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, void* out, float* partial, int M,
-                int N, int num_kb, int kb_per_split, int splits, dim3 grid, cudaStream_t st) {
+// STAGES: 4 keeps several CTAs on an SM (grids with many more CTAs than SMs overlap one
+// CTA's ramp-up with another's stream); 8 keeps more bytes in flight for a CTA that has
+// the SM to itself and a long range of k to walk.
+template <int BN, typename OutT, bool GATED, int STAGES>
+int launch_swap_stages(const CUtensorMap& mw, const CUtensorMap& mx, void* out, float* partial,
+                       int M, int N, int num_kb, int kb_per_split, int splits, dim3 grid,
+                       cudaStream_t st) {
   constexpr size_t smem =
       (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
-  auto kern = gemm_swap_kernel<BN, OutT, GATED>;
+  auto kern = gemm_swap_kernel<BN, OutT, GATED, STAGES>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
@@ -324,6 +327,18 @@ int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, void* out, float* 
                                     splits);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
+}
+
+template <int BN, typename OutT, bool GATED = false>
+int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, void* out, float* partial, int M,
+                int N, int num_kb, int kb_per_split, int splits, dim3 grid, cudaStream_t st) {
+  const long long ctas = (long long)grid.x * grid.y * grid.z;
+  constexpr int DEEP = BN <= 32 ? 8 : (BN <= 64 ? 6 : 5);
+  if (kb_per_split >= 6 && ctas <= 2 * 160)
+    return launch_swap_stages<BN, OutT, GATED, DEEP>(mw, mx, out, partial, M, N, num_kb,
+                                                     kb_per_split, splits, grid, st);
+  return launch_swap_stages<BN, OutT, GATED, 4>(mw, mx, out, partial, M, N, num_kb, kb_per_split,
+                                                splits, grid, st);
 }
 
 }  // namespace
