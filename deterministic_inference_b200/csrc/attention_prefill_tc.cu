@@ -8,15 +8,16 @@
 // token, so the order of a row's reduction depends on its position alone.  Ten warps:
 //   warps 0-7  softmax: two threads share a row (tensor-memory lane = row; warp w reads
 //              lanes 32(w%4).., and half w/4 of the columns).  Both read all of S_j for
-//              the row's maximum; each computes the probabilities of its 64 keys, writes
-//              them (bf16) to shared memory as the A operand of the second product, keeps
-//              the sum of its half, and adds its 64 dims of O_j into a float32
-//              accumulator (rescaled by exp(m_old - m_new)).
+//              the row's maximum; each computes the probabilities of its 64 keys against
+//              a reference maximum, writes them (bf16) to shared memory as the A operand
+//              of the second product and keeps the sum of its half.  O stays in tensor
+//              memory and is accumulated there by the MMA; a row's O is rescaled (read,
+//              multiplied, written back) only when the reference maximum has to rise.
 //   warp 8     TMA: one copy per (page, key-or-value, 64-column half) of a tile, two
 //              stages.
-//   warp 9     MMA issue: S_j = Q K_j^T, then (after the P of the tile is in shared
-//              memory) O_j = P_j V_j, then at once S_{j+1}, which overlaps the
-//              accumulation of O_j.
+//   warp 9     MMA issue: S is double-buffered in tensor memory, so S_{j+1} = Q K_{j+1}^T
+//              runs while the softmax threads work on S_j; O += P_j V_j follows as soon
+//              as P_j is in shared memory.
 // Operand layouts (all 128-byte swizzle): Q, K, P K-major [halves][rows][64]; V is
 // read as the MN-major B operand straight from its [key][dim] tile.  head_dim 128,
 // group ratio dividing 128, page_size dividing 128 (at least 8).  Every mbarrier wait
@@ -86,6 +87,21 @@ __device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned (&r)[32]) {
       : "r"(taddr));
 }
 
+__device__ __forceinline__ void tc_st32(unsigned taddr, const unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, "
+      "%12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, "
+      "%30, %31, %32};\n" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+      "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // K-major operand, rows of 128 bytes, 128-byte swizzle: 8-row groups 1024 bytes apart.
 __device__ __forceinline__ unsigned long long desc_k_major(unsigned addr) {
   unsigned long long d = 0;
@@ -132,12 +148,13 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
   unsigned char* sP = smem + TILE_BYTES;          // 32 KB
   unsigned char* sKV = smem + 2 * TILE_BYTES;     // 2 stages x (K 32 KB + V 32 KB)
   unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + 6 * TILE_BYTES);
-  unsigned long long* kv_full = bars;             // [2]
-  unsigned long long* kv_empty = bars + 2;        // [2]
-  unsigned long long* bar_s = bars + 4;           // S_j is in tensor memory
-  unsigned long long* bar_p = bars + 5;           // P_j is in shared memory (128 arrivals)
-  unsigned long long* bar_o = bars + 6;           // O_j is in tensor memory
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 7);
+  unsigned long long* kv_full = bars;             // [2] K and V of a tile are in shared memory
+  unsigned long long* kv_empty = bars + 2;        // [2] both products of the tile have read them
+  unsigned long long* s_full = bars + 4;          // [2] S_j is in tensor memory (buffer j & 1)
+  unsigned long long* s_free = bars + 6;          // [2] the softmax threads have read it (256)
+  unsigned long long* p_full = bars + 8;          // P_j is in shared memory, O is rescaled (256)
+  unsigned long long* o_done = bars + 9;          // O += P_j V_j has completed
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 10);
 
   // blocks are handed out in x-then-y order: y counts the tiles from the longest down
   const int tile = gridDim.y - 1 - blockIdx.y, kvh = blockIdx.x;
@@ -159,19 +176,20 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
   const int ntiles = j1 - j0 + 1;
 
   if (warp == MMA_WARP && lane == 0) {
-    mbar_init(&kv_full[0], 1);
-    mbar_init(&kv_full[1], 1);
-    mbar_init(&kv_empty[0], 1);
-    mbar_init(&kv_empty[1], 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_p, 256);
-    mbar_init(bar_o, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_free[i], 256);
+    }
+    mbar_init(p_full, 256);
+    mbar_init(o_done, 1);
     mbar_fence_init();
   }
   if (warp == TMA_WARP) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
-                 "r"(256u));
+                 "r"(512u));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   // Q tile -> shared memory, swizzled; rows beyond the tile's tokens are zero
@@ -190,7 +208,7 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
   __syncthreads();
   tc_fence_after();
   const unsigned tmem = *tmem_slot;
-  const unsigned tmem_s = tmem, tmem_o = tmem + 128;   // columns 0..127: S, 128..255: O_j
+  const unsigned tmem_o = tmem + 256;   // columns 0..127: S (even tiles), 128..255: S (odd), 256..383: O
   bool ok = true;
 
   if (warp == TMA_WARP) {
@@ -216,7 +234,8 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
       }
     }
   } else if (warp == MMA_WARP) {
-    // ---- MMA issue (one lane)
+    // ---- MMA issue (one lane).  S of the next tile is issued before P V of this one, so
+    // it runs while the softmax threads work on this tile.
     if (lane == 0) {
       constexpr unsigned idesc_s = idesc_f16(TC_M, TC_N, 0);
       constexpr unsigned idesc_o = idesc_f16(TC_M, TC_D, 1);
@@ -226,10 +245,10 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
 #pragma unroll
         for (int ks = 0; ks < TC_D / 16; ++ks) {
           const unsigned off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          tc_mma(tmem_s, desc_k_major(q_addr + off), desc_k_major(k_addr + off), idesc_s,
-                 ks > 0 ? 1u : 0u);
+          tc_mma(tmem + (i & 1) * 128, desc_k_major(q_addr + off), desc_k_major(k_addr + off),
+                 idesc_s, ks > 0 ? 1u : 0u);
         }
-        tc_commit(bar_s);
+        tc_commit(&s_full[i & 1]);
       };
       ok = mbar_wait(&kv_full[0], 0);
       if (ok) {
@@ -237,30 +256,34 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
         issue_s(0);
       }
       for (int i = 0; i < ntiles && ok; ++i) {
-        const int st = i & 1;
-        ok = mbar_wait(bar_p, i & 1);   // P_i is in shared memory, S_i has been read
+        if (i + 1 < ntiles) {
+          ok = mbar_wait(&kv_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
+          if (ok && i + 1 >= 2) ok = mbar_wait(&s_free[(i + 1) & 1], (((i + 1) >> 1) - 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(i + 1);
+        }
+        ok = mbar_wait(p_full, i & 1);   // P_i is in shared memory, O is rescaled
         if (!ok) break;
         tc_fence_after();
-        const unsigned v_addr = smem_u32(sKV + st * 2 * TILE_BYTES + TILE_BYTES);
+        const unsigned v_addr = smem_u32(sKV + (i & 1) * 2 * TILE_BYTES + TILE_BYTES);
 #pragma unroll
         for (int ks = 0; ks < TC_N / 16; ++ks) {
           const unsigned a_off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;   // 16 keys of P
           const unsigned b_off = ks * 16 * 128;                            // 16 key rows of V
           tc_mma(tmem_o, desc_k_major(p_addr + a_off), desc_mn_major(v_addr + b_off, HALF_BYTES),
-                 idesc_o, ks > 0 ? 1u : 0u);
+                 idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
         }
-        tc_commit(bar_o);
-        tc_commit(&kv_empty[st]);
-        if (i + 1 < ntiles) {
-          ok = mbar_wait(&kv_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
-          if (!ok) break;
-          tc_fence_after();
-          issue_s(i + 1);
-        }
+        tc_commit(o_done);
+        tc_commit(&kv_empty[i & 1]);
       }
     }
   } else {
-    // ---- softmax: two threads per row, each with half of the keys and of the dims
+    // ---- softmax: two threads per row, each with half of the keys and of the dims.
+    // The exponentials are taken against a reference maximum that is only raised when the
+    // tile's maximum exceeds it by more than 2^8; O (in tensor memory) and the sum are
+    // rescaled then.  The result is the same sum, scaled by a common factor that the
+    // final division removes.
     const int r = threadIdx.x & 127;
     const int hf = threadIdx.x >> 7;                 // 0: keys/dims 0..63, 1: 64..127
     const int tl = r / G, g = r % G;
@@ -269,12 +292,10 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
     const int lo = (valid && window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
     const float scale_log2 = scale * LOG2E;
     const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;
-    float acc[TC_D / 2];
-#pragma unroll
-    for (int d = 0; d < TC_D / 2; ++d) acc[d] = 0.f;
-    float m = NEG_BIG, l = 0.f;
+    float m_ref = NEG_BIG, l = 0.f;
     for (int i = 0; i < ntiles && ok; ++i) {
-      ok = mbar_wait(bar_s, i & 1);
+      const unsigned tmem_s = tmem + (i & 1) * 128;
+      ok = mbar_wait(&s_full[i & 1], (i >> 1) & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -302,81 +323,95 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
         }
       }
       mx = mx <= -1e29f ? NEG_BIG : mx * scale_log2;   // scale is positive
-      const float m_new = fmaxf(m, mx);
-      const float m_safe = m_new <= -1e29f ? 0.f : m_new;
-      const float alpha = fast_exp2(m - m_safe);
-      // pass 2: probabilities of this thread's 64 keys -> bf16 -> shared memory
+      // raise the reference only when it must be (or at the first visible key)
+      float factor = 1.0f;
+      bool rescale = false;
+      if (mx > m_ref + 8.0f) {
+        rescale = m_ref > -1e29f;
+        factor = rescale ? fast_exp2(m_ref - mx) : 0.f;
+        m_ref = mx;
+        l *= factor;
+      }
+      const float m_use = m_ref <= -1e29f ? 0.f : m_ref;
+      // pass 2: probabilities of this thread's 64 keys, 32 at a time
+      unsigned pk[32];
       float sum = 0.f;
-      {
-        unsigned v0[32], v1[32];
-        tc_ld32(tmem_s + lane_base + hf * 64, v0);
-        tc_ld32(tmem_s + lane_base + hf * 64 + 32, v1);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        unsigned v[32];
+        tc_ld32(tmem_s + lane_base + hf * 64 + c * 32, v);
         tc_wait_ld();
-        float p0[32], p1[32];
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const int key = kbase + hf * 64 + k;
+        for (int k = 0; k < 32; k += 2) {
+          const int key = kbase + hf * 64 + c * 32 + k;
           const bool vis0 = full || (key >= lo && key <= hi);
-          const bool vis1 = full || (key + 32 >= lo && key + 32 <= hi);
-          p0[k] = vis0 ? fast_exp2(__uint_as_float(v0[k]) * scale_log2 - m_safe) : 0.f;
-          p1[k] = vis1 ? fast_exp2(__uint_as_float(v1[k]) * scale_log2 - m_safe) : 0.f;
-          sum += p0[k] + p1[k];
-        }
-#pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint4 pk;
-          pk.x = pack_bf16(p0[ch * 8 + 0], p0[ch * 8 + 1]);
-          pk.y = pack_bf16(p0[ch * 8 + 2], p0[ch * 8 + 3]);
-          pk.z = pack_bf16(p0[ch * 8 + 4], p0[ch * 8 + 5]);
-          pk.w = pack_bf16(p0[ch * 8 + 6], p0[ch * 8 + 7]);
-          *reinterpret_cast<uint4*>(sP + sw_chunk_off(r, hf * 8 + ch)) = pk;
-          pk.x = pack_bf16(p1[ch * 8 + 0], p1[ch * 8 + 1]);
-          pk.y = pack_bf16(p1[ch * 8 + 2], p1[ch * 8 + 3]);
-          pk.z = pack_bf16(p1[ch * 8 + 4], p1[ch * 8 + 5]);
-          pk.w = pack_bf16(p1[ch * 8 + 6], p1[ch * 8 + 7]);
-          *reinterpret_cast<uint4*>(sP + sw_chunk_off(r, hf * 8 + 4 + ch)) = pk;
+          const bool vis1 = full || (key + 1 >= lo && key + 1 <= hi);
+          const float p0 = vis0 ? fast_exp2(__uint_as_float(v[k]) * scale_log2 - m_use) : 0.f;
+          const float p1 = vis1 ? fast_exp2(__uint_as_float(v[k + 1]) * scale_log2 - m_use) : 0.f;
+          sum += p0 + p1;
+          pk[c * 16 + (k >> 1)] = pack_bf16(p0, p1);
         }
       }
-      l = l * alpha + sum;
-      m = m_new;
+      l += sum;
+      tc_fence_before();
+      mbar_arrive(&s_free[i & 1]);            // S_i has been read: S_{i+2} may overwrite it
+      // P_{i-1} V_{i-1} must have completed before P is overwritten and O is touched
+      if (i > 0) {
+        ok = mbar_wait(o_done, (i - 1) & 1);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          unsigned v[32];
+          tc_ld32(tmem_o + lane_base + hf * 64 + c * 32, v);
+          tc_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 32; ++k) v[k] = __float_as_uint(__uint_as_float(v[k]) * (rescale ? factor : 1.0f));
+          tc_st32(tmem_o + lane_base + hf * 64 + c * 32, v);
+        }
+        tc_wait_st();
+      }
+#pragma unroll
+      for (int ch = 0; ch < 8; ++ch)
+        *reinterpret_cast<uint4*>(sP + sw_chunk_off(r, hf * 8 + ch)) =
+            make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       tc_fence_before();
-      mbar_arrive(bar_p);
-      // this thread's 64 dims of O_j -> accumulator
-      ok = mbar_wait(bar_o, i & 1);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      tc_fence_after();
-      {
-        unsigned v0[32], v1[32];
-        tc_ld32(tmem_o + lane_base + hf * 64, v0);
-        tc_ld32(tmem_o + lane_base + hf * 64 + 32, v1);
-        tc_wait_ld();
-#pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          acc[k] = acc[k] * alpha + __uint_as_float(v0[k]);
-          acc[32 + k] = acc[32 + k] * alpha + __uint_as_float(v1[k]);
-        }
-      }
-      tc_fence_before();
+      mbar_arrive(p_full);
     }
-    // the row's sum is the sum of its two halves (sP is free now: reuse it)
-    float* sL = reinterpret_cast<float*>(sP);
+    // the last product, then O / (sum of the row's two halves)
+    if (ok) {
+      ok = mbar_wait(o_done, (ntiles - 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    tc_fence_after();
+    float* sL = reinterpret_cast<float*>(sP);       // free now
     sL[hf * 128 + r] = l;
     asm volatile("bar.sync 1, 256;" ::: "memory");
     const float l_row = sL[r] + sL[128 + r];
-    if (ok && valid) {
+    if (ok) {
       const float inv = 1.0f / l_row;
       const size_t t = (size_t)(q_begin + tok0 + tl);
       __nv_bfloat16* dst = out + (t * Hq + (size_t)kvh * G + g) * TC_D + hf * 64;
 #pragma unroll
-      for (int ch = 0; ch < TC_D / 16; ++ch) {
-        uint4 pk;
-        pk.x = pack_bf16(acc[ch * 8 + 0] * inv, acc[ch * 8 + 1] * inv);
-        pk.y = pack_bf16(acc[ch * 8 + 2] * inv, acc[ch * 8 + 3] * inv);
-        pk.z = pack_bf16(acc[ch * 8 + 4] * inv, acc[ch * 8 + 5] * inv);
-        pk.w = pack_bf16(acc[ch * 8 + 6] * inv, acc[ch * 8 + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + ch * 8) = pk;
+      for (int c = 0; c < 2; ++c) {
+        unsigned v[32];
+        tc_ld32(tmem_o + lane_base + hf * 64 + c * 32, v);
+        tc_wait_ld();
+        if (valid) {
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 o4;
+            o4.x = pack_bf16(__uint_as_float(v[ch * 8 + 0]) * inv, __uint_as_float(v[ch * 8 + 1]) * inv);
+            o4.y = pack_bf16(__uint_as_float(v[ch * 8 + 2]) * inv, __uint_as_float(v[ch * 8 + 3]) * inv);
+            o4.z = pack_bf16(__uint_as_float(v[ch * 8 + 4]) * inv, __uint_as_float(v[ch * 8 + 5]) * inv);
+            o4.w = pack_bf16(__uint_as_float(v[ch * 8 + 6]) * inv, __uint_as_float(v[ch * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c * 32 + ch * 8) = o4;
+          }
+        }
       }
     }
   }
@@ -384,7 +419,7 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
   tc_fence_before();
   __syncthreads();
   if (warp == TMA_WARP) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u));
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
   }
 }
 
@@ -447,7 +482,7 @@ int dib_extend_attention_tc(const void* q, void* out, const void* cache, long lo
     return DIB_BAD_SIZE;
   const CUtensorMap* map = cache_map(cache, num_pages, Hkv, page_size, D);
   if (map == nullptr) return DIB_LAUNCH_FAILED;
-  const size_t smem = 6 * TILE_BYTES + 8 * 8 + 16 + 1024;
+  const size_t smem = 6 * TILE_BYTES + 10 * 8 + 16 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(extend_attention_tc_kernel,
