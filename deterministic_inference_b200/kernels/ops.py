@@ -43,7 +43,16 @@ def _ptr(t):
     return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
 
 
+try:
+    _raw_stream = torch._C._cuda_getCurrentRawStream      # a plain integer handle, cheap
+except AttributeError:                                     # pragma: no cover
+    _raw_stream = None
+
+
 def _stream():
+    """Handle of the current CUDA stream of the current device."""
+    if _raw_stream is not None:
+        return c_void_p(_raw_stream(torch.cuda.current_device()))
     return c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
