@@ -141,6 +141,10 @@ def main() -> int:
     ap.add_argument("--points", default="1,64", help="extra decode batch sizes")
     ap.add_argument("--point-steps", type=int, default=64)
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--workload", default="decode", choices=["decode", "mixed"],
+                    help="mixed: the continuous-batching run of the benchmark configurations "
+                         "(64 requests, prompts uniform in [128, 2048], 256 outputs each, "
+                         "temperature 0.7) through Engine.generate; prints its own line")
     ap.add_argument("--no-prefill", action="store_true")
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
                     help="bracket this region with cudaProfilerStart/Stop (for ncu "
@@ -192,6 +196,28 @@ def main() -> int:
         e.record()
         torch.cuda.synchronize()
         return s.elapsed_time(e)
+
+    if a.workload == "mixed":
+        n_req, n_out = 64, 256
+        lens = torch.randint(128, 2049, (n_req,), generator=gen).tolist()
+        prompts = [random_prompt(n) for n in lens]
+        sp = SamplingParams(max_new_tokens=n_out, temperature=0.7, seed=7, ignore_eos=True)
+        engine.generate(prompts[:4], SamplingParams(max_new_tokens=8, temperature=0.7, ignore_eos=True))
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        outs = engine.generate(prompts, sp)
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        assert all(len(o.token_ids) == n_out for o in outs)
+        print(json.dumps({
+            "metric": "continuous batching output tok/s (bf16, 1 B200)", "value": n_req * n_out / dt,
+            "unit": "tokens/s", "n_gpus": 1, "seconds": dt, "requests": n_req,
+            "prompt_tokens": sum(lens), "output_tokens": n_req * n_out, "temperature": 0.7,
+            "steps": engine.runner.steps_run, "preemptions": engine.scheduler.num_preemptions,
+            "graph_replays": graphs.replays if graphs else 0, "dtype": "bf16", "data": "synthetic",
+            "config": {"model": a.preset, "layers": layers, "layers_full": full.num_hidden_layers,
+                       "max_prefill_tokens": ecfg.max_prefill_tokens}}))
+        return 0
 
     # ---------------- prefill of one prompt, whole ----------------
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > L2

@@ -7,6 +7,8 @@ keep their names here (``--model``, ``--kv-pool-tokens``).
   generate   run prompts (token ids) to completion and print the generated ids
   random     write a model folder with random weights from a preset and a seed
   build      compile every CUDA library for sm_100a
+  replay     trace replay (the program bin/trace_run: steps on standard input, logits to disk)
+  bench      the benchmark (the program bench.py at the repository root)
 """
 
 from __future__ import annotations
@@ -73,7 +75,31 @@ def _cmd_build(a) -> int:
     return 0
 
 
+def _run_script(path, args) -> int:
+    import runpy
+    from pathlib import Path
+
+    script = Path(__file__).resolve().parent.parent / path
+    if not script.exists():
+        print(f"{script} is not there (this command needs the repository checkout)", file=sys.stderr)
+        return 2
+    old = sys.argv
+    sys.argv = [str(script)] + list(args)
+    try:
+        runpy.run_path(str(script), run_name="__main__")
+    except SystemExit as e:
+        return int(e.code or 0)
+    finally:
+        sys.argv = old
+    return 0
+
+
 def main(argv=None) -> int:
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv and argv[0] == "replay":
+        return _run_script("bin/trace_run", argv[1:])
+    if argv and argv[0] == "bench":
+        return _run_script("bench.py", argv[1:])
     ap = argparse.ArgumentParser(prog="python -m deterministic_inference_b200", description=__doc__,
                                  formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)

@@ -526,11 +526,11 @@ int launch_rms(void* x, void* res, const float* w, void* out, int rows, int H, f
                        (res == nullptr || reinterpret_cast<uintptr_t>(res) % 16 == 0) &&
                        (out == nullptr || reinterpret_cast<uintptr_t>(out) % 16 == 0) &&
                        (reinterpret_cast<uintptr_t>(w) % 16 == 0);
-  if (H % N == 0 && aligned && H / N <= 4 * 1024) {
+  // few rows: a wide block (more loads in flight per row); many rows: 256 threads
+  const int th_max = rows <= 64 ? 1024 : 256;
+  if (H % N == 0 && aligned && H / N <= 4 * th_max) {   // at most 4 vectors per thread
     const int vecs = H / N;
     int th = 32;
-    // few rows: a wide block (more loads in flight per row); many rows: 256 threads
-    const int th_max = rows <= 64 ? 1024 : 256;
     while (th < vecs && th < th_max) th <<= 1;
     const int iters = (vecs + th - 1) / th;
     if (iters == 1)
@@ -760,10 +760,10 @@ int dib_add_rms_norm_split(const float* parts, int S, long long split_stride, vo
                            const float* w, void* out, int rows, int H, float eps, int dtype,
                            cudaStream_t st) {
   if (rows == 0) return DIB_OK;
-  if (H % 4 != 0 || H / 4 > 4 * 1024 || S < 1) return DIB_BAD_SIZE;
+  const int th_max = rows <= 128 ? 1024 : 256;
+  if (H % 4 != 0 || H / 4 > 4 * th_max || S < 1) return DIB_BAD_SIZE;   // at most 4 per thread
   const int vecs = H / 4;
   int th = 32;
-  const int th_max = rows <= 64 ? 1024 : 256;
   while (th < vecs && th < th_max) th <<= 1;
   const int iters = (vecs + th - 1) / th;
 #define DIB_ARS(TT, IT)                                                                         \

@@ -205,7 +205,7 @@ def add_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, 
         if tuple(residual.shape) != (rows, h) or weight.shape[0] != h:
             raise KernelError(f"add_rms_norm: x {(rows, h)} vs residual {tuple(residual.shape)}, "
                               f"weight {weight.shape[0]}")
-        if h % 4 == 0 and h <= 16384:
+        if h % 4 == 0 and h <= (16384 if rows <= 128 else 4096):
             out = torch.empty(rows, h, dtype=x.dtype, device=x.device)
             st = _lib("elementwise").dib_add_rms_norm_split(
                 _ptr(x.parts), c_int(s_), c_longlong(rows * h), _ptr(residual), _ptr(weight),

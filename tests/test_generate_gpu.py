@@ -154,3 +154,57 @@ def test_preset_with_random_weights_on_the_device():
                                   device="cuda:0"))
         outs.append(eng.generate([[1, 2, 3, 4, 5]], SamplingParams(max_new_tokens=8, ignore_eos=True))[0].token_ids)
     assert outs[0] == outs[1] and len(outs[0]) == 8
+
+
+@pytest.mark.parametrize("name,layers", [("qwen3_0_6b", 2), ("qwen3_8b", 2), ("qwen3_32b", 1)])
+def test_published_shapes_run(name, layers):
+    """The layer sizes of the three benchmark shapes (16/8, 32/8 and 64/8 heads of 128,
+    widths 1024/4096/5120, intermediate 3072/12288/25600, vocabulary 151936) with a few
+    layers and random weights drawn on the device: a prompt in two portions, a second
+    request, then decoding through the graph path; every kernel takes its fast path
+    without complaint and the float32 engine agrees on the first tokens."""
+    from deterministic_inference_b200 import Engine, EngineConfig, SamplingParams, preset
+    from deterministic_inference_b200.kernels import attention_bf16, gemm_bf16, ops
+    cfg = preset(name, num_hidden_layers=layers, max_window_layers=layers)
+    prompts = _prompts(cfg.vocab_size, (300, 37), 9)
+    outs = {}
+    for dtype in ("bfloat16", "float32"):
+        eng = Engine(EngineConfig(model_config=cfg, random_seed=1, dtype=dtype, kv_pool_tokens=2048,
+                                  max_reqs=8, max_seq_len=1024, max_prefill_tokens=256,
+                                  device="cuda:0"))
+        n = 24 if dtype == "bfloat16" else 3
+        outs[dtype] = [o.token_ids for o in eng.generate(
+            prompts, SamplingParams(max_new_tokens=n, ignore_eos=True))]
+        del eng
+        torch.cuda.empty_cache()
+    assert all(len(t) == 24 for t in outs["bfloat16"])
+    assert gemm_bf16.status() == 0
+    assert ops._lib("attention_bf16").dib_attention_bf16_status() == 0
+    # the first token of each request agrees with the 32-bit path (later ones may flip on
+    # near ties of a random model's flat logits)
+    assert [t[0] for t in outs["bfloat16"]] == [t[0] for t in outs["float32"]]
+
+
+@pytest.mark.parametrize("name,layers", [("qwen3_0_6b", 2), ("qwen3_8b", 2), ("qwen3_32b", 1)])
+def test_published_shapes_logits_agree_across_dtypes(name, layers):
+    """At the benchmark layer sizes the bfloat16 and the float32 step give the same
+    logits up to bfloat16 storage (about 1% of the largest logit after a few layers):
+    a kernel that mishandles a width, a head count or an intermediate size in one of the
+    two paths shows here as a difference of the logits' own size."""
+    from deterministic_inference_b200 import EngineConfig, preset
+    from deterministic_inference_b200.engine.batch import SequenceInput
+    from deterministic_inference_b200.engine.runner import ModelRunner
+    cfg = preset(name, num_hidden_layers=layers, max_window_layers=layers)
+    toks = _prompts(cfg.vocab_size, (300,), 9)[0]
+    res = {}
+    for dtype in ("bfloat16", "float32"):
+        r = ModelRunner(EngineConfig(model_config=cfg, random_seed=1, dtype=dtype, kv_pool_tokens=1024,
+                                     max_reqs=4, max_seq_len=512, device="cuda:0"))
+        slot = r.cache.allocate_slot()
+        r.step([SequenceInput(slot, toks[:200], 0, [])])
+        logits, _ = r.step([SequenceInput(slot, toks[200:], 200, [0, 50, 99])])
+        res[dtype] = logits.float().cpu()
+        del r
+        torch.cuda.empty_cache()
+    a, b = res["bfloat16"], res["float32"]
+    assert (a - b).abs().max().item() <= 0.03 * b.abs().max().item()

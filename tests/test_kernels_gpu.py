@@ -34,7 +34,8 @@ def test_embedding(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,h", [(1, 1024), (7, 5120), (33, 200), (128, 96), (3, 12288)])
+@pytest.mark.parametrize("rows,h", [(1, 1024), (7, 5120), (33, 200), (128, 96), (3, 12288),
+                                    (200, 5120), (70, 8192), (65, 4100), (2, 16384), (100, 20000)])
 def test_rms_norm(dtype, rows, h):
     torch.manual_seed(1)
     x = torch.randn(rows, h, device="cuda").to(dtype)
@@ -45,7 +46,8 @@ def test_rms_norm(dtype, rows, h):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("rows,h", [(1, 1024), (9, 4096), (33, 200)])
+@pytest.mark.parametrize("rows,h", [(1, 1024), (9, 4096), (33, 200), (200, 5120), (66, 8192),
+                                    (3, 16384), (80, 12288)])
 def test_add_rms_norm(dtype, rows, h):
     torch.manual_seed(2)
     x = torch.randn(rows, h, device="cuda").to(dtype)
@@ -233,6 +235,28 @@ def test_readers_of_split_k_partials(m):
     q1 = o.qk_norm_rope_cache(qkv, hq, hkv, d, qn, kn, 1e-6, table, pos, c1, slots, 16)
     q2 = o.qk_norm_rope_cache(qkv.tensor(), hq, hkv, d, qn, kn, 1e-6, table, pos, c2, slots, 16)
     assert torch.equal(q1, q2) and torch.equal(c1, c2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,h,splits", [(3, 5120, 2), (100, 5120, 3), (128, 8192, 2), (5, 16384, 4),
+                                           (128, 20000, 2), (7, 1028, 5)])
+def test_add_rms_norm_of_partials_wide_rows(dtype, rows, h, splits):
+    """Residual-add + norm reading split-k partials at row widths beyond what one
+    pass of a block covers (also the widths that take the summed-tensor route)."""
+    o = ops()
+    torch.manual_seed(rows + h)
+    parts = torch.randn(splits, rows, h, device="cuda")
+    res = torch.randn(rows, h, device="cuda").to(dtype)
+    w = torch.randn(h, device="cuda")
+    got, r1 = o.add_rms_norm(o.SplitSum(parts, dtype), res.clone(), w, 1e-5)
+    acc = parts[0].clone()
+    for i in range(1, splits):
+        acc += parts[i]
+    x = acc.to(dtype)
+    want, r2 = ref.add_rms_norm(x.clone(), res.clone(), w, 1e-5)
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(r1.float(), r2.float(), **tol)
+    torch.testing.assert_close(got.float(), want.float(), **tol)
 
 
 # ------------------------------------------------------------------ attention
