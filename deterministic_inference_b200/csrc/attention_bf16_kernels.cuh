@@ -64,21 +64,6 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned by
       ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
-// Wait for a phase of the barrier with a bound: after ~2^20 polls (each poll may
-// itself block for a while in hardware) the wait gives up and reports false.
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-  for (int i = 0; i < (1 << 20); ++i) {
-    unsigned ok;
-    asm volatile(
-        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; "
-        "selp.u32 %0, 1, 0, p; }"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
 
 // Set when a bounded wait ran out; read by dib_attention_bf16_status().
 __device__ int dib_attention_error_word = 0;
@@ -188,7 +173,7 @@ __device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&p)[N
 // (row0 = lane/4, row1 = row0 + 8).  Scores arrive as raw dot products; they leave as
 // exp2((s*scale - m) * log2e).  `o` is rescaled.  key index of s[nt][i]:
 // kbase + nt*8 + (lane%4)*2 + (i&1), row (i>>1).
-template <int D, int NK>
+template <int D, int NK, bool FIRST = false>   // FIRST: o is still zero, nothing to rescale
 __device__ __forceinline__ void softmax_tile(float (&s)[NK / 8][4], float (&o)[D / 8][4],
                                              float (&mrow)[2], float (&lrow)[2], int kbase,
                                              const int (&lo)[2], const int (&hi)[2],
@@ -229,12 +214,14 @@ __device__ __forceinline__ void softmax_tile(float (&s)[NK / 8][4], float (&o)[D
     sum[rr] += __shfl_xor_sync(0xffffffffu, sum[rr], 2);
     lrow[rr] = lrow[rr] * alpha[rr] + sum[rr];
   }
+  if (!FIRST) {
 #pragma unroll
-  for (int dt = 0; dt < D / 8; ++dt) {
-    o[dt][0] *= alpha[0];
-    o[dt][1] *= alpha[0];
-    o[dt][2] *= alpha[1];
-    o[dt][3] *= alpha[1];
+    for (int dt = 0; dt < D / 8; ++dt) {
+      o[dt][0] *= alpha[0];
+      o[dt][1] *= alpha[0];
+      o[dt][2] *= alpha[1];
+      o[dt][3] *= alpha[1];
+    }
   }
 }
 

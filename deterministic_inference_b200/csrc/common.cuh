@@ -112,3 +112,32 @@ static inline void dib_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   cfg.numAttrs = dib_pdl_enabled() ? 1 : 0;
   cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
+
+// ---- bounded wait on a shared-memory mbarrier.  A copy or a tensor-core operation
+// completes within microseconds; a wait that has lasted a second means the kernel's
+// bookkeeping is broken.  It then gives up and reports false, so that the kernel can
+// set its error word and end instead of spinning for good.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(bar);
+  unsigned long long t0 = 0;
+  for (unsigned i = 1;; ++i) {
+    unsigned ok;
+    asm volatile(
+        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; "
+        "selp.u32 %0, 1, 0, p; }"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((i & 255u) == 0) {
+      const unsigned long long t = global_timer_ns();
+      if (t0 == 0) t0 = t;
+      else if (t - t0 > 1000000000ull) return false;
+    }
+  }
+}

@@ -44,19 +44,6 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned
                "r"(bytes)
                : "memory");
 }
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
-  for (int i = 0; i < (1 << 20); ++i) {
-    unsigned ok;
-    asm volatile(
-        "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; "
-        "selp.u32 %0, 1, 0, p; }"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    if (ok) return true;
-  }
-  return false;
-}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1,
                                             unsigned long long* bar) {
   asm volatile(

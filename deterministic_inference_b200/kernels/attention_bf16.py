@@ -51,11 +51,14 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
                   torch.empty(nd, hq, max_splits, dtype=torch.float32, device=q.device))
             meta.scratch[("decode_ws", hq, d, max_splits)] = ws
         use_tma = os.environ.get("DIB200_DECODE_TMA", "1") != "0"
+        # 0: one split per CTA; 1: one CTA per SM walks the splits, copies pipelined;
+        # 2: the latter when the step has more splits than CTAs that run at once
+        pipelined = int(os.environ.get("DIB200_DECODE_PIPE", "2"))
         st = lib.dib_decode_attention_bf16(
             _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0] if use_tma else 0),
             _ptr(bt), c_int(bt.shape[1]), _ptr(meta.seq_lens),
             _ptr(ws[0]), _ptr(ws[1]), c_int(nd), c_int(max_splits), c_int(hq), c_int(hkv), c_int(d),
-            c_int(page_size), c_float(scale), c_int(window), _stream())
+            c_int(page_size), c_float(scale), c_int(window), c_int(pipelined), _stream())
         _check(st, "decode_attention_bf16", f"heads {hq}/{hkv}, head_dim {d}", kernels=2)
     group = hq // hkv
     if b > nd and d == 128 and TC_TILE_ROWS % group == 0 and page_size in (8, 16, 32, 64, 128) \

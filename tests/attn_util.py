@@ -49,10 +49,10 @@ class PagedCase:
         for s, n in enumerate(lens):
             pl = [perm.pop() for _ in range(pages_per[s])]
             self.tables.append(pl)
-            for pos in range(n):
-                p, o = pl[pos // page_size], pos % page_size
-                self.cache[p, 0, :, o] = self.k[s][pos]
-                self.cache[p, 1, :, o] = self.v[s][pos]
+            pos = torch.arange(n, device=device)
+            pidx = torch.tensor(pl, device=device)[pos // page_size]
+            self.cache[pidx, 0, :, pos % page_size] = self.k[s]
+            self.cache[pidx, 1, :, pos % page_size] = self.v[s]
         self.device = device
 
     def meta(self, seqs, q_ranges):

@@ -289,6 +289,33 @@ def test_paged_attention_mixed_batch(dtype, hq, hkv, d, page):
         off += n
 
 
+@pytest.mark.parametrize("hq,hkv,d,page,window", [(16, 8, 128, 16, None), (8, 2, 128, 8, 300), (64, 8, 128, 128, None),
+                                                  (4, 1, 64, 32, None), (6, 3, 64, 16, 129), (32, 8, 128, 64, 1000)])
+def test_decode_attention_pipelined_walk_gives_the_same_bits(monkeypatch, hq, hkv, d, page, window):
+    """The decode kernel that walks many splits per CTA with its copies pipelined gives,
+    bit for bit, what the one-split-per-CTA kernel gives (each split is computed alike),
+    with enough splits that every CTA reuses its stages several times, ragged lengths at
+    split and page edges, and windows that cut splits off the front; both agree with the
+    dense reference."""
+    g = torch.Generator().manual_seed(5)
+    n_seq = 24 * max(1, 8 // hkv)
+    lens = torch.randint(1, 1400, (n_seq,), generator=g).tolist()
+    lens[:6] = [1, 128, 129, 1280, 127, 1399]
+    case = PagedCase(lens, hkv, d, page, torch.bfloat16, seed=21)
+    seqs = list(range(n_seq))
+    meta = case.meta(seqs, [(n - 1, 1) for n in lens])
+    q = torch.randn(n_seq, hq, d, generator=g).to(device="cuda", dtype=torch.bfloat16)
+    outs = {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("DIB200_DECODE_PIPE", mode)
+        outs[mode] = ops().paged_attention(q, case.cache, meta, d ** -0.5, window).clone()
+    assert ops()._lib("attention_bf16").dib_attention_bf16_status() == 0
+    assert torch.equal(outs["0"], outs["1"])
+    for s in (0, 1, 2, 3, 5, n_seq - 1):
+        want = dense_reference(q[s:s + 1], case.k[s], case.v[s], d ** -0.5, [lens[s] - 1], window)
+        torch.testing.assert_close(outs["1"][s:s + 1].float(), want, **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 7, 16, 24, 33, 500])
 def test_paged_attention_window_edge(dtype, window):
