@@ -29,6 +29,22 @@
 
 #include "attention_bf16_kernels.cuh"
 
+// Phase clocks of the two-tile kernel (a development build only, -DDIB_PREFILL_CLOCKS):
+// the longest CTA of kv head 0 records clock64 per key tile, for the MMA lane (slots
+// 0..5) and for the first softmax thread of tile A (slots 6..11).
+#ifdef DIB_PREFILL_CLOCKS
+__device__ long long dib_prefill_clocks[64 * 12];
+#define DIB_PCLOCK(it, slot)                                                              \
+  do {                                                                                    \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 64) dib_prefill_clocks[(it) * 12 + (slot)] = clock64(); \
+  } while (0)
+extern "C" int dib_prefill_clocks_read(long long* host) {
+  return cudaMemcpyFromSymbol(host, dib_prefill_clocks, sizeof(dib_prefill_clocks)) == cudaSuccess ? 0 : -1;
+}
+#else
+#define DIB_PCLOCK(it, slot) do {} while (0)
+#endif
+
 namespace {
 
 constexpr int TC_M = 128, TC_N = 128, TC_D = 128, TC_THREADS = 320;
@@ -423,6 +439,389 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
   }
 }
 
+// ------------------------------------------------------------------------------
+// Two query tiles per CTA.  The CTA owns two consecutive tiles A and B of 128 rows
+// (same sequence, same kv head), which share every key/value tile they both need.
+// Warps 0-3 are the softmax threads of A, warps 4-7 those of B: ONE thread per row,
+// the row's 128 scores in registers, so maximum, exponentials and sum need no
+// exchange.  The probabilities go back to tensor memory, packed as bfloat16 over the
+// scores they came from, and are the A operand of the second product straight from
+// there (no shared memory, no proxy fence).  The MMA warp staggers the two tiles:
+// after O_A += P_A V it issues S_A of the next key tile at once, then turns to B, so
+// each tile's softmax runs while the tensor core works for the other tile.
+// Tensor memory: S_A/P_A columns 0..127, S_B/P_B 128..255, O_A 256..383, O_B 384..511.
+__device__ __forceinline__ void tc_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long desc_b,
+                                          unsigned idesc, unsigned accum) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accum), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+
+// 2^x for x <= ~8 on the FMA and integer pipes (the special-function unit makes 16
+// exponentials per clock and SM, which would bound the softmax of a tile): x = n + f
+// with n the nearest integer, 2^f by a cubic (relative error 1e-4, below the bfloat16
+// step of the probabilities), 2^n by adding n to the exponent bits.
+__device__ __forceinline__ float exp2_fma(float x) {
+  x = fmaxf(x, -125.0f);
+  const float xf = x + 12582912.0f;          // 1.5 * 2^23: the sum's low mantissa bits hold n
+  const float f = x - (xf - 12582912.0f);    // in [-0.5, 0.5]
+  float p = fmaf(f, 0.05500893f, 0.24221095f);
+  p = fmaf(p, f, 0.6932829f);
+  p = fmaf(p, f, 1.0f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(xf) << 23));
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
+                                const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
+                                const int* __restrict__ block_table, int max_blocks,
+                                const int* __restrict__ cu_q_lens, const int* __restrict__ seq_lens,
+                                const int* __restrict__ tile_seq, const int* __restrict__ tile_start,
+                                int Hq, int Hkv, int page_size, float scale, int window) {
+  pdl_prologue();
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  unsigned char* sQ = smem;                       // [2] x 32 KB
+  unsigned char* sKV = smem + 2 * TILE_BYTES;     // 2 stages x (K 32 KB + V 32 KB)
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + 6 * TILE_BYTES);
+  unsigned long long* k_full = bars;              // [2] the keys of a key tile are in shared memory
+  unsigned long long* k_empty = bars + 2;         // [2] both score products have read them
+  unsigned long long* v_full = bars + 4;          // [2] the values of a key tile are in shared memory
+  unsigned long long* v_empty = bars + 6;         // [2] both output products have read them
+  unsigned long long* s_full = bars + 8;          // [2: A, B] the tile's scores are in tensor memory
+  unsigned long long* p_full = bars + 10;         // [2] its probabilities are, and O is rescaled (128)
+  unsigned long long* o_final = bars + 12;        // [2] its last product has completed
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 14);
+
+  const int tile = gridDim.y - 1 - blockIdx.y, kvh = blockIdx.x;
+  const int G = Hq / Hkv;
+  const int npt = TC_M / G;                       // tokens of one query tile
+  const int seq = tile_seq[tile];
+  const int tok0 = tile_start[tile];
+  const int q_begin = cu_q_lens[seq];
+  const int q_len = cu_q_lens[seq + 1] - q_begin;
+  const int kv_len = seq_lens[seq];
+  const int prefix = kv_len - q_len;
+  const int* bt = block_table + (size_t)seq * max_blocks;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // per query tile: its tokens and the key tiles it needs
+  int ntok[2], jf[2], jl[2];
+#pragma unroll
+  for (int x = 0; x < 2; ++x) {
+    const int t0 = tok0 + x * npt;
+    ntok[x] = max(0, min(npt, q_len - t0));
+    const int first_pos = prefix + t0, last_pos = prefix + t0 + ntok[x] - 1;
+    const int first_key = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+    jf[x] = first_key / TC_N;
+    jl[x] = ntok[x] > 0 ? last_pos / TC_N : -1;     // an empty tile is never active
+  }
+  const int j0 = jf[0];
+  const int ntiles = max(jl[0], jl[1]) - j0 + 1;
+  auto active = [&](int x, int i) { return j0 + i >= jf[x] && j0 + i <= jl[x]; };
+
+  if (warp == MMA_WARP && lane == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&o_final[i], 1);
+    }
+    mbar_fence_init();
+  }
+  if (warp == TMA_WARP) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(512u));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  // both Q tiles -> shared memory, swizzled; rows beyond a tile's tokens are zero
+  for (int c = threadIdx.x; c < 2 * TC_M * 16; c += TC_THREADS) {
+    const int x = c >> 11, r = (c >> 4) & 127, ch = c & 15;
+    const int tl = r / G, g = r % G;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tl < ntok[x]) {
+      const size_t t = (size_t)(q_begin + tok0 + x * npt + tl);
+      v = *reinterpret_cast<const uint4*>(q + (t * Hq + (size_t)kvh * G + g) * TC_D + ch * 8);
+    }
+    *reinterpret_cast<uint4*>(sQ + x * TILE_BYTES + sw_chunk_off(r, ch)) = v;
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // Q is read by the MMA unit
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem = *tmem_slot;
+  bool ok = true;
+
+  if (warp == TMA_WARP) {
+    // keys and values of a key tile are fetched, waited for and handed back apart: the
+    // keys are free again after the two score products, long before the values
+    const int pages = TC_N / page_size;
+    const int ops = pages * 2;
+    for (int i = 0; i < ntiles && ok; ++i) {
+      const int st = i & 1;
+      const int k0 = (j0 + i) * TC_N;
+#pragma unroll
+      for (int kv = 0; kv < 2; ++kv) {
+        unsigned long long* full = kv ? &v_full[st] : &k_full[st];
+        if (i >= 2) ok = mbar_wait(kv ? &v_empty[st] : &k_empty[st], ((i >> 1) - 1) & 1);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        if (lane == 0) mbar_expect_tx(full, TILE_BYTES);
+        __syncwarp();
+        for (int op = lane; op < ops; op += 32) {
+          const int pi = op >> 1, half = op & 1;
+          const int idx = k0 / page_size + pi;
+          const int page = idx < max_blocks ? bt[idx] : 0;
+          const int row0 = (((page * 2 + kv) * Hkv) + kvh) * page_size;
+          unsigned char* dst = sKV + st * 2 * TILE_BYTES + kv * TILE_BYTES + half * HALF_BYTES +
+                               pi * page_size * 128;
+          tma_load_2d(dst, &map, half * 64, row0, full);
+        }
+      }
+    }
+  } else if (warp == MMA_WARP) {
+    if (lane == 0) {
+      constexpr unsigned idesc_s = idesc_f16(TC_M, TC_N, 0);
+      constexpr unsigned idesc_o = idesc_f16(TC_M, TC_D, 1);
+      // Descriptors are made once: the issuing thread is alone, and what it computes
+      // between two products delays the next one.  A descriptor's low bits hold the
+      // address in 16-byte units, so a step inside a tile is an addition.
+      unsigned long long q_desc[2][TC_D / 16];
+#pragma unroll
+      for (int x = 0; x < 2; ++x)
+#pragma unroll
+        for (int ks = 0; ks < TC_D / 16; ++ks)
+          q_desc[x][ks] = desc_k_major(smem_u32(sQ + x * TILE_BYTES) + (ks >> 2) * HALF_BYTES + (ks & 3) * 32);
+      unsigned long long k_desc[2], v_desc[2];
+#pragma unroll
+      for (int st = 0; st < 2; ++st) {
+        k_desc[st] = desc_k_major(smem_u32(sKV + st * 2 * TILE_BYTES));
+        v_desc[st] = desc_mn_major(smem_u32(sKV + st * 2 * TILE_BYTES + TILE_BYTES), HALF_BYTES);
+      }
+      auto issue_s = [&](int x, int i) {
+        const unsigned long long kd = k_desc[i & 1];
+#pragma unroll
+        for (int ks = 0; ks < TC_D / 16; ++ks)
+          tc_mma(tmem + x * 128, q_desc[x][ks],
+                 kd + (unsigned long long)(((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4), idesc_s,
+                 ks > 0 ? 1u : 0u);
+        tc_commit(&s_full[x]);
+      };
+      int uses[2] = {0, 0};     // completed phases of p_full[x]
+      int have_k = 0;           // keys of key tiles 0..have_k have been waited for
+      int have_v = -1;          // values likewise
+      ok = mbar_wait(&k_full[0], 0);
+      if (ok) {
+        tc_fence_after();
+        if (active(0, 0)) issue_s(0, 0);
+        if (active(1, 0)) issue_s(1, 0);
+        tc_commit(&k_empty[0]);
+      }
+      for (int i = 0; i < ntiles && ok; ++i) {
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (active(x, i)) {
+            DIB_PCLOCK(i, x * 3);
+            ok = mbar_wait(&p_full[x], uses[x] & 1);
+            DIB_PCLOCK(i, x * 3 + 1);
+            if (!ok) break;
+            ++uses[x];
+            if (have_v < i) {
+              ok = mbar_wait(&v_full[i & 1], (i >> 1) & 1);
+              if (!ok) break;
+              have_v = i;
+            }
+            tc_fence_after();
+            const unsigned long long vd = v_desc[i & 1];
+            const bool first = j0 + i == jf[x];
+#pragma unroll
+            for (int ks = 0; ks < TC_N / 16; ++ks)
+              tc_mma_ts(tmem + 256 + x * 128, tmem + x * 128 + ks * 8,
+                        vd + (unsigned long long)((ks * 16 * 128) >> 4), idesc_o,
+                        (!first || ks > 0) ? 1u : 0u);
+            if (j0 + i == jl[x]) tc_commit(&o_final[x]);
+          }
+          if (x == 1) tc_commit(&v_empty[i & 1]);   // both output products of key tile i have been issued
+          if (i + 1 < ntiles && active(x, i + 1)) {
+            if (have_k < i + 1) {
+              ok = mbar_wait(&k_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
+              if (!ok) break;
+              have_k = i + 1;
+              tc_fence_after();
+            }
+            issue_s(x, i + 1);
+          }
+          if (x == 1 && i + 1 < ntiles) tc_commit(&k_empty[(i + 1) & 1]);   // both score products of key tile i+1
+          DIB_PCLOCK(i, x * 3 + 2);
+        }
+      }
+    }
+  } else {
+    // ---- softmax: thread r of group x owns row r of tile x
+    const int x = threadIdx.x >> 7, r = threadIdx.x & 127;
+    const int tl = r / G, g = r % G;
+    const bool valid = tl < ntok[x];
+    const int hi = valid ? prefix + tok0 + x * npt + tl : -1;
+    const int lo = (valid && window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
+    const float scale_log2 = scale * LOG2E;
+    const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;
+    const unsigned tmem_s = tmem + lane_base + x * 128;
+    const unsigned tmem_o = tmem + lane_base + 256 + x * 128;
+    float m_ref = NEG_BIG, l = 0.f;
+    int uses = 0;
+    for (int i = 0; i < ntiles && ok; ++i) {
+      if (!active(x, i)) continue;
+      if (threadIdx.x == 0) DIB_PCLOCK(i, 6);
+      ok = mbar_wait(&s_full[x], uses & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ++uses;
+      tc_fence_after();
+      if (threadIdx.x == 0) DIB_PCLOCK(i, 7);
+      const int kbase = (j0 + i) * TC_N;
+      const bool full = kbase >= lo && kbase + TC_N - 1 <= hi;   // no key of the tile is masked
+      unsigned v[4][32];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) tc_ld32(tmem_s + c * 32, v[c]);
+      tc_wait_ld();
+      if (threadIdx.x == 0) DIB_PCLOCK(i, 8);
+      // Four independent chains for the maximum and for the sum (a thread has few warps
+      // beside it to hide the latency of one long chain).  Tiles without a masked key,
+      // nearly all of them, take a path without the per-key tests.
+      float m4[4] = {NEG_BIG, NEG_BIG, NEG_BIG, NEG_BIG};
+      if (full) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int k = 0; k < 32; ++k) m4[k & 3] = fmaxf(m4[k & 3], __uint_as_float(v[c][k]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int k = 0; k < 32; ++k) {
+            const int key = kbase + c * 32 + k;
+            if (key >= lo && key <= hi) m4[k & 3] = fmaxf(m4[k & 3], __uint_as_float(v[c][k]));
+          }
+      }
+      float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      mx = mx <= -1e29f ? NEG_BIG : mx * scale_log2;   // scale is positive
+      // the reference maximum rises only when it must (or at the first visible key)
+      float factor = 1.0f;
+      bool rescale = false;
+      if (mx > m_ref + 8.0f) {
+        rescale = m_ref > -1e29f;
+        factor = rescale ? fast_exp2(m_ref - mx) : 0.f;
+        m_ref = mx;
+        l *= factor;
+      }
+      const float m_use = m_ref <= -1e29f ? 0.f : m_ref;
+      // One key in four (position % 4 == 3) takes its exponential on the FMA pipe, the
+      // others on the special-function unit: about what keeps both pipes equally busy.
+      float s4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (full) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int k = 0; k < 32; k += 4) {
+            const float p0 = fast_exp2(fmaf(__uint_as_float(v[c][k]), scale_log2, -m_use));
+            const float p1 = fast_exp2(fmaf(__uint_as_float(v[c][k + 1]), scale_log2, -m_use));
+            const float p2 = fast_exp2(fmaf(__uint_as_float(v[c][k + 2]), scale_log2, -m_use));
+            const float p3 = exp2_fma(fmaf(__uint_as_float(v[c][k + 3]), scale_log2, -m_use));
+            s4[0] += p0;
+            s4[1] += p1;
+            s4[2] += p2;
+            s4[3] += p3;
+            v[c >> 1][(c & 1) * 16 + (k >> 1)] = pack_bf16(p0, p1);   // 64 packed pairs in v[0], v[1]
+            v[c >> 1][(c & 1) * 16 + (k >> 1) + 1] = pack_bf16(p2, p3);
+          }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int k = 0; k < 32; k += 4) {
+            const int key = kbase + c * 32 + k;
+            float pj[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float xj = fmaf(__uint_as_float(v[c][k + j]), scale_log2, -m_use);
+              const float e = j == 3 ? exp2_fma(xj) : fast_exp2(xj);
+              pj[j] = (key + j >= lo && key + j <= hi) ? e : 0.f;
+              s4[j] += pj[j];
+            }
+            v[c >> 1][(c & 1) * 16 + (k >> 1)] = pack_bf16(pj[0], pj[1]);
+            v[c >> 1][(c & 1) * 16 + (k >> 1) + 1] = pack_bf16(pj[2], pj[3]);
+          }
+      }
+      const float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
+      l += sum;
+      if (threadIdx.x == 0) DIB_PCLOCK(i, 9);
+      // O of this tile (its last product completed before these scores did) is rescaled
+      // when a row of the warp raised its reference
+      if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          tc_ld32(tmem_o + c * 32, v[2]);
+          tc_wait_ld();
+#pragma unroll
+          for (int k = 0; k < 32; ++k)
+            v[2][k] = __float_as_uint(__uint_as_float(v[2][k]) * (rescale ? factor : 1.0f));
+          tc_st32(tmem_o + c * 32, v[2]);
+        }
+      }
+      tc_st32(tmem_s, v[0]);          // probabilities over the scores they came from
+      tc_st32(tmem_s + 32, v[1]);
+      if (threadIdx.x == 0) DIB_PCLOCK(i, 10);
+      tc_wait_st();
+      tc_fence_before();
+      mbar_arrive(&p_full[x]);
+      if (threadIdx.x == 0) DIB_PCLOCK(i, 11);
+    }
+    if (ok && jl[x] >= jf[x]) {
+      ok = mbar_wait(&o_final[x], 0);
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after();
+      if (ok) {
+        const float inv = 1.0f / l;
+        const size_t t = (size_t)(q_begin + tok0 + x * npt + tl);
+        __nv_bfloat16* dst = out + (t * Hq + (size_t)kvh * G + g) * TC_D;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          unsigned o[32];
+          tc_ld32(tmem_o + c * 32, o);
+          tc_wait_ld();
+          if (valid) {
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+              uint4 o4;
+              o4.x = pack_bf16(__uint_as_float(o[ch * 8 + 0]) * inv, __uint_as_float(o[ch * 8 + 1]) * inv);
+              o4.y = pack_bf16(__uint_as_float(o[ch * 8 + 2]) * inv, __uint_as_float(o[ch * 8 + 3]) * inv);
+              o4.z = pack_bf16(__uint_as_float(o[ch * 8 + 4]) * inv, __uint_as_float(o[ch * 8 + 5]) * inv);
+              o4.w = pack_bf16(__uint_as_float(o[ch * 8 + 6]) * inv, __uint_as_float(o[ch * 8 + 7]) * inv);
+              *reinterpret_cast<uint4*>(dst + c * 32 + ch * 8) = o4;
+            }
+          }
+        }
+      }
+    }
+  }
+  if (!ok) atomicExch(&dib_attention_error_word, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == TMA_WARP) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -491,6 +890,36 @@ int dib_extend_attention_tc(const void* q, void* out, const void* cache, long lo
     attr_set = true;
   }
   dib_launch(extend_attention_tc_kernel, dim3(Hkv, num_tiles), dim3(TC_THREADS), smem, st, *map,
+             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, max_blocks, cu_q_lens,
+             seq_lens, tile_seq, tile_start, Hq, Hkv, page_size, scale, window);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+// The same with two consecutive query tiles per CTA: tiles name (sequence, first token)
+// with 2 * 128 / (Hq/Hkv) tokens each.
+int dib_extend_attention_tc_pair(const void* q, void* out, const void* cache, long long num_pages,
+                                 const int* block_table, int max_blocks, const int* cu_q_lens,
+                                 const int* seq_lens, const int* tile_seq, const int* tile_start,
+                                 int num_tiles, int Hq, int Hkv, int D, int page_size, float scale,
+                                 int window, cudaStream_t st) {
+  if (num_tiles == 0) return DIB_OK;
+  if (D != TC_D || Hkv < 1 || Hq % Hkv != 0 || TC_M % (Hq / Hkv) != 0 || page_size < 8 ||
+      page_size > TC_N || TC_N % page_size != 0 || num_tiles > 65535 ||
+      (long long)num_pages * 2 * Hkv * page_size >= (1ll << 31) ||
+      reinterpret_cast<uintptr_t>(cache) % 16 != 0 || reinterpret_cast<uintptr_t>(q) % 16 != 0)
+    return DIB_BAD_SIZE;
+  const CUtensorMap* map = cache_map(cache, num_pages, Hkv, page_size, D);
+  if (map == nullptr) return DIB_LAUNCH_FAILED;
+  const size_t smem = 6 * TILE_BYTES + 14 * 8 + 16 + 1024;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(extend_attention_tc_pair_kernel,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+      return DIB_LAUNCH_FAILED;
+    attr_set = true;
+  }
+  dib_launch(extend_attention_tc_pair_kernel, dim3(Hkv, num_tiles), dim3(TC_THREADS), smem, st, *map,
              (const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, max_blocks, cu_q_lens,
              seq_lens, tile_seq, tile_start, Hq, Hkv, page_size, scale, window);
   DIB_CHECK_LAUNCH();

@@ -61,17 +61,20 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
             c_int(page_size), c_float(scale), c_int(window), c_int(pipelined), _stream())
         _check(st, "decode_attention_bf16", f"heads {hq}/{hkv}, head_dim {d}", kernels=2)
     group = hq // hkv
+    tc_mode = os.environ.get("DIB200_PREFILL_TC", "2")   # 0: mma.sync kernel; 1: one query tile per CTA; 2: two
     if b > nd and d == 128 and TC_TILE_ROWS % group == 0 and page_size in (8, 16, 32, 64, 128) \
-            and os.environ.get("DIB200_PREFILL_TC", "1") != "0":
-        # tcgen05 kernel: 128 rows per tile
-        tpt = TC_TILE_ROWS // group
+            and tc_mode != "0":
+        # tcgen05 kernels: 128 rows per query tile, one or two tiles per CTA
+        pair = tc_mode != "1"
+        tpt = TC_TILE_ROWS // group * (2 if pair else 1)
         tiles = meta.scratch.get(("extend_tiles", tpt))
         if tiles is None:
             seqs, starts = extend_tiles(meta.q_lens, nd, tpt)
             both = torch.tensor([seqs, starts], dtype=torch.int32).to(q.device, non_blocking=True)
             tiles = (both[0], both[1], len(seqs))
             meta.scratch[("extend_tiles", tpt)] = tiles
-        st = _lib("attention_prefill_tc").dib_extend_attention_tc(
+        tc_lib = _lib("attention_prefill_tc")
+        st = (tc_lib.dib_extend_attention_tc_pair if pair else tc_lib.dib_extend_attention_tc)(
             _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0]), _ptr(bt),
             c_int(bt.shape[1]), _ptr(meta.cu_q_lens), _ptr(meta.seq_lens), _ptr(tiles[0]),
             _ptr(tiles[1]), c_int(tiles[2]), c_int(hq), c_int(hkv), c_int(d), c_int(page_size),

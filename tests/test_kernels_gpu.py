@@ -357,6 +357,55 @@ def test_paged_attention_far_key_stands_out(dtype):
                                        atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("mode", ["0", "1", "2"])
+@pytest.mark.parametrize("hq,hkv,page,window", [(16, 8, 16, None), (32, 8, 16, 300), (8, 8, 32, None),
+                                                (16, 1, 128, 200), (64, 8, 8, None)])
+def test_prefill_attention_head_size_128_kernels(monkeypatch, mode, hq, hkv, page, window):
+    """The three bfloat16 prompt kernels for heads of 128 (mma.sync; tcgen05 with one
+    query tile per CTA; tcgen05 with two) on prompts that span many key tiles: whole,
+    behind a cached prefix, ending one token after a tile edge; group sizes 1 to 16."""
+    monkeypatch.setenv("DIB200_PREFILL_TC", mode)
+    d = 128
+    lens = [700, 300, 129, 257]
+    cuts = [(0, 700), (100, 200), (1, 128), (0, 257)]
+    case = PagedCase(lens, hkv, d, page, torch.bfloat16, seed=41)
+    g = torch.Generator().manual_seed(42)
+    q = torch.randn(sum(n for _, n in cuts), hq, d, generator=g).to(device="cuda", dtype=torch.bfloat16)
+    got = ops().paged_attention(q, case.cache, case.meta([0, 1, 2, 3], cuts), d ** -0.5, window)
+    assert ops()._lib("attention_prefill_tc").dib_attention_prefill_tc_status() == 0
+    off = 0
+    for s_, (start, n) in enumerate(cuts):
+        want = dense_reference(q[off:off + n], case.k[s_], case.v[s_], d ** -0.5,
+                               list(range(start, start + n)), window)
+        torch.testing.assert_close(got[off:off + n].float(), want, **tol(torch.bfloat16))
+        off += n
+
+
+@pytest.mark.parametrize("mode", ["1", "2"])
+def test_prefill_attention_far_key_stands_out(monkeypatch, mode):
+    """In a 700-token prompt one key matches every query strongly: each position at or
+    after it must return that key's value, whichever key tile and query tile it is in."""
+    monkeypatch.setenv("DIB200_PREFILL_TC", mode)
+    hq, hkv, d, page, n = 4, 2, 128, 16, 700
+    g = torch.Generator().manual_seed(43)
+    for far in (0, 127, 128, 383, 500):
+        k = 0.1 * torch.randn(n, hkv, d, generator=g)
+        v = torch.randn(n, hkv, d, generator=g)
+        q = 0.1 * torch.randn(n, hq, d, generator=g)
+        direction = torch.randn(d, generator=g)
+        direction /= direction.norm()
+        k[far] += 30 * direction
+        q += 30 * direction
+        case = PagedCase([n], hkv, d, page, torch.bfloat16, seed=44,
+                         k=[k.to(device="cuda", dtype=torch.bfloat16)],
+                         v=[v.to(device="cuda", dtype=torch.bfloat16)])
+        got = ops().paged_attention(q.to(device="cuda", dtype=torch.bfloat16), case.cache,
+                                    case.meta([0], [(0, n)]), 1.0)
+        for h in range(hq):
+            want = case.v[0][far, h // 2].float().expand(n - far, d)
+            torch.testing.assert_close(got[far:, h].float(), want, atol=2e-2, rtol=2e-2)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_paged_attention_cut_and_batch_invariance(dtype):
     """The same query position gives close results (float32: the same bits)
