@@ -22,6 +22,8 @@
 // returns.
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -318,14 +320,61 @@ int launch_swap_stages(const CUtensorMap& mw, const CUtensorMap& mx, void* out, 
 
 template <int BN, typename OutT, bool GATED = false>
 int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, void* out, float* partial, int M,
-                int N, int num_kb, int kb_per_split, int splits, dim3 grid, cudaStream_t st) {
+                int N, int num_kb, int kb_per_split, int splits, dim3 grid, int sm_count,
+                cudaStream_t st) {
+  // a deep ring where a CTA has its SM to itself; else four stages, so that several
+  // CTAs share an SM and stream side by side
   const long long ctas = (long long)grid.x * grid.y * grid.z;
   constexpr int DEEP = BN <= 32 ? 8 : (BN <= 64 ? 6 : 5);
-  if (kb_per_split >= 6 && ctas <= 2 * 160)
+  if (kb_per_split >= 6 && ctas <= sm_count)
     return launch_swap_stages<BN, OutT, GATED, DEEP>(mw, mx, out, partial, M, N, num_kb,
                                                      kb_per_split, splits, grid, st);
   return launch_swap_stages<BN, OutT, GATED, 4>(mw, mx, out, partial, M, N, num_kb, kb_per_split,
                                                 splits, grid, st);
+}
+
+}  // namespace
+
+namespace {
+
+// The time of a product, in units of one SM streaming one k-block of a weight tile.
+// The CTAs spread over the SMs, up to RESIDENT of them on an SM at a time (four-stage
+// ring, small token tile); an SM's time is its k-blocks plus a start-up per round of
+// resident CTAs, which weighs more on a CTA that is alone on its SM (nothing else
+// streams while its first block is on the way).  Splitting k makes more, shorter CTAs:
+// the SMs get equal loads and the start-ups hide behind one another.  Measured on the
+// layer shapes of the 0.6B, 8B and 32B presets.  Depends on N, K and the number of SMs
+// only, never on the number of rows, so a row's order of summation does not depend on
+// the batch.
+constexpr int RESIDENT = 3;
+constexpr int START_ALONE_KB = 7, START_SHARED_KB = 3;
+constexpr int READER_KB = 8;     // the kernel that reads split gate_up partials and gates
+long long cost_of(long long ctas, int per, int sm_count) {
+  if (ctas <= sm_count) return per + START_ALONE_KB;
+  const long long on_sm = (ctas + sm_count - 1) / sm_count;
+  const long long rounds = (on_sm + RESIDENT - 1) / RESIDENT;
+  return on_sm * per + START_SHARED_KB * rounds;
+}
+long long plan_cost(int n_tiles, int num_kb, int sm_count, int* per_out) {
+  long long best = -1;
+  int best_per = num_kb;
+  if (sm_count < 1) sm_count = 1;
+  for (int s = 1; s <= 16 && s <= num_kb; ++s) {
+    const int per = (num_kb + s - 1) / s;
+    const int real = (num_kb + per - 1) / per;
+    if (real != s) continue;   // the same cut as a smaller s
+    // In twentieths of a unit.  A split also writes and reads its partial products:
+    // counted for 32 rows (the plan must not know the real number), 8 bytes per
+    // element and split against the 16 KB of a weight k-block, spread over the SMs.
+    long long cost = cost_of((long long)n_tiles * real, per, sm_count) * 20;
+    if (s > 1) cost += 20ll * s * 32 * n_tiles * BM * 8 / (BM * BK * 2) / sm_count;
+    if (best < 0 || cost < best) {
+      best = cost;
+      best_per = per;
+    }
+  }
+  *per_out = best_per;
+  return best;
 }
 
 }  // namespace
@@ -347,13 +396,29 @@ void dib_gemm_bf16_plan(int M, int N, int K, int sm_count, int* bn, int* kb_per_
   while (b < M && b < 128) b <<= 1;
   const int n_tiles = (N + BM - 1) / BM;
   const int num_kb = (K + BK - 1) / BK;
-  int want = sm_count / n_tiles;          // CTAs per weight tile that would fill the GPU
-  if (want < 1) want = 1;
-  int per = (num_kb + want - 1) / want;
-  if (per < 2) per = num_kb < 2 ? num_kb : 2;
+  int per = num_kb;
+  plan_cost(n_tiles, num_kb, sm_count, &per);
+  if (const char* forced = getenv("DIB200_GEMM_SPLITS")) {   // for measurements
+    const int want = atoi(forced);
+    if (want >= 1) per = (num_kb + want - 1) / want;
+    if (per < 1) per = 1;
+  }
   *bn = b;
   *kb_per_split = per;
   *splits = (num_kb + per - 1) / per;
+}
+
+// 1 if the gate_up product of intermediate size I is better run as one kernel with the
+// gate in its epilogue (one CTA per 64 features, k not split) than as the split product
+// followed by the kernel that adds the partials and applies the gate.
+int dib_gemm_bf16_gated_pays(int I, int K, int sm_count) {
+  if (sm_count < 1) return 0;
+  const int num_kb = (K + BK - 1) / BK;
+  const int ctas = I / 64;
+  const long long gated = cost_of(ctas, num_kb, sm_count) * 20;
+  int per;
+  const long long split = plan_cost((2 * I + BM - 1) / BM, num_kb, sm_count, &per) + READER_KB * 20;
+  return gated <= split ? 1 : 0;
 }
 
 // x[M, K] * w[N, K]^T, bf16 inputs, float32 accumulation.  With `splits` == 1 (as
@@ -380,9 +445,9 @@ int dib_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K, 
   if (!make_map(&mw, w, N, K, BM) || !make_map(&mx, x, M, K, bn)) return DIB_LAUNCH_FAILED;
   dim3 grid(n_tiles, m_tiles, splits);
 #define CALL(BNV)                                                                              \
-  (out_fp32 ? launch_swap<BNV, float>(mw, mx, out, partial, M, N, num_kb, per, splits, grid, st) \
+  (out_fp32 ? launch_swap<BNV, float>(mw, mx, out, partial, M, N, num_kb, per, splits, grid, sm_count, st) \
             : launch_swap<BNV, __nv_bfloat16>(mw, mx, out, partial, M, N, num_kb, per, splits,  \
-                                              grid, st))
+                                              grid, sm_count, st))
   switch (bn) {
     case 16: return CALL(16);
     case 32: return CALL(32);
@@ -396,7 +461,7 @@ int dib_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K, 
 // (bf16 in, bf16 out; the two products are rounded to bf16 before the gate, as stored
 // products would be).  I must be a multiple of 64, K of 8.
 int dib_gemm_bf16_gated(const void* x, const void* w, void* out, int M, int I, int K,
-                        cudaStream_t st) {
+                        int sm_count, cudaStream_t st) {
   if (M == 0 || I == 0) return DIB_OK;
   if (K < 8 || K % 8 != 0 || I % 64 != 0) return DIB_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w)) % 16 != 0) return DIB_BAD_ALIGN;
@@ -408,7 +473,7 @@ int dib_gemm_bf16_gated(const void* x, const void* w, void* out, int M, int I, i
   if (!make_map(&mw, w, 2ll * I, K, BM / 2) || !make_map(&mx, x, M, K, bn)) return DIB_LAUNCH_FAILED;
   dim3 grid(I / 64, m_tiles, 1);
 #define CALL(BNV) \
-  launch_swap<BNV, __nv_bfloat16, true>(mw, mx, out, nullptr, M, I, num_kb, num_kb, 1, grid, st)
+  launch_swap<BNV, __nv_bfloat16, true>(mw, mx, out, nullptr, M, I, num_kb, num_kb, 1, grid, sm_count, st)
   switch (bn) {
     case 16: return CALL(16);
     case 32: return CALL(32);

@@ -80,16 +80,19 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor):
     from . import ops
     m, k = x.shape
     i = w_gate_up.shape[0] // 2
-    # one CTA per 64 features and no split of k: worth it when that alone fills the GPU
-    # (measured on the 0.6B shape, 48 tiles: 1.458 ms per step against 1.435 ms with the
-    # split product and the separate gate)
-    if i // 64 < int(os.environ.get("DIB200_GATED_MIN_TILES", "96")):
+    # one CTA per 64 features and no split of k: worth it when those CTAs fill whole waves
+    # of the GPU about as well as the split product does (the kernel's own estimate; 0.6B
+    # shape, 48 tiles: 1.458 ms per step against 1.435 ms with the split product and the
+    # separate gate).  DIB200_GATED=0/1 forces the choice.
+    forced = os.environ.get("DIB200_GATED")
+    if forced == "0" or (forced != "1" and not ops._lib("gemm_bf16").dib_gemm_bf16_gated_pays(
+            c_int(i), c_int(k), c_int(_sms(x.device)))):
         return None
     if not (m <= MAX_ROWS and k % 8 == 0 and k >= 8 and i % 64 == 0 and w_gate_up.shape[0] == 2 * i
             and x.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0):
         return None
     out = torch.empty(m, i, dtype=torch.bfloat16, device=x.device)
     st = ops._lib("gemm_bf16").dib_gemm_bf16_gated(ops._ptr(x), ops._ptr(w_gate_up), ops._ptr(out),
-                                                   c_int(m), c_int(i), c_int(k), ops._stream())
+                                                   c_int(m), c_int(i), c_int(k), c_int(_sms(x.device)), ops._stream())
     ops._check(st, "gated_linear(bfloat16)", f"M={m} I={i} K={k}")
     return out

@@ -107,4 +107,5 @@ class DecoderModel:
         else:
             res_rows = ops.gather_rows(residual, step.logit_indices)
             rows, _ = self.final_norm.add_forward(rows, res_rows)
-        return ops.linear(rows, self.head, out_dtype=torch.float32)
+        # logits leave as a plain tensor (the product may come as split-k partials)
+        return ops.as_tensor(ops.linear(rows, self.head, out_dtype=torch.float32))

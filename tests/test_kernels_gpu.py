@@ -185,7 +185,7 @@ def test_gated_linear(m, i, k, monkeypatch):
     """silu(x Wg^T) * (x Wu^T) with the gate in the product's epilogue (few rows, I a
     multiple of 64) or as two kernels; both against the formula with the two products
     rounded to bfloat16 as stored."""
-    monkeypatch.setenv("DIB200_GATED_MIN_TILES", "1")      # also the small shapes take the epilogue
+    monkeypatch.setenv("DIB200_GATED", "1")      # also the small shapes take the epilogue
     torch.manual_seed(12)
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (0.08 * torch.randn(2 * i, k, device="cuda")).to(torch.bfloat16)
