@@ -8,6 +8,8 @@
 // Paged cache layout of one layer: [num_pages, 2 (key,value), num_kv_heads,
 // page_size, head_dim], so the keys (or values) of one head inside one page are
 // contiguous.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace {
@@ -328,6 +330,122 @@ __global__ void qk_norm_rope_cache_vec_kernel(
   }
 }
 
+// The same for many rows of bfloat16 heads of 128 with a full rotation (prompt
+// portions): eight lanes share a (token, head) row, each with the elements 8l..8l+7 and
+// 64+8l..64+8l+7, so a rotation pair lies in one lane (no exchange), every load and
+// store moves 16 bytes, and a warp has four rows in flight; each group of eight lanes
+// takes ROWS rows and issues all their loads first.
+template <int ROWS>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_cache_rows128_kernel(
+    const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out,
+    __nv_bfloat16* __restrict__ kv_cache, const float* __restrict__ q_norm_w,
+    const float* __restrict__ k_norm_w, float eps, const float* __restrict__ cos_sin, int max_pos,
+    const int* __restrict__ positions, const int* __restrict__ slot_mapping, int T_tokens, int Hq,
+    int Hkv, int page_size, long long num_pages) {
+  pdl_prologue();
+  constexpr int D = 128;
+  const int heads = Hq + 2 * Hkv;
+  const long long total = (long long)T_tokens * heads;
+  const int l = threadIdx.x & 7;
+  const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+  const long long row0 = group * ROWS;
+  const unsigned mask = 0xffu << (threadIdx.x & 24);   // the eight lanes of this group
+
+  uint4 lo[ROWS], hi[ROWS];
+  int tok[ROWS], head[ROWS];
+  bool act[ROWS];
+#pragma unroll
+  for (int it = 0; it < ROWS; ++it) {
+    const long long row = row0 + it;
+    act[it] = row < total;
+    tok[it] = act[it] ? (int)(row / heads) : 0;
+    head[it] = act[it] ? (int)(row % heads) : 0;
+    if (act[it]) {
+      const __nv_bfloat16* src = qkv + ((size_t)tok[it] * heads + head[it]) * D + l * 8;
+      lo[it] = *reinterpret_cast<const uint4*>(src);
+      hi[it] = *reinterpret_cast<const uint4*>(src + 64);
+    }
+  }
+#pragma unroll
+  for (int it = 0; it < ROWS; ++it) {
+    if (!act[it]) continue;   // uniform over the group
+    const bool is_q = head[it] < Hq;
+    const bool is_k = !is_q && head[it] < Hq + Hkv;
+    __nv_bfloat16* dst;
+    if (is_q) {
+      dst = q_out + ((size_t)tok[it] * Hq + head[it]) * D;
+    } else {
+      const int slot = kv_cache != nullptr ? slot_mapping[tok[it]] : -1;
+      if (slot < 0) continue;
+      const long long page = slot / page_size;
+      if (page >= num_pages) continue;
+      const int h = is_k ? head[it] - Hq : head[it] - Hq - Hkv;
+      dst = kv_cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * Hkv + h) * page_size + slot % page_size) * D;
+    }
+    if (is_q || is_k) {
+      float a[8], b[8];   // elements 8l.. and 64+8l..
+      const __nv_bfloat162* pl = reinterpret_cast<const __nv_bfloat162*>(&lo[it]);
+      const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&hi[it]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float2 x = __bfloat1622float2(pl[k]), y = __bfloat1622float2(ph[k]);
+        a[2 * k] = x.x; a[2 * k + 1] = x.y;
+        b[2 * k] = y.x; b[2 * k + 1] = y.y;
+      }
+      const float* nw = is_q ? q_norm_w : k_norm_w;
+      if (nw != nullptr) {
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss = fmaf(a[k], a[k], ss);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ss = fmaf(b[k], b[k], ss);
+        ss += __shfl_xor_sync(mask, ss, 4);
+        ss += __shfl_xor_sync(mask, ss, 2);
+        ss += __shfl_xor_sync(mask, ss, 1);
+        const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+        const float4 w0 = *reinterpret_cast<const float4*>(nw + l * 8);
+        const float4 w1 = *reinterpret_cast<const float4*>(nw + l * 8 + 4);
+        const float4 w2 = *reinterpret_cast<const float4*>(nw + 64 + l * 8);
+        const float4 w3 = *reinterpret_cast<const float4*>(nw + 64 + l * 8 + 4);
+        const float wa[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+        const float wb[8] = {w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          a[k] = a[k] * rstd * wa[k];
+          b[k] = b[k] * rstd * wb[k];
+        }
+      }
+      if (cos_sin != nullptr) {
+        int p = positions[tok[it]];
+        p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
+        const float* tab = cos_sin + (size_t)p * D + l * 8;
+        const float4 c0 = *reinterpret_cast<const float4*>(tab);
+        const float4 c1 = *reinterpret_cast<const float4*>(tab + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(tab + 64);
+        const float4 s1 = *reinterpret_cast<const float4*>(tab + 68);
+        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const float x = a[k], y = b[k];
+          a[k] = x * c[k] - y * sn[k];
+          b[k] = y * c[k] + x * sn[k];
+        }
+      }
+      __nv_bfloat162* ql = reinterpret_cast<__nv_bfloat162*>(&lo[it]);
+      __nv_bfloat162* qh = reinterpret_cast<__nv_bfloat162*>(&hi[it]);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        ql[k] = __floats2bfloat162_rn(a[2 * k], a[2 * k + 1]);
+        qh[k] = __floats2bfloat162_rn(b[2 * k], b[2 * k + 1]);
+      }
+    }
+    *reinterpret_cast<uint4*>(dst + l * 8) = lo[it];
+    *reinterpret_cast<uint4*>(dst + 64 + l * 8) = hi[it];
+  }
+}
+
 // ------------------------------------------------ standalone cache write
 // k, v: [T, Hkv, D] -> the page slot of each token (slot < 0: skipped).
 template <typename T>
@@ -629,6 +747,19 @@ int dib_qk_norm_rope_cache_split(const void* qkv, const float* parts, int S, lon
                        reinterpret_cast<uintptr_t>(parts) % 16 == 0 &&
                        reinterpret_cast<uintptr_t>(q_out) % 16 == 0 &&
                        reinterpret_cast<uintptr_t>(kv_cache) % 16 == 0;
+  if (aligned && parts == nullptr && dtype == 1 && D == 128 && (cos_sin == nullptr || rotary_dim == D) &&
+      items >= 2048 && getenv("DIB200_QK_ROWS_OFF") == nullptr &&
+      reinterpret_cast<uintptr_t>(q_norm_w) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(k_norm_w) % 16 == 0 && reinterpret_cast<uintptr_t>(cos_sin) % 16 == 0) {
+    constexpr int ROWS = 2;
+    const long long groups = (items + ROWS - 1) / ROWS;
+    dib_launch(qk_norm_rope_cache_rows128_kernel<ROWS>, dim3(ceil_div_host(groups * 8, 256)), dim3(256),
+               0, st, (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_cache,
+               q_norm_w, k_norm_w, eps, cos_sin, max_pos, positions, slot_mapping, T, Hq, Hkv,
+               page_size, num_pages);
+    DIB_CHECK_LAUNCH();
+    return DIB_OK;
+  }
   if (aligned && (D == 64 || D == 128 || D == 256) && (cos_sin == nullptr || rotary_dim == D) &&
       (dtype == 0 || dtype == 1)) {
     // many items: 4 per warp (their loads overlap); few items: one per warp

@@ -126,9 +126,23 @@ def step_views(td: torch.Tensor, lay: PackedLayout, group_list: list, q_lens: li
         patch_dst=lay.seg(td, "patch_dst"), patch_src=lay.seg(td, "patch_src"))
 
 
-def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatch:
-    """Pack ``entries`` (``SequenceInput``; pages already allocated) into a
-    ``StepBatch`` on ``device``."""
+@dataclass
+class StepShape:
+    """What a step's entries come to, before anything is packed: the batch order (one-token
+    sequences first), lengths, where the wanted logits lie."""
+    order: list            # batch order -> index of the caller's entry
+    seqs: list             # the entries in batch order
+    q_lens: list
+    kv_lens: list
+    num_decode: int
+    t: int                 # tokens of the step
+    logit_rows: list       # per caller's entry: its rows of the logits
+    logit_index: list      # per logits row: its row of the token list
+    slots: list
+    width: int             # pages of the longest sequence
+
+
+def describe_step(entries: list, cache) -> StepShape:
     if not entries:
         raise ValueError("a step needs at least one sequence")
     for e in entries:
@@ -139,12 +153,8 @@ def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatc
                 raise ValueError(f"wanted place {w} is outside the {len(e.tokens)} tokens given")
     order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
     seqs = [entries[i] for i in order]
-    b = len(seqs)
     q_lens = [len(e.tokens) for e in seqs]
     kv_lens = [e.num_computed + len(e.tokens) for e in seqs]
-    num_decode = sum(1 for q in q_lens if q == 1)
-    t = sum(q_lens)
-
     logit_rows: list = [None] * len(entries)
     logit_index: list = []
     start = 0
@@ -155,13 +165,18 @@ def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatc
             logit_index.append(start + w)
         logit_rows[order[bi]] = rows
         start += q_lens[bi]
-    r = len(logit_index)
+    return StepShape(order=order, seqs=seqs, q_lens=q_lens, kv_lens=kv_lens,
+                     num_decode=sum(1 for q in q_lens if q == 1), t=sum(q_lens),
+                     logit_rows=logit_rows, logit_index=logit_index, slots=[e.slot for e in seqs],
+                     width=max(1, max(-(-kv // cache.page_size) for kv in kv_lens)))
 
-    group_list = list(cache.page_groups.values())
-    width = max(1, max(-(-kv // cache.page_size) for kv in kv_lens))
-    lay = PackedLayout(t, b, r, width, len(group_list))
-    host = np.zeros(lay.size, dtype=np.int32)
 
+def fill_packed(host: np.ndarray, lay: PackedLayout, shape: StepShape, cache, group_list: list) -> int:
+    """Write the step's integer metadata into the packed array ``host`` laid out by
+    ``lay`` (block tables ``lay.width`` >= ``shape.width`` pages wide).  Returns the number
+    of tokens that are to be patched in from the previous step's samples."""
+    host[:] = 0
+    seqs, q_lens = shape.seqs, shape.q_lens
     ids, pos, tseq = lay.seg(host, "input_ids"), lay.seg(host, "positions"), lay.seg(host, "token_seq")
     cu = lay.seg(host, "cu_q_lens")
     start = 0
@@ -172,10 +187,9 @@ def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatc
         tseq[start:start + q] = bi
         cu[bi + 1] = start + q
         start += q
-    lay.seg(host, "seq_lens")[:] = kv_lens
-    slots = [e.slot for e in seqs]
-    lay.seg(host, "state_slots")[:] = slots
-    lay.seg(host, "logit_indices")[:] = logit_index
+    lay.seg(host, "seq_lens")[:] = shape.kv_lens
+    lay.seg(host, "state_slots")[:] = shape.slots
+    lay.seg(host, "logit_indices")[:] = shape.logit_index
     pdst, psrc = lay.seg(host, "patch_dst"), lay.seg(host, "patch_src")
     pdst[:] = -1
     num_patches = 0
@@ -185,14 +199,24 @@ def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatc
             psrc[bi] = e.pending_row
             num_patches += 1
     for gi, g in enumerate(group_list):
-        lay.seg(host, ("bt", gi))[:] = cache.block_table(g, slots, width).reshape(-1)
+        lay.seg(host, ("bt", gi))[:] = cache.block_table(g, shape.slots, lay.width).reshape(-1)
         sm = lay.seg(host, ("sm", gi))
         start = 0
         for bi, e in enumerate(seqs):
             q = q_lens[bi]
             sm[start:start + q] = cache.slot_mapping(g, e.slot, e.num_computed, q)
             start += q
+    return num_patches
 
+
+def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatch:
+    """Pack ``entries`` (``SequenceInput``; pages already allocated) into a
+    ``StepBatch`` on ``device``."""
+    shape = describe_step(entries, cache)
+    group_list = list(cache.page_groups.values())
+    lay = PackedLayout(shape.t, len(shape.seqs), len(shape.logit_index), shape.width, len(group_list))
+    host = np.zeros(lay.size, dtype=np.int32)
+    num_patches = fill_packed(host, lay, shape, cache, group_list)
     dev = torch.device(device)
     th = torch.from_numpy(host)
     if dev.type == "cuda":
@@ -201,6 +225,7 @@ def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatc
         td = th.to(dev, non_blocking=True)
     else:
         td = th
-    batch = step_views(td, lay, group_list, q_lens, kv_lens, slots, num_decode, logit_rows, order)
+    batch = step_views(td, lay, group_list, shape.q_lens, shape.kv_lens, shape.slots, shape.num_decode,
+                       shape.logit_rows, shape.order)
     batch.num_patches = num_patches
     return batch

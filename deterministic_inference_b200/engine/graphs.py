@@ -17,7 +17,10 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from .batch import PackedLayout, step_views
+import dataclasses
+from collections import OrderedDict
+
+from .batch import PackedLayout, describe_step, fill_packed, step_views
 
 
 def _bucket(n: int, smallest: int = 1) -> int:
@@ -35,6 +38,17 @@ class _Captured:
     def __init__(self, graph, static_meta, host_meta, layout, logits, batch):
         self.graph, self.static_meta, self.host_meta = graph, static_meta, host_meta
         self.layout, self.logits, self.batch = layout, logits, batch
+        self.uploaded = torch.cuda.Event()
+
+    def upload(self, fill) -> object:
+        """Fill the pinned metadata (``fill(array)``) and copy it to the device.  The
+        pinned array is written again only after the copy before has run: a caller may
+        issue steps faster than the GPU takes them."""
+        self.uploaded.synchronize()
+        result = fill(self.host_meta.numpy())
+        self.static_meta.copy_(self.host_meta, non_blocking=True)
+        self.uploaded.record()
+        return result
 
 
 class DecodeGraphs:
@@ -134,8 +148,7 @@ class DecodeGraphs:
         cap = self.graphs.get(key)
         if cap is None:
             cap = self._capture(key, entries)
-        self._fill(cap.host_meta.numpy(), cap.layout, entries)
-        cap.static_meta.copy_(cap.host_meta, non_blocking=True)
+        cap.upload(lambda host: self._fill(host, cap.layout, entries))
         if any(e.pending_row >= 0 for e in entries):
             from ..kernels import ops
             ops.patch_token_ids(cap.batch.input_ids, cap.batch.patch_dst, cap.batch.patch_src,
@@ -148,3 +161,92 @@ class DecodeGraphs:
         self.runner.tokens_run += len(entries)
         n = len(entries)
         return cap.logits[:n], [[i] for i in range(n)]
+
+
+class StepGraphs:
+    """CUDA-graph replay of steps of any shape that come again: the same token counts
+    per sequence (in batch order), the same wanted places, block tables of the same
+    bucket of width.  Portions of long prompts cut under one token budget, and whole
+    prompts of one length, are such steps; a small model's step of 2,048 prompt tokens
+    is a few hundred launches that the host otherwise issues barely faster than the GPU
+    runs them.  A shape is captured when it shows up the third time; the least recently
+    used graph goes when there are more than ``max_graphs`` (each keeps its own
+    activations).  Not used while the cache holds per-request state of a part (a part
+    may read its slots on the host)."""
+
+    def __init__(self, runner, max_graphs: int = 8, min_repeats: int = 3, min_width: int = 8):
+        self.runner = runner
+        self.cache = runner.cache
+        self.max_graphs, self.min_repeats, self.min_width = max_graphs, min_repeats, min_width
+        self.graphs: "OrderedDict[tuple, _Captured]" = OrderedDict()
+        self.seen: dict = {}
+        self.group_list = list(self.cache.page_groups.values())
+        self.replays = 0
+        self.captures = 0
+
+    def _width_bucket(self, width: int) -> int:
+        wb = _bucket(width, self.min_width) if width <= 32 else -(-width // 32) * 32
+        return min(wb, self.cache.max_blocks)
+
+    def run(self, entries, prev_tokens=None):
+        """(logits, StepBatch) like ``ModelRunner.step``, or None if this step is to be
+        run launch by launch.  The pages of the entries are allocated already."""
+        if self.cache.state_groups:
+            return None
+        shape = describe_step(entries, self.cache)
+        wb = self._width_bucket(shape.width)
+        if wb < shape.width:
+            return None
+        key = (tuple(shape.q_lens), tuple(shape.logit_index), wb)
+        cap = self.graphs.get(key)
+        if cap is None:
+            n = self.seen.get(key, 0) + 1
+            if len(self.seen) > 4096:
+                self.seen.clear()
+            self.seen[key] = n
+            if n < self.min_repeats:
+                return None
+            cap = self._capture(key, shape, wb)
+        else:
+            self.graphs.move_to_end(key)
+        num_patches = cap.upload(
+            lambda host: fill_packed(host, cap.layout, shape, self.cache, self.group_list))
+        if num_patches:
+            from ..kernels import ops
+            ops.patch_token_ids(cap.batch.input_ids, cap.batch.patch_dst, cap.batch.patch_src,
+                                prev_tokens)
+        cap.graph.replay()
+        self.replays += 1
+        batch = dataclasses.replace(cap.batch, logit_rows=shape.logit_rows, order=shape.order,
+                                    slots=shape.slots)
+        batch.num_patches = num_patches
+        # the caller owns what it gets: the graph's own logits are overwritten by its next replay
+        return cap.logits.clone(), batch
+
+    def _capture(self, key: tuple, shape, wb: int) -> _Captured:
+        dev = self.runner.device
+        b = len(shape.seqs)
+        lay = PackedLayout(shape.t, b, len(shape.logit_index), wb, len(self.group_list))
+        host = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
+        static = torch.zeros(lay.size, dtype=torch.int32, device=dev)
+        upper = wb * self.cache.page_size      # what kernels size their grids for
+        batch = step_views(static, lay, self.group_list, list(shape.q_lens), [upper] * b,
+                           list(shape.slots), shape.num_decode, shape.logit_rows, shape.order)
+        fill_packed(host.numpy(), lay, shape, self.cache, self.group_list)
+        static.copy_(host, non_blocking=True)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                self.runner.model.forward(batch, self.cache)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            logits = self.runner.model.forward(batch, self.cache)
+        cap = _Captured(graph, static, host, lay, logits, batch)
+        while len(self.graphs) >= self.max_graphs:
+            self.graphs.popitem(last=False)
+        self.graphs[key] = cap
+        self.captures += 1
+        return cap

@@ -54,6 +54,11 @@ class ModelRunner:
                                   dtype=self.dtype, device=self.device)
         self.steps_run = 0
         self.tokens_run = 0
+        # steps whose shape comes again are replayed as CUDA graphs
+        self.step_graphs = None
+        if cfg.cuda_graphs and self.device.type == "cuda":
+            from .graphs import StepGraphs
+            self.step_graphs = StepGraphs(self)
 
     @torch.inference_mode()
     def step(self, entries: list[SequenceInput], prev_tokens=None):
@@ -65,11 +70,15 @@ class ModelRunner:
         for e in entries:
             self.cache.allocate(e.slot, e.num_computed + len(e.tokens))
         self.cache.reset_fresh_state()
-        batch = build_step_batch(entries, self.cache, self.device)
-        if batch.num_patches:
-            from ..kernels import ops
-            ops.patch_token_ids(batch.input_ids, batch.patch_dst, batch.patch_src, prev_tokens)
-        logits = self.model.forward(batch, self.cache)
+        replayed = self.step_graphs.run(entries, prev_tokens) if self.step_graphs is not None else None
+        if replayed is not None:
+            logits, batch = replayed
+        else:
+            batch = build_step_batch(entries, self.cache, self.device)
+            if batch.num_patches:
+                from ..kernels import ops
+                ops.patch_token_ids(batch.input_ids, batch.patch_dst, batch.patch_src, prev_tokens)
+            logits = self.model.forward(batch, self.cache)
         for e in entries:
             self.cache.release_passed(e.slot, e.num_computed + len(e.tokens))
         self.steps_run += 1

@@ -208,3 +208,39 @@ def test_published_shapes_logits_agree_across_dtypes(name, layers):
         torch.cuda.empty_cache()
     a, b = res["bfloat16"], res["float32"]
     assert (a - b).abs().max().item() <= 0.03 * b.abs().max().item()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_replayed_as_graphs_give_the_bits_of_launched_steps(dtype, tiny_model_dirs):
+    """Steps of a shape that comes again are captured and replayed as CUDA graphs (from
+    the third time on): prompts of one length one after the other, a two-sequence mixed
+    step repeated, decode steps.  Every step's logits equal, bit for bit, those of a
+    runner that launches every step kernel by kernel; and the graphs were in fact used."""
+    from deterministic_inference_b200 import EngineConfig
+    from deterministic_inference_b200.engine.batch import SequenceInput
+    from deterministic_inference_b200.engine.runner import ModelRunner
+    model_dir = tiny_model_dirs["b"]
+    vocab = plain_qwen3.read_model_dir(model_dir)[0]["vocab_size"]
+    runners = [ModelRunner(EngineConfig(model_path=str(model_dir), dtype=dtype, device="cuda:0",
+                                        kv_pool_tokens=4096, page_size=TINY["b"]["page_size"],
+                                        max_reqs=16, max_seq_len=512, cuda_graphs=g)) for g in (True, False)]
+    assert runners[0].step_graphs is not None and runners[1].step_graphs is None
+    prompts = _prompts(vocab, (40,) * 6 + (25,) * 5, 21)
+    outs = [[], []]
+    for k, r in enumerate(runners):
+        slots = [r.cache.allocate_slot() for _ in prompts]
+        for s, p in zip(slots[:6], prompts[:6]):                    # the shape (40,) six times
+            outs[k].append(r.step([SequenceInput(s, p, 0, [0, 39])])[0].clone())
+        done = [0] * 5
+        for rep in range(5):                                        # (1, 5) with a decode beside a portion
+            s_dec, s_pre = slots[0], slots[6 + rep]
+            outs[k].append(r.step([SequenceInput(s_pre, prompts[6 + rep][:5], 0, [4]),
+                                   SequenceInput(s_dec, [rep + 1], 40 + rep, [0])])[0].clone())
+        for step in range(6):                                       # pure decode of three requests
+            outs[k].append(r.step([SequenceInput(slots[i], [step + 7], 40 + step, [0])
+                                   for i in (1, 2, 3)])[0].clone())
+    assert len(outs[0]) == len(outs[1]) == 17
+    for a, b in zip(*outs):
+        assert torch.equal(a, b)
+    g = runners[0].step_graphs
+    assert g.captures >= 3 and g.replays >= 4 + 3 + 4

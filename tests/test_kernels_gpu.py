@@ -60,12 +60,16 @@ def test_add_rms_norm(dtype, rows, h):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("hq,hkv,d,rot,norm", [
-    (16, 8, 128, 128, True), (6, 2, 32, 32, True), (5, 5, 48, 48, True), (4, 1, 80, 32, False),
-    (8, 1, 16, 16, True), (3, 3, 64, 0, True), (7, 7, 256, 256, True)])
-def test_qk_norm_rope_cache(dtype, hq, hkv, d, rot, norm):
+@pytest.mark.parametrize("hq,hkv,d,rot,norm,t", [
+    (16, 8, 128, 128, True, 37), (6, 2, 32, 32, True, 37), (5, 5, 48, 48, True, 37), (4, 1, 80, 32, False, 37),
+    (8, 1, 16, 16, True, 37), (3, 3, 64, 0, True, 37), (7, 7, 256, 256, True, 37),
+    # many rows of 128: the kernel with eight lanes per row (odd head counts, rows that end a group)
+    (16, 8, 128, 128, True, 301), (5, 1, 128, 128, True, 333), (12, 4, 128, 128, False, 200),
+    (16, 8, 128, 0, True, 129)])
+def test_qk_norm_rope_cache(dtype, hq, hkv, d, rot, norm, t):
     torch.manual_seed(3)
-    t, page, pages, max_pos = 37, 16, 11, 300
+    page, max_pos = 16, 300
+    pages = -(-t // page) + 3
     qkv = torch.randn(t, (hq + 2 * hkv) * d, device="cuda").to(dtype)
     qw = torch.randn(d, device="cuda") if norm else None
     kw = torch.randn(d, device="cuda") if norm else None
