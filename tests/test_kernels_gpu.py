@@ -502,3 +502,37 @@ def test_no_cpu_path():
     from deterministic_inference_b200.kernels.ops import KernelError
     with pytest.raises(KernelError, match="CUDA"):
         ops().rms_norm(torch.randn(2, 8), torch.ones(8), 1e-6)
+
+
+def test_sizes_outside_a_kernels_range_are_refused_with_a_clear_error():
+    """What a kernel cannot take it refuses by name and size; it never runs on it."""
+    from deterministic_inference_b200.kernels.ops import KernelError
+    o = ops()
+    dev = "cuda"
+    # attention: heads of more than 256 elements
+    d = 272
+    q = torch.zeros(1, 2, d, device=dev)
+    cache = torch.zeros(3, 2, 2, 16, d, device=dev)
+    case_meta = PagedCase([4], 2, 16, 16, torch.float32, seed=1).meta([0], [(3, 1)])
+    with pytest.raises(KernelError, match="head_dim 272"):
+        o.paged_attention(q, cache, case_meta, 1.0)
+    # query heads that the kv heads do not divide
+    with pytest.raises(KernelError, match="q .* vs cache"):
+        o.paged_attention(torch.zeros(1, 3, 16, device=dev), torch.zeros(3, 2, 2, 16, 16, device=dev),
+                          case_meta, 1.0)
+    # norm: a row wider than the widest kernel's shared memory, and a weight of another width
+    with pytest.raises(KernelError, match="row width 70001"):
+        o.rms_norm(torch.zeros(2, 70001, device=dev), torch.ones(70001, device=dev), 1e-6)
+    with pytest.raises(KernelError, match="weight has 7 elements"):
+        o.rms_norm(torch.zeros(2, 8, device=dev), torch.ones(7, device=dev), 1e-6)
+    # rotation over an odd number of dimensions
+    with pytest.raises(KernelError):
+        o.qk_norm_rope_cache(torch.zeros(1, 4 * 16, device=dev), 2, 1, 16, None, None, 1e-6,
+                             torch.zeros(8, 7, device=dev), torch.zeros(1, dtype=torch.int32, device=dev),
+                             None, None, 16)
+    # dtypes the package does not compute in
+    with pytest.raises(KernelError, match="float32 or bfloat16|must be"):
+        o.rms_norm(torch.zeros(2, 8, device=dev, dtype=torch.float16), torch.ones(8, device=dev), 1e-6)
+    # a non-contiguous input is named, not silently copied
+    with pytest.raises(KernelError, match="contiguous"):
+        o.rms_norm(torch.zeros(8, 4, device=dev).t(), torch.ones(8, device=dev), 1e-6)
