@@ -41,8 +41,21 @@ __device__ long long dib_prefill_clocks[64 * 12];
 extern "C" int dib_prefill_clocks_read(long long* host) {
   return cudaMemcpyFromSymbol(host, dib_prefill_clocks, sizeof(dib_prefill_clocks)) == cudaSuccess ? 0 : -1;
 }
+__device__ unsigned long long dib_prefill_timeline[4096 * 3];
+#define DIB_PTIME(slot)                                                                   \
+  do {                                                                                    \
+    const unsigned bid = blockIdx.y * gridDim.x + blockIdx.x;                              \
+    if (threadIdx.x == 0 && bid < 4096) {                                                 \
+      if ((slot) == 2) { unsigned sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); dib_prefill_timeline[bid * 3 + 2] = sm; } \
+      else dib_prefill_timeline[bid * 3 + (slot)] = global_timer_ns();                    \
+    }                                                                                     \
+  } while (0)
+extern "C" int dib_prefill_timeline_read(unsigned long long* host) {
+  return cudaMemcpyFromSymbol(host, dib_prefill_timeline, sizeof(dib_prefill_timeline)) == cudaSuccess ? 0 : -1;
+}
 #else
 #define DIB_PCLOCK(it, slot) do {} while (0)
+#define DIB_PTIME(slot) do {} while (0)
 #endif
 
 namespace {
@@ -482,8 +495,14 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
                                 const int* __restrict__ block_table, int max_blocks,
                                 const int* __restrict__ cu_q_lens, const int* __restrict__ seq_lens,
                                 const int* __restrict__ tile_seq, const int* __restrict__ tile_start,
-                                int Hq, int Hkv, int page_size, float scale, int window) {
+                                int Hq, int Hkv, int page_size, float scale, int window,
+                                int chunk_tiles, const int* __restrict__ tile_chunk, int max_chunks,
+                                float* __restrict__ part_o, float* __restrict__ part_ml) {
+  if (threadIdx.x == 0) DIB_PCLOCK(63, 0);
+  DIB_PTIME(0);
+  DIB_PTIME(2);
   pdl_prologue();
+  if (threadIdx.x == 0) DIB_PCLOCK(63, 1);
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
@@ -511,19 +530,32 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   const int* bt = block_table + (size_t)seq * max_blocks;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // per query tile: its tokens and the key tiles it needs
+  // Per query tile: its tokens and the key tiles it needs.  With chunk_tiles > 0 the key
+  // range is cut into chunks of that many key tiles, anchored at key 0, and this CTA
+  // takes the chunk its list entry names: a tile whose range spans several chunks gets
+  // partial results (unnormalised O, reference maximum, sum) that a second kernel
+  // merges; a tile whose range lies in one chunk is finished here.
   int ntok[2], jf[2], jl[2];
+  bool whole[2];
+  const int chunk = chunk_tiles > 0 ? tile_chunk[tile] : 0;
+  const int c_lo = chunk * chunk_tiles;
+  const int c_hi = chunk_tiles > 0 ? c_lo + chunk_tiles - 1 : 0x7fffffff;
 #pragma unroll
   for (int x = 0; x < 2; ++x) {
     const int t0 = tok0 + x * npt;
     ntok[x] = max(0, min(npt, q_len - t0));
     const int first_pos = prefix + t0, last_pos = prefix + t0 + ntok[x] - 1;
     const int first_key = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
-    jf[x] = first_key / TC_N;
-    jl[x] = ntok[x] > 0 ? last_pos / TC_N : -1;     // an empty tile is never active
+    const int f = first_key / TC_N;
+    const int l = ntok[x] > 0 ? last_pos / TC_N : -1;     // an empty tile is never active
+    whole[x] = chunk_tiles <= 0 || f / chunk_tiles == l / chunk_tiles;
+    jf[x] = max(f, c_lo);
+    jl[x] = min(l, c_hi);
   }
-  const int j0 = jf[0];
-  const int ntiles = max(jl[0], jl[1]) - j0 + 1;
+  const bool any0 = jl[0] >= jf[0], any1 = jl[1] >= jf[1];
+  if (!any0 && !any1) return;     // nothing of this chunk concerns the pair
+  const int j0 = any0 && any1 ? min(jf[0], jf[1]) : (any0 ? jf[0] : jf[1]);
+  const int ntiles = max(any0 ? jl[0] : -1, any1 ? jl[1] : -1) - j0 + 1;
   auto active = [&](int x, int i) { return j0 + i >= jf[x] && j0 + i <= jl[x]; };
 
   if (warp == MMA_WARP && lane == 0) {
@@ -544,16 +576,28 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
                  "r"(512u));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
-  // both Q tiles -> shared memory, swizzled; rows beyond a tile's tokens are zero
-  for (int c = threadIdx.x; c < 2 * TC_M * 16; c += TC_THREADS) {
-    const int x = c >> 11, r = (c >> 4) & 127, ch = c & 15;
-    const int tl = r / G, g = r % G;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (tl < ntok[x]) {
-      const size_t t = (size_t)(q_begin + tok0 + x * npt + tl);
-      v = *reinterpret_cast<const uint4*>(q + (t * Hq + (size_t)kvh * G + g) * TC_D + ch * 8);
+  // both Q tiles -> shared memory, swizzled; rows beyond a tile's tokens are zero.  All of
+  // a thread's loads go out before its first store (one memory round-trip, not thirteen).
+  {
+    constexpr int PER_THREAD = (2 * TC_M * 16 + TC_THREADS - 1) / TC_THREADS;
+    uint4 v[PER_THREAD];
+#pragma unroll
+    for (int it = 0; it < PER_THREAD; ++it) {
+      const int c = threadIdx.x + it * TC_THREADS;
+      const int x = c >> 11, r = (c >> 4) & 127, ch = c & 15;
+      const int tl = r / G, g = r % G;
+      v[it] = make_uint4(0, 0, 0, 0);
+      if (c < 2 * TC_M * 16 && tl < ntok[x]) {
+        const size_t t = (size_t)(q_begin + tok0 + x * npt + tl);
+        v[it] = *reinterpret_cast<const uint4*>(q + (t * Hq + (size_t)kvh * G + g) * TC_D + ch * 8);
+      }
     }
-    *reinterpret_cast<uint4*>(sQ + x * TILE_BYTES + sw_chunk_off(r, ch)) = v;
+#pragma unroll
+    for (int it = 0; it < PER_THREAD; ++it) {
+      const int c = threadIdx.x + it * TC_THREADS;
+      const int x = c >> 11, r = (c >> 4) & 127, ch = c & 15;
+      if (c < 2 * TC_M * 16) *reinterpret_cast<uint4*>(sQ + x * TILE_BYTES + sw_chunk_off(r, ch)) = v[it];
+    }
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // Q is read by the MMA unit
   tc_fence_before();
@@ -561,6 +605,7 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   tc_fence_after();
   const unsigned tmem = *tmem_slot;
   bool ok = true;
+  if (threadIdx.x == 0) DIB_PCLOCK(63, 2);
 
   if (warp == TMA_WARP) {
     // keys and values of a key tile are fetched, waited for and handed back apart: the
@@ -786,11 +831,30 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
       mbar_arrive(&p_full[x]);
       if (threadIdx.x == 0) DIB_PCLOCK(i, 11);
     }
+    if (threadIdx.x == 0) DIB_PCLOCK(63, 3);
     if (ok && jl[x] >= jf[x]) {
       ok = mbar_wait(&o_final[x], 0);
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
-      if (ok) {
+      if (ok && !whole[x]) {
+        // a partial result of this chunk: O as accumulated (against m_ref), m_ref, l
+        const size_t t = (size_t)(q_begin + tok0 + x * npt + tl);
+        const size_t row = (t * Hq + (size_t)kvh * G + g) * max_chunks + chunk;
+        float* dst = part_o + row * TC_D;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          unsigned o[32];
+          tc_ld32(tmem_o + c * 32, o);
+          tc_wait_ld();
+          if (valid) {
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch)
+              *reinterpret_cast<uint4*>(dst + c * 32 + ch * 4) =
+                  make_uint4(o[ch * 4], o[ch * 4 + 1], o[ch * 4 + 2], o[ch * 4 + 3]);
+          }
+        }
+        if (valid) *reinterpret_cast<float2*>(part_ml + row * 2) = make_float2(m_ref, l);
+      } else if (ok) {
         const float inv = 1.0f / l;
         const size_t t = (size_t)(q_begin + tok0 + x * npt + tl);
         __nv_bfloat16* dst = out + (t * Hq + (size_t)kvh * G + g) * TC_D;
@@ -815,10 +879,102 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
     }
   }
   if (!ok) atomicExch(&dib_attention_error_word, 1);
+  if (threadIdx.x == 0) DIB_PCLOCK(63, 4);
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) DIB_PCLOCK(63, 5);
+  DIB_PTIME(1);
   if (warp == TMA_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
+  }
+}
+
+// Rows whose key range spans several chunks: out = sum_c O_c 2^(m_c - M) / sum_c l_c
+// 2^(m_c - M) over the chunks of the row's query tile, in chunk order.  A warp takes a
+// token (a lane four dimensions) and walks its query heads; tokens that the attention
+// kernel finished itself cost one look at their lengths.
+__global__ void __launch_bounds__(256)
+extend_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                              __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q_lens,
+                              const int* __restrict__ seq_lens, const int* __restrict__ token_seq,
+                              int t_first, int num_tokens, int Hq, int Hkv, int max_chunks,
+                              int chunk_tiles, int window) {
+  pdl_prologue();
+  const int lane = threadIdx.x & 31;
+  const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (idx >= num_tokens) return;
+  const int t = t_first + idx;
+  const int seq = token_seq[t];
+  const int q_begin = cu_q_lens[seq];
+  const int q_len = cu_q_lens[seq + 1] - q_begin;
+  const int prefix = seq_lens[seq] - q_len;
+  const int npt = TC_M / (Hq / Hkv);
+  const int tile_tok0 = (t - q_begin) / npt * npt;
+  const int first_pos = prefix + tile_tok0;
+  const int last_pos = first_pos + min(npt, q_len - tile_tok0) - 1;
+  const int first_key = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
+  const int c0 = first_key / TC_N / chunk_tiles, c1 = last_pos / TC_N / chunk_tiles;
+  if (c0 == c1) return;     // finished by the attention kernel itself
+  // Lane j first works out head j's (and j+32's, ...) weights of the chunks, all heads'
+  // loads in flight together; then the warp walks the heads, four at a time, with the
+  // weights handed round by shuffles.
+  for (int h0 = 0; h0 < Hq; h0 += 32) {
+    const int hl = h0 + lane;
+    float w[8], inv = 0.f;     // at most 8 chunks of a row are merged here (see the launcher)
+    {
+      float m[8], l[8], M = NEG_BIG, L = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        m[c] = NEG_BIG;
+        l[c] = 0.f;
+        if (hl < Hq && c0 + c <= c1) {
+          const float2 ml = *reinterpret_cast<const float2*>(
+              part_ml + (((size_t)t * Hq + hl) * max_chunks + c0 + c) * 2);
+          m[c] = ml.x;
+          l[c] = ml.y;
+        }
+        M = fmaxf(M, m[c]);
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        w[c] = m[c] <= -1e29f ? 0.f : fast_exp2(m[c] - M);
+        L += l[c] * w[c];
+      }
+      inv = 1.0f / L;
+    }
+    const int nh = min(32, Hq - h0);
+    for (int hb = 0; hb < nh; hb += 4) {
+      float4 acc[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        if (c0 + c > c1) break;     // uniform
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int src = min(hb + j, nh - 1);
+          const float f = __shfl_sync(0xffffffffu, w[c], src);
+          if (hb + j < nh) {
+            const float4 o = *reinterpret_cast<const float4*>(
+                part_o + (((size_t)t * Hq + h0 + hb + j) * max_chunks + c0 + c) * TC_D + lane * 4);
+            acc[j].x += o.x * f;
+            acc[j].y += o.y * f;
+            acc[j].z += o.z * f;
+            acc[j].w += o.w * f;
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float iv = __shfl_sync(0xffffffffu, inv, min(hb + j, nh - 1));
+        if (hb + j < nh) {
+          uint2 packed;
+          packed.x = pack_bf16(acc[j].x * iv, acc[j].y * iv);
+          packed.y = pack_bf16(acc[j].z * iv, acc[j].w * iv);
+          *reinterpret_cast<uint2*>(out + ((size_t)t * Hq + h0 + hb + j) * TC_D + lane * 4) = packed;
+        }
+      }
+    }
   }
 }
 
@@ -898,11 +1054,20 @@ int dib_extend_attention_tc(const void* q, void* out, const void* cache, long lo
 
 // The same with two consecutive query tiles per CTA: tiles name (sequence, first token)
 // with 2 * 128 / (Hq/Hkv) tokens each.
+// chunk_tiles > 0: the key range is cut into chunks of that many tiles of 128 keys and a
+// list entry names (sequence, first token, chunk tile_chunk[i] < max_chunks): several CTAs
+// share a pair of query tiles (the caller lists every chunk a pair may need, longest
+// first); part_o (float32 [T, Hq, max_chunks, 128])
+// and part_ml ([T, Hq, max_chunks, 2]) take the partial results, which a second kernel
+// merges for the tokens t_first .. t_first + num_tokens - 1 (the step's prompt tokens;
+// token_seq names their sequences).
 int dib_extend_attention_tc_pair(const void* q, void* out, const void* cache, long long num_pages,
                                  const int* block_table, int max_blocks, const int* cu_q_lens,
                                  const int* seq_lens, const int* tile_seq, const int* tile_start,
                                  int num_tiles, int Hq, int Hkv, int D, int page_size, float scale,
-                                 int window, cudaStream_t st) {
+                                 int window, int chunk_tiles, const int* tile_chunk, int max_chunks,
+                                 float* part_o, float* part_ml, const int* token_seq, int t_first,
+                                 int num_tokens, cudaStream_t st) {
   if (num_tiles == 0) return DIB_OK;
   if (D != TC_D || Hkv < 1 || Hq % Hkv != 0 || TC_M % (Hq / Hkv) != 0 || page_size < 8 ||
       page_size > TC_N || TC_N % page_size != 0 || num_tiles > 65535 ||
@@ -919,10 +1084,24 @@ int dib_extend_attention_tc_pair(const void* q, void* out, const void* cache, lo
       return DIB_LAUNCH_FAILED;
     attr_set = true;
   }
+  if (chunk_tiles <= 0) {
+    chunk_tiles = 0;
+    max_chunks = 1;
+  } else if (max_chunks < 1 || max_chunks > 8 || tile_chunk == nullptr || part_o == nullptr || part_ml == nullptr ||
+             token_seq == nullptr || num_tokens < 1) {
+    return DIB_BAD_SIZE;
+  }
   dib_launch(extend_attention_tc_pair_kernel, dim3(Hkv, num_tiles), dim3(TC_THREADS), smem, st, *map,
-             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, max_blocks, cu_q_lens,
-             seq_lens, tile_seq, tile_start, Hq, Hkv, page_size, scale, window);
+             (const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, max_blocks, cu_q_lens, seq_lens,
+             tile_seq, tile_start, Hq, Hkv, page_size, scale, window, chunk_tiles, tile_chunk,
+             max_chunks, part_o, part_ml);
   DIB_CHECK_LAUNCH();
+  if (chunk_tiles > 0 && max_chunks > 1) {
+    dib_launch(extend_attention_merge_kernel, dim3((num_tokens + 7) / 8), dim3(256), 0, st,
+               (const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, cu_q_lens, seq_lens,
+               token_seq, t_first, num_tokens, Hq, Hkv, max_chunks, chunk_tiles, window);
+    DIB_CHECK_LAUNCH();
+  }
   return DIB_OK;
 }
 

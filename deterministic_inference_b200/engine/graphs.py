@@ -17,10 +17,27 @@ from __future__ import annotations
 import numpy as np
 import torch
 
+import contextlib
 import dataclasses
+import gc
 from collections import OrderedDict
 
 from .batch import PackedLayout, describe_step, fill_packed, step_views
+
+
+@contextlib.contextmanager
+def _no_collection():
+    """No cyclic garbage collection while a graph is captured: a collected object that
+    owns device memory or another graph would call into CUDA in the middle of the
+    capture and invalidate it."""
+    was = gc.isenabled()
+    gc.collect()
+    gc.disable()
+    try:
+        yield
+    finally:
+        if was:
+            gc.enable()
 
 
 def _bucket(n: int, smallest: int = 1) -> int:
@@ -127,7 +144,7 @@ class DecodeGraphs:
         from ..kernels import ops
         n0 = ops.launch_count
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
+        with _no_collection(), torch.cuda.graph(graph):
             logits = self.runner.model.forward(batch, self.cache)
         self.kernels_per_graph[key] = ops.launch_count - n0
         cap = _Captured(graph, static, host, lay, logits, batch)
@@ -174,9 +191,12 @@ class StepGraphs:
     activations).  Not used while the cache holds per-request state of a part (a part
     may read its slots on the host)."""
 
-    def __init__(self, runner, max_graphs: int = 8, min_repeats: int = 3, min_width: int = 8):
-        self.runner = runner
-        self.cache = runner.cache
+    def __init__(self, model, cache, device, max_graphs: int = 8, min_repeats: int = 3,
+                 min_width: int = 8):
+        # the model, the cache and the device, not the runner that owns this object: a
+        # cycle would leave captured graphs to the garbage collector, which may then
+        # destroy one in the middle of another capture
+        self.model, self.cache, self.device = model, cache, device
         self.max_graphs, self.min_repeats, self.min_width = max_graphs, min_repeats, min_width
         self.graphs: "OrderedDict[tuple, _Captured]" = OrderedDict()
         self.seen: dict = {}
@@ -224,7 +244,7 @@ class StepGraphs:
         return cap.logits.clone(), batch
 
     def _capture(self, key: tuple, shape, wb: int) -> _Captured:
-        dev = self.runner.device
+        dev = self.device
         b = len(shape.seqs)
         lay = PackedLayout(shape.t, b, len(shape.logit_index), wb, len(self.group_list))
         host = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
@@ -238,15 +258,15 @@ class StepGraphs:
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
             for _ in range(2):
-                self.runner.model.forward(batch, self.cache)
+                self.model.forward(batch, self.cache)
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            logits = self.runner.model.forward(batch, self.cache)
-        cap = _Captured(graph, static, host, lay, logits, batch)
-        while len(self.graphs) >= self.max_graphs:
+        while len(self.graphs) >= self.max_graphs:      # before the capture, not inside it
             self.graphs.popitem(last=False)
+        graph = torch.cuda.CUDAGraph()
+        with _no_collection(), torch.cuda.graph(graph):
+            logits = self.model.forward(batch, self.cache)
+        cap = _Captured(graph, static, host, lay, logits, batch)
         self.graphs[key] = cap
         self.captures += 1
         return cap

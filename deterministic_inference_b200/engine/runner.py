@@ -58,7 +58,7 @@ class ModelRunner:
         self.step_graphs = None
         if cfg.cuda_graphs and self.device.type == "cuda":
             from .graphs import StepGraphs
-            self.step_graphs = StepGraphs(self)
+            self.step_graphs = StepGraphs(self.model, self.cache, self.device)
 
     @torch.inference_mode()
     def step(self, entries: list[SequenceInput], prev_tokens=None):

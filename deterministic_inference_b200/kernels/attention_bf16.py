@@ -26,6 +26,41 @@ def supports(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -
     return head_dim % 16 == 0 and 16 <= head_dim <= 128 and group <= 16 and num_kv_heads <= 65535
 
 
+CHUNK_TILES = 8     # fewest key tiles of 128 per chunk when a prompt's key range is shared by several CTAs
+
+_sms: dict = {}
+
+
+def _sm_count(device) -> int:
+    n = _sms.get(device)
+    if n is None:
+        n = torch.cuda.get_device_properties(device).multi_processor_count
+        _sms[device] = n
+    return n
+
+
+def extend_chunk_units(q_lens: list, kv_lens: list, first_seq: int, tokens_per_pair: int,
+                       chunk_tiles: int):
+    """(sequence, first token, chunk) for every chunk of ``chunk_tiles`` key tiles that a pair
+    of query tiles may need: chunks 0 .. the one of the pair's last position, with the
+    lengths the host knows (under a captured graph an upper bound: a chunk past the real
+    range costs a CTA that leaves at once).  Longest first, so that the CTAs the GPU takes
+    up last are the short ones."""
+    units = []
+    span = chunk_tiles * 128
+    for s in range(first_seq, len(q_lens)):
+        prefix = kv_lens[s] - q_lens[s]
+        for t0 in range(0, q_lens[s], tokens_per_pair):
+            last_pos = prefix + min(t0 + tokens_per_pair, q_lens[s]) - 1
+            for c in range(last_pos // span + 1):
+                keys = min(last_pos + 1, (c + 1) * span) - c * span
+                units.append((-keys, s, t0, c))
+    units.sort()
+    # the kernel takes its list from the end (the last entry first)
+    units.reverse()
+    return [u[1] for u in units], [u[2] for u in units], [u[3] for u in units]
+
+
 def extend_tiles(q_lens: list, first_seq: int, tokens_per_tile: int):
     seqs, starts = [], []
     for s in range(first_seq, len(q_lens)):
@@ -74,12 +109,47 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
             tiles = (both[0], both[1], len(seqs))
             meta.scratch[("extend_tiles", tpt)] = tiles
         tc_lib = _lib("attention_prefill_tc")
-        st = (tc_lib.dib_extend_attention_tc_pair if pair else tc_lib.dib_extend_attention_tc)(
+        if not pair:
+            st = tc_lib.dib_extend_attention_tc(
+                _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0]), _ptr(bt),
+                c_int(bt.shape[1]), _ptr(meta.cu_q_lens), _ptr(meta.seq_lens), _ptr(tiles[0]),
+                _ptr(tiles[1]), c_int(tiles[2]), c_int(hq), c_int(hkv), c_int(d), c_int(page_size),
+                c_float(scale), c_int(window), _stream())
+            _check(st, "extend_attention_tc", f"heads {hq}/{hkv}, head_dim {d}")
+            return
+        # Few pairs of query tiles for the GPU and long key ranges (a short prompt portion
+        # behind a long prefix): the key range is cut into at most 8 chunks of at least
+        # CHUNK_TILES tiles of 128 keys and several CTAs share a pair; a second kernel
+        # merges their partial results.  A CTA costs about 10 us beside its key tiles (2 us
+        # a pair), so this pays only when the CTAs there are leave most SMs idle: at 128
+        # CTAs of 1 to 16 tile pairs (2,048 tokens, 8 kv heads) it measured 45 + 5 us
+        # against 48 us unsplit.  DIB200_PREFILL_SPLIT=0/1 forces the choice.
+        max_chunks, ws, chunk_list, chunk_tiles = 1, (None, None), None, 0
+        split = os.environ.get("DIB200_PREFILL_SPLIT", "auto")
+        n_keys = max(meta.kv_lens[nd:])
+        want_split = split == "1" or (split != "0" and tiles[2] * hkv * 2 <= _sm_count(q.device)
+                                      and n_keys >= 4 * CHUNK_TILES * 128)
+        if want_split and n_keys > CHUNK_TILES * 128:
+            chunk_tiles = max(CHUNK_TILES, -(-(-(-n_keys // 128)) // 8))
+            max_chunks = -(-n_keys // (chunk_tiles * 128))
+            got = meta.scratch.get(("extend_chunks", tpt, chunk_tiles))
+            if got is None:
+                seqs, starts, chunks = extend_chunk_units(meta.q_lens, meta.kv_lens, nd, tpt, chunk_tiles)
+                both = torch.tensor([seqs, starts, chunks], dtype=torch.int32).to(q.device, non_blocking=True)
+                got = ((both[0], both[1], len(seqs)), both[2],
+                       (torch.empty(t, hq, max_chunks, d, dtype=torch.float32, device=q.device),
+                        torch.empty(t, hq, max_chunks, 2, dtype=torch.float32, device=q.device)))
+                meta.scratch[("extend_chunks", tpt, chunk_tiles)] = got
+            tiles, chunk_list, ws = got
+        st = tc_lib.dib_extend_attention_tc_pair(
             _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0]), _ptr(bt),
             c_int(bt.shape[1]), _ptr(meta.cu_q_lens), _ptr(meta.seq_lens), _ptr(tiles[0]),
             _ptr(tiles[1]), c_int(tiles[2]), c_int(hq), c_int(hkv), c_int(d), c_int(page_size),
-            c_float(scale), c_int(window), _stream())
-        _check(st, "extend_attention_tc", f"heads {hq}/{hkv}, head_dim {d}")
+            c_float(scale), c_int(window), c_int(chunk_tiles if max_chunks > 1 else 0),
+            _ptr(chunk_list), c_int(max_chunks), _ptr(ws[0]), _ptr(ws[1]), _ptr(meta.token_seq),
+            c_int(nd), c_int(t - nd), _stream())
+        _check(st, "extend_attention_tc_pair", f"heads {hq}/{hkv}, head_dim {d}",
+               kernels=2 if max_chunks > 1 else 1)
         return
     if b > nd:
         tpt = TILE_ROWS // (hq // hkv)

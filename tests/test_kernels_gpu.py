@@ -385,6 +385,33 @@ def test_prefill_attention_head_size_128_kernels(monkeypatch, mode, hq, hkv, pag
         off += n
 
 
+@pytest.mark.parametrize("hq,hkv,window", [(4, 2, None), (8, 2, 1100), (2, 2, None)])
+def test_prefill_attention_key_range_shared_by_several_ctas(monkeypatch, hq, hkv, window):
+    """Long key ranges cut into chunks of 1,024 keys that several CTAs take, with a merge
+    of their partial results: a whole prompt of three chunks, a portion behind a prefix
+    whose range starts inside a chunk, a short sequence that one chunk finishes, and a
+    decode token beside them; against the dense reference and against the unsplit run."""
+    d, page = 128, 16
+    lens = [5, 2500, 1500, 200]
+    cuts = [(4, 1), (0, 2500), (1100, 400), (0, 200)]
+    case = PagedCase(lens, hkv, d, page, torch.bfloat16, seed=51)
+    g = torch.Generator().manual_seed(52)
+    q = torch.randn(sum(n for _, n in cuts), hq, d, generator=g).to(device="cuda", dtype=torch.bfloat16)
+    outs = {}
+    for split in ("0", "1"):
+        monkeypatch.setenv("DIB200_PREFILL_SPLIT", split)
+        outs[split] = ops().paged_attention(q, case.cache, case.meta([0, 1, 2, 3], cuts), d ** -0.5, window)
+    assert ops()._lib("attention_prefill_tc").dib_attention_prefill_tc_status() == 0
+    torch.testing.assert_close(outs["1"].float(), outs["0"].float(), **tol(torch.bfloat16))
+    off = 0
+    for s_, (start, n) in enumerate(cuts):
+        rows = list(range(0, n, 7)) + [n - 1]          # every 7th position, and the last
+        want = dense_reference(q[off:off + n][rows], case.k[s_], case.v[s_], d ** -0.5,
+                               [start + r for r in rows], window)
+        torch.testing.assert_close(outs["1"][off:off + n][rows].float(), want, **tol(torch.bfloat16))
+        off += n
+
+
 @pytest.mark.parametrize("mode", ["1", "2"])
 def test_prefill_attention_far_key_stands_out(monkeypatch, mode):
     """In a 700-token prompt one key matches every query strongly: each position at or
