@@ -107,10 +107,28 @@ constexpr unsigned make_idesc(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
 }
 
+// ---- thread-block clusters: the CTAs that share one output tile (one per slice of k)
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::
+                   : "memory");
+}
+// a float at the same shared-memory offset in the cluster's CTA `rank`
+__device__ __forceinline__ float ld_peer_smem(const float* local, unsigned rank) {
+  unsigned remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
 // GATED: w is [gate rows ; up rows] of a gated feed-forward ([2N, K]); a tile holds 64
 // gate rows and the 64 up rows of the same features, and the epilogue writes
-// silu(gate) * up, [M, N], so the gate/up product never goes to memory.  k is not split.
-template <int BN, typename OutT, bool GATED, int STAGES>
+// silu(gate) * up, [M, N], so the gate/up product never goes to memory.
+// CLUSTER: the `splits` CTAs of a tile (grid z) form a thread-block cluster; each leaves
+// its partial tile in its shared memory, and each then adds up, over all of them in split
+// order, its share of the tile's rows through distributed shared memory and writes the
+// finished values: no partial products in global memory, and a gate can follow a split k.
+template <int BN, typename OutT, bool GATED, int STAGES, bool CLUSTER>
 __global__ void __launch_bounds__(THREADS)
 gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  OutT* __restrict__ out, float* __restrict__ partial, int M, int N, int num_kb,
@@ -207,7 +225,54 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   if (!acc_ok) atomicExch(&dib_gemm_error_word, 1);
   tc_fence_after();
   const int n = n0 + warp * 32 + lane;
-  if (GATED) {
+  if (CLUSTER) {
+    // the pipeline stages are free (every MMA has completed): this CTA's partial tile
+    // goes there as [128 rows][BN + 1] float
+    constexpr int LD = BN + 1;
+    float* stg = reinterpret_cast<float*>(smem);
+#pragma unroll 1
+    for (int c = 0; c < BN / 16; ++c) {
+      unsigned r[16];
+      if (acc_ok) {
+        tc_ld16(tmem + ((unsigned)(warp * 32) << 16) + c * 16, r);
+        tc_wait_ld();
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        stg[(warp * 32 + lane) * LD + c * 16 + j] = acc_ok ? __uint_as_float(r[j]) : 0.f;
+    }
+    cluster_sync_all();
+    const unsigned rank = blockIdx.z;
+    const int cols = min(BN, M - m0);
+    if (GATED) {
+      // feature pairs (gate row p, up row 64 + p): this CTA's share of the 64
+      const int per = (BM / 2 + splits - 1) / splits;
+      const int p0 = rank * per, np = max(0, min(BM / 2, p0 + per) - p0);
+      for (int e = threadIdx.x; e < np * cols; e += THREADS) {
+        const int p = p0 + e % np, col = e / np;
+        if (n0 + p >= N) continue;
+        float g = 0.f, u = 0.f;
+        for (int sp = 0; sp < splits; ++sp) {
+          g += ld_peer_smem(stg + p * LD + col, sp);
+          u += ld_peer_smem(stg + (BM / 2 + p) * LD + col, sp);
+        }
+        g = round_to<__nv_bfloat16>(g);
+        u = round_to<__nv_bfloat16>(u);
+        Elem<OutT>::store(out + (size_t)(m0 + col) * N + n0 + p, g / (1.0f + expf(-g)) * u);
+      }
+    } else {
+      const int per = (BM + splits - 1) / splits;
+      const int r0 = rank * per, nr = max(0, min(BM, r0 + per) - r0);
+      for (int e = threadIdx.x; e < nr * cols; e += THREADS) {
+        const int row = r0 + e % nr, col = e / nr;
+        if (n0 + row >= N) continue;
+        float acc = 0.f;
+        for (int sp = 0; sp < splits; ++sp) acc += ld_peer_smem(stg + row * LD + col, sp);
+        Elem<OutT>::store(out + (size_t)(m0 + col) * N + n0 + row, acc);
+      }
+    }
+    cluster_sync_all();   // nobody leaves while a peer may still read its tile
+  } else if (GATED) {
     // rows 0..63 of the tile are gate rows (warps 0, 1), rows 64..127 the up rows of
     // the same features (warps 2, 3): the up values go through shared memory (the
     // pipeline stages are free: every MMA has completed)
@@ -298,13 +363,14 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, in
 // STAGES: 4 keeps several CTAs on an SM (grids with many more CTAs than SMs overlap one
 // CTA's ramp-up with another's stream); 8 keeps more bytes in flight for a CTA that has
 // the SM to itself and a long range of k to walk.
-template <int BN, typename OutT, bool GATED, int STAGES>
+template <int BN, typename OutT, bool GATED, int STAGES, bool CLUSTER>
 int launch_swap_stages(const CUtensorMap& mw, const CUtensorMap& mx, void* out, float* partial,
                        int M, int N, int num_kb, int kb_per_split, int splits, dim3 grid,
                        cudaStream_t st) {
-  constexpr size_t smem =
-      (size_t)STAGES * (BM * BK * 2 + BN * BK * 2) + (2 * STAGES + 1) * 8 + 16 + 1024;
-  auto kern = gemm_swap_kernel<BN, OutT, GATED, STAGES>;
+  constexpr size_t ring = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2);
+  static_assert(!CLUSTER || ring >= (size_t)BM * (BN + 1) * 4, "the partial tile must fit in the ring");
+  constexpr size_t smem = ring + (2 * STAGES + 1) * 8 + 16 + 1024;
+  auto kern = gemm_swap_kernel<BN, OutT, GATED, STAGES, CLUSTER>;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
@@ -312,8 +378,26 @@ int launch_swap_stages(const CUtensorMap& mw, const CUtensorMap& mx, void* out, 
       return DIB_LAUNCH_FAILED;
     attr_set = true;
   }
-  dib_launch(kern, dim3(grid), dim3(THREADS), smem, st, mw, mx, (OutT*)out, partial, M, N, num_kb, kb_per_split,
-                                    splits);
+  if (CLUSTER) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)splits;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = dib_pdl_enabled() ? 2 : 1;
+    cudaLaunchKernelEx(&cfg, kern, mw, mx, (OutT*)out, partial, M, N, num_kb, kb_per_split, splits);
+  } else {
+    dib_launch(kern, dim3(grid), dim3(THREADS), smem, st, mw, mx, (OutT*)out, partial, M, N, num_kb,
+               kb_per_split, splits);
+  }
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -321,16 +405,23 @@ int launch_swap_stages(const CUtensorMap& mw, const CUtensorMap& mx, void* out, 
 template <int BN, typename OutT, bool GATED = false>
 int launch_swap(const CUtensorMap& mw, const CUtensorMap& mx, void* out, float* partial, int M,
                 int N, int num_kb, int kb_per_split, int splits, dim3 grid, int sm_count,
-                cudaStream_t st) {
+                bool cluster, cudaStream_t st) {
   // a deep ring where a CTA has its SM to itself; else four stages, so that several
   // CTAs share an SM and stream side by side
   const long long ctas = (long long)grid.x * grid.y * grid.z;
   constexpr int DEEP = BN <= 32 ? 8 : (BN <= 64 ? 6 : 5);
+  if (cluster) {
+    if (kb_per_split >= 6 && ctas <= sm_count)
+      return launch_swap_stages<BN, OutT, GATED, DEEP, true>(mw, mx, out, partial, M, N, num_kb,
+                                                             kb_per_split, splits, grid, st);
+    return launch_swap_stages<BN, OutT, GATED, 4, true>(mw, mx, out, partial, M, N, num_kb,
+                                                        kb_per_split, splits, grid, st);
+  }
   if (kb_per_split >= 6 && ctas <= sm_count)
-    return launch_swap_stages<BN, OutT, GATED, DEEP>(mw, mx, out, partial, M, N, num_kb,
-                                                     kb_per_split, splits, grid, st);
-  return launch_swap_stages<BN, OutT, GATED, 4>(mw, mx, out, partial, M, N, num_kb, kb_per_split,
-                                                splits, grid, st);
+    return launch_swap_stages<BN, OutT, GATED, DEEP, false>(mw, mx, out, partial, M, N, num_kb,
+                                                            kb_per_split, splits, grid, st);
+  return launch_swap_stages<BN, OutT, GATED, 4, false>(mw, mx, out, partial, M, N, num_kb,
+                                                       kb_per_split, splits, grid, st);
 }
 
 }  // namespace
@@ -355,11 +446,23 @@ long long cost_of(long long ctas, int per, int sm_count) {
   const long long rounds = (on_sm + RESIDENT - 1) / RESIDENT;
   return on_sm * per + START_SHARED_KB * rounds;
 }
+// The CTAs of a tile as a thread-block cluster (8 at most) that adds its partial tiles up
+// itself, instead of partial products in global memory that the next kernel adds.  Off
+// unless DIB200_GEMM_CLUSTER=1: it measured slower on B200 (N=4096, K=1024, 8 splits: 6.2
+// against 2.7 us with 8 rows, 18.7 against 4.7 us with 64 rows; the cluster launch and
+// its two barriers alone cost 2 us, the reads from the peers' shared memory the rest).
+bool cluster_enabled() {
+  const char* e = getenv("DIB200_GEMM_CLUSTER");
+  return e != nullptr && e[0] == '1';
+}
+constexpr int MAX_CLUSTER = 8;
+
 long long plan_cost(int n_tiles, int num_kb, int sm_count, int* per_out) {
   long long best = -1;
   int best_per = num_kb;
   if (sm_count < 1) sm_count = 1;
-  for (int s = 1; s <= 16 && s <= num_kb; ++s) {
+  const int max_splits = cluster_enabled() ? MAX_CLUSTER : 16;
+  for (int s = 1; s <= max_splits && s <= num_kb; ++s) {
     const int per = (num_kb + s - 1) / s;
     const int real = (num_kb + per - 1) / per;
     if (real != s) continue;   // the same cut as a smaller s
@@ -367,7 +470,7 @@ long long plan_cost(int n_tiles, int num_kb, int sm_count, int* per_out) {
     // counted for 32 rows (the plan must not know the real number), 8 bytes per
     // element and split against the 16 KB of a weight k-block, spread over the SMs.
     long long cost = cost_of((long long)n_tiles * real, per, sm_count) * 20;
-    if (s > 1) cost += 20ll * s * 32 * n_tiles * BM * 8 / (BM * BK * 2) / sm_count;
+    if (s > 1 && !cluster_enabled()) cost += 20ll * s * 32 * n_tiles * BM * 8 / (BM * BK * 2) / sm_count;
     if (best < 0 || cost < best) {
       best = cost;
       best_per = per;
@@ -375,6 +478,18 @@ long long plan_cost(int n_tiles, int num_kb, int sm_count, int* per_out) {
   }
   *per_out = best_per;
   return best;
+}
+
+// k-blocks per split: the model's choice, or DIB200_GEMM_SPLITS=n splits (measurements, tests)
+int planned_per(int n_tiles, int num_kb, int sm_count) {
+  int per = num_kb;
+  plan_cost(n_tiles, num_kb, sm_count, &per);
+  if (const char* forced = getenv("DIB200_GEMM_SPLITS")) {
+    const int want = atoi(forced);
+    if (want >= 1) per = (num_kb + want - 1) / want;
+    if (per < 1) per = 1;
+  }
+  return per;
 }
 
 }  // namespace
@@ -396,13 +511,7 @@ void dib_gemm_bf16_plan(int M, int N, int K, int sm_count, int* bn, int* kb_per_
   while (b < M && b < 128) b <<= 1;
   const int n_tiles = (N + BM - 1) / BM;
   const int num_kb = (K + BK - 1) / BK;
-  int per = num_kb;
-  plan_cost(n_tiles, num_kb, sm_count, &per);
-  if (const char* forced = getenv("DIB200_GEMM_SPLITS")) {   // for measurements
-    const int want = atoi(forced);
-    if (want >= 1) per = (num_kb + want - 1) / want;
-    if (per < 1) per = 1;
-  }
+  const int per = planned_per(n_tiles, num_kb, sm_count);
   *bn = b;
   *kb_per_split = per;
   *splits = (num_kb + per - 1) / per;
@@ -413,6 +522,7 @@ void dib_gemm_bf16_plan(int M, int N, int K, int sm_count, int* bn, int* kb_per_
 // followed by the kernel that adds the partials and applies the gate.
 int dib_gemm_bf16_gated_pays(int I, int K, int sm_count) {
   if (sm_count < 1) return 0;
+  if (cluster_enabled()) return 1;   // the gate follows the cluster's sum: no second kernel either way
   const int num_kb = (K + BK - 1) / BK;
   const int ctas = I / 64;
   const long long gated = cost_of(ctas, num_kb, sm_count) * 20;
@@ -427,6 +537,15 @@ int dib_gemm_bf16_gated_pays(int I, int K, int sm_count) {
 // partial [splits, M, N] float32 receives the partial products, to be added in split
 // order by the reader.  K must be a multiple of 8 (TMA wants 16-byte row strides); x
 // and w must be 16-byte aligned.
+// 1 if a product of these sizes has its split of k added up inside the kernel (by the
+// cluster of a tile's CTAs), so that it comes out finished although k is split.
+int dib_gemm_bf16_cluster_reduces(int N, int K, int sm_count) {
+  if (!cluster_enabled()) return 0;
+  int bn, per, splits;
+  dib_gemm_bf16_plan(1, N, K, sm_count, &bn, &per, &splits);
+  return splits >= 2 && splits <= MAX_CLUSTER ? 1 : 0;
+}
+
 int dib_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K, int out_fp32,
                   float* partial, int sm_count, cudaStream_t st) {
   if (M == 0 || N == 0) return DIB_OK;
@@ -436,7 +555,10 @@ int dib_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K, 
   dib_gemm_bf16_plan(M, N, K, sm_count, &bn, &per, &splits);
   const int n_tiles = (N + BM - 1) / BM, m_tiles = (M + bn - 1) / bn;
   const int num_kb = (K + BK - 1) / BK;
-  if (partial == nullptr) {   // the caller wants the finished product: one CTA walks all of k
+  // no buffer for partial products: the finished product is wanted, from the tile's
+  // cluster if the plan splits k and clusters are on, else from one CTA that walks all of k
+  const bool cluster = partial == nullptr && splits >= 2 && splits <= MAX_CLUSTER && cluster_enabled();
+  if (partial == nullptr && !cluster) {
     splits = 1;
     per = num_kb;
   }
@@ -445,9 +567,10 @@ int dib_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K, 
   if (!make_map(&mw, w, N, K, BM) || !make_map(&mx, x, M, K, bn)) return DIB_LAUNCH_FAILED;
   dim3 grid(n_tiles, m_tiles, splits);
 #define CALL(BNV)                                                                              \
-  (out_fp32 ? launch_swap<BNV, float>(mw, mx, out, partial, M, N, num_kb, per, splits, grid, sm_count, st) \
+  (out_fp32 ? launch_swap<BNV, float>(mw, mx, out, partial, M, N, num_kb, per, splits, grid, sm_count, \
+                                      cluster, st)                                                \
             : launch_swap<BNV, __nv_bfloat16>(mw, mx, out, partial, M, N, num_kb, per, splits,  \
-                                              grid, sm_count, st))
+                                              grid, sm_count, cluster, st))
   switch (bn) {
     case 16: return CALL(16);
     case 32: return CALL(32);
@@ -471,9 +594,17 @@ int dib_gemm_bf16_gated(const void* x, const void* w, void* out, int M, int I, i
   if (m_tiles > 65535) return DIB_BAD_SIZE;
   CUtensorMap mw, mx;
   if (!make_map(&mw, w, 2ll * I, K, BM / 2) || !make_map(&mx, x, M, K, bn)) return DIB_LAUNCH_FAILED;
-  dim3 grid(I / 64, m_tiles, 1);
+  // k is split over a cluster of CTAs per tile where that fills the GPU better
+  int per = num_kb, splits = 1;
+  if (cluster_enabled()) {
+    per = planned_per(I / 64, num_kb, sm_count);
+    splits = (num_kb + per - 1) / per;
+    if (splits > MAX_CLUSTER) { splits = 1; per = num_kb; }
+  }
+  const bool cluster = splits > 1;
+  dim3 grid(I / 64, m_tiles, splits);
 #define CALL(BNV) \
-  launch_swap<BNV, __nv_bfloat16, true>(mw, mx, out, nullptr, M, I, num_kb, num_kb, 1, grid, sm_count, st)
+  launch_swap<BNV, __nv_bfloat16, true>(mw, mx, out, nullptr, M, I, num_kb, per, splits, grid, sm_count, cluster, st)
   switch (bn) {
     case 16: return CALL(16);
     case 32: return CALL(32);

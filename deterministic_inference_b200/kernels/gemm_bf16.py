@@ -55,6 +55,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, allow_
         lib = ops._lib("gemm_bf16")
         splits = plan(m, n, k, x.device)[2] if allow_split else 1
         fp32 = c_int(1 if out_dtype == torch.float32 else 0)
+        # a split of k that the tile's cluster adds up itself comes out finished
+        if splits > 1 and lib.dib_gemm_bf16_cluster_reduces(c_int(n), c_int(k), c_int(_sms(x.device))):
+            splits = 1
         if splits > 1:
             parts = torch.empty(splits, m, n, dtype=torch.float32, device=x.device)
             st = lib.dib_gemm_bf16(ops._ptr(x), ops._ptr(weight), c_void_p(0), c_int(m), c_int(n),

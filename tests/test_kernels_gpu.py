@@ -153,16 +153,20 @@ def test_linear_fp32_row_does_not_depend_on_batch():
     (1, 4096, 1024), (8, 1024, 3072), (8, 1024, 2048), (8, 6144, 1024), (64, 200, 136),
     (17, 130, 72), (128, 256, 64), (33, 100, 8), (5, 151936, 1024), (100, 3000, 520),
     (129, 152, 96), (300, 152, 96), (2048, 512, 256)])
-def test_linear_bf16(m, n, k):
+@pytest.mark.parametrize("cluster", ["1", "0"])
+def test_linear_bf16(m, n, k, cluster, monkeypatch):
     """Rows up to 128 run the package's tcgen05 kernel (tails in N and K, split k,
-    one to four token tiles), more rows the library."""
+    one to four token tiles), more rows the library.  A split of k is added up by the
+    tile's cluster of CTAs (a finished tensor comes back) or left as partial products."""
     from deterministic_inference_b200.kernels import gemm_bf16
+    monkeypatch.setenv("DIB200_GEMM_CLUSTER", cluster)
     torch.manual_seed(8)
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (0.05 * torch.randn(n, k, device="cuda")).to(torch.bfloat16)
     want = x.float() @ w.float().T
     got = ops().linear(x, w)
-    assert isinstance(got, ops().SplitSum) == (m <= 128 and gemm_bf16.plan(m, n, k, x.device)[2] > 1)
+    assert isinstance(got, ops().SplitSum) == (cluster == "0" and m <= 128
+                                               and gemm_bf16.plan(m, n, k, x.device)[2] > 1)
     torch.testing.assert_close(ops().as_tensor(got).float(), want, atol=2e-2, rtol=2e-2)
     got32 = ops().as_tensor(ops().linear(x, w, out_dtype=torch.float32))
     assert got32.dtype == torch.float32
@@ -199,6 +203,33 @@ def test_gated_linear(m, i, k, monkeypatch):
     got = ops().gated_linear(x, w)
     assert got.shape == (m, i) and got.dtype == torch.bfloat16
     torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("m,n,k,splits", [(8, 1024, 2048, 8), (1, 4096, 1024, 4), (64, 1024, 3072, 6),
+                                          (128, 300, 520, 3), (17, 6144, 1024, 2), (33, 200, 1024, 7)])
+def test_cluster_sum_of_a_split_gives_the_bits_of_the_partials(m, n, k, splits, monkeypatch):
+    """The same split of k (forced), once added up by the tile's cluster through
+    distributed shared memory, once left as partial products that a reader adds in split
+    order: the same bits, in bfloat16 and float32 outputs; and the gate after a cluster's
+    sum gives what the gate kernel gives on the partials."""
+    monkeypatch.setenv("DIB200_GEMM_SPLITS", str(splits))
+    torch.manual_seed(14)
+    x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
+    w = (0.05 * torch.randn(n, k, device="cuda")).to(torch.bfloat16)
+    outs = {}
+    for cluster in ("1", "0"):
+        monkeypatch.setenv("DIB200_GEMM_CLUSTER", cluster)
+        y = ops().linear(x, w)
+        assert isinstance(y, ops().SplitSum) == (cluster == "0")
+        outs[cluster] = (ops().as_tensor(y), ops().as_tensor(ops().linear(x, w, out_dtype=torch.float32)))
+    assert torch.equal(outs["1"][0], outs["0"][0]) and torch.equal(outs["1"][1], outs["0"][1])
+    if n % 128 == 0:
+        gated = {}
+        for cluster in ("1", "0"):
+            monkeypatch.setenv("DIB200_GEMM_CLUSTER", cluster)
+            monkeypatch.setenv("DIB200_GATED", "1" if cluster == "1" else "0")
+            gated[cluster] = ops().gated_linear(x, w)
+        assert torch.equal(gated["1"], gated["0"])
 
 
 @pytest.mark.parametrize("m", [1, 8, 50])
