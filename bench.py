@@ -104,7 +104,7 @@ class ClockSampler:
 
 def reference_arm() -> int:
     # The reference is a source tree without packaging metadata: the offline
-    # install (pip --no-index --target baseline/_ref /root/reference) stops with
+    # install (pip --no-index --target baseline/_ref <the reference's tree>) stops with
     # "neither 'setup.py' nor 'pyproject.toml' found".  Run from its tree it needs
     # Triton kernels for every norm/rope/prefill, a downloaded Qwen3-0.6B checkpoint
     # and tokenizer (no network here), and its CUDA kernel is fixed to 16 query /
