@@ -147,6 +147,70 @@ __global__ void gumbel_sample_kernel(const float* __restrict__ logits,
   b = block_best(b, bscratch);
   if (threadIdx.x == 0) out[r] = b.i == INT_MAX_ ? 0 : b.i;
 }
+// Wide rows in chunks of ARGMAX_CHUNK ids, one block per (row, chunk), three kernels:
+// the chunk's maximum of logits / temperature and its sum of exponentials against that
+// maximum; then, with the row's maximum and sum put together from the chunks' in chunk
+// order (a row's normaliser never depends on the batch), the chunk's best score; then
+// the best chunk (argmax_final_kernel).
+__global__ void gumbel_stats_kernel(const float* __restrict__ logits,
+                                    const float* __restrict__ temperatures,
+                                    float* __restrict__ cmax, float* __restrict__ csum, int V,
+                                    int chunks) {
+  pdl_prologue();
+  __shared__ float fscratch[32];
+  const int r = blockIdx.y, c = blockIdx.x;
+  const float temp = temperatures[r];
+  if (temp <= 0.f) return;     // a greedy row needs no normaliser
+  const float* row = logits + (size_t)r * V;
+  const int lo = c * ARGMAX_CHUNK, hi = min(V, lo + ARGMAX_CHUNK);
+  float mx = -INFINITY;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) mx = fmaxf(mx, row[i] / temp);
+  mx = block_max(mx, fscratch);
+  float sum = 0.f;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) sum += expf(row[i] / temp - mx);
+  sum = block_sum(sum, fscratch);
+  if (threadIdx.x == 0) {
+    cmax[(size_t)r * chunks + c] = mx;
+    csum[(size_t)r * chunks + c] = sum;
+  }
+}
+
+__global__ void gumbel_pick_kernel(const float* __restrict__ logits,
+                                   const float* __restrict__ temperatures,
+                                   const long long* __restrict__ seeds,
+                                   const long long* __restrict__ sample_pos,
+                                   const unsigned char* __restrict__ keep,
+                                   const float* __restrict__ cmax, const float* __restrict__ csum,
+                                   float* __restrict__ pv, int* __restrict__ pi, int V, int chunks) {
+  pdl_prologue();
+  __shared__ Best bscratch[32];
+  const int r = blockIdx.y, c = blockIdx.x;
+  const float* row = logits + (size_t)r * V;
+  const int lo = c * ARGMAX_CHUNK, hi = min(V, lo + ARGMAX_CHUNK);
+  const float temp = temperatures[r];
+  Best b{-INFINITY, INT_MAX_};
+  if (temp <= 0.f) {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) b = better(b, Best{row[i], i});
+  } else {
+    float mx = -INFINITY;
+    for (int k = 0; k < chunks; ++k) mx = fmaxf(mx, cmax[(size_t)r * chunks + k]);
+    float sum = 0.f;
+    for (int k = 0; k < chunks; ++k)
+      sum += csum[(size_t)r * chunks + k] * expf(cmax[(size_t)r * chunks + k] - mx);
+    const long long seed = seeds[r], pos = sample_pos[r];
+    const unsigned char* krow = keep ? keep + (size_t)r * V : nullptr;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+      if (krow && !krow[i]) continue;
+      const float p = expf(row[i] / temp - mx) / sum;
+      b = better(b, Best{logf(p + 1e-10f) + seeded_gumbel(seed, pos, i), i});
+    }
+  }
+  b = block_best(b, bscratch);
+  if (threadIdx.x == 0) {
+    pv[(size_t)r * chunks + c] = b.v;
+    pi[(size_t)r * chunks + c] = b.i;
+  }
+}
 
 }  // namespace
 
@@ -181,6 +245,30 @@ int dib_gumbel_sample(const float* logits, const float* temperatures, const long
   if (R == 0) return DIB_OK;
   if (V < 1) return DIB_BAD_SIZE;
   dib_launch(gumbel_sample_kernel, dim3(R), dim3(1024), 0, st, logits, temperatures, seeds, sample_pos, keep, out, V);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+// The same in chunks (see gumbel_stats_kernel).  scratch_f: float [3, R, chunks];
+// scratch_i: int [R, chunks], chunks = dib_argmax_chunks(V).
+int dib_gumbel_sample_chunked(const float* logits, const float* temperatures, const long long* seeds,
+                              const long long* sample_pos, const unsigned char* keep,
+                              float* scratch_f, int* scratch_i, int* out, int R, int V,
+                              cudaStream_t st) {
+  if (R == 0) return DIB_OK;
+  if (V < 1 || R > 65535) return DIB_BAD_SIZE;
+  const int chunks = (V + ARGMAX_CHUNK - 1) / ARGMAX_CHUNK;
+  float* cmax = scratch_f;
+  float* csum = scratch_f + (size_t)R * chunks;
+  float* pv = scratch_f + 2 * (size_t)R * chunks;
+  dib_launch(gumbel_stats_kernel, dim3(chunks, R), dim3(256), 0, st, logits, temperatures, cmax, csum, V,
+             chunks);
+  DIB_CHECK_LAUNCH();
+  dib_launch(gumbel_pick_kernel, dim3(chunks, R), dim3(256), 0, st, logits, temperatures, seeds,
+             sample_pos, keep, (const float*)cmax, (const float*)csum, pv, scratch_i, V, chunks);
+  DIB_CHECK_LAUNCH();
+  dib_launch(argmax_final_kernel, dim3(R), dim3(64), 0, st, (const float*)pv, (const int*)scratch_i, out,
+             chunks);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }

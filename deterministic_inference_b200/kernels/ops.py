@@ -463,8 +463,18 @@ def gumbel_sample(logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch
         if tuple(keep.shape) != (r, v):
             raise KernelError(f"gumbel_sample: keep {tuple(keep.shape)} vs logits {(r, v)}")
     out = torch.empty(r, dtype=torch.int32, device=logits.device)
-    st = _lib("sampling").dib_gumbel_sample(_ptr(logits), _ptr(temperatures), _ptr(seeds),
-                                            _ptr(sample_positions), _ptr(keep), _ptr(out),
-                                            c_int(r), c_int(v), _stream())
+    lib = _lib("sampling")
+    if v > 8192 and r <= 65535:
+        # wide rows: a block per chunk of a row (normaliser, then scores), then the best chunk
+        chunks = -(-v // 4096)
+        sf = torch.empty(3, r, chunks, dtype=torch.float32, device=logits.device)
+        si = torch.empty(r, chunks, dtype=torch.int32, device=logits.device)
+        st = lib.dib_gumbel_sample_chunked(_ptr(logits), _ptr(temperatures), _ptr(seeds),
+                                           _ptr(sample_positions), _ptr(keep), _ptr(sf), _ptr(si),
+                                           _ptr(out), c_int(r), c_int(v), _stream())
+        _check(st, "gumbel_sample", kernels=3)
+        return out
+    st = lib.dib_gumbel_sample(_ptr(logits), _ptr(temperatures), _ptr(seeds), _ptr(sample_positions),
+                               _ptr(keep), _ptr(out), c_int(r), c_int(v), _stream())
     _check(st, "gumbel_sample")
     return out

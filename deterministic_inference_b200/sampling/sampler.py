@@ -49,12 +49,20 @@ def sample(logits: torch.Tensor, params: list, sample_positions: list) -> torch.
     if all(p.temperature <= 0 for p in params):
         return ops.argmax(logits)
     dev = logits.device
-    temps = torch.tensor([p.temperature for p in params], dtype=torch.float32, device=dev)
-    seeds = torch.tensor([p.seed for p in params], dtype=torch.int64, device=dev)
-    pos = torch.tensor(list(sample_positions), dtype=torch.int64, device=dev)
-    keep = None
-    if any(p.temperature > 0 and (p.top_k > 0 or p.top_p < 1.0) for p in params):
-        top_ks = torch.tensor([p.top_k if p.top_k > 0 else -1 for p in params], dtype=torch.int64, device=dev)
-        top_ps = torch.tensor([p.top_p for p in params], dtype=torch.float32, device=dev)
-        keep = keep_mask(logits, temps, top_ks, top_ps)
+    filtered = any(p.temperature > 0 and (p.top_k > 0 or p.top_p < 1.0) for p in params)
+    # the rows' parameters go to the device in ONE copy from pinned memory that does not
+    # make the host wait: int64 [seeds | positions | top_k], float32 [temperatures | top_p]
+    n64, n32 = (3 if filtered else 2) * r, (2 if filtered else 1) * r
+    host = torch.empty(n64 * 8 + n32 * 4, dtype=torch.uint8, pin_memory=dev.type == "cuda")
+    h64, h32 = host[:n64 * 8].view(torch.int64), host[n64 * 8:].view(torch.float32)
+    h64[:r] = torch.tensor([p.seed for p in params], dtype=torch.int64)
+    h64[r:2 * r] = torch.tensor(list(sample_positions), dtype=torch.int64)
+    h32[:r] = torch.tensor([p.temperature for p in params], dtype=torch.float32)
+    if filtered:
+        h64[2 * r:] = torch.tensor([p.top_k if p.top_k > 0 else -1 for p in params], dtype=torch.int64)
+        h32[r:] = torch.tensor([p.top_p for p in params], dtype=torch.float32)
+    device = host.to(dev, non_blocking=True)
+    d64, d32 = device[:n64 * 8].view(torch.int64), device[n64 * 8:].view(torch.float32)
+    seeds, pos, temps = d64[:r], d64[r:2 * r], d32[:r]
+    keep = keep_mask(logits, temps, d64[2 * r:], d32[r:]) if filtered else None
     return ops.gumbel_sample(logits, temps, seeds, pos, keep)

@@ -512,32 +512,39 @@ def test_argmax_lowest_index_on_ties():
     assert ops().argmax(x).tolist() == torch.argmax(x, -1).tolist()
 
 
-def test_gumbel_sample_matches_formula():
+@pytest.mark.parametrize("v,masked", [(5003, False), (151936, False), (20001, True), (8193, False)])
+def test_gumbel_sample_matches_formula(v, masked):
+    """Narrow rows take one block per row, wide rows a block per chunk of 4,096 ids
+    (normaliser put together from the chunks, then the scores)."""
     torch.manual_seed(20)
-    r, v = 16, 5003
+    r = 16
     logits = 3 * torch.randn(r, v, device="cuda")
     temps = torch.tensor([0.0, 0.8, 1.5, 0.3] * 4, device="cuda")
     seeds = torch.arange(r, device="cuda", dtype=torch.int64) * 977 - 5
     pos = torch.arange(100, 100 + r, device="cuda", dtype=torch.int64)
-    got = ops().gumbel_sample(logits, temps, seeds, pos)
-    scores = ref.gumbel_scores(logits, temps, seeds, pos)
-    want = ref.gumbel_sample(logits, temps, seeds, pos)
+    keep = (torch.rand(r, v, device="cuda") < 0.3).to(torch.uint8) if masked else None
+    got = ops().gumbel_sample(logits, temps, seeds, pos, keep)
+    scores = ref.gumbel_scores(logits, temps, seeds, pos, keep)
+    want = ref.gumbel_sample(logits, temps, seeds, pos, keep)
+    if masked:
+        assert all(keep[i, got[i]] == 1 for i in range(r) if temps[i] > 0)
     for i in range(r):
         if got[i] != want[i]:      # only a near tie of the two scores may differ
             assert abs(float(scores[i, got[i]] - scores[i, want[i]])) < 1e-4, (i, got[i], want[i])
     assert (got == want).float().mean() > 0.9
 
 
-def test_gumbel_draw_independent_of_batch_and_depends_on_position():
+@pytest.mark.parametrize("v", [5000, 151936])
+def test_gumbel_draw_independent_of_batch_and_depends_on_position(v):
     torch.manual_seed(21)
-    row = torch.randn(1, 5000, device="cuda")
+    row = torch.randn(1, v, device="cuda")
     one = lambda lg, seeds, pos: ops().gumbel_sample(
         lg, torch.full((lg.shape[0],), 0.8, device="cuda"),
         torch.tensor(seeds, dtype=torch.int64, device="cuda"),
         torch.tensor(pos, dtype=torch.int64, device="cuda"))
     alone = one(row, [1234], [17])
     for batch in (2, 7, 33):
-        lg = torch.cat([torch.randn(batch - 1, 5000, device="cuda"), row])
+        lg = torch.cat([torch.randn(batch - 1, v, device="cuda"), row])
         toks = one(lg, [1234] * batch, list(range(100, 100 + batch - 1)) + [17])
         assert toks[-1] == alone[0]
     same = torch.randn(1, 1000, device="cuda").repeat(64, 1)
