@@ -30,6 +30,21 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
   }
 }
 
+// Rows copied 16 bytes a thread: out row r = src row idx[r] (rows of row_bytes, a multiple
+// of 16; an index outside [0, rows_in) gives zeros if zero_bad, else is clamped).
+__global__ void copy_rows16_kernel(const uint4* __restrict__ src, const int* __restrict__ idx,
+                                   uint4* __restrict__ out, int vecs, int rows_in, int zero_bad) {
+  pdl_prologue();
+  const int r = blockIdx.x;
+  int id = idx[r];
+  const bool bad = id < 0 || id >= rows_in;
+  if (bad) id = id < 0 ? 0 : rows_in - 1;
+  const uint4* s = src + (size_t)id * vecs;
+  uint4* d = out + (size_t)r * vecs;
+  for (int i = threadIdx.x; i < vecs; i += blockDim.x)
+    d[i] = (bad && zero_bad) ? make_uint4(0, 0, 0, 0) : s[i];
+}
+
 // ---------------------------------------------------------------- RMSNorm
 // y = x * 1/sqrt(mean(x^2) + eps) * w; one block per row; the row is staged in
 // shared memory as float32.  With ADD: residual += x first (stored rounded to T),
@@ -685,6 +700,15 @@ int dib_embedding(const void* table, const int* ids, void* out, int T, int H, in
                   cudaStream_t st) {
   if (T == 0) return DIB_OK;
   const int th = pick_threads(H) > 256 ? 256 : pick_threads(H);
+  const size_t row_bytes = (size_t)H * (dtype == 0 ? 4 : 2);
+  if ((dtype == 0 || dtype == 1) && row_bytes % 16 == 0 && V > 0 &&
+      (reinterpret_cast<uintptr_t>(table) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
+    const int vecs = (int)(row_bytes / 16);
+    dib_launch(copy_rows16_kernel, dim3(T), dim3(vecs < 256 ? pick_threads(vecs) : 256), 0, st,
+               (const uint4*)table, ids, (uint4*)out, vecs, V, 1);
+    DIB_CHECK_LAUNCH();
+    return DIB_OK;
+  }
   if (dtype == 0)
     dib_launch(embedding_kernel<float>, dim3(T), dim3(th), 0, st, (const float*)table, ids, (float*)out, H, V);
   else if (dtype == 1)
@@ -859,6 +883,15 @@ int dib_gather_rows(const void* x, const int* idx, void* out, int R, int H, int 
   if (R == 0) return DIB_OK;
   int th = pick_threads(H);
   if (th > 256) th = 256;
+  const size_t row_bytes = (size_t)H * (dtype == 0 ? 4 : 2);
+  if ((dtype == 0 || dtype == 1) && row_bytes % 16 == 0 && T_rows > 0 &&
+      (reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out)) % 16 == 0) {
+    const int vecs = (int)(row_bytes / 16);
+    dib_launch(copy_rows16_kernel, dim3(R), dim3(vecs < 256 ? pick_threads(vecs) : 256), 0, st,
+               (const uint4*)x, idx, (uint4*)out, vecs, T_rows, 0);
+    DIB_CHECK_LAUNCH();
+    return DIB_OK;
+  }
   if (dtype == 0)
     dib_launch(gather_rows_kernel<float>, dim3(R), dim3(th), 0, st, (const float*)x, idx, (float*)out, H, T_rows);
   else if (dtype == 1)

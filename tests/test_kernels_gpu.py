@@ -26,11 +26,18 @@ def ops():
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_embedding(dtype):
+@pytest.mark.parametrize("h", [200, 201, 4096, 8])
+def test_embedding(dtype, h):
+    """Rows of a multiple of 16 bytes are copied 16 bytes a thread, others element by element;
+    an id outside the table gives a row of zeros."""
     torch.manual_seed(0)
-    table = torch.randn(1000, 200, device="cuda").to(dtype)
+    table = torch.randn(1000, h, device="cuda").to(dtype)
     ids = torch.tensor([0, 999, 5, 5, 123, 998, 1], dtype=torch.int32, device="cuda")
     assert torch.equal(ops().embedding(ids, table), ref.embedding(ids, table))
+    bad = torch.tensor([3, -1, 1000, 7], dtype=torch.int32, device="cuda")
+    got = ops().embedding(bad, table)
+    assert torch.equal(got[0], table[3]) and torch.equal(got[3], table[7])
+    assert float(got[1].abs().sum()) == 0.0 and float(got[2].abs().sum()) == 0.0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -120,8 +127,9 @@ def test_silu_mul(dtype, t, i):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_gather_rows(dtype):
-    x = torch.randn(40, 200, device="cuda").to(dtype)
+@pytest.mark.parametrize("h", [200, 203, 4096])
+def test_gather_rows(dtype, h):
+    x = torch.randn(40, h, device="cuda").to(dtype)
     idx = torch.tensor([39, 0, 7, 7], dtype=torch.int32, device="cuda")
     assert torch.equal(ops().gather_rows(x, idx), x[idx.long()])
 
