@@ -217,6 +217,11 @@ def main() -> int:
         print(json.dumps({
             "metric": "continuous batching output tok/s (bf16, 1 B200)", "value": n_req * n_out / dt,
             "first_pass_value": n_req * n_out / runs[0],
+            "graph_captures": {"decode": graphs.captures if graphs else 0,
+                               "decode_seconds": graphs.capture_seconds if graphs else 0.0,
+                               "steps": engine.runner.step_graphs.captures if engine.runner.step_graphs else 0,
+                               "steps_seconds": engine.runner.step_graphs.capture_seconds
+                               if engine.runner.step_graphs else 0.0},
             "unit": "tokens/s", "n_gpus": 1, "seconds": dt, "requests": n_req,
             "prompt_tokens": sum(lens), "output_tokens": n_req * n_out, "temperature": 0.7,
             "steps": engine.runner.steps_run - steps0, "preemptions": engine.scheduler.num_preemptions,

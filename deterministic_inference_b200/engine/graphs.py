@@ -20,6 +20,7 @@ import torch
 import contextlib
 import dataclasses
 import gc
+import time
 from collections import OrderedDict
 
 from .batch import PackedLayout, describe_step, fill_packed, step_views
@@ -77,6 +78,8 @@ class DecodeGraphs:
         self.graphs: dict[tuple, _Captured] = {}
         self.group_list = list(self.cache.page_groups.values())
         self.replays = 0
+        self.captures = 0
+        self.capture_seconds = 0.0
         self.kernels_per_graph: dict[tuple, int] = {}
 
     def usable(self, entries) -> bool:
@@ -123,6 +126,13 @@ class DecodeGraphs:
                 sm[i] = pl[e.num_computed // g.page_size] * g.page_size + e.num_computed % g.page_size
 
     def _capture(self, key: tuple, entries) -> _Captured:
+        t0 = time.perf_counter()
+        cap = self._capture_timed(key, entries)
+        self.captures += 1
+        self.capture_seconds += time.perf_counter() - t0
+        return cap
+
+    def _capture_timed(self, key: tuple, entries) -> _Captured:
         bb, w = key
         dev = self.runner.device
         lay = PackedLayout(bb, bb, bb, w, len(self.group_list))
@@ -203,6 +213,7 @@ class StepGraphs:
         self.group_list = list(self.cache.page_groups.values())
         self.replays = 0
         self.captures = 0
+        self.capture_seconds = 0.0
 
     def _width_bucket(self, width: int) -> int:
         wb = _bucket(width, self.min_width) if width <= 32 else -(-width // 32) * 32
@@ -226,7 +237,9 @@ class StepGraphs:
             self.seen[key] = n
             if n < self.min_repeats:
                 return None
+            t0 = time.perf_counter()
             cap = self._capture(key, shape, wb)
+            self.capture_seconds += time.perf_counter() - t0
         else:
             self.graphs.move_to_end(key)
         num_patches = cap.upload(
