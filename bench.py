@@ -179,8 +179,9 @@ def main() -> int:
     per_req = a.context + max(a.steps + a.warmup, a.point_steps + a.warmup) + 96
     pool = max_b * (-(-per_req // 16) * 16) + a.prefill_tokens + 1024
     ecfg = EngineConfig(model_config=cfg, random_seed=0, dtype="bfloat16", kv_pool_tokens=pool,
-                        page_size=16, max_reqs=max(256, max_b + 8), max_seq_len=8192,
-                        max_prefill_tokens=8192, max_decode_batch=max(256, max_b), device="cuda:0")
+                        page_size=16, max_reqs=max(256, max_b + 8),
+                        max_seq_len=max(8192, -(-per_req // 1024) * 1024, a.prefill_tokens),
+                        max_prefill_tokens=max(8192, a.prefill_tokens), max_decode_batch=max(256, max_b), device="cuda:0")
     engine = Engine(ecfg)
     runner, cache, graphs = engine.runner, engine.cache, engine.decode_graphs
     gen = torch.Generator().manual_seed(1)
