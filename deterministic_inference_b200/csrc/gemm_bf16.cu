@@ -143,6 +143,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   unsigned long long* accum = empty + STAGES;
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(accum + 1);
 
+  pdl_trigger();   // the kernel after this one may set itself up (and fetch its weights) beside this one
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * (GATED ? BM / 2 : BM), m0 = blockIdx.y * BN, split = blockIdx.z;
   const int kb_begin = split * kb_per_split;
@@ -168,7 +169,6 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const unsigned tmem = *tmem_slot;
   bool ok = true;
 
-  pdl_trigger();
   if (warp == 0 && lane == 0) {
     // ---- TMA producer.  The weights do not depend on the kernel before this one, so
     // their loads for the first stages start before the wait for that kernel; the
