@@ -244,3 +244,47 @@ def test_steps_replayed_as_graphs_give_the_bits_of_launched_steps(dtype, tiny_mo
         assert torch.equal(a, b)
     g = runners[0].step_graphs
     assert g.captures >= 3 and g.replays >= 4 + 3 + 4
+
+
+def test_long_prompts_and_a_wide_decode_batch_agree_across_dtypes():
+    """At the 0.6B layer sizes (2 layers): 24 requests with prompts of 1,200 to 1,400 tokens
+    fed in portions of 512, then decoded together for a few steps.  The bfloat16 steps take
+    the tcgen05 prompt kernel behind cached prefixes over many key tiles, and the decode
+    attention that walks many splits per CTA inside a replayed graph; the float32 engine
+    takes the generic kernels.  Their logits agree up to bfloat16 storage."""
+    from deterministic_inference_b200 import EngineConfig, preset
+    from deterministic_inference_b200.engine.batch import SequenceInput
+    from deterministic_inference_b200.engine.graphs import DecodeGraphs
+    from deterministic_inference_b200.engine.runner import ModelRunner
+    cfg = preset("qwen3_0_6b", num_hidden_layers=2, max_window_layers=2)
+    n_req, steps = 24, 4
+    g = torch.Generator().manual_seed(31)
+    lens = torch.randint(1200, 1401, (n_req,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n + steps,), generator=g).tolist() for n in lens]
+    res = {}
+    for dtype in ("bfloat16", "float32"):
+        r = ModelRunner(EngineConfig(model_config=cfg, random_seed=2, dtype=dtype, kv_pool_tokens=40960,
+                                     max_reqs=32, max_seq_len=2048, device="cuda:0"))
+        graphs = DecodeGraphs(r)
+        slots = [r.cache.allocate_slot() for _ in range(n_req)]
+        out = []
+        for i in (0, 7, 23):                                   # three prompts portion by portion
+            for a in range(0, lens[i], 512):
+                b = min(lens[i], a + 512)
+                lg, _ = r.step([SequenceInput(slots[i], prompts[i][a:b], a, [b - a - 1] if b == lens[i] else [])])
+            out.append(lg.float().cpu())
+        rest = [i for i in range(n_req) if i not in (0, 7, 23)]
+        for k in range(0, len(rest), 7):                        # the others whole, seven at a time
+            r.step([SequenceInput(slots[i], prompts[i][:lens[i]], 0, []) for i in rest[k:k + 7]])
+        for s in range(steps):                                  # all decode together, given tokens
+            lg, _ = graphs.run([SequenceInput(slots[i], [prompts[i][lens[i] + s]], lens[i] + s, [0])
+                                for i in range(n_req)])
+            out.append(lg.float().cpu().clone())
+        res[dtype] = out
+        del r, graphs
+        torch.cuda.empty_cache()
+    from deterministic_inference_b200.kernels import ops
+    assert ops._lib("attention_bf16").dib_attention_bf16_status() == 0
+    assert ops._lib("attention_prefill_tc").dib_attention_prefill_tc_status() == 0
+    for a, b in zip(res["bfloat16"], res["float32"]):
+        assert (a - b).abs().max().item() <= 0.03 * b.abs().max().item()
