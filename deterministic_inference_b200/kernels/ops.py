@@ -447,10 +447,15 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
 
 
 def gumbel_sample(logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch.Tensor,
-                  sample_positions: torch.Tensor, keep=None) -> torch.Tensor:
+                  sample_positions: torch.Tensor, keep=None, top_ks=None, top_ps=None,
+                  return_thresholds: bool = False):
     """int32 [R]: rows with temperature <= 0 take the argmax; the others the
     position-seeded Gumbel-max draw from softmax(logits / temperature), restricted
-    to ids with keep != 0 when a mask (uint8 [R, V]) is given."""
+    to ids with keep != 0 when a mask (uint8 [R, V]) is given.  ``top_ks`` (int64 [R],
+    <= 0: off) and ``top_ps`` (float32 [R], >= 1: off), for rows wider than 8,192 ids:
+    top-k / top-p applied inside the kernels by a probability threshold found without a
+    sort (``return_thresholds``: also the int32 bits of each row's smallest kept
+    probability, 0 where nothing is dropped)."""
     _need(logits, "logits", torch.float32, 2)
     r, v = logits.shape
     _need(temperatures, "temperatures", torch.float32, 1)
@@ -469,11 +474,25 @@ def gumbel_sample(logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch
         chunks = -(-v // 4096)
         sf = torch.empty(3, r, chunks, dtype=torch.float32, device=logits.device)
         si = torch.empty(r, chunks, dtype=torch.int32, device=logits.device)
+        thresh = None
+        if top_ks is not None or top_ps is not None:
+            _need(top_ks, "top_ks", torch.int64, 1)
+            _need(top_ps, "top_ps", torch.float32, 1)
+            if top_ks.shape[0] != r or top_ps.shape[0] != r:
+                raise KernelError("gumbel_sample: top_ks / top_ps lengths differ from the number of rows")
+            thresh = torch.empty(r, dtype=torch.int32, device=logits.device)
+            # histograms of the four radix passes: [4, r, 256] 64-bit masses, then 32-bit counts
+            hist = torch.empty(4 * r * 256 * 3 // 2, dtype=torch.int64, device=logits.device)
         st = lib.dib_gumbel_sample_chunked(_ptr(logits), _ptr(temperatures), _ptr(seeds),
-                                           _ptr(sample_positions), _ptr(keep), _ptr(sf), _ptr(si),
-                                           _ptr(out), c_int(r), c_int(v), _stream())
-        _check(st, "gumbel_sample", kernels=3)
-        return out
+                                           _ptr(sample_positions), _ptr(keep), _ptr(top_ks),
+                                           _ptr(top_ps), _ptr(thresh),
+                                           _ptr(hist) if thresh is not None else c_void_p(0),
+                                           _ptr(sf), _ptr(si), _ptr(out), c_int(r), c_int(v), _stream())
+        _check(st, "gumbel_sample", kernels=3 if thresh is None else 7)
+        return (out, thresh) if return_thresholds else out
+    if top_ks is not None or top_ps is not None:
+        raise KernelError("gumbel_sample: top_ks / top_ps are taken for rows wider than 8192 ids; "
+                          "pass a keep mask for narrower rows")
     st = lib.dib_gumbel_sample(_ptr(logits), _ptr(temperatures), _ptr(seeds), _ptr(sample_positions),
                                _ptr(keep), _ptr(out), c_int(r), c_int(v), _stream())
     _check(st, "gumbel_sample")

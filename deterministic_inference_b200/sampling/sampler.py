@@ -8,9 +8,11 @@ vocabulary id), so a request's draw does not depend on the batch
 the token generated after n tokens of the sequence has position n
 (sid/engine/batch.py:3-10).
 
-argmax and the Gumbel draw are this package's kernels; the top-k / top-p mask is
-built with a sort on the device, as in the reference, and only when some row
-asks for it.
+argmax and the Gumbel draw are this package's kernels.  top-k / top-p: for rows wider
+than 8,192 ids the kernels find, without a sort, the probability threshold that the
+reference's sort-and-cumulate rule amounts to (tokens that tie with the threshold all
+stay; masses are added in fixed point); for narrower rows the mask is built with a sort
+on the device as in the reference.  Only when some row asks for it.
 """
 
 from __future__ import annotations
@@ -64,5 +66,8 @@ def sample(logits: torch.Tensor, params: list, sample_positions: list) -> torch.
     device = host.to(dev, non_blocking=True)
     d64, d32 = device[:n64 * 8].view(torch.int64), device[n64 * 8:].view(torch.float32)
     seeds, pos, temps = d64[:r], d64[r:2 * r], d32[:r]
+    if filtered and logits.shape[1] > 8192:
+        # wide rows: the kernels drop what top-k / top-p drop, by a threshold found without a sort
+        return ops.gumbel_sample(logits, temps, seeds, pos, top_ks=d64[2 * r:], top_ps=d32[r:])
     keep = keep_mask(logits, temps, d64[2 * r:], d32[r:]) if filtered else None
     return ops.gumbel_sample(logits, temps, seeds, pos, keep)

@@ -559,6 +559,43 @@ def test_gumbel_draw_independent_of_batch_and_depends_on_position(v):
     assert len(set(one(same, [42] * 64, list(range(64))).tolist())) > 1
 
 
+@pytest.mark.parametrize("v", [151936, 20001])
+def test_top_k_top_p_threshold_is_what_the_sort_rule_keeps(v):
+    """Wide rows: the kernels keep {p >= threshold}; the threshold they find without a sort
+    keeps what the reference's rule keeps (sort descending, drop when the mass before a
+    token exceeds top_p or its rank reaches top_k), up to a token at the boundary whose
+    probability the two computations round differently."""
+    from deterministic_inference_b200.sampling.sampler import keep_mask
+    torch.manual_seed(23)
+    r = 12
+    logits = 4 * torch.randn(r, v, device="cuda")
+    temps = torch.tensor([0.6, 0.6, 1.0, 0.8, 1.3, 0.0, 0.7, 0.6, 2.0, 0.6, 1.0, 0.9], device="cuda")
+    top_ks = torch.tensor([20, -1, 50, 1, 7, 5, -1, 20, 1000, 3, -1, 40000], device="cuda", dtype=torch.int64)
+    top_ps = torch.tensor([0.95, 0.9, 1.0, 0.5, 1.0, 0.9, 1.0, 1.0, 0.99, 0.2, 0.5, 0.999], device="cuda")
+    seeds = torch.arange(r, device="cuda", dtype=torch.int64) + 11
+    pos = torch.arange(50, 50 + r, device="cuda", dtype=torch.int64)
+    toks, thr = ops().gumbel_sample(logits, temps, seeds, pos, top_ks=top_ks, top_ps=top_ps,
+                                    return_thresholds=True)
+    want_keep = keep_mask(logits, temps, top_ks, top_ps).bool()
+    t_safe = torch.where(temps > 0, temps, torch.ones_like(temps))
+    probs = torch.softmax(logits / t_safe.unsqueeze(-1), dim=-1)
+    mine = probs.view(torch.int32) >= thr.unsqueeze(-1)
+    for i in range(r):
+        if temps[i] <= 0:
+            assert toks[i] == logits[i].argmax() and thr[i] == 0
+            continue
+        if top_ks[i] <= 0 and top_ps[i] >= 1:
+            assert thr[i] == 0
+            continue
+        differ = int((mine[i] ^ want_keep[i]).sum())
+        assert differ <= 2, (i, differ, int(mine[i].sum()), int(want_keep[i].sum()))
+        assert bool(mine[i, toks[i]]) or bool(want_keep[i, toks[i]])
+    # the draw itself: the same as with the reference's mask wherever the two sets agree
+    with_mask = ops().gumbel_sample(logits, temps, seeds, pos, want_keep.to(torch.uint8).contiguous())
+    agree = [(mine[i] ^ want_keep[i]).sum() == 0 for i in range(r)]
+    assert all(toks[i] == with_mask[i] for i in range(r) if agree[i]) and sum(map(bool, agree)) >= r - 3
+
+
 def test_top_k_top_p_respected():
     from deterministic_inference_b200.config import SamplingParams
     from deterministic_inference_b200.sampling import sample
