@@ -17,6 +17,7 @@ on the device as in the reference.  Only when some row asks for it.
 
 from __future__ import annotations
 
+import numpy as np
 import torch
 
 from ..kernels import ops
@@ -56,13 +57,14 @@ def sample(logits: torch.Tensor, params: list, sample_positions: list) -> torch.
     # make the host wait: int64 [seeds | positions | top_k], float32 [temperatures | top_p]
     n64, n32 = (3 if filtered else 2) * r, (2 if filtered else 1) * r
     host = torch.empty(n64 * 8 + n32 * 4, dtype=torch.uint8, pin_memory=dev.type == "cuda")
-    h64, h32 = host[:n64 * 8].view(torch.int64), host[n64 * 8:].view(torch.float32)
-    h64[:r] = torch.tensor([p.seed for p in params], dtype=torch.int64)
-    h64[r:2 * r] = torch.tensor(list(sample_positions), dtype=torch.int64)
-    h32[:r] = torch.tensor([p.temperature for p in params], dtype=torch.float32)
+    view = host.numpy()
+    h64, h32 = view[:n64 * 8].view(np.int64), view[n64 * 8:].view(np.float32)
+    h64[:r] = [p.seed for p in params]
+    h64[r:2 * r] = sample_positions
+    h32[:r] = [p.temperature for p in params]
     if filtered:
-        h64[2 * r:] = torch.tensor([p.top_k if p.top_k > 0 else -1 for p in params], dtype=torch.int64)
-        h32[r:] = torch.tensor([p.top_p for p in params], dtype=torch.float32)
+        h64[2 * r:] = [p.top_k if p.top_k > 0 else -1 for p in params]
+        h32[r:] = [p.top_p for p in params]
     device = host.to(dev, non_blocking=True)
     d64, d32 = device[:n64 * 8].view(torch.int64), device[n64 * 8:].view(torch.float32)
     seeds, pos, temps = d64[:r], d64[r:2 * r], d32[:r]
