@@ -81,6 +81,9 @@ class DecodeGraphs:
         self.captures = 0
         self.capture_seconds = 0.0
         self.kernels_per_graph: dict[tuple, int] = {}
+        # one memory pool for all graphs of this object: only one of them runs at a time,
+        # and what a replay leaves (its logits) is read before the next replay is issued
+        self.pool = torch.cuda.graph_pool_handle() if torch.cuda.is_available() else None
 
     def usable(self, entries) -> bool:
         return (0 < len(entries) <= self.max_batch
@@ -154,7 +157,7 @@ class DecodeGraphs:
         from ..kernels import ops
         n0 = ops.launch_count
         graph = torch.cuda.CUDAGraph()
-        with _no_collection(), torch.cuda.graph(graph):
+        with _no_collection(), torch.cuda.graph(graph, pool=self.pool):
             logits = self.runner.model.forward(batch, self.cache)
         self.kernels_per_graph[key] = ops.launch_count - n0
         cap = _Captured(graph, static, host, lay, logits, batch)
@@ -214,6 +217,9 @@ class StepGraphs:
         self.replays = 0
         self.captures = 0
         self.capture_seconds = 0.0
+        # one memory pool for all graphs (their activations never live at the same time;
+        # a replay's logits are copied out before the next replay)
+        self.pool = torch.cuda.graph_pool_handle() if torch.cuda.is_available() else None
 
     def _width_bucket(self, width: int) -> int:
         wb = _bucket(width, self.min_width) if width <= 32 else -(-width // 32) * 32
@@ -277,7 +283,7 @@ class StepGraphs:
         while len(self.graphs) >= self.max_graphs:      # before the capture, not inside it
             self.graphs.popitem(last=False)
         graph = torch.cuda.CUDAGraph()
-        with _no_collection(), torch.cuda.graph(graph):
+        with _no_collection(), torch.cuda.graph(graph, pool=self.pool):
             logits = self.model.forward(batch, self.cache)
         cap = _Captured(graph, static, host, lay, logits, batch)
         self.graphs[key] = cap
