@@ -11,6 +11,7 @@ requests.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -22,6 +23,10 @@ from .batch import SequenceInput
 from .request import Request
 from .runner import ModelRunner
 from .scheduler import Scheduler
+
+
+# DIB200_NVTX=1: every engine step is an NVTX range (for a timeline profiler)
+_NVTX = os.environ.get("DIB200_NVTX", "0") == "1"
 
 
 @dataclass
@@ -135,7 +140,16 @@ class Engine:
                 rids.append(self.add_request(prompt_ids=p, params=sp))
         while self.has_work():
             self.step()
+        self.check_kernels()
         return [self._output(self._done.pop(rid)) for rid in rids]
+
+    def check_kernels(self) -> None:
+        """Raise if a bounded wait inside a kernel ran out since the engine started (the
+        kernels then set an error word and end instead of spinning; their results are not
+        valid).  ``generate`` calls it at its end, ``step`` every 256 steps; it synchronises."""
+        if self.runner.device.type == "cuda":
+            from ..kernels import ops
+            ops.check_kernel_status()
 
     def get_output(self, rid: int) -> Optional[RequestOutput]:
         req = self._done.pop(rid, None)
@@ -150,6 +164,20 @@ class Engine:
         them one step late, while the GPU already runs that next step.  A request
         that turns out to have stopped on an end-of-sequence token has then been fed
         one token too many; that result is dropped."""
+        self._steps_since_check = getattr(self, "_steps_since_check", 0) + 1
+        if self._steps_since_check >= 256:
+            self._steps_since_check = 0
+            self.check_kernels()
+        nvtx = _NVTX and self.runner.device.type == "cuda"
+        if nvtx:
+            torch.cuda.nvtx.range_push("engine.step")
+        try:
+            self._step()
+        finally:
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
+
+    def _step(self) -> None:
         sched = self.scheduler.schedule()
         if not sched:
             if self._inflight is not None:

@@ -102,6 +102,27 @@ def _lib(name: str) -> ctypes.CDLL:
     return lib
 
 
+def kernel_status() -> dict:
+    """The error words of the libraries with bounded waits that have been loaded: name ->
+    0, or the code of a wait that ran out (the results of that launch are not valid).
+    Reading them synchronises with the device."""
+    out = {}
+    for name, fn in (("gemm_bf16", "dib_gemm_bf16_status"), ("attention_bf16", "dib_attention_bf16_status"),
+                     ("attention_prefill_tc", "dib_attention_prefill_tc_status")):
+        lib = _libs.get(name)
+        if lib is not None:
+            out[name] = int(getattr(lib, fn)())
+    return out
+
+
+def check_kernel_status() -> None:
+    """Raise ``KernelError`` if a bounded wait inside a kernel ever ran out."""
+    bad = {k: v for k, v in kernel_status().items() if v != 0}
+    if bad:
+        raise KernelError(f"a bounded wait inside a kernel ran out (library: code): {bad}; results of "
+                          "the steps since the last check are not valid")
+
+
 # ---------------------------------------------------------------- deferred sums
 
 class SplitSum:
