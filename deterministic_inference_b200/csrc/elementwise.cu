@@ -284,11 +284,20 @@ __global__ void qk_norm_rope_cache_vec_kernel(
       const float* src = parts + ((size_t)tok[it] * heads + head[it]) * D + lane * EPL;
 #pragma unroll
       for (int k = 0; k < EPL; ++k) v[it][k] = 0.f;
-#pragma unroll 4
-      for (int sp = 0; sp < S; ++sp) {
-        const Pack<float, EPL> in = *reinterpret_cast<const Pack<float, EPL>*>(src + sp * split_stride);
+      // up to 8 splits' loads go out together, then the sums in split order
+      for (int sp0 = 0; sp0 < S; sp0 += 8) {
+        Pack<float, EPL> in[8];
 #pragma unroll
-        for (int k = 0; k < EPL; ++k) v[it][k] += in.e[k];
+        for (int j = 0; j < 8; ++j)
+          if (sp0 + j < S)
+            in[j] = *reinterpret_cast<const Pack<float, EPL>*>(src + (sp0 + j) * split_stride);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (sp0 + j < S) {
+#pragma unroll
+            for (int k = 0; k < EPL; ++k) v[it][k] += in[j].e[k];
+          }
+        }
       }
 #pragma unroll
       for (int k = 0; k < EPL; ++k) v[it][k] = round_to<T>(v[it][k]);
@@ -544,7 +553,8 @@ __global__ void sum_split_kernel(const float* __restrict__ parts, T* __restrict_
 
 // residual += x (stored rounded), out = rms_norm(unrounded sum), x given as partials.
 template <typename T, int ITERS>
-__global__ void add_rms_norm_split_kernel(const float* __restrict__ parts, int S,
+__global__ void __launch_bounds__(ITERS == 4 ? 1024 : 512)
+add_rms_norm_split_kernel(const float* __restrict__ parts, int S,
                                           long long split_stride, T* __restrict__ residual,
                                           const float* __restrict__ w, T* __restrict__ out, int H,
                                           float eps) {
@@ -553,17 +563,25 @@ __global__ void add_rms_norm_split_kernel(const float* __restrict__ parts, int S
   const size_t base = (size_t)blockIdx.x * H;
   float v[ITERS][4];
   float ss = 0.f;
+  // The kernel is a chain of memory round-trips, so it makes few of them: the residual
+  // and up to 16 partials of an element are requested together, then added in split order.
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
     const int i = (it * blockDim.x + threadIdx.x) * 4;
     if (i < H) {
-      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 8
-      for (int sp = 0; sp < S; ++sp) {
-        const float4 p = *reinterpret_cast<const float4*>(parts + sp * split_stride + base + i);
-        a.x += p.x; a.y += p.y; a.z += p.z; a.w += p.w;
-      }
       const Pack<T, 4> r = *reinterpret_cast<const Pack<T, 4>*>(residual + base + i);
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+      constexpr int BATCH = ITERS == 1 ? 16 : ITERS == 2 ? 8 : 4;   // what the block's registers hold
+      for (int sp0 = 0; sp0 < S; sp0 += BATCH) {
+        float4 p[BATCH];
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j)
+          if (sp0 + j < S)
+            p[j] = *reinterpret_cast<const float4*>(parts + (sp0 + j) * split_stride + base + i);
+#pragma unroll
+        for (int j = 0; j < BATCH; ++j)
+          if (sp0 + j < S) { a.x += p[j].x; a.y += p[j].y; a.z += p[j].z; a.w += p[j].w; }
+      }
       v[it][0] = round_to<T>(a.x) + Elem<T>::load(&r.e[0]);
       v[it][1] = round_to<T>(a.y) + Elem<T>::load(&r.e[1]);
       v[it][2] = round_to<T>(a.z) + Elem<T>::load(&r.e[2]);
@@ -577,18 +595,23 @@ __global__ void add_rms_norm_split_kernel(const float* __restrict__ parts, int S
       *reinterpret_cast<Pack<T, 4>*>(residual + base + i) = o;
     }
   }
+  float4 ww[ITERS];     // requested before the reduction, used after it
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const int i = (it * blockDim.x + threadIdx.x) * 4;
+    ww[it] = i < H ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   const float total = block_sum(ss, scratch);
   const float rstd = 1.0f / sqrtf(total / (float)H + eps);
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
     const int i = (it * blockDim.x + threadIdx.x) * 4;
     if (i < H) {
-      const float4 ww = *reinterpret_cast<const float4*>(w + i);
       Pack<T, 4> o;
-      Elem<T>::store(&o.e[0], v[it][0] * rstd * ww.x);
-      Elem<T>::store(&o.e[1], v[it][1] * rstd * ww.y);
-      Elem<T>::store(&o.e[2], v[it][2] * rstd * ww.z);
-      Elem<T>::store(&o.e[3], v[it][3] * rstd * ww.w);
+      Elem<T>::store(&o.e[0], v[it][0] * rstd * ww[it].x);
+      Elem<T>::store(&o.e[1], v[it][1] * rstd * ww[it].y);
+      Elem<T>::store(&o.e[2], v[it][2] * rstd * ww[it].z);
+      Elem<T>::store(&o.e[3], v[it][3] * rstd * ww[it].w);
       *reinterpret_cast<Pack<T, 4>*>(out + base + i) = o;
     }
   }
@@ -604,13 +627,24 @@ __global__ void silu_mul_split_kernel(const float* __restrict__ parts, int S, lo
   const long long t = idx / per_row;
   const int i = (int)(idx % per_row) * 4;
   float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
-#pragma unroll 4
-  for (int sp = 0; sp < S; ++sp) {
-    const float* row = parts + sp * split_stride + t * 2 * I;
-    const float4 a = *reinterpret_cast<const float4*>(row + i);
-    const float4 b = *reinterpret_cast<const float4*>(row + I + i);
-    g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
-    u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+  // up to 8 splits' loads go out together (one memory round-trip), then the sums in split order
+  for (int sp0 = 0; sp0 < S; sp0 += 8) {
+    float4 a[8], b[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (sp0 + j < S) {
+        const float* row = parts + (sp0 + j) * split_stride + t * 2 * I;
+        a[j] = *reinterpret_cast<const float4*>(row + i);
+        b[j] = *reinterpret_cast<const float4*>(row + I + i);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (sp0 + j < S) {
+        g.x += a[j].x; g.y += a[j].y; g.z += a[j].z; g.w += a[j].w;
+        u.x += b[j].x; u.y += b[j].y; u.z += b[j].z; u.w += b[j].w;
+      }
+    }
   }
   const float gg[4] = {round_to<T>(g.x), round_to<T>(g.y), round_to<T>(g.z), round_to<T>(g.w)};
   const float uu[4] = {round_to<T>(u.x), round_to<T>(u.y), round_to<T>(u.z), round_to<T>(u.w)};
@@ -924,9 +958,11 @@ int dib_add_rms_norm_split(const float* parts, int S, long long split_stride, vo
                            const float* w, void* out, int rows, int H, float eps, int dtype,
                            cudaStream_t st) {
   if (rows == 0) return DIB_OK;
-  const int th_max = rows <= 128 ? 1024 : 256;
-  if (H % 4 != 0 || H / 4 > 4 * th_max || S < 1) return DIB_BAD_SIZE;   // at most 4 per thread
+  if (H % 4 != 0 || S < 1) return DIB_BAD_SIZE;
   const int vecs = H / 4;
+  // Few rows: wide blocks, but 1,024 threads (64 registers each) only where 512 x 4 is too few.
+  const int th_max = rows <= 128 ? (vecs > 2048 ? 1024 : 512) : 256;
+  if (vecs > 4 * th_max) return DIB_BAD_SIZE;                           // at most 4 per thread
   int th = 32;
   while (th < vecs && th < th_max) th <<= 1;
   const int iters = (vecs + th - 1) / th;
