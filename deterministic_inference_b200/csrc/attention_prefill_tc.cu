@@ -62,6 +62,7 @@ namespace {
 
 constexpr int TC_M = 128, TC_N = 128, TC_D = 128, TC_THREADS = 320;
 constexpr int TMA_WARP = 8, MMA_WARP = 9;
+constexpr int PAIR_THREADS = 352, PAIR_V_WARP = 10;   // the pair kernel fetches keys (warp 8) and values apart
 constexpr int TILE_BYTES = 128 * 128 * 2;   // a [128 x 128] bf16 tile (two 64-column halves)
 constexpr int HALF_BYTES = 128 * 64 * 2;
 
@@ -453,8 +454,8 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
 }
 
 // ------------------------------------------------------------------------------
-// Two query tiles per CTA.  The CTA owns two consecutive tiles A and B of 128 rows
-// (same sequence, same kv head), which share every key/value tile they both need.
+// Two query tiles per CTA.  The CTA owns two tiles A and B of 128 rows (same sequence,
+// same kv head, anywhere in it), which share every key/value tile they both need.
 // Warps 0-3 are the softmax threads of A, warps 4-7 those of B: ONE thread per row,
 // the row's 128 scores in registers, so maximum, exponentials and sum need no
 // exchange.  The probabilities go back to tensor memory, packed as bfloat16 over the
@@ -489,13 +490,14 @@ __device__ __forceinline__ float exp2_fma(float x) {
   return __int_as_float(__float_as_int(p) + (__float_as_int(xf) << 23));
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
 extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
                                 const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                                 const int* __restrict__ block_table, int max_blocks,
                                 const int* __restrict__ cu_q_lens, const int* __restrict__ seq_lens,
                                 const int* __restrict__ tile_seq, const int* __restrict__ tile_start,
-                                int Hq, int Hkv, int page_size, float scale, int window,
+                                const int* __restrict__ tile_start_b, int Hq, int Hkv,
+                                int page_size, float scale, int window,
                                 int chunk_tiles, const int* __restrict__ tile_chunk, int max_chunks,
                                 float* __restrict__ part_o, float* __restrict__ part_ml) {
   if (threadIdx.x == 0) DIB_PCLOCK(63, 0);
@@ -516,13 +518,14 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   unsigned long long* s_full = bars + 8;          // [2: A, B] the tile's scores are in tensor memory
   unsigned long long* p_full = bars + 10;         // [2] its probabilities are, and O is rescaled (128)
   unsigned long long* o_final = bars + 12;        // [2] its last product has completed
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 14);
+  unsigned long long* pv_done = bars + 14;        // an output product of the tile that runs alone has completed
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 15);
 
   const int tile = gridDim.y - 1 - blockIdx.y, kvh = blockIdx.x;
   const int G = Hq / Hkv;
   const int npt = TC_M / G;                       // tokens of one query tile
   const int seq = tile_seq[tile];
-  const int tok0 = tile_start[tile];
+  const int tokx[2] = {tile_start[tile], tile_start_b[tile]};   // first token of A and of B (-1: no B)
   const int q_begin = cu_q_lens[seq];
   const int q_len = cu_q_lens[seq + 1] - q_begin;
   const int kv_len = seq_lens[seq];
@@ -542,8 +545,8 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   const int c_hi = chunk_tiles > 0 ? c_lo + chunk_tiles - 1 : 0x7fffffff;
 #pragma unroll
   for (int x = 0; x < 2; ++x) {
-    const int t0 = tok0 + x * npt;
-    ntok[x] = max(0, min(npt, q_len - t0));
+    const int t0 = tokx[x];
+    ntok[x] = t0 >= 0 ? max(0, min(npt, q_len - t0)) : 0;
     const int first_pos = prefix + t0, last_pos = prefix + t0 + ntok[x] - 1;
     const int first_key = (window > 0 && first_pos - window + 1 > 0) ? first_pos - window + 1 : 0;
     const int f = first_key / TC_N;
@@ -557,20 +560,62 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   const int j0 = any0 && any1 ? min(jf[0], jf[1]) : (any0 ? jf[0] : jf[1]);
   const int ntiles = max(any0 ? jl[0] : -1, any1 ? jl[1] : -1) - j0 + 1;
   auto active = [&](int x, int i) { return j0 + i >= jf[x] && j0 + i <= jl[x]; };
+  // Once one tile has had its last key tile, the other runs alone (a tile early in a
+  // prompt beside one late in it).  Alone it would wait for the tensor core and the
+  // tensor core for it, in turn; so from key tile `solo_from` on it takes the finished
+  // tile's score columns as a second buffer: the scores of key tile i + 1 are computed
+  // while its softmax works on tile i.  solo_x is that tile, 1 - solo_x the finished one.
+  const int solo_x = (any1 && (!any0 || jl[1] >= jl[0])) ? 1 : 0;
+  const int n_other = (solo_x ? any0 : any1) ? jl[1 - solo_x] - jf[1 - solo_x] + 1 : 0;   // its key tiles
+  const int solo_from = max((solo_x ? any0 : any1) ? jl[1 - solo_x] - j0 + 1 : 0, jf[solo_x] - j0);
 
-  if (warp == MMA_WARP && lane == 0) {
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
-      mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&p_full[i], 128);
-      mbar_init(&o_final[i], 1);
+  bool ok = true;
+  // The warp that fetches the keys and the one that fetches the values each prepare
+  // their own barriers and send for the first two key tiles at once, beside the loading
+  // of Q below.  Lane l takes half (64 dimensions) l & 1 of page l >> 1 of a key tile.
+  const int tile_ops = TC_N / page_size * 2;
+  auto fetch = [&](int kv, int i, int page) {
+    const int st = i & 1;
+    unsigned long long* full = kv ? &v_full[st] : &k_full[st];
+    if (lane == 0) mbar_expect_tx(full, TILE_BYTES);
+    __syncwarp();
+    if (lane < tile_ops) {
+      const int pi = lane >> 1, half = lane & 1;
+      const int row0 = (((page * 2 + kv) * Hkv) + kvh) * page_size;
+      unsigned char* dst = sKV + st * 2 * TILE_BYTES + kv * TILE_BYTES + half * HALF_BYTES +
+                           pi * page_size * 128;
+      tma_load_2d(dst, &map, half * 64, row0, full);
     }
-    mbar_fence_init();
+  };
+  auto page_of = [&](int i) {      // this lane's page of key tile i
+    const int idx = (j0 + i) * (TC_N / page_size) + (lane >> 1);
+    return (lane < tile_ops && i < ntiles && idx < max_blocks) ? bt[idx] : 0;
+  };
+  if (warp == TMA_WARP || warp == PAIR_V_WARP) {
+    const int kv = warp == PAIR_V_WARP;
+    if (lane == 0) {
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(kv ? &v_full[i] : &k_full[i], 1);
+        mbar_init(kv ? &v_empty[i] : &k_empty[i], 1);
+      }
+      mbar_fence_init();
+    }
+    __syncwarp();
+    const int p0 = page_of(0), p1 = page_of(1);
+    fetch(kv, 0, p0);
+    if (ntiles > 1) fetch(kv, 1, p1);
   }
-  if (warp == TMA_WARP) {
+  if (warp == MMA_WARP) {
+    if (lane == 0) {
+      mbar_init(pv_done, 1);
+      for (int i = 0; i < 2; ++i) {
+        mbar_init(&s_full[i], 1);
+        mbar_init(&p_full[i], 128);
+        mbar_init(&o_final[i], 1);
+      }
+      mbar_fence_init();
+    }
+    __syncwarp();
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                      smem_u32(tmem_slot)),
                  "r"(512u));
@@ -579,24 +624,25 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   // both Q tiles -> shared memory, swizzled; rows beyond a tile's tokens are zero.  All of
   // a thread's loads go out before its first store (one memory round-trip, not thirteen).
   {
-    constexpr int PER_THREAD = (2 * TC_M * 16 + TC_THREADS - 1) / TC_THREADS;
+    constexpr int LOADERS = 256;      // the softmax threads: the other warps are busy with keys, values and tensor memory
+    constexpr int PER_THREAD = 2 * TC_M * 16 / LOADERS;
     uint4 v[PER_THREAD];
 #pragma unroll
     for (int it = 0; it < PER_THREAD; ++it) {
-      const int c = threadIdx.x + it * TC_THREADS;
+      const int c = threadIdx.x + it * LOADERS;
       const int x = c >> 11, r = (c >> 4) & 127, ch = c & 15;
       const int tl = r / G, g = r % G;
       v[it] = make_uint4(0, 0, 0, 0);
-      if (c < 2 * TC_M * 16 && tl < ntok[x]) {
-        const size_t t = (size_t)(q_begin + tok0 + x * npt + tl);
+      if (threadIdx.x < LOADERS && tl < ntok[x]) {
+        const size_t t = (size_t)(q_begin + tokx[x] + tl);
         v[it] = *reinterpret_cast<const uint4*>(q + (t * Hq + (size_t)kvh * G + g) * TC_D + ch * 8);
       }
     }
 #pragma unroll
     for (int it = 0; it < PER_THREAD; ++it) {
-      const int c = threadIdx.x + it * TC_THREADS;
+      const int c = threadIdx.x + it * LOADERS;
       const int x = c >> 11, r = (c >> 4) & 127, ch = c & 15;
-      if (c < 2 * TC_M * 16) *reinterpret_cast<uint4*>(sQ + x * TILE_BYTES + sw_chunk_off(r, ch)) = v[it];
+      if (threadIdx.x < LOADERS) *reinterpret_cast<uint4*>(sQ + x * TILE_BYTES + sw_chunk_off(r, ch)) = v[it];
     }
   }
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // Q is read by the MMA unit
@@ -604,35 +650,20 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   __syncthreads();
   tc_fence_after();
   const unsigned tmem = *tmem_slot;
-  bool ok = true;
   if (threadIdx.x == 0) DIB_PCLOCK(63, 2);
 
-  if (warp == TMA_WARP) {
-    // keys and values of a key tile are fetched, waited for and handed back apart: the
-    // keys are free again after the two score products, long before the values
-    const int pages = TC_N / page_size;
-    const int ops = pages * 2;
-    for (int i = 0; i < ntiles && ok; ++i) {
-      const int st = i & 1;
-      const int k0 = (j0 + i) * TC_N;
-#pragma unroll
-      for (int kv = 0; kv < 2; ++kv) {
-        unsigned long long* full = kv ? &v_full[st] : &k_full[st];
-        if (i >= 2) ok = mbar_wait(kv ? &v_empty[st] : &k_empty[st], ((i >> 1) - 1) & 1);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        if (lane == 0) mbar_expect_tx(full, TILE_BYTES);
-        __syncwarp();
-        for (int op = lane; op < ops; op += 32) {
-          const int pi = op >> 1, half = op & 1;
-          const int idx = k0 / page_size + pi;
-          const int page = idx < max_blocks ? bt[idx] : 0;
-          const int row0 = (((page * 2 + kv) * Hkv) + kvh) * page_size;
-          unsigned char* dst = sKV + st * 2 * TILE_BYTES + kv * TILE_BYTES + half * HALF_BYTES +
-                               pi * page_size * 128;
-          tma_load_2d(dst, &map, half * 64, row0, full);
-        }
-      }
+  if (warp == TMA_WARP || warp == PAIR_V_WARP) {
+    // Keys and values of a key tile are fetched, waited for and handed back apart, each
+    // by a warp of its own: the keys are free again after the score products, long
+    // before the values, and neither waits for the other's stage.  The page ids of the
+    // next key tile are read while the warp waits for its stage.
+    const int kv = warp == PAIR_V_WARP;
+    for (int i = 2; i < ntiles && ok; ++i) {
+      const int page = page_of(i);
+      ok = mbar_wait(kv ? &v_empty[i & 1] : &k_empty[i & 1], ((i >> 1) - 1) & 1);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      fetch(kv, i, page);
     }
   } else if (warp == MMA_WARP) {
     if (lane == 0) {
@@ -653,15 +684,16 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
         k_desc[st] = desc_k_major(smem_u32(sKV + st * 2 * TILE_BYTES));
         v_desc[st] = desc_mn_major(smem_u32(sKV + st * 2 * TILE_BYTES + TILE_BYTES), HALF_BYTES);
       }
-      auto issue_s = [&](int x, int i) {
+      auto issue_s_to = [&](int x, int buf, int i) {     // scores of tile x, key tile i -> columns of buf
         const unsigned long long kd = k_desc[i & 1];
 #pragma unroll
         for (int ks = 0; ks < TC_D / 16; ++ks)
-          tc_mma(tmem + x * 128, q_desc[x][ks],
+          tc_mma(tmem + buf * 128, x ? q_desc[1][ks] : q_desc[0][ks],
                  kd + (unsigned long long)(((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4), idesc_s,
                  ks > 0 ? 1u : 0u);
-        tc_commit(&s_full[x]);
+        tc_commit(&s_full[buf]);
       };
+      auto issue_s = [&](int x, int i) { issue_s_to(x, x, i); };
       int uses[2] = {0, 0};     // completed phases of p_full[x]
       int have_k = 0;           // keys of key tiles 0..have_k have been waited for
       int have_v = -1;          // values likewise
@@ -672,7 +704,8 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
         if (active(1, 0)) issue_s(1, 0);
         tc_commit(&k_empty[0]);
       }
-      for (int i = 0; i < ntiles && ok; ++i) {
+      const int paired_end = min(ntiles, solo_from);
+      for (int i = 0; i < paired_end && ok; ++i) {
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (active(x, i)) {
@@ -710,54 +743,103 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
           DIB_PCLOCK(i, x * 3 + 2);
         }
       }
+      // ---- one tile alone: its scores of key tile i are in buffer (i - solo_from) & 1
+      // (0: its own columns, 1: the finished tile's); those of i + 1 go to the other one
+      // before this loop waits for the probabilities of i.
+      for (int i = solo_from; i < ntiles && ok; ++i) {
+        const int x = solo_x;
+        const int buf = ((i - solo_from) & 1) ? 1 - x : x;
+        DIB_PCLOCK(i, 0);
+        if (i + 1 < ntiles) {
+          if (have_k < i + 1) {
+            ok = mbar_wait(&k_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
+            if (!ok) break;
+            have_k = i + 1;
+            tc_fence_after();
+          }
+          DIB_PCLOCK(i, 1);
+          issue_s_to(x, 1 - buf, i + 1);
+          tc_commit(&k_empty[(i + 1) & 1]);
+        }
+        DIB_PCLOCK(i, 2);
+        DIB_PCLOCK(i, 3);
+        ok = mbar_wait(&p_full[buf], uses[buf] & 1);
+        DIB_PCLOCK(i, 4);
+        if (!ok) break;
+        ++uses[buf];
+        if (have_v < i) {
+          ok = mbar_wait(&v_full[i & 1], (i >> 1) & 1);
+          if (!ok) break;
+          have_v = i;
+        }
+        tc_fence_after();
+        const unsigned long long vd = v_desc[i & 1];
+        const bool first = j0 + i == jf[x];
+#pragma unroll
+        for (int ks = 0; ks < TC_N / 16; ++ks)
+          tc_mma_ts(tmem + 256 + x * 128, tmem + buf * 128 + ks * 8,
+                    vd + (unsigned long long)((ks * 16 * 128) >> 4), idesc_o,
+                    (!first || ks > 0) ? 1u : 0u);
+        tc_commit(&v_empty[i & 1]);
+        tc_commit(pv_done);
+        if (i == ntiles - 1) tc_commit(&o_final[x]);
+        DIB_PCLOCK(i, 5);
+      }
     }
   } else {
     // ---- softmax: thread r of group x owns row r of tile x
     const int x = threadIdx.x >> 7, r = threadIdx.x & 127;
     const int tl = r / G, g = r % G;
     const bool valid = tl < ntok[x];
-    const int hi = valid ? prefix + tok0 + x * npt + tl : -1;
+    const int hi = valid ? prefix + tokx[x] + tl : -1;
     const int lo = (valid && window > 0 && hi - window + 1 > 0) ? hi - window + 1 : 0;
     const float scale_log2 = scale * LOG2E;
     const unsigned lane_base = (unsigned)((warp & 3) * 32) << 16;
-    const unsigned tmem_s = tmem + lane_base + x * 128;
     const unsigned tmem_o = tmem + lane_base + 256 + x * 128;
     float m_ref = NEG_BIG, l = 0.f;
-    int uses = 0;
+    // completed phases of s_full[own columns] and s_full[the other tile's]: the latter has
+    // served the other tile's key tiles before this one borrows it
+    int uses_own = 0, uses_other = n_other;
+    const int my_solo = x == solo_x ? solo_from : 0x7fffffff;
     for (int i = 0; i < ntiles && ok; ++i) {
       if (!active(x, i)) continue;
-      if (threadIdx.x == 0) DIB_PCLOCK(i, 6);
-      ok = mbar_wait(&s_full[x], uses & 1);
+      if (threadIdx.x == 128) DIB_PCLOCK(i, 6);
+      const bool borrowed = i >= my_solo && ((i - my_solo) & 1);
+      const int buf = borrowed ? 1 - x : x;
+      const unsigned tmem_s = tmem + lane_base + buf * 128;
+      ok = mbar_wait(&s_full[buf], (borrowed ? uses_other : uses_own) & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
-      ++uses;
+      if (borrowed) ++uses_other; else ++uses_own;
       tc_fence_after();
-      if (threadIdx.x == 0) DIB_PCLOCK(i, 7);
+      if (threadIdx.x == 128) DIB_PCLOCK(i, 7);
       const int kbase = (j0 + i) * TC_N;
       const bool full = kbase >= lo && kbase + TC_N - 1 <= hi;   // no key of the tile is masked
       unsigned v[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tc_ld32(tmem_s + c * 32, v[c]);
       tc_wait_ld();
-      if (threadIdx.x == 0) DIB_PCLOCK(i, 8);
+      if (threadIdx.x == 128) DIB_PCLOCK(i, 8);
       // Four independent chains for the maximum and for the sum (a thread has few warps
       // beside it to hide the latency of one long chain).  Tiles without a masked key,
       // nearly all of them, take a path without the per-key tests.
       float m4[4] = {NEG_BIG, NEG_BIG, NEG_BIG, NEG_BIG};
-      if (full) {
+      if (!full) {
+        // keys outside [lo, hi] get the score NEG_BIG: one subtraction and one unsigned
+        // comparison each; their exponentials below are exactly zero
+        const int a = lo - kbase, b = hi - kbase;
+        const int first_vis = b >= a ? a : (1 << 20);
+        const unsigned span = b >= a ? (unsigned)(b - a) : 0u;
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int k = 0; k < 32; ++k) m4[k & 3] = fmaxf(m4[k & 3], __uint_as_float(v[c][k]));
-      } else {
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-#pragma unroll
-          for (int k = 0; k < 32; ++k) {
-            const int key = kbase + c * 32 + k;
-            if (key >= lo && key <= hi) m4[k & 3] = fmaxf(m4[k & 3], __uint_as_float(v[c][k]));
-          }
+          for (int k = 0; k < 32; ++k)
+            if ((unsigned)(c * 32 + k - first_vis) > span) v[c][k] = __float_as_uint(NEG_BIG);
       }
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int k = 0; k < 32; ++k) m4[k & 3] = fmaxf(m4[k & 3], __uint_as_float(v[c][k]));
       float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       mx = mx <= -1e29f ? NEG_BIG : mx * scale_log2;   // scale is positive
       // the reference maximum rises only when it must (or at the first visible key)
@@ -790,17 +872,16 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
             v[c >> 1][(c & 1) * 16 + (k >> 1) + 1] = pack_bf16(p2, p3);
           }
       } else {
+        // a tile with masked keys: every exponential on the special-function unit, whose
+        // result for a masked score (NEG_BIG) is exactly zero
 #pragma unroll
         for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int k = 0; k < 32; k += 4) {
-            const int key = kbase + c * 32 + k;
             float pj[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              const float xj = fmaf(__uint_as_float(v[c][k + j]), scale_log2, -m_use);
-              const float e = j == 3 ? exp2_fma(xj) : fast_exp2(xj);
-              pj[j] = (key + j >= lo && key + j <= hi) ? e : 0.f;
+              pj[j] = fast_exp2(fmaf(__uint_as_float(v[c][k + j]), scale_log2, -m_use));
               s4[j] += pj[j];
             }
             v[c >> 1][(c & 1) * 16 + (k >> 1)] = pack_bf16(pj[0], pj[1]);
@@ -809,10 +890,18 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
       }
       const float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
       l += sum;
-      if (threadIdx.x == 0) DIB_PCLOCK(i, 9);
-      // O of this tile (its last product completed before these scores did) is rescaled
-      // when a row of the warp raised its reference
+      if (threadIdx.x == 128) DIB_PCLOCK(i, 9);
+      // O of this tile is rescaled when a row of the warp raised its reference.  Its last
+      // product completed before these scores did, except where the tile runs alone: there
+      // the scores of key tile i were issued before the product of i - 1, which is waited
+      // for here (phase i - 1 - my_solo of pv_done; that of i - 2 completed before the scores).
       if (__any_sync(0xffffffffu, rescale)) {
+        if (i > my_solo) {
+          ok = mbar_wait(pv_done, (i - 1 - my_solo) & 1);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+        }
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
           tc_ld32(tmem_o + c * 32, v[2]);
@@ -825,11 +914,11 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
       }
       tc_st32(tmem_s, v[0]);          // probabilities over the scores they came from
       tc_st32(tmem_s + 32, v[1]);
-      if (threadIdx.x == 0) DIB_PCLOCK(i, 10);
+      if (threadIdx.x == 128) DIB_PCLOCK(i, 10);
       tc_wait_st();
       tc_fence_before();
-      mbar_arrive(&p_full[x]);
-      if (threadIdx.x == 0) DIB_PCLOCK(i, 11);
+      mbar_arrive(&p_full[buf]);
+      if (threadIdx.x == 128) DIB_PCLOCK(i, 11);
     }
     if (threadIdx.x == 0) DIB_PCLOCK(63, 3);
     if (ok && jl[x] >= jf[x]) {
@@ -838,7 +927,7 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
       tc_fence_after();
       if (ok && !whole[x]) {
         // a partial result of this chunk: O as accumulated (against m_ref), m_ref, l
-        const size_t t = (size_t)(q_begin + tok0 + x * npt + tl);
+        const size_t t = (size_t)(q_begin + tokx[x] + tl);
         const size_t row = (t * Hq + (size_t)kvh * G + g) * max_chunks + chunk;
         float* dst = part_o + row * TC_D;
 #pragma unroll
@@ -856,7 +945,7 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
         if (valid) *reinterpret_cast<float2*>(part_ml + row * 2) = make_float2(m_ref, l);
       } else if (ok) {
         const float inv = 1.0f / l;
-        const size_t t = (size_t)(q_begin + tok0 + x * npt + tl);
+        const size_t t = (size_t)(q_begin + tokx[x] + tl);
         __nv_bfloat16* dst = out + (t * Hq + (size_t)kvh * G + g) * TC_D;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -884,7 +973,7 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   __syncthreads();
   if (threadIdx.x == 0) DIB_PCLOCK(63, 5);
   DIB_PTIME(1);
-  if (warp == TMA_WARP) {
+  if (warp == MMA_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
   }
 }
@@ -1052,8 +1141,10 @@ int dib_extend_attention_tc(const void* q, void* out, const void* cache, long lo
   return DIB_OK;
 }
 
-// The same with two consecutive query tiles per CTA: tiles name (sequence, first token)
-// with 2 * 128 / (Hq/Hkv) tokens each.
+// The same with two query tiles of one sequence per CTA: a list entry names the sequence
+// and the first tokens of tile A and of tile B (128 / (Hq/Hkv) tokens each; -1: no B).  The
+// two share the key tiles that both need; the caller pairs a tile early in a prompt with
+// one late in it, so that every CTA has about the same number of key tiles.
 // chunk_tiles > 0: the key range is cut into chunks of that many tiles of 128 keys and a
 // list entry names (sequence, first token, chunk tile_chunk[i] < max_chunks): several CTAs
 // share a pair of query tiles (the caller lists every chunk a pair may need, longest
@@ -1064,8 +1155,8 @@ int dib_extend_attention_tc(const void* q, void* out, const void* cache, long lo
 int dib_extend_attention_tc_pair(const void* q, void* out, const void* cache, long long num_pages,
                                  const int* block_table, int max_blocks, const int* cu_q_lens,
                                  const int* seq_lens, const int* tile_seq, const int* tile_start,
-                                 int num_tiles, int Hq, int Hkv, int D, int page_size, float scale,
-                                 int window, int chunk_tiles, const int* tile_chunk, int max_chunks,
+                                 const int* tile_start_b, int num_tiles, int Hq, int Hkv, int D,
+                                 int page_size, float scale, int window, int chunk_tiles, const int* tile_chunk, int max_chunks,
                                  float* part_o, float* part_ml, const int* token_seq, int t_first,
                                  int num_tokens, cudaStream_t st) {
   if (num_tiles == 0) return DIB_OK;
@@ -1076,7 +1167,7 @@ int dib_extend_attention_tc_pair(const void* q, void* out, const void* cache, lo
     return DIB_BAD_SIZE;
   const CUtensorMap* map = cache_map(cache, num_pages, Hkv, page_size, D);
   if (map == nullptr) return DIB_LAUNCH_FAILED;
-  const size_t smem = 6 * TILE_BYTES + 14 * 8 + 16 + 1024;
+  const size_t smem = 6 * TILE_BYTES + 15 * 8 + 16 + 1024;
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(extend_attention_tc_pair_kernel,
@@ -1091,10 +1182,10 @@ int dib_extend_attention_tc_pair(const void* q, void* out, const void* cache, lo
              token_seq == nullptr || num_tokens < 1) {
     return DIB_BAD_SIZE;
   }
-  dib_launch(extend_attention_tc_pair_kernel, dim3(Hkv, num_tiles), dim3(TC_THREADS), smem, st, *map,
+  dib_launch(extend_attention_tc_pair_kernel, dim3(Hkv, num_tiles), dim3(PAIR_THREADS), smem, st, *map,
              (const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, max_blocks, cu_q_lens, seq_lens,
-             tile_seq, tile_start, Hq, Hkv, page_size, scale, window, chunk_tiles, tile_chunk,
-             max_chunks, part_o, part_ml);
+             tile_seq, tile_start, tile_start_b, Hq, Hkv, page_size, scale, window, chunk_tiles,
+             tile_chunk, max_chunks, part_o, part_ml);
   DIB_CHECK_LAUNCH();
   if (chunk_tiles > 0 && max_chunks > 1) {
     dib_launch(extend_attention_merge_kernel, dim3((num_tokens + 7) / 8), dim3(256), 0, st,

@@ -39,25 +39,53 @@ def _sm_count(device) -> int:
     return n
 
 
-def extend_chunk_units(q_lens: list, kv_lens: list, first_seq: int, tokens_per_pair: int,
+def extend_chunk_units(q_lens: list, kv_lens: list, first_seq: int, tokens_per_tile: int,
                        chunk_tiles: int):
-    """(sequence, first token, chunk) for every chunk of ``chunk_tiles`` key tiles that a pair
-    of query tiles may need: chunks 0 .. the one of the pair's last position, with the
-    lengths the host knows (under a captured graph an upper bound: a chunk past the real
-    range costs a CTA that leaves at once).  Longest first, so that the CTAs the GPU takes
-    up last are the short ones."""
+    """(sequence, first token of A, of B, chunk) for every chunk of ``chunk_tiles`` key tiles
+    that a pair of consecutive query tiles may need: chunks 0 .. the one of the pair's last
+    position, with the lengths the host knows (under a captured graph an upper bound: a
+    chunk past the real range costs a CTA that leaves at once).  Longest first, so that the
+    CTAs the GPU takes up last are the short ones."""
     units = []
     span = chunk_tiles * 128
     for s in range(first_seq, len(q_lens)):
         prefix = kv_lens[s] - q_lens[s]
-        for t0 in range(0, q_lens[s], tokens_per_pair):
-            last_pos = prefix + min(t0 + tokens_per_pair, q_lens[s]) - 1
+        for t0 in range(0, q_lens[s], 2 * tokens_per_tile):
+            t1 = t0 + tokens_per_tile if t0 + tokens_per_tile < q_lens[s] else -1
+            last_pos = prefix + min(t0 + 2 * tokens_per_tile, q_lens[s]) - 1
             for c in range(last_pos // span + 1):
                 keys = min(last_pos + 1, (c + 1) * span) - c * span
-                units.append((-keys, s, t0, c))
+                units.append((-keys, s, t0, t1, c))
     units.sort()
     # the kernel takes its list from the end (the last entry first)
     units.reverse()
+    return [u[1] for u in units], [u[2] for u in units], [u[3] for u in units], [u[4] for u in units]
+
+
+def extend_tile_pairs(q_lens: list, kv_lens: list, first_seq: int, tokens_per_tile: int,
+                      window: int):
+    """(sequence, first token of A, first token of B or -1) for the CTAs of the kernel
+    that takes two query tiles of a sequence at once.  Under a causal mask the k-th tile
+    of a prompt needs about k key tiles more than the first, so the k-th tile is paired
+    with the k-th from the end: every pair then needs the same number of key-tile products,
+    and the short tile's key tiles are among the long one's.  With a window every tile
+    needs about as many key tiles as the next, and neighbours share most of them: they
+    are paired.  The entries are sorted by the key tiles they need, the longest last (the
+    kernel takes its list from the end)."""
+    units = []
+    for s in range(first_seq, len(q_lens)):
+        prefix = kv_lens[s] - q_lens[s]
+        starts = list(range(0, q_lens[s], tokens_per_tile))
+        n = len(starts)
+        if window > 0:
+            pairs = [(starts[i], starts[i + 1] if i + 1 < n else -1) for i in range(0, n, 2)]
+        else:
+            pairs = [(starts[i], starts[n - 1 - i] if n - 1 - i > i else -1) for i in range((n + 1) // 2)]
+        for a, b in pairs:
+            last = prefix + min(max(a, b) + tokens_per_tile, q_lens[s]) - 1
+            first = max(0, prefix + a - window + 1) if window > 0 else 0
+            units.append((last // 128 - first // 128 + 1, s, a, b))
+    units.sort()
     return [u[1] for u in units], [u[2] for u in units], [u[3] for u in units]
 
 
@@ -101,13 +129,17 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
             and tc_mode != "0":
         # tcgen05 kernels: 128 rows per query tile, one or two tiles per CTA
         pair = tc_mode != "1"
-        tpt = TC_TILE_ROWS // group * (2 if pair else 1)
-        tiles = meta.scratch.get(("extend_tiles", tpt))
+        tpt = TC_TILE_ROWS // group
+        tiles = meta.scratch.get(("extend_tiles", tpt, pair, window > 0))
         if tiles is None:
-            seqs, starts = extend_tiles(meta.q_lens, nd, tpt)
-            both = torch.tensor([seqs, starts], dtype=torch.int32).to(q.device, non_blocking=True)
-            tiles = (both[0], both[1], len(seqs))
-            meta.scratch[("extend_tiles", tpt)] = tiles
+            if pair:
+                seqs, starts, starts_b = extend_tile_pairs(meta.q_lens, meta.kv_lens, nd, tpt, window)
+            else:
+                seqs, starts = extend_tiles(meta.q_lens, nd, tpt)
+                starts_b = starts
+            both = torch.tensor([seqs, starts, starts_b], dtype=torch.int32).to(q.device, non_blocking=True)
+            tiles = (both[0], both[1], len(seqs), both[2])
+            meta.scratch[("extend_tiles", tpt, pair, window > 0)] = tiles
         tc_lib = _lib("attention_prefill_tc")
         if not pair:
             st = tc_lib.dib_extend_attention_tc(
@@ -134,9 +166,11 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
             max_chunks = -(-n_keys // (chunk_tiles * 128))
             got = meta.scratch.get(("extend_chunks", tpt, chunk_tiles))
             if got is None:
-                seqs, starts, chunks = extend_chunk_units(meta.q_lens, meta.kv_lens, nd, tpt, chunk_tiles)
-                both = torch.tensor([seqs, starts, chunks], dtype=torch.int32).to(q.device, non_blocking=True)
-                got = ((both[0], both[1], len(seqs)), both[2],
+                seqs, starts, starts_b, chunks = extend_chunk_units(meta.q_lens, meta.kv_lens, nd, tpt,
+                                                                    chunk_tiles)
+                both = torch.tensor([seqs, starts, chunks, starts_b], dtype=torch.int32).to(
+                    q.device, non_blocking=True)
+                got = ((both[0], both[1], len(seqs), both[3]), both[2],
                        (torch.empty(t, hq, max_chunks, d, dtype=torch.float32, device=q.device),
                         torch.empty(t, hq, max_chunks, 2, dtype=torch.float32, device=q.device)))
                 meta.scratch[("extend_chunks", tpt, chunk_tiles)] = got
@@ -144,8 +178,8 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
         st = tc_lib.dib_extend_attention_tc_pair(
             _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0]), _ptr(bt),
             c_int(bt.shape[1]), _ptr(meta.cu_q_lens), _ptr(meta.seq_lens), _ptr(tiles[0]),
-            _ptr(tiles[1]), c_int(tiles[2]), c_int(hq), c_int(hkv), c_int(d), c_int(page_size),
-            c_float(scale), c_int(window), c_int(chunk_tiles if max_chunks > 1 else 0),
+            _ptr(tiles[1]), _ptr(tiles[3]), c_int(tiles[2]), c_int(hq), c_int(hkv), c_int(d),
+            c_int(page_size), c_float(scale), c_int(window), c_int(chunk_tiles if max_chunks > 1 else 0),
             _ptr(chunk_list), c_int(max_chunks), _ptr(ws[0]), _ptr(ws[1]), _ptr(meta.token_seq),
             c_int(nd), c_int(t - nd), _stream())
         _check(st, "extend_attention_tc_pair", f"heads {hq}/{hkv}, head_dim {d}",
