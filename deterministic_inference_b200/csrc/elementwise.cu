@@ -505,26 +505,34 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
   const int i = (int)(idx % I);
   const float g = Elem<T>::load(gu + t * 2 * I + i);
   const float u = Elem<T>::load(gu + t * 2 * I + I + i);
-  const float sg = g / (1.0f + expf(-g));
-  Elem<T>::store(out + idx, sg * u);
+  Elem<T>::store(out + idx, silu_gate<T>(g, u));
 }
 
-template <typename T>
-__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, long long vecs,
+// blockIdx.x names ROWS consecutive tokens, blockIdx.y and the thread a vector of the row
+// (no division); a thread sends for its vectors of all ROWS tokens before it computes.
+template <typename T, int ROWS>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int T_rows,
                                     int I) {
   pdl_prologue();
   constexpr int N = Vec<T>::N;
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= vecs) return;
-  const int per_row = I / N;
-  const long long t = idx / per_row;
-  const int i = (int)(idx % per_row) * N;
-  float g[N], u[N], y[N];
-  Vec<T>::load(gu + t * 2 * I + i, g);
-  Vec<T>::load(gu + t * 2 * I + I + i, u);
+  const int i = (blockIdx.y * blockDim.x + threadIdx.x) * N;
+  if (i >= I) return;
+  const long long t0 = (long long)blockIdx.x * ROWS;
+  float g[ROWS][N], u[ROWS][N];
 #pragma unroll
-  for (int k = 0; k < N; ++k) y[k] = g[k] / (1.0f + expf(-g[k])) * u[k];
-  Vec<T>::store(out + t * I + i, y);
+  for (int r = 0; r < ROWS; ++r)
+    if (t0 + r < T_rows) {
+      Vec<T>::load(gu + (t0 + r) * 2 * I + i, g[r]);
+      Vec<T>::load(gu + (t0 + r) * 2 * I + I + i, u[r]);
+    }
+#pragma unroll
+  for (int r = 0; r < ROWS; ++r)
+    if (t0 + r < T_rows) {
+      float y[N];
+#pragma unroll
+      for (int k = 0; k < N; ++k) y[k] = silu_gate<T>(g[r][k], u[r][k]);
+      Vec<T>::store(out + (t0 + r) * I + i, y);
+    }
 }
 
 // ------------------------------------------------ readers of split-k partials
@@ -650,7 +658,7 @@ __global__ void silu_mul_split_kernel(const float* __restrict__ parts, int S, lo
   const float uu[4] = {round_to<T>(u.x), round_to<T>(u.y), round_to<T>(u.z), round_to<T>(u.w)};
   Pack<T, 4> o;
 #pragma unroll
-  for (int k = 0; k < 4; ++k) Elem<T>::store(&o.e[k], gg[k] / (1.0f + expf(-gg[k])) * uu[k]);
+  for (int k = 0; k < 4; ++k) Elem<T>::store(&o.e[k], silu_gate<T>(gg[k], uu[k]));
   *reinterpret_cast<Pack<T, 4>*>(out + t * I + i) = o;
 }
 
@@ -887,17 +895,24 @@ int dib_silu_mul(const void* gu, void* out, int T, int I, int dtype, cudaStream_
   if (total == 0) return DIB_OK;
   const int th = 256;
   const bool aligned = reinterpret_cast<uintptr_t>(gu) % 16 == 0 && reinterpret_cast<uintptr_t>(out) % 16 == 0;
-  if (aligned && dtype == 1 && I % 8 == 0) {
-    const long long vecs = total / 8;
-    dib_launch(silu_mul_vec_kernel<__nv_bfloat16>, dim3(ceil_div_host(vecs, th)), dim3(th), 0, st, 
-        (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, vecs, I);
+  if (aligned && dtype == 1 && I % 8 == 0 && I / 8 <= 65535 * 32) {
+    const int per_row = I / 8;
+    const int tx = per_row >= 256 ? 128 : pick_threads(per_row);
+    const dim3 grid1(T, ceil_div_host(per_row, tx)), grid2((T + 1) / 2, ceil_div_host(per_row, tx));
+    if ((long long)T * per_row >= 2 * 148 * 2048ll)
+      dib_launch(silu_mul_vec_kernel<__nv_bfloat16, 2>, grid2, dim3(tx), 0, st,
+                 (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I);
+    else
+      dib_launch(silu_mul_vec_kernel<__nv_bfloat16, 1>, grid1, dim3(tx), 0, st,
+                 (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, T, I);
     DIB_CHECK_LAUNCH();
     return DIB_OK;
   }
-  if (aligned && dtype == 0 && I % 4 == 0) {
-    const long long vecs = total / 4;
-    dib_launch(silu_mul_vec_kernel<float>, dim3(ceil_div_host(vecs, th)), dim3(th), 0, st, (const float*)gu,
-                                                                      (float*)out, vecs, I);
+  if (aligned && dtype == 0 && I % 4 == 0 && I / 4 <= 65535 * 32) {
+    const int per_row = I / 4;
+    const int tx = per_row >= 256 ? 128 : pick_threads(per_row);
+    dib_launch(silu_mul_vec_kernel<float, 1>, dim3(T, ceil_div_host(per_row, tx)), dim3(tx), 0, st,
+               (const float*)gu, (float*)out, T, I);
     DIB_CHECK_LAUNCH();
     return DIB_OK;
   }

@@ -258,7 +258,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         }
         g = round_to<__nv_bfloat16>(g);
         u = round_to<__nv_bfloat16>(u);
-        Elem<OutT>::store(out + (size_t)(m0 + col) * N + n0 + p, g / (1.0f + expf(-g)) * u);
+        Elem<OutT>::store(out + (size_t)(m0 + col) * N + n0 + p, silu_gate<OutT>(g, u));
       }
     } else {
       const int per = (BM + splits - 1) / splits;
@@ -297,7 +297,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           if (m >= M) break;
           const float g = round_to<__nv_bfloat16>(__uint_as_float(r[j]));
           const float u = round_to<__nv_bfloat16>(ex[pr * 17 + j]);
-          Elem<OutT>::store(out + (size_t)m * N + n0 + pr, g / (1.0f + expf(-g)) * u);
+          Elem<OutT>::store(out + (size_t)m * N + n0 + pr, silu_gate<OutT>(g, u));
         }
       }
       __syncthreads();
