@@ -370,25 +370,44 @@ qk_norm_rope_cache_rows128_kernel(
   pdl_prologue();
   constexpr int D = 128;
   const int heads = Hq + 2 * Hkv;
-  const long long total = (long long)T_tokens * heads;
+  const int total = T_tokens * heads;            // the launcher keeps this below 2^31
   const int l = threadIdx.x & 7;
-  const long long group = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3;
-  const long long row0 = group * ROWS;
+  const int group = (int)(((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 3);
+  const int row0 = group * ROWS;
   const unsigned mask = 0xffu << (threadIdx.x & 24);   // the eight lanes of this group
 
+  // Three rounds of loads, each issued for all ROWS rows before anything waits for them:
+  // the row itself with its token's position and slot; the rotation table's row; then
+  // the arithmetic and the stores.
   uint4 lo[ROWS], hi[ROWS];
-  int tok[ROWS], head[ROWS];
+  int tok[ROWS], head[ROWS], pos[ROWS], slot[ROWS];
   bool act[ROWS];
 #pragma unroll
   for (int it = 0; it < ROWS; ++it) {
-    const long long row = row0 + it;
+    const int row = row0 + it;
     act[it] = row < total;
-    tok[it] = act[it] ? (int)(row / heads) : 0;
-    head[it] = act[it] ? (int)(row % heads) : 0;
+    tok[it] = act[it] ? row / heads : 0;
+    head[it] = act[it] ? row - tok[it] * heads : 0;
+    pos[it] = 0;
+    slot[it] = -1;
     if (act[it]) {
       const __nv_bfloat16* src = qkv + ((size_t)tok[it] * heads + head[it]) * D + l * 8;
       lo[it] = *reinterpret_cast<const uint4*>(src);
       hi[it] = *reinterpret_cast<const uint4*>(src + 64);
+      if (head[it] < Hq + Hkv && cos_sin != nullptr) pos[it] = positions[tok[it]];
+      if (head[it] >= Hq && kv_cache != nullptr) slot[it] = slot_mapping[tok[it]];
+    }
+  }
+  float4 c0[ROWS], c1[ROWS], s0[ROWS], s1[ROWS];
+#pragma unroll
+  for (int it = 0; it < ROWS; ++it) {
+    if (act[it] && head[it] < Hq + Hkv && cos_sin != nullptr) {
+      const int p = pos[it] < 0 ? 0 : (pos[it] >= max_pos ? max_pos - 1 : pos[it]);
+      const float* tab = cos_sin + (size_t)p * D + l * 8;
+      c0[it] = *reinterpret_cast<const float4*>(tab);
+      c1[it] = *reinterpret_cast<const float4*>(tab + 4);
+      s0[it] = *reinterpret_cast<const float4*>(tab + 64);
+      s1[it] = *reinterpret_cast<const float4*>(tab + 68);
     }
   }
 #pragma unroll
@@ -400,12 +419,12 @@ qk_norm_rope_cache_rows128_kernel(
     if (is_q) {
       dst = q_out + ((size_t)tok[it] * Hq + head[it]) * D;
     } else {
-      const int slot = kv_cache != nullptr ? slot_mapping[tok[it]] : -1;
-      if (slot < 0) continue;
-      const long long page = slot / page_size;
+      if (slot[it] < 0) continue;
+      const int page = slot[it] / page_size;
       if (page >= num_pages) continue;
       const int h = is_k ? head[it] - Hq : head[it] - Hq - Hkv;
-      dst = kv_cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * Hkv + h) * page_size + slot % page_size) * D;
+      dst = kv_cache + ((((size_t)page * 2 + (is_k ? 0 : 1)) * Hkv + h) * page_size +
+                        (slot[it] - page * page_size)) * D;
     }
     if (is_q || is_k) {
       float a[8], b[8];   // elements 8l.. and 64+8l..
@@ -441,15 +460,8 @@ qk_norm_rope_cache_rows128_kernel(
         }
       }
       if (cos_sin != nullptr) {
-        int p = positions[tok[it]];
-        p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
-        const float* tab = cos_sin + (size_t)p * D + l * 8;
-        const float4 c0 = *reinterpret_cast<const float4*>(tab);
-        const float4 c1 = *reinterpret_cast<const float4*>(tab + 4);
-        const float4 s0 = *reinterpret_cast<const float4*>(tab + 64);
-        const float4 s1 = *reinterpret_cast<const float4*>(tab + 68);
-        const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-        const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+        const float c[8] = {c0[it].x, c0[it].y, c0[it].z, c0[it].w, c1[it].x, c1[it].y, c1[it].z, c1[it].w};
+        const float sn[8] = {s0[it].x, s0[it].y, s0[it].z, s0[it].w, s1[it].x, s1[it].y, s1[it].z, s1[it].w};
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const float x = a[k], y = b[k];
@@ -814,12 +826,13 @@ int dib_qk_norm_rope_cache_split(const void* qkv, const float* parts, int S, lon
                        reinterpret_cast<uintptr_t>(q_out) % 16 == 0 &&
                        reinterpret_cast<uintptr_t>(kv_cache) % 16 == 0;
   if (aligned && parts == nullptr && dtype == 1 && D == 128 && (cos_sin == nullptr || rotary_dim == D) &&
-      items >= 2048 && getenv("DIB200_QK_ROWS_OFF") == nullptr &&
+      items >= 2048 && items < (1ll << 31) - 4096 && getenv("DIB200_QK_ROWS_OFF") == nullptr &&
       reinterpret_cast<uintptr_t>(q_norm_w) % 16 == 0 &&
       reinterpret_cast<uintptr_t>(k_norm_w) % 16 == 0 && reinterpret_cast<uintptr_t>(cos_sin) % 16 == 0) {
-    constexpr int ROWS = 2;
-    const long long groups = (items + ROWS - 1) / ROWS;
-    dib_launch(qk_norm_rope_cache_rows128_kernel<ROWS>, dim3(ceil_div_host(groups * 8, 256)), dim3(256),
+    // one row per group of eight lanes: with two, the registers of the second cost more
+    // threads per multiprocessor than its loads in flight gain (12.2 us against 9.7 us for
+    // 2,048 tokens of 16 + 2 x 8 heads)
+    dib_launch(qk_norm_rope_cache_rows128_kernel<1>, dim3(ceil_div_host(items * 8, 256)), dim3(256),
                0, st, (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kv_cache,
                q_norm_w, k_norm_w, eps, cos_sin, max_pos, positions, slot_mapping, T, Hq, Hkv,
                page_size, num_pages);
