@@ -350,7 +350,7 @@ decode_attention_stage1_tma_kernel(const __grid_constant__ CUtensorMap map,
   const int row0 = (((page * 2 + kv) * Hkv) + kvh) * page_size;
   __nv_bfloat16* dst = (kv ? sV : sK) + half * (DEC_SPLIT * 64) + pi * page_size * 64;
   if (issuer && early) tma_load_2d(dst, &map, half * 64, row0, &bars[kv]);
-  pdl_wait();
+  pdl_wait(q);
   if (issuer && !early) tma_load_2d(dst, &map, half * 64, row0, &bars[kv]);
 
   bool dead = false;
@@ -504,7 +504,7 @@ decode_attention_stage1_pipe_kernel(const __grid_constant__ CUtensorMap map,
 #pragma unroll
     for (int j = 0; j < FIRST; ++j)
       if (j < n) send(j, first_it[j], first_page[j], 0);
-    pdl_wait();
+    pdl_wait(q);
 #pragma unroll
     for (int j = 0; j < FIRST; ++j)
       if (j < n) send(j, first_it[j], first_page[j], 1);
@@ -542,7 +542,7 @@ decode_attention_stage1_pipe_kernel(const __grid_constant__ CUtensorMap map,
 
   // ---------------- consumers: group g takes this CTA's splits g, g + GROUPS, ...
   const int g = warp >> 2, tid = threadIdx.x & (DEC_THREADS - 1);
-  pdl_wait();   // transitively, everything this kernel writes over has been read
+  pdl_wait(q);   // transitively, everything this kernel writes over has been read
   for (int n = g;; n += GROUPS) {
     const int ks = n % KS, vs = n % VS;
     DIB_CLOCK(n / GROUPS, 0);

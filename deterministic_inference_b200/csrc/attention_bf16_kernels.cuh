@@ -236,7 +236,7 @@ extend_attention_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __re
                         const int* __restrict__ cu_q_lens, const int* __restrict__ seq_lens,
                         const int* __restrict__ tile_seq, const int* __restrict__ tile_start,
                         int Hq, int Hkv, int page_size, float scale, int window) {
-  pdl_prologue();
+  pdl_prologue(q, cache);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* sK0 = sQ + EXT_M * (D + PAD);
@@ -358,7 +358,7 @@ decode_attention_stage1_kernel(const __nv_bfloat16* __restrict__ q,
                                const int* __restrict__ seq_lens, float* __restrict__ part_o,
                                float* __restrict__ part_lse, int max_splits, int Hq, int Hkv,
                                int page_size, float scale, int window) {
-  pdl_prologue();
+  pdl_prologue(q, cache);
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(smem_raw);
   __nv_bfloat16* sV = sK + DEC_SPLIT * (D + PAD);
@@ -494,29 +494,52 @@ decode_attention_stage1_kernel(const __nv_bfloat16* __restrict__ q,
   }
 }
 
-// Stage 2: merge the splits of one (sequence, head) in index order.
+// Stage 2: merge the splits of one (sequence, head) in index order.  The partial results
+// of the first 16 splits are requested before the sequence's length is known (what lies
+// beyond its last split is read but not used), so the kernel waits for memory once.
 __global__ void decode_attention_stage2_kernel(const float* __restrict__ part_o,
                                                const float* __restrict__ part_lse,
                                                const int* __restrict__ seq_lens,
                                                __nv_bfloat16* __restrict__ out, int max_splits,
                                                int Hq, int D, int window) {
-  pdl_prologue();
+  pdl_prologue(part_o, part_lse);
+  constexpr int EARLY = 16;
   const int b = blockIdx.x, h = blockIdx.y;
+  const size_t row = ((size_t)b * Hq + h) * max_splits;
   const int kv_len = seq_lens[b];
+  float lse_r[EARLY], o_r[EARLY];
+#pragma unroll
+  for (int j = 0; j < EARLY; ++j) lse_r[j] = j < max_splits ? part_lse[row + j] : NEG_BIG;
+#pragma unroll
+  for (int j = 0; j < EARLY; ++j)
+    o_r[j] = (j < max_splits && (int)threadIdx.x < D) ? part_o[(row + j) * D + threadIdx.x] : 0.f;
   const int pos = kv_len - 1;
   const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int s0 = first_key / DEC_SPLIT, s1 = pos / DEC_SPLIT;
-  const size_t row = ((size_t)b * Hq + h) * max_splits;
   float M = NEG_BIG;
-  for (int s = s0; s <= s1; ++s) M = fmaxf(M, part_lse[row + s]);
+#pragma unroll
+  for (int j = 0; j < EARLY; ++j)
+    if (j >= s0 && j <= s1) M = fmaxf(M, lse_r[j]);
+  for (int s = max(s0, EARLY); s <= s1; ++s) M = fmaxf(M, part_lse[row + s]);
+  bool first = true;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float acc = 0.f, den = 0.f;
-    for (int s = s0; s <= s1; ++s) {
+#pragma unroll
+    for (int j = 0; j < EARLY; ++j) {
+      if (j >= s0 && j <= s1) {
+        const float o = first ? o_r[j] : part_o[(row + j) * D + d];
+        const float w = expf(lse_r[j] - M);
+        acc += w * o;
+        den += w;
+      }
+    }
+    for (int s = max(s0, EARLY); s <= s1; ++s) {
       const float w = expf(part_lse[row + s] - M);
       acc += w * part_o[(row + s) * D + d];
       den += w;
     }
     out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(acc / den);
+    first = false;
   }
 }
 

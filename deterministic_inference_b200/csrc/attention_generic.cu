@@ -30,7 +30,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out,
                                const int* __restrict__ token_seq,
                                const int* __restrict__ positions, int T_tokens, int Hq, int Hkv,
                                int D, int page_size, float scale, int window) {
-  pdl_prologue();
+  pdl_prologue(q, kv_cache, block_table, token_seq, positions);
   __shared__ float sq[WARPS][MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp;

@@ -170,7 +170,7 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
                            const int* __restrict__ cu_q_lens, const int* __restrict__ seq_lens,
                            const int* __restrict__ tile_seq, const int* __restrict__ tile_start,
                            int Hq, int Hkv, int page_size, float scale, int window) {
-  pdl_prologue();
+  pdl_prologue(q);
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
@@ -503,7 +503,7 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   if (threadIdx.x == 0) DIB_PCLOCK(63, 0);
   DIB_PTIME(0);
   DIB_PTIME(2);
-  pdl_prologue();
+  pdl_prologue(q);
   if (threadIdx.x == 0) DIB_PCLOCK(63, 1);
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -988,7 +988,7 @@ extend_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
                               const int* __restrict__ seq_lens, const int* __restrict__ token_seq,
                               int t_first, int num_tokens, int Hq, int Hkv, int max_chunks,
                               int chunk_tiles, int window) {
-  pdl_prologue();
+  pdl_prologue(part_o, part_ml);
   const int lane = threadIdx.x & 31;
   const int idx = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (idx >= num_tokens) return;

@@ -98,11 +98,22 @@ static inline int ceil_div_host(long long a, long long b) { return (int)((a + b 
 // are read before the wait.  In a chain A, B, C each kernel waits for the one before
 // it, which itself only finished after its own wait, so C also sees A complete.  Set
 // DIB200_PDL=0 to launch the plain way.
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+//
+// The wait takes the pointers through which the kernel reads what its predecessor
+// wrote, and hands them back as values the compiler knows nothing about.  Without
+// that, a load through a `const T* __restrict__` parameter counts as a load of data
+// that never changes while the kernel runs, and the compiler may move it above the
+// wait (it did, in the kernel that merges the splits of decode attention: the partial
+// results were read before the kernel that writes them had finished).
+template <typename P> __device__ __forceinline__ void pdl_fresh(P& p) { asm volatile("" : "+l"(p)); }
+template <typename... P> __device__ __forceinline__ void pdl_wait(P&... p) {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  (pdl_fresh(p), ...);
+}
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::); }
-__device__ __forceinline__ void pdl_prologue() {
+template <typename... P> __device__ __forceinline__ void pdl_prologue(P&... p) {
   pdl_trigger();
-  pdl_wait();
+  pdl_wait(p...);
 }
 
 static inline bool dib_pdl_enabled() {

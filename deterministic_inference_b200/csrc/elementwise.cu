@@ -18,7 +18,7 @@ namespace {
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  T* __restrict__ out, int H, int V) {
-  pdl_prologue();
+  pdl_prologue(ids);
   const int t = blockIdx.x;
   const int id = ids[t];
   const bool ok = id >= 0 && id < V;
@@ -34,7 +34,7 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
 // of 16; an index outside [0, rows_in) gives zeros if zero_bad, else is clamped).
 __global__ void copy_rows16_kernel(const uint4* __restrict__ src, const int* __restrict__ idx,
                                    uint4* __restrict__ out, int vecs, int rows_in, int zero_bad) {
-  pdl_prologue();
+  pdl_prologue(src, idx);
   const int r = blockIdx.x;
   int id = idx[r];
   const bool bad = id < 0 || id >= rows_in;
@@ -53,7 +53,7 @@ template <typename T, bool ADD>
 __global__ void rms_norm_kernel(T* __restrict__ x, T* __restrict__ residual,
                                 const float* __restrict__ w, T* __restrict__ out,
                                 int H, float eps) {
-  pdl_prologue();
+  pdl_prologue(x, residual);
   extern __shared__ float row[];
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * H;
@@ -112,7 +112,7 @@ template <typename T, bool ADD, int ITERS>
 __global__ void rms_norm_vec_kernel(T* __restrict__ x, T* __restrict__ residual,
                                     const float* __restrict__ w, T* __restrict__ out, int H,
                                     float eps) {
-  pdl_prologue();
+  pdl_prologue(x, residual);
   constexpr int N = Vec<T>::N;
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * H;
@@ -169,7 +169,7 @@ __global__ void qk_norm_rope_cache_kernel(
     const float* __restrict__ cos_sin, int rotary_dim, int max_pos,
     const int* __restrict__ positions, const int* __restrict__ slot_mapping,
     int T_tokens, int Hq, int Hkv, int D, int page_size, long long num_pages) {
-  pdl_prologue();
+  pdl_prologue(qkv, positions, slot_mapping);
   extern __shared__ float smem[];
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -250,7 +250,7 @@ __global__ void qk_norm_rope_cache_vec_kernel(
     const float* __restrict__ cos_sin, int max_pos, const int* __restrict__ positions,
     const int* __restrict__ slot_mapping, int T_tokens, int Hq, int Hkv, int page_size,
     long long num_pages) {
-  pdl_prologue();
+  pdl_prologue(qkv, parts, positions, slot_mapping);
   constexpr int D = EPL * 32;
   const int warps_per_block = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -367,7 +367,7 @@ qk_norm_rope_cache_rows128_kernel(
     const float* __restrict__ k_norm_w, float eps, const float* __restrict__ cos_sin, int max_pos,
     const int* __restrict__ positions, const int* __restrict__ slot_mapping, int T_tokens, int Hq,
     int Hkv, int page_size, long long num_pages) {
-  pdl_prologue();
+  pdl_prologue(qkv, positions, slot_mapping);
   constexpr int D = 128;
   const int heads = Hq + 2 * Hkv;
   const int total = T_tokens * heads;            // the launcher keeps this below 2^31
@@ -489,7 +489,7 @@ __global__ void reshape_and_cache_kernel(const T* __restrict__ k, const T* __res
                                          T* __restrict__ kv_cache,
                                          const int* __restrict__ slot_mapping, int Hkv, int D,
                                          int page_size, long long num_pages) {
-  pdl_prologue();
+  pdl_prologue(k, v, slot_mapping);
   const int t = blockIdx.x;
   const int slot = slot_mapping[t];
   if (slot < 0) return;
@@ -510,7 +510,7 @@ __global__ void reshape_and_cache_kernel(const T* __restrict__ k, const T* __res
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total,
                                 int I) {
-  pdl_prologue();
+  pdl_prologue(gu);
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const long long t = idx / I;
@@ -525,7 +525,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ out, l
 template <typename T, int ROWS>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int T_rows,
                                     int I) {
-  pdl_prologue();
+  pdl_prologue(gu);
   constexpr int N = Vec<T>::N;
   const int i = (blockIdx.y * blockDim.x + threadIdx.x) * N;
   if (i >= I) return;
@@ -555,7 +555,7 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ ou
 template <typename T>
 __global__ void sum_split_kernel(const float* __restrict__ parts, T* __restrict__ out,
                                  long long total4, long long split_stride, int S) {
-  pdl_prologue();
+  pdl_prologue(parts);
   const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total4) return;
   float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -578,7 +578,7 @@ add_rms_norm_split_kernel(const float* __restrict__ parts, int S,
                                           long long split_stride, T* __restrict__ residual,
                                           const float* __restrict__ w, T* __restrict__ out, int H,
                                           float eps) {
-  pdl_prologue();
+  pdl_prologue(parts, residual);
   __shared__ float scratch[32];
   const size_t base = (size_t)blockIdx.x * H;
   float v[ITERS][4];
@@ -640,7 +640,7 @@ add_rms_norm_split_kernel(const float* __restrict__ parts, int S,
 template <typename T>
 __global__ void silu_mul_split_kernel(const float* __restrict__ parts, int S, long long split_stride,
                                       T* __restrict__ out, long long vecs, int I) {
-  pdl_prologue();
+  pdl_prologue(parts);
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= vecs) return;
   const int per_row = I / 4;
@@ -680,7 +680,7 @@ __global__ void silu_mul_split_kernel(const float* __restrict__ parts, int S, lo
 __global__ void patch_ids_kernel(int* __restrict__ ids, const int* __restrict__ dst,
                                  const int* __restrict__ src, const int* __restrict__ prev, int n,
                                  int num_ids, int num_prev) {
-  pdl_prologue();
+  pdl_prologue(dst, src, prev);
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const int d = dst[i], sidx = src[i];
@@ -691,7 +691,7 @@ __global__ void patch_ids_kernel(int* __restrict__ ids, const int* __restrict__ 
 template <typename T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ idx,
                                    T* __restrict__ out, int H, int T_rows) {
-  pdl_prologue();
+  pdl_prologue(x, idx);
   const int r = blockIdx.x;
   int src = idx[r];
   src = src < 0 ? 0 : (src >= T_rows ? T_rows - 1 : src);

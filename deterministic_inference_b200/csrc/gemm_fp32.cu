@@ -15,7 +15,7 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 __global__ void __launch_bounds__(256)
 gemm_fp32_kernel(const float* __restrict__ A, const float* __restrict__ W, float* __restrict__ C,
                  int M, int N, int K) {
-  pdl_prologue();
+  pdl_prologue(A);
   __shared__ float sA[BK][BM + 4];
   __shared__ float sW[BK][BN + 4];
   const int tid = threadIdx.x;

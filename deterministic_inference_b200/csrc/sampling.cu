@@ -56,7 +56,7 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 constexpr int INT_MAX_ = 0x7fffffff;
 
 __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V) {
-  pdl_prologue();
+  pdl_prologue(logits);
   __shared__ Best scratch[32];
   const float* row = logits + (size_t)blockIdx.x * V;
   Best b{-INFINITY, INT_MAX_};
@@ -75,7 +75,7 @@ constexpr int ARGMAX_CHUNK = 4096;
 
 __global__ void argmax_partial_kernel(const float* __restrict__ logits, float* __restrict__ pv,
                                       int* __restrict__ pi, int V, int chunks) {
-  pdl_prologue();
+  pdl_prologue(logits);
   __shared__ Best scratch[32];
   const int r = blockIdx.y, c = blockIdx.x;
   const float* row = logits + (size_t)r * V;
@@ -91,7 +91,7 @@ __global__ void argmax_partial_kernel(const float* __restrict__ logits, float* _
 
 __global__ void argmax_final_kernel(const float* __restrict__ pv, const int* __restrict__ pi,
                                     int* __restrict__ out, int chunks) {
-  pdl_prologue();
+  pdl_prologue(pv, pi);
   __shared__ Best scratch[32];
   const int r = blockIdx.x;
   Best b{-INFINITY, INT_MAX_};
@@ -116,7 +116,7 @@ __global__ void gumbel_sample_kernel(const float* __restrict__ logits,
                                      const long long* __restrict__ sample_pos,
                                      const unsigned char* __restrict__ keep,
                                      int* __restrict__ out, int V) {
-  pdl_prologue();
+  pdl_prologue(logits, temperatures, seeds, sample_pos, keep);
   __shared__ Best bscratch[32];
   __shared__ float fscratch[32];
   const int r = blockIdx.x;
@@ -158,7 +158,7 @@ __global__ void gumbel_stats_kernel(const float* __restrict__ logits,
                                     unsigned* __restrict__ hist_cnt,
                                     unsigned long long* __restrict__ hist_mass, int R, int V,
                                     int chunks) {
-  pdl_prologue();
+  pdl_prologue(logits, temperatures);
   __shared__ float fscratch[32];
   const int r = blockIdx.y, c = blockIdx.x;
   // the row's top-k / top-p histograms (4 passes x 256 bins) start from zero: the blocks
@@ -291,7 +291,7 @@ filter_histogram_kernel(const float* __restrict__ logits, const float* __restric
                         const float* __restrict__ cmax, const float* __restrict__ csum,
                         unsigned* __restrict__ hist_cnt, unsigned long long* __restrict__ hist_mass,
                         int pass, int R, int V, int chunks) {
-  pdl_prologue();
+  pdl_prologue(logits, temperatures, top_ks, top_ps, cmax, csum);
   __shared__ unsigned s_cnt[256];
   __shared__ unsigned long long s_mass[256];
   __shared__ unsigned s_prefix;
@@ -362,7 +362,7 @@ __global__ void gumbel_pick_kernel(const float* __restrict__ logits,
                                    const float* __restrict__ cmax, const float* __restrict__ csum,
                                    float* __restrict__ pv, int* __restrict__ pi, int R, int V,
                                    int chunks) {
-  pdl_prologue();
+  pdl_prologue(logits, temperatures, seeds, sample_pos, keep, top_ks, top_ps, hist_cnt, hist_mass);
   __shared__ Best bscratch[32];
   __shared__ unsigned s_thresh;
   const int r = blockIdx.y, c = blockIdx.x;

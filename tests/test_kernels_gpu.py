@@ -359,6 +359,33 @@ def test_decode_attention_pipelined_walk_gives_the_same_bits(monkeypatch, hq, hk
         torch.testing.assert_close(outs["1"][s:s + 1].float(), want, **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("tma", ["0", "1"])
+def test_decode_attention_reads_its_partial_results_after_they_are_written(monkeypatch, tma):
+    """The kernel that merges the splits starts beside the kernel that writes them
+    (programmatic dependent launch) and must not read a partial result before its wait:
+    the scratch is filled with NaN, huge values and plain numbers before each call, and
+    every call gives the bits of the first."""
+    monkeypatch.setenv("DIB200_DECODE_TMA", tma)
+    hq, hkv, d, page = 16, 8, 128, 16
+    lens = [513, 2, 129, 1, 33, 257, 700, 128]
+    case = PagedCase(lens, hkv, d, page, torch.bfloat16, seed=3)
+    meta = case.meta(list(range(len(lens))), [(n - 1, 1) for n in lens])
+    g = torch.Generator().manual_seed(4)
+    q = torch.randn(len(lens), hq, d, generator=g).to(device="cuda", dtype=torch.bfloat16)
+    ref = ops().paged_attention(q, case.cache, meta, d ** -0.5, None).clone()
+    scratch = [v for k, v in meta.scratch.items() if k[0] == "decode_ws"]
+    assert len(scratch) == 1
+    for rep in range(4):
+        for fill in (float("nan"), 1e30, -1e30, 0.0, 123.0):
+            for w in scratch[0]:
+                w.fill_(fill)
+            out = ops().paged_attention(q, case.cache, meta, d ** -0.5, None)
+            assert torch.equal(out, ref), (rep, fill)
+    for s_ in (0, 1, 6):
+        want = dense_reference(q[s_:s_ + 1], case.k[s_], case.v[s_], d ** -0.5, [lens[s_] - 1], None)
+        torch.testing.assert_close(ref[s_:s_ + 1].float(), want, **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("window", [1, 7, 16, 24, 33, 500])
 def test_paged_attention_window_edge(dtype, window):
