@@ -63,21 +63,25 @@ def extend_chunk_units(q_lens: list, kv_lens: list, first_seq: int, tokens_per_t
 
 
 def extend_tile_pairs(q_lens: list, kv_lens: list, first_seq: int, tokens_per_tile: int,
-                      window: int):
+                      window: int, alone: bool = False):
     """(sequence, first token of A, first token of B or -1) for the CTAs of the kernel
     that takes two query tiles of a sequence at once.  Under a causal mask the k-th tile
     of a prompt needs about k key tiles more than the first, so the k-th tile is paired
     with the k-th from the end: every pair then needs the same number of key-tile products,
     and the short tile's key tiles are among the long one's.  With a window every tile
     needs about as many key tiles as the next, and neighbours share most of them: they
-    are paired.  The entries are sorted by the key tiles they need, the longest last (the
-    kernel takes its list from the end)."""
+    are paired.  ``alone``: every tile gets a CTA of its own (B = -1), for steps with so few
+    tiles that pairs would leave most of the GPU idle; the kernel then keeps two key tiles
+    of that one query tile in flight.  The entries are sorted by the key tiles they need,
+    the longest last (the kernel takes its list from the end)."""
     units = []
     for s in range(first_seq, len(q_lens)):
         prefix = kv_lens[s] - q_lens[s]
         starts = list(range(0, q_lens[s], tokens_per_tile))
         n = len(starts)
-        if window > 0:
+        if alone:
+            pairs = [(a, -1) for a in starts]
+        elif window > 0:
             pairs = [(starts[i], starts[i + 1] if i + 1 < n else -1) for i in range(0, n, 2)]
         else:
             pairs = [(starts[i], starts[n - 1 - i] if n - 1 - i > i else -1) for i in range((n + 1) // 2)]
@@ -133,7 +137,11 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
         tiles = meta.scratch.get(("extend_tiles", tpt, pair, window > 0))
         if tiles is None:
             if pair:
-                seqs, starts, starts_b = extend_tile_pairs(meta.q_lens, meta.kv_lens, nd, tpt, window)
+                # pairs while they give at least a CTA for every second SM, else a CTA per tile
+                n_tiles = sum(-(-n // tpt) for n in meta.q_lens[nd:])
+                alone = os.environ.get("DIB200_PREFILL_PAIR", "auto")
+                alone = alone == "0" or (alone != "1" and (n_tiles + 1) // 2 * hkv * 2 <= _sm_count(q.device))
+                seqs, starts, starts_b = extend_tile_pairs(meta.q_lens, meta.kv_lens, nd, tpt, window, alone)
             else:
                 seqs, starts = extend_tiles(meta.q_lens, nd, tpt)
                 starts_b = starts
