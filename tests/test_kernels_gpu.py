@@ -427,14 +427,18 @@ def test_paged_attention_far_key_stands_out(dtype):
                                        atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("mode", ["0", "1", "2"])
+@pytest.mark.parametrize("mode", ["0", "1", "2", "2-pairs", "2-alone"])
 @pytest.mark.parametrize("hq,hkv,page,window", [(16, 8, 16, None), (32, 8, 16, 300), (8, 8, 32, None),
                                                 (16, 1, 128, 200), (64, 8, 8, None)])
 def test_prefill_attention_head_size_128_kernels(monkeypatch, mode, hq, hkv, page, window):
     """The three bfloat16 prompt kernels for heads of 128 (mma.sync; tcgen05 with one
-    query tile per CTA; tcgen05 with two) on prompts that span many key tiles: whole,
-    behind a cached prefix, ending one token after a tile edge; group sizes 1 to 16."""
-    monkeypatch.setenv("DIB200_PREFILL_TC", mode)
+    query tile per CTA; tcgen05 with two, as the step's size decides, with tiles paired
+    from both ends of a prompt, and with a CTA for every tile) on prompts that span many
+    key tiles: whole, behind a cached prefix, ending one token after a tile edge; group
+    sizes 1 to 16."""
+    monkeypatch.setenv("DIB200_PREFILL_TC", mode[0])
+    if len(mode) > 1:
+        monkeypatch.setenv("DIB200_PREFILL_PAIR", "1" if mode.endswith("pairs") else "0")
     d = 128
     lens = [700, 300, 129, 257]
     cuts = [(0, 700), (100, 200), (1, 128), (0, 257)]
