@@ -657,9 +657,7 @@ int launch_decode_tma(const void* q, void* out, const void* cache, long long num
                page_size, scale, window);
     DIB_CHECK_LAUNCH();
   }
-  const int th = D < 32 ? 32 : (D + 31) / 32 * 32;
-  dib_launch(decode_attention_stage2_kernel, dim3(num_seqs, Hq), dim3(th), 0, st, part_o, part_lse,
-             seq_lens, (__nv_bfloat16*)out, max_splits, Hq, D, window);
+  launch_decode_merge(part_o, part_lse, seq_lens, out, num_seqs, max_splits, Hq, D, window, st);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }

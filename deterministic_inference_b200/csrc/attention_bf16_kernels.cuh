@@ -543,6 +543,99 @@ __global__ void decode_attention_stage2_kernel(const float* __restrict__ part_o,
   }
 }
 
+// The same for sequences of more than 16 splits.  The splits are taken in chunks of 16;
+// chunk c belongs to group c % 8 of the block's eight groups of D threads, a group adds
+// its chunks in rising order (each chunk's loads requested together), and the groups'
+// sums are added in group order.  A sequence of at most 16 splits is summed by group 0
+// alone, in the order of the kernel above: its bits do not depend on whether a longer
+// sequence in the batch brought it here.  The grouping depends on nothing but the
+// sequence's own length.
+constexpr int MERGE_GROUPS = 8;
+__global__ void __launch_bounds__(1024)
+decode_attention_stage2_wide_kernel(const float* __restrict__ part_o,
+                                    const float* __restrict__ part_lse,
+                                    const int* __restrict__ seq_lens,
+                                    __nv_bfloat16* __restrict__ out, int max_splits, int Hq, int D,
+                                    int window) {
+  pdl_prologue(part_o, part_lse);
+  constexpr int CH = 16;
+  __shared__ float s_acc[MERGE_GROUPS][128];
+  __shared__ float s_den[MERGE_GROUPS];
+  __shared__ float s_max[32];
+  const int b = blockIdx.x, h = blockIdx.y;
+  const int d = threadIdx.x, g = threadIdx.y;
+  const int tid = g * blockDim.x + d, nthreads = blockDim.x * MERGE_GROUPS;
+  const size_t row = ((size_t)b * Hq + h) * max_splits;
+  const int kv_len = seq_lens[b];
+  const int pos = kv_len - 1;
+  const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int s0 = first_key / DEC_SPLIT, s1 = pos / DEC_SPLIT;
+  // the largest lse of the sequence's splits (a maximum does not depend on the order)
+  float m = NEG_BIG;
+  for (int s = s0 + tid; s <= s1; s += nthreads) m = fmaxf(m, part_lse[row + s]);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((tid & 31) == 0) s_max[tid >> 5] = m;
+  __syncthreads();
+  float M = NEG_BIG;
+  for (int w = 0; w < (nthreads + 31) / 32; ++w) M = fmaxf(M, s_max[w]);
+
+  float acc = 0.f, den = 0.f;
+  const int c0 = s0 / CH, c1 = s1 / CH;
+  const int c_first = c0 + ((g - c0 % MERGE_GROUPS) + MERGE_GROUPS) % MERGE_GROUPS;   // first chunk >= c0 of group g
+  for (int c = c_first; c <= c1; c += MERGE_GROUPS) {
+    float lse_r[CH], o_r[CH];
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+      const int s = c * CH + j;
+      const bool in = s >= s0 && s <= s1;
+      lse_r[j] = in ? part_lse[row + s] : NEG_BIG;
+      o_r[j] = (in && d < D) ? part_o[(row + s) * D + d] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < CH; ++j) {
+      const int s = c * CH + j;
+      if (s >= s0 && s <= s1) {
+        const float w = expf(lse_r[j] - M);
+        acc += w * o_r[j];
+        den += w;
+      }
+    }
+  }
+  const bool one_group = c0 == c1;     // uniform over the block
+  if (one_group) {
+    if (g == c0 % MERGE_GROUPS && d < D)
+      out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(acc / den);
+    return;
+  }
+  if (d < D) s_acc[g][d] = acc;
+  if (d == 0) s_den[g] = den;
+  __syncthreads();
+  if (g == 0 && d < D) {
+    float a = 0.f, dn = 0.f;
+#pragma unroll
+    for (int k = 0; k < MERGE_GROUPS; ++k) {
+      a += s_acc[k][d];
+      dn += s_den[k];
+    }
+    out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(a / dn);
+  }
+}
+
+// Stage 2 of the split-KV decode attention: the kernel for at most 16 splits, or the
+// wide one.
+static inline void launch_decode_merge(const float* part_o, const float* part_lse, const int* seq_lens,
+                                       void* out, int num_seqs, int max_splits, int Hq, int D,
+                                       int window, cudaStream_t st) {
+  const int th = D < 32 ? 32 : (D + 31) / 32 * 32;
+  if (max_splits > 16 && th <= 128)
+    dib_launch(decode_attention_stage2_wide_kernel, dim3(num_seqs, Hq), dim3(th, MERGE_GROUPS), 0, st,
+               part_o, part_lse, seq_lens, (__nv_bfloat16*)out, max_splits, Hq, D, window);
+  else
+    dib_launch(decode_attention_stage2_kernel, dim3(num_seqs, Hq), dim3(th), 0, st, part_o, part_lse,
+               seq_lens, (__nv_bfloat16*)out, max_splits, Hq, D, window);
+}
+
 template <int D>
 int launch_extend(const void* q, void* out, const void* cache, const int* bt, int max_blocks,
                   const int* cu_q_lens, const int* seq_lens, const int* tile_seq,
@@ -586,11 +679,7 @@ int launch_decode(const void* q, void* out, const void* cache, const int* bt, in
                                         max_blocks, seq_lens, part_o, part_lse, max_splits, Hq, Hkv,
                                         page_size, scale, window);
   DIB_CHECK_LAUNCH();
-  dim3 grid2(num_seqs, Hq);
-  const int th = D < 32 ? 32 : (D + 31) / 32 * 32;
-  dib_launch(decode_attention_stage2_kernel, dim3(grid2), dim3(th), 0, st, part_o, part_lse, seq_lens,
-                                                       (__nv_bfloat16*)out, max_splits, Hq, D,
-                                                       window);
+  launch_decode_merge(part_o, part_lse, seq_lens, out, num_seqs, max_splits, Hq, D, window, st);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }

@@ -359,6 +359,35 @@ def test_decode_attention_pipelined_walk_gives_the_same_bits(monkeypatch, hq, hk
         torch.testing.assert_close(outs["1"][s:s + 1].float(), want, **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("hq,hkv,d,page,window", [(16, 8, 128, 16, None), (8, 2, 128, 32, 2500), (6, 3, 64, 16, None)])
+def test_decode_attention_long_sequences_beside_short_ones(monkeypatch, hq, hkv, d, page, window):
+    """Sequences of more than 16 splits of 128 keys take the merge kernel that adds chunks
+    of 16 splits in eight groups; a short sequence beside them keeps the bits it has
+    alone (the order of its sum depends on its own length only), both launch forms of
+    stage 1 agree in every bit, and all agree with the dense reference."""
+    lens = [5000, 300, 2049, 2048, 129, 4097]
+    case = PagedCase(lens, hkv, d, page, torch.bfloat16, seed=61)
+    g = torch.Generator().manual_seed(62)
+    q = torch.randn(len(lens), hq, d, generator=g).to(device="cuda", dtype=torch.bfloat16)
+    seqs = list(range(len(lens)))
+    outs = {}
+    for mode in ("0", "1"):
+        monkeypatch.setenv("DIB200_DECODE_PIPE", mode)
+        outs[mode] = ops().paged_attention(q, case.cache, case.meta(seqs, [(n - 1, 1) for n in lens]),
+                                           d ** -0.5, window).clone()
+    assert ops()._lib("attention_bf16").dib_attention_bf16_status() == 0
+    assert torch.equal(outs["0"], outs["1"])
+    monkeypatch.delenv("DIB200_DECODE_PIPE")
+    for s_ in seqs:
+        want = dense_reference(q[s_:s_ + 1], case.k[s_], case.v[s_], d ** -0.5, [lens[s_] - 1], window)
+        torch.testing.assert_close(outs["0"][s_:s_ + 1].float(), want, **tol(torch.bfloat16))
+    # the short ones alone (at most 16 splits in the batch: the other merge kernel)
+    short = [1, 3, 4]
+    alone = ops().paged_attention(q[short].contiguous(), case.cache,
+                                  case.meta(short, [(lens[i] - 1, 1) for i in short]), d ** -0.5, window)
+    assert torch.equal(alone, outs["0"][short])
+
+
 @pytest.mark.parametrize("tma", ["0", "1"])
 def test_decode_attention_reads_its_partial_results_after_they_are_written(monkeypatch, tma):
     """The kernel that merges the splits starts beside the kernel that writes them
