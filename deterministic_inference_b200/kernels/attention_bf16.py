@@ -63,14 +63,19 @@ def extend_chunk_units(q_lens: list, kv_lens: list, first_seq: int, tokens_per_t
 
 
 def extend_tile_pairs(q_lens: list, kv_lens: list, first_seq: int, tokens_per_tile: int,
-                      window: int, alone: bool = False):
+                      window: int, alone: bool = False, neighbours: bool = False):
     """(sequence, first token of A, first token of B or -1) for the CTAs of the kernel
     that takes two query tiles of a sequence at once.  Under a causal mask the k-th tile
     of a prompt needs about k key tiles more than the first, so the k-th tile is paired
     with the k-th from the end: every pair then needs the same number of key-tile products,
     and the short tile's key tiles are among the long one's.  With a window every tile
     needs about as many key tiles as the next, and neighbours share most of them: they
-    are paired.  ``alone``: every tile gets a CTA of its own (B = -1), for steps with so few
+    are paired.  ``neighbours``: neighbours are paired under a causal mask too, for steps
+    with more CTAs than SMs: the GPU then evens the CTAs out by itself (the longest come
+    first), and neighbours read each key tile once for both, where a pair from both ends
+    reads the long tile's keys for one tile most of the time (one layer of 16 + 8 heads:
+    3,072 tokens 66 us against 81 us, 8,192 tokens 290 us against 347 us; but 2,048 tokens,
+    one CTA per SM at most, 47 us against 36 us).  ``alone``: every tile gets a CTA of its own (B = -1), for steps with so few
     tiles that pairs would leave most of the GPU idle; the kernel then keeps two key tiles
     of that one query tile in flight.  The entries are sorted by the key tiles they need,
     the longest last (the kernel takes its list from the end)."""
@@ -81,7 +86,7 @@ def extend_tile_pairs(q_lens: list, kv_lens: list, first_seq: int, tokens_per_ti
         n = len(starts)
         if alone:
             pairs = [(a, -1) for a in starts]
-        elif window > 0:
+        elif window > 0 or neighbours:
             pairs = [(starts[i], starts[i + 1] if i + 1 < n else -1) for i in range(0, n, 2)]
         else:
             pairs = [(starts[i], starts[n - 1 - i] if n - 1 - i > i else -1) for i in range((n + 1) // 2)]
@@ -138,10 +143,14 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
         if tiles is None:
             if pair:
                 # pairs while they give at least a CTA for every second SM, else a CTA per tile
+                # (DIB200_PREFILL_PAIR=0/1/2 forces: alone, from both ends, neighbours)
                 n_tiles = sum(-(-n // tpt) for n in meta.q_lens[nd:])
-                alone = os.environ.get("DIB200_PREFILL_PAIR", "auto")
-                alone = alone == "0" or (alone != "1" and (n_tiles + 1) // 2 * hkv * 2 <= _sm_count(q.device))
-                seqs, starts, starts_b = extend_tile_pairs(meta.q_lens, meta.kv_lens, nd, tpt, window, alone)
+                ctas = (n_tiles + 1) // 2 * hkv
+                how = os.environ.get("DIB200_PREFILL_PAIR", "auto")
+                alone = how == "0" or (how == "auto" and ctas * 2 <= _sm_count(q.device))
+                neighbours = how == "2" or (how == "auto" and ctas > _sm_count(q.device))
+                seqs, starts, starts_b = extend_tile_pairs(meta.q_lens, meta.kv_lens, nd, tpt, window,
+                                                           alone, neighbours)
             else:
                 seqs, starts = extend_tiles(meta.q_lens, nd, tpt)
                 starts_b = starts
