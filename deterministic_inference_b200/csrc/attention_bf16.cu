@@ -302,6 +302,7 @@ decode_attention_stage1_tma_kernel(const __grid_constant__ CUtensorMap map,
   // lengths: their loads start at once; only the page that holds the new token, and
   // the query, wait for that kernel.
   pdl_trigger();
+  if (threadIdx.x == 0) prefetch_tensormap(&map);
   constexpr int HALVES = D / 64;
   constexpr int TILE = DEC_SPLIT * D;   // elements of the K (or V) tile
   extern __shared__ unsigned char smem_dyn[];
@@ -403,6 +404,7 @@ decode_attention_stage1_pipe_kernel(const __grid_constant__ CUtensorMap map,
                                     float* __restrict__ part_lse, int num_seqs, int max_splits,
                                     int Hq, int Hkv, int page_size, float scale, int window) {
   pdl_trigger();
+  if (threadIdx.x == 0) prefetch_tensormap(&map);
   constexpr int HALVES = D / 64;
   constexpr int TILE = DEC_SPLIT * D;
   constexpr int QS = D + Q_ROW_PAD;

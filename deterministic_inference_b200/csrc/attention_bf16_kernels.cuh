@@ -494,63 +494,82 @@ decode_attention_stage1_kernel(const __nv_bfloat16* __restrict__ q,
   }
 }
 
-// Stage 2: merge the splits of one (sequence, head) in index order.  The partial results
-// of the first 16 splits are requested before the sequence's length is known (what lies
-// beyond its last split is read but not used), so the kernel waits for memory once.
+// Stage 2: merge the splits of one (sequence, head).  The order of the sums depends on
+// the sequence's own length only: the splits are taken in chunks of 16 (chunk c = splits
+// 16c .. 16c+15), a chunk is added up in split order, and the chunks' sums are added in
+// chunk order.  Two kernels do this: the first with one thread per output dimension,
+// for steps whose longest sequence has few chunks; the second with a group of threads per
+// chunk, for long sequences.  Both give the same bits for a sequence, whatever else is in
+// the batch.  The partial results of the first chunk are requested before the
+// sequence's length is known (what lies beyond its last split is read but not used), so
+// a sequence of one chunk waits for memory once.
+constexpr int MERGE_CH = 16;
 __global__ void decode_attention_stage2_kernel(const float* __restrict__ part_o,
                                                const float* __restrict__ part_lse,
                                                const int* __restrict__ seq_lens,
                                                __nv_bfloat16* __restrict__ out, int max_splits,
                                                int Hq, int D, int window) {
   pdl_prologue(part_o, part_lse);
-  constexpr int EARLY = 16;
+  constexpr int CH = MERGE_CH;
   const int b = blockIdx.x, h = blockIdx.y;
   const size_t row = ((size_t)b * Hq + h) * max_splits;
   const int kv_len = seq_lens[b];
-  float lse_r[EARLY], o_r[EARLY];
+  float lse_r[CH], o_r[CH];
 #pragma unroll
-  for (int j = 0; j < EARLY; ++j) lse_r[j] = j < max_splits ? part_lse[row + j] : NEG_BIG;
+  for (int j = 0; j < CH; ++j) lse_r[j] = j < max_splits ? part_lse[row + j] : NEG_BIG;
 #pragma unroll
-  for (int j = 0; j < EARLY; ++j)
+  for (int j = 0; j < CH; ++j)
     o_r[j] = (j < max_splits && (int)threadIdx.x < D) ? part_o[(row + j) * D + threadIdx.x] : 0.f;
   const int pos = kv_len - 1;
   const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int s0 = first_key / DEC_SPLIT, s1 = pos / DEC_SPLIT;
+  const int c0 = s0 / CH, c1 = s1 / CH;
   float M = NEG_BIG;
 #pragma unroll
-  for (int j = 0; j < EARLY; ++j)
+  for (int j = 0; j < CH; ++j)
     if (j >= s0 && j <= s1) M = fmaxf(M, lse_r[j]);
-  for (int s = max(s0, EARLY); s <= s1; ++s) M = fmaxf(M, part_lse[row + s]);
+  for (int s = max(s0, CH); s <= s1; ++s) M = fmaxf(M, part_lse[row + s]);
   bool first = true;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.f, den = 0.f;
+    float total = 0.f, total_den = 0.f;
+    for (int c = c0; c <= c1; ++c) {
+      if (c > 0 || !first) {
 #pragma unroll
-    for (int j = 0; j < EARLY; ++j) {
-      if (j >= s0 && j <= s1) {
-        const float o = first ? o_r[j] : part_o[(row + j) * D + d];
-        const float w = expf(lse_r[j] - M);
-        acc += w * o;
-        den += w;
+        for (int j = 0; j < CH; ++j) {
+          const int s = c * CH + j;
+          const bool in = s >= s0 && s <= s1;
+          lse_r[j] = in ? part_lse[row + s] : NEG_BIG;
+          o_r[j] = in ? part_o[(row + s) * D + d] : 0.f;
+        }
+      }
+      float acc = 0.f, den = 0.f;
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int s = c * CH + j;
+        if (s >= s0 && s <= s1) {
+          const float w = expf(lse_r[j] - M);
+          acc += w * o_r[j];
+          den += w;
+        }
+      }
+      if (c == c0) {
+        total = acc;
+        total_den = den;
+      } else {
+        total += acc;
+        total_den += den;
       }
     }
-    for (int s = max(s0, EARLY); s <= s1; ++s) {
-      const float w = expf(part_lse[row + s] - M);
-      acc += w * part_o[(row + s) * D + d];
-      den += w;
-    }
-    out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(acc / den);
+    out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(total / total_den);
     first = false;
   }
 }
 
-// The same for sequences of more than 16 splits.  The splits are taken in chunks of 16;
-// chunk c belongs to group c % 8 of the block's eight groups of D threads, a group adds
-// its chunks in rising order (each chunk's loads requested together), and the groups'
-// sums are added in group order.  A sequence of at most 16 splits is summed by group 0
-// alone, in the order of the kernel above: its bits do not depend on whether a longer
-// sequence in the batch brought it here.  The grouping depends on nothing but the
-// sequence's own length.
-constexpr int MERGE_GROUPS = 8;
+// The kernel for long sequences: chunk c belongs to group c % 8 of the block's groups of
+// D threads (a block has as many groups as the step's longest sequence has chunks, 8 at
+// most); a group leaves each of its chunks' sums in shared memory, and the first group
+// adds them in chunk order.  For at most MERGE_MAX_CHUNKS chunks of a sequence's range.
+constexpr int MERGE_GROUPS = 8, MERGE_MAX_CHUNKS = 64;
 __global__ void __launch_bounds__(1024)
 decode_attention_stage2_wide_kernel(const float* __restrict__ part_o,
                                     const float* __restrict__ part_lse,
@@ -558,40 +577,58 @@ decode_attention_stage2_wide_kernel(const float* __restrict__ part_o,
                                     __nv_bfloat16* __restrict__ out, int max_splits, int Hq, int D,
                                     int window) {
   pdl_prologue(part_o, part_lse);
-  constexpr int CH = 16;
-  __shared__ float s_acc[MERGE_GROUPS][128];
-  __shared__ float s_den[MERGE_GROUPS];
-  __shared__ float s_max[32];
+  constexpr int CH = MERGE_CH;
+  __shared__ float s_acc[MERGE_MAX_CHUNKS][128];
+  __shared__ float s_den[MERGE_MAX_CHUNKS];
+  __shared__ float s_max[MERGE_GROUPS];
   const int b = blockIdx.x, h = blockIdx.y;
   const int d = threadIdx.x, g = threadIdx.y;
-  const int tid = g * blockDim.x + d, nthreads = blockDim.x * MERGE_GROUPS;
+  const int groups = blockDim.y;
   const size_t row = ((size_t)b * Hq + h) * max_splits;
   const int kv_len = seq_lens[b];
+  // chunk g is requested before the sequence's length is known: it is this group's
+  // first chunk unless a window has moved the range past it
+  float lse_r[CH], o_r[CH];
+#pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const int s = g * CH + j;
+    lse_r[j] = s < max_splits ? part_lse[row + s] : NEG_BIG;
+    o_r[j] = (s < max_splits && d < D) ? part_o[(row + s) * D + d] : 0.f;
+  }
   const int pos = kv_len - 1;
   const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   const int s0 = first_key / DEC_SPLIT, s1 = pos / DEC_SPLIT;
-  // the largest lse of the sequence's splits (a maximum does not depend on the order)
-  float m = NEG_BIG;
-  for (int s = s0 + tid; s <= s1; s += nthreads) m = fmaxf(m, part_lse[row + s]);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if ((tid & 31) == 0) s_max[tid >> 5] = m;
-  __syncthreads();
-  float M = NEG_BIG;
-  for (int w = 0; w < (nthreads + 31) / 32; ++w) M = fmaxf(M, s_max[w]);
-
-  float acc = 0.f, den = 0.f;
   const int c0 = s0 / CH, c1 = s1 / CH;
-  const int c_first = c0 + ((g - c0 % MERGE_GROUPS) + MERGE_GROUPS) % MERGE_GROUPS;   // first chunk >= c0 of group g
-  for (int c = c_first; c <= c1; c += MERGE_GROUPS) {
-    float lse_r[CH], o_r[CH];
+  // the largest lse of the sequence's splits (a maximum does not depend on the order):
+  // every thread of a group over the group's chunks, then over the groups
+  float m = NEG_BIG;
 #pragma unroll
+  for (int j = 0; j < CH; ++j) {
+    const int s = g * CH + j;
+    if (s >= s0 && s <= s1) m = fmaxf(m, lse_r[j]);
+  }
+  for (int c = g + MERGE_GROUPS; c <= c1; c += MERGE_GROUPS)
     for (int j = 0; j < CH; ++j) {
       const int s = c * CH + j;
-      const bool in = s >= s0 && s <= s1;
-      lse_r[j] = in ? part_lse[row + s] : NEG_BIG;
-      o_r[j] = (in && d < D) ? part_o[(row + s) * D + d] : 0.f;
+      if (s >= s0 && s <= s1) m = fmaxf(m, part_lse[row + s]);
     }
+  if (d == 0) s_max[g] = m;
+  __syncthreads();
+  float M = NEG_BIG;
+  for (int k = 0; k < groups; ++k) M = fmaxf(M, s_max[k]);
+
+  for (int c = g; c <= c1; c += MERGE_GROUPS) {
+    if (c < c0) continue;
+    if (c != g) {
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int s = c * CH + j;
+        const bool in = s >= s0 && s <= s1;
+        lse_r[j] = in ? part_lse[row + s] : NEG_BIG;
+        o_r[j] = (in && d < D) ? part_o[(row + s) * D + d] : 0.f;
+      }
+    }
+    float acc = 0.f, den = 0.f;
 #pragma unroll
     for (int j = 0; j < CH; ++j) {
       const int s = c * CH + j;
@@ -601,24 +638,22 @@ decode_attention_stage2_wide_kernel(const float* __restrict__ part_o,
         den += w;
       }
     }
+    if (c0 == c1) {      // one chunk: its sum is the result
+      if (d < D) out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(acc / den);
+    } else {
+      if (d < D) s_acc[c - c0][d] = acc;
+      if (d == 0) s_den[c - c0] = den;
+    }
   }
-  const bool one_group = c0 == c1;     // uniform over the block
-  if (one_group) {
-    if (g == c0 % MERGE_GROUPS && d < D)
-      out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(acc / den);
-    return;
-  }
-  if (d < D) s_acc[g][d] = acc;
-  if (d == 0) s_den[g] = den;
+  if (c0 == c1) return;    // uniform over the block
   __syncthreads();
   if (g == 0 && d < D) {
-    float a = 0.f, dn = 0.f;
-#pragma unroll
-    for (int k = 0; k < MERGE_GROUPS; ++k) {
-      a += s_acc[k][d];
-      dn += s_den[k];
+    float total = s_acc[0][d], total_den = s_den[0];
+    for (int k = 1; k <= c1 - c0; ++k) {
+      total += s_acc[k][d];
+      total_den += s_den[k];
     }
-    out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(a / dn);
+    out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(total / total_den);
   }
 }
 
@@ -628,8 +663,13 @@ static inline void launch_decode_merge(const float* part_o, const float* part_ls
                                        void* out, int num_seqs, int max_splits, int Hq, int D,
                                        int window, cudaStream_t st) {
   const int th = D < 32 ? 32 : (D + 31) / 32 * 32;
-  if (max_splits > 16 && th <= 128)
-    dib_launch(decode_attention_stage2_wide_kernel, dim3(num_seqs, Hq), dim3(th, MERGE_GROUPS), 0, st,
+  const int chunks = (max_splits + 15) / 16;
+  // DIB200_MERGE_WIDE_FROM=n: the kernel with a group per chunk from n splits on (measurements)
+  const char* env = getenv("DIB200_MERGE_WIDE_FROM");
+  const int wide_from = env ? atoi(env) : 49;
+  if (max_splits >= wide_from && max_splits > MERGE_CH && th <= 128 && chunks <= MERGE_MAX_CHUNKS)
+    dib_launch(decode_attention_stage2_wide_kernel, dim3(num_seqs, Hq),
+               dim3(th, chunks < MERGE_GROUPS ? chunks : MERGE_GROUPS), 0, st,
                part_o, part_lse, seq_lens, (__nv_bfloat16*)out, max_splits, Hq, D, window);
   else
     dib_launch(decode_attention_stage2_kernel, dim3(num_seqs, Hq), dim3(th), 0, st, part_o, part_lse,

@@ -170,6 +170,7 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
                            const int* __restrict__ cu_q_lens, const int* __restrict__ seq_lens,
                            const int* __restrict__ tile_seq, const int* __restrict__ tile_start,
                            int Hq, int Hkv, int page_size, float scale, int window) {
+  if (threadIdx.x == 0) prefetch_tensormap(&map);
   pdl_prologue(q);
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
@@ -503,6 +504,7 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   if (threadIdx.x == 0) DIB_PCLOCK(63, 0);
   DIB_PTIME(0);
   DIB_PTIME(2);
+  if (threadIdx.x == 0) prefetch_tensormap(&map);
   pdl_prologue(q);
   if (threadIdx.x == 0) DIB_PCLOCK(63, 1);
   extern __shared__ unsigned char smem_dyn[];

@@ -110,6 +110,10 @@ template <typename... P> __device__ __forceinline__ void pdl_wait(P&... p) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   (pdl_fresh(p), ...);
 }
+// Ask for a tensor map (a kernel parameter) ahead of the first copy that uses it.
+__device__ __forceinline__ void prefetch_tensormap(const void* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<unsigned long long>(map)) : "memory");
+}
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::); }
 template <typename... P> __device__ __forceinline__ void pdl_prologue(P&... p) {
   pdl_trigger();

@@ -144,6 +144,10 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   unsigned* tmem_slot = reinterpret_cast<unsigned*>(accum + 1);
 
   pdl_trigger();   // the kernel after this one may set itself up (and fetch its weights) beside this one
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_x);
+  }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * (GATED ? BM / 2 : BM), m0 = blockIdx.y * BN, split = blockIdx.z;
   const int kb_begin = split * kb_per_split;

@@ -361,10 +361,11 @@ def test_decode_attention_pipelined_walk_gives_the_same_bits(monkeypatch, hq, hk
 
 @pytest.mark.parametrize("hq,hkv,d,page,window", [(16, 8, 128, 16, None), (8, 2, 128, 32, 2500), (6, 3, 64, 16, None)])
 def test_decode_attention_long_sequences_beside_short_ones(monkeypatch, hq, hkv, d, page, window):
-    """Sequences of more than 16 splits of 128 keys take the merge kernel that adds chunks
-    of 16 splits in eight groups; a short sequence beside them keeps the bits it has
-    alone (the order of its sum depends on its own length only), both launch forms of
-    stage 1 agree in every bit, and all agree with the dense reference."""
+    """Sequences of more than 16 splits of 128 keys: their splits are added chunk by chunk
+    (16 splits), by one thread per dimension or by a group of threads per chunk, with the
+    same bits; a short sequence beside them keeps the bits it has alone (the order of its
+    sum depends on its own length only), both launch forms of stage 1 agree in every bit,
+    and all agree with the dense reference."""
     lens = [5000, 300, 2049, 2048, 129, 4097]
     case = PagedCase(lens, hkv, d, page, torch.bfloat16, seed=61)
     g = torch.Generator().manual_seed(62)
@@ -378,6 +379,12 @@ def test_decode_attention_long_sequences_beside_short_ones(monkeypatch, hq, hkv,
     assert ops()._lib("attention_bf16").dib_attention_bf16_status() == 0
     assert torch.equal(outs["0"], outs["1"])
     monkeypatch.delenv("DIB200_DECODE_PIPE")
+    for wide_from in ("17", "100000"):
+        monkeypatch.setenv("DIB200_MERGE_WIDE_FROM", wide_from)
+        got = ops().paged_attention(q, case.cache, case.meta(seqs, [(n - 1, 1) for n in lens]),
+                                    d ** -0.5, window)
+        assert torch.equal(got, outs["0"]), wide_from
+    monkeypatch.delenv("DIB200_MERGE_WIDE_FROM")
     for s_ in seqs:
         want = dense_reference(q[s_:s_ + 1], case.k[s_], case.v[s_], d ** -0.5, [lens[s_] - 1], window)
         torch.testing.assert_close(outs["0"][s_:s_ + 1].float(), want, **tol(torch.bfloat16))
