@@ -118,3 +118,41 @@ def test_no_cpu_path_in_the_product():
         ops.rms_norm(torch.randn(2, 8), torch.ones(8), 1e-6)
     with pytest.raises(KernelError, match="no CPU path"):
         ops.linear(torch.randn(2, 8), torch.randn(4, 8))
+
+
+def test_prompt_tile_lists_name_every_tile_once():
+    """The lists of query tiles that the prompt attention kernels take (a CTA per pair of
+    tiles from both ends of a prompt, per pair of neighbours, per tile, per chunk of a
+    pair's key range) name every tile of every prompt sequence exactly once per chunk it
+    needs, never a tile of a decoding sequence, and pair only tiles of one sequence."""
+    import random
+    from deterministic_inference_b200.kernels.attention_bf16 import (extend_chunk_units, extend_tile_pairs,
+                                                                     extend_tiles)
+    rng = random.Random(5)
+    for _ in range(200):
+        nd = rng.randint(0, 3)
+        q_lens = [1] * nd + [rng.choice([1, 2, 63, 64, 65, 128, 129, rng.randint(1, 1500)])
+                             for _ in range(rng.randint(1, 5))]
+        kv_lens = [q + rng.choice([0, 0, 1, 700, 5000]) for q in q_lens]
+        tpt = rng.choice([8, 64, 128])
+        want = sorted((s, t0) for s in range(nd, len(q_lens)) for t0 in range(0, q_lens[s], tpt))
+        seqs, starts = extend_tiles(q_lens, nd, tpt)
+        assert sorted(zip(seqs, starts)) == want
+        for window, alone, neighbours in ((0, False, False), (0, True, False), (0, False, True), (300, False, False)):
+            seqs, a, b = extend_tile_pairs(q_lens, kv_lens, nd, tpt, window, alone, neighbours)
+            got = sorted([(s, x) for s, x in zip(seqs, a)] + [(s, y) for s, y in zip(seqs, b) if y >= 0])
+            assert got == want, (q_lens, tpt, window, alone, neighbours)
+            assert all(x >= 0 and (y < 0 or y != x) for x, y in zip(a, b))
+            if alone:
+                assert all(y < 0 for y in b)
+        chunk_tiles = rng.choice([1, 8, 11])
+        seqs, a, b, chunks = extend_chunk_units(q_lens, kv_lens, nd, tpt, chunk_tiles)
+        span = chunk_tiles * 128
+        need = []
+        for s in range(nd, len(q_lens)):
+            prefix = kv_lens[s] - q_lens[s]
+            for t0 in range(0, q_lens[s], 2 * tpt):
+                last = prefix + min(t0 + 2 * tpt, q_lens[s]) - 1
+                need += [(s, t0, c) for c in range(last // span + 1)]
+        assert sorted(zip(seqs, a, chunks)) == sorted(need)
+        assert all(y < 0 or y == x + tpt for x, y in zip(a, b))
