@@ -1,9 +1,10 @@
 // Prefill / extend attention over the paged cache on the 5th-generation tensor
 // cores: S = Q K^T and O_j = P V by tcgen05.mma with accumulators in tensor memory,
 // K and V pages fetched by TMA into 128-byte-swizzled tiles, softmax in float32 by
-// one thread per query row.
+// one thread per query row.  Two kernels: the one described first (one query tile per
+// CTA), and the default, which gives a CTA two query tiles (described at its definition).
 //
-// A CTA owns 128 rows = (token, query head of one kv group) pairs of one sequence and
+// First kernel.  A CTA owns 128 rows = (token, query head of one kv group) pairs of one sequence and
 // walks the key tiles of 128 keys from position 0 (or the window's start) to its last
 // token, so the order of a row's reduction depends on its position alone.  Ten warps:
 //   warps 0-7  softmax: two threads share a row (tensor-memory lane = row; warp w reads
@@ -31,7 +32,7 @@
 
 // Phase clocks of the two-tile kernel (a development build only, -DDIB_PREFILL_CLOCKS):
 // the longest CTA of kv head 0 records clock64 per key tile, for the MMA lane (slots
-// 0..5) and for the first softmax thread of tile A (slots 6..11).
+// 0..5) and for the first softmax thread of tile B (slots 6..11).
 #ifdef DIB_PREFILL_CLOCKS
 __device__ long long dib_prefill_clocks[64 * 12];
 #define DIB_PCLOCK(it, slot)                                                              \
@@ -464,6 +465,10 @@ extend_attention_tc_kernel(const __grid_constant__ CUtensorMap map,
 // there (no shared memory, no proxy fence).  The MMA warp staggers the two tiles:
 // after O_A += P_A V it issues S_A of the next key tile at once, then turns to B, so
 // each tile's softmax runs while the tensor core works for the other tile.
+// Warp 8 fetches the keys, warp 10 the values (each refills a stage as soon as it is
+// free; both send for the first two key tiles before Q is loaded), warp 9 issues the
+// products.  When one tile has had its last key tile, or has none (B = -1), the other
+// runs alone and takes the idle tile's score columns as a second buffer (see solo_from).
 // Tensor memory: S_A/P_A columns 0..127, S_B/P_B 128..255, O_A 256..383, O_B 384..511.
 __device__ __forceinline__ void tc_mma_ts(unsigned tmem_d, unsigned tmem_a, unsigned long long desc_b,
                                           unsigned idesc, unsigned accum) {
