@@ -152,3 +152,52 @@ def test_lone_request_that_outgrows_the_pool_preempts_itself_and_is_not_readmitt
         run_step(sched)
     assert r.num_preemptions >= 1
     cache.check_invariants()
+
+
+import pytest
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_arrivals_under_a_small_pool(seed):
+    """Requests of random lengths arrive at random steps into a pool that holds only a few
+    of them: every step keeps the token budget and the limit on running requests, a
+    request never gets more tokens than it has left, decode tokens are single, no page
+    is lost, a preempted request was admitted after every request that keeps running,
+    and in the end every request has all its outputs and every page is free."""
+    import random
+    rng = random.Random(seed)
+    pages, page, budget, max_running = rng.choice([8, 12, 20]), rng.choice([2, 4]), rng.choice([5, 16, 64]), rng.choice([2, 4, 8])
+    sched, cache = make(pages=pages, page=page, budget=budget, max_running=max_running, reqs=12)
+    cap = pages * page
+    todo = []
+    for rid in range(12):
+        plen = rng.randint(1, max(1, cap // 2))
+        max_new = rng.randint(1, max(1, cap - plen))          # fits the pool alone
+        todo.append((rng.randint(0, 30), req(rid, plen, max_new=max_new)))
+    todo.sort(key=lambda x: x[0])
+    all_reqs = [r for _, r in todo]
+    step = 0
+    while todo or sched.has_work():
+        while todo and todo[0][0] <= step:
+            sched.add(todo.pop(0)[1])
+        running_before = [r for r in all_reqs if r.state == RequestState.RUNNING]
+        admitted_before = {r.rid: r.admit_order for r in running_before}
+        preempts_before = {r.rid: r.num_preemptions for r in all_reqs}
+        out, _ = run_step(sched)
+        assert sum(s.num_tokens for s in out) <= budget
+        assert len({s.request.rid for s in out}) == len(out) <= max_running
+        for s in out:
+            assert 1 <= s.num_tokens
+        victims = [r for r in all_reqs if r.num_preemptions > preempts_before[r.rid]]
+        if victims and len(running_before) > 1:
+            # a victim was admitted after every request that kept running
+            survivors = [r for r in running_before if r not in victims and r.finished_reason is None]
+            for v in victims:
+                if v.rid in admitted_before:
+                    assert all(admitted_before[v.rid] > admitted_before[k.rid] for k in survivors)
+        step += 1
+        assert step < 5000
+    for r in all_reqs:
+        assert len(r.output_ids) == r.params.max_new_tokens, (r.rid, len(r.output_ids))
+    assert cache.num_free_pages() == pages
+    cache.check_invariants()
