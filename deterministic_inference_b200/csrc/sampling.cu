@@ -362,7 +362,8 @@ __global__ void gumbel_pick_kernel(const float* __restrict__ logits,
                                    const float* __restrict__ cmax, const float* __restrict__ csum,
                                    float* __restrict__ pv, int* __restrict__ pi, int R, int V,
                                    int chunks) {
-  pdl_prologue(logits, temperatures, seeds, sample_pos, keep, top_ks, top_ps, hist_cnt, hist_mass);
+  pdl_prologue(logits, temperatures, seeds, sample_pos, keep, top_ks, top_ps, hist_cnt, hist_mass, cmax,
+               csum);
   __shared__ Best bscratch[32];
   __shared__ unsigned s_thresh;
   const int r = blockIdx.y, c = blockIdx.x;
