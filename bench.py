@@ -102,17 +102,161 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def reference_arm() -> int:
-    # The reference is a source tree without packaging metadata: the offline
-    # install (pip --no-index --target baseline/_ref <the reference's tree>) stops with
-    # "neither 'setup.py' nor 'pyproject.toml' found".  Run from its tree it needs
-    # Triton kernels for every norm/rope/prefill, a downloaded Qwen3-0.6B checkpoint
-    # and tokenizer (no network here), and its CUDA kernel is fixed to 16 query /
-    # 8 kv heads of 128.
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "reference has no setup.py/pyproject.toml (offline pip install fails) and "
-                      "needs a downloaded Qwen3-0.6B checkpoint and tokenizer; no network"}))
+REF_TREE = ROOT / "baseline" / "_ref"
+
+
+def _stub_tokenizer(folder: Path) -> None:
+    """The reference's ``Engine`` builds a tokenizer from the model folder whatever the
+    prompts are; a three-word one satisfies it (requests come as token ids)."""
+    from tokenizers import Tokenizer
+    from tokenizers.models import WordLevel
+    from tokenizers.pre_tokenizers import Whitespace
+    tok = Tokenizer(WordLevel({"<unk>": 0, "a": 1, "b": 2}, unk_token="<unk>"))
+    tok.pre_tokenizer = Whitespace()
+    tok.save(str(folder / "tokenizer.json"))
+    (folder / "tokenizer_config.json").write_text(json.dumps(
+        {"tokenizer_class": "PreTrainedTokenizerFast", "unk_token": "<unk>"}))
+
+
+def reference_arm(a) -> int:
+    """The unmodified reference (a copy of its tree under ``baseline/_ref``; it has no
+    packaging metadata, so it is put on the module path instead of installed) through its
+    own public API: ``sid.engine.engine.Engine(EngineConfig(mode=NONDET))``,
+    ``add_request(prompt_ids=...)`` and ``step()``.  Same model shape, random weights,
+    batch, context, steps and warm-up as this repository's arm.  Its ``step()`` ends with
+    the device-to-host read of the sampled tokens, so one timing gives both ``value`` and
+    ``e2e``.  Nothing of this package's kernels is loaded in this process: only the
+    random-weights writer (plain torch on the CPU) makes the model folder."""
+    def unavailable(why: str) -> int:
+        print(json.dumps({"impl": "reference", "unavailable": " ".join(str(why).split())[:400]}))
+        return 0
+
+    if a.gpus != 1:
+        return unavailable("the reference is a single-GPU engine (no collective code); N>1 is not run")
+    if not (REF_TREE / "sid" / "engine" / "engine.py").exists():
+        return unavailable("no copy of the reference's tree under baseline/_ref")
+    import tempfile
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return unavailable("no CUDA device")
+        from deterministic_inference_b200.config import preset
+        from deterministic_inference_b200.weights import write_random_model
+        full = preset(a.preset)
+        layers = a.layers or full.num_hidden_layers
+        cfg = preset(a.preset, num_hidden_layers=layers, max_window_layers=layers)
+        pk = peaks()
+        sizes = sorted({a.batch, *[int(x) for x in a.points.split(",") if x.strip()]})
+        max_b = max(sizes)
+        new_tokens = max(a.steps, a.point_steps) + a.warmup + 32
+        with tempfile.TemporaryDirectory(prefix="dib200_ref_model_") as folder:
+            folder = Path(folder)
+            write_random_model(cfg, 0, folder)
+            _stub_tokenizer(folder)
+            sys.path.insert(0, str(REF_TREE))
+            from sid.config import EngineConfig as RefEngineConfig, Mode, SamplingParams as RefParams
+            from sid.engine.engine import Engine as RefEngine
+            pool = max_b * (a.context + new_tokens + 64) + a.prefill_tokens + 4096
+            eng = RefEngine(RefEngineConfig(
+                model_path=str(folder), mode=Mode.NONDET, kv_pool_tokens=pool,
+                max_reqs=max(256, max_b + 8), max_seq_len=max(8192, a.context + new_tokens + 64),
+                max_prompt_len=max(a.context, a.prefill_tokens), max_prefill_tokens=8192,
+                max_decode_batch=max(256, max_b), device="cuda"))
+            gen = torch.Generator().manual_seed(1)
+
+            def random_prompt(n):
+                return torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()
+
+            def timed(fn):
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                s.record()
+                fn()
+                e.record()
+                torch.cuda.synchronize()
+                return s.elapsed_time(e)
+
+            def drain():
+                while eng.scheduler.has_work():
+                    eng.step()
+                eng._done.clear()
+
+            # prefill of one whole prompt: the step that admits it runs it and samples one token
+            prompt = random_prompt(a.prefill_tokens)
+            flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+            ms_list = []
+            for it in range(0 if a.no_prefill else 6):
+                eng.add_request(prompt_ids=prompt, params=RefParams(max_new_tokens=1, ignore_eos=True))
+                flush.zero_()
+                ms = timed(eng.step)
+                drain()
+                if it >= 3:
+                    ms_list.append(ms)
+            prefill = None
+            if ms_list:
+                pms = sorted(ms_list)[len(ms_list) // 2]
+                _, flops = model_bytes_and_flops(cfg, layers, 1, 0, a.prefill_tokens)
+                prefill = {"value": a.prefill_tokens / (pms / 1e3), "tokens": a.prefill_tokens, "ms": pms,
+                           "frac": flops / (pms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+
+            def decode(batch, steps, sample_clocks=False):
+                sp = RefParams(max_new_tokens=steps + a.warmup + 32, ignore_eos=True)
+                for _ in range(batch):
+                    eng.add_request(prompt_ids=random_prompt(a.context), params=sp)
+                eng.step()                          # admits all and prefills them, untimed
+                assert len(eng.scheduler.active) == batch and not eng.scheduler.waiting
+                for _ in range(a.warmup):
+                    eng.step()
+                sampler = ClockSampler()
+                if sample_clocks:
+                    sampler.start()
+                ms = timed(lambda: [eng.step() for _ in range(steps)])
+                clocks = sampler.stop() if sample_clocks else None
+                assert all(len(r.output_ids) >= steps + a.warmup for r in eng.scheduler.active)
+                for r in eng.scheduler.active:      # stop them: the next step retires them
+                    r.params.max_new_tokens = len(r.output_ids)
+                    r.check_finished()
+                drain()
+                return ms, clocks
+
+            ms, clocks = decode(a.batch, a.steps, sample_clocks=True)
+            points = {}
+            for b in sizes:
+                if b != a.batch:
+                    pms, _ = decode(b, a.point_steps)
+                    points[f"decode_b{b}"] = b * a.point_steps / (pms / 1e3)
+    except Exception as exc:  # the reference's kernels or its build failed here: say so, run nothing again
+        return unavailable(f"{type(exc).__name__}: {exc}")
+    value = a.batch * a.steps / (ms / 1e3)
+    mean_ctx = a.context + a.warmup + a.steps / 2
+    decode_bytes, _ = model_bytes_and_flops(cfg, layers, a.batch, mean_ctx, 0)
+    achieved = decode_bytes / (ms / a.steps / 1e3) / 1e9
+    print(json.dumps({
+        "metric": "decode tok/s (bf16, 1 B200)", "value": value, "unit": "tokens/s", "n_gpus": 1,
+        "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "impl": "reference",
+        "config": dict(bench_config(a, cfg, full, layers), page_size=1),
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": None,
+                "d2h_bytes_per_step": a.batch * 8,
+                "note": "the reference's step() reads the sampled tokens on the host every step; "
+                        "value and e2e are the same timing"},
+        "clocks": clocks, "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "peaks": pk["source"]},
+        "points": points}))
     return 0
+
+
+def bench_config(a, cfg, full, layers: int) -> dict:
+    return {"model": a.preset, "layers": layers, "layers_full": full.num_hidden_layers,
+            "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
+            "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+            "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+            "tied_head": cfg.tie_word_embeddings, "global_batch": a.batch,
+            "seq_len": a.context, "context": 4096, "page_size": 16,
+            "weights": "random N(0,0.02) seed 0", "parallelism": "1 GPU",
+            "l2": "inputs larger than L2 (weights+cache per step)"}
 
 
 def model_bytes_and_flops(cfg, layers: int, batch: int, ctx: float, prefill_tokens: int):
@@ -151,13 +295,13 @@ def main() -> int:
                          "--profile-from-start off); the numbers of such a run are not a result")
     a = ap.parse_args()
 
+    if a.warmup < 3:
+        a.warmup = 3
     if a.impl == "reference":
-        return reference_arm()
+        return reference_arm(a)
     if a.gpus != 1:
         print(f"bench.py measures one GPU only (this engine is single-GPU); --gpus {a.gpus} is not run")
         return 2
-    if a.warmup < 3:
-        a.warmup = 3
 
     import numpy as np
     import torch
@@ -341,14 +485,7 @@ def main() -> int:
         "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "impl": "ours",
-        "config": {"model": a.preset, "layers": layers, "layers_full": full.num_hidden_layers,
-                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
-                   "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
-                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "tied_head": cfg.tie_word_embeddings, "global_batch": a.batch,
-                   "seq_len": a.context, "context": 4096, "page_size": 16,
-                   "weights": "random N(0,0.02) seed 0", "parallelism": "1 GPU",
-                   "l2": "inputs larger than L2 (weights+cache per step)"},
+        "config": bench_config(a, cfg, full, layers),
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "prefill": prefill,
         "roofline": roofline, "points": points,
     }

@@ -183,6 +183,8 @@ class Engine:
             if self._inflight is not None:
                 self._collect()
                 return
+            for req in self.scheduler.release_finished():
+                self._done[req.rid] = req
             if self.scheduler.waiting and not self.scheduler.running:
                 head = self.scheduler.waiting[0]
                 raise RuntimeError(

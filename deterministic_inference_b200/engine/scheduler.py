@@ -112,10 +112,17 @@ class Scheduler:
     # ---- after a step ------------------------------------------------------------
 
     def release_finished(self) -> list[Request]:
+        """Retire every finished request.  A running one gives its pages and slot back.  A
+        waiting one can be finished too: it was preempted while its last token was still on
+        its way from the device, holds nothing, and must not be admitted again."""
         done = [r for r in self.running if r.finished_reason is not None]
         for r in done:
             self.cache.release_slot(r.slot)
             r.slot = -1
             r.state = RequestState.DONE
             self.running.remove(r)
-        return done
+        late = [r for r in self.waiting if r.finished_reason is not None]
+        for r in late:
+            r.state = RequestState.DONE
+            self.waiting.remove(r)
+        return done + late

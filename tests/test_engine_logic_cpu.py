@@ -156,3 +156,39 @@ def test_prompt_tile_lists_name_every_tile_once():
                 need += [(s, t0, c) for c in range(last // span + 1)]
         assert sorted(zip(seqs, a, chunks)) == sorted(need)
         assert all(y < 0 or y == x + tpt for x, y in zip(a, b))
+
+
+@pytest.mark.parametrize("seed", [2553, 2734, 2789])
+def test_a_request_preempted_with_its_last_token_in_flight_retires(seed, tiny_model_dirs, torch_ops):
+    """Tokens are read one step late.  A request can be preempted in the very step whose
+    in-flight token is its last: it is then finished while it waits, holds nothing, and has
+    to be retired from the waiting queue.  Re-admitted it would run a first portion without
+    a logits row (its prompt plus outputs exceed the token budget), never be scheduled
+    again and keep ``has_work()`` true for ever.  These draws (pool of 48 tokens, budget 8)
+    reach that state."""
+    import random
+    d = tiny_model_dirs["a"]
+    cfg, w = plain_qwen3.read_model_dir(d)
+    rnd = random.Random(seed)
+    pool, budget = rnd.choice([48, 64]), rnd.choice([8, 12, 16])
+    eng = Engine(EngineConfig(model_path=str(d), dtype="float32", device="cpu", page_size=16,
+                              kv_pool_tokens=pool, max_reqs=8, max_seq_len=256,
+                              max_prefill_tokens=budget))
+    prompts, news, rids = [], [], []
+    for _ in range(rnd.randint(2, 4)):
+        pl, mn = rnd.randint(10, 40), rnd.randint(1, 6)
+        pl = min(pl, pool - mn)
+        prompts.append([rnd.randrange(255) for _ in range(pl)])
+        news.append(mn)
+        rids.append(eng.add_request(prompt_ids=prompts[-1],
+                                    params=SamplingParams(max_new_tokens=mn, ignore_eos=True)))
+    steps = 0
+    while eng.has_work():
+        eng.step()
+        steps += 1
+        assert steps < 400, (eng.scheduler.running, list(eng.scheduler.waiting))
+    outs = [eng.get_output(r) for r in rids]
+    assert sum(o.num_preemptions for o in outs) > 0
+    assert [o.token_ids for o in outs] == [plain_qwen3.generate(cfg, w, p, n) for p, n in zip(prompts, news)]
+    eng.cache.check_invariants()
+    assert eng.cache.num_free_pages() == eng.cache.usable_pages()
