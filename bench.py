@@ -8,13 +8,19 @@ Qwen3-0.6B (28 layers, hidden 1024, 16/8 heads of 128, intermediate 3072,
 vocabulary 151936, tied head), random weights N(0, 0.02) from seed 0, bfloat16,
 page size 16; each request holds 2,048 cached tokens when decoding starts.
 
-``value``   decode tokens/s timed on the device (CUDA events): the captured decode
-            step, sampling (argmax) and the on-device hand-over of the sampled
-            tokens to the next step, K steps back to back.
+``value``   decode tokens/s timed on the device (CUDA events): K decode steps through
+            ``ModelRunner.step`` and the sampler (argmax), the sampled tokens handed to
+            the next step on the device; nothing is read on the host in between.
 ``e2e``     the same through ``Engine.step()``: scheduler, packing, one
             host-to-device copy of the step's metadata from pinned memory, the
             graph, sampling, and the device-to-host read of the sampled tokens,
             every step.
+``prefill`` a prompt of 2,048 tokens, whole: launched kernel by kernel (``value``,
+            ``cold_ms``) and as the replayed graph of that step shape (``replayed_ms``).
+``points``  decode at batch 1 and 64; ``points_<preset>``: decode and prefill at a larger
+            model's layer sizes with fewer layers (``config.second_model`` names both
+            layer counts).
+``--impl reference`` runs the unmodified reference engine on the same workload.
 Every decode step reads all weights and the live cache (about 3 GB at batch 8),
 far more than the 126 MB L2, so no L2 flush is needed between steps.
 """
@@ -290,6 +296,10 @@ def main() -> int:
                          "(64 requests, prompts uniform in [128, 2048], 256 outputs each, "
                          "temperature 0.7) through Engine.generate; prints its own line")
     ap.add_argument("--no-prefill", action="store_true")
+    ap.add_argument("--second-preset", default="qwen3_8b",
+                    help="layer sizes measured after the main model (decode batch 8 and 64, prefill), "
+                         "with --second-layers layers; 'none' to skip")
+    ap.add_argument("--second-layers", type=int, default=12)
     ap.add_argument("--profile", default=None, choices=["decode", "prefill"],
                     help="bracket this region with cudaProfilerStart/Stop (for ncu "
                          "--profile-from-start off); the numbers of such a run are not a result")
@@ -303,13 +313,13 @@ def main() -> int:
         print(f"bench.py measures one GPU only (this engine is single-GPU); --gpus {a.gpus} is not run")
         return 2
 
-    import numpy as np
     import torch
 
     from deterministic_inference_b200 import EngineConfig, SamplingParams, preset
     from deterministic_inference_b200.engine.batch import SequenceInput
     from deterministic_inference_b200.engine.engine import Engine
     from deterministic_inference_b200.kernels import ops
+    from deterministic_inference_b200.sampling.sampler import sample
 
     full = preset(a.preset)
     layers = a.layers or full.num_hidden_layers
@@ -317,21 +327,11 @@ def main() -> int:
     pk = peaks()
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
-
-    sizes = sorted({a.batch, *[int(x) for x in a.points.split(",") if x.strip()]})
-    max_b = max(sizes)
-    per_req = a.context + max(a.steps + a.warmup, a.point_steps + a.warmup) + 96
-    pool = max_b * (-(-per_req // 16) * 16) + a.prefill_tokens + 1024
-    ecfg = EngineConfig(model_config=cfg, random_seed=0, dtype="bfloat16", kv_pool_tokens=pool,
-                        page_size=16, max_reqs=max(256, max_b + 8),
-                        max_seq_len=max(8192, -(-per_req // 1024) * 1024, a.prefill_tokens),
-                        max_prefill_tokens=max(8192, a.prefill_tokens), max_decode_batch=max(256, max_b), device="cuda:0")
-    engine = Engine(ecfg)
-    runner, cache, graphs = engine.runner, engine.cache, engine.decode_graphs
     gen = torch.Generator().manual_seed(1)
+    greedy = SamplingParams(max_new_tokens=1 << 20, ignore_eos=True)
 
-    def random_prompt(n):
-        return torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist()
+    def random_prompt(vocab, n):
+        return torch.randint(0, vocab, (n,), generator=gen).tolist()
 
     def timed(fn):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -342,10 +342,124 @@ def main() -> int:
         torch.cuda.synchronize()
         return s.elapsed_time(e)
 
+    def make_engine(mcfg, sizes, steps_most):
+        max_b = max(sizes)
+        per_req = a.context + steps_most + a.warmup + 96
+        pool = max_b * (-(-per_req // 16) * 16) + a.prefill_tokens + 1024
+        return Engine(EngineConfig(
+            model_config=mcfg, random_seed=0, dtype="bfloat16", kv_pool_tokens=pool, page_size=16,
+            max_reqs=max(256, max_b + 8),
+            max_seq_len=max(8192, -(-per_req // 1024) * 1024, a.prefill_tokens),
+            max_prefill_tokens=max(8192, a.prefill_tokens), max_decode_batch=max(256, max_b),
+            device="cuda:0"))
+
+    def launches_now(runner):
+        """Kernels launched so far: the wrappers' own count plus what replayed graphs hold."""
+        n = ops.launch_count
+        for g in (runner.decode_graphs, runner.step_graphs):
+            if g is not None:
+                n += g.kernels_replayed
+        return n
+
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > L2
+
+    def measure_prefill(engine, mcfg, n_layers, profile=False):
+        """One prompt of ``--prefill-tokens`` tokens, whole, to its first logits.  A step
+        shape is launched kernel by kernel the first two times it is seen and replayed as
+        a captured graph from the third time on: both are timed, ``value`` is the launched
+        one (what a prompt length seen for the first time costs once the libraries are
+        loaded)."""
+        runner, cache = engine.runner, engine.cache
+        n = a.prefill_tokens
+        prompt = random_prompt(mcfg.vocab_size, n + 1)
+
+        def once(tokens, profiled=False):
+            slot = cache.allocate_slot()
+            flush.zero_()
+            if profiled:
+                torch.cuda.synchronize()
+                torch.cuda.profiler.start()
+            ms = timed(lambda: runner.step([SequenceInput(slot, tokens, 0, [len(tokens) - 1])]))
+            if profiled:
+                torch.cuda.profiler.stop()
+            cache.release_slot(slot)
+            return ms
+
+        for extra in (1, -1, 1):                 # other shapes: load the libraries, warm the clocks
+            once(prompt[:n + extra])
+        launched = [once(prompt[:n], profiled=profile and i == 1) for i in range(2)]
+        once(prompt[:n])                         # the third time: captured, then replayed
+        replayed = [once(prompt[:n]) for _ in range(3)]
+        sg = runner.step_graphs
+        cold_ms, replayed_ms = min(launched), sorted(replayed)[1]
+        if sg is None or sg.replays < 3:
+            replayed_ms = None
+        _, flops = model_bytes_and_flops(mcfg, n_layers, 1, 0, n)
+        return {"value": n / (cold_ms / 1e3), "tokens": n, "ms": cold_ms, "cold_ms": cold_ms,
+                "replayed_ms": replayed_ms,
+                "frac": flops / (cold_ms / 1e3) / (pk["bf16_tflops"] * 1e12),
+                "frac_replayed": (flops / (replayed_ms / 1e3) / (pk["bf16_tflops"] * 1e12)
+                                  if replayed_ms else None),
+                "note": "value, ms and frac: launched kernel by kernel (a prompt length seen the "
+                        "first or second time); replayed_ms: the captured graph of this step shape"}
+
+    def fill_requests(engine, mcfg, batch):
+        slots = [engine.cache.allocate_slot() for _ in range(batch)]
+        group = max(1, 8192 // a.context)
+        for i in range(0, batch, group):
+            engine.runner.step([SequenceInput(s, random_prompt(mcfg.vocab_size, a.context), 0, [])
+                                for s in slots[i:i + group]])
+        return slots
+
+    def device_decode(engine, mcfg, batch, steps, warmup, sample_clocks=False, profile=False):
+        """``steps`` decode steps of ``batch`` requests through ``ModelRunner.step`` and the
+        sampler, the sampled tokens handed to the next step on the device; nothing is read
+        on the host inside the timed region."""
+        runner = engine.runner
+        slots = fill_requests(engine, mcfg, batch)
+        params = [greedy] * batch
+        state = {"tokens": None}
+
+        def one(k):
+            pend = state["tokens"] is not None
+            entries = [SequenceInput(s, [0], a.context + k, [0], i if pend else -1)
+                       for i, s in enumerate(slots)]
+            logits, _ = runner.step(entries, state["tokens"])
+            state["tokens"] = sample(logits, params, [a.context + k + 1] * batch)
+
+        for k in range(warmup):
+            one(k)
+        sampler = ClockSampler()
+        if sample_clocks:
+            sampler.start()
+        n0 = launches_now(runner)
+        if profile:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()
+        ms = timed(lambda: [one(k) for k in range(warmup, warmup + steps)])
+        if profile:
+            torch.cuda.profiler.stop()
+        launches = launches_now(runner) - n0
+        clocks = sampler.stop() if sample_clocks else None
+        for s in slots:
+            engine.cache.release_slot(s)
+        return ms, launches, clocks
+
+    def decode_roofline(mcfg, n_layers, batch, steps, warmup, ms):
+        mean_ctx = a.context + warmup + steps / 2
+        nbytes, _ = model_bytes_and_flops(mcfg, n_layers, batch, mean_ctx, 0)
+        achieved = nbytes / (ms / steps / 1e3) / 1e9
+        return {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / pk["hbm_gbs"], "peaks": pk["source"]}
+
+    sizes = sorted({a.batch, *[int(x) for x in a.points.split(",") if x.strip()]})
+    engine = make_engine(cfg, sizes, max(a.steps, a.point_steps))
+    graphs = engine.runner.decode_graphs
+
     if a.workload == "mixed":
         n_req, n_out = 64, 256
         lens = torch.randint(128, 2049, (n_req,), generator=gen).tolist()
-        prompts = [random_prompt(n) for n in lens]
+        prompts = [random_prompt(cfg.vocab_size, n) for n in lens]
         sp = SamplingParams(max_new_tokens=n_out, temperature=0.7, seed=7, ignore_eos=True)
         # the first pass captures the CUDA graphs this workload needs (one per bucket of batch
         # size and context length, tens of milliseconds each); the second is the steady state
@@ -372,122 +486,76 @@ def main() -> int:
             "steps": engine.runner.steps_run - steps0, "preemptions": engine.scheduler.num_preemptions,
             "graph_replays": (graphs.replays if graphs else 0) - replays0, "dtype": "bf16", "data": "synthetic",
             "config": {"model": a.preset, "layers": layers, "layers_full": full.num_hidden_layers,
-                       "max_prefill_tokens": ecfg.max_prefill_tokens}}))
+                       "max_prefill_tokens": engine.cfg.max_prefill_tokens}}))
         return 0
 
-    # ---------------- prefill of one prompt, whole ----------------
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > L2
-    prompt = random_prompt(a.prefill_tokens)
-    prefill_ms = []
-    reps = (0 if a.no_prefill else 3 + 3) if a.profile != "prefill" else 3 + 1
-    for it in range(reps):
-        slot = cache.allocate_slot()
-        flush.zero_()
-        if a.profile == "prefill" and it == reps - 1:
-            torch.cuda.synchronize()
-            torch.cuda.profiler.start()
-        ms = timed(lambda: runner.step([SequenceInput(slot, prompt, 0, [len(prompt) - 1])]))
-        if a.profile == "prefill" and it == reps - 1:
-            torch.cuda.profiler.stop()
-        cache.release_slot(slot)
-        if it >= 3:
-            prefill_ms.append(ms)
-    prefill_ms = sorted(prefill_ms)[len(prefill_ms) // 2] if prefill_ms else float("nan")
-    _, prefill_flops = model_bytes_and_flops(cfg, layers, 1, 0, a.prefill_tokens)
-    prefill = {"value": a.prefill_tokens / (prefill_ms / 1e3), "tokens": a.prefill_tokens,
-               "ms": prefill_ms,
-               "frac": prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+    prefill = None if a.no_prefill else measure_prefill(engine, cfg, layers, a.profile == "prefill")
 
     # ---------------- decode, timed on the device ----------------
-    def fill_requests(batch):
-        slots = [cache.allocate_slot() for _ in range(batch)]
-        group = max(1, 8192 // a.context)
-        for i in range(0, batch, group):
-            runner.step([SequenceInput(s, random_prompt(a.context), 0, []) for s in slots[i:i + group]])
-        return slots
-
-    def device_decode(batch, steps, warmup, sample_clocks=False):
-        slots = fill_requests(batch)
-        total = steps + warmup
-        last = [SequenceInput(s, [0], a.context + total - 1, [0]) for s in slots]
-        for e in last:
-            cache.allocate(e.slot, e.num_computed + 1)
-        key = graphs._key(last)
-        cap = graphs.graphs.get(key) or graphs._capture(key, last)
-        lay = cap.layout
-        host = np.zeros((total, lay.size), dtype=np.int32)
-        for k in range(total):
-            graphs._fill(host[k], lay, [SequenceInput(s, [0], a.context + k, [0]) for s in slots])
-        pre = torch.from_numpy(host).pin_memory().to(dev)
-        ids_off, _ = lay.off["input_ids"]
-        tokens = torch.zeros(batch, dtype=torch.int32, device=dev)
-
-        def one(k):
-            nonlocal tokens
-            cap.static_meta.copy_(pre[k])
-            cap.static_meta[ids_off:ids_off + batch].copy_(tokens)
-            cap.graph.replay()
-            tokens = ops.argmax(cap.logits[:batch])
-
-        for k in range(warmup):
-            one(k)
-        sampler = ClockSampler()
-        if sample_clocks:
-            sampler.start()
-        n0 = ops.launch_count
-        if a.profile == "decode" and sample_clocks:
-            torch.cuda.synchronize()
-            torch.cuda.profiler.start()
-        ms = timed(lambda: [one(k) for k in range(warmup, total)])
-        if a.profile == "decode" and sample_clocks:
-            torch.cuda.profiler.stop()
-        per_graph = graphs.kernels_per_graph.get(key, 0)
-        launches = steps * (per_graph + 2) + (ops.launch_count - n0)
-        clocks = sampler.stop() if sample_clocks else None
-        for s in slots:
-            cache.release_slot(s)
-        return ms, launches, clocks, lay.size * 4
-
-    ms, launches, clocks, meta_bytes = device_decode(a.batch, a.steps, a.warmup, sample_clocks=True)
+    ms, launches, clocks = device_decode(engine, cfg, a.batch, a.steps, a.warmup, sample_clocks=True,
+                                         profile=a.profile == "decode")
     value = a.batch * a.steps / (ms / 1e3)
-    mean_ctx = a.context + a.warmup + a.steps / 2
-    decode_bytes, _ = model_bytes_and_flops(cfg, layers, a.batch, mean_ctx, 0)
-    achieved = decode_bytes / (ms / a.steps / 1e3) / 1e9
-    roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / pk["hbm_gbs"], "peaks": pk["source"]}
-
+    roofline = decode_roofline(cfg, layers, a.batch, a.steps, a.warmup, ms)
     points = {}
     for b in sizes:
-        if b == a.batch:
-            continue
-        pms, _, _, _ = device_decode(b, a.point_steps, a.warmup)
-        points[f"decode_b{b}"] = b * a.point_steps / (pms / 1e3)
+        if b != a.batch:
+            pms, _, _ = device_decode(engine, cfg, b, a.point_steps, a.warmup)
+            points[f"decode_b{b}"] = b * a.point_steps / (pms / 1e3)
+            points[f"decode_b{b}_frac"] = decode_roofline(cfg, layers, b, a.point_steps, a.warmup, pms)["frac"]
 
     # ---------------- decode end to end through Engine.step() ----------------
     e2e = None
     if not a.no_e2e:
         sp = SamplingParams(max_new_tokens=a.steps + a.warmup + 32, ignore_eos=True)   # nobody finishes inside the timed steps
         for _ in range(a.batch):
-            engine.add_request(prompt_ids=random_prompt(a.context), params=sp)
+            engine.add_request(prompt_ids=random_prompt(cfg.vocab_size, a.context), params=sp)
         while any(r.num_output == 0 for r in list(engine.scheduler.running) + list(engine.scheduler.waiting)):
             engine.step()                       # prefill, untimed
         for _ in range(a.warmup):
             engine.step()
         e2e_ms = timed(lambda: [engine.step() for _ in range(a.steps)])
         assert all(r.num_output + r.num_pending >= a.steps for r in engine.scheduler.running)
+        meta_bytes = max(c.layout.size for c in graphs.graphs.values()) * 4 if graphs and graphs.graphs else 0
         e2e = {"value": a.batch * a.steps / (e2e_ms / 1e3), "unit": "tokens/s",
+               "ms_per_step": e2e_ms / a.steps,
                "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": a.batch * 4}
         while engine.has_work():
             engine.step()
 
+    # ---------------- the same at a larger model's layer sizes, fewer layers ----------------
+    second = None
+    if a.second_preset and a.second_preset != "none" and a.profile is None:
+        del engine, graphs
+        import gc
+        gc.collect()
+        torch.cuda.empty_cache()
+        full2 = preset(a.second_preset)
+        l2 = min(a.second_layers, full2.num_hidden_layers)
+        cfg2 = preset(a.second_preset, num_hidden_layers=l2, max_window_layers=l2)
+        eng2 = make_engine(cfg2, [8, 64], a.point_steps)
+        second = {"model": a.second_preset, "layers": l2, "layers_full": full2.num_hidden_layers,
+                  "hidden": cfg2.hidden_size, "heads": cfg2.num_attention_heads,
+                  "kv_heads": cfg2.num_key_value_heads, "intermediate": cfg2.intermediate_size}
+        if not a.no_prefill:
+            pf = measure_prefill(eng2, cfg2, l2)
+            second.update(prefill_tok_s=pf["value"], prefill_ms=pf["ms"], prefill_frac=pf["frac"],
+                          prefill_replayed_ms=pf["replayed_ms"])
+        for b in (8, 64):
+            pms, _, _ = device_decode(eng2, cfg2, b, a.point_steps, a.warmup)
+            second[f"decode_b{b}"] = b * a.point_steps / (pms / 1e3)
+            second[f"decode_b{b}_frac"] = decode_roofline(cfg2, l2, b, a.point_steps, a.warmup, pms)["frac"]
+        del eng2
+
+    config = bench_config(a, cfg, full, layers)
+    if second is not None:
+        config["second_model"] = f"{second['model']} layer sizes, {second['layers']} of {second['layers_full']} layers"
     line = {
         "metric": "decode tok/s (bf16, 1 B200)", "value": value, "unit": "tokens/s", "n_gpus": 1,
         "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "impl": "ours",
-        "config": bench_config(a, cfg, full, layers),
+        "impl": "ours", "config": config,
         "e2e": e2e, "gpu_launches": launches, "clocks": clocks, "prefill": prefill,
-        "roofline": roofline, "points": points,
+        "roofline": roofline, "points": points, "points_" + (a.second_preset or "none"): second,
     }
     print(json.dumps(line))
     return 0

@@ -130,10 +130,59 @@ class StateGroup:
         self.array: Optional[torch.Tensor] = None
 
 
+def _element_size(dtype: torch.dtype) -> int:
+    return torch.empty(0, dtype=dtype).element_size()
+
+
+def group_page_bytes(cache_specs: dict, page_size: int, dtype: torch.dtype) -> dict:
+    """group key -> (spec, bytes of one page over all caches of the group), for the groups
+    of paged caches among ``cache_specs`` (cache id -> need)."""
+    count: dict = {}
+    specs: dict = {}
+    for spec in cache_specs.values():
+        if isinstance(spec, PagedKVSpec):
+            count[spec.group_key()] = count.get(spec.group_key(), 0) + 1
+            specs[spec.group_key()] = spec
+    item = _element_size(dtype)
+    return {k: (specs[k], n * 2 * specs[k].num_kv_heads * page_size * specs[k].head_dim * item)
+            for k, n in count.items()}
+
+
+def pages_for_budget(cache_specs: dict, byte_budget: int, page_size: int, dtype: torch.dtype,
+                     max_reqs: int, step_tokens: int) -> dict:
+    """Pages per group (page 0 included) that ``byte_budget`` bytes pay for.  Groups that keep
+    all keys get the same number of pages n, as many as fit.  A window group never needs more
+    than what ``max_reqs`` requests can hold at a time (the window, a step's new tokens and
+    two pages of rounding each), so it gets min(n, that) and the bytes saved go to the
+    others."""
+    groups = group_page_bytes(cache_specs, page_size, dtype)
+    if not groups:
+        return {}
+    cap = {}
+    for k, (spec, _) in groups.items():
+        if spec.window is not None:
+            cap[k] = 1 + max_reqs * (-(-(spec.window + step_tokens) // page_size) + 2)
+    lo, hi = 2, max(2, byte_budget // min(b for _, b in groups.values()))
+    def cost(n):
+        return sum(min(n, cap.get(k, n)) * b for k, (_, b) in groups.items())
+    if cost(lo) > byte_budget:
+        raise CacheError(f"{byte_budget} bytes do not pay for two pages in every cache group "
+                         f"({cost(lo)} bytes)")
+    while lo < hi:                       # the largest n whose cost fits
+        mid = (lo + hi + 1) // 2
+        if cost(mid) <= byte_budget:
+            lo = mid
+        else:
+            hi = mid - 1
+    return {k: min(lo, cap.get(k, lo)) for k in groups}
+
+
 class CacheManager:
-    def __init__(self, cache_specs: dict, num_pages: int, page_size: int, max_reqs: int,
+    def __init__(self, cache_specs: dict, num_pages, page_size: int, max_reqs: int,
                  max_seq_len: int, dtype: torch.dtype = torch.bfloat16, device="cuda",
                  allocate_device: bool = True):
+        """``num_pages``: pages of every group's pool (page 0 included), or a dict from
+        group key to the pages of that group (``pages_for_budget``)."""
         self.page_size, self.max_reqs = int(page_size), int(max_reqs)
         self.max_seq_len = int(max_seq_len)
         self.max_blocks = -(-self.max_seq_len // self.page_size)
@@ -151,7 +200,8 @@ class CacheManager:
         for key, cids in by_key.items():
             spec = specs[key]
             if isinstance(spec, PagedKVSpec):
-                g = PageGroup(key, spec, cids, num_pages, page_size, max_reqs)
+                n = num_pages[key] if isinstance(num_pages, dict) else num_pages
+                g = PageGroup(key, spec, cids, n, page_size, max_reqs)
                 self.page_groups[key] = g
             elif isinstance(spec, StateSpec):
                 g = StateGroup(key, spec, cids)
@@ -172,7 +222,7 @@ class CacheManager:
 
     def bytes_per_page(self) -> int:
         """Bytes of one page over all groups and caches (for sizing the pool)."""
-        item = torch.empty(0, dtype=self.dtype).element_size()
+        item = _element_size(self.dtype)
         return sum(len(g.cache_ids) * 2 * g.spec.num_kv_heads * g.page_size * g.spec.head_dim * item
                    for g in self.page_groups.values())
 
@@ -235,9 +285,12 @@ class CacheManager:
         return min(g.num_free for g in self.page_groups.values())
 
     def usable_pages(self) -> int:
-        if not self.page_groups:
+        """Pages a request can ever hold in the groups that keep all keys (they bound how
+        long a request may grow; a window group gives pages back as the window moves)."""
+        full = [g.num_pages - 1 for g in self.page_groups.values() if g.window is None]
+        if not full:
             return 1 << 30
-        return min(g.num_pages - 1 for g in self.page_groups.values())
+        return min(full)
 
     def can_allocate(self, slot: Optional[int], total_len: int) -> bool:
         """Whether every group can cover positions < total_len of the request in

@@ -25,6 +25,10 @@ class EngineConfig:
 
     # cache (sid/config.py:66-70)
     kv_pool_tokens: int = 256 * 1024     # tokens the page pool of each layer group holds
+    # If set (0 < f <= 1): the pools are sized instead from the device memory that is free
+    # once the weights are loaded: f of it pays for pages, shared between the groups by
+    # their bytes per page (a window group gets no more than its requests can ever hold).
+    gpu_memory_fraction: Optional[float] = None
     page_size: int = 16                  # tokens per page
     max_reqs: int = 256                  # per-request state slots (block-table rows)
     max_seq_len: int = 32768             # block-table width in tokens
@@ -33,6 +37,13 @@ class EngineConfig:
     # scheduling (sid/config.py:73-74)
     max_prefill_tokens: int = 8192       # token budget of one step; prompts are cut to fit
     max_decode_batch: int = 256          # sequences running at a time
+
+    # bfloat16 matrix products of more than 128 rows go to the library (cuBLAS), as all of
+    # the reference's do.  False: every product runs on the package's own kernel, whose
+    # order of summation depends on the weight's shape alone; a token's bfloat16 bits are
+    # then the same whatever its step holds (prompt portions are slower).  The switch is
+    # one per process: the engine built last sets it.
+    library_products: bool = True
 
     cuda_graphs: bool = True             # replay pure-decode steps as CUDA graphs
     async_scheduling: bool = True        # sampled tokens stay on the device for the next step;
@@ -52,6 +63,8 @@ class EngineConfig:
         for name in ("max_reqs", "max_seq_len", "max_prefill_tokens", "max_decode_batch"):
             if getattr(self, name) < 1:
                 raise ValueError(f"{name} must be positive")
+        if self.gpu_memory_fraction is not None and not 0.0 < self.gpu_memory_fraction <= 1.0:
+            raise ValueError("gpu_memory_fraction must be in (0, 1]")
         if self.max_prompt_len is None:
             self.max_prompt_len = self.max_seq_len
 

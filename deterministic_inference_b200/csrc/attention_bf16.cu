@@ -7,22 +7,6 @@
 
 #include "attention_bf16_kernels.cuh"
 
-// Phase clocks of the pipelined decode kernel (a development build only: compiled in
-// with -DDIB_DECODE_CLOCKS; CTA 0's first consumer group records clock64 at ten points
-// of each of its first 64 splits).
-#ifdef DIB_DECODE_CLOCKS
-__device__ long long dib_decode_clocks[64 * 10];
-#define DIB_CLOCK(item, i)                                                                    \
-  do {                                                                                        \
-    if (blockIdx.x == 0 && threadIdx.x == 0 && (item) < 64) dib_decode_clocks[(item) * 10 + (i)] = clock64(); \
-  } while (0)
-extern "C" int dib_decode_clocks_read(long long* host) {
-  return cudaMemcpyFromSymbol(host, dib_decode_clocks, sizeof(dib_decode_clocks)) == cudaSuccess ? 0 : -1;
-}
-#else
-#define DIB_CLOCK(item, i) do {} while (0)
-#endif
-
 // ------------------------------------------------------------------------------
 // Decode stage 1 with page-granular TMA loads.  The cache of a layer is a 2-D
 // matrix [pages * 2 * kv_heads * page_size rows, head_dim]; the keys (or values) of
@@ -110,7 +94,7 @@ template <int D, bool PIPE>
 __device__ __forceinline__ void decode_split_compute(
     __nv_bfloat16* sK, __nv_bfloat16* sV, const __nv_bfloat16* sQ, unsigned char* exch,
     unsigned long long* bar_k, unsigned parity_k, unsigned long long* bar_v, unsigned parity_v,
-    unsigned long long* rel_k, unsigned long long* rel_v, int tid, int bar_id, bool& dead, int ord,
+    unsigned long long* rel_k, unsigned long long* rel_v, int tid, int bar_id, bool& dead,
     const __nv_bfloat16* __restrict__ q, int b, int kvh, int split, int kv_len,
     float* __restrict__ part_o, float* __restrict__ part_lse, int max_splits, int Hq, int Hkv,
     float scale, int window) {
@@ -144,7 +128,6 @@ __device__ __forceinline__ void decode_split_compute(
 
   // ---- scores of this warp's 32 keys
   mbar_wait_once(bar_k, parity_k, dead, 1);
-  DIB_CLOCK(ord, 1);
   if (sQ != nullptr) {
     constexpr int QS = D + Q_ROW_PAD;
 #pragma unroll
@@ -171,7 +154,6 @@ __device__ __forceinline__ void decode_split_compute(
       mma_16816(s[np * 2 + 1], qf[ks], bf[2], bf[3]);
     }
   }
-  DIB_CLOCK(ord, 2);
   if (PIPE) {   // this warp has read its keys (and the query rows)
     __syncwarp();
     if (lane == 0) mbar_arrive(rel_k);
@@ -197,7 +179,6 @@ __device__ __forceinline__ void decode_split_compute(
     if ((lane & 3) == 0 && r0 + rr * 8 < G) sM[warp * 16 + r0 + rr * 8] = mx[rr];
   }
   group_sync(bar_id);
-  DIB_CLOCK(ord, 3);
   float M[2], msafe[2], sum[2] = {0.f, 0.f};
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
@@ -232,14 +213,12 @@ __device__ __forceinline__ void decode_split_compute(
   // ---- values; rows beyond the sequence are zeroed first (their probability is 0,
   // but 0 * garbage must stay 0)
   mbar_wait_once(bar_v, parity_v, dead, 2);
-  DIB_CLOCK(ord, 4);
   if (nvalid < DEC_SPLIT && tid >= nvalid) {
 #pragma unroll
     for (int c = 0; c < D / 8; ++c)
       *reinterpret_cast<uint4*>(sV + sw_off(tid, c * 8)) = make_uint4(0, 0, 0, 0);
   }
   dead = group_sync_any(bar_id, dead);   // probabilities, sums and zeroed rows are in place
-  DIB_CLOCK(ord, 5);
   if (dead) return;   // a wait ran out somewhere in the group: nothing of this split is written
 
   // ---- O[16 x WCOLS] = P[16 x 128] V[128 x this warp's columns]; rows >= G of P are
@@ -261,7 +240,6 @@ __device__ __forceinline__ void decode_split_compute(
       mma_16816(o[dp * 2 + 1], a, bf[2], bf[3]);
     }
   }
-  DIB_CLOCK(ord, 6);
 #pragma unroll
   for (int rr = 0; rr < 2; ++rr) {
     const int row = r0 + rr * 8;
@@ -278,7 +256,6 @@ __device__ __forceinline__ void decode_split_compute(
       if (warp == 0 && (lane & 3) == 0) part_lse[prow] = (M[rr] + log2f(L)) / LOG2E;
     }
   }
-  DIB_CLOCK(ord, 8);
   if (PIPE) {
     // rows of the V tile may have been zeroed: order that before the producer's next
     // copy into it, then hand it back
@@ -356,7 +333,7 @@ decode_attention_stage1_tma_kernel(const __grid_constant__ CUtensorMap map,
 
   bool dead = false;
   decode_split_compute<D, false>(sK, sV, nullptr, exch, &bars[0], 0, &bars[1], 0, nullptr, nullptr,
-                                 threadIdx.x, 0, dead, 64, q, b, kvh, split, kv_len, part_o, part_lse,
+                                 threadIdx.x, 0, dead, q, b, kvh, split, kv_len, part_o, part_lse,
                                  max_splits, Hq, Hkv, scale, window);
 }
 
@@ -547,7 +524,6 @@ decode_attention_stage1_pipe_kernel(const __grid_constant__ CUtensorMap map,
   pdl_wait(q);   // transitively, everything this kernel writes over has been read
   for (int n = g;; n += GROUPS) {
     const int ks = n % KS, vs = n % VS;
-    DIB_CLOCK(n / GROUPS, 0);
     // this group's own count of uses of the tile: every second use of a ring of odd length
     const unsigned par_k = ((KS % 2) ? (n / KS) >> 1 : n / KS) & 1;
     const unsigned par_v = ((VS % 2) ? (n / VS) >> 1 : n / VS) & 1;
@@ -562,7 +538,7 @@ decode_attention_stage1_pipe_kernel(const __grid_constant__ CUtensorMap map,
                                   n < KS ? nullptr : q_rows + (size_t)ks * G * QS,
                                   exch + (size_t)g * EXCH_BYTES,
                                   fk, par_k, fv, par_v, &empty_k[ks],
-                                  &empty_v[vs], tid, 1 + g, dead, g == 0 ? n / GROUPS : 64, q, it.b,
+                                  &empty_v[vs], tid, 1 + g, dead, q, it.b,
                                   it.kvh, it.split, it.kv_len, part_o, part_lse, max_splits, Hq, Hkv,
                                   scale, window);
   }
@@ -647,12 +623,12 @@ int launch_decode_tma(const void* q, void* out, const void* cache, long long num
   } else {
     const size_t smem = (size_t)2 * DEC_SPLIT * D * 2 + 16 + EXCH_BYTES + 1024;
     auto kern = decode_attention_stage1_tma_kernel<D>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static DeviceOnce attr_set;
+    if (!attr_set.done()) {
       if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
           cudaSuccess)
         return DIB_LAUNCH_FAILED;
-      attr_set = true;
+      attr_set.mark();
     }
     dib_launch(kern, dim3(Hkv, num_seqs, max_splits), dim3(DEC_THREADS), smem, st, *map,
                (const __nv_bfloat16*)q, bt, max_blocks, seq_lens, part_o, part_lse, max_splits, Hq, Hkv,
@@ -677,7 +653,14 @@ int dib_attention_bf16_status() {
   if (cudaMemcpyFromSymbol(&v, dib_attention_error_word, sizeof(int)) != cudaSuccess) return -1;
   return v;
 }
+int dib_attention_bf16_status_clear() {
+  const int v = 0;
+  return cudaMemcpyToSymbol(dib_attention_error_word, &v, sizeof(int)) == cudaSuccess ? 0 : -1;
+}
 int dib_attention_bf16_tile_rows() { return EXT_M; }
+// From how many splits on stage 2 runs as the kernel with a group of threads per chunk
+// (both kernels give the same bits; 49 unless set).
+void dib_attention_bf16_set_merge_wide_from(int n) { merge_wide_from() = n; }
 
 // Sequences with more than one new token.  q/out are the step's full [T, Hq, D]
 // tensors; tiles name (sequence, first token of the tile among its new tokens), with

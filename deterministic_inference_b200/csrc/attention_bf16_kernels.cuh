@@ -522,7 +522,9 @@ __global__ void decode_attention_stage2_kernel(const float* __restrict__ part_o,
     o_r[j] = (j < max_splits && (int)threadIdx.x < D) ? part_o[(row + j) * D + threadIdx.x] : 0.f;
   const int pos = kv_len - 1;
   const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int s0 = first_key / DEC_SPLIT, s1 = pos / DEC_SPLIT;
+  // (a caller that passes fewer splits than the sequence has keys for gets a result over
+  // the splits there are, never a read beyond the row)
+  const int s0 = first_key / DEC_SPLIT, s1 = min(pos / DEC_SPLIT, max_splits - 1);
   const int c0 = s0 / CH, c1 = s1 / CH;
   float M = NEG_BIG;
 #pragma unroll
@@ -597,7 +599,7 @@ decode_attention_stage2_wide_kernel(const float* __restrict__ part_o,
   }
   const int pos = kv_len - 1;
   const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int s0 = first_key / DEC_SPLIT, s1 = pos / DEC_SPLIT;
+  const int s0 = first_key / DEC_SPLIT, s1 = min(pos / DEC_SPLIT, max_splits - 1);
   const int c0 = s0 / CH, c1 = s1 / CH;
   // the largest lse of the sequence's splits (a maximum does not depend on the order):
   // every thread of a group over the group's chunks, then over the groups
@@ -657,6 +659,13 @@ decode_attention_stage2_wide_kernel(const float* __restrict__ part_o,
   }
 }
 
+// From how many splits on the merge runs as the kernel with a group of threads per chunk
+// (measurements and tests change it through dib_attention_bf16_set_merge_wide_from).
+static inline int& merge_wide_from() {
+  static int v = 49;
+  return v;
+}
+
 // Stage 2 of the split-KV decode attention: the kernel for at most 16 splits, or the
 // wide one.
 static inline void launch_decode_merge(const float* part_o, const float* part_lse, const int* seq_lens,
@@ -664,9 +673,7 @@ static inline void launch_decode_merge(const float* part_o, const float* part_ls
                                        int window, cudaStream_t st) {
   const int th = D < 32 ? 32 : (D + 31) / 32 * 32;
   const int chunks = (max_splits + 15) / 16;
-  // DIB200_MERGE_WIDE_FROM=n: the kernel with a group per chunk from n splits on (measurements)
-  const char* env = getenv("DIB200_MERGE_WIDE_FROM");
-  const int wide_from = env ? atoi(env) : 49;
+  const int wide_from = merge_wide_from();
   if (max_splits >= wide_from && max_splits > MERGE_CH && th <= 128 && chunks <= MERGE_MAX_CHUNKS)
     dib_launch(decode_attention_stage2_wide_kernel, dim3(num_seqs, Hq),
                dim3(th, chunks < MERGE_GROUPS ? chunks : MERGE_GROUPS), 0, st,
@@ -683,12 +690,12 @@ int launch_extend(const void* q, void* out, const void* cache, const int* bt, in
                   int window, cudaStream_t st) {
   const size_t smem = (size_t)(EXT_M + 4 * EXT_N) * (D + PAD) * sizeof(__nv_bfloat16);
   auto kern = extend_attention_kernel<D>;
-  static bool attr_set = false;  // once per instantiation; never during a stream capture
-  if (!attr_set && smem > 40 * 1024) {
+  static DeviceOnce attr_set;  // once per instantiation and device; never during a stream capture
+  if (smem > 40 * 1024 && !attr_set.done()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return DIB_LAUNCH_FAILED;
-    attr_set = true;
+    attr_set.mark();
   }
   dim3 grid(Hkv, num_tiles);   // x-then-y order: all kv heads of the longest tile first
   dib_launch(kern, dim3(grid), dim3(EXT_THREADS), smem, st, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,
@@ -707,12 +714,12 @@ int launch_decode(const void* q, void* out, const void* cache, const int* bt, in
   const size_t merge = (size_t)(4 * 16 * D + 2 * 4 * 16) * sizeof(float);
   if (merge > smem) smem = merge;
   auto kern = decode_attention_stage1_kernel<D>;
-  static bool attr_set = false;
-  if (!attr_set && smem > 40 * 1024) {
+  static DeviceOnce attr_set;
+  if (smem > 40 * 1024 && !attr_set.done()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return DIB_LAUNCH_FAILED;
-    attr_set = true;
+    attr_set.mark();
   }
   dim3 grid(Hkv, num_seqs, max_splits);
   dib_launch(kern, dim3(grid), dim3(DEC_THREADS), smem, st, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, bt,

@@ -30,35 +30,6 @@
 
 #include "attention_bf16_kernels.cuh"
 
-// Phase clocks of the two-tile kernel (a development build only, -DDIB_PREFILL_CLOCKS):
-// the longest CTA of kv head 0 records clock64 per key tile, for the MMA lane (slots
-// 0..5) and for the first softmax thread of tile B (slots 6..11).
-#ifdef DIB_PREFILL_CLOCKS
-__device__ long long dib_prefill_clocks[64 * 12];
-#define DIB_PCLOCK(it, slot)                                                              \
-  do {                                                                                    \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && (it) < 64) dib_prefill_clocks[(it) * 12 + (slot)] = clock64(); \
-  } while (0)
-extern "C" int dib_prefill_clocks_read(long long* host) {
-  return cudaMemcpyFromSymbol(host, dib_prefill_clocks, sizeof(dib_prefill_clocks)) == cudaSuccess ? 0 : -1;
-}
-__device__ unsigned long long dib_prefill_timeline[4096 * 3];
-#define DIB_PTIME(slot)                                                                   \
-  do {                                                                                    \
-    const unsigned bid = blockIdx.y * gridDim.x + blockIdx.x;                              \
-    if (threadIdx.x == 0 && bid < 4096) {                                                 \
-      if ((slot) == 2) { unsigned sm; asm volatile("mov.u32 %0, %%smid;" : "=r"(sm)); dib_prefill_timeline[bid * 3 + 2] = sm; } \
-      else dib_prefill_timeline[bid * 3 + (slot)] = global_timer_ns();                    \
-    }                                                                                     \
-  } while (0)
-extern "C" int dib_prefill_timeline_read(unsigned long long* host) {
-  return cudaMemcpyFromSymbol(host, dib_prefill_timeline, sizeof(dib_prefill_timeline)) == cudaSuccess ? 0 : -1;
-}
-#else
-#define DIB_PCLOCK(it, slot) do {} while (0)
-#define DIB_PTIME(slot) do {} while (0)
-#endif
-
 namespace {
 
 constexpr int TC_M = 128, TC_N = 128, TC_D = 128, TC_THREADS = 320;
@@ -506,12 +477,8 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
                                 int page_size, float scale, int window,
                                 int chunk_tiles, const int* __restrict__ tile_chunk, int max_chunks,
                                 float* __restrict__ part_o, float* __restrict__ part_ml) {
-  if (threadIdx.x == 0) DIB_PCLOCK(63, 0);
-  DIB_PTIME(0);
-  DIB_PTIME(2);
   if (threadIdx.x == 0) prefetch_tensormap(&map);
   pdl_prologue(q);
-  if (threadIdx.x == 0) DIB_PCLOCK(63, 1);
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
@@ -657,7 +624,6 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   __syncthreads();
   tc_fence_after();
   const unsigned tmem = *tmem_slot;
-  if (threadIdx.x == 0) DIB_PCLOCK(63, 2);
 
   if (warp == TMA_WARP || warp == PAIR_V_WARP) {
     // Keys and values of a key tile are fetched, waited for and handed back apart, each
@@ -716,9 +682,7 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
           if (active(x, i)) {
-            DIB_PCLOCK(i, x * 3);
             ok = mbar_wait(&p_full[x], uses[x] & 1);
-            DIB_PCLOCK(i, x * 3 + 1);
             if (!ok) break;
             ++uses[x];
             if (have_v < i) {
@@ -747,7 +711,6 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
             issue_s(x, i + 1);
           }
           if (x == 1 && i + 1 < ntiles) tc_commit(&k_empty[(i + 1) & 1]);   // both score products of key tile i+1
-          DIB_PCLOCK(i, x * 3 + 2);
         }
       }
       // ---- one tile alone: its scores of key tile i are in buffer (i - solo_from) & 1
@@ -756,7 +719,6 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
       for (int i = solo_from; i < ntiles && ok; ++i) {
         const int x = solo_x;
         const int buf = ((i - solo_from) & 1) ? 1 - x : x;
-        DIB_PCLOCK(i, 0);
         if (i + 1 < ntiles) {
           if (have_k < i + 1) {
             ok = mbar_wait(&k_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
@@ -764,14 +726,10 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
             have_k = i + 1;
             tc_fence_after();
           }
-          DIB_PCLOCK(i, 1);
           issue_s_to(x, 1 - buf, i + 1);
           tc_commit(&k_empty[(i + 1) & 1]);
         }
-        DIB_PCLOCK(i, 2);
-        DIB_PCLOCK(i, 3);
         ok = mbar_wait(&p_full[buf], uses[buf] & 1);
-        DIB_PCLOCK(i, 4);
         if (!ok) break;
         ++uses[buf];
         if (have_v < i) {
@@ -790,7 +748,6 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
         tc_commit(&v_empty[i & 1]);
         tc_commit(pv_done);
         if (i == ntiles - 1) tc_commit(&o_final[x]);
-        DIB_PCLOCK(i, 5);
       }
     }
   } else {
@@ -810,7 +767,6 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
     const int my_solo = x == solo_x ? solo_from : 0x7fffffff;
     for (int i = 0; i < ntiles && ok; ++i) {
       if (!active(x, i)) continue;
-      if (threadIdx.x == 128) DIB_PCLOCK(i, 6);
       const bool borrowed = i >= my_solo && ((i - my_solo) & 1);
       const int buf = borrowed ? 1 - x : x;
       const unsigned tmem_s = tmem + lane_base + buf * 128;
@@ -819,14 +775,12 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
       if (!ok) break;
       if (borrowed) ++uses_other; else ++uses_own;
       tc_fence_after();
-      if (threadIdx.x == 128) DIB_PCLOCK(i, 7);
       const int kbase = (j0 + i) * TC_N;
       const bool full = kbase >= lo && kbase + TC_N - 1 <= hi;   // no key of the tile is masked
       unsigned v[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tc_ld32(tmem_s + c * 32, v[c]);
       tc_wait_ld();
-      if (threadIdx.x == 128) DIB_PCLOCK(i, 8);
       // Four independent chains for the maximum and for the sum (a thread has few warps
       // beside it to hide the latency of one long chain).  Tiles without a masked key,
       // nearly all of them, take a path without the per-key tests.
@@ -897,7 +851,6 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
       }
       const float sum = (s4[0] + s4[1]) + (s4[2] + s4[3]);
       l += sum;
-      if (threadIdx.x == 128) DIB_PCLOCK(i, 9);
       // O of this tile is rescaled when a row of the warp raised its reference.  Its last
       // product completed before these scores did, except where the tile runs alone: there
       // the scores of key tile i were issued before the product of i - 1, which is waited
@@ -921,13 +874,10 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
       }
       tc_st32(tmem_s, v[0]);          // probabilities over the scores they came from
       tc_st32(tmem_s + 32, v[1]);
-      if (threadIdx.x == 128) DIB_PCLOCK(i, 10);
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[buf]);
-      if (threadIdx.x == 128) DIB_PCLOCK(i, 11);
     }
-    if (threadIdx.x == 0) DIB_PCLOCK(63, 3);
     if (ok && jl[x] >= jf[x]) {
       ok = mbar_wait(&o_final[x], 0);
       ok = __all_sync(0xffffffffu, ok);
@@ -975,11 +925,8 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
     }
   }
   if (!ok) atomicExch(&dib_attention_error_word, 1);
-  if (threadIdx.x == 0) DIB_PCLOCK(63, 4);
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) DIB_PCLOCK(63, 5);
-  DIB_PTIME(1);
   if (warp == MMA_WARP) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
   }
@@ -989,6 +936,7 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
 // 2^(m_c - M) over the chunks of the row's query tile, in chunk order.  A warp takes a
 // token (a lane four dimensions) and walks its query heads; tokens that the attention
 // kernel finished itself cost one look at their lengths.
+constexpr int MERGE_MAX = 16;     // chunks of one row
 __global__ void __launch_bounds__(256)
 extend_attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                               __nv_bfloat16* __restrict__ out, const int* __restrict__ cu_q_lens,
@@ -1016,11 +964,11 @@ extend_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
   // weights handed round by shuffles.
   for (int h0 = 0; h0 < Hq; h0 += 32) {
     const int hl = h0 + lane;
-    float w[8], inv = 0.f;     // at most 8 chunks of a row are merged here (see the launcher)
+    float w[MERGE_MAX], inv = 0.f;     // at most MERGE_MAX chunks of a row are merged here (see the launcher)
     {
-      float m[8], l[8], M = NEG_BIG, L = 0.f;
+      float m[MERGE_MAX], l[MERGE_MAX], M = NEG_BIG, L = 0.f;
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < MERGE_MAX; ++c) {
         m[c] = NEG_BIG;
         l[c] = 0.f;
         if (hl < Hq && c0 + c <= c1) {
@@ -1032,7 +980,7 @@ extend_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
         M = fmaxf(M, m[c]);
       }
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < MERGE_MAX; ++c) {
         w[c] = m[c] <= -1e29f ? 0.f : fast_exp2(m[c] - M);
         L += l[c] * w[c];
       }
@@ -1044,7 +992,7 @@ extend_attention_merge_kernel(const float* __restrict__ part_o, const float* __r
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < MERGE_MAX; ++c) {
         if (c0 + c > c1) break;     // uniform
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -1116,6 +1064,10 @@ int dib_attention_prefill_tc_status() {
   if (cudaMemcpyFromSymbol(&v, dib_attention_error_word, sizeof(int)) != cudaSuccess) return -1;
   return v;
 }
+int dib_attention_prefill_tc_status_clear() {
+  const int v = 0;
+  return cudaMemcpyToSymbol(dib_attention_error_word, &v, sizeof(int)) == cudaSuccess ? 0 : -1;
+}
 
 // Sequences with more than one new token; tiles name (sequence, first token of the
 // tile among its new tokens) with 128 / (Hq/Hkv) tokens per tile.  Returns -2 for
@@ -1134,12 +1086,12 @@ int dib_extend_attention_tc(const void* q, void* out, const void* cache, long lo
   const CUtensorMap* map = cache_map(cache, num_pages, Hkv, page_size, D);
   if (map == nullptr) return DIB_LAUNCH_FAILED;
   const size_t smem = 6 * TILE_BYTES + 10 * 8 + 16 + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static DeviceOnce attr_set;
+  if (!attr_set.done()) {
     if (cudaFuncSetAttribute(extend_attention_tc_kernel,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return DIB_LAUNCH_FAILED;
-    attr_set = true;
+    attr_set.mark();
   }
   dib_launch(extend_attention_tc_kernel, dim3(Hkv, num_tiles), dim3(TC_THREADS), smem, st, *map,
              (const __nv_bfloat16*)q, (__nv_bfloat16*)out, block_table, max_blocks, cu_q_lens,
@@ -1175,17 +1127,17 @@ int dib_extend_attention_tc_pair(const void* q, void* out, const void* cache, lo
   const CUtensorMap* map = cache_map(cache, num_pages, Hkv, page_size, D);
   if (map == nullptr) return DIB_LAUNCH_FAILED;
   const size_t smem = 6 * TILE_BYTES + 15 * 8 + 16 + 1024;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static DeviceOnce attr_set;
+  if (!attr_set.done()) {
     if (cudaFuncSetAttribute(extend_attention_tc_pair_kernel,
                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
       return DIB_LAUNCH_FAILED;
-    attr_set = true;
+    attr_set.mark();
   }
   if (chunk_tiles <= 0) {
     chunk_tiles = 0;
     max_chunks = 1;
-  } else if (max_chunks < 1 || max_chunks > 8 || tile_chunk == nullptr || part_o == nullptr || part_ml == nullptr ||
+  } else if (max_chunks < 1 || max_chunks > MERGE_MAX || tile_chunk == nullptr || part_o == nullptr || part_ml == nullptr ||
              token_seq == nullptr || num_tokens < 1) {
     return DIB_BAD_SIZE;
   }

@@ -87,7 +87,90 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
   return total;
 }
 
+// ---- the one order in which a row's sum of squares (the RMSNorm statistic) is added up,
+// whatever kernel, block size or launch form computes it, so that a row's norm never
+// depends on what else is in the launch: the row is cut into vectors of 4 consecutive
+// elements; a vector's sum is the chain fma(x3,x3, fma(x2,x2, fma(x1,x1, x0*x0))); 32
+// consecutive vectors (128 elements) form a group, added by the butterfly over the vector
+// index (partners 16, 8, 4, 2, 1 apart, missing vectors count as 0); the groups' sums are
+// added one after the other in index order.
+__device__ __forceinline__ float sumsq4(float x0, float x1, float x2, float x3) {
+  return __fmaf_rn(x3, x3, __fmaf_rn(x2, x2, __fmaf_rn(x1, x1, __fmul_rn(x0, x0))));
+}
+// VPT vectors per thread: thread `lane` of a warp holds the vectors VPT*lane .. VPT*lane +
+// VPT-1 of 32*VPT consecutive ones (VPT 1 or 2).  Returns the sum of the group this lane's
+// vectors belong to: the whole warp (VPT 1) or its half-warp (VPT 2).
+template <int VPT> __device__ __forceinline__ float sumsq_group(const float (&s)[VPT]);
+template <> __device__ __forceinline__ float sumsq_group<1>(const float (&s)[1]) {
+  float v = s[0];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <> __device__ __forceinline__ float sumsq_group<2>(const float (&s)[2]) {
+  float a = s[0], b = s[1];     // vector indices 2*lane and 2*lane + 1 inside the half-warp's group
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) {   // partners 16, 8, 4, 2 vectors apart: 8, 4, 2, 1 lanes
+    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, o));
+    b = __fadd_rn(b, __shfl_xor_sync(0xffffffffu, b, o));
+  }
+  return __fadd_rn(a, b);             // partner 1 vector apart: in this thread
+}
+// Block-wide: thread t holds, for iteration it, the vectors VPT*(it*blockDim.x + t) ..; the
+// block's threads cover the row's `num_vectors` vectors.  `scratch` holds at least
+// ceil(num_vectors / 32) floats.  Every thread gets the row's total.
+template <int ITERS, int VPT>
+__device__ __forceinline__ float sumsq_row(const float (&s)[ITERS][VPT], int num_vectors,
+                                           float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  __syncthreads();   // scratch may still be read from a previous call
+#pragma unroll
+  for (int it = 0; it < ITERS; ++it) {
+    const float g = sumsq_group<VPT>(s[it]);
+    const int group = (it * nwarps + warp) * VPT + (VPT == 2 ? (lane >> 4) : 0);
+    if ((lane & (VPT == 2 ? 15 : 31)) == 0 && group * 32 < num_vectors) scratch[group] = g;
+  }
+  __syncthreads();
+  const int groups = (num_vectors + 31) >> 5;
+  float total = scratch[0];
+  for (int g = 1; g < groups; ++g) total = __fadd_rn(total, scratch[g]);
+  return total;
+}
+// y = x * rstd * w and the rotate-half pair, with every rounding spelled out so that all
+// kernels that norm and rotate give the same bits.
+__device__ __forceinline__ float norm_scale(float x, float rstd, float w) {
+  return __fmul_rn(__fmul_rn(x, rstd), w);
+}
+__device__ __forceinline__ float rope_first(float x1, float x2, float c, float sn) {   // x1 cos - x2 sin
+  return __fmaf_rn(x1, c, -__fmul_rn(x2, sn));
+}
+__device__ __forceinline__ float rope_second(float x1, float x2, float c, float sn) {  // x2 cos + x1 sin
+  return __fmaf_rn(x2, c, __fmul_rn(x1, sn));
+}
+__device__ __forceinline__ float rms_rstd(float sumsq, int n, float eps) {
+  return __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq, (float)n), eps)));
+}
+
 static inline int ceil_div_host(long long a, long long b) { return (int)((a + b - 1) / b); }
+
+// "Done once on the current device": a kernel's attributes (its shared-memory limit) are
+// kept per device, so a set-up step done on one device has to be done again on the next.
+struct DeviceOnce {
+  unsigned long long mask[4] = {0, 0, 0, 0};   // devices 0..255
+  static int current() {
+    int dev = 0;
+    return cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 256 ? dev : -1;
+  }
+  bool done() const {
+    const int d = current();
+    return d >= 0 && ((mask[d >> 6] >> (d & 63)) & 1ull);
+  }
+  void mark() {
+    const int d = current();
+    if (d >= 0) mask[d >> 6] |= 1ull << (d & 63);
+  }
+};
 
 // ---- programmatic dependent launch
 // Every kernel of this package is launched with the attribute that lets it start
@@ -146,15 +229,17 @@ static inline void dib_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 }
 
 // ---- bounded wait on a shared-memory mbarrier.  A copy or a tensor-core operation
-// completes within microseconds; a wait that has lasted a second means the kernel's
-// bookkeeping is broken.  It then gives up and reports false, so that the kernel can
-// set its error word and end instead of spinning for good.
+// completes within microseconds; a wait that has lasted `limit_ns` (a second unless the
+// caller says otherwise) means the kernel's bookkeeping is broken.  It then gives up and
+// reports false, so that the kernel can set its error word and end instead of spinning
+// for good.
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity) {
+__device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned parity,
+                                          unsigned long long limit_ns = 1000000000ull) {
   const unsigned addr = (unsigned)__cvta_generic_to_shared(bar);
   unsigned long long t0 = 0;
   for (unsigned i = 1;; ++i) {
@@ -166,10 +251,10 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long* bar, unsigned pari
         : "r"(addr), "r"(parity)
         : "memory");
     if (ok) return true;
-    if ((i & 255u) == 0) {
+    if ((i & 63u) == 0) {
       const unsigned long long t = global_timer_ns();
       if (t0 == 0) t0 = t;
-      else if (t - t0 > 1000000000ull) return false;
+      else if (t - t0 > limit_ns) return false;
     }
   }
 }

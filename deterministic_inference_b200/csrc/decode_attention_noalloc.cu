@@ -1,7 +1,7 @@
 // dib_decode_attention_bf16_noalloc: the split-KV decode attention with its
 // scratch memory inside the library, for callers that cannot allocate (see
-// decode_attention_noalloc.h).  The kernels are the ones the regular entry point
-// launches.
+// decode_attention_noalloc.h).  The kernels are the row-copy first stage and the merge
+// that the regular entry point launches for shapes its TMA kernels do not take.
 #include "decode_attention_noalloc.h"
 
 #include "attention_bf16_kernels.cuh"
@@ -31,6 +31,16 @@ int scratch_for_current_device(float** out) {
 }  // namespace
 
 extern "C" {
+
+int dib_decode_attention_noalloc_status(void) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, dib_attention_error_word, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+int dib_decode_attention_noalloc_status_clear(void) {
+  const int v = 0;
+  return cudaMemcpyToSymbol(dib_attention_error_word, &v, sizeof(int)) == cudaSuccess ? 0 : -1;
+}
 
 long long dib_decode_attention_noalloc_scratch_needed(int num_seqs, int max_splits, int Hq, int D) {
   return (long long)num_seqs * Hq * max_splits * ((long long)D + 1);

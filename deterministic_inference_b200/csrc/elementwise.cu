@@ -48,7 +48,9 @@ __global__ void copy_rows16_kernel(const uint4* __restrict__ src, const int* __r
 // ---------------------------------------------------------------- RMSNorm
 // y = x * 1/sqrt(mean(x^2) + eps) * w; one block per row; the row is staged in
 // shared memory as float32.  With ADD: residual += x first (stored rounded to T),
-// and the norm reads the unrounded float32 sum; y overwrites x.
+// and the norm reads the unrounded float32 sum; y overwrites x.  This form serves row
+// widths the vector kernels do not take (not a multiple of the vector width); which form a
+// width gets never depends on the number of rows.
 template <typename T, bool ADD>
 __global__ void rms_norm_kernel(T* __restrict__ x, T* __restrict__ residual,
                                 const float* __restrict__ w, T* __restrict__ out,
@@ -68,10 +70,10 @@ __global__ void rms_norm_kernel(T* __restrict__ x, T* __restrict__ residual,
     ss += v * v;
   }
   const float total = block_sum(ss, scratch);
-  const float rstd = 1.0f / sqrtf(total / (float)H + eps);
+  const float rstd = rms_rstd(total, H, eps);
   T* dst = ADD ? x : out;
   for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    Elem<T>::store(dst + base + i, row[i] * rstd * w[i]);
+    Elem<T>::store(dst + base + i, norm_scale(row[i], rstd, w[i]));
   }
 }
 
@@ -113,29 +115,32 @@ __global__ void rms_norm_vec_kernel(T* __restrict__ x, T* __restrict__ residual,
                                     const float* __restrict__ w, T* __restrict__ out, int H,
                                     float eps) {
   pdl_prologue(x, residual);
-  constexpr int N = Vec<T>::N;
-  __shared__ float scratch[32];
+  constexpr int N = Vec<T>::N, VPT = N / 4;
+  __shared__ float scratch[128];
   const size_t base = (size_t)blockIdx.x * H;
   float v[ITERS][N];
-  float ss = 0.f;
+  float ss[ITERS][VPT];
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
     const int i = (it * blockDim.x + threadIdx.x) * N;
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) ss[it][k] = 0.f;
     if (i < H) {
       Vec<T>::load(x + base + i, v[it]);
       if (ADD) {
         float r[N];
         Vec<T>::load(residual + base + i, r);
 #pragma unroll
-        for (int k = 0; k < N; ++k) v[it][k] += r[k];
+        for (int k = 0; k < N; ++k) v[it][k] = __fadd_rn(v[it][k], r[k]);
         Vec<T>::store(residual + base + i, v[it]);
       }
 #pragma unroll
-      for (int k = 0; k < N; ++k) ss += v[it][k] * v[it][k];
+      for (int k = 0; k < VPT; ++k)
+        ss[it][k] = sumsq4(v[it][4 * k], v[it][4 * k + 1], v[it][4 * k + 2], v[it][4 * k + 3]);
     }
   }
-  const float total = block_sum(ss, scratch);
-  const float rstd = 1.0f / sqrtf(total / (float)H + eps);
+  const float total = sumsq_row<ITERS, VPT>(ss, H / 4, scratch);
+  const float rstd = rms_rstd(total, H, eps);
   T* dst = ADD ? x : out;
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
@@ -145,10 +150,10 @@ __global__ void rms_norm_vec_kernel(T* __restrict__ x, T* __restrict__ residual,
 #pragma unroll
       for (int k = 0; k < N; k += 4) {
         const float4 ww = *reinterpret_cast<const float4*>(w + i + k);
-        y[k] = v[it][k] * rstd * ww.x;
-        y[k + 1] = v[it][k + 1] * rstd * ww.y;
-        y[k + 2] = v[it][k + 2] * rstd * ww.z;
-        y[k + 3] = v[it][k + 3] * rstd * ww.w;
+        y[k] = norm_scale(v[it][k], rstd, ww.x);
+        y[k + 1] = norm_scale(v[it][k + 1], rstd, ww.y);
+        y[k + 2] = norm_scale(v[it][k + 2], rstd, ww.z);
+        y[k + 3] = norm_scale(v[it][k + 3], rstd, ww.w);
       }
       Vec<T>::store(dst + base + i, y);
     }
@@ -209,9 +214,9 @@ __global__ void qk_norm_rope_cache_kernel(
   }
   if (nw != nullptr) {
     ss = warp_sum(ss);
-    const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+    const float rstd = rms_rstd(ss, D, eps);
     __syncwarp();
-    for (int d = lane; d < D; d += 32) s[d] = s[d] * rstd * nw[d];
+    for (int d = lane; d < D; d += 32) s[d] = norm_scale(s[d], rstd, nw[d]);
   }
   __syncwarp();
 
@@ -224,8 +229,8 @@ __global__ void qk_norm_rope_cache_kernel(
     for (int d = lane; d < half; d += 32) {
       const float c = tab[d], sn = tab[half + d];
       const float x1 = s[d], x2 = s[d + half];
-      Elem<T>::store(dst + d, x1 * c - x2 * sn);
-      Elem<T>::store(dst + d + half, x2 * c + x1 * sn);
+      Elem<T>::store(dst + d, rope_first(x1, x2, c, sn));
+      Elem<T>::store(dst + d + half, rope_second(x1, x2, c, sn));
     }
     for (int d = rotary_dim + lane; d < D; d += 32) Elem<T>::store(dst + d, s[d]);
   } else {
@@ -328,13 +333,16 @@ __global__ void qk_norm_rope_cache_vec_kernel(
       dst = kv_cache + ((((size_t)page * 2 + kv) * Hkv + h) * page_size + off) * D;
     }
     if (nw != nullptr) {
-      float ss = 0.f;
+      // a lane's EPL consecutive elements as a chain of fused multiply-adds, the lanes by
+      // the butterfly: for heads of 128 (EPL 4) this is the order of a row's norm statistic
+      float ss = __fmul_rn(v[it][0], v[it][0]);
 #pragma unroll
-      for (int k = 0; k < EPL; ++k) ss += v[it][k] * v[it][k];
-      ss = warp_sum(ss);
-      const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+      for (int k = 1; k < EPL; ++k) ss = __fmaf_rn(v[it][k], v[it][k], ss);
+      const float one[1] = {ss};
+      ss = sumsq_group<1>(one);
+      const float rstd = rms_rstd(ss, D, eps);
 #pragma unroll
-      for (int k = 0; k < EPL; ++k) v[it][k] = v[it][k] * rstd * nw[lane * EPL + k];
+      for (int k = 0; k < EPL; ++k) v[it][k] = norm_scale(v[it][k], rstd, nw[lane * EPL + k]);
     }
     if (cos_sin != nullptr && (is_q || is_k)) {
       const float* tab = cos_sin + (size_t)pos[it] * D;
@@ -344,7 +352,7 @@ __global__ void qk_norm_rope_cache_vec_kernel(
       for (int k = 0; k < EPL; ++k) {
         const float partner = __shfl_xor_sync(0xffffffffu, v[it][k], 16);
         const float c = tab[j0 + k], sn = tab[D / 2 + j0 + k];
-        v[it][k] = upper ? (v[it][k] * c + partner * sn) : (v[it][k] * c - partner * sn);
+        v[it][k] = upper ? rope_second(partner, v[it][k], c, sn) : rope_first(v[it][k], partner, c, sn);
       }
     }
     Pack<T, EPL> o;
@@ -438,15 +446,18 @@ qk_norm_rope_cache_rows128_kernel(
       }
       const float* nw = is_q ? q_norm_w : k_norm_w;
       if (nw != nullptr) {
-        float ss = 0.f;
+        // The order of the one-warp-per-row kernel (a lane there holds 4 consecutive
+        // elements, lanes combine 16, 8, 4, 2, 1 apart), so both give the same bits: this
+        // lane holds that kernel's lanes 2l, 2l+1 (a) and 2l+16, 2l+17 (b).
+        float e = __fadd_rn(sumsq4(a[0], a[1], a[2], a[3]), sumsq4(b[0], b[1], b[2], b[3]));
+        float o = __fadd_rn(sumsq4(a[4], a[5], a[6], a[7]), sumsq4(b[4], b[5], b[6], b[7]));
 #pragma unroll
-        for (int k = 0; k < 8; ++k) ss = fmaf(a[k], a[k], ss);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) ss = fmaf(b[k], b[k], ss);
-        ss += __shfl_xor_sync(mask, ss, 4);
-        ss += __shfl_xor_sync(mask, ss, 2);
-        ss += __shfl_xor_sync(mask, ss, 1);
-        const float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+        for (int sh = 4; sh > 0; sh >>= 1) {
+          e = __fadd_rn(e, __shfl_xor_sync(mask, e, sh));
+          o = __fadd_rn(o, __shfl_xor_sync(mask, o, sh));
+        }
+        const float ss = __fadd_rn(e, o);
+        const float rstd = rms_rstd(ss, D, eps);
         const float4 w0 = *reinterpret_cast<const float4*>(nw + l * 8);
         const float4 w1 = *reinterpret_cast<const float4*>(nw + l * 8 + 4);
         const float4 w2 = *reinterpret_cast<const float4*>(nw + 64 + l * 8);
@@ -455,8 +466,8 @@ qk_norm_rope_cache_rows128_kernel(
         const float wb[8] = {w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          a[k] = a[k] * rstd * wa[k];
-          b[k] = b[k] * rstd * wb[k];
+          a[k] = norm_scale(a[k], rstd, wa[k]);
+          b[k] = norm_scale(b[k], rstd, wb[k]);
         }
       }
       if (cos_sin != nullptr) {
@@ -465,8 +476,8 @@ qk_norm_rope_cache_rows128_kernel(
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const float x = a[k], y = b[k];
-          a[k] = x * c[k] - y * sn[k];
-          b[k] = y * c[k] + x * sn[k];
+          a[k] = rope_first(x, y, c[k], sn[k]);
+          b[k] = rope_second(x, y, c[k], sn[k]);
         }
       }
       __nv_bfloat162* ql = reinterpret_cast<__nv_bfloat162*>(&lo[it]);
@@ -573,21 +584,22 @@ __global__ void sum_split_kernel(const float* __restrict__ parts, T* __restrict_
 
 // residual += x (stored rounded), out = rms_norm(unrounded sum), x given as partials.
 template <typename T, int ITERS>
-__global__ void __launch_bounds__(ITERS == 4 ? 1024 : 512)
+__global__ void __launch_bounds__(ITERS >= 4 ? 1024 : 512)
 add_rms_norm_split_kernel(const float* __restrict__ parts, int S,
                                           long long split_stride, T* __restrict__ residual,
                                           const float* __restrict__ w, T* __restrict__ out, int H,
                                           float eps) {
   pdl_prologue(parts, residual);
-  __shared__ float scratch[32];
+  __shared__ float scratch[128];
   const size_t base = (size_t)blockIdx.x * H;
   float v[ITERS][4];
-  float ss = 0.f;
+  float ss[ITERS][1];
   // The kernel is a chain of memory round-trips, so it makes few of them: the residual
   // and up to 16 partials of an element are requested together, then added in split order.
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
     const int i = (it * blockDim.x + threadIdx.x) * 4;
+    ss[it][0] = 0.f;
     if (i < H) {
       const Pack<T, 4> r = *reinterpret_cast<const Pack<T, 4>*>(residual + base + i);
       float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -602,16 +614,14 @@ add_rms_norm_split_kernel(const float* __restrict__ parts, int S,
         for (int j = 0; j < BATCH; ++j)
           if (sp0 + j < S) { a.x += p[j].x; a.y += p[j].y; a.z += p[j].z; a.w += p[j].w; }
       }
-      v[it][0] = round_to<T>(a.x) + Elem<T>::load(&r.e[0]);
-      v[it][1] = round_to<T>(a.y) + Elem<T>::load(&r.e[1]);
-      v[it][2] = round_to<T>(a.z) + Elem<T>::load(&r.e[2]);
-      v[it][3] = round_to<T>(a.w) + Elem<T>::load(&r.e[3]);
+      v[it][0] = __fadd_rn(round_to<T>(a.x), Elem<T>::load(&r.e[0]));
+      v[it][1] = __fadd_rn(round_to<T>(a.y), Elem<T>::load(&r.e[1]));
+      v[it][2] = __fadd_rn(round_to<T>(a.z), Elem<T>::load(&r.e[2]));
+      v[it][3] = __fadd_rn(round_to<T>(a.w), Elem<T>::load(&r.e[3]));
       Pack<T, 4> o;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        Elem<T>::store(&o.e[k], v[it][k]);
-        ss += v[it][k] * v[it][k];
-      }
+      for (int k = 0; k < 4; ++k) Elem<T>::store(&o.e[k], v[it][k]);
+      ss[it][0] = sumsq4(v[it][0], v[it][1], v[it][2], v[it][3]);
       *reinterpret_cast<Pack<T, 4>*>(residual + base + i) = o;
     }
   }
@@ -621,17 +631,17 @@ add_rms_norm_split_kernel(const float* __restrict__ parts, int S,
     const int i = (it * blockDim.x + threadIdx.x) * 4;
     ww[it] = i < H ? *reinterpret_cast<const float4*>(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  const float total = block_sum(ss, scratch);
-  const float rstd = 1.0f / sqrtf(total / (float)H + eps);
+  const float total = sumsq_row<ITERS, 1>(ss, H / 4, scratch);
+  const float rstd = rms_rstd(total, H, eps);
 #pragma unroll
   for (int it = 0; it < ITERS; ++it) {
     const int i = (it * blockDim.x + threadIdx.x) * 4;
     if (i < H) {
       Pack<T, 4> o;
-      Elem<T>::store(&o.e[0], v[it][0] * rstd * ww[it].x);
-      Elem<T>::store(&o.e[1], v[it][1] * rstd * ww[it].y);
-      Elem<T>::store(&o.e[2], v[it][2] * rstd * ww[it].z);
-      Elem<T>::store(&o.e[3], v[it][3] * rstd * ww[it].w);
+      Elem<T>::store(&o.e[0], norm_scale(v[it][0], rstd, ww[it].x));
+      Elem<T>::store(&o.e[1], norm_scale(v[it][1], rstd, ww[it].y));
+      Elem<T>::store(&o.e[2], norm_scale(v[it][2], rstd, ww[it].z));
+      Elem<T>::store(&o.e[3], norm_scale(v[it][3], rstd, ww[it].w));
       *reinterpret_cast<Pack<T, 4>*>(out + base + i) = o;
     }
   }
@@ -713,19 +723,22 @@ int launch_rms(void* x, void* res, const float* w, void* out, int rows, int H, f
                        (res == nullptr || reinterpret_cast<uintptr_t>(res) % 16 == 0) &&
                        (out == nullptr || reinterpret_cast<uintptr_t>(out) % 16 == 0) &&
                        (reinterpret_cast<uintptr_t>(w) % 16 == 0);
-  // few rows: a wide block (more loads in flight per row); many rows: 256 threads
+  // few rows: a wide block (more loads in flight per row); many rows: 256 threads.  The
+  // block's width changes who holds which elements, not the order of the row's sums.
   const int th_max = rows <= 64 ? 1024 : 256;
-  if (H % N == 0 && aligned && H / N <= 4 * th_max) {   // at most 4 vectors per thread
+  if (H % N == 0 && aligned && H / N <= 4096) {   // at most 4 (16) vectors per thread
     const int vecs = H / N;
     int th = 32;
     while (th < vecs && th < th_max) th <<= 1;
     const int iters = (vecs + th - 1) / th;
-    if (iters == 1)
-      dib_launch(rms_norm_vec_kernel<T, ADD, 1>, dim3(rows), dim3(th), 0, st, (T*)x, (T*)res, w, (T*)out, H, eps);
-    else if (iters == 2)
-      dib_launch(rms_norm_vec_kernel<T, ADD, 2>, dim3(rows), dim3(th), 0, st, (T*)x, (T*)res, w, (T*)out, H, eps);
-    else
-      dib_launch(rms_norm_vec_kernel<T, ADD, 4>, dim3(rows), dim3(th), 0, st, (T*)x, (T*)res, w, (T*)out, H, eps);
+#define DIB_RMS(IT) \
+  dib_launch(rms_norm_vec_kernel<T, ADD, IT>, dim3(rows), dim3(th), 0, st, (T*)x, (T*)res, w, (T*)out, H, eps)
+    if (iters == 1) DIB_RMS(1);
+    else if (iters == 2) DIB_RMS(2);
+    else if (iters <= 4) DIB_RMS(4);
+    else if (iters <= 8) DIB_RMS(8);
+    else DIB_RMS(16);
+#undef DIB_RMS
     DIB_CHECK_LAUNCH();
     return DIB_OK;
   }
@@ -826,7 +839,7 @@ int dib_qk_norm_rope_cache_split(const void* qkv, const float* parts, int S, lon
                        reinterpret_cast<uintptr_t>(q_out) % 16 == 0 &&
                        reinterpret_cast<uintptr_t>(kv_cache) % 16 == 0;
   if (aligned && parts == nullptr && dtype == 1 && D == 128 && (cos_sin == nullptr || rotary_dim == D) &&
-      items >= 2048 && items < (1ll << 31) - 4096 && getenv("DIB200_QK_ROWS_OFF") == nullptr &&
+      items >= 2048 && items < (1ll << 31) - 4096 &&
       reinterpret_cast<uintptr_t>(q_norm_w) % 16 == 0 &&
       reinterpret_cast<uintptr_t>(k_norm_w) % 16 == 0 && reinterpret_cast<uintptr_t>(cos_sin) % 16 == 0) {
     // one row per group of eight lanes: with two, the registers of the second cost more

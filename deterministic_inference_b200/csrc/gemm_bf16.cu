@@ -375,12 +375,12 @@ int launch_swap_stages(const CUtensorMap& mw, const CUtensorMap& mx, void* out, 
   static_assert(!CLUSTER || ring >= (size_t)BM * (BN + 1) * 4, "the partial tile must fit in the ring");
   constexpr size_t smem = ring + (2 * STAGES + 1) * 8 + 16 + 1024;
   auto kern = gemm_swap_kernel<BN, OutT, GATED, STAGES, CLUSTER>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  static DeviceOnce attr_set;
+  if (!attr_set.done()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
         cudaSuccess)
       return DIB_LAUNCH_FAILED;
-    attr_set = true;
+    attr_set.mark();
   }
   if (CLUSTER) {
     cudaLaunchConfig_t cfg = {};
@@ -455,9 +455,21 @@ long long cost_of(long long ctas, int per, int sm_count) {
 // unless DIB200_GEMM_CLUSTER=1: it measured slower on B200 (N=4096, K=1024, 8 splits: 6.2
 // against 2.7 us with 8 rows, 18.7 against 4.7 us with 64 rows; the cluster launch and
 // its two barriers alone cost 2 us, the reads from the peers' shared memory the rest).
+int& cluster_option() {
+  static int v = -1;     // -1: not yet read from the environment (read once)
+  return v;
+}
 bool cluster_enabled() {
-  const char* e = getenv("DIB200_GEMM_CLUSTER");
-  return e != nullptr && e[0] == '1';
+  int& v = cluster_option();
+  if (v < 0) {
+    const char* e = getenv("DIB200_GEMM_CLUSTER");
+    v = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+int& forced_splits_option() {
+  static int v = -1;     // -1: not yet read; 0: the model's choice
+  return v;
 }
 constexpr int MAX_CLUSTER = 8;
 
@@ -484,13 +496,19 @@ long long plan_cost(int n_tiles, int num_kb, int sm_count, int* per_out) {
   return best;
 }
 
-// k-blocks per split: the model's choice, or DIB200_GEMM_SPLITS=n splits (measurements, tests)
+// k-blocks per split: the model's choice, or a forced number of splits (DIB200_GEMM_SPLITS=n
+// in the environment when the library is first used, or dib_gemm_bf16_configure)
 int planned_per(int n_tiles, int num_kb, int sm_count) {
   int per = num_kb;
   plan_cost(n_tiles, num_kb, sm_count, &per);
-  if (const char* forced = getenv("DIB200_GEMM_SPLITS")) {
-    const int want = atoi(forced);
-    if (want >= 1) per = (num_kb + want - 1) / want;
+  int& forced = forced_splits_option();
+  if (forced < 0) {
+    const char* e = getenv("DIB200_GEMM_SPLITS");
+    forced = e != nullptr ? atoi(e) : 0;
+    if (forced < 0) forced = 0;
+  }
+  if (forced >= 1) {
+    per = (num_kb + forced - 1) / forced;
     if (per < 1) per = 1;
   }
   return per;
@@ -504,6 +522,21 @@ int dib_gemm_bf16_status() {
   int v = 0;
   if (cudaMemcpyFromSymbol(&v, dib_gemm_error_word, sizeof(int)) != cudaSuccess) return -1;
   return v;
+}
+// Measurement and test switches (both are read from the environment once, at first use):
+// cluster 0/1: the CTAs of a tile add their partial tiles up as a thread-block cluster;
+// forced_splits 0: the model's choice of the split of k, n >= 1: n splits.  A negative
+// value leaves a switch as it is.
+void dib_gemm_bf16_configure(int cluster, int forced_splits) {
+  cluster_enabled();
+  if (cluster >= 0) cluster_option() = cluster ? 1 : 0;
+  if (forced_splits >= 0) forced_splits_option() = forced_splits;
+  else if (forced_splits_option() < 0) forced_splits_option() = 0;
+}
+// Sets the error word back to 0 (after the failure has been reported).
+int dib_gemm_bf16_status_clear() {
+  const int v = 0;
+  return cudaMemcpyToSymbol(dib_gemm_error_word, &v, sizeof(int)) == cudaSuccess ? 0 : -1;
 }
 
 // How the product of these sizes is cut: tokens per tile, k-blocks per split, number

@@ -174,37 +174,68 @@ def describe_step(entries: list, cache) -> StepShape:
 def fill_packed(host: np.ndarray, lay: PackedLayout, shape: StepShape, cache, group_list: list) -> int:
     """Write the step's integer metadata into the packed array ``host`` laid out by
     ``lay`` (block tables ``lay.width`` >= ``shape.width`` pages wide).  Returns the number
-    of tokens that are to be patched in from the previous step's samples."""
+    of tokens that are to be patched in from the previous step's samples.
+
+    ``lay`` may hold more sequences than the step has (a captured decode graph is made
+    for a bucket of batch sizes): the rest are padding sequences of one token each that
+    live on page 0 and state slot 0, which no request owns, at position 0 with a key
+    count of 1; each asks for one logits row, which the caller drops."""
     host[:] = 0
     seqs, q_lens = shape.seqs, shape.q_lens
+    n_pad = lay.b - len(seqs)
+    if n_pad < 0 or lay.t - shape.t != n_pad or lay.r - len(shape.logit_index) not in (0, n_pad):
+        raise ValueError(f"layout of {lay.b} sequences / {lay.t} tokens does not fit a step of "
+                         f"{len(seqs)} sequences / {shape.t} tokens")
+    if n_pad and shape.num_decode != len(seqs):
+        raise ValueError("only steps of one-token sequences are padded")
     ids, pos, tseq = lay.seg(host, "input_ids"), lay.seg(host, "positions"), lay.seg(host, "token_seq")
     cu = lay.seg(host, "cu_q_lens")
-    start = 0
-    for bi, e in enumerate(seqs):
-        q = q_lens[bi]
-        ids[start:start + q] = e.tokens
-        pos[start:start + q] = np.arange(e.num_computed, e.num_computed + q)
-        tseq[start:start + q] = bi
-        cu[bi + 1] = start + q
-        start += q
-    lay.seg(host, "seq_lens")[:] = shape.kv_lens
-    lay.seg(host, "state_slots")[:] = shape.slots
-    lay.seg(host, "logit_indices")[:] = shape.logit_index
     pdst, psrc = lay.seg(host, "patch_dst"), lay.seg(host, "patch_src")
     pdst[:] = -1
     num_patches = 0
+    start = 0
     for bi, e in enumerate(seqs):
+        q = q_lens[bi]
+        if q == 1:
+            ids[start] = e.tokens[0]
+            pos[start] = e.num_computed
+        else:
+            ids[start:start + q] = e.tokens
+            pos[start:start + q] = np.arange(e.num_computed, e.num_computed + q)
+        tseq[start:start + q] = bi
+        start += q
+        cu[bi + 1] = start
         if e.pending_row >= 0:
-            pdst[bi] = int(cu[bi + 1]) - 1       # the sequence's last token
+            pdst[bi] = start - 1                 # the sequence's last token
             psrc[bi] = e.pending_row
             num_patches += 1
+    n = len(seqs)
+    lay.seg(host, "seq_lens")[:n] = shape.kv_lens
+    lay.seg(host, "state_slots")[:n] = shape.slots
+    lay.seg(host, "logit_indices")[:len(shape.logit_index)] = shape.logit_index
+    if n_pad:
+        tseq[start:] = np.arange(n, lay.b)
+        cu[n + 1:] = np.arange(start + 1, start + n_pad + 1)
+        lay.seg(host, "seq_lens")[n:] = 1
+        if lay.r > len(shape.logit_index):
+            lay.seg(host, "logit_indices")[len(shape.logit_index):] = np.arange(start, start + n_pad)
     for gi, g in enumerate(group_list):
-        lay.seg(host, ("bt", gi))[:] = cache.block_table(g, shape.slots, lay.width).reshape(-1)
+        bt = lay.seg(host, ("bt", gi)).reshape(lay.b, lay.width)
         sm = lay.seg(host, ("sm", gi))
+        ps = g.page_size
         start = 0
         for bi, e in enumerate(seqs):
+            pl = g.pages[e.slot]
+            m = min(len(pl), lay.width)
+            bt[bi, :m] = pl[:m]
             q = q_lens[bi]
-            sm[start:start + q] = cache.slot_mapping(g, e.slot, e.num_computed, q)
+            if q == 1:
+                page = pl[e.num_computed // ps]
+                if page == 0:
+                    raise ValueError(f"slot {e.slot}: position {e.num_computed} is not covered by a page")
+                sm[start] = page * ps + e.num_computed % ps
+            else:
+                sm[start:start + q] = cache.slot_mapping(g, e.slot, e.num_computed, q)
             start += q
     return num_patches
 

@@ -74,10 +74,7 @@ class Engine:
         self._pool_capacity = self.cache.usable_pages() * cfg.page_size
         self._inflight = None
         self.async_scheduling = cfg.async_scheduling
-        self.decode_graphs = None
-        if cfg.cuda_graphs and self.runner.device.type == "cuda":
-            from .graphs import DecodeGraphs
-            self.decode_graphs = DecodeGraphs(self.runner)
+        self.decode_graphs = self.runner.decode_graphs
 
     # ---- public API -----------------------------------------------------------
 
@@ -144,9 +141,11 @@ class Engine:
         return [self._output(self._done.pop(rid)) for rid in rids]
 
     def check_kernels(self) -> None:
-        """Raise if a bounded wait inside a kernel ran out since the engine started (the
-        kernels then set an error word and end instead of spinning; their results are not
-        valid).  ``generate`` calls it at its end, ``step`` every 256 steps; it synchronises."""
+        """Raise if a bounded wait inside a kernel ran out since the last check (the kernels
+        then set an error word and end instead of spinning; their results are not valid).
+        The words are read after the first launched step, after the warm-up of every graph
+        capture, every 32 steps and at the end of ``generate``; reading synchronises.  A
+        failure is reported once: the words are cleared when it is raised."""
         if self.runner.device.type == "cuda":
             from ..kernels import ops
             ops.check_kernel_status()
@@ -165,7 +164,7 @@ class Engine:
         that turns out to have stopped on an end-of-sequence token has then been fed
         one token too many; that result is dropped."""
         self._steps_since_check = getattr(self, "_steps_since_check", 0) + 1
-        if self._steps_since_check >= 256:
+        if self._steps_since_check >= 32:
             self._steps_since_check = 0
             self.check_kernels()
         nvtx = _NVTX and self.runner.device.type == "cuda"
@@ -201,11 +200,8 @@ class Engine:
             entries.append(SequenceInput(r.slot, r.next_tokens(n), r.num_computed,
                                          [n - 1] if last else [], pending_row))
         prev_tokens = prev.tokens_dev if prev is not None else None
-        if self.decode_graphs is not None and self.decode_graphs.usable(entries):
-            logits, rows = self.decode_graphs.run(entries, prev_tokens)
-        else:
-            logits, batch = self.runner.step(entries, prev_tokens)
-            rows = batch.logit_rows
+        logits, batch = self.runner.step(entries, prev_tokens)
+        rows = batch.logit_rows
         row_req: list = [None] * logits.shape[0]
         for i, s in enumerate(sched):
             s.request.num_computed += s.num_tokens

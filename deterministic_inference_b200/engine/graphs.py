@@ -70,9 +70,10 @@ class _Captured:
 
 
 class DecodeGraphs:
-    def __init__(self, runner, max_batch: int = 256, min_width: int = 8):
-        self.runner = runner
-        self.cache = runner.cache
+    def __init__(self, model, cache, device, max_batch: int = 256, min_width: int = 8):
+        # the model, the cache and the device, not the runner that owns this object: a
+        # cycle would leave captured graphs to the garbage collector
+        self.model, self.cache, self.device = model, cache, device
         self.max_batch = max_batch
         self.min_width = min_width
         self.graphs: dict[tuple, _Captured] = {}
@@ -81,84 +82,59 @@ class DecodeGraphs:
         self.captures = 0
         self.capture_seconds = 0.0
         self.kernels_per_graph: dict[tuple, int] = {}
+        self.kernels_replayed = 0          # kernels inside the graphs replayed so far
         # one memory pool for all graphs of this object: only one of them runs at a time,
         # and what a replay leaves (its logits) is read before the next replay is issued
         self.pool = torch.cuda.graph_pool_handle() if torch.cuda.is_available() else None
 
     def usable(self, entries) -> bool:
-        return (0 < len(entries) <= self.max_batch
+        """Pure-decode steps only; and not while a part keeps per-request state: the
+        capture runs the model twice as a warm-up, which would advance that state, and
+        such a part may read its slots on the host."""
+        return (not self.cache.state_groups and 0 < len(entries) <= self.max_batch
                 and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries))
 
     # ---- capture ---------------------------------------------------------------
 
-    def _key(self, entries) -> tuple:
-        ps = self.cache.page_size
-        width = max(-(-(e.num_computed + 1) // ps) for e in entries)
+    def _key(self, shape) -> tuple:
         # block-table width: powers of two up to 32 pages, then multiples of 32 (grids
         # sized for the width's longest sequence should not be mostly empty)
+        width = shape.width
         wb = _bucket(width, self.min_width) if width <= 32 else -(-width // 32) * 32
-        return (_bucket(len(entries)), min(wb, self.cache.max_blocks))
+        return (_bucket(len(shape.seqs)), min(wb, self.cache.max_blocks))
 
-    def _fill(self, host: np.ndarray, lay: PackedLayout, entries) -> None:
-        """Packed metadata of a pure-decode step, padded to the bucket."""
-        n, bb, w = len(entries), lay.b, lay.width
-        host[:] = 0
-        ids, pos = lay.seg(host, "input_ids"), lay.seg(host, "positions")
-        lay.seg(host, "token_seq")[:] = np.arange(bb)
-        lay.seg(host, "cu_q_lens")[:] = np.arange(bb + 1)
-        lay.seg(host, "logit_indices")[:] = np.arange(bb)
-        seq_lens = lay.seg(host, "seq_lens")
-        seq_lens[:] = 1
-        slots = lay.seg(host, "state_slots")
-        pdst, psrc = lay.seg(host, "patch_dst"), lay.seg(host, "patch_src")
-        pdst[:] = -1
-        for i, e in enumerate(entries):
-            if e.pending_row >= 0:
-                pdst[i], psrc[i] = i, e.pending_row
-            ids[i] = e.tokens[0]
-            pos[i] = e.num_computed
-            seq_lens[i] = e.num_computed + 1
-            slots[i] = e.slot
-        for gi, g in enumerate(self.group_list):
-            bt = lay.seg(host, ("bt", gi)).reshape(bb, w)
-            sm = lay.seg(host, ("sm", gi))
-            for i, e in enumerate(entries):
-                pl = g.pages[e.slot]
-                m = min(len(pl), w)
-                bt[i, :m] = pl[:m]
-                sm[i] = pl[e.num_computed // g.page_size] * g.page_size + e.num_computed % g.page_size
-
-    def _capture(self, key: tuple, entries) -> _Captured:
+    def _capture(self, key: tuple, shape) -> _Captured:
         t0 = time.perf_counter()
-        cap = self._capture_timed(key, entries)
+        cap = self._capture_timed(key, shape)
         self.captures += 1
         self.capture_seconds += time.perf_counter() - t0
         return cap
 
-    def _capture_timed(self, key: tuple, entries) -> _Captured:
+    def _capture_timed(self, key: tuple, shape) -> _Captured:
         bb, w = key
-        dev = self.runner.device
+        dev = self.device
         lay = PackedLayout(bb, bb, bb, w, len(self.group_list))
         host = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
         static = torch.zeros(lay.size, dtype=torch.int32, device=dev)
         upper = w * self.cache.page_size
         batch = step_views(static, lay, self.group_list, [1] * bb, [upper] * bb, [0] * bb, bb,
                            [[i] for i in range(bb)], list(range(bb)))
-        self._fill(host.numpy(), lay, entries)
+        fill_packed(host.numpy(), lay, shape, self.cache, self.group_list)
         static.copy_(host, non_blocking=True)
         # warm up on a side stream (library handles, lazy module loading), then capture
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
             for _ in range(2):
-                self.runner.model.forward(batch, self.cache)
+                self.model.forward(batch, self.cache)
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         from ..kernels import ops
+        ops.check_kernel_status()        # the warm-up launched every kernel of the step
         n0 = ops.launch_count
         graph = torch.cuda.CUDAGraph()
         with _no_collection(), torch.cuda.graph(graph, pool=self.pool):
-            logits = self.runner.model.forward(batch, self.cache)
+            logits = self.model.forward(batch, self.cache)
         self.kernels_per_graph[key] = ops.launch_count - n0
         cap = _Captured(graph, static, host, lay, logits, batch)
         self.graphs[key] = cap
@@ -168,29 +144,28 @@ class DecodeGraphs:
 
     @torch.inference_mode()
     def run(self, entries, prev_tokens=None):
-        """Same contract as ``ModelRunner.step`` for a pure-decode batch: returns
-        (logits [B, V], rows per entry)."""
+        """(logits [B, V], StepBatch) for a pure-decode step whose pages are allocated
+        already.  The logits are a view of the graph's own buffer: they hold until the
+        next replay of a decode graph."""
         cache = self.cache
-        for e in entries:
-            cache.allocate(e.slot, e.num_computed + 1)
-        cache.reset_fresh_state()
-        key = self._key(entries)
+        shape = describe_step(entries, cache)
+        key = self._key(shape)
         cap = self.graphs.get(key)
         if cap is None:
-            cap = self._capture(key, entries)
-        cap.upload(lambda host: self._fill(host, cap.layout, entries))
-        if any(e.pending_row >= 0 for e in entries):
+            cap = self._capture(key, shape)
+        num_patches = cap.upload(
+            lambda host: fill_packed(host, cap.layout, shape, cache, self.group_list))
+        if num_patches:
             from ..kernels import ops
             ops.patch_token_ids(cap.batch.input_ids, cap.batch.patch_dst, cap.batch.patch_src,
                                 prev_tokens)
         cap.graph.replay()
-        for e in entries:
-            cache.release_passed(e.slot, e.num_computed + 1)
         self.replays += 1
-        self.runner.steps_run += 1
-        self.runner.tokens_run += len(entries)
-        n = len(entries)
-        return cap.logits[:n], [[i] for i in range(n)]
+        self.kernels_replayed += self.kernels_per_graph.get(key, 0)
+        batch = dataclasses.replace(cap.batch, logit_rows=shape.logit_rows, order=shape.order,
+                                    slots=shape.slots)
+        batch.num_patches = num_patches
+        return cap.logits[:len(entries)], batch
 
 
 class StepGraphs:
@@ -217,6 +192,8 @@ class StepGraphs:
         self.replays = 0
         self.captures = 0
         self.capture_seconds = 0.0
+        self.kernels_per_graph: dict[tuple, int] = {}
+        self.kernels_replayed = 0
         # one memory pool for all graphs (their activations never live at the same time;
         # a replay's logits are copied out before the next replay)
         self.pool = torch.cuda.graph_pool_handle() if torch.cuda.is_available() else None
@@ -256,6 +233,7 @@ class StepGraphs:
                                 prev_tokens)
         cap.graph.replay()
         self.replays += 1
+        self.kernels_replayed += self.kernels_per_graph.get(key, 0)
         batch = dataclasses.replace(cap.batch, logit_rows=shape.logit_rows, order=shape.order,
                                     slots=shape.slots)
         batch.num_patches = num_patches
@@ -280,11 +258,15 @@ class StepGraphs:
                 self.model.forward(batch, self.cache)
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
+        from ..kernels import ops
+        ops.check_kernel_status()        # the warm-up launched every kernel of the step
         while len(self.graphs) >= self.max_graphs:      # before the capture, not inside it
             self.graphs.popitem(last=False)
+        n0 = ops.launch_count
         graph = torch.cuda.CUDAGraph()
         with _no_collection(), torch.cuda.graph(graph, pool=self.pool):
             logits = self.model.forward(batch, self.cache)
+        self.kernels_per_graph[key] = ops.launch_count - n0
         cap = _Captured(graph, static, host, lay, logits, batch)
         self.graphs[key] = cap
         self.captures += 1

@@ -12,7 +12,7 @@ from __future__ import annotations
 
 import torch
 
-from ..cache.manager import CacheManager
+from ..cache.manager import CacheManager, pages_for_budget
 from ..config.engine_config import EngineConfig
 from ..models.registry import build_model, config_from_dir
 from ..weights.loader import load_weights
@@ -48,17 +48,29 @@ class ModelRunner:
                 tensors = random_tensors_on_device(specs, cfg.random_seed, self.dtype, self.device)
             self.model.load(tensors)
         self.max_positions = self.model.plan.max_positions
-        self.cache = CacheManager(self.model.cache_specs(), num_pages=cfg.num_pages + 1,
+        if self.dtype == torch.bfloat16 and self.device.type == "cuda":
+            from ..kernels import gemm_bf16
+            gemm_bf16.set_library_products(cfg.library_products)
+        num_pages = cfg.num_pages + 1
+        if cfg.gpu_memory_fraction is not None and self.device.type == "cuda":
+            free, _ = torch.cuda.mem_get_info(self.device)
+            num_pages = pages_for_budget(self.model.cache_specs(), int(free * cfg.gpu_memory_fraction),
+                                         cfg.page_size, self.dtype, cfg.max_reqs + 1,
+                                         cfg.max_prefill_tokens)
+        self.cache = CacheManager(self.model.cache_specs(), num_pages=num_pages,
                                   page_size=cfg.page_size, max_reqs=cfg.max_reqs + 1,
                                   max_seq_len=min(cfg.max_seq_len, self.max_positions),
                                   dtype=self.dtype, device=self.device)
         self.steps_run = 0
         self.tokens_run = 0
-        # steps whose shape comes again are replayed as CUDA graphs
-        self.step_graphs = None
+        # pure-decode steps, and steps of any other shape that come again, are replayed as
+        # CUDA graphs
+        self.step_graphs = self.decode_graphs = None
         if cfg.cuda_graphs and self.device.type == "cuda":
-            from .graphs import StepGraphs
+            from .graphs import DecodeGraphs, StepGraphs
             self.step_graphs = StepGraphs(self.model, self.cache, self.device)
+            self.decode_graphs = DecodeGraphs(self.model, self.cache, self.device)
+        self._checked_kernels = False
 
     @torch.inference_mode()
     def step(self, entries: list[SequenceInput], prev_tokens=None):
@@ -70,7 +82,11 @@ class ModelRunner:
         for e in entries:
             self.cache.allocate(e.slot, e.num_computed + len(e.tokens))
         self.cache.reset_fresh_state()
-        replayed = self.step_graphs.run(entries, prev_tokens) if self.step_graphs is not None else None
+        replayed = None
+        if self.decode_graphs is not None and self.decode_graphs.usable(entries):
+            replayed = self.decode_graphs.run(entries, prev_tokens)
+        elif self.step_graphs is not None:
+            replayed = self.step_graphs.run(entries, prev_tokens)
         if replayed is not None:
             logits, batch = replayed
         else:
@@ -79,8 +95,14 @@ class ModelRunner:
                 from ..kernels import ops
                 ops.patch_token_ids(batch.input_ids, batch.patch_dst, batch.patch_src, prev_tokens)
             logits = self.model.forward(batch, self.cache)
+            if not self._checked_kernels and self.device.type == "cuda":
+                # the first launched step loads the kernel libraries: read their error
+                # words once here (a synchronisation), later ones at the engine's checks
+                from ..kernels import ops
+                ops.check_kernel_status()
+                self._checked_kernels = True
         for e in entries:
             self.cache.release_passed(e.slot, e.num_computed + len(e.tokens))
         self.steps_run += 1
-        self.tokens_run += batch.num_tokens
+        self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits, batch

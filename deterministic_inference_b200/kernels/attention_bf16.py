@@ -26,7 +26,26 @@ def supports(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int) -
     return head_dim % 16 == 0 and 16 <= head_dim <= 128 and group <= 16 and num_kv_heads <= 65535
 
 
-CHUNK_TILES = 8     # fewest key tiles of 128 per chunk when a prompt's key range is shared by several CTAs
+# A prompt's key range is cut at every multiple of CHUNK_TILES key tiles of 128 (chunks
+# anchored at key 0, a constant size): a query tile whose keys reach beyond a cut is worked
+# on by one CTA per chunk and a second kernel adds their partial results in chunk order.
+# The cuts depend on positions alone, never on the step, so a token's bits do not either.
+CHUNK_TILES = 32
+MAX_CHUNKS = 16     # chunks the merge kernel adds for one row: 65,536 keys
+
+# Switches for measurements and tests, read ONCE when the module is imported (the
+# environment is not looked at again); tests set the entries of this dictionary.
+#   decode_tma   0: keys copied row by row instead of page-wise by TMA
+#   decode_pipe  0: one split per CTA; 1: one CTA per SM walks the splits, copies pipelined;
+#                2: the latter when the step has more splits than CTAs that run at once
+#   prefill_tc   0: mma.sync kernel; 1: one query tile per CTA; 2: two
+#   prefill_pair auto | 0: every tile alone | 1: pairs from both ends | 2: neighbours
+SWITCHES = {
+    "decode_tma": os.environ.get("DIB200_DECODE_TMA", "1") != "0",
+    "decode_pipe": int(os.environ.get("DIB200_DECODE_PIPE", "2")),
+    "prefill_tc": os.environ.get("DIB200_PREFILL_TC", "2"),
+    "prefill_pair": os.environ.get("DIB200_PREFILL_PAIR", "auto"),
+}
 
 _sms: dict = {}
 
@@ -107,6 +126,30 @@ def extend_tiles(q_lens: list, first_seq: int, tokens_per_tile: int):
     return seqs, starts
 
 
+def _pair_lists(meta, nd: int, tpt: int, window: int, hkv: int, max_chunks: int, t: int, hq: int,
+                d: int, device):
+    """The CTA list of the two-tile prompt kernel for this step, on the device: (sequences,
+    first tokens of A, count, first tokens of B), the chunk of each entry (or None) and
+    the scratch for partial results (or Nones).  How tiles are paired depends on the step
+    (few tiles: each alone; more CTAs than SMs: neighbours; else from both ends); the
+    arithmetic of a tile does not depend on its partner."""
+    if max_chunks > 1:
+        seqs, starts, starts_b, chunks = extend_chunk_units(meta.q_lens, meta.kv_lens, nd, tpt,
+                                                            CHUNK_TILES)
+        both = torch.tensor([seqs, starts, chunks, starts_b], dtype=torch.int32).to(device, non_blocking=True)
+        ws = (torch.empty(t, hq, max_chunks, d, dtype=torch.float32, device=device),
+              torch.empty(t, hq, max_chunks, 2, dtype=torch.float32, device=device))
+        return (both[0], both[1], len(seqs), both[3]), both[2], ws
+    n_tiles = sum(-(-n // tpt) for n in meta.q_lens[nd:])
+    ctas = (n_tiles + 1) // 2 * hkv
+    how = SWITCHES["prefill_pair"]
+    alone = how == "0" or (how == "auto" and ctas * 2 <= _sm_count(device))
+    neighbours = how == "2" or (how == "auto" and ctas > _sm_count(device))
+    seqs, starts, starts_b = extend_tile_pairs(meta.q_lens, meta.kv_lens, nd, tpt, window, alone, neighbours)
+    both = torch.tensor([seqs, starts, starts_b], dtype=torch.int32).to(device, non_blocking=True)
+    return (both[0], both[1], len(seqs), both[2]), None, (None, None)
+
+
 def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
     from .ops import _check, _lib, _ptr, _stream
 
@@ -122,10 +165,7 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
             ws = (torch.empty(nd, hq, max_splits, d, dtype=torch.float32, device=q.device),
                   torch.empty(nd, hq, max_splits, dtype=torch.float32, device=q.device))
             meta.scratch[("decode_ws", hq, d, max_splits)] = ws
-        use_tma = os.environ.get("DIB200_DECODE_TMA", "1") != "0"
-        # 0: one split per CTA; 1: one CTA per SM walks the splits, copies pipelined;
-        # 2: the latter when the step has more splits than CTAs that run at once
-        pipelined = int(os.environ.get("DIB200_DECODE_PIPE", "2"))
+        use_tma, pipelined = SWITCHES["decode_tma"], SWITCHES["decode_pipe"]
         st = lib.dib_decode_attention_bf16(
             _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0] if use_tma else 0),
             _ptr(bt), c_int(bt.shape[1]), _ptr(meta.seq_lens),
@@ -133,32 +173,20 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
             c_int(page_size), c_float(scale), c_int(window), c_int(pipelined), _stream())
         _check(st, "decode_attention_bf16", f"heads {hq}/{hkv}, head_dim {d}", kernels=2)
     group = hq // hkv
-    tc_mode = os.environ.get("DIB200_PREFILL_TC", "2")   # 0: mma.sync kernel; 1: one query tile per CTA; 2: two
+    tc_mode = SWITCHES["prefill_tc"]
     if b > nd and d == 128 and TC_TILE_ROWS % group == 0 and page_size in (8, 16, 32, 64, 128) \
             and tc_mode != "0":
         # tcgen05 kernels: 128 rows per query tile, one or two tiles per CTA
         pair = tc_mode != "1"
         tpt = TC_TILE_ROWS // group
-        tiles = meta.scratch.get(("extend_tiles", tpt, pair, window > 0))
-        if tiles is None:
-            if pair:
-                # pairs while they give at least a CTA for every second SM, else a CTA per tile
-                # (DIB200_PREFILL_PAIR=0/1/2 forces: alone, from both ends, neighbours)
-                n_tiles = sum(-(-n // tpt) for n in meta.q_lens[nd:])
-                ctas = (n_tiles + 1) // 2 * hkv
-                how = os.environ.get("DIB200_PREFILL_PAIR", "auto")
-                alone = how == "0" or (how == "auto" and ctas * 2 <= _sm_count(q.device))
-                neighbours = how == "2" or (how == "auto" and ctas > _sm_count(q.device))
-                seqs, starts, starts_b = extend_tile_pairs(meta.q_lens, meta.kv_lens, nd, tpt, window,
-                                                           alone, neighbours)
-            else:
-                seqs, starts = extend_tiles(meta.q_lens, nd, tpt)
-                starts_b = starts
-            both = torch.tensor([seqs, starts, starts_b], dtype=torch.int32).to(q.device, non_blocking=True)
-            tiles = (both[0], both[1], len(seqs), both[2])
-            meta.scratch[("extend_tiles", tpt, pair, window > 0)] = tiles
         tc_lib = _lib("attention_prefill_tc")
         if not pair:
+            tiles = meta.scratch.get(("extend_tiles", tpt))
+            if tiles is None:
+                seqs, starts = extend_tiles(meta.q_lens, nd, tpt)
+                both = torch.tensor([seqs, starts], dtype=torch.int32).to(q.device, non_blocking=True)
+                tiles = (both[0], both[1], len(seqs))
+                meta.scratch[("extend_tiles", tpt)] = tiles
             st = tc_lib.dib_extend_attention_tc(
                 _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0]), _ptr(bt),
                 c_int(bt.shape[1]), _ptr(meta.cu_q_lens), _ptr(meta.seq_lens), _ptr(tiles[0]),
@@ -166,42 +194,28 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
                 c_float(scale), c_int(window), _stream())
             _check(st, "extend_attention_tc", f"heads {hq}/{hkv}, head_dim {d}")
             return
-        # Few pairs of query tiles for the GPU and long key ranges (a short prompt portion
-        # behind a long prefix): the key range is cut into at most 8 chunks of at least
-        # CHUNK_TILES tiles of 128 keys and several CTAs share a pair; a second kernel
-        # merges their partial results.  A CTA costs about 10 us beside its key tiles (2 us
-        # a pair), so this pays only when the CTAs there are leave most SMs idle: at 128
-        # CTAs of 1 to 16 tile pairs (2,048 tokens, 8 kv heads) it measured 45 + 5 us
-        # against 48 us unsplit.  DIB200_PREFILL_SPLIT=0/1 forces the choice.
-        max_chunks, ws, chunk_list, chunk_tiles = 1, (None, None), None, 0
-        split = os.environ.get("DIB200_PREFILL_SPLIT", "auto")
+        # The lengths the host knows (under a captured graph an upper bound) say how many
+        # chunks the launch must provide for; which chunks a row's result is added from
+        # follows from its position alone (see CHUNK_TILES).
         n_keys = max(meta.kv_lens[nd:])
-        want_split = split == "1" or (split != "0" and tiles[2] * hkv * 2 <= _sm_count(q.device)
-                                      and n_keys >= 4 * CHUNK_TILES * 128)
-        if want_split and n_keys > CHUNK_TILES * 128:
-            chunk_tiles = max(CHUNK_TILES, -(-(-(-n_keys // 128)) // 8))
-            max_chunks = -(-n_keys // (chunk_tiles * 128))
-            got = meta.scratch.get(("extend_chunks", tpt, chunk_tiles))
+        max_chunks = -(-n_keys // (CHUNK_TILES * 128))
+        if max_chunks <= MAX_CHUNKS:
+            got = meta.scratch.get(("extend_pairs", tpt, window > 0))
             if got is None:
-                seqs, starts, starts_b, chunks = extend_chunk_units(meta.q_lens, meta.kv_lens, nd, tpt,
-                                                                    chunk_tiles)
-                both = torch.tensor([seqs, starts, chunks, starts_b], dtype=torch.int32).to(
-                    q.device, non_blocking=True)
-                got = ((both[0], both[1], len(seqs), both[3]), both[2],
-                       (torch.empty(t, hq, max_chunks, d, dtype=torch.float32, device=q.device),
-                        torch.empty(t, hq, max_chunks, 2, dtype=torch.float32, device=q.device)))
-                meta.scratch[("extend_chunks", tpt, chunk_tiles)] = got
+                got = _pair_lists(meta, nd, tpt, window, hkv, max_chunks, t, hq, d, q.device)
+                meta.scratch[("extend_pairs", tpt, window > 0)] = got
             tiles, chunk_list, ws = got
-        st = tc_lib.dib_extend_attention_tc_pair(
-            _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0]), _ptr(bt),
-            c_int(bt.shape[1]), _ptr(meta.cu_q_lens), _ptr(meta.seq_lens), _ptr(tiles[0]),
-            _ptr(tiles[1]), _ptr(tiles[3]), c_int(tiles[2]), c_int(hq), c_int(hkv), c_int(d),
-            c_int(page_size), c_float(scale), c_int(window), c_int(chunk_tiles if max_chunks > 1 else 0),
-            _ptr(chunk_list), c_int(max_chunks), _ptr(ws[0]), _ptr(ws[1]), _ptr(meta.token_seq),
-            c_int(nd), c_int(t - nd), _stream())
-        _check(st, "extend_attention_tc_pair", f"heads {hq}/{hkv}, head_dim {d}",
-               kernels=2 if max_chunks > 1 else 1)
-        return
+            st = tc_lib.dib_extend_attention_tc_pair(
+                _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0]), _ptr(bt),
+                c_int(bt.shape[1]), _ptr(meta.cu_q_lens), _ptr(meta.seq_lens), _ptr(tiles[0]),
+                _ptr(tiles[1]), _ptr(tiles[3]), c_int(tiles[2]), c_int(hq), c_int(hkv), c_int(d),
+                c_int(page_size), c_float(scale), c_int(window), c_int(CHUNK_TILES if max_chunks > 1 else 0),
+                _ptr(chunk_list), c_int(max_chunks), _ptr(ws[0]), _ptr(ws[1]), _ptr(meta.token_seq),
+                c_int(nd), c_int(t - nd), _stream())
+            _check(st, "extend_attention_tc_pair", f"heads {hq}/{hkv}, head_dim {d}",
+                   kernels=2 if max_chunks > 1 else 1)
+            return
+        # longer than the merge kernel takes: the mma.sync kernel below
     if b > nd:
         tpt = TILE_ROWS // (hq // hkv)
         tiles = meta.scratch.get(("extend_tiles", tpt))

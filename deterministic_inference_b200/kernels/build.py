@@ -61,6 +61,16 @@ class KernelBuildError(RuntimeError):
     pass
 
 
+def register_source(name: str, path, headers=(), flags=()) -> None:
+    """Make a CUDA source outside ``csrc/`` buildable and loadable under ``name`` with the
+    flags of this package (it may include the package's headers)."""
+    SOURCES[name] = str(Path(path).resolve())
+    if headers:
+        EXTRA_HEADERS[name] = tuple(headers)
+    if flags:
+        EXTRA_FLAGS[name] = list(flags)
+
+
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 _dir_lock = threading.Lock()
@@ -137,7 +147,7 @@ def compile_library(name: str, verbose: bool = True) -> Path:
            *EXTRA_FLAGS.get(name, [])]
     t0 = time.time()
     if verbose:
-        print(f"[dib200] compiling {SOURCES[name]} for sm_100a (first use) ...", file=sys.stderr,
+        print(f"[dib200] compiling {Path(SOURCES[name]).name} for sm_100a (first use) ...", file=sys.stderr,
               flush=True)
     proc = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     done = threading.Event()
@@ -168,7 +178,7 @@ def compile_library(name: str, verbose: bool = True) -> Path:
 
 def compile_all(names=None, verbose: bool = True) -> dict[str, Path]:
     """Compile several libraries at once (one nvcc process each, in parallel)."""
-    names = list(names or SOURCES)
+    names = list(names or [n for n in SOURCES if not Path(SOURCES[n]).is_absolute()])
     names = [n for n in names if (CSRC / SOURCES[n]).exists()]
     out: dict[str, Path] = {}
     errors: list[str] = []

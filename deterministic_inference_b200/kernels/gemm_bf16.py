@@ -15,8 +15,19 @@ from ctypes import byref, c_int, c_void_p
 
 import torch
 
-# rows up to which the package's own kernel is used
-MAX_ROWS = int(os.environ.get("DIB200_GEMM_MAX_ROWS", "128"))
+# Rows up to which the package's own kernel is used; products of more rows go to the
+# library.  ``set_library_products(False)`` sends every product to the package's kernel,
+# whose order of summation does not depend on the number of rows: a token's bits are then
+# the same whatever else the step holds (the library's algorithm depends on the shape).
+OWN_KERNEL_ROWS = int(os.environ.get("DIB200_GEMM_MAX_ROWS", "128"))
+MAX_ROWS = OWN_KERNEL_ROWS
+# DIB200_GATED=0/1 (read once): never / always the gate in the product's epilogue
+GATED = os.environ.get("DIB200_GATED")
+
+
+def set_library_products(on: bool) -> None:
+    global MAX_ROWS
+    MAX_ROWS = OWN_KERNEL_ROWS if on else 1 << 30
 
 _sm_count: dict = {}
 
@@ -27,6 +38,14 @@ def _sms(device) -> int:
         n = torch.cuda.get_device_properties(device).multi_processor_count
         _sm_count[device] = n
     return n
+
+
+def configure(cluster: int = -1, forced_splits: int = -1) -> None:
+    """Measurement and test switches of the kernel library (negative: leave as it is):
+    ``cluster`` 0/1: the CTAs of a tile add their partial tiles up as a thread-block
+    cluster; ``forced_splits`` n >= 1: split k n ways, 0: the cost model's choice."""
+    from .ops import _lib
+    _lib("gemm_bf16").dib_gemm_bf16_configure(c_int(cluster), c_int(forced_splits))
 
 
 def status() -> int:
@@ -86,8 +105,8 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor):
     # one CTA per 64 features and no split of k: worth it when those CTAs fill whole waves
     # of the GPU about as well as the split product does (the kernel's own estimate; 0.6B
     # shape, 48 tiles: 1.458 ms per step against 1.435 ms with the split product and the
-    # separate gate).  DIB200_GATED=0/1 forces the choice.
-    forced = os.environ.get("DIB200_GATED")
+    # separate gate).  ``GATED`` forces the choice.
+    forced = GATED
     if forced == "0" or (forced != "1" and not ops._lib("gemm_bf16").dib_gemm_bf16_gated_pays(
             c_int(i), c_int(k), c_int(_sms(x.device)))):
         return None

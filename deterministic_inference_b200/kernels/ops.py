@@ -102,23 +102,52 @@ def _lib(name: str) -> ctypes.CDLL:
     return lib
 
 
+# Libraries whose kernels have bounded waits: name -> (read, clear) of its error word.
+_STATUS_FUNCTIONS = {
+    "gemm_bf16": ("dib_gemm_bf16_status", "dib_gemm_bf16_status_clear"),
+    "attention_bf16": ("dib_attention_bf16_status", "dib_attention_bf16_status_clear"),
+    "attention_prefill_tc": ("dib_attention_prefill_tc_status", "dib_attention_prefill_tc_status_clear"),
+}
+_extra_status: dict = {}
+
+
+def register_kernel_status(name: str, read, clear) -> None:
+    """Add the error word of a library loaded from outside this module: ``read()`` gives 0
+    or the code of a wait that ran out, ``clear()`` sets it back to 0."""
+    _extra_status[name] = (read, clear)
+
+
 def kernel_status() -> dict:
     """The error words of the libraries with bounded waits that have been loaded: name ->
     0, or the code of a wait that ran out (the results of that launch are not valid).
     Reading them synchronises with the device."""
     out = {}
-    for name, fn in (("gemm_bf16", "dib_gemm_bf16_status"), ("attention_bf16", "dib_attention_bf16_status"),
-                     ("attention_prefill_tc", "dib_attention_prefill_tc_status")):
+    for name, (read, _) in _STATUS_FUNCTIONS.items():
         lib = _libs.get(name)
         if lib is not None:
-            out[name] = int(getattr(lib, fn)())
+            out[name] = int(getattr(lib, read)())
+    for name, (read, _) in _extra_status.items():
+        out[name] = int(read())
     return out
 
 
+def clear_kernel_status() -> None:
+    """Set every error word back to 0."""
+    for name, (_, clear) in _STATUS_FUNCTIONS.items():
+        lib = _libs.get(name)
+        if lib is not None:
+            getattr(lib, clear)()
+    for _, clear in _extra_status.values():
+        clear()
+
+
 def check_kernel_status() -> None:
-    """Raise ``KernelError`` if a bounded wait inside a kernel ever ran out."""
+    """Raise ``KernelError`` if a bounded wait inside a kernel ran out since the last check.
+    The words are cleared first, so the failure is reported once and later work is judged
+    on its own."""
     bad = {k: v for k, v in kernel_status().items() if v != 0}
     if bad:
+        clear_kernel_status()
         raise KernelError(f"a bounded wait inside a kernel ran out (library: code): {bad}; results of "
                           "the steps since the last check are not valid")
 

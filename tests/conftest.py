@@ -44,6 +44,27 @@ TINY = {
                              head_dim=48, intermediate_size=112, vocab_size=300,
                              num_hidden_layers=1, rms_norm_eps=1e-4, rope_theta=5e4,
                              tie_word_embeddings=False, eos_token_id=299)),
+    # Heads of 128, the head size of the benchmark shapes: the tcgen05 prompt kernel, the
+    # page-wise TMA decode kernels and the eight-lane q/k kernel run inside these models.
+    # "d": group ratio 2, page 16, tied head; "e": ratio 8 (one kv head), page 32, untied
+    # head, other eps / theta, and a window on its last layer.
+    "d": dict(preset="tiny_a", seed=11, page_size=16,
+              overrides=dict(hidden_size=256, num_attention_heads=4, num_key_value_heads=2,
+                             head_dim=128, intermediate_size=384, vocab_size=320,
+                             num_hidden_layers=2, max_position_embeddings=1024, eos_token_id=319)),
+    "e": dict(preset="tiny_b", seed=13, page_size=32,
+              overrides=dict(hidden_size=384, num_attention_heads=8, num_key_value_heads=1,
+                             head_dim=128, intermediate_size=640, vocab_size=704,
+                             num_hidden_layers=3, max_position_embeddings=1024, eos_token_id=703,
+                             use_sliding_window=True, sliding_window=200, max_window_layers=2)),
+    # The layer sizes of the smallest benchmark shape (width 1,024, 16 + 8 heads of 128,
+    # intermediate 3,072) with two layers, a small vocabulary (the plain implementation must
+    # stay fast) and a window on the second layer: the matrix-product shapes, split counts
+    # and attention launch forms of the benchmark run inside the parity tests.
+    "f": dict(preset="qwen3_0_6b", seed=17, page_size=16,
+              overrides=dict(num_hidden_layers=2, vocab_size=2048, max_position_embeddings=4096,
+                             eos_token_id=2047, use_sliding_window=True, sliding_window=600,
+                             max_window_layers=1)),
 }
 
 

@@ -81,6 +81,23 @@ def portions(trace, requests, sizes=(13, 7, 2, 5, 2, 31, 3, 2, 64, 2), prefix=""
             c += n
 
 
+def lockstep(trace, requests, portion=96, tail=8, prefix=""):
+    """All requests (of one length) live at once and cut alike: every step brings the same
+    portion of each, then single tokens, so the same step shapes come again and again (a
+    step function that replays captured graphs of repeated shapes does so here)."""
+    n = len(requests[0])
+    assert all(len(r) == n for r in requests)
+    keys = [f"{prefix}l{i}" for i in range(len(requests))]
+    c = 0
+    while c < n:
+        left = n - c
+        q = 1 if left <= tail else min(portion, left - tail)
+        last = c + q == n
+        trace.add_step([(k, c, r[c:c + q], list(range(q))) for k, r in zip(keys, requests)],
+                       end=keys if last else [])
+        c += q
+
+
 def mixed(trace, requests, max_live=4, sizes=(11, 2, 17, 5, 2, 29, 3), tail=6, prefix=""):
     """Up to ``max_live`` requests at a time: each live request brings a portion
     (the last ``tail`` tokens one by one, like decoding), some steps leave a
@@ -110,13 +127,15 @@ def mixed(trace, requests, max_live=4, sizes=(11, 2, 17, 5, 2, 29, 3), tail=6, p
 
 
 def run_trace(model_dir, dtype, trace, out_dir, max_tokens=None, page_size=16, timeout=900,
-              user=None):
+              user=None, cuda_graphs=False):
     """Run the trace through bin/trace_run; returns {step: float32 array [wanted, V]}."""
     out_dir = Path(out_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
     cmd = [sys.executable, str(TRACE_RUN), "--model", str(model_dir), "--dtype", dtype, "--out",
            str(out_dir), "--max-tokens", str(max_tokens or trace.peak_tokens),
            "--page-size", str(page_size)]
+    if cuda_graphs:
+        cmd.append("--cuda-graphs")
     env = dict(os.environ)
     proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
     try:

@@ -163,3 +163,39 @@ def test_random_orders_keep_the_invariants(seed):
         c.release_slot(s)
     c.check_invariants()
     assert all(g.num_free == g.num_pages - 1 for g in c.page_groups.values())
+
+
+def test_pages_for_a_byte_budget_are_shared_by_bytes_per_page_and_window_groups_are_capped():
+    """Pools sized from a byte budget: groups that keep all keys get the same number of
+    pages; a window group gets no more than its requests can ever hold, and what that
+    saves goes to the others."""
+    from deterministic_inference_b200.cache.manager import group_page_bytes, pages_for_budget
+    specs = {0: PagedKVSpec(2, 32, None), 1: PagedKVSpec(2, 32, None), 2: PagedKVSpec(2, 32, 24),
+             3: PagedKVSpec(4, 16, None), 4: StateSpec((8,), "float32")}
+    page, dt = 16, torch.bfloat16
+    per = group_page_bytes(specs, page, dt)
+    full_a, win, full_b = PagedKVSpec(2, 32, None).group_key(), PagedKVSpec(2, 32, 24).group_key(), \
+        PagedKVSpec(4, 16, None).group_key()
+    assert per[full_a][1] == 2 * 2 * 2 * page * 32 * 2 and per[win][1] == 2 * 2 * page * 32 * 2
+    budget = 10_000_000
+    pages = pages_for_budget(specs, budget, page, dt, max_reqs=4, step_tokens=64)
+    assert pages[full_a] == pages[full_b] and pages[win] == 1 + 4 * (-(-(24 + 64) // page) + 2)
+    cost = sum(pages[k] * per[k][1] for k in pages)
+    assert cost <= budget < cost + per[full_a][1] + per[full_b][1]     # one more page would not fit
+    # a budget so small that the window group is not capped: all groups get the same pages
+    small = pages_for_budget(specs, 20 * sum(b for _, b in per.values()), page, dt, 4, 64)
+    assert small[full_a] == small[win] == small[full_b] == 20
+    with pytest.raises(CacheError):
+        pages_for_budget(specs, 1000, page, dt, 4, 64)
+    # the manager takes the dict: each group has its own pool size, and a request's length is
+    # bounded by the groups that keep all keys
+    m = CacheManager(specs, pages, page, max_reqs=5, max_seq_len=4096, dtype=dt, device="cpu",
+                     allocate_device=False)
+    assert {g.key: g.num_pages for g in m.page_groups.values()} == pages
+    assert m.usable_pages() == pages[full_a] - 1
+    s = m.allocate_slot()
+    m.allocate(s, 200)
+    m.release_passed(s, 200)
+    m.check_invariants()
+    m.release_slot(s)
+    m.check_invariants()

@@ -246,45 +246,122 @@ def test_steps_replayed_as_graphs_give_the_bits_of_launched_steps(dtype, tiny_mo
     assert g.captures >= 3 and g.replays >= 4 + 3 + 4
 
 
-def test_long_prompts_and_a_wide_decode_batch_agree_across_dtypes():
-    """At the 0.6B layer sizes (2 layers): 24 requests with prompts of 1,200 to 1,400 tokens
-    fed in portions of 512, then decoded together for a few steps.  The bfloat16 steps take
-    the tcgen05 prompt kernel behind cached prefixes over many key tiles, and the decode
-    attention that walks many splits per CTA inside a replayed graph; the float32 engine
-    takes the generic kernels.  Their logits agree up to bfloat16 storage."""
-    from deterministic_inference_b200 import EngineConfig, preset
+def test_long_prompts_and_a_wide_decode_batch_against_plain(tiny_model_dirs):
+    """At the benchmark's layer sizes (model "f": width 1,024, 16 + 8 heads of 128, a window
+    on the second layer, sharpened weights): 24 requests with prompts of 1,200 to 1,400
+    tokens, three of them fed in portions of 512, the others whole seven at a time, then
+    all decoded together for a few steps through the replayed graph.  The bfloat16 steps
+    take the tcgen05 prompt kernel behind cached prefixes over many key tiles and the
+    decode attention that walks many splits per CTA; the logits of six of the requests are
+    compared with the plain implementation (bfloat16 storage emulated) under the bound of
+    the replay tests."""
+    from deterministic_inference_b200 import EngineConfig
     from deterministic_inference_b200.engine.batch import SequenceInput
-    from deterministic_inference_b200.engine.graphs import DecodeGraphs
     from deterministic_inference_b200.engine.runner import ModelRunner
-    cfg = preset("qwen3_0_6b", num_hidden_layers=2, max_window_layers=2)
+    from tests.test_replay_gpu import BF16_FRAC, BF16_ROUNDING_SHARE
+    model_dir = tiny_model_dirs["f"]
+    cfg, w = plain_qwen3.read_model_dir(model_dir)
     n_req, steps = 24, 4
     g = torch.Generator().manual_seed(31)
     lens = torch.randint(1200, 1401, (n_req,), generator=g).tolist()
-    prompts = [torch.randint(0, cfg.vocab_size, (n + steps,), generator=g).tolist() for n in lens]
-    res = {}
-    for dtype in ("bfloat16", "float32"):
-        r = ModelRunner(EngineConfig(model_config=cfg, random_seed=2, dtype=dtype, kv_pool_tokens=40960,
-                                     max_reqs=32, max_seq_len=2048, device="cuda:0"))
-        graphs = DecodeGraphs(r)
-        slots = [r.cache.allocate_slot() for _ in range(n_req)]
-        out = []
-        for i in (0, 7, 23):                                   # three prompts portion by portion
-            for a in range(0, lens[i], 512):
-                b = min(lens[i], a + 512)
-                lg, _ = r.step([SequenceInput(slots[i], prompts[i][a:b], a, [b - a - 1] if b == lens[i] else [])])
-            out.append(lg.float().cpu())
-        rest = [i for i in range(n_req) if i not in (0, 7, 23)]
-        for k in range(0, len(rest), 7):                        # the others whole, seven at a time
-            r.step([SequenceInput(slots[i], prompts[i][:lens[i]], 0, []) for i in rest[k:k + 7]])
-        for s in range(steps):                                  # all decode together, given tokens
-            lg, _ = graphs.run([SequenceInput(slots[i], [prompts[i][lens[i] + s]], lens[i] + s, [0])
-                                for i in range(n_req)])
-            out.append(lg.float().cpu().clone())
-        res[dtype] = out
-        del r, graphs
-        torch.cuda.empty_cache()
+    prompts = [torch.randint(0, cfg["vocab_size"], (n + steps,), generator=g).tolist() for n in lens]
+    r = ModelRunner(EngineConfig(model_path=str(model_dir), dtype="bfloat16", kv_pool_tokens=40960,
+                                 max_reqs=32, max_seq_len=2048, device="cuda:0"))
+    slots = [r.cache.allocate_slot() for _ in range(n_req)]
+    got = {}                                               # (request, position) -> logits row
+    for i in (0, 7, 23):                                   # three prompts portion by portion
+        for a in range(0, lens[i], 512):
+            b = min(lens[i], a + 512)
+            lg, _ = r.step([SequenceInput(slots[i], prompts[i][a:b], a, [b - a - 1] if b == lens[i] else [])])
+        got[(i, lens[i] - 1)] = lg[0].float().cpu()
+    rest = [i for i in range(n_req) if i not in (0, 7, 23)]
+    for k in range(0, len(rest), 7):                        # the others whole, seven at a time
+        group = rest[k:k + 7]
+        lg, batch = r.step([SequenceInput(slots[i], prompts[i][:lens[i]], 0, [lens[i] - 1]) for i in group])
+        for i, rows in zip(group, batch.logit_rows):
+            got[(i, lens[i] - 1)] = lg[rows[0]].float().cpu()
+    for s in range(steps):                                  # all decode together, given tokens
+        lg, batch = r.step([SequenceInput(slots[i], [prompts[i][lens[i] + s]], lens[i] + s, [0])
+                            for i in range(n_req)])
+        for i, rows in enumerate(batch.logit_rows):
+            got[(i, lens[i] + s)] = lg[rows[0]].float().cpu()
+    assert r.decode_graphs.replays == steps
     from deterministic_inference_b200.kernels import ops
-    assert ops._lib("attention_bf16").dib_attention_bf16_status() == 0
-    assert ops._lib("attention_prefill_tc").dib_attention_prefill_tc_status() == 0
-    for a, b in zip(res["bfloat16"], res["float32"]):
-        assert (a - b).abs().max().item() <= 0.03 * b.abs().max().item()
+    ops.check_kernel_status()
+    for i in (0, 7, 23, 3, 12, 18):
+        emu = plain_qwen3.forward(cfg, w, prompts[i], store_bf16=True)
+        p32 = plain_qwen3.forward(cfg, w, prompts[i])
+        yard = float((emu - p32).abs().max())
+        for pos in range(lens[i] - 1, lens[i] + steps):
+            want = emu[pos]
+            scale = max(1.0, float(want.abs().max()))
+            err = float((got[(i, pos)].double() - want.double()).abs().max())
+            assert err <= max(BF16_FRAC * scale, BF16_ROUNDING_SHARE * yard), (i, pos, err, scale, yard)
+
+
+@pytest.mark.parametrize("name", ["d", "e"])
+def test_bfloat16_bits_of_a_token_do_not_depend_on_its_step(name, tiny_model_dirs):
+    """With ``library_products=False`` every bfloat16 kernel adds up in an order that
+    depends on the token's own position and the weights' shapes alone.  So the logits of
+    a request are the same bits (a) alone and beside three other requests of other
+    lengths, (b) launched kernel by kernel and replayed from a captured graph, (c) with
+    its prompt cut into portions of 512 and of 100 tokens.  Heads of 128: the tcgen05
+    prompt kernel in its paired, neighbour and single-tile forms, the TMA decode kernels,
+    the package's matrix product at 1 to 1,700 rows."""
+    from deterministic_inference_b200 import EngineConfig
+    from deterministic_inference_b200.engine.batch import SequenceInput
+    from deterministic_inference_b200.engine.runner import ModelRunner
+    model_dir = tiny_model_dirs[name]
+    vocab = plain_qwen3.read_model_dir(model_dir)[0]["vocab_size"]
+    g = torch.Generator().manual_seed(77)
+    main = torch.randint(0, vocab, (1000,), generator=g).tolist()
+    others = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in (700, 40, 333)]
+    want_places = [0, 99, 100, 511, 512, 998, 999]
+
+    def runner(graphs):
+        return ModelRunner(EngineConfig(model_path=str(model_dir), dtype="bfloat16", device="cuda:0",
+                                        kv_pool_tokens=8192, page_size=TINY[name]["page_size"], max_reqs=16,
+                                        max_seq_len=1024, cuda_graphs=graphs, library_products=False))
+
+    def feed(r, portion, beside=(), decode_tail=8):
+        """The main request in portions of ``portion`` tokens (its last tokens one by one),
+        each step together with the next portions of the ``beside`` requests; returns its
+        logits at ``want_places`` and at the single tokens."""
+        slot = r.cache.allocate_slot()
+        oslots = [r.cache.allocate_slot() for _ in beside]
+        odone = [0] * len(beside)
+        rows, c = {}, 0
+        while c < len(main):
+            left = len(main) - c
+            n = 1 if left <= decode_tail else min(portion, left - decode_tail)
+            want = [p - c for p in want_places if c <= p < c + n] if n > 1 else [0]
+            entries = [SequenceInput(slot, main[c:c + n], c, want)]
+            for i, o in enumerate(beside):
+                if odone[i] < len(o):
+                    m = min(1 if odone[i] > len(o) - 5 else 150, len(o) - odone[i])
+                    entries.append(SequenceInput(oslots[i], o[odone[i]:odone[i] + m], odone[i], []))
+                    odone[i] += m
+            logits, batch = r.step(entries)
+            for w, row in zip(want, batch.logit_rows[0]):
+                rows[c + w] = logits[row].clone()
+            c += n
+        for s in [slot] + oslots:
+            r.cache.release_slot(s)
+        return rows
+
+    base = feed(runner(False), 512)
+    assert sorted(base) == sorted(set(want_places) | set(range(992, 1000)))
+    variants = {
+        "beside three others": feed(runner(False), 512, beside=others),
+        "portions of 100": feed(runner(False), 100),
+        "portions of 100 beside others": feed(runner(False), 100, beside=others),
+    }
+    r = runner(True)
+    for _ in range(3):                      # the third time every repeated shape is replayed
+        variants["replayed"] = feed(r, 512)
+    assert r.step_graphs.replays >= 2 and r.decode_graphs.replays >= 8
+    for what, rows in variants.items():
+        for p, row in base.items():
+            assert torch.equal(rows[p], row), (what, p)
+    from deterministic_inference_b200.kernels import gemm_bf16
+    gemm_bf16.set_library_products(True)

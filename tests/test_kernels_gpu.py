@@ -20,6 +20,36 @@ def tol(dtype):
     return dict(atol=2e-2, rtol=2e-2) if dtype == torch.bfloat16 else dict(atol=2e-6, rtol=2e-6)
 
 
+@pytest.fixture
+def switches(monkeypatch):
+    """Sets the kernels' measurement switches for one test and puts them back."""
+    from ctypes import c_int
+    from deterministic_inference_b200.kernels import attention_bf16, gemm_bf16
+    from deterministic_inference_b200.kernels import ops as _ops
+
+    class Switches:
+        def attention(self, **kw):
+            for k, v in kw.items():
+                assert k in attention_bf16.SWITCHES, k
+                monkeypatch.setitem(attention_bf16.SWITCHES, k, v)
+
+        def chunk_tiles(self, n):
+            monkeypatch.setattr(attention_bf16, "CHUNK_TILES", n)
+
+        def gemm(self, cluster=-1, splits=-1):
+            gemm_bf16.configure(int(cluster), int(splits))
+
+        def gated(self, v):
+            monkeypatch.setattr(gemm_bf16, "GATED", v)
+
+        def merge_wide_from(self, n):
+            _ops._lib("attention_bf16").dib_attention_bf16_set_merge_wide_from(c_int(n))
+
+    yield Switches()
+    gemm_bf16.configure(0, 0)
+    _ops._lib("attention_bf16").dib_attention_bf16_set_merge_wide_from(c_int(49))
+
+
 def ops():
     from deterministic_inference_b200.kernels import ops as o
     return o
@@ -162,12 +192,12 @@ def test_linear_fp32_row_does_not_depend_on_batch():
     (17, 130, 72), (128, 256, 64), (33, 100, 8), (5, 151936, 1024), (100, 3000, 520),
     (129, 152, 96), (300, 152, 96), (2048, 512, 256)])
 @pytest.mark.parametrize("cluster", ["1", "0"])
-def test_linear_bf16(m, n, k, cluster, monkeypatch):
+def test_linear_bf16(m, n, k, cluster, switches):
     """Rows up to 128 run the package's tcgen05 kernel (tails in N and K, split k,
     one to four token tiles), more rows the library.  A split of k is added up by the
     tile's cluster of CTAs (a finished tensor comes back) or left as partial products."""
     from deterministic_inference_b200.kernels import gemm_bf16
-    monkeypatch.setenv("DIB200_GEMM_CLUSTER", cluster)
+    switches.gemm(cluster=cluster)
     torch.manual_seed(8)
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (0.05 * torch.randn(n, k, device="cuda")).to(torch.bfloat16)
@@ -197,11 +227,11 @@ def test_linear_bf16_row_does_not_depend_on_batch():
 
 @pytest.mark.parametrize("m,i,k", [(1, 3072, 1024), (8, 128, 72), (40, 192, 520), (100, 64, 64),
                                    (200, 128, 96), (8, 100, 64)])
-def test_gated_linear(m, i, k, monkeypatch):
+def test_gated_linear(m, i, k, switches):
     """silu(x Wg^T) * (x Wu^T) with the gate in the product's epilogue (few rows, I a
     multiple of 64) or as two kernels; both against the formula with the two products
     rounded to bfloat16 as stored."""
-    monkeypatch.setenv("DIB200_GATED", "1")      # also the small shapes take the epilogue
+    switches.gated("1")      # also the small shapes take the epilogue
     torch.manual_seed(12)
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (0.08 * torch.randn(2 * i, k, device="cuda")).to(torch.bfloat16)
@@ -215,18 +245,18 @@ def test_gated_linear(m, i, k, monkeypatch):
 
 @pytest.mark.parametrize("m,n,k,splits", [(8, 1024, 2048, 8), (1, 4096, 1024, 4), (64, 1024, 3072, 6),
                                           (128, 300, 520, 3), (17, 6144, 1024, 2), (33, 200, 1024, 7)])
-def test_cluster_sum_of_a_split_gives_the_bits_of_the_partials(m, n, k, splits, monkeypatch):
+def test_cluster_sum_of_a_split_gives_the_bits_of_the_partials(m, n, k, splits, switches):
     """The same split of k (forced), once added up by the tile's cluster through
     distributed shared memory, once left as partial products that a reader adds in split
     order: the same bits, in bfloat16 and float32 outputs; and the gate after a cluster's
     sum gives what the gate kernel gives on the partials."""
-    monkeypatch.setenv("DIB200_GEMM_SPLITS", str(splits))
+    switches.gemm(splits=splits)
     torch.manual_seed(14)
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (0.05 * torch.randn(n, k, device="cuda")).to(torch.bfloat16)
     outs = {}
     for cluster in ("1", "0"):
-        monkeypatch.setenv("DIB200_GEMM_CLUSTER", cluster)
+        switches.gemm(cluster=cluster)
         y = ops().linear(x, w)
         assert isinstance(y, ops().SplitSum) == (cluster == "0")
         outs[cluster] = (ops().as_tensor(y), ops().as_tensor(ops().linear(x, w, out_dtype=torch.float32)))
@@ -234,8 +264,8 @@ def test_cluster_sum_of_a_split_gives_the_bits_of_the_partials(m, n, k, splits, 
     if n % 128 == 0:
         gated = {}
         for cluster in ("1", "0"):
-            monkeypatch.setenv("DIB200_GEMM_CLUSTER", cluster)
-            monkeypatch.setenv("DIB200_GATED", "1" if cluster == "1" else "0")
+            switches.gemm(cluster=cluster)
+            switches.gated("1" if cluster == "1" else "0")
             gated[cluster] = ops().gated_linear(x, w)
         assert torch.equal(gated["1"], gated["0"])
 
@@ -334,7 +364,7 @@ def test_paged_attention_mixed_batch(dtype, hq, hkv, d, page):
 
 @pytest.mark.parametrize("hq,hkv,d,page,window", [(16, 8, 128, 16, None), (8, 2, 128, 8, 300), (64, 8, 128, 128, None),
                                                   (4, 1, 64, 32, None), (6, 3, 64, 16, 129), (32, 8, 128, 64, 1000)])
-def test_decode_attention_pipelined_walk_gives_the_same_bits(monkeypatch, hq, hkv, d, page, window):
+def test_decode_attention_pipelined_walk_gives_the_same_bits(switches, hq, hkv, d, page, window):
     """The decode kernel that walks many splits per CTA with its copies pipelined gives,
     bit for bit, what the one-split-per-CTA kernel gives (each split is computed alike),
     with enough splits that every CTA reuses its stages several times, ragged lengths at
@@ -350,7 +380,7 @@ def test_decode_attention_pipelined_walk_gives_the_same_bits(monkeypatch, hq, hk
     q = torch.randn(n_seq, hq, d, generator=g).to(device="cuda", dtype=torch.bfloat16)
     outs = {}
     for mode in ("0", "1"):
-        monkeypatch.setenv("DIB200_DECODE_PIPE", mode)
+        switches.attention(decode_pipe=int(mode))
         outs[mode] = ops().paged_attention(q, case.cache, meta, d ** -0.5, window).clone()
     assert ops()._lib("attention_bf16").dib_attention_bf16_status() == 0
     assert torch.equal(outs["0"], outs["1"])
@@ -360,7 +390,7 @@ def test_decode_attention_pipelined_walk_gives_the_same_bits(monkeypatch, hq, hk
 
 
 @pytest.mark.parametrize("hq,hkv,d,page,window", [(16, 8, 128, 16, None), (8, 2, 128, 32, 2500), (6, 3, 64, 16, None)])
-def test_decode_attention_long_sequences_beside_short_ones(monkeypatch, hq, hkv, d, page, window):
+def test_decode_attention_long_sequences_beside_short_ones(switches, hq, hkv, d, page, window):
     """Sequences of more than 16 splits of 128 keys: their splits are added chunk by chunk
     (16 splits), by one thread per dimension or by a group of threads per chunk, with the
     same bits; a short sequence beside them keeps the bits it has alone (the order of its
@@ -373,18 +403,18 @@ def test_decode_attention_long_sequences_beside_short_ones(monkeypatch, hq, hkv,
     seqs = list(range(len(lens)))
     outs = {}
     for mode in ("0", "1"):
-        monkeypatch.setenv("DIB200_DECODE_PIPE", mode)
+        switches.attention(decode_pipe=int(mode))
         outs[mode] = ops().paged_attention(q, case.cache, case.meta(seqs, [(n - 1, 1) for n in lens]),
                                            d ** -0.5, window).clone()
     assert ops()._lib("attention_bf16").dib_attention_bf16_status() == 0
     assert torch.equal(outs["0"], outs["1"])
-    monkeypatch.delenv("DIB200_DECODE_PIPE")
-    for wide_from in ("17", "100000"):
-        monkeypatch.setenv("DIB200_MERGE_WIDE_FROM", wide_from)
+    switches.attention(decode_pipe=2)
+    for wide_from in (17, 100000):
+        switches.merge_wide_from(wide_from)
         got = ops().paged_attention(q, case.cache, case.meta(seqs, [(n - 1, 1) for n in lens]),
                                     d ** -0.5, window)
         assert torch.equal(got, outs["0"]), wide_from
-    monkeypatch.delenv("DIB200_MERGE_WIDE_FROM")
+    switches.merge_wide_from(49)
     for s_ in seqs:
         want = dense_reference(q[s_:s_ + 1], case.k[s_], case.v[s_], d ** -0.5, [lens[s_] - 1], window)
         torch.testing.assert_close(outs["0"][s_:s_ + 1].float(), want, **tol(torch.bfloat16))
@@ -396,12 +426,12 @@ def test_decode_attention_long_sequences_beside_short_ones(monkeypatch, hq, hkv,
 
 
 @pytest.mark.parametrize("tma", ["0", "1"])
-def test_decode_attention_reads_its_partial_results_after_they_are_written(monkeypatch, tma):
+def test_decode_attention_reads_its_partial_results_after_they_are_written(switches, tma):
     """The kernel that merges the splits starts beside the kernel that writes them
     (programmatic dependent launch) and must not read a partial result before its wait:
     the scratch is filled with NaN, huge values and plain numbers before each call, and
     every call gives the bits of the first."""
-    monkeypatch.setenv("DIB200_DECODE_TMA", tma)
+    switches.attention(decode_tma=tma == "1")
     hq, hkv, d, page = 16, 8, 128, 16
     lens = [513, 2, 129, 1, 33, 257, 700, 128]
     case = PagedCase(lens, hkv, d, page, torch.bfloat16, seed=3)
@@ -466,15 +496,15 @@ def test_paged_attention_far_key_stands_out(dtype):
 @pytest.mark.parametrize("mode", ["0", "1", "2", "2-pairs", "2-alone"])
 @pytest.mark.parametrize("hq,hkv,page,window", [(16, 8, 16, None), (32, 8, 16, 300), (8, 8, 32, None),
                                                 (16, 1, 128, 200), (64, 8, 8, None)])
-def test_prefill_attention_head_size_128_kernels(monkeypatch, mode, hq, hkv, page, window):
+def test_prefill_attention_head_size_128_kernels(switches, mode, hq, hkv, page, window):
     """The three bfloat16 prompt kernels for heads of 128 (mma.sync; tcgen05 with one
     query tile per CTA; tcgen05 with two, as the step's size decides, with tiles paired
     from both ends of a prompt, and with a CTA for every tile) on prompts that span many
     key tiles: whole, behind a cached prefix, ending one token after a tile edge; group
     sizes 1 to 16."""
-    monkeypatch.setenv("DIB200_PREFILL_TC", mode[0])
+    switches.attention(prefill_tc=mode[0])
     if len(mode) > 1:
-        monkeypatch.setenv("DIB200_PREFILL_PAIR", "1" if mode.endswith("pairs") else "0")
+        switches.attention(prefill_pair="1" if mode.endswith("pairs") else "0")
     d = 128
     lens = [700, 300, 129, 257]
     cuts = [(0, 700), (100, 200), (1, 128), (0, 257)]
@@ -492,11 +522,13 @@ def test_prefill_attention_head_size_128_kernels(monkeypatch, mode, hq, hkv, pag
 
 
 @pytest.mark.parametrize("hq,hkv,window", [(4, 2, None), (8, 2, 1100), (2, 2, None)])
-def test_prefill_attention_key_range_shared_by_several_ctas(monkeypatch, hq, hkv, window):
-    """Long key ranges cut into chunks of 1,024 keys that several CTAs take, with a merge
-    of their partial results: a whole prompt of three chunks, a portion behind a prefix
-    whose range starts inside a chunk, a short sequence that one chunk finishes, and a
-    decode token beside them; against the dense reference and against the unsplit run."""
+def test_prefill_attention_key_range_shared_by_several_ctas(switches, hq, hkv, window):
+    """Key ranges are cut at fixed multiples of a chunk (here 1,024 keys instead of the
+    product's 4,096, so that small cases cross cuts); several CTAs take the chunks of a
+    query tile and a merge adds their partial results: a whole prompt of three chunks, a
+    portion behind a prefix whose range starts inside a chunk, a short sequence that one
+    chunk finishes, and a decode token beside them; against the dense reference and
+    against the run with one chunk."""
     d, page = 128, 16
     lens = [5, 2500, 1500, 200]
     cuts = [(4, 1), (0, 2500), (1100, 400), (0, 200)]
@@ -504,25 +536,66 @@ def test_prefill_attention_key_range_shared_by_several_ctas(monkeypatch, hq, hkv
     g = torch.Generator().manual_seed(52)
     q = torch.randn(sum(n for _, n in cuts), hq, d, generator=g).to(device="cuda", dtype=torch.bfloat16)
     outs = {}
-    for split in ("0", "1"):
-        monkeypatch.setenv("DIB200_PREFILL_SPLIT", split)
-        outs[split] = ops().paged_attention(q, case.cache, case.meta([0, 1, 2, 3], cuts), d ** -0.5, window)
+    for chunk in (8, 32):
+        switches.chunk_tiles(chunk)
+        outs[chunk] = ops().paged_attention(q, case.cache, case.meta([0, 1, 2, 3], cuts), d ** -0.5, window)
     assert ops()._lib("attention_prefill_tc").dib_attention_prefill_tc_status() == 0
-    torch.testing.assert_close(outs["1"].float(), outs["0"].float(), **tol(torch.bfloat16))
+    torch.testing.assert_close(outs[8].float(), outs[32].float(), **tol(torch.bfloat16))
     off = 0
     for s_, (start, n) in enumerate(cuts):
         rows = list(range(0, n, 7)) + [n - 1]          # every 7th position, and the last
         want = dense_reference(q[off:off + n][rows], case.k[s_], case.v[s_], d ** -0.5,
                                [start + r for r in rows], window)
-        torch.testing.assert_close(outs["1"][off:off + n][rows].float(), want, **tol(torch.bfloat16))
+        torch.testing.assert_close(outs[8][off:off + n][rows].float(), want, **tol(torch.bfloat16))
         off += n
 
 
+@pytest.mark.parametrize("chunk", [8, 32])
+@pytest.mark.parametrize("hq,hkv,window", [(4, 2, None), (8, 1, 1500)])
+def test_prefill_attention_bits_depend_on_the_position_alone(switches, chunk, hq, hkv, window):
+    """The same query rows (positions 2,000..2,511 of a sequence) give the same bits
+    whether their step holds them alone behind a prefix, the whole prompt, a longer
+    portion, or other sequences beside them (longer and shorter ones, prompt portions and
+    decode tokens): the key tiles and the chunk cuts are anchored at position 0, and how
+    query tiles are paired or spread over CTAs is the only thing the step decides.  With
+    chunks of 1,024 keys (several per row, merged) and of 4,096 (one)."""
+    switches.chunk_tiles(chunk)
+    d, page = 128, 16
+    lens = [2512, 5000, 300, 77]
+    case = PagedCase(lens, hkv, d, page, torch.bfloat16, seed=71)
+    g = torch.Generator().manual_seed(72)
+    q_all = torch.randn(2512, hq, d, generator=g).to(device="cuda", dtype=torch.bfloat16)
+    q_other = torch.randn(1024, hq, d, generator=g).to(device="cuda", dtype=torch.bfloat16)
+    scale = d ** -0.5
+
+    def run(entries):        # entries: [(sequence, start, count, queries)]
+        qs = torch.cat([e[3] for e in entries])
+        meta = case.meta([e[0] for e in entries], [(e[1], e[2]) for e in entries])
+        out = ops().paged_attention(qs, case.cache, meta, scale, window)
+        res, off = {}, 0
+        for e in entries:
+            res[e[0]] = out[off:off + e[2]]
+            off += e[2]
+        return res
+
+    alone = run([(0, 2000, 512, q_all[2000:2512])])[0]
+    whole = run([(0, 0, 2512, q_all)])[0][2000:]
+    longer = run([(0, 1990, 522, q_all[1990:2512])])[0][10:]
+    # decode tokens first (the batch order of a step), then portions of other sequences
+    mixed = run([(2, 299, 1, q_other[:1]), (3, 76, 1, q_other[1:2]),
+                 (0, 2000, 512, q_all[2000:2512]), (1, 4200, 800, q_other[2:802])])[0]
+    assert torch.equal(alone, whole)
+    assert torch.equal(alone, longer)
+    assert torch.equal(alone, mixed)
+    want = dense_reference(q_all[2000:2512:37], case.k[0], case.v[0], scale, list(range(2000, 2512, 37)), window)
+    torch.testing.assert_close(alone[::37].float(), want, **tol(torch.bfloat16))
+
+
 @pytest.mark.parametrize("mode", ["1", "2"])
-def test_prefill_attention_far_key_stands_out(monkeypatch, mode):
+def test_prefill_attention_far_key_stands_out(switches, mode):
     """In a 700-token prompt one key matches every query strongly: each position at or
     after it must return that key's value, whichever key tile and query tile it is in."""
-    monkeypatch.setenv("DIB200_PREFILL_TC", mode)
+    switches.attention(prefill_tc=mode)
     hq, hkv, d, page, n = 4, 2, 128, 16, 700
     g = torch.Generator().manual_seed(43)
     for far in (0, 127, 128, 383, 500):
@@ -713,3 +786,42 @@ def test_sizes_outside_a_kernels_range_are_refused_with_a_clear_error():
     # a non-contiguous input is named, not silently copied
     with pytest.raises(KernelError, match="contiguous"):
         o.rms_norm(torch.zeros(8, 4, device=dev).t(), torch.ones(8, device=dev), 1e-6)
+
+
+def test_a_wait_that_runs_out_ends_the_kernel_and_is_reported_once():
+    """Every mbarrier wait of the package's kernels is bounded.  A test-only kernel waits
+    one millisecond on a barrier that nothing arrives on (and that no copy targets): the
+    launch ends by itself, its error word is set, ``ops.check_kernel_status`` raises a
+    ``KernelError`` that names the library, clears the word, and the next check passes; a
+    wait whose barrier is arrived on sets nothing."""
+    import time
+    from ctypes import c_int, c_ulonglong, c_void_p
+    from pathlib import Path
+    from deterministic_inference_b200.kernels import build
+    from deterministic_inference_b200.kernels.ops import KernelError
+    build.register_source("test_wait", Path(__file__).parent / "kernels" / "wait_runs_out.cu")
+    lib = build.load_library("test_wait")
+    ops().register_kernel_status("test_wait", lib.test_wait_status, lib.test_wait_status_clear)
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    try:
+        ops().check_kernel_status()
+        assert lib.test_wait_launch(c_ulonglong(1_000_000), c_int(1), stream) == 0
+        torch.cuda.synchronize()
+        ops().check_kernel_status()                       # the barrier was arrived on: nothing set
+        t0 = time.perf_counter()
+        assert lib.test_wait_launch(c_ulonglong(1_000_000), c_int(0), stream) == 0
+        torch.cuda.synchronize()
+        assert time.perf_counter() - t0 < 1.0             # it gave up after about a millisecond
+        assert ops().kernel_status()["test_wait"] == 7
+        with pytest.raises(KernelError, match="test_wait"):
+            ops().check_kernel_status()
+        assert ops().kernel_status()["test_wait"] == 0    # reported once, then cleared
+        ops().check_kernel_status()
+        # the context is as usable as before
+        x = torch.ones(8, 64, device="cuda", dtype=torch.bfloat16)
+        w = torch.ones(64, device="cuda", dtype=torch.float32)
+        torch.testing.assert_close(ops().rms_norm(x, w, 1e-6).float(), torch.ones(8, 64, device="cuda"),
+                                   atol=1e-2, rtol=1e-2)
+    finally:
+        from deterministic_inference_b200.kernels import ops as _ops
+        _ops._extra_status.pop("test_wait", None)

@@ -54,6 +54,19 @@ CASES = {
     "b": ([1, 9, 31, 64, 100], 4),
     "bw": ([3, 40, 77, 130, 24], 6),
     "c": ([2, 16, 48, 95], 8),
+    # heads of 128: lengths around the tiles of 128 keys and rows, up to several tiles
+    "d": ([5, 129, 300, 517, 700], 12),
+    "e": ([64, 128, 257, 390, 655], 14),
+    # benchmark layer sizes: prompts of many key tiles and decode over many splits
+    "f": ([1300, 150, 2100, 700], 16),
+}
+# portion sizes of the "portions" and "mixed" cuttings: the long requests of the head-128
+# models also get portions above 128 rows (the library's matrix product, several query
+# tiles per sequence) beside the small ones
+SIZES = {
+    "d": dict(portions=(13, 130, 2, 257, 5, 2, 64, 200, 3), mixed=(11, 150, 2, 17, 129, 5, 2, 300, 3)),
+    "e": dict(portions=(200, 7, 2, 131, 2, 31, 256, 3), mixed=(140, 2, 17, 260, 5, 2, 29, 3)),
+    "f": dict(portions=(512, 100, 2, 700, 129, 31), mixed=(400, 2, 130, 512, 17, 257, 3)),
 }
 
 
@@ -71,20 +84,9 @@ def plain_logits(tiny_model_dirs):
     return out
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", list(CASES))
-def test_replay_all_cuttings(name, dtype, tiny_model_dirs, plain_logits, tmp_path):
-    cfg, reqs, refs = plain_logits[name]
-    page = TINY[name]["page_size"]
-    trace = ru.Trace()
-    # the mixed cutting first sizes the pool; the others reuse it one request at a time
-    ru.mixed(trace, reqs)
-    ru.whole(trace, reqs)
-    ru.last_one_by_one(trace, reqs)
-    ru.portions(trace, reqs)
-    out = ru.run_trace(tiny_model_dirs[name], dtype, trace, tmp_path / "out", page_size=page)
-    got = ru.read_rows(out, trace, cfg["vocab_size"])
-    assert got, "the trace wrote nothing"
+def check_rows(name, dtype, got, refs):
+    """Every written row against the plain implementation, within the bounds of this file's
+    header; returns the worst difference as a share of its row's scale."""
     if dtype == "float32":
         want = refs["float64"]
         yard = [max(row_error(a, b) for a, b in zip(p32, p64))
@@ -103,11 +105,78 @@ def test_replay_all_cuttings(name, dtype, tiny_model_dirs, plain_logits, tmp_pat
         assert err <= bound, (f"{name}/{dtype}: request {key} position {pos}: "
                               f"abs diff {err:.4g} exceeds {bound:.4g}")
         worst = max(worst, err / scale)
-    # every cutting covered every position of every request
-    for kind in "mwtp":
+    return worst
+
+
+def covered(got, reqs, kinds):
+    """Every cutting wrote every position of every request."""
+    for kind in kinds:
         for i, r in enumerate(reqs):
             assert all((f"{kind}{i}", p) in got for p in range(len(r))), (kind, i)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(CASES))
+def test_replay_all_cuttings(name, dtype, tiny_model_dirs, plain_logits, tmp_path):
+    cfg, reqs, refs = plain_logits[name]
+    page = TINY[name]["page_size"]
+    sizes = SIZES.get(name, {})
+    trace = ru.Trace()
+    # the mixed cutting first sizes the pool; the others reuse it one request at a time
+    ru.mixed(trace, reqs, **({"sizes": sizes["mixed"]} if sizes else {}))
+    ru.whole(trace, reqs)
+    ru.last_one_by_one(trace, reqs)
+    ru.portions(trace, reqs, **({"sizes": sizes["portions"]} if sizes else {}))
+    out = ru.run_trace(tiny_model_dirs[name], dtype, trace, tmp_path / "out", page_size=page)
+    got = ru.read_rows(out, trace, cfg["vocab_size"])
+    assert got, "the trace wrote nothing"
+    worst = check_rows(name, dtype, got, refs)
+    covered(got, reqs, "mwtp")
     print(f"{name}/{dtype}: worst diff {worst:.3e} of the row's scale")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["d", "e", "b"])
+def test_replay_with_captured_graphs(name, dtype, tiny_model_dirs, tmp_path):
+    """The step function as generation runs it: pure-decode steps and steps whose shape
+    has come twice before are replayed as captured CUDA graphs.  Four requests of one
+    length, cut alike, so that every shape repeats (portions of 96 and of 200 tokens, then
+    single tokens), and the mixed cutting on top; every row against the plain
+    implementation, and the replayed run against a launched run of the same trace: equal
+    bits (a captured step sizes its grids for the longest sequence its block-table width
+    allows, which must not change what a row adds up)."""
+    cfg, w = plain_qwen3.read_model_dir(tiny_model_dirs[name])
+    _, w64 = plain_qwen3.read_model_dir(tiny_model_dirs[name], torch.float64)
+    n = 200 if name == "b" else 520
+    same = _requests(cfg["vocab_size"], [n] * 4, 41)
+    other = _requests(cfg["vocab_size"], [33, 150, 77], 42)
+    reqs = same + other
+    refs = {"float64": [plain_qwen3.forward(cfg, w64, r) for r in reqs],
+            "float32": [plain_qwen3.forward(cfg, w, r) for r in reqs],
+            "bfloat16": [plain_qwen3.forward(cfg, w, r, store_bf16=True) for r in reqs]}
+    trace = ru.Trace()
+    passes = {"": 96, "x": 96, "y": 200, "z": 200}     # every shape of a pass comes again in the next
+    for prefix, portion in passes.items():
+        ru.lockstep(trace, same, portion=portion, prefix=prefix)
+    ru.mixed(trace, reqs)
+    page = TINY[name]["page_size"]
+    outs = {}
+    for graphs in (True, False):
+        out = ru.run_trace(tiny_model_dirs[name], dtype, trace, tmp_path / f"out{int(graphs)}",
+                           page_size=page, cuda_graphs=graphs)
+        outs[graphs] = ru.read_rows(out, trace, cfg["vocab_size"])
+    for key_pos, row in outs[True].items():
+        assert torch.equal(row, outs[False][key_pos]), key_pos
+    worst = 0.0
+    for prefix in passes:                              # "xl0" is request 0 again
+        got = {(k[len(prefix):], pos): row for (k, pos), row in outs[True].items()
+               if k.startswith(prefix + "l")}
+        worst = max(worst, check_rows(name, dtype, got, refs))
+        covered(got, same, "l")
+    got = {kp: row for kp, row in outs[True].items() if kp[0].startswith("m")}
+    worst = max(worst, check_rows(name, dtype, got, refs))
+    covered(got, reqs, "m")
+    print(f"{name}/{dtype} with graphs: worst diff {worst:.3e} of the row's scale")
 
 
 def test_cuttings_agree_bitwise_in_float32(tiny_model_dirs, plain_logits, tmp_path):

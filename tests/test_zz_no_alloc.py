@@ -60,9 +60,10 @@ def test_noalloc_entry_matches_regular_entry_twice(monkeypatch, hq, hkv, d, page
         want = ops.paged_attention(q, case.cache, meta, d ** -0.5, window or None)
         # the regular entry point on the kernels this entry point launches (keys copied row
         # by row instead of page-wise by TMA)
-        monkeypatch.setenv("DIB200_DECODE_TMA", "0")
+        from deterministic_inference_b200.kernels import attention_bf16
+        monkeypatch.setitem(attention_bf16.SWITCHES, "decode_tma", False)
         want_same = ops.paged_attention(q, case.cache, meta, d ** -0.5, window or None)
-        monkeypatch.delenv("DIB200_DECODE_TMA")
+        monkeypatch.setitem(attention_bf16.SWITCHES, "decode_tma", True)
         out = torch.full_like(q, float("nan"))
         max_splits = -(-max(lens) // 128)
         assert need(c_int(len(lens)), c_int(max_splits), c_int(hq), c_int(d)) <= MAX_FLOATS
@@ -74,6 +75,9 @@ def test_noalloc_entry_matches_regular_entry_twice(monkeypatch, hq, hkv, d, page
         torch.testing.assert_close(out.float(), want.float(), atol=2e-2, rtol=2e-2)
         assert torch.equal(out, want_same)
         prev = out
+    from deterministic_inference_b200.kernels import build
+    lib = build.load_library("decode_attention_noalloc")
+    assert lib.dib_decode_attention_noalloc_status() == 0
 
 
 def test_noalloc_entry_refuses_what_does_not_fit():
