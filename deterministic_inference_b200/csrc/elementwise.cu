@@ -116,7 +116,7 @@ __global__ void rms_norm_vec_kernel(T* __restrict__ x, T* __restrict__ residual,
                                     float eps) {
   pdl_prologue(x, residual);
   constexpr int N = Vec<T>::N, VPT = N / 4;
-  __shared__ float scratch[128];
+  __shared__ float scratch[256];   // groups of 128 elements: at most 4096 vectors of N
   const size_t base = (size_t)blockIdx.x * H;
   float v[ITERS][N];
   float ss[ITERS][VPT];

@@ -105,7 +105,11 @@ def check_rows(name, dtype, got, refs):
         assert err <= bound, (f"{name}/{dtype}: request {key} position {pos}: "
                               f"abs diff {err:.4g} exceeds {bound:.4g}")
         worst = max(worst, err / scale)
+        WORST_SHARE[(name, dtype)] = max(WORST_SHARE.get((name, dtype), 0.0), err / max(yard[i], 1e-30))
     return worst
+
+
+WORST_SHARE: dict = {}     # (case, dtype) -> largest difference seen, in units of the request's yardstick
 
 
 def covered(got, reqs, kinds):
@@ -132,7 +136,8 @@ def test_replay_all_cuttings(name, dtype, tiny_model_dirs, plain_logits, tmp_pat
     assert got, "the trace wrote nothing"
     worst = check_rows(name, dtype, got, refs)
     covered(got, reqs, "mwtp")
-    print(f"{name}/{dtype}: worst diff {worst:.3e} of the row's scale")
+    print(f"{name}/{dtype}: worst diff {worst:.3e} of the row's scale, "
+          f"{WORST_SHARE[(name, dtype)]:.3f} of the request's yardstick")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -176,7 +181,8 @@ def test_replay_with_captured_graphs(name, dtype, tiny_model_dirs, tmp_path):
     got = {kp: row for kp, row in outs[True].items() if kp[0].startswith("m")}
     worst = max(worst, check_rows(name, dtype, got, refs))
     covered(got, reqs, "m")
-    print(f"{name}/{dtype} with graphs: worst diff {worst:.3e} of the row's scale")
+    print(f"{name}/{dtype} with graphs: worst diff {worst:.3e} of the row's scale, "
+          f"{WORST_SHARE[(name, dtype)]:.3f} of the request's yardstick")
 
 
 def test_cuttings_agree_bitwise_in_float32(tiny_model_dirs, plain_logits, tmp_path):
