@@ -502,10 +502,9 @@ def gumbel_sample(logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch
     """int32 [R]: rows with temperature <= 0 take the argmax; the others the
     position-seeded Gumbel-max draw from softmax(logits / temperature), restricted
     to ids with keep != 0 when a mask (uint8 [R, V]) is given.  ``top_ks`` (int64 [R],
-    <= 0: off) and ``top_ps`` (float32 [R], >= 1: off), for rows wider than 8,192 ids:
-    top-k / top-p applied inside the kernels by a probability threshold found without a
-    sort (``return_thresholds``: also the int32 bits of each row's smallest kept
-    probability, 0 where nothing is dropped)."""
+    <= 0: off) and ``top_ps`` (float32 [R], >= 1: off): top-k / top-p applied inside the
+    kernels by a probability threshold found without a sort (``return_thresholds``: also
+    the int32 bits of each row's smallest kept probability, 0 where nothing is dropped)."""
     _need(logits, "logits", torch.float32, 2)
     r, v = logits.shape
     _need(temperatures, "temperatures", torch.float32, 1)
@@ -519,8 +518,9 @@ def gumbel_sample(logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch
             raise KernelError(f"gumbel_sample: keep {tuple(keep.shape)} vs logits {(r, v)}")
     out = torch.empty(r, dtype=torch.int32, device=logits.device)
     lib = _lib("sampling")
-    if v > 8192 and r <= 65535:
-        # wide rows: a block per chunk of a row (normaliser, then scores), then the best chunk
+    filtered = top_ks is not None or top_ps is not None
+    if (v > 8192 or filtered) and r <= 65535:
+        # a block per chunk of a row (normaliser, then scores), then the best chunk
         chunks = -(-v // 4096)
         sf = torch.empty(3, r, chunks, dtype=torch.float32, device=logits.device)
         si = torch.empty(r, chunks, dtype=torch.int32, device=logits.device)
@@ -540,9 +540,8 @@ def gumbel_sample(logits: torch.Tensor, temperatures: torch.Tensor, seeds: torch
                                            _ptr(sf), _ptr(si), _ptr(out), c_int(r), c_int(v), _stream())
         _check(st, "gumbel_sample", kernels=3 if thresh is None else 7)
         return (out, thresh) if return_thresholds else out
-    if top_ks is not None or top_ps is not None:
-        raise KernelError("gumbel_sample: top_ks / top_ps are taken for rows wider than 8192 ids; "
-                          "pass a keep mask for narrower rows")
+    if filtered:
+        raise KernelError("gumbel_sample: top_ks / top_ps with more than 65535 rows")
     st = lib.dib_gumbel_sample(_ptr(logits), _ptr(temperatures), _ptr(seeds), _ptr(sample_positions),
                                _ptr(keep), _ptr(out), c_int(r), c_int(v), _stream())
     _check(st, "gumbel_sample")

@@ -1,1 +1,1 @@
-from .sampler import keep_mask, sample
+from .sampler import sample

@@ -8,11 +8,10 @@ vocabulary id), so a request's draw does not depend on the batch
 the token generated after n tokens of the sequence has position n
 (sid/engine/batch.py:3-10).
 
-argmax and the Gumbel draw are this package's kernels.  top-k / top-p: for rows wider
-than 8,192 ids the kernels find, without a sort, the probability threshold that the
-reference's sort-and-cumulate rule amounts to (tokens that tie with the threshold all
-stay; masses are added in fixed point); for narrower rows the mask is built with a sort
-on the device as in the reference.  Only when some row asks for it.
+argmax and the Gumbel draw are this package's kernels.  top-k / top-p: the kernels find,
+without a sort, the probability threshold that the reference's sort-and-cumulate rule
+amounts to (tokens that tie with the threshold all stay; masses are added in fixed
+point), and draw among the ids at or above it.  Only when some row asks for it.
 """
 
 from __future__ import annotations
@@ -21,26 +20,6 @@ import numpy as np
 import torch
 
 from ..kernels import ops
-
-
-def keep_mask(logits: torch.Tensor, temperatures: torch.Tensor, top_ks: torch.Tensor,
-              top_ps: torch.Tensor) -> torch.Tensor:
-    """uint8 [R, V]: 1 for ids that survive top-k / top-p
-    (sid/engine/sampler.py:44-62): sort the probabilities descending; drop a token
-    when the mass before it exceeds top_p or its rank >= top_k; rank 0 stays."""
-    stochastic = temperatures > 0
-    temps = torch.where(stochastic, temperatures, torch.ones_like(temperatures))
-    probs = torch.softmax(logits / temps.unsqueeze(-1), dim=-1)
-    probs_sort, probs_idx = probs.sort(dim=-1, descending=True)
-    cum = torch.cumsum(probs_sort, dim=-1)
-    dropped = (cum - probs_sort) > top_ps.unsqueeze(-1)
-    ranks = torch.arange(probs.shape[-1], device=probs.device).expand_as(probs_sort)
-    k = torch.where(top_ks > 0, top_ks, torch.full_like(top_ks, probs.shape[-1]))
-    dropped |= ranks >= k.unsqueeze(-1)
-    dropped[:, 0] = False
-    keep = torch.zeros_like(dropped)
-    keep.scatter_(-1, probs_idx, ~dropped)
-    return keep.to(torch.uint8).contiguous()
 
 
 def sample(logits: torch.Tensor, params: list, sample_positions: list) -> torch.Tensor:
@@ -68,8 +47,7 @@ def sample(logits: torch.Tensor, params: list, sample_positions: list) -> torch.
     device = host.to(dev, non_blocking=True)
     d64, d32 = device[:n64 * 8].view(torch.int64), device[n64 * 8:].view(torch.float32)
     seeds, pos, temps = d64[:r], d64[r:2 * r], d32[:r]
-    if filtered and logits.shape[1] > 8192:
-        # wide rows: the kernels drop what top-k / top-p drop, by a threshold found without a sort
+    if filtered:
+        # the kernels drop what top-k / top-p drop, by a threshold found without a sort
         return ops.gumbel_sample(logits, temps, seeds, pos, top_ks=d64[2 * r:], top_ps=d32[r:])
-    keep = keep_mask(logits, temps, d64[2 * r:], d32[r:]) if filtered else None
-    return ops.gumbel_sample(logits, temps, seeds, pos, keep)
+    return ops.gumbel_sample(logits, temps, seeds, pos)

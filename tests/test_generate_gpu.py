@@ -11,6 +11,7 @@ import pytest
 import torch
 
 from tests import plain_qwen3
+from tests.rounding import divergence_is_a_rounding_flip
 from tests.conftest import ROOT, TINY
 
 pytestmark = pytest.mark.gpu
@@ -26,24 +27,6 @@ def _engine(model_dir, dtype, **kw):
 def _prompts(vocab, lens, seed):
     g = torch.Generator().manual_seed(seed)
     return [torch.randint(0, vocab - 1, (n,), generator=g).tolist() for n in lens]
-
-
-def _divergence_is_a_rounding_flip(cfg, w, prompt, got, want):
-    """bfloat16 greedy tokens may leave the float32 plain implementation's only where
-    rounding can flip the argmax.  At the first differing token: R = what bfloat16
-    storage rounding does to this position's logits (plain implementation with
-    storage emulated minus plain float32).  The engine's logits lie within 1.5 R of
-    the float32 ones (tests/test_replay_gpu.py), so the token it picked must be within
-    3 R of the best one in the float32 logits."""
-    for i, (a, b) in enumerate(zip(got, want)):
-        if a != b:
-            ctx = prompt + want[:i]
-            l32 = plain_qwen3.forward(cfg, w, ctx)[-1]
-            lemu = plain_qwen3.forward(cfg, w, ctx, store_bf16=True)[-1]
-            r = float((l32 - lemu).abs().max())
-            gap = float(l32[b] - l32[a])
-            return gap <= 3 * r + 1e-3, f"token {i}: gap {gap:.3f}, rounding effect {r:.3f}"
-    return True, ""
 
 
 @pytest.mark.parametrize("name", ["a", "b"])
@@ -89,9 +72,9 @@ def test_greedy_bfloat16_follows_plain(name, tiny_model_dirs):
                   max_prefill_tokens=24)
     outs = eng.generate(prompts, SamplingParams(max_new_tokens=10, ignore_eos=True))
     for p, o, wnt in zip(prompts, outs, want):
-        ok, why = _divergence_is_a_rounding_flip(cfg, w, p, o.token_ids, wnt)
+        ok, why = divergence_is_a_rounding_flip(cfg, w, p, o.token_ids, wnt)
         assert ok, (why, o.token_ids, wnt)
-        assert o.token_ids[0] == wnt[0] or why      # (a flip at the very first token is reported too)
+        assert len(o.token_ids) == len(wnt)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -126,7 +109,7 @@ def test_first_tokens_of_a_sequence(dtype, tiny_model_dirs):
         assert [o.token_ids for o in outs] == want
     else:
         for p, o, wnt in zip(prompts, outs, want):
-            ok, why = _divergence_is_a_rounding_flip(cfg, w, p, o.token_ids, wnt)
+            ok, why = divergence_is_a_rounding_flip(cfg, w, p, o.token_ids, wnt)
             assert ok, (why, o.token_ids, wnt)
 
 

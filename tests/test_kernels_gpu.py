@@ -699,13 +699,13 @@ def test_gumbel_draw_independent_of_batch_and_depends_on_position(v):
     assert len(set(one(same, [42] * 64, list(range(64))).tolist())) > 1
 
 
-@pytest.mark.parametrize("v", [151936, 20001])
+@pytest.mark.parametrize("v", [151936, 20001, 5000, 300])
 def test_top_k_top_p_threshold_is_what_the_sort_rule_keeps(v):
-    """Wide rows: the kernels keep {p >= threshold}; the threshold they find without a sort
+    """The kernels keep {p >= threshold}; the threshold they find without a sort
     keeps what the reference's rule keeps (sort descending, drop when the mass before a
     token exceeds top_p or its rank reaches top_k), up to a token at the boundary whose
     probability the two computations round differently."""
-    from deterministic_inference_b200.sampling.sampler import keep_mask
+    from tests.torch_kernels import keep_mask
     torch.manual_seed(23)
     r = 12
     logits = 4 * torch.randn(r, v, device="cuda")

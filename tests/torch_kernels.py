@@ -162,8 +162,28 @@ def gumbel_scores(logits, temperatures, seeds, sample_positions, keep=None):
     return logp + seeded_gumbel(seeds, sample_positions, logits.shape[1])
 
 
-def gumbel_sample(logits, temperatures, seeds, sample_positions, keep=None):
+def keep_mask(logits, temperatures, top_ks, top_ps):
+    """uint8 [R, V]: 1 for ids that survive top-k / top-p by the reference's rule
+    (sid/engine/sampler.py:44-62): probabilities sorted descending; a token is dropped when
+    the mass before it exceeds top_p or its rank reaches top_k; the first stays."""
+    temps = torch.where(temperatures > 0, temperatures, torch.ones_like(temperatures))
+    p = torch.softmax(logits / temps.unsqueeze(-1), dim=-1)
+    order = torch.argsort(p, dim=-1, descending=True, stable=True)
+    sorted_p = torch.gather(p, -1, order)
+    before = torch.cumsum(sorted_p, dim=-1) - sorted_p
+    rank = torch.arange(p.shape[-1], device=p.device).unsqueeze(0)
+    limit = torch.where(top_ks > 0, top_ks, torch.full_like(top_ks, p.shape[-1])).unsqueeze(-1)
+    stays = (before <= top_ps.unsqueeze(-1)) & (rank < limit)
+    stays[:, 0] = True
+    mask = torch.zeros_like(stays)
+    mask.scatter_(-1, order, stays)
+    return mask.to(torch.uint8).contiguous()
+
+
+def gumbel_sample(logits, temperatures, seeds, sample_positions, keep=None, top_ks=None, top_ps=None):
     """sid/engine/sampler.py:32-69"""
+    if top_ks is not None:
+        keep = keep_mask(logits, temperatures, top_ks, top_ps)
     greedy = torch.argmax(logits, dim=-1)
     sampled = torch.argmax(gumbel_scores(logits, temperatures, seeds, sample_positions, keep), dim=-1)
     return torch.where(temperatures > 0, sampled, greedy).to(torch.int32)
