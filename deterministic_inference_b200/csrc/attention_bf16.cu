@@ -346,6 +346,7 @@ decode_attention_stage1_tma_kernel(const __grid_constant__ CUtensorMap map,
 // nor the arithmetic of a split stand between two copies.  Each split is computed
 // exactly as by the kernel above.
 struct DecodeItem { int b, kvh, split, kv_len; };
+constexpr int gcd_c(int a, int b) { return b == 0 ? a : gcd_c(b, a % b); }
 
 // The next split at or after flat index idx that belongs to this CTA and lies inside
 // its sequence's visible range; false when there is none.  idx is left on the item.
@@ -397,7 +398,6 @@ decode_attention_stage1_pipe_kernel(const __grid_constant__ CUtensorMap map,
   // "full" barriers exist once per (tile of the ring, consumer group): a wait names a
   // phase by its parity alone, so a barrier must have one waiter that takes its phases
   // in order; a tile that serves the groups in turn has one barrier for each.
-  static_assert(GROUPS == 2, "the use counts below assume two groups");
   unsigned long long* full_k = reinterpret_cast<unsigned long long*>(tail);   // [KS][GROUPS]
   unsigned long long* empty_k = full_k + KS * GROUPS;                         // [KS]
   unsigned long long* full_v = empty_k + KS;                                  // [VS][GROUPS]
@@ -524,9 +524,11 @@ decode_attention_stage1_pipe_kernel(const __grid_constant__ CUtensorMap map,
   pdl_wait(q);   // transitively, everything this kernel writes over has been read
   for (int n = g;; n += GROUPS) {
     const int ks = n % KS, vs = n % VS;
-    // this group's own count of uses of the tile: every second use of a ring of odd length
-    const unsigned par_k = ((KS % 2) ? (n / KS) >> 1 : n / KS) & 1;
-    const unsigned par_v = ((VS % 2) ? (n / VS) >> 1 : n / VS) & 1;
+    // this group's own count of uses of the tile: item m uses stage m % KS for group
+    // m % GROUPS, so the pair (stage, group) comes again every lcm(KS, GROUPS) items
+    constexpr int LCM_K = KS * GROUPS / gcd_c(KS, GROUPS), LCM_V = VS * GROUPS / gcd_c(VS, GROUPS);
+    const unsigned par_k = (n / LCM_K) & 1;
+    const unsigned par_v = (n / LCM_V) & 1;
     unsigned long long* fk = &full_k[ks * GROUPS + g];
     unsigned long long* fv = &full_v[vs * GROUPS + g];
     mbar_wait_once(fk, par_k, dead, 7);
@@ -635,8 +637,10 @@ int launch_decode_tma(const void* q, void* out, const void* cache, long long num
                page_size, scale, window);
     DIB_CHECK_LAUNCH();
   }
-  launch_decode_merge(part_o, part_lse, seq_lens, out, num_seqs, max_splits, Hq, D, window, st);
-  DIB_CHECK_LAUNCH();
+  if (out != nullptr) {   // (no output: the caller merges the partial results itself)
+    launch_decode_merge(part_o, part_lse, seq_lens, out, num_seqs, max_splits, Hq, D, window, st);
+    DIB_CHECK_LAUNCH();
+  }
   return DIB_OK;
 }
 
@@ -679,9 +683,22 @@ int dib_extend_attention_bf16(const void* q, void* out, const void* cache, const
 #undef CALL
 }
 
+// Stage 2 alone: out [num_seqs, Hq, D] from the partial results of a call that was made
+// without an output.
+int dib_decode_attention_merge(const float* part_o, const float* part_lse, const int* seq_lens,
+                               void* out, int num_seqs, int max_splits, int Hq, int D, int window,
+                               cudaStream_t st) {
+  if (num_seqs == 0) return DIB_OK;
+  if (num_seqs > 65535 || max_splits < 1 || D < 1 || D > 1024) return DIB_BAD_SIZE;
+  launch_decode_merge(part_o, part_lse, seq_lens, out, num_seqs, max_splits, Hq, D, window, st);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
 // The first num_seqs sequences of the batch, one token each (token index = sequence
 // index).  part_o: float32 [num_seqs, Hq, max_splits, D]; part_lse: [num_seqs, Hq,
-// max_splits]; max_splits >= ceil(longest sequence / 128).
+// max_splits]; max_splits >= ceil(longest sequence / 128).  out == nullptr: only the
+// partial results are made (the caller merges them, see dib_decode_attention_merge).
 int dib_decode_attention_bf16(const void* q, void* out, const void* cache, long long num_pages,
                               const int* block_table, int max_blocks, const int* seq_lens,
                               float* part_o, float* part_lse, int num_seqs, int max_splits, int Hq,

@@ -18,6 +18,7 @@
 // Cache layout of a layer: [num_pages, 2, num_kv_heads, page_size, head_dim].
 // head_dim: multiples of 16 up to 128.  Group ratio: up to 64 (extend), 16 (decode).
 #pragma once
+#include "attention_merge.cuh"
 #include "common.cuh"
 
 namespace {
@@ -378,6 +379,7 @@ decode_attention_stage1_kernel(const __nv_bfloat16* __restrict__ q,
   // are contiguous, so a row is D*2 contiguous bytes).  Two barriers count the
   // bytes, so the scores can start while V is still arriving.  Rows at or beyond
   // the sequence's length are zero-filled by their thread.
+  static_assert(DEC_SPLIT == MERGE_SPLIT, "one split size");
   static_assert(DEC_THREADS == DEC_SPLIT, "one thread per key row");
   unsigned long long* bars =
       reinterpret_cast<unsigned long long*>(smem_raw + (size_t)2 * DEC_SPLIT * (D + PAD) * 2);
@@ -503,7 +505,6 @@ decode_attention_stage1_kernel(const __nv_bfloat16* __restrict__ q,
 // the batch.  The partial results of the first chunk are requested before the
 // sequence's length is known (what lies beyond its last split is read but not used), so
 // a sequence of one chunk waits for memory once.
-constexpr int MERGE_CH = 16;
 __global__ void decode_attention_stage2_kernel(const float* __restrict__ part_o,
                                                const float* __restrict__ part_lse,
                                                const int* __restrict__ seq_lens,
@@ -514,17 +515,16 @@ __global__ void decode_attention_stage2_kernel(const float* __restrict__ part_o,
   const int b = blockIdx.x, h = blockIdx.y;
   const size_t row = ((size_t)b * Hq + h) * max_splits;
   const int kv_len = seq_lens[b];
-  float lse_r[CH], o_r[CH];
+  float lse_r[CH], o_r[CH][1];
 #pragma unroll
   for (int j = 0; j < CH; ++j) lse_r[j] = j < max_splits ? part_lse[row + j] : NEG_BIG;
 #pragma unroll
   for (int j = 0; j < CH; ++j)
-    o_r[j] = (j < max_splits && (int)threadIdx.x < D) ? part_o[(row + j) * D + threadIdx.x] : 0.f;
-  const int pos = kv_len - 1;
-  const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    o_r[j][0] = (j < max_splits && (int)threadIdx.x < D) ? part_o[(row + j) * D + threadIdx.x] : 0.f;
   // (a caller that passes fewer splits than the sequence has keys for gets a result over
   // the splits there are, never a read beyond the row)
-  const int s0 = first_key / DEC_SPLIT, s1 = min(pos / DEC_SPLIT, max_splits - 1);
+  int s0, s1;
+  merge_range(kv_len, window, max_splits, s0, s1);
   const int c0 = s0 / CH, c1 = s1 / CH;
   float M = NEG_BIG;
 #pragma unroll
@@ -533,7 +533,7 @@ __global__ void decode_attention_stage2_kernel(const float* __restrict__ part_o,
   for (int s = max(s0, CH); s <= s1; ++s) M = fmaxf(M, part_lse[row + s]);
   bool first = true;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float total = 0.f, total_den = 0.f;
+    float total[1] = {0.f}, total_den = 0.f;
     for (int c = c0; c <= c1; ++c) {
       if (c > 0 || !first) {
 #pragma unroll
@@ -541,28 +541,14 @@ __global__ void decode_attention_stage2_kernel(const float* __restrict__ part_o,
           const int s = c * CH + j;
           const bool in = s >= s0 && s <= s1;
           lse_r[j] = in ? part_lse[row + s] : NEG_BIG;
-          o_r[j] = in ? part_o[(row + s) * D + d] : 0.f;
+          o_r[j][0] = in ? part_o[(row + s) * D + d] : 0.f;
         }
       }
-      float acc = 0.f, den = 0.f;
-#pragma unroll
-      for (int j = 0; j < CH; ++j) {
-        const int s = c * CH + j;
-        if (s >= s0 && s <= s1) {
-          const float w = expf(lse_r[j] - M);
-          acc += w * o_r[j];
-          den += w;
-        }
-      }
-      if (c == c0) {
-        total = acc;
-        total_den = den;
-      } else {
-        total += acc;
-        total_den += den;
-      }
+      float acc[1], den;
+      merge_chunk<1>(lse_r, o_r, c, s0, s1, M, acc, den);
+      merge_add<1>(c == c0, acc, den, total, total_den);
     }
-    out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(total / total_den);
+    out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(merge_finish(total[0], total_den));
     first = false;
   }
 }
@@ -590,16 +576,15 @@ decode_attention_stage2_wide_kernel(const float* __restrict__ part_o,
   const int kv_len = seq_lens[b];
   // chunk g is requested before the sequence's length is known: it is this group's
   // first chunk unless a window has moved the range past it
-  float lse_r[CH], o_r[CH];
+  float lse_r[CH], o_r[CH][1];
 #pragma unroll
   for (int j = 0; j < CH; ++j) {
     const int s = g * CH + j;
     lse_r[j] = s < max_splits ? part_lse[row + s] : NEG_BIG;
-    o_r[j] = (s < max_splits && d < D) ? part_o[(row + s) * D + d] : 0.f;
+    o_r[j][0] = (s < max_splits && d < D) ? part_o[(row + s) * D + d] : 0.f;
   }
-  const int pos = kv_len - 1;
-  const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int s0 = first_key / DEC_SPLIT, s1 = min(pos / DEC_SPLIT, max_splits - 1);
+  int s0, s1;
+  merge_range(kv_len, window, max_splits, s0, s1);
   const int c0 = s0 / CH, c1 = s1 / CH;
   // the largest lse of the sequence's splits (a maximum does not depend on the order):
   // every thread of a group over the group's chunks, then over the groups
@@ -627,23 +612,15 @@ decode_attention_stage2_wide_kernel(const float* __restrict__ part_o,
         const int s = c * CH + j;
         const bool in = s >= s0 && s <= s1;
         lse_r[j] = in ? part_lse[row + s] : NEG_BIG;
-        o_r[j] = (in && d < D) ? part_o[(row + s) * D + d] : 0.f;
+        o_r[j][0] = (in && d < D) ? part_o[(row + s) * D + d] : 0.f;
       }
     }
-    float acc = 0.f, den = 0.f;
-#pragma unroll
-    for (int j = 0; j < CH; ++j) {
-      const int s = c * CH + j;
-      if (s >= s0 && s <= s1) {
-        const float w = expf(lse_r[j] - M);
-        acc += w * o_r[j];
-        den += w;
-      }
-    }
+    float acc[1], den;
+    merge_chunk<1>(lse_r, o_r, c, s0, s1, M, acc, den);
     if (c0 == c1) {      // one chunk: its sum is the result
-      if (d < D) out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(acc / den);
+      if (d < D) out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(merge_finish(acc[0], den));
     } else {
-      if (d < D) s_acc[c - c0][d] = acc;
+      if (d < D) s_acc[c - c0][d] = acc[0];
       if (d == 0) s_den[c - c0] = den;
     }
   }
@@ -652,10 +629,10 @@ decode_attention_stage2_wide_kernel(const float* __restrict__ part_o,
   if (g == 0 && d < D) {
     float total = s_acc[0][d], total_den = s_den[0];
     for (int k = 1; k <= c1 - c0; ++k) {
-      total += s_acc[k][d];
-      total_den += s_den[k];
+      total = __fadd_rn(total, s_acc[k][d]);
+      total_den = __fadd_rn(total_den, s_den[k]);
     }
-    out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(total / total_den);
+    out[((size_t)b * Hq + h) * D + d] = __float2bfloat16_rn(merge_finish(total, total_den));
   }
 }
 
@@ -726,8 +703,10 @@ int launch_decode(const void* q, void* out, const void* cache, const int* bt, in
                                         max_blocks, seq_lens, part_o, part_lse, max_splits, Hq, Hkv,
                                         page_size, scale, window);
   DIB_CHECK_LAUNCH();
-  launch_decode_merge(part_o, part_lse, seq_lens, out, num_seqs, max_splits, Hq, D, window, st);
-  DIB_CHECK_LAUNCH();
+  if (out != nullptr) {
+    launch_decode_merge(part_o, part_lse, seq_lens, out, num_seqs, max_splits, Hq, D, window, st);
+    DIB_CHECK_LAUNCH();
+  }
   return DIB_OK;
 }
 

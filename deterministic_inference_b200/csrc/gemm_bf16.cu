@@ -24,6 +24,7 @@
 
 #include <cstdlib>
 
+#include "attention_merge.cuh"
 #include "common.cuh"
 
 namespace {
@@ -121,6 +122,183 @@ __device__ __forceinline__ float ld_peer_smem(const float* local, unsigned rank)
   return v;
 }
 
+// ---- the token operand made inside the kernel.  Instead of fetching X by TMA, the CTA
+// computes the columns of X it needs (its range of k) from what the kernel before it left,
+// and writes them to shared memory in the layout the TMA would have produced (rows of 128
+// bytes per k-block, 128-byte swizzle), so the kernel that would have made X, and the trip
+// of X through memory, are gone.  Two forms:
+//   PRO_GATE:  X = silu(gate) * up of a gated feed-forward whose [gate | up] product lies
+//              in memory as `S` float32 partial products of a split k (the sums in split
+//              order, rounded to bfloat16 as stored products, then the gate, as the
+//              kernel that reads such partials computes it);
+//   PRO_MERGE: X = the split-KV decode attention's output, merged from the per-split partial
+//              results (merge_chunk / merge_add of attention_merge.cuh, as its second stage
+//              computes it).
+// Either gives, bit for bit, the X the separate kernel writes.
+enum { PRO_TMA = 0, PRO_GATE = 1, PRO_MERGE = 2 };
+struct Operand {
+  // PRO_GATE: parts [S][M][2 * I] float32
+  const float* parts;
+  int S;
+  long long split_stride;
+  // PRO_MERGE: part_o [M][Hq][max_splits][D], part_lse [M][Hq][max_splits], seq_lens [M]
+  const float* part_o;
+  const float* part_lse;
+  const int* seq_lens;
+  int max_splits, D, window;
+};
+
+// byte offset of the 16-byte chunk c8 (8 elements) of row r in k-block kb of the operand
+// slab [k-blocks][BN rows][64 elements], 128-byte swizzle (the slab starts on 1,024 bytes)
+template <int BN> __device__ __forceinline__ int slab_off(int kb, int r, int c8) {
+  return kb * (BN * 128) + r * 128 + ((c8 ^ (r & 7)) << 4);
+}
+__device__ __forceinline__ unsigned pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+// Both forms first bring what they read into shared memory with bulk copies that are all in
+// flight together (one trip to memory, whatever the number of splits), then compute from
+// there.  `stage` is that buffer, `bar` the barrier its copies complete on.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes,
+                                         unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+// X[m][k0 .. k0 + nkb*64) for m < M of the gated feed-forward; K = I.
+// stage: [S][M][2 (gate, up)][len] float32, len = the CTA's columns.
+template <int BN>
+__device__ __forceinline__ bool operand_gate(unsigned char* slab, float* stage, unsigned long long* bar,
+                                             const Operand& op, int M, int K, int k0, int nkb) {
+  const int len = min(nkb * 64, K - k0);            // a multiple of 8
+  const int copies = op.S * M * 2;
+  if (threadIdx.x == 0) mbar_expect_tx(bar, (unsigned)copies * len * 4);
+  __syncthreads();
+  for (int c = threadIdx.x; c < copies; c += THREADS) {
+    const int gu = c & 1, m = (c >> 1) % M, sp = (c >> 1) / M;
+    bulk_g2s(stage + (size_t)c * len, op.parts + sp * op.split_stride + (size_t)m * 2 * K + gu * K + k0,
+             (unsigned)len * 4, bar);
+  }
+  const bool ok = mbar_wait(bar, 0);
+  // rows beyond M stay as they are: what the product makes of them is never stored
+  const int quads = len / 4;
+  for (int id = threadIdx.x; id < M * quads; id += THREADS) {     // a thread takes 4 columns of a row
+    const int r = id / quads, col = (id % quads) * 4;
+    float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+    for (int sp = 0; sp < op.S; ++sp) {              // the sums in split order
+      const float* p = stage + ((size_t)(sp * M + r) * 2) * len + col;
+      const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + len);
+      g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+      u.x += b.x; u.y += b.y; u.z += b.z; u.w += b.w;
+    }
+    const float y0 = silu_gate<__nv_bfloat16>(round_to<__nv_bfloat16>(g.x), round_to<__nv_bfloat16>(u.x));
+    const float y1 = silu_gate<__nv_bfloat16>(round_to<__nv_bfloat16>(g.y), round_to<__nv_bfloat16>(u.y));
+    const float y2 = silu_gate<__nv_bfloat16>(round_to<__nv_bfloat16>(g.z), round_to<__nv_bfloat16>(u.z));
+    const float y3 = silu_gate<__nv_bfloat16>(round_to<__nv_bfloat16>(g.w), round_to<__nv_bfloat16>(u.w));
+    *reinterpret_cast<uint2*>(slab + slab_off<BN>(col >> 6, r, (col & 63) >> 3) + ((col >> 2) & 1) * 8) =
+        ok ? make_uint2(pack2_bf16(y0, y1), pack2_bf16(y2, y3)) : make_uint2(0, 0);
+  }
+  return ok;
+}
+
+// X[m][k0 .. ) = merged attention output of sequence m, column k = head * D + dim; K = Hq * D.
+// The CTA's columns are `seg` consecutive dimensions of each of `nh` heads (seg = D when the
+// range covers whole heads, else the range lies inside one head).
+// stage: [M][nh][max_splits][seg] float32, then the log-sum-exps and the weights
+// [M][nh][max_splits] each, and the sequences' lengths [M].
+template <int BN>
+__device__ __forceinline__ bool operand_merge(unsigned char* slab, float* stage, unsigned long long* bar,
+                                              const Operand& op, int M, int K, int k0, int nkb) {
+  constexpr int CH = MERGE_CH;
+  const int D = op.D, Hq = K / D, S = op.max_splits;
+  const int len = min(nkb * 64, K - k0);
+  const int h0 = k0 / D, d0 = k0 % D;
+  const int seg = min(D - d0, len), nh = (len + seg - 1) / seg;     // (the launcher checks the fit)
+  float* s_lse = stage + (size_t)M * nh * S * seg;
+  float* s_w = s_lse + (size_t)M * nh * S;                             // the splits' weights
+  int* s_len = reinterpret_cast<int*>(s_w + (size_t)M * nh * S);       // the sequences' lengths
+  // whole heads: one copy per (sequence, head) of all its splits; part of a head: one per split
+  const int per_copy = seg == D ? S : 1;
+  const int copies = M * nh * (S / per_copy);
+  if (threadIdx.x == 0) mbar_expect_tx(bar, (unsigned)(M * nh * S) * seg * 4);
+  __syncthreads();
+  for (int c = threadIdx.x; c < copies; c += THREADS) {
+    const int unit = c * per_copy;                  // index of (m, head, split) in stage order
+    const int sp = unit % S, hh = (unit / S) % nh, m = unit / (S * nh);
+    bulk_g2s(stage + (size_t)unit * seg,
+             op.part_o + ((((size_t)m * Hq + h0 + hh) * S + sp) * D + d0), (unsigned)(per_copy * seg) * 4, bar);
+  }
+  for (int e = threadIdx.x; e < M * nh * S; e += THREADS) {
+    const int sp = e % S, hh = (e / S) % nh, m = e / (S * nh);
+    s_lse[e] = op.part_lse[((size_t)m * Hq + h0 + hh) * S + sp];
+  }
+  for (int e = threadIdx.x; e < M; e += THREADS) s_len[e] = op.seq_lens[e];
+  const bool ok = mbar_wait(bar, 0);
+  __syncthreads();                                   // the log-sum-exps and lengths are in place
+  // every split's weight once
+  for (int e = threadIdx.x; e < M * nh * S; e += THREADS) {
+    const int sp = e % S, m = e / (S * nh);
+    int s0, s1;
+    merge_range(s_len[m], op.window, S, s0, s1);
+    float w = 0.f;
+    if (sp >= s0 && sp <= s1) {
+      const float* pl = s_lse + (e - sp);
+      float M_lse = MERGE_NEG_BIG;
+      for (int t = s0; t <= s1; ++t) M_lse = fmaxf(M_lse, pl[t]);
+      w = merge_weight(pl[sp], M_lse);
+    }
+    s_w[e] = w;
+  }
+  __syncthreads();
+  // a thread takes V dimensions of a row: 4 when that keeps every thread busy, else 1
+  const bool four = M * len >= 4 * THREADS;
+  const int per_row = four ? len / 4 : len;
+  for (int id = threadIdx.x; id < M * per_row; id += THREADS) {
+    const int r = id / per_row, col = (id % per_row) * (four ? 4 : 1);
+    const int hh = col / seg, d = col % seg;       // seg is a multiple of 4: the 4 dimensions share a head
+    const float* po = stage + ((size_t)(r * nh + hh) * S) * seg + d;
+    const float* pw = s_w + (size_t)(r * nh + hh) * S;
+    int s0, s1;
+    merge_range(s_len[r], op.window, S, s0, s1);
+    const int c0 = s0 / CH, c1 = s1 / CH;
+    float total[4] = {0.f, 0.f, 0.f, 0.f}, total_den = 0.f;
+    for (int c = c0; c <= c1; ++c) {
+      float w[CH], o[CH][4];
+#pragma unroll
+      for (int j = 0; j < CH; ++j) {
+        const int sp = c * CH + j;
+        const bool in = sp >= s0 && sp <= s1;
+        w[j] = in ? pw[sp] : 0.f;
+        if (four) {
+          const float4 v = in ? *reinterpret_cast<const float4*>(po + (size_t)sp * seg)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);
+          o[j][0] = v.x; o[j][1] = v.y; o[j][2] = v.z; o[j][3] = v.w;
+        } else {
+          o[j][0] = in ? po[(size_t)sp * seg] : 0.f;
+          o[j][1] = o[j][2] = o[j][3] = 0.f;
+        }
+      }
+      float acc[4], den;
+      merge_chunk_weighted<4>(w, o, c, s0, s1, acc, den);
+      merge_add<4>(c == c0, acc, den, total, total_den);
+    }
+    unsigned char* dst = slab + slab_off<BN>(col >> 6, r, (col & 63) >> 3) + (col & 7) * 2;
+    if (four) {
+      *reinterpret_cast<uint2*>(dst) =
+          ok ? make_uint2(pack2_bf16(merge_finish(total[0], total_den), merge_finish(total[1], total_den)),
+                          pack2_bf16(merge_finish(total[2], total_den), merge_finish(total[3], total_den)))
+             : make_uint2(0, 0);
+    } else {
+      *reinterpret_cast<__nv_bfloat16*>(dst) = __float2bfloat16_rn(ok ? merge_finish(total[0], total_den) : 0.f);
+    }
+  }
+  return ok;
+}
+
 // GATED: w is [gate rows ; up rows] of a gated feed-forward ([2N, K]); a tile holds 64
 // gate rows and the 64 up rows of the same features, and the epilogue writes
 // silu(gate) * up, [M, N], so the gate/up product never goes to memory.
@@ -128,25 +306,33 @@ __device__ __forceinline__ float ld_peer_smem(const float* local, unsigned rank)
 // its partial tile in its shared memory, and each then adds up, over all of them in split
 // order, its share of the tile's rows through distributed shared memory and writes the
 // finished values: no partial products in global memory, and a gate can follow a split k.
-template <int BN, typename OutT, bool GATED, int STAGES, bool CLUSTER>
+template <int BN, typename OutT, bool GATED, int STAGES, bool CLUSTER, int PRO = PRO_TMA>
 __global__ void __launch_bounds__(THREADS)
 gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  OutT* __restrict__ out, float* __restrict__ partial, int M, int N, int num_kb,
-                 int kb_per_split, int splits) {
-  constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+                 int kb_per_split, int splits, int K, const Operand op) {
+  static_assert(PRO == PRO_TMA || (!GATED && !CLUSTER), "an operand made in the kernel: plain product only");
+  constexpr int A_BYTES = BM * BK * 2, B_BYTES = PRO == PRO_TMA ? BN * BK * 2 : 0;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  // with an operand made in the kernel: its slab first (kb_per_split k-blocks of BN rows of
+  // 128 bytes, rounded up to 1,024 bytes), then the ring of weight stages
+  unsigned char* slab = smem;
+  if (PRO != PRO_TMA) smem += ((size_t)kb_per_split * BN * 128 + 1023) & ~(size_t)1023;
   unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
   unsigned long long* empty = full + STAGES;
   unsigned long long* accum = empty + STAGES;
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(accum + 1);
+  unsigned long long* stage_bar = accum + 1;
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(stage_bar + 1);
+  float* stage = reinterpret_cast<float*>(tmem_slot + 4);     // 16-byte aligned; only with PRO
 
   pdl_trigger();   // the kernel after this one may set itself up (and fetch its weights) beside this one
   if (threadIdx.x == 0) {
     prefetch_tensormap(&map_w);
-    prefetch_tensormap(&map_x);
+    if (PRO == PRO_TMA) prefetch_tensormap(&map_x);
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * (GATED ? BM / 2 : BM), m0 = blockIdx.y * BN, split = blockIdx.z;
@@ -159,6 +345,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       mbar_init(&empty[s], 1);
     }
     mbar_init(accum, 1);
+    mbar_init(stage_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 0) {
@@ -172,25 +359,45 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   tc_fence_after();
   const unsigned tmem = *tmem_slot;
   bool ok = true;
+  const int pre = nkb < STAGES ? nkb : STAGES;
+
+  if (PRO != PRO_TMA) {
+    // The weights of the first stages are sent for, then every thread waits for the kernel
+    // before this one and the CTA builds its slab of the token operand; the roles follow.
+    if (warp == 0 && lane == 0) {
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full[i], STAGE_BYTES);
+        tma_load_2d(smem + i * STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full[i]);
+      }
+    }
+    pdl_wait();
+    bool made;
+    if (PRO == PRO_GATE) made = operand_gate<BN>(slab, stage, stage_bar, op, M, K, kb_begin * BK, nkb);
+    else made = operand_merge<BN>(slab, stage, stage_bar, op, M, K, kb_begin * BK, nkb);
+    if (!made) atomicExch(&dib_gemm_error_word, 1);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the slab is read by the MMA unit
+    __syncthreads();
+  }
 
   if (warp == 0 && lane == 0) {
     // ---- TMA producer.  The weights do not depend on the kernel before this one, so
     // their loads for the first stages start before the wait for that kernel; the
     // activations follow after it.
-    const int pre = nkb < STAGES ? nkb : STAGES;
-    for (int i = 0; i < pre; ++i) {
-      mbar_expect_tx(&full[i], STAGE_BYTES);
-      if (GATED) {
-        tma_load_2d(smem + i * STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full[i]);
-        tma_load_2d(smem + i * STAGE_BYTES + A_BYTES / 2, &map_w, (kb_begin + i) * BK, N + n0,
-                    &full[i]);
-      } else {
-        tma_load_2d(smem + i * STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full[i]);
+    if (PRO == PRO_TMA) {
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full[i], STAGE_BYTES);
+        if (GATED) {
+          tma_load_2d(smem + i * STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full[i]);
+          tma_load_2d(smem + i * STAGE_BYTES + A_BYTES / 2, &map_w, (kb_begin + i) * BK, N + n0,
+                      &full[i]);
+        } else {
+          tma_load_2d(smem + i * STAGE_BYTES, &map_w, (kb_begin + i) * BK, n0, &full[i]);
+        }
       }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem + i * STAGE_BYTES + A_BYTES, &map_x, (kb_begin + i) * BK, m0, &full[i]);
     }
-    pdl_wait();
-    for (int i = 0; i < pre; ++i)
-      tma_load_2d(smem + i * STAGE_BYTES + A_BYTES, &map_x, (kb_begin + i) * BK, m0, &full[i]);
     for (int i = pre; i < nkb && ok; ++i) {
       const int s = i % STAGES;
       ok = mbar_wait(&empty[s], ((i / STAGES) - 1) & 1);
@@ -200,7 +407,7 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       const int k = (kb_begin + i) * BK;
       tma_load_2d(a, &map_w, k, n0, &full[s]);
       if (GATED) tma_load_2d(a + A_BYTES / 2, &map_w, k, N + n0, &full[s]);
-      tma_load_2d(a + A_BYTES, &map_x, k, m0, &full[s]);
+      if (PRO == PRO_TMA) tma_load_2d(a + A_BYTES, &map_x, k, m0, &full[s]);
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer
@@ -210,7 +417,8 @@ gemm_swap_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       ok = mbar_wait(&full[s], (i / STAGES) & 1);
       if (!ok) break;
       tc_fence_after();
-      const unsigned a = smem_u32(smem + s * STAGE_BYTES), b = a + A_BYTES;
+      const unsigned a = smem_u32(smem + s * STAGE_BYTES);
+      const unsigned b = PRO == PRO_TMA ? a + A_BYTES : smem_u32(slab) + i * (BN * 128);
 #pragma unroll
       for (int k = 0; k < BK / UMMA_K; ++k)
         tc_mma(tmem, smem_desc_sw128(a + k * UMMA_K * 2), smem_desc_sw128(b + k * UMMA_K * 2), idesc,
@@ -373,7 +581,7 @@ int launch_swap_stages(const CUtensorMap& mw, const CUtensorMap& mx, void* out, 
                        cudaStream_t st) {
   constexpr size_t ring = (size_t)STAGES * (BM * BK * 2 + BN * BK * 2);
   static_assert(!CLUSTER || ring >= (size_t)BM * (BN + 1) * 4, "the partial tile must fit in the ring");
-  constexpr size_t smem = ring + (2 * STAGES + 1) * 8 + 16 + 1024;
+  constexpr size_t smem = ring + (2 * STAGES + 2) * 8 + 16 + 1024;
   auto kern = gemm_swap_kernel<BN, OutT, GATED, STAGES, CLUSTER>;
   static DeviceOnce attr_set;
   if (!attr_set.done()) {
@@ -397,11 +605,38 @@ int launch_swap_stages(const CUtensorMap& mw, const CUtensorMap& mx, void* out, 
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = dib_pdl_enabled() ? 2 : 1;
-    cudaLaunchKernelEx(&cfg, kern, mw, mx, (OutT*)out, partial, M, N, num_kb, kb_per_split, splits);
+    cudaLaunchKernelEx(&cfg, kern, mw, mx, (OutT*)out, partial, M, N, num_kb, kb_per_split, splits, 0,
+                       Operand{});
   } else {
     dib_launch(kern, dim3(grid), dim3(THREADS), smem, st, mw, mx, (OutT*)out, partial, M, N, num_kb,
-               kb_per_split, splits);
+               kb_per_split, splits, 0, Operand{});
   }
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+// The product with its token operand made in the kernel (PRO_GATE / PRO_MERGE): one tile of
+// tokens, a slab of at most MAX_SLAB bytes, four weight stages.
+constexpr size_t MAX_OPERAND_SMEM = 220 * 1024;     // slab + staged inputs + ring + barriers
+template <int BN, typename OutT, int PRO>
+int launch_operand(const CUtensorMap& mw, void* out, float* partial, int M, int N, int K, int num_kb,
+                   int kb_per_split, int splits, const Operand& op, size_t stage_bytes,
+                   cudaStream_t st) {
+  constexpr int STAGES = 4;
+  constexpr size_t ring = (size_t)STAGES * (BM * BK * 2);
+  const size_t slab = ((size_t)kb_per_split * BN * 128 + 1023) & ~(size_t)1023;
+  const size_t smem = slab + ring + (2 * STAGES + 2) * 8 + 32 + stage_bytes + 1024;
+  if (smem > MAX_OPERAND_SMEM) return DIB_BAD_SIZE;
+  auto kern = gemm_swap_kernel<BN, OutT, false, STAGES, false, PRO>;
+  static DeviceOnce attr_set;
+  if (!attr_set.done()) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)MAX_OPERAND_SMEM) != cudaSuccess)
+      return DIB_LAUNCH_FAILED;
+    attr_set.mark();
+  }
+  dib_launch(kern, dim3((N + BM - 1) / BM, 1, splits), dim3(THREADS), smem, st, mw, mw, (OutT*)out, partial,
+             M, N, num_kb, kb_per_split, splits, K, op);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -614,6 +849,78 @@ int dib_gemm_bf16(const void* x, const void* w, void* out, int M, int N, int K, 
     case 64: return CALL(64);
     default: return CALL(128);
   }
+#undef CALL
+}
+
+// The product out[M, N] = X[M, K] * w[N, K]^T whose X is not in memory yet: the kernel makes
+// the columns of X it needs while it waits for its weights.
+//   pro 1: X = silu(gate) * up, [gate | up] given as float32 partial products of a split k,
+//          parts [S][M][2K] (split_stride elements apart);
+//   pro 2: X = the split-KV decode attention's output [M][Hq * D], given as its per-split
+//          partial results part_o [M][Hq][max_splits][D], part_lse [M][Hq][max_splits] and
+//          the sequences' lengths (seq_lens [M], window).
+// The split of k is the one dib_gemm_bf16_plan gives for (N, K); out / partial as in
+// dib_gemm_bf16.  Returns -2 for shapes it does not take (more than 128 rows, inputs of X
+// that do not fit a CTA's shared memory, widths that are no multiples of 8): the caller then makes X with the
+// kernel of its own and calls dib_gemm_bf16.
+int dib_gemm_bf16_operand(int pro, const void* w, void* out, int M, int N, int K, int out_fp32,
+                          float* partial, int sm_count, const float* parts, int S,
+                          long long split_stride, const float* part_o, const float* part_lse,
+                          const int* seq_lens, int max_splits, int D, int window, cudaStream_t st) {
+  if (M == 0 || N == 0) return DIB_OK;
+  if (K < 8 || K % 8 != 0 || M > 128) return DIB_BAD_SIZE;
+  if (reinterpret_cast<uintptr_t>(w) % 16 != 0) return DIB_BAD_ALIGN;
+  Operand op = {};
+  if (pro == PRO_GATE) {
+    if (parts == nullptr || S < 1 || split_stride % 4 != 0 || reinterpret_cast<uintptr_t>(parts) % 16 != 0)
+      return DIB_BAD_SIZE;
+    op.parts = parts; op.S = S; op.split_stride = split_stride;
+  } else if (pro == PRO_MERGE) {
+    if (part_o == nullptr || part_lse == nullptr || seq_lens == nullptr || max_splits < 1 || D < 4 ||
+        D % 4 != 0 || K % D != 0 || reinterpret_cast<uintptr_t>(part_o) % 16 != 0)
+      return DIB_BAD_SIZE;
+    op.part_o = part_o; op.part_lse = part_lse; op.seq_lens = seq_lens;
+    op.max_splits = max_splits; op.D = D; op.window = window;
+  } else {
+    return DIB_BAD_SIZE;
+  }
+  int bn, per, splits;
+  dib_gemm_bf16_plan(M, N, K, sm_count, &bn, &per, &splits);
+  const int num_kb = (K + BK - 1) / BK;
+  if (partial == nullptr) {
+    splits = 1;
+    per = num_kb;
+  }
+  if (splits > 65535) return DIB_BAD_SIZE;
+  // what a CTA stages of the inputs of X: its columns (at most per * 64) of every row
+  const long long len = per * BK < K ? per * BK : K;
+  size_t stage_bytes;
+  if (pro == PRO_GATE) {
+    stage_bytes = (size_t)S * M * 2 * len * 4;
+  } else {
+    // the range of a CTA is whole heads, or lies inside one head
+    if (!((per * BK) % D == 0 || D % (per * BK) == 0)) return DIB_BAD_SIZE;
+    const long long seg = len < D ? len : D, nh = (len + seg - 1) / seg;
+    stage_bytes = (size_t)M * nh * max_splits * (seg + 2) * 4 + (size_t)M * 4;
+    if ((seg * 4) % 16 != 0) return DIB_BAD_SIZE;
+  }
+  CUtensorMap mw;
+  if (!make_map(&mw, w, N, K, BM)) return DIB_LAUNCH_FAILED;
+#define CALL(BNV, PROV)                                                                                \
+  (out_fp32 ? launch_operand<BNV, float, PROV>(mw, out, partial, M, N, K, num_kb, per, splits, op,    \
+                                               stage_bytes, st)                                       \
+            : launch_operand<BNV, __nv_bfloat16, PROV>(mw, out, partial, M, N, K, num_kb, per, splits, \
+                                                       op, stage_bytes, st))
+#define CALL_BN(PROV)                  \
+  switch (bn) {                        \
+    case 16: return CALL(16, PROV);    \
+    case 32: return CALL(32, PROV);    \
+    case 64: return CALL(64, PROV);    \
+    default: return CALL(128, PROV);   \
+  }
+  if (pro == PRO_GATE) { CALL_BN(PRO_GATE) }
+  CALL_BN(PRO_MERGE)
+#undef CALL_BN
 #undef CALL
 }
 

@@ -40,11 +40,16 @@ MAX_CHUNKS = 16     # chunks the merge kernel adds for one row: 65,536 keys
 #                2: the latter when the step has more splits than CTAs that run at once
 #   prefill_tc   0: mma.sync kernel; 1: one query tile per CTA; 2: two
 #   prefill_pair auto | 0: every tile alone | 1: pairs from both ends | 2: neighbours
+#   defer_merge  True: decode-only steps leave the merge of the splits to the output projection
 SWITCHES = {
     "decode_tma": os.environ.get("DIB200_DECODE_TMA", "1") != "0",
     "decode_pipe": int(os.environ.get("DIB200_DECODE_PIPE", "2")),
     "prefill_tc": os.environ.get("DIB200_PREFILL_TC", "2"),
     "prefill_pair": os.environ.get("DIB200_PREFILL_PAIR", "auto"),
+    # 1: a decode-only step's attention leaves its splits unmerged and the output projection
+    # merges them while it loads its operand (the same bits; measured slower than the merge
+    # kernel on B200, so off)
+    "defer_merge": os.environ.get("DIB200_DEFER_MERGE", "0") == "1",
 }
 
 _sms: dict = {}
@@ -150,8 +155,11 @@ def _pair_lists(meta, nd: int, tpt: int, window: int, hkv: int, max_chunks: int,
     return (both[0], both[1], len(seqs), both[2]), None, (None, None)
 
 
-def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
-    from .ops import _check, _lib, _ptr, _stream
+def run(q, out, kv_cache, meta, scale: float, window: int, defer: bool = False):
+    """Fills ``out``; or, with ``defer`` and a step of one-token sequences only, returns an
+    ``ops.SplitAttention`` (the decode kernel's partial results, not merged) and leaves
+    ``out`` alone."""
+    from .ops import SplitAttention, _check, _lib, _ptr, _stream
 
     lib = _lib("attention_bf16")
     t, hq, d = q.shape
@@ -166,12 +174,16 @@ def run(q, out, kv_cache, meta, scale: float, window: int) -> None:
                   torch.empty(nd, hq, max_splits, dtype=torch.float32, device=q.device))
             meta.scratch[("decode_ws", hq, d, max_splits)] = ws
         use_tma, pipelined = SWITCHES["decode_tma"], SWITCHES["decode_pipe"]
+        deferred = defer and nd == b and SWITCHES["defer_merge"]
         st = lib.dib_decode_attention_bf16(
-            _ptr(q), _ptr(out), _ptr(kv_cache), c_longlong(kv_cache.shape[0] if use_tma else 0),
+            _ptr(q), c_void_p(0) if deferred else _ptr(out), _ptr(kv_cache),
+            c_longlong(kv_cache.shape[0] if use_tma else 0),
             _ptr(bt), c_int(bt.shape[1]), _ptr(meta.seq_lens),
             _ptr(ws[0]), _ptr(ws[1]), c_int(nd), c_int(max_splits), c_int(hq), c_int(hkv), c_int(d),
             c_int(page_size), c_float(scale), c_int(window), c_int(pipelined), _stream())
-        _check(st, "decode_attention_bf16", f"heads {hq}/{hkv}, head_dim {d}", kernels=2)
+        _check(st, "decode_attention_bf16", f"heads {hq}/{hkv}, head_dim {d}", kernels=1 if deferred else 2)
+        if deferred:
+            return SplitAttention(ws[0], ws[1], meta.seq_lens, nd, window, q.dtype)
     group = hq // hkv
     tc_mode = SWITCHES["prefill_tc"]
     if b > nd and d == 128 and TC_TILE_ROWS % group == 0 and page_size in (8, 16, 32, 64, 128) \

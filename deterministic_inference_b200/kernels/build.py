@@ -39,7 +39,7 @@ SOURCES = {
     "decode_attention_noalloc": "decode_attention_noalloc.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",
 }
-HEADERS = ("common.cuh",)
+HEADERS = ("common.cuh", "attention_merge.cuh")
 # further headers a library includes
 EXTRA_HEADERS = {
     "attention_bf16": ("attention_bf16_kernels.cuh",),

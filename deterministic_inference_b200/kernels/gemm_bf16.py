@@ -11,7 +11,7 @@ sid/model/qwen3.py:38).
 from __future__ import annotations
 
 import os
-from ctypes import byref, c_int, c_void_p
+from ctypes import byref, c_int, c_longlong, c_void_p
 
 import torch
 
@@ -93,6 +93,41 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, allow_
     if out_dtype == torch.bfloat16:
         return torch.mm(x, weight.t())
     return torch.mm(x, weight.t(), out_dtype=out_dtype)
+
+
+def linear_of_deferred(x, weight: torch.Tensor, out_dtype: torch.dtype):
+    """x @ weight^T for an ``ops.GatedSplit`` or ``ops.SplitAttention`` x: the kernel makes
+    its token operand from the partial results while its weights arrive.  None if the shape
+    is not one the kernel takes (the caller then materialises x)."""
+    from . import ops
+    m, k = x.shape
+    n = weight.shape[0]
+    if not (m <= min(MAX_ROWS, 128) and k % 8 == 0 and out_dtype in (torch.bfloat16, torch.float32)
+            and weight.data_ptr() % 16 == 0 and weight.is_contiguous()):
+        return None
+    lib = ops._lib("gemm_bf16")
+    splits = plan(m, n, k, weight.device)[2]
+    fp32 = c_int(1 if out_dtype == torch.float32 else 0)
+    if isinstance(x, ops.GatedSplit):
+        g = x.gate_up.parts
+        pro, args = 1, (ops._ptr(g), c_int(g.shape[0]), c_longlong(g.shape[1] * g.shape[2]),
+                        c_void_p(0), c_void_p(0), c_void_p(0), c_int(0), c_int(0), c_int(0))
+    else:
+        if x.head_dim % 4:
+            return None
+        pro, args = 2, (c_void_p(0), c_int(0), c_longlong(0), ops._ptr(x.part_o), ops._ptr(x.part_lse),
+                        ops._ptr(x.seq_lens), c_int(x.max_splits), c_int(x.head_dim), c_int(x.window))
+    parts = out = None
+    if splits > 1:
+        parts = torch.empty(splits, m, n, dtype=torch.float32, device=weight.device)
+    else:
+        out = torch.empty(m, n, dtype=out_dtype, device=weight.device)
+    st = lib.dib_gemm_bf16_operand(c_int(pro), ops._ptr(weight), ops._ptr(out), c_int(m), c_int(n), c_int(k),
+                                   fp32, ops._ptr(parts), c_int(_sms(weight.device)), *args, ops._stream())
+    if st == -2:
+        return None
+    ops._check(st, "linear(bfloat16, operand made in the kernel)", f"M={m} N={n} K={k}")
+    return ops.SplitSum(parts, out_dtype) if parts is not None else out
 
 
 def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor):

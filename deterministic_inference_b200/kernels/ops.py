@@ -193,9 +193,81 @@ class SplitSum:
         return acc.to(self.dtype)
 
 
+# Rows up to which the gate of a gated feed-forward is left to the product that follows
+# (``GatedSplit``).  The product then stages the partial products of its columns in shared
+# memory; with more than a few rows that costs more than the separate gate kernel (B200,
+# width 1,024 / 3,072: 6.2 against 7.2 us for both products at 1 row, 8.2 against 7.5 us at 8).
+GATE_IN_PRODUCT_ROWS = 2
+
+
+class GatedSplit:
+    """silu(gate) * up that is not computed yet: the [gate | up] product exists as the
+    split-k partial products ``gate_up`` (a ``SplitSum``, [rows, 2I]).  The matrix product
+    that follows makes its operand from them while it loads (``linear``); anything else gets
+    the tensor [rows, I] from ``tensor()`` (the gate kernel that reads partials)."""
+
+    def __init__(self, gate_up: SplitSum):
+        self.gate_up = gate_up
+        self.dtype = gate_up.dtype
+
+    @property
+    def shape(self):
+        rows, two_i = self.gate_up.shape
+        return torch.Size((rows, two_i // 2))
+
+    @property
+    def device(self):
+        return self.gate_up.device
+
+    def tensor(self) -> torch.Tensor:
+        return silu_mul(self.gate_up)
+
+
+class SplitAttention:
+    """The output of the split-KV decode attention before its splits are merged:
+    ``part_o`` float32 [sequences, heads, splits, head_dim], ``part_lse`` [sequences, heads,
+    splits], the sequences' lengths on the device and the window.  Its logical shape is
+    [sequences, heads * head_dim].  The output projection merges while it loads its
+    operand (``linear``); ``tensor()`` runs the merge kernel."""
+
+    def __init__(self, part_o, part_lse, seq_lens, num_seqs: int, window: int, dtype):
+        self.part_o, self.part_lse, self.seq_lens = part_o, part_lse, seq_lens
+        self.num_seqs, self.window, self.dtype = num_seqs, window, dtype
+        _, self.num_heads, self.max_splits, self.head_dim = part_o.shape
+
+    @property
+    def shape(self):
+        return torch.Size((self.num_seqs, self.num_heads * self.head_dim))
+
+    @property
+    def device(self):
+        return self.part_o.device
+
+    def tensor(self) -> torch.Tensor:
+        out = torch.empty(self.num_seqs, self.num_heads, self.head_dim, dtype=self.dtype,
+                          device=self.part_o.device)
+        st = _lib("attention_bf16").dib_decode_attention_merge(
+            _ptr(self.part_o), _ptr(self.part_lse), _ptr(self.seq_lens), _ptr(out), c_int(self.num_seqs),
+            c_int(self.max_splits), c_int(self.num_heads), c_int(self.head_dim), c_int(self.window),
+            _stream())
+        _check(st, "decode_attention_merge")
+        return out.view(self.num_seqs, self.num_heads * self.head_dim)
+
+
+_DEFERRED = (SplitSum, GatedSplit, SplitAttention)
+
+
 def as_tensor(x):
     """A plain tensor, whatever ``x`` is."""
-    return x.tensor() if isinstance(x, SplitSum) else x
+    return x.tensor() if isinstance(x, _DEFERRED) else x
+
+
+def merge_heads(o):
+    """Attention output [T, heads, head_dim] as the output projection's operand
+    [T, heads * head_dim] (a ``SplitAttention`` has that shape already)."""
+    if isinstance(o, SplitAttention):
+        return o
+    return o.view(o.shape[0], o.shape[1] * o.shape[2])
 
 
 # ---------------------------------------------------------------- embedding
@@ -359,13 +431,15 @@ def reshape_and_cache(k: torch.Tensor, v: torch.Tensor, kv_cache: torch.Tensor,
 # ---------------------------------------------------------------- attention
 
 def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float,
-                    window=None) -> torch.Tensor:
+                    window=None, defer: bool = False):
     """Causal attention of every token of the step over its sequence's keys in the
     paged cache.  q [T, Hq, D]; kv_cache [pages, 2, Hkv, page_size, D]; ``meta``
     is the step's attention metadata for this cache's group (``AttentionMeta``:
     block_table [B, max_blocks], token_seq [T], positions [T], cu_q_lens [B+1],
     seq_lens [B], host copies of the lengths, number of leading decode
-    sequences).  A query at position p sees keys max(0, p-window+1) .. p."""
+    sequences).  A query at position p sees keys max(0, p-window+1) .. p.
+    ``defer``: a step of one-token sequences only may come back as a ``SplitAttention``
+    (its splits not yet merged) for the matrix product that follows to merge."""
     _need(q, "q", None, 3)
     _need(kv_cache, "kv_cache", q.dtype, 5)
     t, hq, d = q.shape
@@ -380,8 +454,8 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, meta, scale: float,
     if q.dtype == torch.bfloat16:
         from . import attention_bf16
         if attention_bf16.supports(hq, hkv, d, page_size):
-            attention_bf16.run(q, out, kv_cache, meta, scale, win)
-            return out
+            deferred = attention_bf16.run(q, out, kv_cache, meta, scale, win, defer)
+            return deferred if deferred is not None else out
     st = _lib("attention_generic").dib_paged_attention_generic(
         _ptr(q), _ptr(out), _ptr(kv_cache), _ptr(meta.block_table), c_int(meta.block_table.shape[1]),
         _ptr(meta.token_seq), _ptr(meta.positions), c_int(t), c_int(hq), c_int(hkv), c_int(d),
@@ -438,6 +512,12 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tenso
     accumulation on the tensor cores; ``out_dtype=torch.float32`` returns the
     accumulator unrounded (used for the logits).  With few rows and a split of k the
     bfloat16 product comes back as a ``SplitSum`` (see there)."""
+    if isinstance(x, (GatedSplit, SplitAttention)) and weight.dtype == torch.bfloat16 \
+            and tuple(x.shape)[1] == weight.shape[1]:
+        from . import gemm_bf16
+        y = gemm_bf16.linear_of_deferred(x, weight, out_dtype or torch.bfloat16)
+        if y is not None:
+            return y
     x = as_tensor(x)
     _need(x, "x", None, 2)
     _need(weight, "weight", x.dtype, 2)
@@ -457,10 +537,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype=None) -> torch.Tenso
     return gemm_bf16.linear(x, weight, out_dtype or torch.bfloat16)
 
 
-def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor):
     """silu(x w_gate^T) * (x w_up^T), [M, I], for the concatenated weight
     [w_gate ; w_up] ([2I, K]).  With few bfloat16 rows the gate is applied in the matrix
-    product's epilogue; otherwise this is ``silu_mul(linear(x, w_gate_up))``."""
+    product's epilogue, or, when the product comes back as split-k partials, left to the
+    reader (a ``GatedSplit``); otherwise this is ``silu_mul(linear(x, w_gate_up))``."""
     x = as_tensor(x)
     if x.dtype == torch.bfloat16 and x.is_cuda:
         _need(x, "x", None, 2)
@@ -471,7 +552,11 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
         out = gemm_bf16.gated_linear(x, w_gate_up)
         if out is not None:
             return out
-    return silu_mul(linear(x, w_gate_up))
+    y = linear(x, w_gate_up)
+    if isinstance(y, SplitSum) and y.dtype == torch.bfloat16 and y.shape[1] % 16 == 0 \
+            and y.shape[0] <= GATE_IN_PRODUCT_ROWS:
+        return GatedSplit(y)          # the gate is applied by the product that reads it
+    return silu_mul(y)
 
 
 # ---------------------------------------------------------------- sampling

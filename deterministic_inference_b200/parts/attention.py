@@ -72,5 +72,7 @@ class GQAAttention(Mixer):
             self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
             self.position_encoding.rotary_table(), step.positions,
             cache.kv if cache.writes else None, cache.slot_mapping, cache.page_size)
-        o = ops.paged_attention(q, cache.kv, cache.attention_meta, self.scale, self.window)
-        return ops.linear(o.view(o.shape[0], self.num_heads * self.head_dim), self.w_o)
+        # (a decode-only step's attention may come back with its splits not yet merged; the
+        # output projection then merges them while it loads its operand)
+        o = ops.paged_attention(q, cache.kv, cache.attention_meta, self.scale, self.window, defer=True)
+        return ops.linear(ops.merge_heads(o), self.w_o)

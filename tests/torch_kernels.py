@@ -89,7 +89,7 @@ def reshape_and_cache(k, v, kv_cache, slot_mapping):
     kv_cache[page, 1, :, off, :] = v[ok]
 
 
-def paged_attention(q, kv_cache, meta, scale, window=None):
+def paged_attention(q, kv_cache, meta, scale, window=None, defer=False):
     """Every token against the cached keys of its sequence, causal by absolute
     position, float32 softmax (sid/kernels/extend_attention.py:80-109,
     tests/conftest.py:11-32)."""
