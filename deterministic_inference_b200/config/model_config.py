@@ -211,8 +211,11 @@ class Qwen3Config:
         return ModelPlan(
             hidden_size=self.hidden_size,
             vocab_size=self.vocab_size,
-            embedding_name="model.embed_tokens.weight",
-            head_name=None if self.tie_word_embeddings else "lm_head.weight",
+            embedding=PartSpec("token_embedding", dict(
+                name="model.embed_tokens.weight", vocab_size=self.vocab_size, hidden_size=self.hidden_size)),
+            head=PartSpec("linear_head", dict(
+                name=None if self.tie_word_embeddings else "lm_head.weight",
+                vocab_size=self.vocab_size, hidden_size=self.hidden_size)),
             ignored_names=("lm_head.weight",) if self.tie_word_embeddings else (),
             ignored_substrings=("rotary",),
             final_norm=PartSpec("rms_norm", dict(

@@ -153,6 +153,13 @@ struct Operand {
 template <int BN> __device__ __forceinline__ int slab_off(int kb, int r, int c8) {
   return kb * (BN * 128) + r * 128 + ((c8 ^ (r & 7)) << 4);
 }
+// The whole slab to zero: columns beyond K (the last k-block of a width that is no multiple
+// of 64) and rows beyond M must not hold what shared memory happened to hold (the weights'
+// columns beyond K are zero, and 0 times a NaN is a NaN).
+template <int BN> __device__ __forceinline__ void slab_clear(unsigned char* slab, int nkb) {
+  for (int i = threadIdx.x; i < nkb * BN * 8; i += THREADS)
+    *reinterpret_cast<uint4*>(slab + (size_t)i * 16) = make_uint4(0, 0, 0, 0);
+}
 __device__ __forceinline__ unsigned pack2_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<unsigned*>(&v);
@@ -177,6 +184,7 @@ __device__ __forceinline__ bool operand_gate(unsigned char* slab, float* stage, 
   const int len = min(nkb * 64, K - k0);            // a multiple of 8
   const int copies = op.S * M * 2;
   if (threadIdx.x == 0) mbar_expect_tx(bar, (unsigned)copies * len * 4);
+  slab_clear<BN>(slab, nkb);
   __syncthreads();
   for (int c = threadIdx.x; c < copies; c += THREADS) {
     const int gu = c & 1, m = (c >> 1) % M, sp = (c >> 1) / M;
@@ -184,7 +192,6 @@ __device__ __forceinline__ bool operand_gate(unsigned char* slab, float* stage, 
              (unsigned)len * 4, bar);
   }
   const bool ok = mbar_wait(bar, 0);
-  // rows beyond M stay as they are: what the product makes of them is never stored
   const int quads = len / 4;
   for (int id = threadIdx.x; id < M * quads; id += THREADS) {     // a thread takes 4 columns of a row
     const int r = id / quads, col = (id % quads) * 4;
@@ -225,6 +232,7 @@ __device__ __forceinline__ bool operand_merge(unsigned char* slab, float* stage,
   const int per_copy = seg == D ? S : 1;
   const int copies = M * nh * (S / per_copy);
   if (threadIdx.x == 0) mbar_expect_tx(bar, (unsigned)(M * nh * S) * seg * 4);
+  slab_clear<BN>(slab, nkb);
   __syncthreads();
   for (int c = threadIdx.x; c < copies; c += THREADS) {
     const int unit = c * per_copy;                  // index of (m, head, split) in stage order

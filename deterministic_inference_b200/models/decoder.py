@@ -1,4 +1,4 @@
-"""The generic decoder: embedding, a schedule of blocks, final norm, head.
+"""The generic decoder: embedding part, a schedule of blocks, final norm, head part.
 
 It is built from a ``ModelPlan`` alone and runs one step: the tokens of the
 batch through every schedule entry, each entry's mixer working on the cache the
@@ -12,7 +12,8 @@ from __future__ import annotations
 import torch
 
 from ..kernels import ops
-from ..parts import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, BuildContext, ModelPlan, TensorSpec
+from ..parts import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, BuildContext, ModelPlan,
+                     TensorSpec)
 
 
 class DecoderModel:
@@ -33,28 +34,27 @@ class DecoderModel:
                                              mixer_norm=n1, feed_forward_norm=n2))
             self.mixers.append(mixer)
         self.final_norm = NORMS.build(plan.final_norm, self.ctx)
-        self.embedding = None
-        self.head = None
+        self.embedding = EMBEDDINGS.build(plan.embedding, self.ctx)
+        self.head = HEADS.build(plan.head, self.ctx)
 
     # ---- weights ------------------------------------------------------------
 
     def parts(self):
+        yield self.embedding
         for b in self.blocks:
             yield b.mixer
             yield b.feed_forward
             yield b.mixer_norm
             yield b.feed_forward_norm
         yield self.final_norm
+        yield self.head
 
     def tensor_specs(self) -> list[TensorSpec]:
         """Every checkpoint tensor the model needs, in a fixed order (the order
-        the random-weights mode draws them in)."""
-        p = self.plan
-        specs = [TensorSpec(p.embedding_name, (p.vocab_size, p.hidden_size), role="table")]
+        the random-weights mode draws them in): embedding, layers, final norm, head."""
+        specs = []
         for part in self.parts():
             specs.extend(part.tensor_specs())
-        if p.head_name is not None:
-            specs.append(TensorSpec(p.head_name, (p.vocab_size, p.hidden_size)))
         seen = set()
         for s in specs:
             if s.name in seen:
@@ -63,11 +63,12 @@ class DecoderModel:
         return specs
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
-        p = self.plan
-        self.embedding = tensors[p.embedding_name]
-        self.head = self.embedding if p.head_name is None else tensors[p.head_name]
         for part in self.parts():
-            part.load(tensors)
+            if part is self.head and self.head.tied:
+                # a tied head shares the embedding's table, handed to it under the key None
+                part.load({**tensors, None: self.embedding.table()})
+            else:
+                part.load(tensors)
 
     # ---- caches ---------------------------------------------------------------
 
@@ -92,7 +93,7 @@ class DecoderModel:
 
     def forward(self, step, cache_manager) -> torch.Tensor:
         """float32 logits [R, V] at ``step.logit_indices``."""
-        hidden = ops.embedding(step.input_ids, self.embedding)
+        hidden = self.embedding.forward(step.input_ids)
         residual = None
         for e in self.plan.schedule:
             cache = cache_manager.view(e.cache, step, writes=e.writes_cache)
@@ -107,5 +108,4 @@ class DecoderModel:
         else:
             res_rows = ops.gather_rows(residual, step.logit_indices)
             rows, _ = self.final_norm.add_forward(rows, res_rows)
-        # logits leave as a plain tensor (the product may come as split-k partials)
-        return ops.as_tensor(ops.linear(rows, self.head, out_dtype=torch.float32))
+        return self.head.forward(rows)

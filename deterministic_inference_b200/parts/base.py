@@ -1,6 +1,9 @@
 """Interfaces of the parts.
 
 Part                 tensor_specs() -> [TensorSpec]; load(tensors: {name: Tensor})
+TokenEmbedding(Part) forward(ids int32 [T]) -> [T, H];  table() -> the [V, H] tensor, or None
+Head(Part)           forward(rows [R, H]) -> float32 logits [R, V];  ``tied``: load() is given
+                     the embedding's table under the key None instead of a tensor of its own
 Norm(Part)           forward(x) -> y;  add_forward(x, residual) -> (y, residual)
 PositionEncoding     prepare(); rotary_table() -> Tensor | None; apply(q, k, positions)
 Mixer(Part)          cache_spec() -> PagedKVSpec | StateSpec | None
@@ -38,6 +41,22 @@ class Part:
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         pass
+
+
+class TokenEmbedding(Part):
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def table(self) -> Optional[torch.Tensor]:
+        """The [vocabulary, hidden] tensor a tied head may share, or None."""
+        return None
+
+
+class Head(Part):
+    tied = False      # True: ``load`` finds the embedding's table under the key None
+
+    def forward(self, rows: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
 
 
 class Norm(Part):

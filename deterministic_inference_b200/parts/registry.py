@@ -54,12 +54,16 @@ class Registry:
         return sorted(self._kinds)
 
 
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 BLOCKS = Registry("block")
 
+register_embedding = EMBEDDINGS.register
+register_head = HEADS.register
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
 register_norm = NORMS.register

@@ -52,8 +52,8 @@ class ScheduleEntry:
 class ModelPlan:
     hidden_size: int
     vocab_size: int
-    embedding_name: str
-    head_name: Optional[str]          # None: the head is the embedding (tied)
+    embedding: PartSpec               # token ids -> hidden states
+    head: PartSpec                    # hidden states of the wanted rows -> float32 logits
     final_norm: PartSpec
     layers: tuple
     schedule: tuple

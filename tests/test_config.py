@@ -72,8 +72,8 @@ def test_plan_is_data():
     assert [e.layer for e in plan.schedule] == [0, 1] and all(e.writes_cache for e in plan.schedule)
     m = plan.layers[0].mixer
     assert m.kind == "gqa_attention" and m.params["head_dim"] == 16 and m.params["scale"] == 16 ** -0.5
-    assert plan.head_name is None                       # tied
-    assert preset("tiny_b").plan().head_name == "lm_head.weight"
+    assert plan.head.params["name"] is None              # tied
+    assert preset("tiny_b").plan().head.params["name"] == "lm_head.weight"
 
 
 def test_presets_and_parameter_counts():

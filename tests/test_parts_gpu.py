@@ -1,8 +1,10 @@
 """Each part alone against its plain counterpart, and the generality of the
-assembly: a toy mixer with state of its own, a toy feed-forward and a toy position
-encoding, all defined here, are registered, built into a model by a plan, loaded
-and stepped through the engine's step function without a change to the package;
-a plan may name a layer twice and let a layer read another layer's cache."""
+assembly: a toy mixer with state of its own, a toy feed-forward with routing, a toy
+position encoding, a toy embedding (scaled) and a toy head (capped logits), all defined
+here, are registered, built into a model by a plan, loaded and stepped through the
+engine's step function without a change to the package; a plan may name a layer twice and
+let a layer read another layer's cache; and a toy architecture registered here generates
+through ``Engine.generate`` from a model folder."""
 
 import pytest
 import torch
@@ -14,9 +16,11 @@ from deterministic_inference_b200.models.decoder import DecoderModel
 from deterministic_inference_b200.parts import (FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS,
                                                 BuildContext, LayerSpec, ModelPlan, PagedKVSpec,
                                                 PartSpec, ScheduleEntry, StateSpec, TensorSpec,
-                                                register_feed_forward, register_mixer,
+                                                register_embedding, register_feed_forward,
+                                                register_head, register_mixer,
                                                 register_position_encoding)
-from deterministic_inference_b200.parts.base import FeedForward, Mixer, PositionEncoding
+from deterministic_inference_b200.parts.base import (FeedForward, Head, Mixer, PositionEncoding,
+                                                     TokenEmbedding)
 from tests import plain_qwen3 as P
 
 pytestmark = pytest.mark.gpu
@@ -187,6 +191,43 @@ class ScaledRope(PositionEncoding):
         return torch.cat([f.cos(), f.sin()], -1).contiguous()
 
 
+@register_embedding("toy_scaled_embedding")
+class ScaledEmbedding(TokenEmbedding):
+    """Another embedding: the gathered rows are multiplied by a constant."""
+
+    def __init__(self, ctx, name, vocab_size, hidden_size, factor):
+        self.name, self.v, self.h, self.factor = name, vocab_size, hidden_size, factor
+
+    def tensor_specs(self):
+        return [TensorSpec(self.name, (self.v, self.h), role="table")]
+
+    def load(self, tensors):
+        self.weight = tensors[self.name]
+
+    def table(self):
+        return self.weight
+
+    def forward(self, ids):
+        return (ops.embedding(ids, self.weight).float() * self.factor).to(self.weight.dtype)
+
+
+@register_head("toy_capped_head")
+class CappedHead(Head):
+    """Another head: tied to the embedding's table, logits squashed to (-cap, cap)."""
+
+    tied = True
+
+    def __init__(self, ctx, cap):
+        self.cap = cap
+
+    def load(self, tensors):
+        self.weight = tensors[None]
+
+    def forward(self, rows):
+        logits = ops.as_tensor(ops.linear(rows, self.weight, out_dtype=torch.float32))
+        return self.cap * torch.tanh(logits / self.cap)
+
+
 def _toy_plan(h=48, vocab=64):
     attn = lambda i: PartSpec("gqa_attention", dict(
         prefix=f"l{i}.attn.", hidden_size=h, num_heads=4, num_kv_heads=2, head_dim=16, scale=0.25,
@@ -205,7 +246,10 @@ def _toy_plan(h=48, vocab=64):
     # the cache its first run wrote; layer 0's state is cache 0
     schedule = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(1, 2),
                 ScheduleEntry(1, 1, writes_cache=False))
-    return ModelPlan(hidden_size=h, vocab_size=vocab, embedding_name="emb", head_name="head",
+    return ModelPlan(hidden_size=h, vocab_size=vocab,
+                     embedding=PartSpec("toy_scaled_embedding", dict(name="emb", vocab_size=vocab,
+                                                                      hidden_size=h, factor=3.0)),
+                     head=PartSpec("toy_capped_head", dict(cap=5.0)),
                      final_norm=norm("final"), layers=layers, schedule=schedule, max_positions=128)
 
 
@@ -243,6 +287,8 @@ def test_toy_parts_are_registered_built_and_stepped(dtype):
     b = cache.allocate_slot()          # the same slot again: its state must start from zero
     parts = run([7, 1, 1, 13, 2, 16], toks, b)
     assert whole.shape == (40, 64) and torch.isfinite(whole).all()
+    assert float(whole.abs().max()) < 5.0 and float(whole.abs().max()) > 0.5      # the head's cap is at work
+    assert [s.name for s in model.tensor_specs()].count("emb") == 1 and model.head.weight is model.embedding.table()
     torch.testing.assert_close(parts, whole, **(dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16
                                                 else dict(atol=1e-4, rtol=1e-4)))
     # two requests in one batch keep their states apart
@@ -270,3 +316,69 @@ def test_plan_validation():
         bad.validate()
     with pytest.raises(KeyError, match="unknown mixer kind"):
         MIXERS.build(PartSpec("nope", {}), ctx(torch.float32))
+
+
+class ToyConfig:
+    """A toy architecture's configuration class, registered from this file: config.json
+    gives the width and the vocabulary, ``plan()`` the toy plan above (a mixer with state,
+    a routed feed-forward, a scaled embedding, a capped head, a layer run twice)."""
+
+    def __init__(self, h, vocab):
+        self.h, self.vocab = h, vocab
+
+    @classmethod
+    def from_dict(cls, d, generation_config=None):
+        return cls(int(d["toy_width"]), int(d["toy_vocab"]))
+
+    @classmethod
+    def from_json(cls, model_dir):
+        import json
+        from pathlib import Path
+        return cls.from_dict(json.loads((Path(model_dir) / "config.json").read_text()))
+
+    def to_dict(self):
+        return {"architectures": ["ToyForCausalLM"], "toy_width": self.h, "toy_vocab": self.vocab}
+
+    def plan(self):
+        return _toy_plan(self.h, self.vocab)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_generates_through_the_engine(dtype, tmp_path):
+    """The toy architecture is registered by name, its model folder is written with the
+    package's random-weights writer and loaded by its loader, and ``Engine.generate`` runs
+    it: prompts in portions under a small token budget, a pool so small that requests are
+    preempted (their state is rebuilt from token 0), decoding with CUDA graphs switched on:
+    the mixer keeps per-request state, so no step is captured, and the tokens are those of
+    an engine without graphs."""
+    import json
+    from deterministic_inference_b200 import Engine, EngineConfig, SamplingParams
+    from deterministic_inference_b200.models.registry import register_architecture
+    from deterministic_inference_b200.weights import write_random_model
+    register_architecture("ToyForCausalLM", ToyConfig)
+    cfg = ToyConfig(48, 64)
+    write_random_model(cfg, 5, tmp_path)
+    assert json.loads((tmp_path / "config.json").read_text())["architectures"] == ["ToyForCausalLM"]
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 64, (n,), generator=g).tolist() for n in (5, 23, 40, 9)]
+    sp = SamplingParams(max_new_tokens=12, ignore_eos=True)
+    outs = {}
+    for name, kw in (("graphs", dict(cuda_graphs=True)), ("launched", dict(cuda_graphs=False)),
+                     ("portions", dict(cuda_graphs=True, max_prefill_tokens=7)),
+                     ("tight", dict(cuda_graphs=True, kv_pool_tokens=96, max_prefill_tokens=16))):
+        eng = Engine(EngineConfig(model_path=str(tmp_path), dtype=dtype, device=DEV, page_size=16,
+                                  max_reqs=8, max_seq_len=128, **{"kv_pool_tokens": 1024, **kw}))
+        res = eng.generate(prompts, sp)
+        outs[name] = [o.token_ids for o in res]
+        assert all(len(t) == 12 for t in outs[name])
+        if eng.runner.decode_graphs is not None:
+            assert eng.runner.decode_graphs.replays == 0 and eng.runner.step_graphs.replays == 0
+        if name == "tight":
+            assert sum(o.num_preemptions for o in res) > 0
+        eng.cache.check_invariants()
+    assert outs["graphs"] == outs["launched"]
+    if dtype == "float32":
+        # other cuts add the mixer's running sums in another order: the first tokens agree
+        # (later ones follow from them)
+        assert [t[0] for t in outs["portions"]] == [t[0] for t in outs["graphs"]]
+        assert [t[0] for t in outs["tight"]] == [t[0] for t in outs["graphs"]]

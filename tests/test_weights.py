@@ -85,7 +85,7 @@ def test_tied_head_ignores_a_stray_lm_head_and_rotary_buffers(tmp_path):
     save_file(t, str(d / "model.safetensors"))
     w = load_weights(d, model.tensor_specs(), model.plan, torch.bfloat16, "cpu")
     model.load(w)
-    assert model.head is model.embedding
+    assert model.head.tied and model.head.weight is model.embedding.table()
 
 
 def test_no_safetensors(tmp_path):
