@@ -45,6 +45,13 @@ class EngineConfig:
     # one per process: the engine built last sets it.
     library_products: bool = True
 
+    # Debug checks on the host, every step: the step's packed metadata is validated before
+    # it reaches the device (every index a kernel follows lies inside what it indexes) and the
+    # cache manager's books are checked (no page lost, held twice or freed twice).  The
+    # counterpart of the reference's SID_DEBUG_ALLOC (sid/engine/kv_cache.py:50-52).  Default:
+    # the environment's DIB200_DEBUG=1.
+    debug_checks: Optional[bool] = None
+
     cuda_graphs: bool = True             # replay pure-decode steps as CUDA graphs
     async_scheduling: bool = True        # sampled tokens stay on the device for the next step;
                                          # the host reads them one step late
@@ -65,6 +72,9 @@ class EngineConfig:
                 raise ValueError(f"{name} must be positive")
         if self.gpu_memory_fraction is not None and not 0.0 < self.gpu_memory_fraction <= 1.0:
             raise ValueError("gpu_memory_fraction must be in (0, 1]")
+        if self.debug_checks is None:
+            import os
+            self.debug_checks = os.environ.get("DIB200_DEBUG", "0") == "1"
         if self.max_prompt_len is None:
             self.max_prompt_len = self.max_seq_len
 

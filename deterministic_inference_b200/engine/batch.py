@@ -240,14 +240,77 @@ def fill_packed(host: np.ndarray, lay: PackedLayout, shape: StepShape, cache, gr
     return num_patches
 
 
-def build_step_batch(entries: list, cache, device, pin: bool = True) -> StepBatch:
+class StepCheckError(ValueError):
+    """A step's metadata names something outside its range (debug checks)."""
+
+
+def check_packed(host: np.ndarray, lay: PackedLayout, cache, group_list: list, vocab_size: int,
+                 max_positions: int, num_prev_tokens: int = 0) -> None:
+    """Debug check of a step's packed metadata, on the host, before it reaches the device:
+    every index a kernel will follow (token ids, positions, block-table entries, cache
+    slots, logit rows, state slots, patch places) lies inside what it indexes.  The kernels
+    read nothing else that a request controls, so this covers their read side; the
+    reference checks its launch arguments on the host in the same spirit
+    (sid/csrc/flash_decode.cu:298-345).  Raises ``StepCheckError`` naming the first
+    offender."""
+    def need(ok, what):
+        if not ok:
+            raise StepCheckError(f"step metadata: {what}")
+
+    t, b = lay.t, lay.b
+    ids, pos = lay.seg(host, "input_ids"), lay.seg(host, "positions")
+    need(t == 0 or (ids.min() >= 0 and ids.max() < vocab_size),
+         f"a token id outside [0, {vocab_size})")
+    need(t == 0 or (pos.min() >= 0 and pos.max() < max_positions),
+         f"a position outside [0, {max_positions})")
+    tseq = lay.seg(host, "token_seq")
+    need(t == 0 or (tseq.min() >= 0 and tseq.max() < b), "a token names a sequence the step does not have")
+    cu = lay.seg(host, "cu_q_lens")
+    need(cu[0] == 0 and cu[b] == t and bool((np.diff(cu) >= 1).all()),
+         "sequence boundaries do not cover the tokens, or a sequence brings none")
+    lens = lay.seg(host, "seq_lens")
+    need(bool((lens >= np.diff(cu)).all()) and (b == 0 or lens.max() <= cache.max_seq_len),
+         "a sequence's key count is below its new tokens or beyond max_seq_len")
+    slots = lay.seg(host, "state_slots")
+    need(b == 0 or (slots.min() >= 0 and slots.max() < cache.max_reqs), "a state slot outside the table")
+    li = lay.seg(host, "logit_indices")
+    need(li.size == 0 or (li.min() >= 0 and li.max() < t), "a logits row names a token the step does not have")
+    pdst, psrc = lay.seg(host, "patch_dst"), lay.seg(host, "patch_src")
+    live = pdst >= 0
+    need(bool((pdst[live] < t).all()) and bool((psrc[live] >= 0).all())
+         and bool((psrc[live] < max(num_prev_tokens, 1)).all()),
+         "a token to be taken from the previous step's samples is out of range")
+    for gi, g in enumerate(group_list):
+        bt = lay.seg(host, ("bt", gi)).reshape(b, lay.width)
+        need(bt.size == 0 or (bt.min() >= 0 and bt.max() < g.num_pages),
+             f"group {g.key}: a block-table entry outside the pool of {g.num_pages} pages")
+        sm = lay.seg(host, ("sm", gi))
+        need(sm.size == 0 or (sm.min() >= 0 and sm.max() < g.num_pages * g.page_size),
+             f"group {g.key}: a cache slot outside the pool")
+        # pages a sequence needs for its keys must be real ones, except those a window gave back
+        for bi in range(b):
+            if slots[bi] == 0:
+                continue        # a padding sequence: it lives on page 0 and slot 0 on purpose
+            first_needed = 0
+            if g.window is not None:
+                first_needed = max(0, int(lens[bi]) - int(cu[bi + 1] - cu[bi]) - g.window + 1) // g.page_size
+            need_pages = -(-int(lens[bi]) // g.page_size)
+            row = bt[bi, first_needed:min(need_pages, lay.width)]
+            need(need_pages <= lay.width and bool((row > 0).all()),
+                 f"group {g.key}: sequence {bi} has keys on a page it does not hold")
+
+
+def build_step_batch(entries: list, cache, device, pin: bool = True, check=None) -> StepBatch:
     """Pack ``entries`` (``SequenceInput``; pages already allocated) into a
-    ``StepBatch`` on ``device``."""
+    ``StepBatch`` on ``device``.  ``check(host array, layout)``: called on the packed
+    metadata before it is copied (debug checks)."""
     shape = describe_step(entries, cache)
     group_list = list(cache.page_groups.values())
     lay = PackedLayout(shape.t, len(shape.seqs), len(shape.logit_index), shape.width, len(group_list))
     host = np.zeros(lay.size, dtype=np.int32)
     num_patches = fill_packed(host, lay, shape, cache, group_list)
+    if check is not None:
+        check(host, lay)
     dev = torch.device(device)
     th = torch.from_numpy(host)
     if dev.type == "cuda":

@@ -57,6 +57,7 @@ class _Captured:
         self.graph, self.static_meta, self.host_meta = graph, static_meta, host_meta
         self.layout, self.logits, self.batch = layout, logits, batch
         self.uploaded = torch.cuda.Event()
+        self.check = None        # debug check of the packed metadata (host array, layout)
 
     def upload(self, fill) -> object:
         """Fill the pinned metadata (``fill(array)``) and copy it to the device.  The
@@ -64,6 +65,8 @@ class _Captured:
         issue steps faster than the GPU takes them."""
         self.uploaded.synchronize()
         result = fill(self.host_meta.numpy())
+        if self.check is not None:
+            self.check(self.host_meta.numpy(), self.layout)
         self.static_meta.copy_(self.host_meta, non_blocking=True)
         self.uploaded.record()
         return result
@@ -83,6 +86,7 @@ class DecodeGraphs:
         self.capture_seconds = 0.0
         self.kernels_per_graph: dict[tuple, int] = {}
         self.kernels_replayed = 0          # kernels inside the graphs replayed so far
+        self.check = None                  # debug check of every step's packed metadata
         # one memory pool for all graphs of this object: only one of them runs at a time,
         # and what a replay leaves (its logits) is read before the next replay is issued
         self.pool = torch.cuda.graph_pool_handle() if torch.cuda.is_available() else None
@@ -137,6 +141,7 @@ class DecodeGraphs:
             logits = self.model.forward(batch, self.cache)
         self.kernels_per_graph[key] = ops.launch_count - n0
         cap = _Captured(graph, static, host, lay, logits, batch)
+        cap.check = self.check
         self.graphs[key] = cap
         return cap
 
@@ -194,6 +199,7 @@ class StepGraphs:
         self.capture_seconds = 0.0
         self.kernels_per_graph: dict[tuple, int] = {}
         self.kernels_replayed = 0
+        self.check = None                  # debug check of every step's packed metadata
         # one memory pool for all graphs (their activations never live at the same time;
         # a replay's logits are copied out before the next replay)
         self.pool = torch.cuda.graph_pool_handle() if torch.cuda.is_available() else None
@@ -268,6 +274,7 @@ class StepGraphs:
             logits = self.model.forward(batch, self.cache)
         self.kernels_per_graph[key] = ops.launch_count - n0
         cap = _Captured(graph, static, host, lay, logits, batch)
+        cap.check = self.check
         self.graphs[key] = cap
         self.captures += 1
         return cap

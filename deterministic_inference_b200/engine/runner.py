@@ -17,7 +17,7 @@ from ..config.engine_config import EngineConfig
 from ..models.registry import build_model, config_from_dir
 from ..weights.loader import load_weights
 from ..weights.random_init import random_tensors_on_device
-from .batch import SequenceInput, StepBatch, build_step_batch
+from .batch import SequenceInput, StepBatch, build_step_batch, check_packed
 
 _TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -71,6 +71,15 @@ class ModelRunner:
             self.step_graphs = StepGraphs(self.model, self.cache, self.device)
             self.decode_graphs = DecodeGraphs(self.model, self.cache, self.device)
         self._checked_kernels = False
+        self._check = None
+        if cfg.debug_checks:
+            groups = list(self.cache.page_groups.values())
+            vocab = self.model.plan.vocab_size
+            self._check = lambda host, lay, prev=0: check_packed(
+                host, lay, self.cache, groups, vocab, self.max_positions, prev)
+            for g in (self.step_graphs, self.decode_graphs):
+                if g is not None:
+                    g.check = self._check
 
     @torch.inference_mode()
     def step(self, entries: list[SequenceInput], prev_tokens=None):
@@ -90,7 +99,11 @@ class ModelRunner:
         if replayed is not None:
             logits, batch = replayed
         else:
-            batch = build_step_batch(entries, self.cache, self.device)
+            check = None
+            if self._check is not None:
+                n_prev = 0 if prev_tokens is None else int(prev_tokens.shape[0])
+                check = lambda host, lay: self._check(host, lay, n_prev)
+            batch = build_step_batch(entries, self.cache, self.device, check=check)
             if batch.num_patches:
                 from ..kernels import ops
                 ops.patch_token_ids(batch.input_ids, batch.patch_dst, batch.patch_src, prev_tokens)
@@ -103,6 +116,8 @@ class ModelRunner:
                 self._checked_kernels = True
         for e in entries:
             self.cache.release_passed(e.slot, e.num_computed + len(e.tokens))
+        if self._check is not None:
+            self.cache.check_invariants()
         self.steps_run += 1
         self.tokens_run += sum(len(e.tokens) for e in entries)
         return logits, batch

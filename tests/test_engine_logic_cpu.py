@@ -192,3 +192,43 @@ def test_a_request_preempted_with_its_last_token_in_flight_retires(seed, tiny_mo
     assert [o.token_ids for o in outs] == [plain_qwen3.generate(cfg, w, p, n) for p, n in zip(prompts, news)]
     eng.cache.check_invariants()
     assert eng.cache.num_free_pages() == eng.cache.usable_pages()
+
+
+def test_debug_checks_catch_bad_step_metadata(tiny_model_dirs, torch_ops):
+    """``debug_checks``: every step's packed metadata is validated on the host before it
+    reaches the device, and the cache's books after it.  A step that is in order passes;
+    a token id outside the vocabulary, a block table that names a page outside the pool,
+    keys on a page the sequence does not hold, and a logits row beyond the step's tokens are
+    each refused by name."""
+    import numpy as np
+    from deterministic_inference_b200.engine.batch import (PackedLayout, StepCheckError, check_packed,
+                                                           describe_step, fill_packed)
+    d = tiny_model_dirs["bw"]          # two cache groups: all keys, and a window
+    r = ModelRunner(EngineConfig(model_path=str(d), dtype="float32", device="cpu", kv_pool_tokens=256,
+                                 page_size=16, max_reqs=8, max_seq_len=256, debug_checks=True))
+    assert r._check is not None
+    s = r.cache.allocate_slot()
+    r.step([SequenceInput(s, list(range(40)), 0, [39])])        # in order: passes, books checked
+    r.step([SequenceInput(s, [1], 40, [0])])
+    with pytest.raises(StepCheckError, match="token id"):
+        r.step([SequenceInput(s, [100000], 41, [0])])
+    # the packed array itself, with one field spoilt at a time
+    groups = list(r.cache.page_groups.values())
+    entries = [SequenceInput(s, [5, 6, 7], 41, [2])]
+    r.cache.allocate(s, 44)
+    shape = describe_step(entries, r.cache)
+    lay = PackedLayout(shape.t, 1, 1, shape.width, len(groups))
+    host = np.zeros(lay.size, dtype=np.int32)
+    fill_packed(host, lay, shape, r.cache, groups)
+    vocab, maxpos = 512, 512
+    check_packed(host, lay, r.cache, groups, vocab, maxpos)
+    for field, value, message in ((("bt", 0), 10 ** 6, "block-table entry"), (("bt", 0), 0, "does not hold"),
+                                  ("logit_indices", 3, "logits row"), ("positions", 600, "position"),
+                                  (("sm", 1), 10 ** 7, "cache slot"), ("state_slots", 99, "state slot")):
+        bad = host.copy()
+        seg = lay.seg(bad, field)
+        seg[-1 if field == ("bt", 0) and value == 0 else 0] = value
+        if field == ("bt", 0) and value == 0:
+            seg[2] = 0          # the page that holds keys 32..47
+        with pytest.raises(StepCheckError, match=message):
+            check_packed(bad, lay, r.cache, groups, vocab, maxpos)

@@ -349,3 +349,21 @@ def test_bfloat16_bits_of_a_token_do_not_depend_on_its_step(name, tiny_model_dir
             assert torch.equal(rows[p], row), (what, p)
     from deterministic_inference_b200.kernels import gemm_bf16
     gemm_bf16.set_library_products(True)
+
+
+def test_generation_with_debug_checks_on(tiny_model_dirs):
+    """``debug_checks=True``: every step's metadata (launched steps, replayed graphs and their
+    padding sequences) passes the host-side checks and the tokens are those of an engine
+    without them."""
+    from deterministic_inference_b200 import SamplingParams
+    cfg = plain_qwen3.read_model_dir(tiny_model_dirs["bw"])[0]
+    prompts = _prompts(cfg["vocab_size"], (3, 20, 47, 20, 20), 5)
+    sp = SamplingParams(max_new_tokens=40, ignore_eos=True)
+    outs = []
+    for debug in (True, False):
+        eng = _engine(tiny_model_dirs["bw"], "bfloat16", page_size=16, max_prefill_tokens=24,
+                      kv_pool_tokens=512, debug_checks=debug)
+        outs.append([o.token_ids for o in eng.generate(prompts, sp)])
+        if debug:
+            assert eng.runner.decode_graphs.replays > 0 and eng.runner._check is not None
+    assert outs[0] == outs[1]
