@@ -396,7 +396,7 @@ def main() -> int:
             replayed_ms = None
         _, flops = model_bytes_and_flops(mcfg, n_layers, 1, 0, n)
         return {"value": n / (cold_ms / 1e3), "tokens": n, "ms": cold_ms, "cold_ms": cold_ms,
-                "replayed_ms": replayed_ms,
+                "launched_ms": [round(x, 3) for x in launched], "replayed_ms": replayed_ms,
                 "frac": flops / (cold_ms / 1e3) / (pk["bf16_tflops"] * 1e12),
                 "frac_replayed": (flops / (replayed_ms / 1e3) / (pk["bf16_tflops"] * 1e12)
                                   if replayed_ms else None),

@@ -1,0 +1,402 @@
+// bfloat16 matrix product out[M, N] = X[M, K] * W[N, K]^T for many rows (prompt portions) on
+// the 5th-generation tensor cores: a persistent kernel, one CTA per SM, that walks output
+// tiles of 128 tokens x 256 features.  tcgen05.mma (M 128, N 256, K 16) with the accumulator
+// in tensor memory, operands staged by TMA (128-byte swizzle) through a ring of four
+// mbarrier-guarded stages of 48 KB, float32 accumulation over all of k in one pass, in the
+// same order for every tile: a row's bits do not depend on how many rows the step has.
+//
+// The accumulator is double-buffered (2 x 256 of the 512 tensor-memory columns): while the
+// four epilogue warps read tile i back (tcgen05.ld: a thread owns one token row), round it
+// and store it, the MMA warp already works on tile i + 1.  Tiles are taken in an order that
+// keeps the CTAs that run side by side on the same 256 weight rows (they differ in their
+// token tile), so a weight tile comes from DRAM once and from L2 afterwards.
+//
+// GATED: W = [gate rows ; up rows] of a gated feed-forward ([2N, K]); a tile holds 128
+// gate rows and the 128 up rows of the same features, and the epilogue writes
+// silu(gate) * up, [M, N]: the [gate | up] product and the gate kernel's pass over it are
+// gone.  The two products are rounded to bfloat16 first, as stored products would be, and
+// the gate is silu_gate<bf16> of common.cuh, so the bits are those of the two-kernel path.
+//
+// Roles in a CTA of 192 threads: warp 0 issues the TMA loads (the weights of the first
+// stages before the programmatic dependency wait, the tokens after it), warp 1 allocates
+// tensor memory and issues the MMAs, warps 2-5 are the epilogue.  Every mbarrier wait is
+// bounded; a wait that runs out sets the error word (dib_gemm_bf16_large_status), tensor
+// memory is still freed and the kernel returns.
+#include <cuda.h>
+
+#include <cstdlib>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BM = 128;       // tokens per tile = MMA M
+constexpr int BNL = 256;      // features per tile = MMA N (GATED: 128 gate + 128 up rows)
+constexpr int BK = 64;        // k per stage: 128 bytes = one swizzle atom
+constexpr int UMMA_K = 16;
+constexpr int STAGES = 4;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNL * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+
+__device__ int dib_gemm_large_error_word = 0;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) {
+  return (unsigned)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1,
+                                            unsigned long long* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(smem_u32(bar)),
+      "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(unsigned long long* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, unsigned long long desc_a,
+                                       unsigned long long desc_b, unsigned idesc, unsigned accum) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accum), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(unsigned taddr, unsigned (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, "
+      "%12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, "
+      "%30, %31}, [%32];\n"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+// K-major bf16 tile, rows of 128 bytes, 128-byte swizzle: 8-row groups 1,024 bytes apart.
+__device__ __forceinline__ unsigned long long smem_desc_sw128(unsigned addr) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((addr & 0x3FFFFu) >> 4);
+  d |= (unsigned long long)(1024u >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+// kind::f16: float32 accumulator, bf16 A and B, both K-major.
+constexpr unsigned make_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(m >> 4) << 24);
+}
+__device__ __forceinline__ unsigned pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+
+template <typename OutT, bool GATED>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                  OutT* __restrict__ out, int M, int N, int K, int m_tiles, int n_tiles) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
+  unsigned long long* empty = full + STAGES;
+  unsigned long long* acc_full = empty + STAGES;     // [2] a tile's accumulator is complete
+  unsigned long long* acc_empty = acc_full + 2;      // [2] the epilogue has read it (128 arrivals)
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty + 2);
+
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&map_x);
+    prefetch_tensormap(&map_w);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_kb = (K + BK - 1) / BK;
+  const int tiles = m_tiles * n_tiles;
+  // tile t: token tile t % m_tiles of feature tile t / m_tiles; this CTA takes
+  // blockIdx.x, blockIdx.x + gridDim.x, ...
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 128);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(512u));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- TMA producer.  The ring runs on across this CTA's tiles: load number c is
+      // k-block c % num_kb of its tile number c / num_kb and goes to stage c % STAGES.  The
+      // weights do not depend on the kernel before this one, so those of the first STAGES
+      // loads are sent for before the wait for that kernel, the tokens after it.
+      const int my_tiles = tiles > (int)blockIdx.x ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+      const int total = my_tiles * num_kb;
+      auto load_w = [&](int c) {
+        const int t = blockIdx.x + (c / num_kb) * gridDim.x, kb = c % num_kb;
+        const int n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
+        unsigned char* b = smem + (c % STAGES) * STAGE_BYTES + A_BYTES;
+        tma_load_2d(b, &map_w, kb * BK, n0, &full[c % STAGES]);
+        tma_load_2d(b + B_BYTES / 2, &map_w, kb * BK, GATED ? N + n0 : n0 + BNL / 2, &full[c % STAGES]);
+      };
+      auto load_x = [&](int c) {
+        const int t = blockIdx.x + (c / num_kb) * gridDim.x, kb = c % num_kb;
+        tma_load_2d(smem + (c % STAGES) * STAGE_BYTES, &map_x, kb * BK, (t % m_tiles) * BM, &full[c % STAGES]);
+      };
+      const int pre = total < STAGES ? total : STAGES;
+      for (int c = 0; c < pre; ++c) {
+        mbar_expect_tx(&full[c], STAGE_BYTES);
+        load_w(c);
+      }
+      pdl_wait();
+      for (int c = 0; c < pre; ++c) load_x(c);
+      for (int c = pre; c < total && ok; ++c) {
+        ok = mbar_wait(&empty[c % STAGES], ((c / STAGES) - 1) & 1);
+        if (!ok) break;
+        mbar_expect_tx(&full[c % STAGES], STAGE_BYTES);
+        load_w(c);
+        load_x(c);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer
+      constexpr unsigned idesc = make_idesc(BM, BNL);
+      int count = 0, local = 0;
+      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
+        const int buf = local & 1;
+        if (local >= 2) {     // the epilogue must have read this buffer's earlier tile
+          ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        for (int kb = 0; kb < num_kb && ok; ++kb, ++count) {
+          const int s = count % STAGES;
+          ok = mbar_wait(&full[s], (count / STAGES) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          const unsigned a = smem_u32(smem + s * STAGE_BYTES), b = a + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            tc_mma(tmem + buf * BNL, smem_desc_sw128(a + k * UMMA_K * 2), smem_desc_sw128(b + k * UMMA_K * 2),
+                   idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&empty[s]);
+        }
+        if (ok) tc_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ---- epilogue: warps 2..5; a warp reads the 32 lanes (token rows) 32 * (warp % 4) ..
+    pdl_wait();      // nothing is stored before the kernel before this one has finished
+    const int quarter = warp & 3;
+    const unsigned lane_base = (unsigned)(quarter * 32) << 16;
+    int local = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++local) {
+      const int buf = local & 1;
+      const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
+      bool got = ok && mbar_wait(&acc_full[buf], (local >> 1) & 1);
+      got = __all_sync(0xffffffffu, got);     // tcgen05.ld below is warp-wide
+      if (!got) { ok = false; break; }
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const unsigned src = tmem + buf * BNL + lane_base;
+      if (GATED) {
+        // columns 0..127: gate, 128..255: up, of features n0 .. n0 + 127
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          unsigned g[32], u[32];
+          tc_ld32(src + c * 32, g);
+          tc_ld32(src + 128 + c * 32, u);
+          tc_wait_ld();
+          if (row < M) {
+            OutT* dst = out + (size_t)row * N + n0 + c * 32;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              float y[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e)
+                y[e] = silu_gate<__nv_bfloat16>(round_to<__nv_bfloat16>(__uint_as_float(g[q * 8 + e])),
+                                                round_to<__nv_bfloat16>(__uint_as_float(u[q * 8 + e])));
+              if (n0 + c * 32 + q * 8 + 8 <= N) {
+                *reinterpret_cast<uint4*>(dst + q * 8) =
+                    make_uint4(pack2_bf16(y[0], y[1]), pack2_bf16(y[2], y[3]), pack2_bf16(y[4], y[5]),
+                               pack2_bf16(y[6], y[7]));
+              } else {
+                for (int e = 0; e < 8; ++e)
+                  if (n0 + c * 32 + q * 8 + e < N) Elem<OutT>::store(dst + q * 8 + e, y[e]);
+              }
+            }
+          }
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BNL / 32; ++c) {
+          unsigned v[32];
+          tc_ld32(src + c * 32, v);
+          tc_wait_ld();
+          if (row < M) {
+            OutT* dst = out + (size_t)row * N + n0 + c * 32;
+            if (sizeof(OutT) == 2 && n0 + c * 32 + 32 <= N) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst) + q * 8) = make_uint4(
+                    pack2_bf16(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])),
+                    pack2_bf16(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])),
+                    pack2_bf16(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])),
+                    pack2_bf16(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7])));
+            } else {
+              for (int e = 0; e < 32; ++e)
+                if (n0 + c * 32 + e < N) Elem<OutT>::store(dst + e, __uint_as_float(v[e]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&acc_empty[buf]);
+    }
+  }
+  if (!ok) atomicExch(&dib_gemm_large_error_word, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
+  }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// Row-major bf16 matrix [rows, K], boxes of box_rows x 64 elements, 128-byte swizzle;
+// out-of-range elements read as zero.
+bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, int box_rows) {
+  EncodeTiledFn enc = encode_tiled();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <typename OutT, bool GATED>
+int launch_large(const void* x, const void* w, void* out, int M, int N, int K, int sm_count,
+                 cudaStream_t st) {
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, GATED ? 2ll * N : (long long)N, K, BNL / 2))
+    return DIB_LAUNCH_FAILED;
+  const int m_tiles = (M + BM - 1) / BM;
+  const int n_tiles = (N + (GATED ? BNL / 2 : BNL) - 1) / (GATED ? BNL / 2 : BNL);
+  const long long tiles = (long long)m_tiles * n_tiles;
+  if (tiles > (1ll << 30)) return DIB_BAD_SIZE;
+  auto kern = gemm_large_kernel<OutT, GATED>;
+  static DeviceOnce attr_set;
+  if (!attr_set.done()) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) !=
+        cudaSuccess)
+      return DIB_LAUNCH_FAILED;
+    attr_set.mark();
+  }
+  const int grid = (int)(tiles < sm_count ? tiles : sm_count);
+  dib_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, st, mx, mw, (OutT*)out, M, N, K, m_tiles,
+             n_tiles);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dib_gemm_bf16_large_status() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, dib_gemm_large_error_word, sizeof(int)) != cudaSuccess) return -1;
+  return v;
+}
+int dib_gemm_bf16_large_status_clear() {
+  const int v = 0;
+  return cudaMemcpyToSymbol(dib_gemm_large_error_word, &v, sizeof(int)) == cudaSuccess ? 0 : -1;
+}
+
+// out[M, N] = x[M, K] * w[N, K]^T; bf16 inputs, float32 accumulation over k in one pass;
+// out bf16 (out_fp32 = 0) or float32.  K a multiple of 8 (TMA wants 16-byte row strides); x,
+// w and out 16-byte aligned, N a multiple of 8 for the bf16 output.
+int dib_gemm_bf16_large(const void* x, const void* w, void* out, int M, int N, int K, int out_fp32,
+                        int sm_count, cudaStream_t st) {
+  if (M == 0 || N == 0) return DIB_OK;
+  if (K < 8 || K % 8 != 0 || sm_count < 1 || (!out_fp32 && N % 8 != 0)) return DIB_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) % 16 != 0)
+    return DIB_BAD_ALIGN;
+  return out_fp32 ? launch_large<float, false>(x, w, out, M, N, K, sm_count, st)
+                  : launch_large<__nv_bfloat16, false>(x, w, out, M, N, K, sm_count, st);
+}
+
+// out[M, I] = silu(x w_gate^T) * (x w_up^T) with w = [w_gate ; w_up] of shape [2I, K]; bf16 in
+// and out.  I a multiple of 8, K of 8.
+int dib_gemm_bf16_large_gated(const void* x, const void* w, void* out, int M, int I, int K,
+                              int sm_count, cudaStream_t st) {
+  if (M == 0 || I == 0) return DIB_OK;
+  if (K < 8 || K % 8 != 0 || I % 8 != 0 || sm_count < 1) return DIB_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) % 16 != 0)
+    return DIB_BAD_ALIGN;
+  return launch_large<__nv_bfloat16, true>(x, w, out, M, I, K, sm_count, st);
+}
+
+}  // extern "C"

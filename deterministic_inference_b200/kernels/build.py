@@ -36,6 +36,7 @@ SOURCES = {
     "attention_generic": "attention_generic.cu",
     "attention_bf16": "attention_bf16.cu",
     "gemm_bf16": "gemm_bf16.cu",
+    "gemm_bf16_large": "gemm_bf16_large.cu",
     "decode_attention_noalloc": "decode_attention_noalloc.cu",
     "attention_prefill_tc": "attention_prefill_tc.cu",
 }
@@ -54,6 +55,7 @@ NVCC_FLAGS = [
 # extra flags / link libraries per library
 EXTRA_FLAGS = {
     "gemm_bf16": ["-lcuda"],
+    "gemm_bf16_large": ["-lcuda"],
 }
 
 

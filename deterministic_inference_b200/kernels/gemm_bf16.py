@@ -25,9 +25,50 @@ MAX_ROWS = OWN_KERNEL_ROWS
 GATED = os.environ.get("DIB200_GATED")
 
 
+# Products of more than MAX_ROWS rows: "library" (cuBLAS through torch.mm) or "own" (the
+# package's persistent tcgen05 kernel for many rows, csrc/gemm_bf16_large.cu, which adds up
+# all of k in one pass, so a row's bits do not depend on how many rows there are).
+# DIB200_LARGE_PRODUCTS=own|library, read once.
+LARGE_PRODUCTS = os.environ.get("DIB200_LARGE_PRODUCTS", "library")
+
+
 def set_library_products(on: bool) -> None:
     global MAX_ROWS
     MAX_ROWS = OWN_KERNEL_ROWS if on else 1 << 30
+
+
+def linear_large(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype):
+    """x [M, K] @ weight[N, K]^T by the package's kernel for many rows, or None if the
+    shape is not one it takes."""
+    from . import ops
+    m, k = x.shape
+    n = weight.shape[0]
+    if not (k % 8 == 0 and k >= 8 and (out_dtype == torch.float32 or n % 8 == 0)
+            and out_dtype in (torch.bfloat16, torch.float32)
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
+        return None
+    out = torch.empty(m, n, dtype=out_dtype, device=x.device)
+    st = ops._lib("gemm_bf16_large").dib_gemm_bf16_large(
+        ops._ptr(x), ops._ptr(weight), ops._ptr(out), c_int(m), c_int(n), c_int(k),
+        c_int(1 if out_dtype == torch.float32 else 0), c_int(_sms(x.device)), ops._stream())
+    ops._check(st, "linear(bfloat16, many rows)", f"M={m} N={n} K={k}")
+    return out
+
+
+def gated_linear_large(x: torch.Tensor, w_gate_up: torch.Tensor):
+    """silu(x @ w_gate^T) * (x @ w_up^T) in the many-rows kernel's epilogue, or None."""
+    from . import ops
+    m, k = x.shape
+    i = w_gate_up.shape[0] // 2
+    if not (k % 8 == 0 and k >= 8 and i % 8 == 0 and w_gate_up.shape[0] == 2 * i
+            and x.data_ptr() % 16 == 0 and w_gate_up.data_ptr() % 16 == 0):
+        return None
+    out = torch.empty(m, i, dtype=torch.bfloat16, device=x.device)
+    st = ops._lib("gemm_bf16_large").dib_gemm_bf16_large_gated(
+        ops._ptr(x), ops._ptr(w_gate_up), ops._ptr(out), c_int(m), c_int(i), c_int(k),
+        c_int(_sms(x.device)), ops._stream())
+    ops._check(st, "gated_linear(bfloat16, many rows)", f"M={m} I={i} K={k}")
+    return out
 
 _sm_count: dict = {}
 
@@ -89,6 +130,10 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype, allow_
                                c_int(k), fp32, c_void_p(0), c_int(_sms(x.device)), ops._stream())
         ops._check(st, "linear(bfloat16)", f"M={m} N={n} K={k}")
         return out
+    if LARGE_PRODUCTS == "own":
+        out = linear_large(x, weight, out_dtype)
+        if out is not None:
+            return out
     ops._launched(1)
     if out_dtype == torch.bfloat16:
         return torch.mm(x, weight.t())
@@ -137,6 +182,8 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor):
     from . import ops
     m, k = x.shape
     i = w_gate_up.shape[0] // 2
+    if m > MAX_ROWS:
+        return gated_linear_large(x, w_gate_up) if LARGE_PRODUCTS == "own" else None
     # one CTA per 64 features and no split of k: worth it when those CTAs fill whole waves
     # of the GPU about as well as the split product does (the kernel's own estimate; 0.6B
     # shape, 48 tiles: 1.458 ms per step against 1.435 ms with the split product and the

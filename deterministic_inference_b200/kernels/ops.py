@@ -105,6 +105,7 @@ def _lib(name: str) -> ctypes.CDLL:
 # Libraries whose kernels have bounded waits: name -> (read, clear) of its error word.
 _STATUS_FUNCTIONS = {
     "gemm_bf16": ("dib_gemm_bf16_status", "dib_gemm_bf16_status_clear"),
+    "gemm_bf16_large": ("dib_gemm_bf16_large_status", "dib_gemm_bf16_large_status_clear"),
     "attention_bf16": ("dib_attention_bf16_status", "dib_attention_bf16_status_clear"),
     "attention_prefill_tc": ("dib_attention_prefill_tc_status", "dib_attention_prefill_tc_status_clear"),
 }
