@@ -44,6 +44,11 @@ class EngineConfig:
     # then the same whatever its step holds (prompt portions are slower).  The switch is
     # one per process: the engine built last sets it.
     library_products: bool = True
+    # Which kernel takes the products of more than 128 rows while ``library_products`` is on:
+    # "library", "own" (the package's tcgen05 kernel for many rows) or "auto" (the package's
+    # kernel where it fuses the feed-forward's gate, the library elsewhere); None: the
+    # environment's DIB200_LARGE_PRODUCTS, else "auto".  One per process, like the switch above.
+    large_products: Optional[str] = None
 
     # Debug checks on the host, every step: the step's packed metadata is validated before
     # it reaches the device (every index a kernel follows lies inside what it indexes) and the
@@ -70,6 +75,8 @@ class EngineConfig:
         for name in ("max_reqs", "max_seq_len", "max_prefill_tokens", "max_decode_batch"):
             if getattr(self, name) < 1:
                 raise ValueError(f"{name} must be positive")
+        if self.large_products not in (None, "library", "own", "auto"):
+            raise ValueError("large_products must be 'library', 'own' or 'auto'")
         if self.gpu_memory_fraction is not None and not 0.0 < self.gpu_memory_fraction <= 1.0:
             raise ValueError("gpu_memory_fraction must be in (0, 1]")
         if self.debug_checks is None:

@@ -31,13 +31,17 @@
 namespace {
 
 constexpr int BM = 128;       // tokens per tile = MMA M
-constexpr int BNL = 256;      // features per tile = MMA N (GATED: 128 gate + 128 up rows)
 constexpr int BK = 64;        // k per stage: 128 bytes = one swizzle atom
 constexpr int UMMA_K = 16;
-constexpr int STAGES = 4;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BNL * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int A_BYTES = BM * BK * 2;
 constexpr int THREADS = 192;
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+// Features per tile = MMA N: 256 (GATED: 128 gate + 128 up rows), or 128 for products with so
+// few tiles of 256 that they would leave SMs idle.  Stages of the ring: what fits.
+template <int BNL> struct Tile {
+  static constexpr int B_BYTES = BNL * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = BNL == 256 ? 4 : 6;
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+};
 
 __device__ int dib_gemm_large_error_word = 0;
 
@@ -119,10 +123,12 @@ __device__ __forceinline__ unsigned pack2_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
-template <typename OutT, bool GATED>
+template <typename OutT, bool GATED, int BNL>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                   OutT* __restrict__ out, int M, int N, int K, int m_tiles, int n_tiles) {
+  static_assert(!GATED || BNL == 256, "the gated epilogue pairs 128 gate rows with 128 up rows");
+  constexpr int B_BYTES = Tile<BNL>::B_BYTES, STAGE_BYTES = Tile<BNL>::STAGE_BYTES, STAGES = Tile<BNL>::STAGES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -178,7 +184,8 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const int n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
         unsigned char* b = smem + (c % STAGES) * STAGE_BYTES + A_BYTES;
         tma_load_2d(b, &map_w, kb * BK, n0, &full[c % STAGES]);
-        tma_load_2d(b + B_BYTES / 2, &map_w, kb * BK, GATED ? N + n0 : n0 + BNL / 2, &full[c % STAGES]);
+        if (BNL == 256)
+          tma_load_2d(b + B_BYTES / 2, &map_w, kb * BK, GATED ? N + n0 : n0 + 128, &full[c % STAGES]);
       };
       auto load_x = [&](int c) {
         const int t = blockIdx.x + (c / num_kb) * gridDim.x, kb = c % num_kb;
@@ -336,17 +343,18 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, in
              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename OutT, bool GATED>
+template <typename OutT, bool GATED, int BNL>
 int launch_large(const void* x, const void* w, void* out, int M, int N, int K, int sm_count,
                  cudaStream_t st) {
   CUtensorMap mx, mw;
-  if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, GATED ? 2ll * N : (long long)N, K, BNL / 2))
+  if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, GATED ? 2ll * N : (long long)N, K, 128))
     return DIB_LAUNCH_FAILED;
   const int m_tiles = (M + BM - 1) / BM;
   const int n_tiles = (N + (GATED ? BNL / 2 : BNL) - 1) / (GATED ? BNL / 2 : BNL);
   const long long tiles = (long long)m_tiles * n_tiles;
   if (tiles > (1ll << 30)) return DIB_BAD_SIZE;
-  auto kern = gemm_large_kernel<OutT, GATED>;
+  auto kern = gemm_large_kernel<OutT, GATED, BNL>;
+  constexpr size_t SMEM_BYTES = Tile<BNL>::SMEM_BYTES;
   static DeviceOnce attr_set;
   if (!attr_set.done()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) !=
@@ -384,8 +392,15 @@ int dib_gemm_bf16_large(const void* x, const void* w, void* out, int M, int N, i
   if (K < 8 || K % 8 != 0 || sm_count < 1 || (!out_fp32 && N % 8 != 0)) return DIB_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) % 16 != 0)
     return DIB_BAD_ALIGN;
-  return out_fp32 ? launch_large<float, false>(x, w, out, M, N, K, sm_count, st)
-                  : launch_large<__nv_bfloat16, false>(x, w, out, M, N, K, sm_count, st);
+  // tiles of 256 features, unless those would be fewer than the SMs (a function of the
+  // shapes and the SM count; the order in which a row's k is added up is the same for both)
+  const long long tiles256 = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);
+  const bool narrow = tiles256 < sm_count && N > 128;
+  if (out_fp32)
+    return narrow ? launch_large<float, false, 128>(x, w, out, M, N, K, sm_count, st)
+                  : launch_large<float, false, 256>(x, w, out, M, N, K, sm_count, st);
+  return narrow ? launch_large<__nv_bfloat16, false, 128>(x, w, out, M, N, K, sm_count, st)
+                : launch_large<__nv_bfloat16, false, 256>(x, w, out, M, N, K, sm_count, st);
 }
 
 // out[M, I] = silu(x w_gate^T) * (x w_up^T) with w = [w_gate ; w_up] of shape [2I, K]; bf16 in
@@ -396,7 +411,7 @@ int dib_gemm_bf16_large_gated(const void* x, const void* w, void* out, int M, in
   if (K < 8 || K % 8 != 0 || I % 8 != 0 || sm_count < 1) return DIB_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) % 16 != 0)
     return DIB_BAD_ALIGN;
-  return launch_large<__nv_bfloat16, true>(x, w, out, M, I, K, sm_count, st);
+  return launch_large<__nv_bfloat16, true, 256>(x, w, out, M, I, K, sm_count, st);
 }
 
 }  // extern "C"

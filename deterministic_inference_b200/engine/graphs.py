@@ -59,14 +59,14 @@ class _Captured:
         self.uploaded = torch.cuda.Event()
         self.check = None        # debug check of the packed metadata (host array, layout)
 
-    def upload(self, fill) -> object:
+    def upload(self, fill, num_prev: int = 0) -> object:
         """Fill the pinned metadata (``fill(array)``) and copy it to the device.  The
         pinned array is written again only after the copy before has run: a caller may
         issue steps faster than the GPU takes them."""
         self.uploaded.synchronize()
         result = fill(self.host_meta.numpy())
         if self.check is not None:
-            self.check(self.host_meta.numpy(), self.layout)
+            self.check(self.host_meta.numpy(), self.layout, num_prev)
         self.static_meta.copy_(self.host_meta, non_blocking=True)
         self.uploaded.record()
         return result
@@ -159,7 +159,8 @@ class DecodeGraphs:
         if cap is None:
             cap = self._capture(key, shape)
         num_patches = cap.upload(
-            lambda host: fill_packed(host, cap.layout, shape, cache, self.group_list))
+            lambda host: fill_packed(host, cap.layout, shape, cache, self.group_list),
+            0 if prev_tokens is None else int(prev_tokens.shape[0]))
         if num_patches:
             from ..kernels import ops
             ops.patch_token_ids(cap.batch.input_ids, cap.batch.patch_dst, cap.batch.patch_src,
@@ -232,7 +233,8 @@ class StepGraphs:
         else:
             self.graphs.move_to_end(key)
         num_patches = cap.upload(
-            lambda host: fill_packed(host, cap.layout, shape, self.cache, self.group_list))
+            lambda host: fill_packed(host, cap.layout, shape, self.cache, self.group_list),
+            0 if prev_tokens is None else int(prev_tokens.shape[0]))
         if num_patches:
             from ..kernels import ops
             ops.patch_token_ids(cap.batch.input_ids, cap.batch.patch_dst, cap.batch.patch_src,

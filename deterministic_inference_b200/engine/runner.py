@@ -51,6 +51,8 @@ class ModelRunner:
         if self.dtype == torch.bfloat16 and self.device.type == "cuda":
             from ..kernels import gemm_bf16
             gemm_bf16.set_library_products(cfg.library_products)
+            if cfg.large_products is not None:
+                gemm_bf16.set_large_products(cfg.large_products)
         num_pages = cfg.num_pages + 1
         if cfg.gpu_memory_fraction is not None and self.device.type == "cuda":
             free, _ = torch.cuda.mem_get_info(self.device)

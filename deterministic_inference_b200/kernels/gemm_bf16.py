@@ -25,11 +25,25 @@ MAX_ROWS = OWN_KERNEL_ROWS
 GATED = os.environ.get("DIB200_GATED")
 
 
-# Products of more than MAX_ROWS rows: "library" (cuBLAS through torch.mm) or "own" (the
-# package's persistent tcgen05 kernel for many rows, csrc/gemm_bf16_large.cu, which adds up
-# all of k in one pass, so a row's bits do not depend on how many rows there are).
-# DIB200_LARGE_PRODUCTS=own|library, read once.
-LARGE_PRODUCTS = os.environ.get("DIB200_LARGE_PRODUCTS", "library")
+# Products of more than MAX_ROWS rows (``EngineConfig.large_products``; DIB200_LARGE_PRODUCTS
+# in the environment, read once, gives the default):
+#   "library"  cuBLAS through torch.mm, as all of the reference's products;
+#   "own"      the package's persistent tcgen05 kernel for many rows (csrc/gemm_bf16_large.cu),
+#              which adds up all of k in one pass, so a row's bits do not depend on how many
+#              rows (above MAX_ROWS) there are, and which the first step of a new length does
+#              not pay a library's kernel loading for;
+#   "auto"     that kernel where it carries the gate of a gated feed-forward in its epilogue
+#              (one kernel and no [gate | up] tensor instead of two), the library elsewhere:
+#              the fastest replayed prompt step on B200 (0.6B sizes, 2,048 tokens, per layer:
+#              61.7 us against 65.5 all-library and 78.2 all-own).
+LARGE_PRODUCTS = os.environ.get("DIB200_LARGE_PRODUCTS", "auto")
+
+
+def set_large_products(how: str) -> None:
+    global LARGE_PRODUCTS
+    if how not in ("library", "own", "auto"):
+        raise ValueError(f"large_products must be 'library', 'own' or 'auto', got {how!r}")
+    LARGE_PRODUCTS = how
 
 
 def set_library_products(on: bool) -> None:
@@ -183,7 +197,7 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor):
     m, k = x.shape
     i = w_gate_up.shape[0] // 2
     if m > MAX_ROWS:
-        return gated_linear_large(x, w_gate_up) if LARGE_PRODUCTS == "own" else None
+        return gated_linear_large(x, w_gate_up) if LARGE_PRODUCTS in ("own", "auto") else None
     # one CTA per 64 features and no split of k: worth it when those CTAs fill whole waves
     # of the GPU about as well as the split product does (the kernel's own estimate; 0.6B
     # shape, 48 tiles: 1.458 ms per step against 1.435 ms with the split product and the
