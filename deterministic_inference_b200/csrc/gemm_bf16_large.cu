@@ -1,9 +1,14 @@
 // bfloat16 matrix product out[M, N] = X[M, K] * W[N, K]^T for many rows (prompt portions) on
-// the 5th-generation tensor cores: a persistent kernel, one CTA per SM, that walks output
-// tiles of 128 tokens x 256 features.  tcgen05.mma (M 128, N 256, K 16) with the accumulator
+// the 5th-generation tensor cores: persistent kernels, one CTA per SM, that walk output
+// tiles.  Two kernels: one CTA on a tile of 128 tokens x 256 (or 128) features, described
+// first, and a pair of CTAs on a tile of 256 x 256 (tcgen05.mma.cta_group::2, described at
+// its definition), which large products take: each SM then fetches a third less per
+// k-block, and the rate at which L2 feeds the SMs is what bounds these products.
+// tcgen05.mma (M 128, N 256, K 16) with the accumulator
 // in tensor memory, operands staged by TMA (128-byte swizzle) through a ring of four
 // mbarrier-guarded stages of 48 KB, float32 accumulation over all of k in one pass, in the
-// same order for every tile: a row's bits do not depend on how many rows the step has.
+// same order for every tile and tile shape: a row's bits do not depend on how many rows the
+// step has.
 //
 // The accumulator is double-buffered (2 x 256 of the 512 tensor-memory columns): while the
 // four epilogue warps read tile i back (tcgen05.ld: a thread owns one token row), round it
@@ -123,12 +128,71 @@ __device__ __forceinline__ unsigned pack2_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
+// The epilogue of one token row of a tile: `src` is the tensor-memory address of the row's
+// accumulator (this thread's lane, the tile's first column); features n0 .. of `row`.  The
+// tcgen05.ld inside is warp-wide: all 32 lanes call this together.
+template <typename OutT, bool GATED, int BNL>
+__device__ __forceinline__ void store_row(unsigned src, OutT* __restrict__ out, int row, int M, int N, int n0) {
+  if (GATED) {
+    // columns 0..127: gate, 128..255: up, of features n0 .. n0 + 127
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      unsigned g[32], u[32];
+      tc_ld32(src + c * 32, g);
+      tc_ld32(src + 128 + c * 32, u);
+      tc_wait_ld();
+      if (row < M) {
+        OutT* dst = out + (size_t)row * N + n0 + c * 32;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float y[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            y[e] = silu_gate<__nv_bfloat16>(round_to<__nv_bfloat16>(__uint_as_float(g[q * 8 + e])),
+                                            round_to<__nv_bfloat16>(__uint_as_float(u[q * 8 + e])));
+          if (n0 + c * 32 + q * 8 + 8 <= N) {
+            *reinterpret_cast<uint4*>(dst + q * 8) =
+                make_uint4(pack2_bf16(y[0], y[1]), pack2_bf16(y[2], y[3]), pack2_bf16(y[4], y[5]),
+                           pack2_bf16(y[6], y[7]));
+          } else {
+            for (int e = 0; e < 8; ++e)
+              if (n0 + c * 32 + q * 8 + e < N) Elem<OutT>::store(dst + q * 8 + e, y[e]);
+          }
+        }
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int c = 0; c < BNL / 32; ++c) {
+      unsigned v[32];
+      tc_ld32(src + c * 32, v);
+      tc_wait_ld();
+      if (row < M) {
+        OutT* dst = out + (size_t)row * N + n0 + c * 32;
+        if (sizeof(OutT) == 2 && n0 + c * 32 + 32 <= N) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst) + q * 8) = make_uint4(
+                pack2_bf16(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])),
+                pack2_bf16(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])),
+                pack2_bf16(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])),
+                pack2_bf16(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7])));
+        } else {
+          for (int e = 0; e < 32; ++e)
+            if (n0 + c * 32 + e < N) Elem<OutT>::store(dst + e, __uint_as_float(v[e]));
+        }
+      }
+    }
+  }
+}
+
 template <typename OutT, bool GATED, int BNL>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                   OutT* __restrict__ out, int M, int N, int K, int m_tiles, int n_tiles) {
   static_assert(!GATED || BNL == 256, "the gated epilogue pairs 128 gate rows with 128 up rows");
-  constexpr int B_BYTES = Tile<BNL>::B_BYTES, STAGE_BYTES = Tile<BNL>::STAGE_BYTES, STAGES = Tile<BNL>::STAGES;
+  using TL = Tile<BNL>;
+  constexpr int B_BYTES = TL::B_BYTES, STAGE_BYTES = TL::STAGE_BYTES, STAGES = TL::STAGES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -246,59 +310,7 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       got = __all_sync(0xffffffffu, got);     // tcgen05.ld below is warp-wide
       if (!got) { ok = false; break; }
       tc_fence_after();
-      const int row = m0 + quarter * 32 + lane;
-      const unsigned src = tmem + buf * BNL + lane_base;
-      if (GATED) {
-        // columns 0..127: gate, 128..255: up, of features n0 .. n0 + 127
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          unsigned g[32], u[32];
-          tc_ld32(src + c * 32, g);
-          tc_ld32(src + 128 + c * 32, u);
-          tc_wait_ld();
-          if (row < M) {
-            OutT* dst = out + (size_t)row * N + n0 + c * 32;
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              float y[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e)
-                y[e] = silu_gate<__nv_bfloat16>(round_to<__nv_bfloat16>(__uint_as_float(g[q * 8 + e])),
-                                                round_to<__nv_bfloat16>(__uint_as_float(u[q * 8 + e])));
-              if (n0 + c * 32 + q * 8 + 8 <= N) {
-                *reinterpret_cast<uint4*>(dst + q * 8) =
-                    make_uint4(pack2_bf16(y[0], y[1]), pack2_bf16(y[2], y[3]), pack2_bf16(y[4], y[5]),
-                               pack2_bf16(y[6], y[7]));
-              } else {
-                for (int e = 0; e < 8; ++e)
-                  if (n0 + c * 32 + q * 8 + e < N) Elem<OutT>::store(dst + q * 8 + e, y[e]);
-              }
-            }
-          }
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BNL / 32; ++c) {
-          unsigned v[32];
-          tc_ld32(src + c * 32, v);
-          tc_wait_ld();
-          if (row < M) {
-            OutT* dst = out + (size_t)row * N + n0 + c * 32;
-            if (sizeof(OutT) == 2 && n0 + c * 32 + 32 <= N) {
-#pragma unroll
-              for (int q = 0; q < 4; ++q)
-                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst) + q * 8) = make_uint4(
-                    pack2_bf16(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])),
-                    pack2_bf16(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])),
-                    pack2_bf16(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])),
-                    pack2_bf16(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7])));
-            } else {
-              for (int e = 0; e < 32; ++e)
-                if (n0 + c * 32 + e < N) Elem<OutT>::store(dst + e, __uint_as_float(v[e]));
-            }
-          }
-        }
-      }
+      store_row<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, out, m0 + quarter * 32 + lane, M, N, n0);
       tc_fence_before();
       mbar_arrive(&acc_empty[buf]);
     }
@@ -308,6 +320,214 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
+  }
+}
+
+// ---------------------------------------------------------------- two CTAs on one tile
+// The same product with a pair of CTAs (a cluster of two, on the two SMs of a TPC) on a tile
+// of 256 tokens x BNL features: tcgen05.mma.cta_group::2 (M 256, N BNL, K 16), issued by the
+// pair's first CTA alone, reads each CTA's own 128 token rows and HALF of the weight rows
+// from each CTA's shared memory and accumulates each CTA's 128 x BNL tile in that CTA's
+// tensor memory.  A CTA so fetches 16 KB of tokens and 16 KB (BNL 256) of weights per k-block
+// instead of 16 + 32 KB: the rate at which L2 feeds the SMs bounds these products, not
+// the tensor cores.  GATED: the first CTA fetches the 128 gate rows, the second the 128 up rows.
+//
+// Protocol, per stage s of the ring (same offsets in both CTAs):
+//   full[s]    of the FIRST CTA counts the bytes of both CTAs' loads (its producer expects
+//              them all; the second CTA's copies signal it through cp.async.bulk.tensor
+//              .cta_group::2);
+//   empty[s]   in each CTA, signalled by the first CTA's tcgen05.commit (multicast to both);
+//   acc_full[b] likewise; acc_empty[b] of the first CTA takes one arrival per epilogue warp
+//              of both CTAs (the second CTA's arrive remotely).
+// The pair synchronises as a cluster after the set-up and before tensor memory is freed.
+__device__ __forceinline__ unsigned cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// the address, in the cluster's shared window, of `local` in the CTA of rank `rank`
+__device__ __forceinline__ unsigned cluster_addr(unsigned local, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_address) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_address) : "memory");
+}
+// a TMA load into this CTA's shared memory whose bytes are counted by the barrier at
+// `bar_cluster_address`, which may be the other CTA's of the pair
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1,
+                                                 unsigned bar_cluster_address) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<unsigned long long>(map)), "r"(bar_cluster_address),
+      "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(unsigned long long* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"((unsigned short)3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(unsigned tmem_d, unsigned long long desc_a,
+                                            unsigned long long desc_b, unsigned idesc, unsigned accum) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accum)
+      : "memory");
+}
+
+template <int BNL> struct PairTile {
+  static constexpr int B_BYTES = (BNL / 2) * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // per CTA
+  static constexpr int STAGES = 6;
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+};
+
+template <typename OutT, bool GATED, int BNL>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                 OutT* __restrict__ out, int M, int N, int K, int m_tiles, int n_tiles) {
+  static_assert(!GATED || BNL == 256, "the gated epilogue pairs 128 gate rows with 128 up rows");
+  using TL = PairTile<BNL>;
+  constexpr int STAGE_BYTES = TL::STAGE_BYTES, STAGES = TL::STAGES;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
+  unsigned long long* empty = full + STAGES;
+  unsigned long long* acc_full = empty + STAGES;     // [2]
+  unsigned long long* acc_empty = acc_full + 2;      // [2]
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(acc_empty + 2);
+
+  if (threadIdx.x == 0) {
+    prefetch_tensormap(&map_x);
+    prefetch_tensormap(&map_w);
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const unsigned rank = cluster_rank();              // 0: the CTA that issues the products
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+  const int num_kb = (K + BK - 1) / BK;
+  const int tiles = m_tiles * n_tiles;               // tiles of 256 tokens x BNL features
+  if (warp == 0 && lane == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&acc_full[b], 1);
+      mbar_init(&acc_empty[b], 8);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"(512u));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();       // both CTAs' barriers and tensor memory exist before either is used
+  tc_fence_after();
+  const unsigned tmem = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- TMA producer of this CTA's halves.  Load number c is k-block c % num_kb of the
+      // pair's tile number c / num_kb and goes to stage c % STAGES.
+      const int my_tiles = tiles > pair ? (tiles - pair + pairs - 1) / pairs : 0;
+      const int total = my_tiles * num_kb;
+      const unsigned full0 = cluster_addr(smem_u32(full), 0);   // the first CTA's full[0], as a cluster address
+      auto load_w = [&](int c) {
+        const int t = pair + (c / num_kb) * pairs, kb = c % num_kb;
+        const int n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
+        const int row = GATED ? (rank ? N + n0 : n0) : n0 + (int)rank * (BNL / 2);
+        tma_load_2d_pair(smem + (c % STAGES) * STAGE_BYTES + A_BYTES, &map_w, kb * BK, row, full0 + (c % STAGES) * 8);
+      };
+      auto load_x = [&](int c) {
+        const int t = pair + (c / num_kb) * pairs, kb = c % num_kb;
+        tma_load_2d_pair(smem + (c % STAGES) * STAGE_BYTES, &map_x, kb * BK,
+                         (t % m_tiles) * 2 * BM + (int)rank * BM, full0 + (c % STAGES) * 8);
+      };
+      const int pre = total < STAGES ? total : STAGES;
+      for (int c = 0; c < pre; ++c) {
+        if (rank == 0) mbar_expect_tx(&full[c], 2 * STAGE_BYTES);
+        load_w(c);
+      }
+      pdl_wait();
+      for (int c = 0; c < pre; ++c) load_x(c);
+      for (int c = pre; c < total && ok; ++c) {
+        ok = mbar_wait(&empty[c % STAGES], ((c / STAGES) - 1) & 1);
+        if (!ok) break;
+        if (rank == 0) mbar_expect_tx(&full[c % STAGES], 2 * STAGE_BYTES);
+        load_w(c);
+        load_x(c);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // ---- MMA issuer of the pair
+      constexpr unsigned idesc = make_idesc(2 * BM, BNL);
+      int count = 0, local = 0;
+      for (int t = pair; t < tiles && ok; t += pairs, ++local) {
+        const int buf = local & 1;
+        if (local >= 2) {     // both CTAs' epilogues must have read this buffer's earlier tile
+          ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1);
+          if (!ok) break;
+          tc_fence_after();
+        }
+        for (int kb = 0; kb < num_kb && ok; ++kb, ++count) {
+          const int s = count % STAGES;
+          ok = mbar_wait(&full[s], (count / STAGES) & 1);
+          if (!ok) break;
+          tc_fence_after();
+          const unsigned a = smem_u32(smem + s * STAGE_BYTES), b = a + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            tc_mma_pair(tmem + buf * BNL, smem_desc_sw128(a + k * UMMA_K * 2),
+                        smem_desc_sw128(b + k * UMMA_K * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          tc_commit_pair(&empty[s]);
+        }
+        if (ok) tc_commit_pair(&acc_full[buf]);
+      }
+    }
+  } else {
+    // ---- epilogue of this CTA's 128 token rows
+    pdl_wait();
+    const int quarter = warp & 3;
+    const unsigned lane_base = (unsigned)(quarter * 32) << 16;
+    const unsigned acc_empty0 = cluster_addr(smem_u32(acc_empty), 0);   // the first CTA's acc_empty[0]
+    int local = 0;
+    for (int t = pair; t < tiles; t += pairs, ++local) {
+      const int buf = local & 1;
+      const int m0 = (t % m_tiles) * 2 * BM + (int)rank * BM, n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
+      bool got = ok && mbar_wait(&acc_full[buf], (local >> 1) & 1);
+      got = __all_sync(0xffffffffu, got);     // tcgen05.ld below is warp-wide
+      if (!got) { ok = false; break; }
+      tc_fence_after();
+      store_row<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, out, m0 + quarter * 32 + lane, M, N, n0);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty0 + buf * 8);
+    }
+  }
+  if (!ok) atomicExch(&dib_gemm_large_error_word, 1);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();       // the other CTA's products and arrivals may still touch this one
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u));
   }
 }
 
@@ -369,9 +589,68 @@ int launch_large(const void* x, const void* w, void* out, int M, int N, int K, i
   return DIB_OK;
 }
 
+template <typename OutT, bool GATED, int BNL>
+int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, int sm_count,
+                cudaStream_t st) {
+  CUtensorMap mx, mw;
+  if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, GATED ? 2ll * N : (long long)N, K, BNL / 2))
+    return DIB_LAUNCH_FAILED;
+  const int m_tiles = (M + 2 * BM - 1) / (2 * BM);
+  const int n_tiles = (N + (GATED ? BNL / 2 : BNL) - 1) / (GATED ? BNL / 2 : BNL);
+  const long long tiles = (long long)m_tiles * n_tiles;
+  if (tiles > (1ll << 30) || sm_count < 2) return DIB_BAD_SIZE;
+  auto kern = gemm_pair_kernel<OutT, GATED, BNL>;
+  constexpr size_t SMEM_BYTES = PairTile<BNL>::SMEM_BYTES;
+  static DeviceOnce attr_set;
+  if (!attr_set.done()) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) !=
+        cudaSuccess)
+      return DIB_LAUNCH_FAILED;
+    attr_set.mark();
+  }
+  const int pairs = (int)(tiles < sm_count / 2 ? tiles : sm_count / 2);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = dib_pdl_enabled() ? 2 : 1;
+  cudaLaunchKernelEx(&cfg, kern, mx, mw, (OutT*)out, M, N, K, m_tiles, n_tiles);
+  DIB_CHECK_LAUNCH();
+  return DIB_OK;
+}
+
+// Tile shape forced for measurements and tests (-1: the choice of tile_shape): 0: 128 x 128,
+// 1: 128 x 256 by one CTA; 2: 256 x 256 by a pair of CTAs.
+int& forced_shape() {
+  static int v = -1;
+  return v;
+}
+// A function of the sizes and the SM count alone (the order in which a row's k is added up
+// is the same for all three, so the choice never changes a bit of the result).  The pair of
+// CTAs where its tiles of 256 x 256 keep two thirds of the SMs busy or more; else tiles of
+// 128 x 256, or of 128 x 128 where those would be fewer than the SMs.
+int tile_shape(int M, int n_rows, int sm_count) {
+  if (forced_shape() >= 0) return forced_shape();
+  const long long pair_tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((n_rows + 255) / 256);
+  if (sm_count >= 2 && 3 * pair_tiles >= sm_count) return 2;
+  const long long tiles256 = (long long)((M + BM - 1) / BM) * ((n_rows + 255) / 256);
+  return tiles256 < sm_count && n_rows > 128 ? 0 : 1;
+}
+
 }  // namespace
 
 extern "C" {
+
+void dib_gemm_bf16_large_force_shape(int shape) { forced_shape() = shape; }
 
 int dib_gemm_bf16_large_status() {
   int v = 0;
@@ -392,15 +671,15 @@ int dib_gemm_bf16_large(const void* x, const void* w, void* out, int M, int N, i
   if (K < 8 || K % 8 != 0 || sm_count < 1 || (!out_fp32 && N % 8 != 0)) return DIB_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) % 16 != 0)
     return DIB_BAD_ALIGN;
-  // tiles of 256 features, unless those would be fewer than the SMs (a function of the
-  // shapes and the SM count; the order in which a row's k is added up is the same for both)
-  const long long tiles256 = (long long)((M + BM - 1) / BM) * ((N + 255) / 256);
-  const bool narrow = tiles256 < sm_count && N > 128;
-  if (out_fp32)
-    return narrow ? launch_large<float, false, 128>(x, w, out, M, N, K, sm_count, st)
-                  : launch_large<float, false, 256>(x, w, out, M, N, K, sm_count, st);
-  return narrow ? launch_large<__nv_bfloat16, false, 128>(x, w, out, M, N, K, sm_count, st)
-                : launch_large<__nv_bfloat16, false, 256>(x, w, out, M, N, K, sm_count, st);
+  const int shape = tile_shape(M, N, sm_count);
+  if (out_fp32) {
+    if (shape == 2) return launch_pair<float, false, 256>(x, w, out, M, N, K, sm_count, st);
+    if (shape == 0) return launch_large<float, false, 128>(x, w, out, M, N, K, sm_count, st);
+    return launch_large<float, false, 256>(x, w, out, M, N, K, sm_count, st);
+  }
+  if (shape == 2) return launch_pair<__nv_bfloat16, false, 256>(x, w, out, M, N, K, sm_count, st);
+  if (shape == 0) return launch_large<__nv_bfloat16, false, 128>(x, w, out, M, N, K, sm_count, st);
+  return launch_large<__nv_bfloat16, false, 256>(x, w, out, M, N, K, sm_count, st);
 }
 
 // out[M, I] = silu(x w_gate^T) * (x w_up^T) with w = [w_gate ; w_up] of shape [2I, K]; bf16 in
@@ -411,7 +690,9 @@ int dib_gemm_bf16_large_gated(const void* x, const void* w, void* out, int M, in
   if (K < 8 || K % 8 != 0 || I % 8 != 0 || sm_count < 1) return DIB_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) % 16 != 0)
     return DIB_BAD_ALIGN;
-  return launch_large<__nv_bfloat16, true, 256>(x, w, out, M, I, K, sm_count, st);
+  return tile_shape(M, 2 * I, sm_count) == 2
+             ? launch_pair<__nv_bfloat16, true, 256>(x, w, out, M, I, K, sm_count, st)
+             : launch_large<__nv_bfloat16, true, 256>(x, w, out, M, I, K, sm_count, st);
 }
 
 }  // extern "C"

@@ -84,6 +84,16 @@ def gated_linear_large(x: torch.Tensor, w_gate_up: torch.Tensor):
     ops._check(st, "gated_linear(bfloat16, many rows)", f"M={m} I={i} K={k}")
     return out
 
+
+
+def force_large_shape(shape: int) -> None:
+    """Measurement and test switch of the many-rows kernel: tiles of 128 x 128 (0) or 128 x 256
+    (1) by one CTA, or of 256 x 256 by a pair of CTAs (2), whatever the sizes; -1: the kernel
+    library's own choice.  The result's bits are the same with all three."""
+    from . import ops
+    ops._lib("gemm_bf16_large").dib_gemm_bf16_large_force_shape(c_int(shape))
+
+
 _sm_count: dict = {}
 
 

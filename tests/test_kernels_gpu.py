@@ -903,16 +903,24 @@ def test_product_that_merges_attention_splits_while_it_loads_gives_the_bits_of_t
 @pytest.mark.parametrize("m,n,k", [(129, 1024, 1024), (2048, 4096, 1024), (300, 6144, 1024), (1000, 1000, 512),
                                    (257, 264, 72), (130, 8, 200), (4096, 1024, 3072), (77, 512, 64)])
 def test_linear_bf16_many_rows_own_kernel(m, n, k):
-    """The package's persistent tcgen05 product for many rows (tiles of 128 tokens x 256
-    features, all of k in one pass) against a float32 product: row counts, widths and depths
-    that are no multiples of the tile, several tiles per CTA; a row's bits are the same in a
-    product of other row counts."""
+    """The package's persistent tcgen05 product for many rows (all of k in one pass) against
+    a float32 product: row counts, widths and depths that are no multiples of the tile,
+    several tiles per CTA; a row's bits are the same in a product of other row counts, and
+    with each of the three tile shapes (128 x 128, 128 x 256, 256 x 256 by a pair of CTAs)."""
     from deterministic_inference_b200.kernels import gemm_bf16
     torch.manual_seed(41)
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (0.05 * torch.randn(n, k, device="cuda")).to(torch.bfloat16)
     want = x.float() @ w.float().T
     got = gemm_bf16.linear_large(x, w, torch.bfloat16)
+    try:
+        for shape in (0, 1, 2):
+            gemm_bf16.force_large_shape(shape)
+            assert torch.equal(gemm_bf16.linear_large(x, w, torch.bfloat16), got), shape
+            if shape == 2:
+                assert torch.equal(gemm_bf16.linear_large(x, w, torch.float32).to(torch.bfloat16), got)
+    finally:
+        gemm_bf16.force_large_shape(-1)
     assert got is not None and got.shape == (m, n) and got.dtype == torch.bfloat16
     torch.testing.assert_close(got.float(), want, atol=2e-2 * float(want.abs().max()), rtol=2e-2)
     got32 = gemm_bf16.linear_large(x, w, torch.float32)
@@ -925,7 +933,7 @@ def test_linear_bf16_many_rows_own_kernel(m, n, k):
     assert ops().kernel_status().get("gemm_bf16_large", 0) == 0
 
 
-@pytest.mark.parametrize("m,i,k", [(2048, 3072, 1024), (129, 200, 72), (700, 1536, 512)])
+@pytest.mark.parametrize("m,i,k", [(2048, 3072, 1024), (129, 200, 72), (700, 1536, 512), (4100, 4096, 264)])
 def test_gated_product_many_rows_gives_the_bits_of_product_and_gate(m, i, k):
     """The many-rows product with the gate in its epilogue against the same product followed
     by the gate kernel: the same bits."""
@@ -936,6 +944,13 @@ def test_gated_product_many_rows_gives_the_bits_of_product_and_gate(m, i, k):
     fused = gemm_bf16.gated_linear_large(x, w)
     two = ops().silu_mul(gemm_bf16.linear_large(x, w, torch.bfloat16))
     assert fused is not None and torch.equal(fused, two)
+    try:
+        for shape in (1, 2):      # one CTA on 128 tokens; a pair of CTAs on 256
+            gemm_bf16.force_large_shape(shape)
+            assert torch.equal(gemm_bf16.gated_linear_large(x, w), fused), shape
+    finally:
+        gemm_bf16.force_large_shape(-1)
+    assert ops().kernel_status().get("gemm_bf16_large", 0) == 0
     y = (x.float() @ w.float().T).to(torch.bfloat16).float()
     want = y[:, :i] * torch.sigmoid(y[:, :i]) * y[:, i:]
     torch.testing.assert_close(fused.float(), want, atol=2e-2 * float(want.abs().max()), rtol=3e-2)
