@@ -34,7 +34,7 @@ namespace {
 
 constexpr int TC_M = 128, TC_N = 128, TC_D = 128, TC_THREADS = 320;
 constexpr int TMA_WARP = 8, MMA_WARP = 9;
-constexpr int PAIR_THREADS = 352, PAIR_V_WARP = 10, KS = 3;   // the pair kernel fetches keys (warp 8) and values apart
+constexpr int PAIR_THREADS = 352, PAIR_V_WARP = 10;   // the pair kernel fetches keys (warp 8) and values apart
 constexpr int TILE_BYTES = 128 * 128 * 2;   // a [128 x 128] bf16 tile (two 64-column halves)
 constexpr int HALF_BYTES = 128 * 64 * 2;
 
@@ -453,22 +453,11 @@ __device__ __forceinline__ void tc_mma_ts(unsigned tmem_d, unsigned tmem_a, unsi
       : "memory");
 }
 
-// 2^x for x <= ~8 on the FMA and integer pipes (the special-function unit makes 16
-// exponentials per clock and SM, which would bound the softmax of a tile): x = n + f
-// with n the nearest integer, 2^f by a cubic (relative error 1e-4, below the bfloat16
-// step of the probabilities), 2^n by adding n to the exponent bits.
-__device__ __forceinline__ float exp2_fma(float x) {
-  x = fmaxf(x, -125.0f);
-  const float xf = x + 12582912.0f;          // 1.5 * 2^23: the sum's low mantissa bits hold n
-  const float f = x - (xf - 12582912.0f);    // in [-0.5, 0.5]
-  float p = fmaf(f, 0.05500893f, 0.24221095f);
-  p = fmaf(p, f, 0.6932829f);
-  p = fmaf(p, f, 1.0f);
-  return __int_as_float(__float_as_int(p) + (__float_as_int(xf) << 23));
-}
-
-// The same for two values at once with the packed float32 instructions (each lane's result
-// is that of exp2_fma: the packed operations round as the single ones do).
+// 2^x for x <= ~8 on the FMA and integer pipes, two values at once with the packed float32
+// instructions (the special-function unit makes 16 exponentials per clock and SM, which
+// would bound the softmax of a tile): x = n + f with n the nearest integer, 2^f by a cubic
+// (relative error 1e-4, below the bfloat16 step of the probabilities), 2^n by adding n to
+// the exponent bits.  The packed operations round each half as the single ones do.
 __device__ __forceinline__ float2 exp2_fma2(float2 x) {
   x.x = fmaxf(x.x, -125.0f);
   x.y = fmaxf(x.y, -125.0f);
@@ -488,8 +477,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return d;
 }
 
-__device__ long long dib_dbg[64];
-__device__ int dib_dbg_y = 3;
 __global__ void __launch_bounds__(PAIR_THREADS, 1)
 extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
                                 const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
@@ -506,21 +493,17 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   unsigned char* sQ = smem;                       // [2] x 32 KB
-  // Keys in KS = 3 stages of 32 KB, values in 2: the keys of key tile i + 1 are wanted one
-  // softmax earlier than its values (the scores of i + 1 are computed during the softmax of
-  // i), and with two stages a tile running alone waited some 500 cycles a key tile for them.
-  unsigned char* sK = smem + 2 * TILE_BYTES;
-  unsigned char* sV = smem + (2 + KS) * TILE_BYTES;
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + (4 + KS) * TILE_BYTES);
-  unsigned long long* k_full = bars;              // [KS] the keys of a key tile are in shared memory
-  unsigned long long* k_empty = bars + KS;        // [KS] both score products have read them
-  unsigned long long* v_full = bars + 2 * KS;     // [2] the values of a key tile are in shared memory
-  unsigned long long* v_empty = bars + 2 * KS + 2;   // [2] both output products have read them
-  unsigned long long* s_full = bars + 2 * KS + 4;    // [2: A, B] the tile's scores are in tensor memory
-  unsigned long long* p_full = bars + 2 * KS + 6;    // [2] its probabilities are, and O is rescaled (128)
-  unsigned long long* o_final = bars + 2 * KS + 8;   // [2] its last product has completed
-  unsigned long long* pv_done = bars + 2 * KS + 10;  // an output product of the tile that runs alone has completed
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 2 * KS + 11);
+  unsigned char* sKV = smem + 2 * TILE_BYTES;     // 2 stages x (K 32 KB + V 32 KB)
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(smem + 6 * TILE_BYTES);
+  unsigned long long* k_full = bars;              // [2] the keys of a key tile are in shared memory
+  unsigned long long* k_empty = bars + 2;         // [2] both score products have read them
+  unsigned long long* v_full = bars + 4;          // [2] the values of a key tile are in shared memory
+  unsigned long long* v_empty = bars + 6;         // [2] both output products have read them
+  unsigned long long* s_full = bars + 8;          // [2: A, B] the tile's scores are in tensor memory
+  unsigned long long* p_full = bars + 10;         // [2] its probabilities are, and O is rescaled (128)
+  unsigned long long* o_final = bars + 12;        // [2] its last product has completed
+  unsigned long long* pv_done = bars + 14;        // an output product of the tile that runs alone has completed
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 15);
 
   const int tile = gridDim.y - 1 - blockIdx.y, kvh = blockIdx.x;
   const int G = Hq / Hkv;
@@ -576,14 +559,15 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   // of Q below.  Lane l takes half (64 dimensions) l & 1 of page l >> 1 of a key tile.
   const int tile_ops = TC_N / page_size * 2;
   auto fetch = [&](int kv, int i, int page) {
-    const int st = kv ? (i & 1) : i % KS;
+    const int st = i & 1;
     unsigned long long* full = kv ? &v_full[st] : &k_full[st];
     if (lane == 0) mbar_expect_tx(full, TILE_BYTES);
     __syncwarp();
     if (lane < tile_ops) {
       const int pi = lane >> 1, half = lane & 1;
       const int row0 = (((page * 2 + kv) * Hkv) + kvh) * page_size;
-      unsigned char* dst = (kv ? sV : sK) + st * TILE_BYTES + half * HALF_BYTES + pi * page_size * 128;
+      unsigned char* dst = sKV + st * 2 * TILE_BYTES + kv * TILE_BYTES + half * HALF_BYTES +
+                           pi * page_size * 128;
       tma_load_2d(dst, &map, half * 64, row0, full);
     }
   };
@@ -594,17 +578,16 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   if (warp == TMA_WARP || warp == PAIR_V_WARP) {
     const int kv = warp == PAIR_V_WARP;
     if (lane == 0) {
-      for (int i = 0; i < (kv ? 2 : KS); ++i) {
+      for (int i = 0; i < 2; ++i) {
         mbar_init(kv ? &v_full[i] : &k_full[i], 1);
         mbar_init(kv ? &v_empty[i] : &k_empty[i], 1);
       }
       mbar_fence_init();
     }
     __syncwarp();
-    const int p0 = page_of(0), p1 = page_of(1), p2 = page_of(2);
+    const int p0 = page_of(0), p1 = page_of(1);
     fetch(kv, 0, p0);
     if (ntiles > 1) fetch(kv, 1, p1);
-    if (!kv && ntiles > 2) fetch(kv, 2, p2);
   }
   if (warp == MMA_WARP) {
     if (lane == 0) {
@@ -658,9 +641,9 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
     // before the values, and neither waits for the other's stage.  The page ids of the
     // next key tile are read while the warp waits for its stage.
     const int kv = warp == PAIR_V_WARP;
-    for (int i = kv ? 2 : KS; i < ntiles && ok; ++i) {
+    for (int i = 2; i < ntiles && ok; ++i) {
       const int page = page_of(i);
-      ok = kv ? mbar_wait(&v_empty[i & 1], ((i >> 1) - 1) & 1) : mbar_wait(&k_empty[i % KS], ((i / KS) - 1) & 1);
+      ok = mbar_wait(kv ? &v_empty[i & 1] : &k_empty[i & 1], ((i >> 1) - 1) & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       fetch(kv, i, page);
@@ -678,12 +661,14 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
 #pragma unroll
         for (int ks = 0; ks < TC_D / 16; ++ks)
           q_desc[x][ks] = desc_k_major(smem_u32(sQ + x * TILE_BYTES) + (ks >> 2) * HALF_BYTES + (ks & 3) * 32);
-      unsigned long long v_desc[2];
+      unsigned long long k_desc[2], v_desc[2];
 #pragma unroll
-      for (int st = 0; st < 2; ++st) v_desc[st] = desc_mn_major(smem_u32(sV + st * TILE_BYTES), HALF_BYTES);
-      const unsigned long long k_desc0 = desc_k_major(smem_u32(sK));
+      for (int st = 0; st < 2; ++st) {
+        k_desc[st] = desc_k_major(smem_u32(sKV + st * 2 * TILE_BYTES));
+        v_desc[st] = desc_mn_major(smem_u32(sKV + st * 2 * TILE_BYTES + TILE_BYTES), HALF_BYTES);
+      }
       auto issue_s_to = [&](int x, int buf, int i) {     // scores of tile x, key tile i -> columns of buf
-        const unsigned long long kd = k_desc0 + (unsigned long long)(((i % KS) * TILE_BYTES) >> 4);
+        const unsigned long long kd = k_desc[i & 1];
 #pragma unroll
         for (int ks = 0; ks < TC_D / 16; ++ks)
           tc_mma(tmem + buf * 128, x ? q_desc[1][ks] : q_desc[0][ks],
@@ -703,18 +688,26 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
         tc_commit(&k_empty[0]);
       }
       const int paired_end = min(ntiles, solo_from);
+      // Keys and values come by TMA and are read by the tensor core, both through the async
+      // proxy: their barrier orders them and no tcgen05 fence follows it.  They have long
+      // arrived as a rule, so they are looked at before the waits for the probabilities,
+      // off the path from a tile's probabilities to its next scores.
       for (int i = 0; i < paired_end && ok; ++i) {
+        if (have_v < i) {
+          ok = mbar_wait(&v_full[i & 1], (i >> 1) & 1);
+          have_v = i;
+        }
+        if (ok && i + 1 < ntiles && have_k < i + 1) {
+          ok = mbar_wait(&k_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
+          have_k = i + 1;
+        }
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
+          if (!ok) break;
           if (active(x, i)) {
             ok = mbar_wait(&p_full[x], uses[x] & 1);
             if (!ok) break;
             ++uses[x];
-            if (have_v < i) {
-              ok = mbar_wait(&v_full[i & 1], (i >> 1) & 1);
-              if (!ok) break;
-              have_v = i;
-            }
             tc_fence_after();
             const unsigned long long vd = v_desc[i & 1];
             const bool first = j0 + i == jf[x];
@@ -726,71 +719,44 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
             if (j0 + i == jl[x]) tc_commit(&o_final[x]);
           }
           if (x == 1) tc_commit(&v_empty[i & 1]);   // both output products of key tile i have been issued
-          if (i + 1 < ntiles && active(x, i + 1)) {
-            if (have_k < i + 1) {
-              ok = mbar_wait(&k_full[(i + 1) % KS], ((i + 1) / KS) & 1);
-              if (!ok) break;
-              have_k = i + 1;
-              tc_fence_after();
-            }
-            issue_s(x, i + 1);
-          }
-          if (x == 1 && i + 1 < ntiles) tc_commit(&k_empty[(i + 1) % KS]);   // both score products of key tile i+1
+          if (i + 1 < ntiles && active(x, i + 1)) issue_s(x, i + 1);
+          if (x == 1 && i + 1 < ntiles) tc_commit(&k_empty[(i + 1) & 1]);   // both score products of key tile i+1
         }
       }
       // ---- one tile alone: its scores of key tile i are in buffer (i - solo_from) & 1
       // (0: its own columns, 1: the finished tile's); those of i + 1 go to the other one
       // before this loop waits for the probabilities of i.
-      const bool mdbg = blockIdx.x == 0 && blockIdx.y == dib_dbg_y;
       for (int i = solo_from; i < ntiles && ok; ++i) {
         const int x = solo_x;
         const int buf = ((i - solo_from) & 1) ? 1 - x : x;
-        long long t0 = clock64(), t1 = t0, t2 = t0;
         if (i + 1 < ntiles) {
           if (have_k < i + 1) {
-            ok = mbar_wait(&k_full[(i + 1) % KS], ((i + 1) / KS) & 1);
+            ok = mbar_wait(&k_full[(i + 1) & 1], ((i + 1) >> 1) & 1);
             if (!ok) break;
             have_k = i + 1;
-            tc_fence_after();
           }
-          t1 = clock64();
           issue_s_to(x, 1 - buf, i + 1);
-          tc_commit(&k_empty[(i + 1) % KS]);
-          t2 = clock64();
+          tc_commit(&k_empty[(i + 1) & 1]);
         }
-        ok = mbar_wait(&p_full[buf], uses[buf] & 1);
-        if (!ok) break;
-        long long t3 = clock64();
-        ++uses[buf];
         if (have_v < i) {
           ok = mbar_wait(&v_full[i & 1], (i >> 1) & 1);
           if (!ok) break;
           have_v = i;
         }
-        long long t4 = clock64();
+        ok = mbar_wait(&p_full[buf], uses[buf] & 1);
+        if (!ok) break;
+        ++uses[buf];
         tc_fence_after();
         const unsigned long long vd = v_desc[i & 1];
         const bool first = j0 + i == jf[x];
-        long long ts[11];
 #pragma unroll
-        for (int ks = 0; ks < TC_N / 16; ++ks) {
+        for (int ks = 0; ks < TC_N / 16; ++ks)
           tc_mma_ts(tmem + 256 + x * 128, tmem + buf * 128 + ks * 8,
                     vd + (unsigned long long)((ks * 16 * 128) >> 4), idesc_o,
                     (!first || ks > 0) ? 1u : 0u);
-          ts[ks] = clock64();
-        }
         tc_commit(&v_empty[i & 1]);
-        ts[8] = clock64();
         tc_commit(pv_done);
-        ts[9] = clock64();
         if (i == ntiles - 1) tc_commit(&o_final[x]);
-        long long t5 = clock64();
-        if (mdbg && i + 1 < ntiles) {
-          for (int j = 0; j < 10; ++j) dib_dbg[40 + j] += ts[j] - (j ? ts[j - 1] : t4);
-        }
-        if (mdbg && i + 1 < ntiles) {
-          dib_dbg[32] += t1 - t0; dib_dbg[33] += t2 - t1; dib_dbg[34] += t3 - t2; dib_dbg[35] += t4 - t3; dib_dbg[36] += t5 - t4; dib_dbg[37] += 1;
-        }
       }
     }
   } else {
@@ -813,9 +779,6 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
       const bool borrowed = i >= my_solo && ((i - my_solo) & 1);
       const int buf = borrowed ? 1 - x : x;
       const unsigned tmem_s = tmem + lane_base + buf * 128;
-      const bool dbg = blockIdx.x == 0 && blockIdx.y == dib_dbg_y && (threadIdx.x & 127) == 0;
-      const int db = (x == solo_x && i >= my_solo) ? 16 : 0;   // solo iterations apart
-      long long c0 = clock64();
       ok = mbar_wait(&s_full[buf], (borrowed ? uses_other : uses_own) & 1);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
@@ -826,9 +789,7 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
       unsigned v[4][32];
 #pragma unroll
       for (int c = 0; c < 4; ++c) tc_ld32(tmem_s + c * 32, v[c]);
-      long long c1 = clock64();
       tc_wait_ld();
-      long long c2 = clock64();
       // Four independent chains for the maximum and for the sum (a thread has few warps
       // beside it to hide the latency of one long chain).  Tiles without a masked key,
       // nearly all of them, take a path without the per-key tests.
@@ -864,7 +825,6 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
         l *= factor;
       }
       const float m_use = m_ref <= -1e29f ? 0.f : m_ref;
-      long long c3 = clock64();
       // Two keys in eight (positions 6 and 7 mod 8) take their exponentials on the FMA pipe,
       // the others on the special-function unit: about what keeps both pipes equally busy.
       // Scaling, the polynomial and the sums use the packed float32 instructions (two values
@@ -909,7 +869,6 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
             v[c >> 1][(c & 1) * 16 + (k >> 1) + 1] = pack_bf16(pj[2], pj[3]);
           }
       }
-      long long c4 = clock64();
       const float sum = ((s8[0].x + s8[0].y) + (s8[1].x + s8[1].y)) + ((s8[2].x + s8[2].y) + (s8[3].x + s8[3].y));
       l += sum;
       // O of this tile is rescaled when a row of the warp raised its reference.  Its last
@@ -938,16 +897,6 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
       tc_wait_st();
       tc_fence_before();
       mbar_arrive(&p_full[buf]);
-      long long c5 = clock64();
-      if (dbg) {
-        dib_dbg[db + x * 8 + 0] += c1 - c0;   // wait for scores
-        dib_dbg[db + x * 8 + 1] += c2 - c1;   // tensor memory load
-        dib_dbg[db + x * 8 + 2] += c3 - c2;   // max
-        dib_dbg[db + x * 8 + 3] += c4 - c3;   // exp
-        dib_dbg[db + x * 8 + 4] += c5 - c4;   // store + arrive
-        dib_dbg[db + x * 8 + 5] += 1;
-        dib_dbg[db + x * 8 + 6] += full ? 1 : 0;
-      }
     }
     if (ok && jl[x] >= jf[x]) {
       ok = mbar_wait(&o_final[x], 0);
@@ -1127,9 +1076,6 @@ const CUtensorMap* cache_map(const void* cache, long long num_pages, int Hkv, in
 }  // namespace
 
 extern "C" {
-void dib_dbg_sel(int y) { cudaMemcpyToSymbol(dib_dbg_y, &y, sizeof(int)); }
-void dib_dbg_read(long long* host) { cudaMemcpyFromSymbol(host, dib_dbg, sizeof(long long) * 64); long long z[64] = {}; cudaMemcpyToSymbol(dib_dbg, z, sizeof(z)); }
-
 
 int dib_attention_prefill_tc_tile_rows() { return TC_M; }
 
@@ -1200,7 +1146,7 @@ int dib_extend_attention_tc_pair(const void* q, void* out, const void* cache, lo
     return DIB_BAD_SIZE;
   const CUtensorMap* map = cache_map(cache, num_pages, Hkv, page_size, D);
   if (map == nullptr) return DIB_LAUNCH_FAILED;
-  const size_t smem = (4 + KS) * TILE_BYTES + (2 * KS + 11) * 8 + 16 + 1024;
+  const size_t smem = 6 * TILE_BYTES + 15 * 8 + 16 + 1024;
   static DeviceOnce attr_set;
   if (!attr_set.done()) {
     if (cudaFuncSetAttribute(extend_attention_tc_pair_kernel,
