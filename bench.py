@@ -15,8 +15,10 @@ page size 16; each request holds 2,048 cached tokens when decoding starts.
             host-to-device copy of the step's metadata from pinned memory, the
             graph, sampling, and the device-to-host read of the sampled tokens,
             every step.
-``prefill`` a prompt of 2,048 tokens, whole: launched kernel by kernel (``value``,
-            ``cold_ms``) and as the replayed graph of that step shape (``replayed_ms``).
+``prefill`` a prompt of 2,048 tokens, whole, of a length not run before, through the
+            captured graph of its bucket of prompt lengths (``value``, ``ms``); the same
+            launched kernel by kernel (``launched_ms``, ``cold_ms``: a bucket's first two
+            prompts) and replayed again (``replayed_ms``).
 ``points``  decode at batch 1 and 64; ``points_<preset>``: decode and prefill at a larger
             model's layer sizes with fewer layers (``config.second_model`` names both
             layer counts).
@@ -364,11 +366,14 @@ def main() -> int:
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)   # > L2
 
     def measure_prefill(engine, mcfg, n_layers, profile=False):
-        """One prompt of ``--prefill-tokens`` tokens, whole, to its first logits.  A step
-        shape is launched kernel by kernel the first two times it is seen and replayed as
-        a captured graph from the third time on: both are timed, ``value`` is the launched
-        one (what a prompt length seen for the first time costs once the libraries are
-        loaded)."""
+        """One prompt of ``--prefill-tokens`` tokens, whole, to its first logits.  The engine
+        launches a step kernel by kernel the first two times its bucket of shapes is seen
+        (prompt lengths rounded up by a sixteenth of an octave) and replays the bucket's
+        captured graph from the third time on, whatever the length inside the bucket.  Timed:
+        ``launched_ms``: the prompt launched, bucket and libraries new (first) and known
+        (second); ``value``/``ms``: a prompt of a length NOT run before, its bucket's graph
+        captured (what a prompt costs in a running engine); ``replayed_ms``: the same length
+        again.  Every timed prompt goes through ``ModelRunner.step`` from host tokens."""
         runner, cache = engine.runner, engine.cache
         n = a.prefill_tokens
         prompt = random_prompt(mcfg.vocab_size, n + 1)
@@ -385,23 +390,25 @@ def main() -> int:
             cache.release_slot(slot)
             return ms
 
-        for extra in (1, -1, 1):                 # other shapes: load the libraries, warm the clocks
-            once(prompt[:n + extra])
-        launched = [once(prompt[:n], profiled=profile and i == 1) for i in range(2)]
-        once(prompt[:n])                         # the third time: captured, then replayed
-        replayed = [once(prompt[:n]) for _ in range(3)]
+        once(prompt[:n + 40])                    # another bucket: load the libraries, warm the clocks
+        launched = [once(prompt[:n - 2]), once(prompt[:n - 1])]      # the bucket's first and second time
+        once(prompt[:n - 3])                     # the third: captured, then replayed
         sg = runner.step_graphs
-        cold_ms, replayed_ms = min(launched), sorted(replayed)[1]
-        if sg is None or sg.replays < 3:
-            replayed_ms = None
+        replays0 = sg.replays if sg is not None else 0
+        fresh = once(prompt[:n], profiled=profile)                   # a length not run before
+        replayed = [once(prompt[:n]) for _ in range(3)]
+        in_graph = sg is not None and sg.replays - replays0 == 4
+        ms = fresh if in_graph else min(launched)
+        replayed_ms = sorted(replayed)[1] if in_graph else None
         _, flops = model_bytes_and_flops(mcfg, n_layers, 1, 0, n)
-        return {"value": n / (cold_ms / 1e3), "tokens": n, "ms": cold_ms, "cold_ms": cold_ms,
+        frac = lambda t: flops / (t / 1e3) / (pk["bf16_tflops"] * 1e12)
+        return {"value": n / (ms / 1e3), "tokens": n, "ms": ms, "cold_ms": min(launched),
                 "launched_ms": [round(x, 3) for x in launched], "replayed_ms": replayed_ms,
-                "frac": flops / (cold_ms / 1e3) / (pk["bf16_tflops"] * 1e12),
-                "frac_replayed": (flops / (replayed_ms / 1e3) / (pk["bf16_tflops"] * 1e12)
-                                  if replayed_ms else None),
-                "note": "value, ms and frac: launched kernel by kernel (a prompt length seen the "
-                        "first or second time); replayed_ms: the captured graph of this step shape"}
+                "frac": frac(ms), "frac_launched": frac(min(launched)),
+                "note": ("value, ms and frac: a prompt length not run before, replayed through the "
+                         "captured graph of its bucket of lengths; launched_ms: kernel by kernel, "
+                         "the bucket's first and second time" if in_graph else
+                         "value, ms and frac: launched kernel by kernel (no graph)")}
 
     def fill_requests(engine, mcfg, batch):
         slots = [engine.cache.allocate_slot() for _ in range(batch)]
@@ -539,7 +546,7 @@ def main() -> int:
         if not a.no_prefill:
             pf = measure_prefill(eng2, cfg2, l2)
             second.update(prefill_tok_s=pf["value"], prefill_ms=pf["ms"], prefill_frac=pf["frac"],
-                          prefill_replayed_ms=pf["replayed_ms"])
+                          prefill_launched_ms=pf["cold_ms"])
         for b in (8, 64):
             pms, _, _ = device_decode(eng2, cfg2, b, a.point_steps, a.warmup)
             second[f"decode_b{b}"] = b * a.point_steps / (pms / 1e3)

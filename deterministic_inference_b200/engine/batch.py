@@ -176,18 +176,22 @@ def fill_packed(host: np.ndarray, lay: PackedLayout, shape: StepShape, cache, gr
     ``lay`` (block tables ``lay.width`` >= ``shape.width`` pages wide).  Returns the number
     of tokens that are to be patched in from the previous step's samples.
 
-    ``lay`` may hold more sequences than the step has (a captured decode graph is made
-    for a bucket of batch sizes): the rest are padding sequences of one token each that
-    live on page 0 and state slot 0, which no request owns, at position 0 with a key
-    count of 1; each asks for one logits row, which the caller drops."""
+    ``lay`` may hold more sequences and more tokens than the step has (a captured graph is
+    made for a bucket of sizes): the rest are padding sequences that live on page 0 and
+    state slot 0, which no request owns.  Each of them brings one token, except the last,
+    which brings what is left of the layout's tokens (none, perhaps); their tokens have id 0,
+    positions inside page 0 and a key count of their own token count (1 at least).  The
+    padding rows follow the step's own rows, so no row of a request moves.  If the layout
+    has more logits rows than the step wants, each padding sequence asks for one, which the
+    caller drops."""
     host[:] = 0
     seqs, q_lens = shape.seqs, shape.q_lens
     n_pad = lay.b - len(seqs)
-    if n_pad < 0 or lay.t - shape.t != n_pad or lay.r - len(shape.logit_index) not in (0, n_pad):
+    pad_t = lay.t - shape.t
+    if n_pad < 0 or pad_t < 0 or (n_pad == 0 and pad_t != 0) or pad_t < n_pad - 1 \
+            or lay.r - len(shape.logit_index) not in (0, n_pad):
         raise ValueError(f"layout of {lay.b} sequences / {lay.t} tokens does not fit a step of "
                          f"{len(seqs)} sequences / {shape.t} tokens")
-    if n_pad and shape.num_decode != len(seqs):
-        raise ValueError("only steps of one-token sequences are padded")
     ids, pos, tseq = lay.seg(host, "input_ids"), lay.seg(host, "positions"), lay.seg(host, "token_seq")
     cu = lay.seg(host, "cu_q_lens")
     pdst, psrc = lay.seg(host, "patch_dst"), lay.seg(host, "patch_src")
@@ -214,11 +218,17 @@ def fill_packed(host: np.ndarray, lay: PackedLayout, shape: StepShape, cache, gr
     lay.seg(host, "state_slots")[:n] = shape.slots
     lay.seg(host, "logit_indices")[:len(shape.logit_index)] = shape.logit_index
     if n_pad:
-        tseq[start:] = np.arange(n, lay.b)
-        cu[n + 1:] = np.arange(start + 1, start + n_pad + 1)
-        lay.seg(host, "seq_lens")[n:] = 1
+        counts = np.ones(n_pad, dtype=np.int64)
+        counts[-1] = pad_t - (n_pad - 1)
+        ends = start + np.cumsum(counts)
+        tseq[start:] = np.repeat(np.arange(n, lay.b), counts)
+        last = int(counts[-1])
+        if last > 1:      # the last one's tokens: positions that stay inside page 0
+            pos[lay.t - last:] = np.arange(last) % min(g.page_size for g in group_list)
+        cu[n + 1:] = ends
+        lay.seg(host, "seq_lens")[n:] = np.maximum(counts, 1)
         if lay.r > len(shape.logit_index):
-            lay.seg(host, "logit_indices")[len(shape.logit_index):] = np.arange(start, start + n_pad)
+            lay.seg(host, "logit_indices")[len(shape.logit_index):] = np.minimum(ends - counts, lay.t - 1)
     for gi, g in enumerate(group_list):
         bt = lay.seg(host, ("bt", gi)).reshape(lay.b, lay.width)
         sm = lay.seg(host, ("sm", gi))
@@ -266,12 +276,12 @@ def check_packed(host: np.ndarray, lay: PackedLayout, cache, group_list: list, v
     tseq = lay.seg(host, "token_seq")
     need(t == 0 or (tseq.min() >= 0 and tseq.max() < b), "a token names a sequence the step does not have")
     cu = lay.seg(host, "cu_q_lens")
-    need(cu[0] == 0 and cu[b] == t and bool((np.diff(cu) >= 1).all()),
-         "sequence boundaries do not cover the tokens, or a sequence brings none")
+    slots = lay.seg(host, "state_slots")
+    need(cu[0] == 0 and cu[b] == t and bool((np.diff(cu) >= np.where(slots == 0, 0, 1)).all()),
+         "sequence boundaries do not cover the tokens, or a request's sequence brings none")
     lens = lay.seg(host, "seq_lens")
     need(bool((lens >= np.diff(cu)).all()) and (b == 0 or lens.max() <= cache.max_seq_len),
          "a sequence's key count is below its new tokens or beyond max_seq_len")
-    slots = lay.seg(host, "state_slots")
     need(b == 0 or (slots.min() >= 0 and slots.max() < cache.max_reqs), "a state slot outside the table")
     li = lay.seg(host, "logit_indices")
     need(li.size == 0 or (li.min() >= 0 and li.max() < t), "a logits row names a token the step does not have")
@@ -300,13 +310,23 @@ def check_packed(host: np.ndarray, lay: PackedLayout, cache, group_list: list, v
                  f"group {g.key}: sequence {bi} has keys on a page it does not hold")
 
 
-def build_step_batch(entries: list, cache, device, pin: bool = True, check=None) -> StepBatch:
+def build_step_batch(entries: list, cache, device, pin: bool = True, check=None,
+                     pad_to=None) -> StepBatch:
     """Pack ``entries`` (``SequenceInput``; pages already allocated) into a
     ``StepBatch`` on ``device``.  ``check(host array, layout)``: called on the packed
-    metadata before it is copied (debug checks)."""
+    metadata before it is copied (debug checks).  ``pad_to(StepShape)``: the number of token
+    rows the step is to run with (its own or more); the rows beyond its own belong to one
+    padding sequence (``fill_packed``), which the host-side lengths list like a sequence of
+    that many new tokens: the attention works on its rows too (over page 0), so every row of
+    every activation is a finite number and what the padding rows leave on page 0 is too (a
+    key tile's masked keys may lie there: their values are multiplied by zero, which must
+    not meet a NaN)."""
     shape = describe_step(entries, cache)
     group_list = list(cache.page_groups.values())
-    lay = PackedLayout(shape.t, len(shape.seqs), len(shape.logit_index), shape.width, len(group_list))
+    rows = shape.t if pad_to is None else max(shape.t, int(pad_to(shape)))
+    padded = rows > shape.t
+    lay = PackedLayout(rows, len(shape.seqs) + (1 if padded else 0), len(shape.logit_index), shape.width,
+                       len(group_list))
     host = np.zeros(lay.size, dtype=np.int32)
     num_patches = fill_packed(host, lay, shape, cache, group_list)
     if check is not None:
@@ -319,7 +339,9 @@ def build_step_batch(entries: list, cache, device, pin: bool = True, check=None)
         td = th.to(dev, non_blocking=True)
     else:
         td = th
-    batch = step_views(td, lay, group_list, shape.q_lens, shape.kv_lens, shape.slots, shape.num_decode,
-                       shape.logit_rows, shape.order)
+    pad = [rows - shape.t] if padded else []
+    batch = step_views(td, lay, group_list, shape.q_lens + pad, shape.kv_lens + pad,
+                       shape.slots + ([0] if padded else []), shape.num_decode, shape.logit_rows,
+                       shape.order)
     batch.num_patches = num_patches
     return batch

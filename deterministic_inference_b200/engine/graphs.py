@@ -174,18 +174,37 @@ class DecodeGraphs:
         return cap.logits[:len(entries)], batch
 
 
-class StepGraphs:
-    """CUDA-graph replay of steps of any shape that come again: the same token counts
-    per sequence (in batch order), the same wanted places, block tables of the same
-    bucket of width.  Portions of long prompts cut under one token budget, and whole
-    prompts of one length, are such steps; a small model's step of 2,048 prompt tokens
-    is a few hundred launches that the host otherwise issues barely faster than the GPU
-    runs them.  A shape is captured when it shows up the third time; the least recently
-    used graph goes when there are more than ``max_graphs`` (each keeps its own
-    activations).  Not used while the cache holds per-request state of a part (a part
-    may read its slots on the host)."""
+def token_bucket(q: int) -> tuple:
+    """(bucket, smallest count of the bucket) for a sequence that brings ``q`` >= 2 tokens
+    to a step: counts are rounded up to a multiple of a sixteenth of the power of two at or
+    below them (16 at least), so a bucket's graph runs 6 % more rows than the step has at
+    worst and about 3 % on average, with 16 buckets to an octave."""
+    step = max(16, (1 << (q.bit_length() - 1)) // 16)
+    b = -(-q // step) * step
+    return b, max(2, b - step + 1)
 
-    def __init__(self, model, cache, device, max_graphs: int = 8, min_repeats: int = 3,
+
+class StepGraphs:
+    """CUDA-graph replay of steps that are no pure decode steps: portions of prompts, whole
+    prompts, and those beside decoded tokens.  A small model's step of 2,048 prompt tokens
+    is a few hundred launches that the host issues barely faster than the GPU runs them.
+
+    A graph is captured for a BUCKET of step shapes: the same number of sequences (in batch
+    order, one-token sequences first), each prompt portion's token count rounded up
+    (``token_bucket``), the same number of wanted logits rows, block tables of the same
+    bucket of width.  The step's real counts reach the kernels through the packed metadata
+    on the device; what the host knows when it captures (grids, the attention's list of query
+    tiles) is sized for the bucket's upper bounds, and a query tile past a sequence's real
+    tokens leaves at once.  The rows that a step does not fill belong to a padding sequence
+    on page 0 and state slot 0 (``fill_packed``) and follow the step's own rows; every
+    kernel works row by row or takes a row's sequence from the metadata, so they reach no
+    request's result (they are worked on like a request's rows, so that they hold finite
+    numbers and leave such on page 0).  A bucket is captured when it shows up the third time; the least
+    recently used graph goes when there are more than ``max_graphs`` (they share one memory
+    pool).  Not used while the cache holds per-request state of a part (a part may read its
+    slots on the host)."""
+
+    def __init__(self, model, cache, device, max_graphs: int = 64, min_repeats: int = 3,
                  min_width: int = 8):
         # the model, the cache and the device, not the runner that owns this object: a
         # cycle would leave captured graphs to the garbage collector, which may then
@@ -209,6 +228,15 @@ class StepGraphs:
         wb = _bucket(width, self.min_width) if width <= 32 else -(-width // 32) * 32
         return min(wb, self.cache.max_blocks)
 
+    @staticmethod
+    def padded_tokens(shape) -> int:
+        """The token rows a step of this shape runs with, replayed or launched: the sum of
+        its sequences' buckets.  A step that is launched kernel by kernel (its bucket has
+        not come three times yet) runs with the same number of rows as the graph will, so
+        that a library's choice of algorithm by the row count, and with it a token's bits,
+        does not depend on how often a bucket has been seen."""
+        return sum(1 if q == 1 else token_bucket(q)[0] for q in shape.q_lens)
+
     def run(self, entries, prev_tokens=None):
         """(logits, StepBatch) like ``ModelRunner.step``, or None if this step is to be
         run launch by launch.  The pages of the entries are allocated already."""
@@ -218,7 +246,8 @@ class StepGraphs:
         wb = self._width_bucket(shape.width)
         if wb < shape.width:
             return None
-        key = (tuple(shape.q_lens), tuple(shape.logit_index), wb)
+        buckets = [(1, 1) if q == 1 else token_bucket(q) for q in shape.q_lens]
+        key = (tuple(b for b, _ in buckets), len(shape.logit_index), wb)
         cap = self.graphs.get(key)
         if cap is None:
             n = self.seen.get(key, 0) + 1
@@ -228,7 +257,7 @@ class StepGraphs:
             if n < self.min_repeats:
                 return None
             t0 = time.perf_counter()
-            cap = self._capture(key, shape, wb)
+            cap = self._capture(key, shape, buckets, wb)
             self.capture_seconds += time.perf_counter() - t0
         else:
             self.graphs.move_to_end(key)
@@ -248,15 +277,27 @@ class StepGraphs:
         # the caller owns what it gets: the graph's own logits are overwritten by its next replay
         return cap.logits.clone(), batch
 
-    def _capture(self, key: tuple, shape, wb: int) -> _Captured:
+    def _capture(self, key: tuple, shape, buckets: list, wb: int) -> _Captured:
         dev = self.device
         b = len(shape.seqs)
-        lay = PackedLayout(shape.t, b, len(shape.logit_index), wb, len(self.group_list))
+        q_upper = [qb for qb, _ in buckets]
+        # one more sequence than the step has: the padding sequence that owns the rows a
+        # step of this bucket does not fill
+        lay = PackedLayout(sum(q_upper), b + 1, len(shape.logit_index), wb, len(self.group_list))
         host = torch.zeros(lay.size, dtype=torch.int32).pin_memory()
         static = torch.zeros(lay.size, dtype=torch.int32, device=dev)
-        upper = wb * self.cache.page_size      # what kernels size their grids for
-        batch = step_views(static, lay, self.group_list, list(shape.q_lens), [upper] * b,
-                           list(shape.slots), shape.num_decode, shape.logit_rows, shape.order)
+        # What kernels size their grids and lists for: every sequence as long as the block
+        # table's width allows, and as many tokens before a portion as the shortest portion
+        # of its bucket would leave of that (the lists take key counts minus new tokens as
+        # the tokens before a portion).
+        upper = wb * self.cache.page_size
+        kv_upper = [upper + qb - lo for qb, lo in buckets]
+        # the padding sequence has the rows that the sequences of a step leave: as many as
+        # the shortest of each bucket would leave, at most.  The attention works on them
+        # too (over page 0), so that every row of every activation is a finite number.
+        pad_upper = sum(qb - lo for qb, lo in buckets)
+        batch = step_views(static, lay, self.group_list, q_upper + [pad_upper], kv_upper + [pad_upper],
+                           list(shape.slots) + [0], shape.num_decode, shape.logit_rows, shape.order)
         fill_packed(host.numpy(), lay, shape, self.cache, self.group_list)
         static.copy_(host, non_blocking=True)
         side = torch.cuda.Stream(device=dev)

@@ -105,7 +105,12 @@ class ModelRunner:
             if self._check is not None:
                 n_prev = 0 if prev_tokens is None else int(prev_tokens.shape[0])
                 check = lambda host, lay: self._check(host, lay, n_prev)
-            batch = build_step_batch(entries, self.cache, self.device, check=check)
+            # with graphs on, a launched step runs with the rows its bucket's graph will have
+            pad_to = None
+            if self.step_graphs is not None and not self.cache.state_groups \
+                    and any(len(e.tokens) > 1 for e in entries):
+                pad_to = self.step_graphs.padded_tokens
+            batch = build_step_batch(entries, self.cache, self.device, check=check, pad_to=pad_to)
             if batch.num_patches:
                 from ..kernels import ops
                 ops.patch_token_ids(batch.input_ids, batch.patch_dst, batch.patch_src, prev_tokens)

@@ -232,3 +232,72 @@ def test_debug_checks_catch_bad_step_metadata(tiny_model_dirs, torch_ops):
             seg[2] = 0          # the page that holds keys 32..47
         with pytest.raises(StepCheckError, match=message):
             check_packed(bad, lay, r.cache, groups, vocab, maxpos)
+
+
+def test_a_step_padded_to_a_bucket_keeps_its_rows_and_parks_the_rest_on_page_zero(tiny_model_dirs, torch_ops):
+    """``fill_packed`` into a layout with more token rows and one more sequence than the step
+    has (a captured graph's bucket, or a launched step that runs with its bucket's rows): the
+    step's own rows, boundaries, lengths and block tables are those of the unpadded layout;
+    the rows after them belong to one padding sequence on state slot 0 whose block table is
+    all page 0, with positions inside one page and cache slots on page 0; the padded array
+    passes the debug check.  A layout with several padding sequences gives each one token
+    and the last the rest; layouts that do not fit are refused.  ``token_bucket`` rounds up
+    by a sixteenth of an octave and names a lower bound of its bucket."""
+    import numpy as np
+    from deterministic_inference_b200.engine.batch import (PackedLayout, build_step_batch, check_packed,
+                                                           describe_step, fill_packed)
+    from deterministic_inference_b200.engine.graphs import StepGraphs, token_bucket
+    d = tiny_model_dirs["bw"]
+    r = ModelRunner(EngineConfig(model_path=str(d), dtype="float32", device="cpu", kv_pool_tokens=512,
+                                 page_size=16, max_reqs=8, max_seq_len=256))
+    s1, s2 = r.cache.allocate_slot(), r.cache.allocate_slot()
+    r.step([SequenceInput(s1, list(range(30)), 0, [])])
+    entries = [SequenceInput(s2, list(range(100, 137)), 0, [36]), SequenceInput(s1, [7], 30, [0])]
+    for e in entries:
+        r.cache.allocate(e.slot, e.num_computed + len(e.tokens))
+    groups = list(r.cache.page_groups.values())
+    shape = describe_step(entries, r.cache)
+    assert shape.q_lens == [1, 37] and StepGraphs.padded_tokens(shape) == 1 + 48
+    exact = PackedLayout(shape.t, 2, 2, shape.width, len(groups))
+    padded = PackedLayout(49, 3, 2, shape.width + 3, len(groups))
+    a, b = np.zeros(exact.size, dtype=np.int32), np.full(padded.size, 77, dtype=np.int32)
+    fill_packed(a, exact, shape, r.cache, groups)
+    fill_packed(b, padded, shape, r.cache, groups)
+    for name in ("input_ids", "positions", "token_seq"):
+        assert (padded.seg(b, name)[:38] == exact.seg(a, name)).all()
+    assert padded.seg(b, "cu_q_lens").tolist() == [0, 1, 38, 49]
+    assert padded.seg(b, "seq_lens").tolist() == [31, 37, 11] and padded.seg(b, "state_slots").tolist()[2] == 0
+    assert (padded.seg(b, "token_seq")[38:] == 2).all() and (padded.seg(b, "input_ids")[38:] == 0).all()
+    assert padded.seg(b, "positions")[38:].max() < 16
+    assert padded.seg(b, "logit_indices").tolist() == exact.seg(a, "logit_indices").tolist()
+    for gi in range(len(groups)):
+        bt = padded.seg(b, ("bt", gi)).reshape(3, padded.width)
+        assert (bt[2] == 0).all() and (bt[:2, :exact.width] == exact.seg(a, ("bt", gi)).reshape(2, exact.width)).all()
+        assert (padded.seg(b, ("sm", gi))[:38] == exact.seg(a, ("sm", gi))).all()
+        assert (padded.seg(b, ("sm", gi))[38:] < 16).all()
+    check_packed(b, padded, r.cache, groups, 512, 512)
+    # a padding sequence may be left without a token; a request's sequence may not
+    tight = PackedLayout(38, 3, 2, shape.width, len(groups))
+    c = np.zeros(tight.size, dtype=np.int32)
+    fill_packed(c, tight, shape, r.cache, groups)
+    assert tight.seg(c, "cu_q_lens").tolist() == [0, 1, 38, 38]
+    check_packed(c, tight, r.cache, groups, 512, 512)
+    # several padding sequences: one token each, the last takes the rest
+    many = PackedLayout(38 + 6, 2 + 3, 2 + 3, shape.width, len(groups))
+    m = np.zeros(many.size, dtype=np.int32)
+    fill_packed(m, many, shape, r.cache, groups)
+    assert many.seg(m, "cu_q_lens").tolist() == [0, 1, 38, 39, 40, 44]
+    assert many.seg(m, "logit_indices").tolist()[2:] == [38, 39, 40]
+    check_packed(m, many, r.cache, groups, 512, 512)
+    for t, nb in ((37, 2), (40, 2), (39, 5)):        # fewer rows than tokens; rows without a sequence; too few rows
+        lay = PackedLayout(t, nb, 2, shape.width, len(groups))
+        with pytest.raises(ValueError, match="does not fit"):
+            fill_packed(np.zeros(lay.size, dtype=np.int32), lay, shape, r.cache, groups)
+    # the launched step that runs with its bucket's rows
+    batch = build_step_batch(entries, r.cache, "cpu", pad_to=StepGraphs.padded_tokens)
+    assert batch.num_tokens == 49 and batch.num_seqs == 3 and batch.q_lens == [1, 37, 11]
+    assert batch.input_ids.shape[0] == 49 and batch.cu_q_lens.tolist() == [0, 1, 38, 49]
+    for q in (2, 16, 17, 100, 128, 129, 1000, 2047, 2048, 2049, 5000):
+        bucket, lowest = token_bucket(q)
+        assert lowest <= q <= bucket and bucket - q <= max(15, q // 16)
+        assert token_bucket(bucket)[0] == bucket and token_bucket(lowest)[0] <= bucket

@@ -195,10 +195,11 @@ def test_published_shapes_logits_agree_across_dtypes(name, layers):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_steps_replayed_as_graphs_give_the_bits_of_launched_steps(dtype, tiny_model_dirs):
-    """Steps of a shape that comes again are captured and replayed as CUDA graphs (from
-    the third time on): prompts of one length one after the other, a two-sequence mixed
-    step repeated, decode steps.  Every step's logits equal, bit for bit, those of a
-    runner that launches every step kernel by kernel; and the graphs were in fact used."""
+    """Steps whose bucket of shapes comes again are captured and replayed as CUDA graphs
+    (from the third time on): prompts of six lengths of one bucket (33 to 48 tokens) one after
+    the other, a two-sequence mixed step with portions of 3 to 7 tokens, decode steps.  Every
+    step's logits equal, bit for bit, those of a runner that launches every step kernel by
+    kernel with no row of padding; and the graphs were in fact used, one for each bucket."""
     from deterministic_inference_b200 import EngineConfig
     from deterministic_inference_b200.engine.batch import SequenceInput
     from deterministic_inference_b200.engine.runner import ModelRunner
@@ -208,25 +209,27 @@ def test_steps_replayed_as_graphs_give_the_bits_of_launched_steps(dtype, tiny_mo
                                         kv_pool_tokens=4096, page_size=TINY["b"]["page_size"],
                                         max_reqs=16, max_seq_len=512, cuda_graphs=g)) for g in (True, False)]
     assert runners[0].step_graphs is not None and runners[1].step_graphs is None
-    prompts = _prompts(vocab, (40,) * 6 + (25,) * 5, 21)
+    lens = (40, 37, 48, 33, 45, 41)
+    portions = (5, 3, 7, 4, 6)
+    prompts = _prompts(vocab, lens + (25,) * 5, 21)
     outs = [[], []]
     for k, r in enumerate(runners):
         slots = [r.cache.allocate_slot() for _ in prompts]
-        for s, p in zip(slots[:6], prompts[:6]):                    # the shape (40,) six times
-            outs[k].append(r.step([SequenceInput(s, p, 0, [0, 39])])[0].clone())
-        done = [0] * 5
-        for rep in range(5):                                        # (1, 5) with a decode beside a portion
+        for s, p in zip(slots[:6], prompts[:6]):                    # one bucket, six lengths
+            outs[k].append(r.step([SequenceInput(s, p, 0, [0, len(p) - 1])])[0].clone())
+        for rep in range(5):                                        # a decode beside a portion
             s_dec, s_pre = slots[0], slots[6 + rep]
-            outs[k].append(r.step([SequenceInput(s_pre, prompts[6 + rep][:5], 0, [4]),
-                                   SequenceInput(s_dec, [rep + 1], 40 + rep, [0])])[0].clone())
+            n = portions[rep]
+            outs[k].append(r.step([SequenceInput(s_pre, prompts[6 + rep][:n], 0, [n - 1]),
+                                   SequenceInput(s_dec, [rep + 1], lens[0] + rep, [0])])[0].clone())
         for step in range(6):                                       # pure decode of three requests
-            outs[k].append(r.step([SequenceInput(slots[i], [step + 7], 40 + step, [0])
+            outs[k].append(r.step([SequenceInput(slots[i], [step + 7], lens[i] + step, [0])
                                    for i in (1, 2, 3)])[0].clone())
     assert len(outs[0]) == len(outs[1]) == 17
     for a, b in zip(*outs):
         assert torch.equal(a, b)
     g = runners[0].step_graphs
-    assert g.captures >= 2 and g.replays >= 4 + 3           # the two prompt shapes
+    assert g.captures == 2 and g.replays == 4 + 3           # the two buckets, from their third step on
     assert runners[0].decode_graphs.replays == 6            # the pure-decode steps
 
 
@@ -288,8 +291,9 @@ def test_bfloat16_bits_of_a_token_do_not_depend_on_its_step(name, tiny_model_dir
     """With ``library_products=False`` every bfloat16 kernel adds up in an order that
     depends on the token's own position and the weights' shapes alone.  So the logits of
     a request are the same bits (a) alone and beside three other requests of other
-    lengths, (b) launched kernel by kernel and replayed from a captured graph, (c) with
-    its prompt cut into portions of 512 and of 100 tokens.  Heads of 128: the tcgen05
+    lengths, (b) launched kernel by kernel and replayed from a captured graph, also one
+    captured for a bucket of longer portions, (c) with its prompt cut into portions of 512,
+    of 500 and of 100 tokens.  Heads of 128: the tcgen05
     prompt kernel in its paired, neighbour and single-tile forms, the TMA decode kernels,
     the package's matrix product at 1 to 1,700 rows."""
     from deterministic_inference_b200 import EngineConfig
@@ -344,6 +348,10 @@ def test_bfloat16_bits_of_a_token_do_not_depend_on_its_step(name, tiny_model_dir
     for _ in range(3):                      # the third time every repeated shape is replayed
         variants["replayed"] = feed(r, 512)
     assert r.step_graphs.replays >= 2 and r.decode_graphs.replays >= 8
+    # portions of 500 run through the graph captured for 497 to 512 tokens, with 12 rows of padding
+    before = r.step_graphs.replays
+    variants["replayed with padding rows"] = feed(r, 500)
+    assert r.step_graphs.replays == before + 1
     for what, rows in variants.items():
         for p, row in base.items():
             assert torch.equal(rows[p], row), (what, p)
