@@ -22,9 +22,10 @@
 // gone.  The two products are rounded to bfloat16 first, as stored products would be, and
 // the gate is silu_gate<bf16> of common.cuh, so the bits are those of the two-kernel path.
 //
-// Roles in a CTA of 192 threads: warp 0 issues the TMA loads (the weights of the first
+// Roles in a CTA of 320 threads: warp 0 issues the TMA loads (the weights of the first
 // stages before the programmatic dependency wait, the tokens after it), warp 1 allocates
-// tensor memory and issues the MMAs, warps 2-5 are the epilogue.  Every mbarrier wait is
+// tensor memory and issues the MMAs, warps 2-9 are the epilogue (two warps to each quarter
+// of the tile's rows, half of its columns each).  Every mbarrier wait is
 // bounded; a wait that runs out sets the error word (dib_gemm_bf16_large_status), tensor
 // memory is still freed and the kernel returns.
 #include <cuda.h>
@@ -39,13 +40,15 @@ constexpr int BM = 128;       // tokens per tile = MMA M
 constexpr int BK = 64;        // k per stage: 128 bytes = one swizzle atom
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int THREADS = 192;
+constexpr int THREADS = 320;   // warps 0, 1: copies and products; 2-9: epilogue
+constexpr int EPI_WARPS = 8;
 // Features per tile = MMA N: 256 (GATED: 128 gate + 128 up rows), or 128 for products with so
 // few tiles of 256 that they would leave SMs idle.  Stages of the ring: what fits.
 template <int BNL> struct Tile {
   static constexpr int B_BYTES = BNL * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = BNL == 256 ? 4 : 6;
-  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+  static constexpr size_t SMEM_BYTES =
+      (size_t)STAGES * STAGE_BYTES + EPI_WARPS * 4096 + (2 * STAGES + 4) * 8 + 16 + 1024;
 };
 
 __device__ int dib_gemm_large_error_word = 0;
@@ -128,21 +131,44 @@ __device__ __forceinline__ unsigned pack2_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 
-// The epilogue of one token row of a tile: `src` is the tensor-memory address of the row's
-// accumulator (this thread's lane, the tile's first column); features n0 .. of `row`.  The
-// tcgen05.ld inside is warp-wide: all 32 lanes call this together.
+// ---- the epilogue.  A warp owns 32 token rows (its quarter of the tile's tensor-memory lanes)
+// and one half of the tile's columns.  It reads them in blocks of 128 bytes of output a row
+// (64 bfloat16 or 32 float32 values), puts a block's 32 rows into its own 4 KB of shared
+// memory in the 128-byte-swizzled layout, and hands that to a TMA store, which writes whole
+// rows of the block and clips what lies beyond M or N.  (A thread that stores its own row
+// 16 bytes at a time makes every store instruction touch 32 cache lines: 4 us for a tile's
+// epilogue instead of 1.)
+constexpr int EPI_STAGE_BYTES = 32 * 128;
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(reinterpret_cast<unsigned long long>(map)), "r"(smem_u32(src)), "r"(c0), "r"(c1)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// 16-byte piece c (0..7) of this lane's row of the warp's staging block
+__device__ __forceinline__ void stage_piece(unsigned char* stage, int lane, int c, uint4 v) {
+  *reinterpret_cast<uint4*>(stage + lane * 128 + ((c ^ (lane & 7)) << 4)) = v;
+}
 template <typename OutT, bool GATED, int BNL>
-__device__ __forceinline__ void store_row(unsigned src, OutT* __restrict__ out, int row, int M, int N, int n0) {
-  if (GATED) {
-    // columns 0..127: gate, 128..255: up, of features n0 .. n0 + 127
+__device__ __forceinline__ void store_rows(unsigned src, const CUtensorMap* map_out, unsigned char* stage,
+                                           int lane, int row0, int n0, int half) {
+  constexpr int PER_BLOCK = 128 / (int)sizeof(OutT);            // output values per row of a block
+  constexpr int OUT_COLS = GATED ? BNL / 2 : BNL;               // output columns of a tile
+  constexpr int BLOCKS = OUT_COLS / 2 / PER_BLOCK;              // blocks of this warp's half
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
-      unsigned g[32], u[32];
-      tc_ld32(src + c * 32, g);
-      tc_ld32(src + 128 + c * 32, u);
-      tc_wait_ld();
-      if (row < M) {
-        OutT* dst = out + (size_t)row * N + n0 + c * 32;
+  for (int blk = 0; blk < BLOCKS; ++blk) {
+    const int col = half * (OUT_COLS / 2) + blk * PER_BLOCK;    // first output column of the block
+    // the store before this one must have read the staging block
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    __syncwarp();
+    if (GATED) {
+      // accumulator columns 0..127: gate, 128..255: up, of the same 128 features
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        unsigned g[32], u[32];
+        tc_ld32(src + col + h * 32, g);
+        tc_ld32(src + 128 + col + h * 32, u);
+        tc_wait_ld();
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           float y[8];
@@ -150,53 +176,56 @@ __device__ __forceinline__ void store_row(unsigned src, OutT* __restrict__ out, 
           for (int e = 0; e < 8; ++e)
             y[e] = silu_gate<__nv_bfloat16>(round_to<__nv_bfloat16>(__uint_as_float(g[q * 8 + e])),
                                             round_to<__nv_bfloat16>(__uint_as_float(u[q * 8 + e])));
-          if (n0 + c * 32 + q * 8 + 8 <= N) {
-            *reinterpret_cast<uint4*>(dst + q * 8) =
-                make_uint4(pack2_bf16(y[0], y[1]), pack2_bf16(y[2], y[3]), pack2_bf16(y[4], y[5]),
-                           pack2_bf16(y[6], y[7]));
-          } else {
-            for (int e = 0; e < 8; ++e)
-              if (n0 + c * 32 + q * 8 + e < N) Elem<OutT>::store(dst + q * 8 + e, y[e]);
-          }
+          stage_piece(stage, lane, h * 4 + q,
+                      make_uint4(pack2_bf16(y[0], y[1]), pack2_bf16(y[2], y[3]), pack2_bf16(y[4], y[5]),
+                                 pack2_bf16(y[6], y[7])));
         }
       }
-    }
-  } else {
-#pragma unroll 1
-    for (int c = 0; c < BNL / 32; ++c) {
-      unsigned v[32];
-      tc_ld32(src + c * 32, v);
-      tc_wait_ld();
-      if (row < M) {
-        OutT* dst = out + (size_t)row * N + n0 + c * 32;
-        if (sizeof(OutT) == 2 && n0 + c * 32 + 32 <= N) {
+    } else if (sizeof(OutT) == 2) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q)
-            *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(dst) + q * 8) = make_uint4(
-                pack2_bf16(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])),
-                pack2_bf16(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])),
-                pack2_bf16(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])),
-                pack2_bf16(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7])));
-        } else {
-          for (int e = 0; e < 32; ++e)
-            if (n0 + c * 32 + e < N) Elem<OutT>::store(dst + e, __uint_as_float(v[e]));
-        }
+      for (int h = 0; h < 2; ++h) {
+        unsigned v[32];
+        tc_ld32(src + col + h * 32, v);
+        tc_wait_ld();
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          stage_piece(stage, lane, h * 4 + q,
+                      make_uint4(pack2_bf16(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])),
+                                 pack2_bf16(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])),
+                                 pack2_bf16(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])),
+                                 pack2_bf16(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]))));
       }
+    } else {
+      unsigned v[32];
+      tc_ld32(src + col, v);
+      tc_wait_ld();
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        stage_piece(stage, lane, q, make_uint4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]));
     }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the TMA reads what the lanes wrote
+    __syncwarp();
+    if (lane == 0) tma_store_2d(map_out, stage, n0 + col, row0);
   }
+}
+// before a CTA ends, its stores must have read their staging blocks
+__device__ __forceinline__ void stores_done(int lane) {
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  __syncwarp();
 }
 
 template <typename OutT, bool GATED, int BNL>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                  OutT* __restrict__ out, int M, int N, int K, int m_tiles, int n_tiles) {
+                  const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int m_tiles, int n_tiles) {
   static_assert(!GATED || BNL == 256, "the gated epilogue pairs 128 gate rows with 128 up rows");
   using TL = Tile<BNL>;
   constexpr int B_BYTES = TL::B_BYTES, STAGE_BYTES = TL::STAGE_BYTES, STAGES = TL::STAGES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
+  unsigned char* epi_stage = smem + STAGES * STAGE_BYTES;      // 4 KB to each epilogue warp
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(epi_stage + EPI_WARPS * EPI_STAGE_BYTES);
   unsigned long long* empty = full + STAGES;
   unsigned long long* acc_full = empty + STAGES;     // [2] a tile's accumulator is complete
   unsigned long long* acc_empty = acc_full + 2;      // [2] the epilogue has read it (128 arrivals)
@@ -206,6 +235,7 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   if (threadIdx.x == 0) {
     prefetch_tensormap(&map_x);
     prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_out);
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = (K + BK - 1) / BK;
@@ -219,7 +249,7 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 128);
+      mbar_init(&acc_empty[b], EPI_WARPS);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -298,9 +328,10 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       }
     }
   } else {
-    // ---- epilogue: warps 2..5; a warp reads the 32 lanes (token rows) 32 * (warp % 4) ..
+    // ---- epilogue: warps 2..9; a warp reads the 32 lanes (token rows) 32 * (warp % 4) ..,
+    // warps 2-5 the first half of the columns, warps 6-9 the second
     pdl_wait();      // nothing is stored before the kernel before this one has finished
-    const int quarter = warp & 3;
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const unsigned lane_base = (unsigned)(quarter * 32) << 16;
     int local = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++local) {
@@ -310,10 +341,13 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       got = __all_sync(0xffffffffu, got);     // tcgen05.ld below is warp-wide
       if (!got) { ok = false; break; }
       tc_fence_after();
-      store_row<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, out, m0 + quarter * 32 + lane, M, N, n0);
+      store_rows<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, &map_out, epi_stage + (warp - 2) * EPI_STAGE_BYTES,
+                                   lane, m0 + quarter * 32, n0, half);
       tc_fence_before();
-      mbar_arrive(&acc_empty[buf]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
+    stores_done(lane);
   }
   if (!ok) atomicExch(&dib_gemm_large_error_word, 1);
   tc_fence_before();
@@ -390,20 +424,22 @@ __device__ __forceinline__ void tc_mma_pair(unsigned tmem_d, unsigned long long 
 template <int BNL> struct PairTile {
   static constexpr int B_BYTES = (BNL / 2) * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // per CTA
   static constexpr int STAGES = 6;
-  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+  static constexpr size_t SMEM_BYTES =
+      (size_t)STAGES * STAGE_BYTES + EPI_WARPS * 4096 + (2 * STAGES + 4) * 8 + 16 + 1024;
 };
 
 template <typename OutT, bool GATED, int BNL>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                 OutT* __restrict__ out, int M, int N, int K, int m_tiles, int n_tiles) {
+                 const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int m_tiles, int n_tiles) {
   static_assert(!GATED || BNL == 256, "the gated epilogue pairs 128 gate rows with 128 up rows");
   using TL = PairTile<BNL>;
   constexpr int STAGE_BYTES = TL::STAGE_BYTES, STAGES = TL::STAGES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned long long* full = reinterpret_cast<unsigned long long*>(smem + STAGES * STAGE_BYTES);
+  unsigned char* epi_stage = smem + STAGES * STAGE_BYTES;      // 4 KB to each epilogue warp
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(epi_stage + EPI_WARPS * EPI_STAGE_BYTES);
   unsigned long long* empty = full + STAGES;
   unsigned long long* acc_full = empty + STAGES;     // [2]
   unsigned long long* acc_empty = acc_full + 2;      // [2]
@@ -412,6 +448,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   if (threadIdx.x == 0) {
     prefetch_tensormap(&map_x);
     prefetch_tensormap(&map_w);
+    prefetch_tensormap(&map_out);
   }
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const unsigned rank = cluster_rank();              // 0: the CTA that issues the products
@@ -425,7 +462,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 8);
+      mbar_init(&acc_empty[b], 2 * EPI_WARPS);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -505,7 +542,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   } else {
     // ---- epilogue of this CTA's 128 token rows
     pdl_wait();
-    const int quarter = warp & 3;
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const unsigned lane_base = (unsigned)(quarter * 32) << 16;
     const unsigned acc_empty0 = cluster_addr(smem_u32(acc_empty), 0);   // the first CTA's acc_empty[0]
     int local = 0;
@@ -516,11 +553,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       got = __all_sync(0xffffffffu, got);     // tcgen05.ld below is warp-wide
       if (!got) { ok = false; break; }
       tc_fence_after();
-      store_row<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, out, m0 + quarter * 32 + lane, M, N, n0);
+      store_rows<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, &map_out, epi_stage + (warp - 2) * EPI_STAGE_BYTES,
+                                   lane, m0 + quarter * 32, n0, half);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty0 + buf * 8);
     }
+    stores_done(lane);
   }
   if (!ok) atomicExch(&dib_gemm_large_error_word, 1);
   tc_fence_before();
@@ -563,11 +602,27 @@ bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long K, in
              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The output [M, N] (bfloat16 or float32), boxes of 32 rows x 128 bytes, 128-byte swizzle; a
+// store clips what lies beyond the matrix.
+template <typename OutT>
+bool make_out_map(CUtensorMap* map, void* ptr, long long M, long long N) {
+  EncodeTiledFn enc = encode_tiled();
+  if (enc == nullptr) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)M};
+  const cuuint64_t strides[1] = {(cuuint64_t)N * sizeof(OutT)};
+  const cuuint32_t box[2] = {(cuuint32_t)(128 / sizeof(OutT)), 32};
+  const cuuint32_t estr[2] = {1, 1};
+  return enc(map, sizeof(OutT) == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr,
+             dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <typename OutT, bool GATED, int BNL>
 int launch_large(const void* x, const void* w, void* out, int M, int N, int K, int sm_count,
                  cudaStream_t st) {
-  CUtensorMap mx, mw;
-  if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, GATED ? 2ll * N : (long long)N, K, 128))
+  CUtensorMap mx, mw, mo;
+  if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, GATED ? 2ll * N : (long long)N, K, 128) ||
+      !make_out_map<OutT>(&mo, out, M, N))
     return DIB_LAUNCH_FAILED;
   const int m_tiles = (M + BM - 1) / BM;
   const int n_tiles = (N + (GATED ? BNL / 2 : BNL) - 1) / (GATED ? BNL / 2 : BNL);
@@ -583,8 +638,7 @@ int launch_large(const void* x, const void* w, void* out, int M, int N, int K, i
     attr_set.mark();
   }
   const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-  dib_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, st, mx, mw, (OutT*)out, M, N, K, m_tiles,
-             n_tiles);
+  dib_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, st, mx, mw, mo, M, N, K, m_tiles, n_tiles);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -592,8 +646,9 @@ int launch_large(const void* x, const void* w, void* out, int M, int N, int K, i
 template <typename OutT, bool GATED, int BNL>
 int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, int sm_count,
                 cudaStream_t st) {
-  CUtensorMap mx, mw;
-  if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, GATED ? 2ll * N : (long long)N, K, BNL / 2))
+  CUtensorMap mx, mw, mo;
+  if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, GATED ? 2ll * N : (long long)N, K, BNL / 2) ||
+      !make_out_map<OutT>(&mo, out, M, N))
     return DIB_LAUNCH_FAILED;
   const int m_tiles = (M + 2 * BM - 1) / (2 * BM);
   const int n_tiles = (N + (GATED ? BNL / 2 : BNL) - 1) / (GATED ? BNL / 2 : BNL);
@@ -623,7 +678,7 @@ int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, in
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = dib_pdl_enabled() ? 2 : 1;
-  cudaLaunchKernelEx(&cfg, kern, mx, mw, (OutT*)out, M, N, K, m_tiles, n_tiles);
+  cudaLaunchKernelEx(&cfg, kern, mx, mw, mo, M, N, K, m_tiles, n_tiles);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -663,12 +718,12 @@ int dib_gemm_bf16_large_status_clear() {
 }
 
 // out[M, N] = x[M, K] * w[N, K]^T; bf16 inputs, float32 accumulation over k in one pass;
-// out bf16 (out_fp32 = 0) or float32.  K a multiple of 8 (TMA wants 16-byte row strides); x,
-// w and out 16-byte aligned, N a multiple of 8 for the bf16 output.
+// out bf16 (out_fp32 = 0) or float32.  K a multiple of 8 and N of 8 (bf16 output) or 4
+// (float32) (TMA wants 16-byte row strides); x, w and out 16-byte aligned.
 int dib_gemm_bf16_large(const void* x, const void* w, void* out, int M, int N, int K, int out_fp32,
                         int sm_count, cudaStream_t st) {
   if (M == 0 || N == 0) return DIB_OK;
-  if (K < 8 || K % 8 != 0 || sm_count < 1 || (!out_fp32 && N % 8 != 0)) return DIB_BAD_SIZE;
+  if (K < 8 || K % 8 != 0 || sm_count < 1 || N % (out_fp32 ? 4 : 8) != 0) return DIB_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) % 16 != 0)
     return DIB_BAD_ALIGN;
   const int shape = tile_shape(M, N, sm_count);

@@ -57,7 +57,7 @@ def linear_large(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype):
     from . import ops
     m, k = x.shape
     n = weight.shape[0]
-    if not (k % 8 == 0 and k >= 8 and (out_dtype == torch.float32 or n % 8 == 0)
+    if not (k % 8 == 0 and k >= 8 and n % (4 if out_dtype == torch.float32 else 8) == 0
             and out_dtype in (torch.bfloat16, torch.float32)
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0):
         return None
