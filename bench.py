@@ -348,11 +348,12 @@ def main() -> int:
         max_b = max(sizes)
         per_req = a.context + steps_most + a.warmup + 96
         pool = max_b * (-(-per_req // 16) * 16) + a.prefill_tokens + 1024
+        longest_prompt = a.prefill_tokens + 64        # the prefill run also feeds a few tokens more
         return Engine(EngineConfig(
             model_config=mcfg, random_seed=0, dtype="bfloat16", kv_pool_tokens=pool, page_size=16,
             max_reqs=max(256, max_b + 8),
-            max_seq_len=max(8192, -(-per_req // 1024) * 1024, a.prefill_tokens),
-            max_prefill_tokens=max(8192, a.prefill_tokens), max_decode_batch=max(256, max_b),
+            max_seq_len=max(8192, -(-per_req // 1024) * 1024, longest_prompt),
+            max_prefill_tokens=max(8192, longest_prompt), max_decode_batch=max(256, max_b),
             device="cuda:0"))
 
     def launches_now(runner):
