@@ -197,8 +197,11 @@ class SplitSum:
 # Rows up to which the gate of a gated feed-forward is left to the product that follows
 # (``GatedSplit``).  The product then stages the partial products of its columns in shared
 # memory; with more than a few rows that costs more than the separate gate kernel (B200,
-# width 1,024 / 3,072: 6.2 against 7.2 us for both products at 1 row, 8.2 against 7.5 us at 8).
+# width 1,024 / 3,072: 6.2 against 7.2 us for both products at 1 row, 8.2 against 7.5 us at 8);
+# and with a wide feed-forward too (width 4,096 / 12,288: a decode step of one request 5 %
+# slower with it), so it is limited to feed-forwards up to GATE_IN_PRODUCT_WIDTH wide.
 GATE_IN_PRODUCT_ROWS = 2
+GATE_IN_PRODUCT_WIDTH = 4096
 
 
 class GatedSplit:
@@ -555,7 +558,7 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor):
             return out
     y = linear(x, w_gate_up)
     if isinstance(y, SplitSum) and y.dtype == torch.bfloat16 and y.shape[1] % 16 == 0 \
-            and y.shape[0] <= GATE_IN_PRODUCT_ROWS:
+            and y.shape[0] <= GATE_IN_PRODUCT_ROWS and y.shape[1] // 2 <= GATE_IN_PRODUCT_WIDTH:
         return GatedSplit(y)          # the gate is applied by the product that reads it
     return silu_mul(y)
 

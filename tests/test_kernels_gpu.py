@@ -848,6 +848,7 @@ def test_product_that_gates_while_it_loads_gives_the_bits_of_the_two_kernels(swi
         switches.gemm(splits=splits)
     switches.gated("0")
     monkeypatch.setattr(o, "GATE_IN_PRODUCT_ROWS", 128)
+    monkeypatch.setattr(o, "GATE_IN_PRODUCT_WIDTH", 1 << 20)
     deferred = o.gated_linear(x, w_gu)
     if not isinstance(deferred, o.GatedSplit):
         pytest.skip("the gate_up product of this shape is not split")
