@@ -201,18 +201,28 @@ class StepGraphs:
     request's result (they are worked on like a request's rows, so that they hold finite
     numbers and leave such on page 0).  A bucket is captured when it shows up the third time; the least
     recently used graph goes when there are more than ``max_graphs`` (they share one memory
-    pool).  Not used while the cache holds per-request state of a part (a part may read its
+    pool).  A capture costs three runs of the step, and a replay only wins where the host
+    issues the step's launches no faster than the GPU runs them: so a bucket's launched steps
+    are timed (host time to issue them, device time between two events), and a bucket whose
+    launches took the host less than ``host_bound_share`` of the device's time is captured
+    only when it has shown up ``patient_repeats`` times: there a replay saves the few
+    microseconds between two launches only (4-5 % of a step of 2,048 tokens at 8B layer
+    sizes), which pays for the capture after a hundred replays or so.  Not used while the cache holds per-request state of a part (a part may read its
     slots on the host)."""
 
     def __init__(self, model, cache, device, max_graphs: int = 64, min_repeats: int = 3,
-                 min_width: int = 8):
+                 min_width: int = 8, host_bound_share: float = 0.5, patient_repeats: int = 16):
         # the model, the cache and the device, not the runner that owns this object: a
         # cycle would leave captured graphs to the garbage collector, which may then
         # destroy one in the middle of another capture
         self.model, self.cache, self.device = model, cache, device
         self.max_graphs, self.min_repeats, self.min_width = max_graphs, min_repeats, min_width
+        self.host_bound_share, self.patient_repeats = host_bound_share, patient_repeats
         self.graphs: "OrderedDict[tuple, _Captured]" = OrderedDict()
         self.seen: dict = {}
+        self.timings: dict = {}            # bucket -> (host seconds, event, event) of its last launched step
+        self.device_bound: set = set()     # buckets whose launched steps the device, not the host, bounds
+        self._launching = None             # the bucket of the step that run() just declined
         self.group_list = list(self.cache.page_groups.values())
         self.replays = 0
         self.captures = 0
@@ -249,12 +259,19 @@ class StepGraphs:
         buckets = [(1, 1) if q == 1 else token_bucket(q) for q in shape.q_lens]
         key = (tuple(b for b, _ in buckets), len(shape.logit_index), wb)
         cap = self.graphs.get(key)
+        self._launching = None
         if cap is None:
             n = self.seen.get(key, 0) + 1
             if len(self.seen) > 4096:
                 self.seen.clear()
+                self.timings.clear()
+                self.device_bound.clear()
             self.seen[key] = n
-            if n < self.min_repeats:
+            if key in self.device_bound:
+                if n < self.patient_repeats:
+                    return None
+            elif n < self.min_repeats or not self._host_bound(key):
+                self._launching = key if key not in self.device_bound else None
                 return None
             t0 = time.perf_counter()
             cap = self._capture(key, shape, buckets, wb)
@@ -276,6 +293,29 @@ class StepGraphs:
         batch.num_patches = num_patches
         # the caller owns what it gets: the graph's own logits are overwritten by its next replay
         return cap.logits.clone(), batch
+
+    def launched(self, host_seconds: float, start, end) -> None:
+        """The runner's report on the step that ``run`` just declined: the host's time to issue
+        its launches and the CUDA events recorded around them."""
+        if self._launching is not None:
+            self.timings[self._launching] = (host_seconds, start, end)
+            self._launching = None
+
+    def _host_bound(self, key) -> bool:
+        """Whether the bucket's last launched step kept the GPU waiting for the host (waits
+        for that step's events: once per bucket, where a capture would synchronise anyway).
+        A bucket found to be bound by the device is remembered and not timed again."""
+        t = self.timings.get(key)
+        if t is None:
+            return False
+        host_s, start, end = t
+        end.synchronize()
+        device_s = start.elapsed_time(end) / 1e3
+        if host_s >= self.host_bound_share * device_s:
+            return True
+        self.device_bound.add(key)
+        self.timings.pop(key, None)
+        return False
 
     def _capture(self, key: tuple, shape, buckets: list, wb: int) -> _Captured:
         dev = self.device

@@ -10,6 +10,8 @@ the library matrix products.
 
 from __future__ import annotations
 
+import time
+
 import torch
 
 from ..cache.manager import CacheManager, pages_for_budget
@@ -110,11 +112,20 @@ class ModelRunner:
             if self.step_graphs is not None and not self.cache.state_groups \
                     and any(len(e.tokens) > 1 for e in entries):
                 pad_to = self.step_graphs.padded_tokens
+            timed = self.step_graphs is not None and self.step_graphs._launching is not None
+            if timed:
+                t0 = time.perf_counter()
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record()
             batch = build_step_batch(entries, self.cache, self.device, check=check, pad_to=pad_to)
             if batch.num_patches:
                 from ..kernels import ops
                 ops.patch_token_ids(batch.input_ids, batch.patch_dst, batch.patch_src, prev_tokens)
             logits = self.model.forward(batch, self.cache)
+            if timed:
+                # what the step graphs decide by: did the host keep the GPU waiting?
+                ev1.record()
+                self.step_graphs.launched(time.perf_counter() - t0, ev0, ev1)
             if not self._checked_kernels and self.device.type == "cuda":
                 # the first launched step loads the kernel libraries: read their error
                 # words once here (a synchronisation), later ones at the engine's checks

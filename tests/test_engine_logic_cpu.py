@@ -301,3 +301,36 @@ def test_a_step_padded_to_a_bucket_keeps_its_rows_and_parks_the_rest_on_page_zer
         bucket, lowest = token_bucket(q)
         assert lowest <= q <= bucket and bucket - q <= max(15, q // 16)
         assert token_bucket(bucket)[0] == bucket and token_bucket(lowest)[0] <= bucket
+
+
+def test_step_graphs_capture_only_where_the_host_is_the_bound(tiny_model_dirs, torch_ops):
+    """The step graphs' decision from a bucket's timed launched step: the host's time to issue
+    the launches against the device's time between two events.  A bucket whose host time is
+    half of the device's or more is host-bound (worth a graph at once); one below that is
+    remembered as device-bound, not timed again, and left to the patient rule."""
+    from deterministic_inference_b200.engine.graphs import StepGraphs
+
+    class Event:
+        def __init__(self, ms):
+            self.ms, self.waited = ms, False
+
+        def synchronize(self):
+            self.waited = True
+
+        def elapsed_time(self, other):
+            return other.ms - self.ms
+
+    r = ModelRunner(EngineConfig(model_path=str(tiny_model_dirs["bw"]), dtype="float32", device="cpu",
+                                 kv_pool_tokens=256, page_size=16, max_reqs=8, max_seq_len=256))
+    sg = StepGraphs(r.model, r.cache, r.device)
+    assert sg.host_bound_share == 0.5 and sg.patient_repeats > sg.min_repeats
+    assert not sg._host_bound("never launched")
+    sg._launching = "a"
+    end = Event(4.0)
+    sg.launched(0.0039, Event(0.0), end)             # 3.9 ms of host time for 4.0 ms on the device
+    assert sg._launching is None and sg._host_bound("a") and end.waited and "a" not in sg.device_bound
+    sg._launching = "b"
+    sg.launched(0.0019, Event(0.0), Event(8.2))      # 1.9 ms of host time for 8.2 ms on the device
+    assert not sg._host_bound("b") and "b" in sg.device_bound and "b" not in sg.timings
+    sg.launched(1.0, Event(0.0), Event(1.0))         # no step was declined: nothing is recorded
+    assert set(sg.timings) == {"a"}
