@@ -183,7 +183,9 @@ def fill_packed(host: np.ndarray, lay: PackedLayout, shape: StepShape, cache, gr
     positions inside page 0 and a key count of their own token count (1 at least).  The
     padding rows follow the step's own rows, so no row of a request moves.  If the layout
     has more logits rows than the step wants, each padding sequence asks for one, which the
-    caller drops."""
+    caller drops.  An entry of the step itself may be a padding sequence too (state slot 0,
+    which no request has: the step graphs add one-token entries of that kind to fill a bucket
+    of decode sequences); it gets an all-zero block table and cache slot 0 like the others."""
     host[:] = 0
     seqs, q_lens = shape.seqs, shape.q_lens
     n_pad = lay.b - len(seqs)
@@ -235,6 +237,9 @@ def fill_packed(host: np.ndarray, lay: PackedLayout, shape: StepShape, cache, gr
         ps = g.page_size
         start = 0
         for bi, e in enumerate(seqs):
+            if e.slot == 0:          # a padding sequence given as an entry: page 0, cache slot 0
+                start += q_lens[bi]
+                continue
             pl = g.pages[e.slot]
             m = min(len(pl), lay.width)
             bt[bi, :m] = pl[:m]

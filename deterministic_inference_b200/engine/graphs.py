@@ -23,7 +23,7 @@ import gc
 import time
 from collections import OrderedDict
 
-from .batch import PackedLayout, describe_step, fill_packed, step_views
+from .batch import PackedLayout, SequenceInput, describe_step, fill_packed, step_views
 
 
 @contextlib.contextmanager
@@ -189,10 +189,11 @@ class StepGraphs:
     prompts, and those beside decoded tokens.  A small model's step of 2,048 prompt tokens
     is a few hundred launches that the host issues barely faster than the GPU runs them.
 
-    A graph is captured for a BUCKET of step shapes: the same number of sequences (in batch
-    order, one-token sequences first), each prompt portion's token count rounded up
-    (``token_bucket``), the same number of wanted logits rows, block tables of the same
-    bucket of width.  The step's real counts reach the kernels through the packed metadata
+    A graph is captured for a BUCKET of step shapes: the number of one-token sequences
+    rounded up to a power of two (the step is filled up with padding entries on state slot 0,
+    one token and one dropped logits row each, as the decode graphs' batches are), the same
+    number of prompt portions, each one's token count rounded up (``token_bucket``), the same
+    number of wanted logits rows, block tables of the same bucket of width.  The step's real counts reach the kernels through the packed metadata
     on the device; what the host knows when it captures (grids, the attention's list of query
     tiles) is sized for the bucket's upper bounds, and a query tile past a sequence's real
     tokens leaves at once.  The rows that a step does not fill belong to a padding sequence
@@ -240,19 +241,26 @@ class StepGraphs:
 
     @staticmethod
     def padded_tokens(shape) -> int:
-        """The token rows a step of this shape runs with, replayed or launched: the sum of
-        its sequences' buckets.  A step that is launched kernel by kernel (its bucket has
-        not come three times yet) runs with the same number of rows as the graph will, so
-        that a library's choice of algorithm by the row count, and with it a token's bits,
-        does not depend on how often a bucket has been seen."""
-        return sum(1 if q == 1 else token_bucket(q)[0] for q in shape.q_lens)
+        """The token rows a step of this shape runs with, replayed or launched: its one-token
+        sequences rounded up to a power of two, plus the sum of the other sequences' buckets.
+        A step that is launched kernel by kernel (its bucket has not come three times yet)
+        runs with the same number of rows as the graph will, so that a library's choice of
+        algorithm by the row count, and with it a token's bits, does not depend on how often
+        a bucket has been seen."""
+        nd = sum(1 for q in shape.q_lens if q == 1)
+        return (_bucket(nd) if nd else 0) + sum(token_bucket(q)[0] for q in shape.q_lens if q != 1)
 
     def run(self, entries, prev_tokens=None):
         """(logits, StepBatch) like ``ModelRunner.step``, or None if this step is to be
         run launch by launch.  The pages of the entries are allocated already."""
         if self.cache.state_groups:
             return None
+        n_own = len(entries)
+        nd = sum(1 for e in entries if len(e.tokens) == 1)
+        if nd and _bucket(nd) > nd:      # fill the bucket of one-token sequences with padding entries
+            entries = list(entries) + [SequenceInput(0, [0], 0, [0])] * (_bucket(nd) - nd)
         shape = describe_step(entries, self.cache)
+        n_fill = len(entries) - n_own
         wb = self._width_bucket(shape.width)
         if wb < shape.width:
             return None
@@ -288,11 +296,19 @@ class StepGraphs:
         cap.graph.replay()
         self.replays += 1
         self.kernels_replayed += self.kernels_per_graph.get(key, 0)
-        batch = dataclasses.replace(cap.batch, logit_rows=shape.logit_rows, order=shape.order,
-                                    slots=shape.slots)
+        # the caller owns what it gets (the graph's own logits are overwritten by its next
+        # replay) and sees its own entries only: the padding entries' rows lie in one run, behind
+        # those of its one-token sequences and before those of its prompt portions
+        if n_fill:
+            a = shape.logit_rows[n_own][0]       # the padding entries' rows: a .. a + n_fill - 1
+            logits = torch.cat([cap.logits[:a], cap.logits[a + n_fill:]])
+            logit_rows = [[r if r < a else r - n_fill for r in rows] for rows in shape.logit_rows[:n_own]]
+            order = [i for i in shape.order if i < n_own]
+        else:
+            logits, logit_rows, order = cap.logits.clone(), shape.logit_rows, shape.order
+        batch = dataclasses.replace(cap.batch, logit_rows=logit_rows, order=order, slots=shape.slots)
         batch.num_patches = num_patches
-        # the caller owns what it gets: the graph's own logits are overwritten by its next replay
-        return cap.logits.clone(), batch
+        return logits, batch
 
     def launched(self, host_seconds: float, start, end) -> None:
         """The runner's report on the step that ``run`` just declined: the host's time to issue
@@ -302,14 +318,14 @@ class StepGraphs:
             self._launching = None
 
     def _host_bound(self, key) -> bool:
-        """Whether the bucket's last launched step kept the GPU waiting for the host (waits
-        for that step's events: once per bucket, where a capture would synchronise anyway).
-        A bucket found to be bound by the device is remembered and not timed again."""
+        """Whether the bucket's last launched step kept the GPU waiting for the host; False
+        while that step has not finished (the host is not made to wait for it: the bucket is
+        asked about again the next time).  A bucket found to be bound by the device is
+        remembered and not timed again."""
         t = self.timings.get(key)
-        if t is None:
+        if t is None or not t[2].query():
             return False
         host_s, start, end = t
-        end.synchronize()
         device_s = start.elapsed_time(end) / 1e3
         if host_s >= self.host_bound_share * device_s:
             return True

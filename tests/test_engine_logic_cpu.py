@@ -293,6 +293,22 @@ def test_a_step_padded_to_a_bucket_keeps_its_rows_and_parks_the_rest_on_page_zer
         lay = PackedLayout(t, nb, 2, shape.width, len(groups))
         with pytest.raises(ValueError, match="does not fit"):
             fill_packed(np.zeros(lay.size, dtype=np.int32), lay, shape, r.cache, groups)
+    # padding sequences given as entries (state slot 0): one-token sequences come first, so they
+    # follow the step's own one-token sequence; block table rows of zeros, cache slot 0
+    with_dummies = entries + [SequenceInput(0, [0], 0, [0])] * 3
+    shape4 = describe_step(with_dummies, r.cache)
+    assert shape4.q_lens == [1, 1, 1, 1, 37] and shape4.order == [1, 2, 3, 4, 0] and shape4.slots[1:4] == [0, 0, 0]
+    assert StepGraphs.padded_tokens(shape4) == 4 + 48 == StepGraphs.padded_tokens(shape) + 3
+    lay4 = PackedLayout(4 + 48, 6, 5, shape.width, len(groups))
+    d = np.zeros(lay4.size, dtype=np.int32)
+    fill_packed(d, lay4, shape4, r.cache, groups)
+    assert lay4.seg(d, "cu_q_lens").tolist() == [0, 1, 2, 3, 4, 41, 52]
+    assert lay4.seg(d, "seq_lens").tolist() == [31, 1, 1, 1, 37, 11]
+    assert lay4.seg(d, "logit_indices").tolist() == [0, 1, 2, 3, 40]
+    for gi in range(len(groups)):
+        bt = lay4.seg(d, ("bt", gi)).reshape(6, lay4.width)
+        assert (bt[1:4] == 0).all() and (bt[5] == 0).all() and (lay4.seg(d, ("sm", gi))[1:4] == 0).all()
+    check_packed(d, lay4, r.cache, groups, 512, 512)
     # the launched step that runs with its bucket's rows
     batch = build_step_batch(entries, r.cache, "cpu", pad_to=StepGraphs.padded_tokens)
     assert batch.num_tokens == 49 and batch.num_seqs == 3 and batch.q_lens == [1, 37, 11]
@@ -312,10 +328,10 @@ def test_step_graphs_capture_only_where_the_host_is_the_bound(tiny_model_dirs, t
 
     class Event:
         def __init__(self, ms):
-            self.ms, self.waited = ms, False
+            self.ms, self.done = ms, True
 
-        def synchronize(self):
-            self.waited = True
+        def query(self):
+            return self.done
 
         def elapsed_time(self, other):
             return other.ms - self.ms
@@ -328,7 +344,10 @@ def test_step_graphs_capture_only_where_the_host_is_the_bound(tiny_model_dirs, t
     sg._launching = "a"
     end = Event(4.0)
     sg.launched(0.0039, Event(0.0), end)             # 3.9 ms of host time for 4.0 ms on the device
-    assert sg._launching is None and sg._host_bound("a") and end.waited and "a" not in sg.device_bound
+    end.done = False                                 # the step has not finished: not known yet, asked again
+    assert sg._launching is None and not sg._host_bound("a") and "a" in sg.timings
+    end.done = True
+    assert sg._host_bound("a") and "a" not in sg.device_bound
     sg._launching = "b"
     sg.launched(0.0019, Event(0.0), Event(8.2))      # 1.9 ms of host time for 8.2 ms on the device
     assert not sg._host_bound("b") and "b" in sg.device_bound and "b" not in sg.timings

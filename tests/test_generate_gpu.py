@@ -197,7 +197,8 @@ def test_published_shapes_logits_agree_across_dtypes(name, layers):
 def test_steps_replayed_as_graphs_give_the_bits_of_launched_steps(dtype, tiny_model_dirs):
     """Steps whose bucket of shapes comes again are captured and replayed as CUDA graphs
     (from the third time on): prompts of six lengths of one bucket (33 to 48 tokens) one after
-    the other, a two-sequence mixed step with portions of 3 to 7 tokens, decode steps.  Every
+    the other, a two-sequence mixed step with portions of 3 to 7 tokens, decode steps, steps of
+    three or four decoded tokens beside a portion (one bucket: padding entries fill it).  Every
     step's logits equal, bit for bit, those of a runner that launches every step kernel by
     kernel with no row of padding; and the graphs were in fact used, one for each bucket."""
     from deterministic_inference_b200 import EngineConfig
@@ -211,25 +212,43 @@ def test_steps_replayed_as_graphs_give_the_bits_of_launched_steps(dtype, tiny_mo
     assert runners[0].step_graphs is not None and runners[1].step_graphs is None
     lens = (40, 37, 48, 33, 45, 41)
     portions = (5, 3, 7, 4, 6)
-    prompts = _prompts(vocab, lens + (25,) * 5, 21)
+    prompts = _prompts(vocab, lens + (25,) * 10, 21)
     outs = [[], []]
     for k, r in enumerate(runners):
         slots = [r.cache.allocate_slot() for _ in prompts]
+        pos = list(lens)                                            # tokens of the first six requests in the cache
+
+        def done(logits):
+            torch.cuda.synchronize()        # the step graphs decide by a finished step's times
+            return logits.clone()
+
         for s, p in zip(slots[:6], prompts[:6]):                    # one bucket, six lengths
-            outs[k].append(r.step([SequenceInput(s, p, 0, [0, len(p) - 1])])[0].clone())
+            outs[k].append(done(r.step([SequenceInput(s, p, 0, [0, len(p) - 1])])[0]))
+
+        def decodes(which, token):
+            es = [SequenceInput(slots[i], [token], pos[i], [0]) for i in which]
+            for i in which:
+                pos[i] += 1
+            return es
+
         for rep in range(5):                                        # a decode beside a portion
-            s_dec, s_pre = slots[0], slots[6 + rep]
             n = portions[rep]
-            outs[k].append(r.step([SequenceInput(s_pre, prompts[6 + rep][:n], 0, [n - 1]),
-                                   SequenceInput(s_dec, [rep + 1], lens[0] + rep, [0])])[0].clone())
+            outs[k].append(done(r.step([SequenceInput(slots[6 + rep], prompts[6 + rep][:n], 0, [n - 1])]
+                                       + decodes((0,), rep + 1))[0]))
         for step in range(6):                                       # pure decode of three requests
-            outs[k].append(r.step([SequenceInput(slots[i], [step + 7], lens[i] + step, [0])
-                                   for i in (1, 2, 3)])[0].clone())
-    assert len(outs[0]) == len(outs[1]) == 17
+            outs[k].append(done(r.step(decodes((1, 2, 3), step + 7))[0]))
+        for rep in range(5):                                        # three or four decodes beside a portion:
+            n = portions[rep]                                       # one bucket of four one-token sequences
+            which = (1, 2, 3, 4) if rep % 2 else (5, 2, 4)
+            logits, batch = r.step(decodes(which, rep + 20)
+                                   + [SequenceInput(slots[11 + rep], prompts[11 + rep][:n], 0, [n - 1])])
+            assert len(batch.logit_rows) == len(which) + 1 and all(len(x) == 1 for x in batch.logit_rows)
+            outs[k].append(done(logits[[x[0] for x in batch.logit_rows]]))
+    assert len(outs[0]) == len(outs[1]) == 22
     for a, b in zip(*outs):
         assert torch.equal(a, b)
     g = runners[0].step_graphs
-    assert g.captures == 2 and g.replays == 4 + 3           # the two buckets, from their third step on
+    assert g.captures == 3 and g.replays == 4 + 3 + 3       # the three buckets, from their third step on
     assert runners[0].decode_graphs.replays == 6            # the pure-decode steps
 
 
