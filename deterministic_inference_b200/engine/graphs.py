@@ -202,7 +202,7 @@ class StepGraphs:
     request's result (they are worked on like a request's rows, so that they hold finite
     numbers and leave such on page 0).  A bucket is captured when it shows up the third time; the least
     recently used graph goes when there are more than ``max_graphs`` (they share one memory
-    pool).  A capture costs three runs of the step, and a replay only wins where the host
+    pool).  A capture costs two runs of the step and the graph's instantiation, and a replay only wins where the host
     issues the step's launches no faster than the GPU runs them: so a bucket's launched steps
     are timed (host time to issue them, device time between two events), and a bucket whose
     launches took the host less than ``host_bound_share`` of the device's time is captured
@@ -359,8 +359,9 @@ class StepGraphs:
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
-            for _ in range(2):
-                self.model.forward(batch, self.cache)
+            # one run before the capture: what the kernels attach to this batch (tile lists,
+            # scratch) is made outside it; the bucket's launched steps have loaded every kernel
+            self.model.forward(batch, self.cache)
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         from ..kernels import ops
