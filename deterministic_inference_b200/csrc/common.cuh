@@ -152,6 +152,64 @@ __device__ __forceinline__ float rms_rstd(float sumsq, int n, float eps) {
   return __frcp_rn(__fsqrt_rn(__fadd_rn(__fdiv_rn(sumsq, (float)n), eps)));
 }
 
+// One (token, head) row of 128 bfloat16 values held by eight lanes: lane l (0..7; `mask` names
+// the eight) has the elements 8l..8l+7 in `lo` and 64+8l..64+8l+7 in `hi`, so a rotation pair
+// lies in one lane.  RMSNorm with the weight nw [128] (or null: none), then the rotate-half
+// rotation by c / sn (the position's cosines and sines of the dimensions 8l..8l+7) if
+// `rotate`.  The sum of squares is taken in the order of the one-warp-per-row kernel (a lane
+// there holds 4 consecutive elements, lanes combine 16, 8, 4, 2, 1 apart: this lane holds
+// that kernel's lanes 2l, 2l+1 (lo) and 2l+16, 2l+17 (hi)), so every kernel that norms a head
+// of 128 gives the same bits.
+__device__ __forceinline__ void qk_row128(uint4& lo, uint4& hi, int l, unsigned mask, const float* nw, float eps,
+                                          bool rotate, const float (&c)[8], const float (&sn)[8]) {
+  float a[8], b[8];
+  const __nv_bfloat162* pl = reinterpret_cast<const __nv_bfloat162*>(&lo);
+  const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&hi);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 x = __bfloat1622float2(pl[k]), y = __bfloat1622float2(ph[k]);
+    a[2 * k] = x.x; a[2 * k + 1] = x.y;
+    b[2 * k] = y.x; b[2 * k + 1] = y.y;
+  }
+  if (nw != nullptr) {
+    float e = __fadd_rn(sumsq4(a[0], a[1], a[2], a[3]), sumsq4(b[0], b[1], b[2], b[3]));
+    float o = __fadd_rn(sumsq4(a[4], a[5], a[6], a[7]), sumsq4(b[4], b[5], b[6], b[7]));
+#pragma unroll
+    for (int sh = 4; sh > 0; sh >>= 1) {
+      e = __fadd_rn(e, __shfl_xor_sync(mask, e, sh));
+      o = __fadd_rn(o, __shfl_xor_sync(mask, o, sh));
+    }
+    const float ss = __fadd_rn(e, o);
+    const float rstd = rms_rstd(ss, 128, eps);
+    const float4 w0 = *reinterpret_cast<const float4*>(nw + l * 8);
+    const float4 w1 = *reinterpret_cast<const float4*>(nw + l * 8 + 4);
+    const float4 w2 = *reinterpret_cast<const float4*>(nw + 64 + l * 8);
+    const float4 w3 = *reinterpret_cast<const float4*>(nw + 64 + l * 8 + 4);
+    const float wa[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+    const float wb[8] = {w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      a[k] = norm_scale(a[k], rstd, wa[k]);
+      b[k] = norm_scale(b[k], rstd, wb[k]);
+    }
+  }
+  if (rotate) {
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float x = a[k], y = b[k];
+      a[k] = rope_first(x, y, c[k], sn[k]);
+      b[k] = rope_second(x, y, c[k], sn[k]);
+    }
+  }
+  __nv_bfloat162* ql = reinterpret_cast<__nv_bfloat162*>(&lo);
+  __nv_bfloat162* qh = reinterpret_cast<__nv_bfloat162*>(&hi);
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    ql[k] = __floats2bfloat162_rn(a[2 * k], a[2 * k + 1]);
+    qh[k] = __floats2bfloat162_rn(b[2 * k], b[2 * k + 1]);
+  }
+}
+
 static inline int ceil_div_host(long long a, long long b) { return (int)((a + b - 1) / b); }
 
 // "Done once on the current device": a kernel's attributes (its shared-memory limit) are

@@ -435,58 +435,9 @@ qk_norm_rope_cache_rows128_kernel(
                         (slot[it] - page * page_size)) * D;
     }
     if (is_q || is_k) {
-      float a[8], b[8];   // elements 8l.. and 64+8l..
-      const __nv_bfloat162* pl = reinterpret_cast<const __nv_bfloat162*>(&lo[it]);
-      const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&hi[it]);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const float2 x = __bfloat1622float2(pl[k]), y = __bfloat1622float2(ph[k]);
-        a[2 * k] = x.x; a[2 * k + 1] = x.y;
-        b[2 * k] = y.x; b[2 * k + 1] = y.y;
-      }
-      const float* nw = is_q ? q_norm_w : k_norm_w;
-      if (nw != nullptr) {
-        // The order of the one-warp-per-row kernel (a lane there holds 4 consecutive
-        // elements, lanes combine 16, 8, 4, 2, 1 apart), so both give the same bits: this
-        // lane holds that kernel's lanes 2l, 2l+1 (a) and 2l+16, 2l+17 (b).
-        float e = __fadd_rn(sumsq4(a[0], a[1], a[2], a[3]), sumsq4(b[0], b[1], b[2], b[3]));
-        float o = __fadd_rn(sumsq4(a[4], a[5], a[6], a[7]), sumsq4(b[4], b[5], b[6], b[7]));
-#pragma unroll
-        for (int sh = 4; sh > 0; sh >>= 1) {
-          e = __fadd_rn(e, __shfl_xor_sync(mask, e, sh));
-          o = __fadd_rn(o, __shfl_xor_sync(mask, o, sh));
-        }
-        const float ss = __fadd_rn(e, o);
-        const float rstd = rms_rstd(ss, D, eps);
-        const float4 w0 = *reinterpret_cast<const float4*>(nw + l * 8);
-        const float4 w1 = *reinterpret_cast<const float4*>(nw + l * 8 + 4);
-        const float4 w2 = *reinterpret_cast<const float4*>(nw + 64 + l * 8);
-        const float4 w3 = *reinterpret_cast<const float4*>(nw + 64 + l * 8 + 4);
-        const float wa[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-        const float wb[8] = {w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          a[k] = norm_scale(a[k], rstd, wa[k]);
-          b[k] = norm_scale(b[k], rstd, wb[k]);
-        }
-      }
-      if (cos_sin != nullptr) {
-        const float c[8] = {c0[it].x, c0[it].y, c0[it].z, c0[it].w, c1[it].x, c1[it].y, c1[it].z, c1[it].w};
-        const float sn[8] = {s0[it].x, s0[it].y, s0[it].z, s0[it].w, s1[it].x, s1[it].y, s1[it].z, s1[it].w};
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const float x = a[k], y = b[k];
-          a[k] = rope_first(x, y, c[k], sn[k]);
-          b[k] = rope_second(x, y, c[k], sn[k]);
-        }
-      }
-      __nv_bfloat162* ql = reinterpret_cast<__nv_bfloat162*>(&lo[it]);
-      __nv_bfloat162* qh = reinterpret_cast<__nv_bfloat162*>(&hi[it]);
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        ql[k] = __floats2bfloat162_rn(a[2 * k], a[2 * k + 1]);
-        qh[k] = __floats2bfloat162_rn(b[2 * k], b[2 * k + 1]);
-      }
+      const float c[8] = {c0[it].x, c0[it].y, c0[it].z, c0[it].w, c1[it].x, c1[it].y, c1[it].z, c1[it].w};
+      const float sn[8] = {s0[it].x, s0[it].y, s0[it].z, s0[it].w, s1[it].x, s1[it].y, s1[it].z, s1[it].w};
+      qk_row128(lo[it], hi[it], l, mask, is_q ? q_norm_w : k_norm_w, eps, cos_sin != nullptr, c, sn);
     }
     *reinterpret_cast<uint4*>(dst + l * 8) = lo[it];
     *reinterpret_cast<uint4*>(dst + 64 + l * 8) = hi[it];

@@ -44,11 +44,13 @@ constexpr int THREADS = 320;   // warps 0, 1: copies and products; 2-9: epilogue
 constexpr int EPI_WARPS = 8;
 // Features per tile = MMA N: 256 (GATED: 128 gate + 128 up rows), or 128 for products with so
 // few tiles of 256 that they would leave SMs idle.  Stages of the ring: what fits.
-template <int BNL> struct Tile {
+// (QKV: the epilogue that norms and rotates heads stages 8 KB a warp instead of 4, a stage of
+// the ring less)
+template <int BNL, bool QKV = false> struct Tile {
   static constexpr int B_BYTES = BNL * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = BNL == 256 ? 4 : 6;
-  static constexpr size_t SMEM_BYTES =
-      (size_t)STAGES * STAGE_BYTES + EPI_WARPS * 4096 + (2 * STAGES + 4) * 8 + 16 + 1024;
+  static constexpr int STAGES = (BNL == 256 ? 4 : 6) - (QKV ? 1 : 0);
+  static constexpr int EPI_BYTES = EPI_WARPS * 4096 * (QKV ? 2 : 1);
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + EPI_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
 };
 
 __device__ int dib_gemm_large_error_word = 0;
@@ -149,6 +151,119 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void*
 __device__ __forceinline__ void stage_piece(unsigned char* stage, int lane, int c, uint4 v) {
   *reinterpret_cast<uint4*>(stage + lane * 128 + ((c ^ (lane & 7)) << 4)) = v;
 }
+// What the epilogue of a fused q/k/v projection needs beside the product (QKV form): the rows
+// of the product are tokens, its columns the heads of 128 of q, then k, then v; a warp's half
+// of a tile's 256 columns is one head.  The epilogue rounds the product to bfloat16 as a
+// stored projection would be, applies the q/k RMSNorm and the rotation with the arithmetic of
+// the q/k kernels of elementwise.cu (sumsq4 in the butterfly's order, rms_rstd, norm_scale,
+// rope_first/second: the same bits), and writes q rows to the output and k, v rows to the
+// tokens' cache slots.
+struct QkvEpilogue {
+  const float* q_norm_w;        // [128] or null
+  const float* k_norm_w;
+  float eps;
+  const float* cos_sin;         // [max_pos, 128] rows cos | sin, or null
+  int max_pos;
+  const int* positions;         // [M]
+  const int* slot_mapping;      // [M] page * page_size + offset, or negative
+  __nv_bfloat16* cache;         // [pages, 2, Hkv, page_size, 128] or null
+  __nv_bfloat16* q_out;         // [M, Hq, 128]
+  long long num_pages;
+  int page_size, Hq, Hkv, M;
+};
+
+// The QKV epilogue of a warp's 32 token rows and one head (see QkvEpilogue), in two stages.
+// First every lane rounds its own row of the product to bfloat16 and puts it into the warp's
+// 8 KB of shared memory (two blocks of 32 rows x 128 bytes, swizzled).  Then the warp takes
+// the rows back four at a time, eight lanes a row (lane l: the dimensions 8l..8l+7 and
+// 64+8l..64+8l+7, a rotation pair in one lane), runs qk_row128 of common.cuh on them, the
+// function the q/k kernels run, and writes whole rows of 128 bytes: the norm weights, the
+// rotation table and the stores are then read and written by neighbouring lanes together.
+__device__ __forceinline__ void store_rows_qkv(unsigned src, __nv_bfloat16* q_out, unsigned char* stage, int lane,
+                                               int row0, int n0, int half, const QkvEpilogue& qk) {
+  const int head = (n0 >> 7) + half;
+  if (head >= qk.Hq + 2 * qk.Hkv) return;          // the tile's second half lies beyond the last head
+  const bool is_q = head < qk.Hq, is_k = !is_q && head < qk.Hq + qk.Hkv;
+  const unsigned acc = src + half * 128;
+  __syncwarp();                                     // the rows of the tile before this one have been taken back
+#pragma unroll
+  for (int blk = 0; blk < 2; ++blk) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      unsigned v[32];
+      tc_ld32(acc + blk * 64 + h * 32, v);
+      tc_wait_ld();
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        stage_piece(stage + blk * EPI_STAGE_BYTES, lane, h * 4 + q,
+                    make_uint4(pack2_bf16(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])),
+                               pack2_bf16(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])),
+                               pack2_bf16(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])),
+                               pack2_bf16(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]))));
+    }
+  }
+  __syncwarp();
+  const int l = lane & 7;
+  const unsigned mask = 0xffu << (lane & 24);
+  const float* nw = is_q ? qk.q_norm_w : (is_k ? qk.k_norm_w : nullptr);
+  const bool rotate = qk.cos_sin != nullptr && (is_q || is_k);
+  // where row r's result goes (an element offset from q_out or the cache, or -1) and its
+  // table row: lane r finds both for its own row, the eight lanes of a row fetch them by shuffle
+  long long my_dst = -1;
+  int my_pos = 0;
+  {
+    const int token = row0 + lane;
+    if (token < qk.M) {
+      if (rotate) {
+        const int p = qk.positions[token];
+        my_pos = p < 0 ? 0 : (p >= qk.max_pos ? qk.max_pos - 1 : p);
+      }
+      if (is_q) {
+        my_dst = ((long long)token * qk.Hq + head) * 128;
+      } else if (qk.cache != nullptr) {
+        const int slot = qk.slot_mapping[token];
+        if (slot >= 0) {
+          const long long page = slot / qk.page_size;
+          if (page < qk.num_pages) {
+            const int h = is_k ? head - qk.Hq : head - qk.Hq - qk.Hkv;
+            my_dst = ((((page * 2 + (is_k ? 0 : 1)) * qk.Hkv + h) * qk.page_size) + (slot - page * qk.page_size)) * 128;
+          }
+        }
+      }
+    }
+  }
+  __nv_bfloat16* base = is_q ? q_out : qk.cache;
+  // the table values of a row are asked for one round ahead of their use (a store to the
+  // output may not be passed by a later load, as far as the compiler knows)
+  float4 tv[4] = {};
+  auto table = [&](int it, float4 (&t)[4]) {
+    if (rotate) {
+      const int p = __shfl_sync(0xffffffffu, my_pos, it * 4 + (lane >> 3));
+      const float* tab = qk.cos_sin + (size_t)p * 128 + l * 8;
+      t[0] = *reinterpret_cast<const float4*>(tab);
+      t[1] = *reinterpret_cast<const float4*>(tab + 4);
+      t[2] = *reinterpret_cast<const float4*>(tab + 64);
+      t[3] = *reinterpret_cast<const float4*>(tab + 68);
+    }
+  };
+  table(0, tv);
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 4 + (lane >> 3);
+    uint4 lo = *reinterpret_cast<const uint4*>(stage + r * 128 + ((l ^ (r & 7)) << 4));
+    uint4 hi = *reinterpret_cast<const uint4*>(stage + EPI_STAGE_BYTES + r * 128 + ((l ^ (r & 7)) << 4));
+    const float c[8] = {tv[0].x, tv[0].y, tv[0].z, tv[0].w, tv[1].x, tv[1].y, tv[1].z, tv[1].w};
+    const float sn[8] = {tv[2].x, tv[2].y, tv[2].z, tv[2].w, tv[3].x, tv[3].y, tv[3].z, tv[3].w};
+    if (it + 1 < 8) table(it + 1, tv);
+    const long long d = __shfl_sync(0xffffffffu, my_dst, r);
+    if (is_q || is_k) qk_row128(lo, hi, l, mask, nw, qk.eps, rotate, c, sn);
+    if (d >= 0) {
+      *reinterpret_cast<uint4*>(base + d + l * 8) = lo;
+      *reinterpret_cast<uint4*>(base + d + 64 + l * 8) = hi;
+    }
+  }
+}
+
 template <typename OutT, bool GATED, int BNL>
 __device__ __forceinline__ void store_rows(unsigned src, const CUtensorMap* map_out, unsigned char* stage,
                                            int lane, int row0, int n0, int half) {
@@ -214,18 +329,19 @@ __device__ __forceinline__ void stores_done(int lane) {
   __syncwarp();
 }
 
-template <typename OutT, bool GATED, int BNL>
+template <typename OutT, bool GATED, int BNL, bool QKV = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                  const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int m_tiles, int n_tiles) {
+                  const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int m_tiles, int n_tiles,
+                  const __grid_constant__ QkvEpilogue qk) {
   static_assert(!GATED || BNL == 256, "the gated epilogue pairs 128 gate rows with 128 up rows");
-  using TL = Tile<BNL>;
+  using TL = Tile<BNL, QKV>;
   constexpr int B_BYTES = TL::B_BYTES, STAGE_BYTES = TL::STAGE_BYTES, STAGES = TL::STAGES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* epi_stage = smem + STAGES * STAGE_BYTES;      // 4 KB to each epilogue warp
-  unsigned long long* full = reinterpret_cast<unsigned long long*>(epi_stage + EPI_WARPS * EPI_STAGE_BYTES);
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(epi_stage + TL::EPI_BYTES);
   unsigned long long* empty = full + STAGES;
   unsigned long long* acc_full = empty + STAGES;     // [2] a tile's accumulator is complete
   unsigned long long* acc_empty = acc_full + 2;      // [2] the epilogue has read it (128 arrivals)
@@ -341,8 +457,12 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       got = __all_sync(0xffffffffu, got);     // tcgen05.ld below is warp-wide
       if (!got) { ok = false; break; }
       tc_fence_after();
-      store_rows<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, &map_out, epi_stage + (warp - 2) * EPI_STAGE_BYTES,
-                                   lane, m0 + quarter * 32, n0, half);
+      if (QKV)
+        store_rows_qkv(tmem + buf * BNL + lane_base, qk.q_out, epi_stage + (warp - 2) * 2 * EPI_STAGE_BYTES, lane,
+                       m0 + quarter * 32, n0, half, qk);
+      else
+        store_rows<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, &map_out, epi_stage + (warp - 2) * EPI_STAGE_BYTES,
+                                     lane, m0 + quarter * 32, n0, half);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
@@ -421,25 +541,26 @@ __device__ __forceinline__ void tc_mma_pair(unsigned tmem_d, unsigned long long 
       : "memory");
 }
 
-template <int BNL> struct PairTile {
+template <int BNL, bool QKV = false> struct PairTile {
   static constexpr int B_BYTES = (BNL / 2) * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // per CTA
-  static constexpr int STAGES = 6;
-  static constexpr size_t SMEM_BYTES =
-      (size_t)STAGES * STAGE_BYTES + EPI_WARPS * 4096 + (2 * STAGES + 4) * 8 + 16 + 1024;
+  static constexpr int STAGES = QKV ? 5 : 6;
+  static constexpr int EPI_BYTES = EPI_WARPS * 4096 * (QKV ? 2 : 1);
+  static constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + EPI_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
 };
 
-template <typename OutT, bool GATED, int BNL>
+template <typename OutT, bool GATED, int BNL, bool QKV = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                 const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int m_tiles, int n_tiles) {
+                 const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int m_tiles, int n_tiles,
+                 const __grid_constant__ QkvEpilogue qk) {
   static_assert(!GATED || BNL == 256, "the gated epilogue pairs 128 gate rows with 128 up rows");
-  using TL = PairTile<BNL>;
+  using TL = PairTile<BNL, QKV>;
   constexpr int STAGE_BYTES = TL::STAGE_BYTES, STAGES = TL::STAGES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* epi_stage = smem + STAGES * STAGE_BYTES;      // 4 KB to each epilogue warp
-  unsigned long long* full = reinterpret_cast<unsigned long long*>(epi_stage + EPI_WARPS * EPI_STAGE_BYTES);
+  unsigned long long* full = reinterpret_cast<unsigned long long*>(epi_stage + TL::EPI_BYTES);
   unsigned long long* empty = full + STAGES;
   unsigned long long* acc_full = empty + STAGES;     // [2]
   unsigned long long* acc_empty = acc_full + 2;      // [2]
@@ -553,8 +674,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       got = __all_sync(0xffffffffu, got);     // tcgen05.ld below is warp-wide
       if (!got) { ok = false; break; }
       tc_fence_after();
-      store_rows<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, &map_out, epi_stage + (warp - 2) * EPI_STAGE_BYTES,
-                                   lane, m0 + quarter * 32, n0, half);
+      if (QKV)
+        store_rows_qkv(tmem + buf * BNL + lane_base, qk.q_out, epi_stage + (warp - 2) * 2 * EPI_STAGE_BYTES, lane,
+                       m0 + quarter * 32, n0, half, qk);
+      else
+        store_rows<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, &map_out, epi_stage + (warp - 2) * EPI_STAGE_BYTES,
+                                     lane, m0 + quarter * 32, n0, half);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty0 + buf * 8);
@@ -617,19 +742,20 @@ bool make_out_map(CUtensorMap* map, void* ptr, long long M, long long N) {
              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <typename OutT, bool GATED, int BNL>
+// (QKV: `out` is the q rows [M, out_cols]; the k and v rows go where `qk` says)
+template <typename OutT, bool GATED, int BNL, bool QKV = false>
 int launch_large(const void* x, const void* w, void* out, int M, int N, int K, int sm_count,
-                 cudaStream_t st) {
+                 cudaStream_t st, const QkvEpilogue& qk = QkvEpilogue{}) {
   CUtensorMap mx, mw, mo;
   if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, GATED ? 2ll * N : (long long)N, K, 128) ||
-      !make_out_map<OutT>(&mo, out, M, N))
+      !make_out_map<OutT>(&mo, out, M, QKV ? (long long)qk.Hq * 128 : (long long)N))
     return DIB_LAUNCH_FAILED;
   const int m_tiles = (M + BM - 1) / BM;
   const int n_tiles = (N + (GATED ? BNL / 2 : BNL) - 1) / (GATED ? BNL / 2 : BNL);
   const long long tiles = (long long)m_tiles * n_tiles;
   if (tiles > (1ll << 30)) return DIB_BAD_SIZE;
-  auto kern = gemm_large_kernel<OutT, GATED, BNL>;
-  constexpr size_t SMEM_BYTES = Tile<BNL>::SMEM_BYTES;
+  auto kern = gemm_large_kernel<OutT, GATED, BNL, QKV>;
+  constexpr size_t SMEM_BYTES = Tile<BNL, QKV>::SMEM_BYTES;
   static DeviceOnce attr_set;
   if (!attr_set.done()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) !=
@@ -638,24 +764,24 @@ int launch_large(const void* x, const void* w, void* out, int M, int N, int K, i
     attr_set.mark();
   }
   const int grid = (int)(tiles < sm_count ? tiles : sm_count);
-  dib_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, st, mx, mw, mo, M, N, K, m_tiles, n_tiles);
+  dib_launch(kern, dim3(grid), dim3(THREADS), SMEM_BYTES, st, mx, mw, mo, M, N, K, m_tiles, n_tiles, qk);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
 
-template <typename OutT, bool GATED, int BNL>
+template <typename OutT, bool GATED, int BNL, bool QKV = false>
 int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, int sm_count,
-                cudaStream_t st) {
+                cudaStream_t st, const QkvEpilogue& qk = QkvEpilogue{}) {
   CUtensorMap mx, mw, mo;
   if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, GATED ? 2ll * N : (long long)N, K, BNL / 2) ||
-      !make_out_map<OutT>(&mo, out, M, N))
+      !make_out_map<OutT>(&mo, out, M, QKV ? (long long)qk.Hq * 128 : (long long)N))
     return DIB_LAUNCH_FAILED;
   const int m_tiles = (M + 2 * BM - 1) / (2 * BM);
   const int n_tiles = (N + (GATED ? BNL / 2 : BNL) - 1) / (GATED ? BNL / 2 : BNL);
   const long long tiles = (long long)m_tiles * n_tiles;
   if (tiles > (1ll << 30) || sm_count < 2) return DIB_BAD_SIZE;
-  auto kern = gemm_pair_kernel<OutT, GATED, BNL>;
-  constexpr size_t SMEM_BYTES = PairTile<BNL>::SMEM_BYTES;
+  auto kern = gemm_pair_kernel<OutT, GATED, BNL, QKV>;
+  constexpr size_t SMEM_BYTES = PairTile<BNL, QKV>::SMEM_BYTES;
   static DeviceOnce attr_set;
   if (!attr_set.done()) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) !=
@@ -678,7 +804,7 @@ int launch_pair(const void* x, const void* w, void* out, int M, int N, int K, in
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = dib_pdl_enabled() ? 2 : 1;
-  cudaLaunchKernelEx(&cfg, kern, mx, mw, mo, M, N, K, m_tiles, n_tiles);
+  cudaLaunchKernelEx(&cfg, kern, mx, mw, mo, M, N, K, m_tiles, n_tiles, qk);
   DIB_CHECK_LAUNCH();
   return DIB_OK;
 }
@@ -748,6 +874,31 @@ int dib_gemm_bf16_large_gated(const void* x, const void* w, void* out, int M, in
   return tile_shape(M, 2 * I, sm_count) == 2
              ? launch_pair<__nv_bfloat16, true, 256>(x, w, out, M, I, K, sm_count, st)
              : launch_large<__nv_bfloat16, true, 256>(x, w, out, M, I, K, sm_count, st);
+}
+
+// The fused q/k/v projection of a prompt portion: x [M, K] times w [(Hq + 2 Hkv) * 128, K]^T,
+// each head's row rounded to bfloat16, q and k normed (weights [128], or null) and rotated
+// (table [max_pos, 128] rows cos | sin, or null) as by dib_qk_norm_rope_cache; q rows to q_out
+// [M, Hq, 128], k and v rows to the tokens' cache slots (cache null: not written).  Heads of
+// 128 only; K a multiple of 8; pointers 16-byte aligned.
+int dib_gemm_bf16_large_qkv(const void* x, const void* w, void* q_out, int M, int K, int Hq, int Hkv,
+                            const float* q_norm_w, const float* k_norm_w, float eps, const float* cos_sin,
+                            int max_pos, const int* positions, const int* slot_mapping, void* cache,
+                            long long num_pages, int page_size, int sm_count, cudaStream_t st) {
+  if (M == 0) return DIB_OK;
+  const int N = (Hq + 2 * Hkv) * 128;
+  if (K < 8 || K % 8 != 0 || sm_count < 1 || Hq < 1 || Hkv < 1 || page_size < 1) return DIB_BAD_SIZE;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(q_out) |
+       reinterpret_cast<uintptr_t>(cache)) % 16 != 0)
+    return DIB_BAD_ALIGN;
+  QkvEpilogue qk = {};
+  qk.q_norm_w = q_norm_w; qk.k_norm_w = k_norm_w; qk.eps = eps; qk.cos_sin = cos_sin; qk.max_pos = max_pos;
+  qk.positions = positions; qk.slot_mapping = slot_mapping; qk.cache = (__nv_bfloat16*)cache;
+  qk.q_out = (__nv_bfloat16*)q_out;
+  qk.num_pages = num_pages; qk.page_size = page_size; qk.Hq = Hq; qk.Hkv = Hkv; qk.M = M;
+  return tile_shape(M, N, sm_count) == 2
+             ? launch_pair<__nv_bfloat16, false, 256, true>(x, w, q_out, M, N, K, sm_count, st, qk)
+             : launch_large<__nv_bfloat16, false, 256, true>(x, w, q_out, M, N, K, sm_count, st, qk);
 }
 
 }  // extern "C"

@@ -11,7 +11,7 @@ sid/model/qwen3.py:38).
 from __future__ import annotations
 
 import os
-from ctypes import byref, c_int, c_longlong, c_void_p
+from ctypes import byref, c_float, c_int, c_longlong, c_void_p
 
 import torch
 
@@ -84,6 +84,40 @@ def gated_linear_large(x: torch.Tensor, w_gate_up: torch.Tensor):
     ops._check(st, "gated_linear(bfloat16, many rows)", f"M={m} I={i} K={k}")
     return out
 
+
+
+# DIB200_QKV_EPILOGUE=0 (read once): q/k norm, rotation and cache write stay a kernel of their own
+QKV_EPILOGUE = os.environ.get("DIB200_QKV_EPILOGUE", "1") != "0"
+
+
+def qkv_large(x: torch.Tensor, w_qkv: torch.Tensor, num_heads: int, num_kv_heads: int, q_norm_weight,
+              k_norm_weight, eps: float, cos_sin, positions, kv_cache, slot_mapping, page_size: int):
+    """q [M, Hq, 128] of the fused projection with q/k norm, rotation and cache write in the
+    many-rows product's epilogue, or None where that kernel does not run the step's
+    projection (few rows, the library for all large products, a shape it refuses)."""
+    from . import ops
+    m, k = x.shape
+    if not QKV_EPILOGUE or m <= MAX_ROWS or LARGE_PRODUCTS not in ("own", "auto"):
+        return None
+    n = (num_heads + 2 * num_kv_heads) * 128
+    if w_qkv.shape[0] != n or w_qkv.shape[1] != k or k % 8 != 0 or k < 8 or w_qkv.dtype != torch.bfloat16 \
+            or kv_cache.dtype != torch.bfloat16 or x.data_ptr() % 16 or w_qkv.data_ptr() % 16 \
+            or kv_cache.data_ptr() % 16 or tuple(kv_cache.shape[1:]) != (2, num_kv_heads, page_size, 128):
+        return None
+    for w in (q_norm_weight, k_norm_weight):
+        if w is not None and (w.dtype != torch.float32 or w.shape[0] != 128):
+            return None
+    if positions.dtype != torch.int32 or slot_mapping.dtype != torch.int32 or positions.shape[0] < m \
+            or slot_mapping.shape[0] < m:
+        return None
+    q = torch.empty(m, num_heads, 128, dtype=torch.bfloat16, device=x.device)
+    st = ops._lib("gemm_bf16_large").dib_gemm_bf16_large_qkv(
+        ops._ptr(x), ops._ptr(w_qkv), ops._ptr(q), c_int(m), c_int(k), c_int(num_heads), c_int(num_kv_heads),
+        ops._ptr(q_norm_weight), ops._ptr(k_norm_weight), c_float(eps), ops._ptr(cos_sin),
+        c_int(cos_sin.shape[0] if cos_sin is not None else 0), ops._ptr(positions), ops._ptr(slot_mapping),
+        ops._ptr(kv_cache), c_longlong(kv_cache.shape[0]), c_int(page_size), c_int(_sms(x.device)), ops._stream())
+    ops._check(st, "qkv projection(bfloat16, many rows)", f"M={m} K={k} heads {num_heads}/{num_kv_heads}")
+    return q
 
 
 def force_large_shape(shape: int) -> None:

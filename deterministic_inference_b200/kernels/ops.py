@@ -415,6 +415,26 @@ def qk_norm_rope_cache(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, hea
     return q
 
 
+def qkv_project(x: torch.Tensor, w_qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                q_norm_weight, k_norm_weight, eps: float, cos_sin, positions: torch.Tensor, kv_cache,
+                slot_mapping, page_size: int) -> torch.Tensor:
+    """The fused q/k/v projection of the step's tokens followed by ``qk_norm_rope_cache``: returns
+    q [T, Hq, D], with k and v in the tokens' cache slots.  Many bfloat16 rows of heads of 128
+    run as ONE kernel when the package's many-rows product is in use (``large_products`` "own"
+    or "auto"): the product's epilogue norms, rotates and writes the cache, with the bits of
+    the two kernels."""
+    x = as_tensor(x)
+    if x.dtype == torch.bfloat16 and x.is_cuda and head_dim == 128 and kv_cache is not None \
+            and (cos_sin is None or cos_sin.shape[1] == head_dim):
+        from . import gemm_bf16
+        q = gemm_bf16.qkv_large(x, w_qkv, num_heads, num_kv_heads, q_norm_weight, k_norm_weight, eps,
+                                cos_sin, positions, kv_cache, slot_mapping, page_size)
+        if q is not None:
+            return q
+    return qk_norm_rope_cache(linear(x, w_qkv), num_heads, num_kv_heads, head_dim, q_norm_weight,
+                              k_norm_weight, eps, cos_sin, positions, kv_cache, slot_mapping, page_size)
+
+
 def reshape_and_cache(k: torch.Tensor, v: torch.Tensor, kv_cache: torch.Tensor,
                       slot_mapping: torch.Tensor) -> None:
     """k, v [T, Hkv, D] into their slots of the paged cache (negative slot: skip)."""

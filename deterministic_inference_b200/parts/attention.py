@@ -66,9 +66,9 @@ class GQAAttention(Mixer):
 
     # -- step
     def forward(self, x, step, cache):
-        qkv = ops.linear(x, self.w_qkv)
-        q = ops.qk_norm_rope_cache(
-            qkv, self.num_heads, self.num_kv_heads, self.head_dim, self.q_norm, self.k_norm,
+        # (one kernel for many bfloat16 rows of heads of 128, else the product and the q/k kernel)
+        q = ops.qkv_project(
+            x, self.w_qkv, self.num_heads, self.num_kv_heads, self.head_dim, self.q_norm, self.k_norm,
             self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
             self.position_encoding.rotary_table(), step.positions,
             cache.kv if cache.writes else None, cache.slot_mapping, cache.page_size)

@@ -955,3 +955,58 @@ def test_gated_product_many_rows_gives_the_bits_of_product_and_gate(m, i, k):
     y = (x.float() @ w.float().T).to(torch.bfloat16).float()
     want = y[:, :i] * torch.sigmoid(y[:, :i]) * y[:, i:]
     torch.testing.assert_close(fused.float(), want, atol=2e-2 * float(want.abs().max()), rtol=3e-2)
+
+
+@pytest.mark.parametrize("t,hq,hkv,k,page_size,norm,rope", [
+    (2048, 16, 8, 1024, 16, True, True), (300, 4, 2, 256, 16, True, True), (130, 8, 1, 384, 32, False, True),
+    (700, 5, 5, 200, 8, True, False), (257, 3, 1, 72, 64, False, False)])
+def test_qkv_projection_with_the_norms_in_its_epilogue_gives_the_bits_of_the_two_kernels(t, hq, hkv, k, page_size,
+                                                                                         norm, rope):
+    """The fused q/k/v projection of many bfloat16 rows whose epilogue norms q and k, rotates them
+    and writes k and v to the cache (one kernel, on one CTA a tile and on a pair of CTAs),
+    against the same product followed by the q/k kernel: the same q rows and the same cache,
+    bit for bit; with and without norm weights and a rotation, an odd number of heads (the
+    last tile's second half lies beyond them), token counts and depths off the tile's sizes,
+    slots spread over pages, some tokens without a slot."""
+    from deterministic_inference_b200.kernels import gemm_bf16
+    o = ops()
+    torch.manual_seed(53)
+    d = 128
+    x = torch.randn(t, k, device="cuda").to(torch.bfloat16)
+    w = (0.08 * torch.randn((hq + 2 * hkv) * d, k, device="cuda")).to(torch.bfloat16)
+    qn = (1 + 0.1 * torch.randn(d, device="cuda")) if norm else None
+    kn = (1 + 0.1 * torch.randn(d, device="cuda")) if norm else None
+    max_pos = 4096
+    table = None
+    if rope:
+        inv = 1.0 / (10000.0 ** (torch.arange(0, d // 2, dtype=torch.float32, device="cuda") / (d // 2)))
+        fr = torch.outer(torch.arange(max_pos, dtype=torch.float32, device="cuda"), inv)
+        table = torch.cat([fr.cos(), fr.sin()], dim=-1).contiguous()
+    positions = torch.randint(0, max_pos, (t,), device="cuda", dtype=torch.int32)
+    pages = -(-t // page_size) + 3
+    slots = torch.randperm((pages - 1) * page_size, device="cuda")[:t].to(torch.int32) + page_size
+    slots[::17] = -1                                        # tokens whose keys are not cached
+    want_cache = torch.full((pages, 2, hkv, page_size, d), 7.0, device="cuda", dtype=torch.bfloat16)
+    want_q = o.qk_norm_rope_cache(gemm_bf16.linear_large(x, w, torch.bfloat16), hq, hkv, d, qn, kn, 1e-6, table,
+                                  positions, want_cache, slots, page_size)
+    try:
+        for shape in (1, 2):
+            gemm_bf16.force_large_shape(shape)
+            cache = torch.full_like(want_cache, 7.0)
+            q = gemm_bf16.qkv_large(x, w, hq, hkv, qn, kn, 1e-6, table, positions, cache, slots, page_size)
+            assert q is not None and torch.equal(q, want_q), shape
+            assert torch.equal(cache, want_cache), shape
+    finally:
+        gemm_bf16.force_large_shape(-1)
+    assert o.kernel_status().get("gemm_bf16_large", 0) == 0
+    # against float32 arithmetic on the rounded product
+    y = (x.float() @ w.float().T).to(torch.bfloat16).float().view(t, hq + 2 * hkv, d)
+    qf = y[:, :hq]
+    if norm:
+        qf = qf * torch.rsqrt(qf.pow(2).mean(-1, keepdim=True) + 1e-6) * qn
+    if rope:
+        cs = table[positions.long()]
+        c, s = cs[:, None, :d // 2], cs[:, None, d // 2:]
+        a, b = qf[..., :d // 2], qf[..., d // 2:]
+        qf = torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+    torch.testing.assert_close(want_q.float(), qf, atol=3e-2 * float(qf.abs().max()), rtol=3e-2)
