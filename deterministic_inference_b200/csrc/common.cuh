@@ -160,9 +160,9 @@ __device__ __forceinline__ float rms_rstd(float sumsq, int n, float eps) {
 // there holds 4 consecutive elements, lanes combine 16, 8, 4, 2, 1 apart: this lane holds
 // that kernel's lanes 2l, 2l+1 (lo) and 2l+16, 2l+17 (hi)), so every kernel that norms a head
 // of 128 gives the same bits.
-__device__ __forceinline__ void qk_row128(uint4& lo, uint4& hi, int l, unsigned mask, const float* nw, float eps,
-                                          bool rotate, const float (&c)[8], const float (&sn)[8]) {
-  float a[8], b[8];
+// (In three steps, so that a kernel with several rows in hand can take the steps of all of
+// them together: the row's 1/rms; the lane's norm weights; norm, rotation and rounding.)
+__device__ __forceinline__ void qk_row128_unpack(const uint4& lo, const uint4& hi, float (&a)[8], float (&b)[8]) {
   const __nv_bfloat162* pl = reinterpret_cast<const __nv_bfloat162*>(&lo);
   const __nv_bfloat162* ph = reinterpret_cast<const __nv_bfloat162*>(&hi);
 #pragma unroll
@@ -171,22 +171,38 @@ __device__ __forceinline__ void qk_row128(uint4& lo, uint4& hi, int l, unsigned 
     a[2 * k] = x.x; a[2 * k + 1] = x.y;
     b[2 * k] = y.x; b[2 * k + 1] = y.y;
   }
-  if (nw != nullptr) {
-    float e = __fadd_rn(sumsq4(a[0], a[1], a[2], a[3]), sumsq4(b[0], b[1], b[2], b[3]));
-    float o = __fadd_rn(sumsq4(a[4], a[5], a[6], a[7]), sumsq4(b[4], b[5], b[6], b[7]));
+}
+// this lane's two sums of the butterfly: lanes combine them 4, 2, 1 apart, then e + o
+__device__ __forceinline__ void qk_row128_sums(const uint4& lo, const uint4& hi, float& e, float& o) {
+  float a[8], b[8];
+  qk_row128_unpack(lo, hi, a, b);
+  e = __fadd_rn(sumsq4(a[0], a[1], a[2], a[3]), sumsq4(b[0], b[1], b[2], b[3]));
+  o = __fadd_rn(sumsq4(a[4], a[5], a[6], a[7]), sumsq4(b[4], b[5], b[6], b[7]));
+}
+__device__ __forceinline__ float qk_row128_rstd(const uint4& lo, const uint4& hi, unsigned mask, float eps) {
+  float e, o;
+  qk_row128_sums(lo, hi, e, o);
 #pragma unroll
-    for (int sh = 4; sh > 0; sh >>= 1) {
-      e = __fadd_rn(e, __shfl_xor_sync(mask, e, sh));
-      o = __fadd_rn(o, __shfl_xor_sync(mask, o, sh));
-    }
-    const float ss = __fadd_rn(e, o);
-    const float rstd = rms_rstd(ss, 128, eps);
-    const float4 w0 = *reinterpret_cast<const float4*>(nw + l * 8);
-    const float4 w1 = *reinterpret_cast<const float4*>(nw + l * 8 + 4);
-    const float4 w2 = *reinterpret_cast<const float4*>(nw + 64 + l * 8);
-    const float4 w3 = *reinterpret_cast<const float4*>(nw + 64 + l * 8 + 4);
-    const float wa[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-    const float wb[8] = {w2.x, w2.y, w2.z, w2.w, w3.x, w3.y, w3.z, w3.w};
+  for (int sh = 4; sh > 0; sh >>= 1) {
+    e = __fadd_rn(e, __shfl_xor_sync(mask, e, sh));
+    o = __fadd_rn(o, __shfl_xor_sync(mask, o, sh));
+  }
+  return rms_rstd(__fadd_rn(e, o), 128, eps);
+}
+__device__ __forceinline__ void qk_row128_weights(const float* nw, int l, float (&wa)[8], float (&wb)[8]) {
+  const float4 w0 = *reinterpret_cast<const float4*>(nw + l * 8);
+  const float4 w1 = *reinterpret_cast<const float4*>(nw + l * 8 + 4);
+  const float4 w2 = *reinterpret_cast<const float4*>(nw + 64 + l * 8);
+  const float4 w3 = *reinterpret_cast<const float4*>(nw + 64 + l * 8 + 4);
+  wa[0] = w0.x; wa[1] = w0.y; wa[2] = w0.z; wa[3] = w0.w; wa[4] = w1.x; wa[5] = w1.y; wa[6] = w1.z; wa[7] = w1.w;
+  wb[0] = w2.x; wb[1] = w2.y; wb[2] = w2.z; wb[3] = w2.w; wb[4] = w3.x; wb[5] = w3.y; wb[6] = w3.z; wb[7] = w3.w;
+}
+__device__ __forceinline__ void qk_row128_apply(uint4& lo, uint4& hi, bool norm, float rstd, const float (&wa)[8],
+                                                const float (&wb)[8], bool rotate, const float (&c)[8],
+                                                const float (&sn)[8]) {
+  float a[8], b[8];
+  qk_row128_unpack(lo, hi, a, b);
+  if (norm) {
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       a[k] = norm_scale(a[k], rstd, wa[k]);
@@ -208,6 +224,16 @@ __device__ __forceinline__ void qk_row128(uint4& lo, uint4& hi, int l, unsigned 
     ql[k] = __floats2bfloat162_rn(a[2 * k], a[2 * k + 1]);
     qh[k] = __floats2bfloat162_rn(b[2 * k], b[2 * k + 1]);
   }
+}
+__device__ __forceinline__ void qk_row128(uint4& lo, uint4& hi, int l, unsigned mask, const float* nw, float eps,
+                                          bool rotate, const float (&c)[8], const float (&sn)[8]) {
+  float wa[8] = {}, wb[8] = {};
+  float rstd = 0.f;
+  if (nw != nullptr) {
+    rstd = qk_row128_rstd(lo, hi, mask, eps);
+    qk_row128_weights(nw, l, wa, wb);
+  }
+  qk_row128_apply(lo, hi, nw != nullptr, rstd, wa, wb, rotate, c, sn);
 }
 
 static inline int ceil_div_host(long long a, long long b) { return (int)((a + b - 1) / b); }

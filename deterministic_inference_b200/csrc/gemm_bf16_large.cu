@@ -40,8 +40,20 @@ constexpr int BM = 128;       // tokens per tile = MMA M
 constexpr int BK = 64;        // k per stage: 128 bytes = one swizzle atom
 constexpr int UMMA_K = 16;
 constexpr int A_BYTES = BM * BK * 2;
-constexpr int THREADS = 320;   // warps 0, 1: copies and products; 2-9: epilogue
+// Three groups of four warps: warp 0 copies, warp 1 issues the products (2 and 3 have no
+// work), warps 4-11 are the epilogue.  Registers are handed out to groups of four warps: in
+// the QKV form the first group gives most of its registers back (setmaxnreg) and the epilogue
+// warps take them, so that the q/k arithmetic of eight rows at a time fits without spills.
+constexpr int THREADS = 384;
+constexpr int EPI_WARP0 = 4;
 constexpr int EPI_WARPS = 8;
+constexpr int REGS_FEW = 40, REGS_MANY = 232;      // 128 * 40 + 256 * 232 = 64,512 registers
+template <int N> __device__ __forceinline__ void regs_give() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void regs_take() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
 // Features per tile = MMA N: 256 (GATED: 128 gate + 128 up rows), or 128 for products with so
 // few tiles of 256 that they would leave SMs idle.  Stages of the ring: what fits.
 // (QKV: the epilogue that norms and rotates heads stages 8 KB a warp instead of 4, a stage of
@@ -179,13 +191,81 @@ struct QkvEpilogue {
 // 64+8l..64+8l+7, a rotation pair in one lane), runs qk_row128 of common.cuh on them, the
 // function the q/k kernels run, and writes whole rows of 128 bytes: the norm weights, the
 // rotation table and the stores are then read and written by neighbouring lanes together.
-__device__ __forceinline__ void store_rows_qkv(unsigned src, __nv_bfloat16* q_out, unsigned char* stage, int lane,
-                                               int row0, int n0, int half, const QkvEpilogue& qk) {
-  const int head = (n0 >> 7) + half;
-  if (head >= qk.Hq + 2 * qk.Hkv) return;          // the tile's second half lies beyond the last head
-  const bool is_q = head < qk.Hq, is_k = !is_q && head < qk.Hq + qk.Hkv;
+//
+// What does not depend on the product is found before the warp waits for it
+// (qkv_rows_prepare): where each row goes, its table row, and the table values of the first
+// QKV_AHEAD rounds of four rows; in the loop the values of round it + QKV_AHEAD are asked for
+// while round it is worked on (a table row comes from L2: several hundred cycles, a round's
+// arithmetic takes a hundred or two).
+constexpr int QKV_AHEAD = 8;
+struct QkvRows {
+  long long my_dst;       // lane r: element offset of row r's result from q_out or the cache, or -1
+  int my_pos;             // lane r: row r's table row
+  int head;
+  bool active, is_q, is_k, rotate;
+  float4 tv[QKV_AHEAD][4];
+};
+__device__ __forceinline__ void qkv_table(const QkvRows& R, int it, int lane, const QkvEpilogue& qk, float4 (&t)[4]) {
+  if (R.rotate) {
+    const int p = __shfl_sync(0xffffffffu, R.my_pos, it * 4 + (lane >> 3));
+    const float* tab = qk.cos_sin + (size_t)p * 128 + (lane & 7) * 8;
+    t[0] = *reinterpret_cast<const float4*>(tab);
+    t[1] = *reinterpret_cast<const float4*>(tab + 4);
+    t[2] = *reinterpret_cast<const float4*>(tab + 64);
+    t[3] = *reinterpret_cast<const float4*>(tab + 68);
+  }
+}
+__device__ __forceinline__ void qkv_rows_prepare(QkvRows& R, int lane, int row0, int n0, int half,
+                                                 const QkvEpilogue& qk) {
+  R.head = (n0 >> 7) + half;
+  R.active = R.head < qk.Hq + 2 * qk.Hkv;          // else the tile's second half lies beyond the last head
+  R.is_q = R.head < qk.Hq;
+  R.is_k = !R.is_q && R.head < qk.Hq + qk.Hkv;
+  R.rotate = R.active && qk.cos_sin != nullptr && (R.is_q || R.is_k);
+  R.my_dst = -1;
+  R.my_pos = 0;
+  if (!R.active) return;
+  const int token = row0 + lane;
+  if (token < qk.M) {
+    if (R.rotate) {
+      const int p = qk.positions[token];
+      R.my_pos = p < 0 ? 0 : (p >= qk.max_pos ? qk.max_pos - 1 : p);
+    }
+    if (R.is_q) {
+      R.my_dst = ((long long)token * qk.Hq + R.head) * 128;
+    } else if (qk.cache != nullptr) {
+      const int slot = qk.slot_mapping[token];
+      if (slot >= 0) {
+        const long long page = slot / qk.page_size;
+        if (page < qk.num_pages) {
+          const int h = R.is_k ? R.head - qk.Hq : R.head - qk.Hq - qk.Hkv;
+          R.my_dst = ((((page * 2 + (R.is_k ? 0 : 1)) * qk.Hkv + h) * qk.page_size) + (slot - page * qk.page_size)) * 128;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int a = 0; a < QKV_AHEAD; ++a) {
+    R.tv[a][0] = R.tv[a][1] = R.tv[a][2] = R.tv[a][3] = make_float4(0.f, 0.f, 0.f, 0.f);
+    qkv_table(R, a, lane, qk, R.tv[a]);
+  }
+}
+__device__ __forceinline__ void store_rows_qkv(unsigned src, unsigned char* stage, int lane, int half,
+                                               const QkvEpilogue& qk, QkvRows& R, const CUtensorMap* map_q,
+                                               int row0) {
+  if (!R.active) return;
   const unsigned acc = src + half * 128;
-  __syncwarp();                                     // the rows of the tile before this one have been taken back
+  // the stores of the tile before this one must have read the staging blocks
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+  __syncwarp();
+  // While a lane has its own row in hand it also takes the row's sum of squares (of the
+  // rounded values), in the order of the butterfly of qk_row128: vector j (elements 4j..4j+3,
+  // sumsq4) is added to vector j + 16, the sixteen sums 8 apart, then 4, 2, 1 apart.  Every
+  // lane works on a row of its own here; eight lanes a row would each redo the chain of a
+  // division, a root and a reciprocal, with shuffles between.
+  const float* nw = R.is_q ? qk.q_norm_w : (R.is_k ? qk.k_norm_w : nullptr);
+  const bool norm = nw != nullptr;
+  float t16[16];
 #pragma unroll
   for (int blk = 0; blk < 2; ++blk) {
 #pragma unroll
@@ -193,73 +273,65 @@ __device__ __forceinline__ void store_rows_qkv(unsigned src, __nv_bfloat16* q_ou
       unsigned v[32];
       tc_ld32(acc + blk * 64 + h * 32, v);
       tc_wait_ld();
+      unsigned p[16];
+#pragma unroll
+      for (int k = 0; k < 16; ++k) p[k] = pack2_bf16(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
 #pragma unroll
       for (int q = 0; q < 4; ++q)
         stage_piece(stage + blk * EPI_STAGE_BYTES, lane, h * 4 + q,
-                    make_uint4(pack2_bf16(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1])),
-                               pack2_bf16(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3])),
-                               pack2_bf16(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5])),
-                               pack2_bf16(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]))));
-    }
-  }
-  __syncwarp();
-  const int l = lane & 7;
-  const unsigned mask = 0xffu << (lane & 24);
-  const float* nw = is_q ? qk.q_norm_w : (is_k ? qk.k_norm_w : nullptr);
-  const bool rotate = qk.cos_sin != nullptr && (is_q || is_k);
-  // where row r's result goes (an element offset from q_out or the cache, or -1) and its
-  // table row: lane r finds both for its own row, the eight lanes of a row fetch them by shuffle
-  long long my_dst = -1;
-  int my_pos = 0;
-  {
-    const int token = row0 + lane;
-    if (token < qk.M) {
-      if (rotate) {
-        const int p = qk.positions[token];
-        my_pos = p < 0 ? 0 : (p >= qk.max_pos ? qk.max_pos - 1 : p);
-      }
-      if (is_q) {
-        my_dst = ((long long)token * qk.Hq + head) * 128;
-      } else if (qk.cache != nullptr) {
-        const int slot = qk.slot_mapping[token];
-        if (slot >= 0) {
-          const long long page = slot / qk.page_size;
-          if (page < qk.num_pages) {
-            const int h = is_k ? head - qk.Hq : head - qk.Hq - qk.Hkv;
-            my_dst = ((((page * 2 + (is_k ? 0 : 1)) * qk.Hkv + h) * qk.page_size) + (slot - page * qk.page_size)) * 128;
-          }
+                    make_uint4(p[q * 4], p[q * 4 + 1], p[q * 4 + 2], p[q * 4 + 3]));
+      if (norm) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {     // vector blk * 16 + h * 8 + j of the row
+          const float sv = sumsq4(__uint_as_float(p[2 * j] << 16), __uint_as_float(p[2 * j] & 0xffff0000u),
+                                  __uint_as_float(p[2 * j + 1] << 16), __uint_as_float(p[2 * j + 1] & 0xffff0000u));
+          if (blk == 0) t16[h * 8 + j] = sv;
+          else t16[h * 8 + j] = __fadd_rn(t16[h * 8 + j], sv);
         }
       }
     }
   }
-  __nv_bfloat16* base = is_q ? q_out : qk.cache;
-  // the table values of a row are asked for one round ahead of their use (a store to the
-  // output may not be passed by a later load, as far as the compiler knows)
-  float4 tv[4] = {};
-  auto table = [&](int it, float4 (&t)[4]) {
-    if (rotate) {
-      const int p = __shfl_sync(0xffffffffu, my_pos, it * 4 + (lane >> 3));
-      const float* tab = qk.cos_sin + (size_t)p * 128 + l * 8;
-      t[0] = *reinterpret_cast<const float4*>(tab);
-      t[1] = *reinterpret_cast<const float4*>(tab + 4);
-      t[2] = *reinterpret_cast<const float4*>(tab + 64);
-      t[3] = *reinterpret_cast<const float4*>(tab + 68);
-    }
-  };
-  table(0, tv);
+  float my_rstd = 0.f;
+  if (norm) {
+#pragma unroll
+    for (int w = 8; w > 0; w >>= 1)
+#pragma unroll
+      for (int j = 0; j < w; ++j) t16[j] = __fadd_rn(t16[j], t16[j + w]);
+    my_rstd = rms_rstd(t16[0], 128, qk.eps);
+  }
+  __syncwarp();
+  const int l = lane & 7;
+  __nv_bfloat16* base = R.is_q ? qk.q_out : qk.cache;
+  float wa[8] = {}, wb[8] = {};
+  if (norm) qk_row128_weights(nw, l, wa, wb);
 #pragma unroll
   for (int it = 0; it < 8; ++it) {
     const int r = it * 4 + (lane >> 3);
     uint4 lo = *reinterpret_cast<const uint4*>(stage + r * 128 + ((l ^ (r & 7)) << 4));
     uint4 hi = *reinterpret_cast<const uint4*>(stage + EPI_STAGE_BYTES + r * 128 + ((l ^ (r & 7)) << 4));
+    float4(&tv)[4] = R.tv[it % QKV_AHEAD];
     const float c[8] = {tv[0].x, tv[0].y, tv[0].z, tv[0].w, tv[1].x, tv[1].y, tv[1].z, tv[1].w};
     const float sn[8] = {tv[2].x, tv[2].y, tv[2].z, tv[2].w, tv[3].x, tv[3].y, tv[3].z, tv[3].w};
-    if (it + 1 < 8) table(it + 1, tv);
-    const long long d = __shfl_sync(0xffffffffu, my_dst, r);
-    if (is_q || is_k) qk_row128(lo, hi, l, mask, nw, qk.eps, rotate, c, sn);
-    if (d >= 0) {
+    if (it + QKV_AHEAD < 8) qkv_table(R, it + QKV_AHEAD, lane, qk, tv);
+    const long long d = __shfl_sync(0xffffffffu, R.my_dst, r);
+    const float rstd = __shfl_sync(0xffffffffu, my_rstd, r);
+    if (R.is_q || R.is_k) qk_row128_apply(lo, hi, norm, rstd, wa, wb, R.rotate, c, sn);
+    if (R.is_q) {
+      // back to where they were staged: the q rows of the warp leave as two stores of
+      // 32 rows x 128 bytes by the copy engine, which clips the rows beyond M
+      *reinterpret_cast<uint4*>(stage + r * 128 + ((l ^ (r & 7)) << 4)) = lo;
+      *reinterpret_cast<uint4*>(stage + EPI_STAGE_BYTES + r * 128 + ((l ^ (r & 7)) << 4)) = hi;
+    } else if (d >= 0) {
       *reinterpret_cast<uint4*>(base + d + l * 8) = lo;
       *reinterpret_cast<uint4*>(base + d + 64 + l * 8) = hi;
+    }
+  }
+  if (R.is_q) {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(map_q, stage, R.head * 128, row0);
+      tma_store_2d(map_q, stage + EPI_STAGE_BYTES, R.head * 128 + 64, row0);
     }
   }
 }
@@ -381,93 +453,100 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   const unsigned tmem = *tmem_slot;
   bool ok = true;
 
-  if (warp == 0) {
-    if (lane == 0) {
-      // ---- TMA producer.  The ring runs on across this CTA's tiles: load number c is
-      // k-block c % num_kb of its tile number c / num_kb and goes to stage c % STAGES.  The
-      // weights do not depend on the kernel before this one, so those of the first STAGES
-      // loads are sent for before the wait for that kernel, the tokens after it.
-      const int my_tiles = tiles > (int)blockIdx.x ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-      const int total = my_tiles * num_kb;
-      auto load_w = [&](int c) {
-        const int t = blockIdx.x + (c / num_kb) * gridDim.x, kb = c % num_kb;
-        const int n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
-        unsigned char* b = smem + (c % STAGES) * STAGE_BYTES + A_BYTES;
-        tma_load_2d(b, &map_w, kb * BK, n0, &full[c % STAGES]);
-        if (BNL == 256)
-          tma_load_2d(b + B_BYTES / 2, &map_w, kb * BK, GATED ? N + n0 : n0 + 128, &full[c % STAGES]);
-      };
-      auto load_x = [&](int c) {
-        const int t = blockIdx.x + (c / num_kb) * gridDim.x, kb = c % num_kb;
-        tma_load_2d(smem + (c % STAGES) * STAGE_BYTES, &map_x, kb * BK, (t % m_tiles) * BM, &full[c % STAGES]);
-      };
-      const int pre = total < STAGES ? total : STAGES;
-      for (int c = 0; c < pre; ++c) {
-        mbar_expect_tx(&full[c], STAGE_BYTES);
-        load_w(c);
-      }
-      pdl_wait();
-      for (int c = 0; c < pre; ++c) load_x(c);
-      for (int c = pre; c < total && ok; ++c) {
-        ok = mbar_wait(&empty[c % STAGES], ((c / STAGES) - 1) & 1);
-        if (!ok) break;
-        mbar_expect_tx(&full[c % STAGES], STAGE_BYTES);
-        load_w(c);
-        load_x(c);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      // ---- MMA issuer
-      constexpr unsigned idesc = make_idesc(BM, BNL);
-      int count = 0, local = 0;
-      for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
-        const int buf = local & 1;
-        if (local >= 2) {     // the epilogue must have read this buffer's earlier tile
-          ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1);
-          if (!ok) break;
-          tc_fence_after();
+  if (warp < EPI_WARP0) {
+    if (QKV) regs_give<REGS_FEW>();
+    if (warp == 0) {
+      if (lane == 0) {
+        // ---- TMA producer.  The ring runs on across this CTA's tiles: load number c is
+        // k-block c % num_kb of its tile number c / num_kb and goes to stage c % STAGES.  The
+        // weights do not depend on the kernel before this one, so those of the first STAGES
+        // loads are sent for before the wait for that kernel, the tokens after it.
+        const int my_tiles = tiles > (int)blockIdx.x ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+        const int total = my_tiles * num_kb;
+        auto load_w = [&](int c) {
+          const int t = blockIdx.x + (c / num_kb) * gridDim.x, kb = c % num_kb;
+          const int n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
+          unsigned char* b = smem + (c % STAGES) * STAGE_BYTES + A_BYTES;
+          tma_load_2d(b, &map_w, kb * BK, n0, &full[c % STAGES]);
+          if (BNL == 256)
+            tma_load_2d(b + B_BYTES / 2, &map_w, kb * BK, GATED ? N + n0 : n0 + 128, &full[c % STAGES]);
+        };
+        auto load_x = [&](int c) {
+          const int t = blockIdx.x + (c / num_kb) * gridDim.x, kb = c % num_kb;
+          tma_load_2d(smem + (c % STAGES) * STAGE_BYTES, &map_x, kb * BK, (t % m_tiles) * BM, &full[c % STAGES]);
+        };
+        const int pre = total < STAGES ? total : STAGES;
+        for (int c = 0; c < pre; ++c) {
+          mbar_expect_tx(&full[c], STAGE_BYTES);
+          load_w(c);
         }
-        for (int kb = 0; kb < num_kb && ok; ++kb, ++count) {
-          const int s = count % STAGES;
-          ok = mbar_wait(&full[s], (count / STAGES) & 1);
+        pdl_wait();
+        for (int c = 0; c < pre; ++c) load_x(c);
+        for (int c = pre; c < total && ok; ++c) {
+          ok = mbar_wait(&empty[c % STAGES], ((c / STAGES) - 1) & 1);
           if (!ok) break;
-          tc_fence_after();
-          const unsigned a = smem_u32(smem + s * STAGE_BYTES), b = a + A_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            tc_mma(tmem + buf * BNL, smem_desc_sw128(a + k * UMMA_K * 2), smem_desc_sw128(b + k * UMMA_K * 2),
-                   idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          tc_commit(&empty[s]);
+          mbar_expect_tx(&full[c % STAGES], STAGE_BYTES);
+          load_w(c);
+          load_x(c);
         }
-        if (ok) tc_commit(&acc_full[buf]);
+      }
+    } else if (warp == 1) {
+      if (lane == 0) {
+        // ---- MMA issuer
+        constexpr unsigned idesc = make_idesc(BM, BNL);
+        int count = 0, local = 0;
+        for (int t = blockIdx.x; t < tiles && ok; t += gridDim.x, ++local) {
+          const int buf = local & 1;
+          if (local >= 2) {     // the epilogue must have read this buffer's earlier tile
+            ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          for (int kb = 0; kb < num_kb && ok; ++kb, ++count) {
+            const int s = count % STAGES;
+            ok = mbar_wait(&full[s], (count / STAGES) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const unsigned a = smem_u32(smem + s * STAGE_BYTES), b = a + A_BYTES;
+  #pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              tc_mma(tmem + buf * BNL, smem_desc_sw128(a + k * UMMA_K * 2), smem_desc_sw128(b + k * UMMA_K * 2),
+                     idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            tc_commit(&empty[s]);
+          }
+          if (ok) tc_commit(&acc_full[buf]);
+        }
       }
     }
   } else {
+    if (QKV) regs_take<REGS_MANY>();
     // ---- epilogue: warps 2..9; a warp reads the 32 lanes (token rows) 32 * (warp % 4) ..,
     // warps 2-5 the first half of the columns, warps 6-9 the second
     pdl_wait();      // nothing is stored before the kernel before this one has finished
-    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int quarter = warp & 3, half = (warp - EPI_WARP0) >> 2;
     const unsigned lane_base = (unsigned)(quarter * 32) << 16;
     int local = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++local) {
       const int buf = local & 1;
       const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
+      QkvRows rows;
+      if (QKV) qkv_rows_prepare(rows, lane, m0 + quarter * 32, n0, half, qk);
       bool got = ok && mbar_wait(&acc_full[buf], (local >> 1) & 1);
       got = __all_sync(0xffffffffu, got);     // tcgen05.ld below is warp-wide
       if (!got) { ok = false; break; }
       tc_fence_after();
       if (QKV)
-        store_rows_qkv(tmem + buf * BNL + lane_base, qk.q_out, epi_stage + (warp - 2) * 2 * EPI_STAGE_BYTES, lane,
-                       m0 + quarter * 32, n0, half, qk);
+        store_rows_qkv(tmem + buf * BNL + lane_base, epi_stage + (warp - EPI_WARP0) * 2 * EPI_STAGE_BYTES, lane, half, qk, rows,
+                       &map_out, m0 + quarter * 32);
       else
-        store_rows<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, &map_out, epi_stage + (warp - 2) * EPI_STAGE_BYTES,
+        store_rows<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, &map_out, epi_stage + (warp - EPI_WARP0) * EPI_STAGE_BYTES,
                                      lane, m0 + quarter * 32, n0, half);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
     stores_done(lane);
+  
   }
   if (!ok) atomicExch(&dib_gemm_large_error_word, 1);
   tc_fence_before();
@@ -600,91 +679,98 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   const unsigned tmem = *tmem_slot;
   bool ok = true;
 
-  if (warp == 0) {
-    if (lane == 0) {
-      // ---- TMA producer of this CTA's halves.  Load number c is k-block c % num_kb of the
-      // pair's tile number c / num_kb and goes to stage c % STAGES.
-      const int my_tiles = tiles > pair ? (tiles - pair + pairs - 1) / pairs : 0;
-      const int total = my_tiles * num_kb;
-      const unsigned full0 = cluster_addr(smem_u32(full), 0);   // the first CTA's full[0], as a cluster address
-      auto load_w = [&](int c) {
-        const int t = pair + (c / num_kb) * pairs, kb = c % num_kb;
-        const int n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
-        const int row = GATED ? (rank ? N + n0 : n0) : n0 + (int)rank * (BNL / 2);
-        tma_load_2d_pair(smem + (c % STAGES) * STAGE_BYTES + A_BYTES, &map_w, kb * BK, row, full0 + (c % STAGES) * 8);
-      };
-      auto load_x = [&](int c) {
-        const int t = pair + (c / num_kb) * pairs, kb = c % num_kb;
-        tma_load_2d_pair(smem + (c % STAGES) * STAGE_BYTES, &map_x, kb * BK,
-                         (t % m_tiles) * 2 * BM + (int)rank * BM, full0 + (c % STAGES) * 8);
-      };
-      const int pre = total < STAGES ? total : STAGES;
-      for (int c = 0; c < pre; ++c) {
-        if (rank == 0) mbar_expect_tx(&full[c], 2 * STAGE_BYTES);
-        load_w(c);
-      }
-      pdl_wait();
-      for (int c = 0; c < pre; ++c) load_x(c);
-      for (int c = pre; c < total && ok; ++c) {
-        ok = mbar_wait(&empty[c % STAGES], ((c / STAGES) - 1) & 1);
-        if (!ok) break;
-        if (rank == 0) mbar_expect_tx(&full[c % STAGES], 2 * STAGE_BYTES);
-        load_w(c);
-        load_x(c);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
-      // ---- MMA issuer of the pair
-      constexpr unsigned idesc = make_idesc(2 * BM, BNL);
-      int count = 0, local = 0;
-      for (int t = pair; t < tiles && ok; t += pairs, ++local) {
-        const int buf = local & 1;
-        if (local >= 2) {     // both CTAs' epilogues must have read this buffer's earlier tile
-          ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1);
-          if (!ok) break;
-          tc_fence_after();
+  if (warp < EPI_WARP0) {
+    if (QKV) regs_give<REGS_FEW>();
+    if (warp == 0) {
+      if (lane == 0) {
+        // ---- TMA producer of this CTA's halves.  Load number c is k-block c % num_kb of the
+        // pair's tile number c / num_kb and goes to stage c % STAGES.
+        const int my_tiles = tiles > pair ? (tiles - pair + pairs - 1) / pairs : 0;
+        const int total = my_tiles * num_kb;
+        const unsigned full0 = cluster_addr(smem_u32(full), 0);   // the first CTA's full[0], as a cluster address
+        auto load_w = [&](int c) {
+          const int t = pair + (c / num_kb) * pairs, kb = c % num_kb;
+          const int n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
+          const int row = GATED ? (rank ? N + n0 : n0) : n0 + (int)rank * (BNL / 2);
+          tma_load_2d_pair(smem + (c % STAGES) * STAGE_BYTES + A_BYTES, &map_w, kb * BK, row, full0 + (c % STAGES) * 8);
+        };
+        auto load_x = [&](int c) {
+          const int t = pair + (c / num_kb) * pairs, kb = c % num_kb;
+          tma_load_2d_pair(smem + (c % STAGES) * STAGE_BYTES, &map_x, kb * BK,
+                           (t % m_tiles) * 2 * BM + (int)rank * BM, full0 + (c % STAGES) * 8);
+        };
+        const int pre = total < STAGES ? total : STAGES;
+        for (int c = 0; c < pre; ++c) {
+          if (rank == 0) mbar_expect_tx(&full[c], 2 * STAGE_BYTES);
+          load_w(c);
         }
-        for (int kb = 0; kb < num_kb && ok; ++kb, ++count) {
-          const int s = count % STAGES;
-          ok = mbar_wait(&full[s], (count / STAGES) & 1);
+        pdl_wait();
+        for (int c = 0; c < pre; ++c) load_x(c);
+        for (int c = pre; c < total && ok; ++c) {
+          ok = mbar_wait(&empty[c % STAGES], ((c / STAGES) - 1) & 1);
           if (!ok) break;
-          tc_fence_after();
-          const unsigned a = smem_u32(smem + s * STAGE_BYTES), b = a + A_BYTES;
-#pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            tc_mma_pair(tmem + buf * BNL, smem_desc_sw128(a + k * UMMA_K * 2),
-                        smem_desc_sw128(b + k * UMMA_K * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          tc_commit_pair(&empty[s]);
+          if (rank == 0) mbar_expect_tx(&full[c % STAGES], 2 * STAGE_BYTES);
+          load_w(c);
+          load_x(c);
         }
-        if (ok) tc_commit_pair(&acc_full[buf]);
+      }
+    } else if (warp == 1) {
+      if (lane == 0 && rank == 0) {
+        // ---- MMA issuer of the pair
+        constexpr unsigned idesc = make_idesc(2 * BM, BNL);
+        int count = 0, local = 0;
+        for (int t = pair; t < tiles && ok; t += pairs, ++local) {
+          const int buf = local & 1;
+          if (local >= 2) {     // both CTAs' epilogues must have read this buffer's earlier tile
+            ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          for (int kb = 0; kb < num_kb && ok; ++kb, ++count) {
+            const int s = count % STAGES;
+            ok = mbar_wait(&full[s], (count / STAGES) & 1);
+            if (!ok) break;
+            tc_fence_after();
+            const unsigned a = smem_u32(smem + s * STAGE_BYTES), b = a + A_BYTES;
+  #pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k)
+              tc_mma_pair(tmem + buf * BNL, smem_desc_sw128(a + k * UMMA_K * 2),
+                          smem_desc_sw128(b + k * UMMA_K * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            tc_commit_pair(&empty[s]);
+          }
+          if (ok) tc_commit_pair(&acc_full[buf]);
+        }
       }
     }
   } else {
+    if (QKV) regs_take<REGS_MANY>();
     // ---- epilogue of this CTA's 128 token rows
     pdl_wait();
-    const int quarter = warp & 3, half = (warp - 2) >> 2;
+    const int quarter = warp & 3, half = (warp - EPI_WARP0) >> 2;
     const unsigned lane_base = (unsigned)(quarter * 32) << 16;
     const unsigned acc_empty0 = cluster_addr(smem_u32(acc_empty), 0);   // the first CTA's acc_empty[0]
     int local = 0;
     for (int t = pair; t < tiles; t += pairs, ++local) {
       const int buf = local & 1;
       const int m0 = (t % m_tiles) * 2 * BM + (int)rank * BM, n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
+      QkvRows rows;
+      if (QKV) qkv_rows_prepare(rows, lane, m0 + quarter * 32, n0, half, qk);
       bool got = ok && mbar_wait(&acc_full[buf], (local >> 1) & 1);
       got = __all_sync(0xffffffffu, got);     // tcgen05.ld below is warp-wide
       if (!got) { ok = false; break; }
       tc_fence_after();
       if (QKV)
-        store_rows_qkv(tmem + buf * BNL + lane_base, qk.q_out, epi_stage + (warp - 2) * 2 * EPI_STAGE_BYTES, lane,
-                       m0 + quarter * 32, n0, half, qk);
+        store_rows_qkv(tmem + buf * BNL + lane_base, epi_stage + (warp - EPI_WARP0) * 2 * EPI_STAGE_BYTES, lane, half, qk, rows,
+                       &map_out, m0 + quarter * 32);
       else
-        store_rows<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, &map_out, epi_stage + (warp - 2) * EPI_STAGE_BYTES,
+        store_rows<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, &map_out, epi_stage + (warp - EPI_WARP0) * EPI_STAGE_BYTES,
                                      lane, m0 + quarter * 32, n0, half);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty0 + buf * 8);
     }
     stores_done(lane);
+  
   }
   if (!ok) atomicExch(&dib_gemm_large_error_word, 1);
   tc_fence_before();
