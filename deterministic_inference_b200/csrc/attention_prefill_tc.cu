@@ -34,7 +34,17 @@ namespace {
 
 constexpr int TC_M = 128, TC_N = 128, TC_D = 128, TC_THREADS = 320;
 constexpr int TMA_WARP = 8, MMA_WARP = 9;
-constexpr int PAIR_THREADS = 352, PAIR_V_WARP = 10;   // the pair kernel fetches keys (warp 8) and values apart
+constexpr int PAIR_THREADS = 384, PAIR_V_WARP = 10;   // the pair kernel fetches keys (warp 8) and values apart
+// Registers are handed out to groups of four warps.  The pair kernel's third group (keys,
+// products, values, one warp without work) gives most of its registers back and the two
+// groups of softmax threads, each of which holds a row of 128 scores, take them.
+constexpr int PAIR_REGS_FEW = 56, PAIR_REGS_MANY = 224;      // 128 * 56 + 256 * 224 = 64,512
+template <int N> __device__ __forceinline__ void regs_give() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void regs_take() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
 constexpr int TILE_BYTES = 128 * 128 * 2;   // a [128 x 128] bf16 tile (two 64-column halves)
 constexpr int HALF_BYTES = 128 * 64 * 2;
 
@@ -635,6 +645,8 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
   tc_fence_after();
   const unsigned tmem = *tmem_slot;
 
+  if (warp >= TMA_WARP) {
+  regs_give<PAIR_REGS_FEW>();
   if (warp == TMA_WARP || warp == PAIR_V_WARP) {
     // Keys and values of a key tile are fetched, waited for and handed back apart, each
     // by a warp of its own: the keys are free again after the score products, long
@@ -759,7 +771,9 @@ extend_attention_tc_pair_kernel(const __grid_constant__ CUtensorMap map,
         if (i == ntiles - 1) tc_commit(&o_final[x]);
       }
     }
+  }
   } else {
+    regs_take<PAIR_REGS_MANY>();
     // ---- softmax: thread r of group x owns row r of tile x
     const int x = threadIdx.x >> 7, r = threadIdx.x & 127;
     const int tl = r / G, g = r % G;
