@@ -22,10 +22,10 @@
 // gone.  The two products are rounded to bfloat16 first, as stored products would be, and
 // the gate is silu_gate<bf16> of common.cuh, so the bits are those of the two-kernel path.
 //
-// Roles in a CTA of 320 threads: warp 0 issues the TMA loads (the weights of the first
+// Roles in a CTA of 384 threads: warp 0 issues the TMA loads (the weights of the first
 // stages before the programmatic dependency wait, the tokens after it), warp 1 allocates
-// tensor memory and issues the MMAs, warps 2-9 are the epilogue (two warps to each quarter
-// of the tile's rows, half of its columns each).  Every mbarrier wait is
+// tensor memory and issues the MMAs, warps 2 and 3 have no work, warps 4-11 are the epilogue
+// (two warps to each quarter of the tile's rows, half of its columns each).  Every mbarrier wait is
 // bounded; a wait that runs out sets the error word (dib_gemm_bf16_large_status), tensor
 // memory is still freed and the kernel returns.
 #include <cuda.h>
@@ -520,8 +520,8 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     }
   } else {
     if (QKV) regs_take<REGS_MANY>();
-    // ---- epilogue: warps 2..9; a warp reads the 32 lanes (token rows) 32 * (warp % 4) ..,
-    // warps 2-5 the first half of the columns, warps 6-9 the second
+    // ---- epilogue: warps 4..11; a warp reads the 32 lanes (token rows) 32 * (warp % 4) ..,
+    // warps 4-7 the first half of the columns, warps 8-11 the second
     pdl_wait();      // nothing is stored before the kernel before this one has finished
     const int quarter = warp & 3, half = (warp - EPI_WARP0) >> 2;
     const unsigned lane_base = (unsigned)(quarter * 32) << 16;
@@ -546,7 +546,6 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
     stores_done(lane);
-  
   }
   if (!ok) atomicExch(&dib_gemm_large_error_word, 1);
   tc_fence_before();
@@ -770,7 +769,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       if (lane == 0) mbar_arrive_cluster(acc_empty0 + buf * 8);
     }
     stores_done(lane);
-  
   }
   if (!ok) atomicExch(&dib_gemm_large_error_word, 1);
   tc_fence_before();
