@@ -73,6 +73,7 @@ class StepBatch:
     patch_dst: Optional[torch.Tensor] = None   # int32 [B]: place in input_ids, or -1
     patch_src: Optional[torch.Tensor] = None   # int32 [B]: row of the previous step's tokens
     num_patches: int = 0
+    logits_of_all_rows: bool = False            # every token's logits are wanted, in the tokens' order
 
 
 def _align(n: int, a: int = 4) -> int:
@@ -123,7 +124,9 @@ def step_views(td: torch.Tensor, lay: PackedLayout, group_list: list, q_lens: li
         seq_lens=lay.seg(td, "seq_lens"), state_slots=lay.seg(td, "state_slots"),
         logit_indices=lay.seg(td, "logit_indices"), q_lens=q_lens, kv_lens=kv_lens, slots=slots,
         groups=groups, logit_rows=logit_rows, order=order,
-        patch_dst=lay.seg(td, "patch_dst"), patch_src=lay.seg(td, "patch_src"))
+        patch_dst=lay.seg(td, "patch_dst"), patch_src=lay.seg(td, "patch_src"),
+        # one-token sequences that all want their logits: row i of the logits is token i
+        logits_of_all_rows=(num_decode == b and lay.t == b and lay.r == b))
 
 
 @dataclass

@@ -102,10 +102,15 @@ class DecoderModel:
         # last residual add and the final norm on those rows
         if step.num_logits == 0:
             return torch.empty(0, self.plan.vocab_size, dtype=torch.float32, device=hidden.device)
-        rows = ops.gather_rows(hidden, step.logit_indices)
-        if residual is None:
+        if step.logits_of_all_rows:
+            # (a decode step: nothing to gather, and the last block's output may stay the
+            # split sums it came as)
+            rows, res_rows = hidden, residual
+        else:
+            rows = ops.gather_rows(hidden, step.logit_indices)
+            res_rows = None if residual is None else ops.gather_rows(residual, step.logit_indices)
+        if res_rows is None:
             rows = self.final_norm.forward(rows)
         else:
-            res_rows = ops.gather_rows(residual, step.logit_indices)
             rows, _ = self.final_norm.add_forward(rows, res_rows)
         return self.head.forward(rows)
