@@ -38,13 +38,13 @@ class EngineConfig:
     max_prefill_tokens: int = 8192       # token budget of one step; prompts are cut to fit
     max_decode_batch: int = 256          # sequences running at a time
 
-    # bfloat16 matrix products of more than 128 rows go to the library (cuBLAS), as all of
+    # bfloat16 matrix products of more than 64 rows go to the library (cuBLAS), as all of
     # the reference's do.  False: every product runs on the package's own kernel, whose
     # order of summation depends on the weight's shape alone; a token's bfloat16 bits are
     # then the same whatever its step holds (prompt portions are slower).  The switch is
     # one per process: the engine built last sets it.
     library_products: bool = True
-    # Which kernel takes the products of more than 128 rows while ``library_products`` is on:
+    # Which kernel takes the products of more than 64 rows while ``library_products`` is on:
     # "library", "own" (the package's tcgen05 kernel for many rows) or "auto" (the package's
     # kernel where it fuses the feed-forward's gate, the library elsewhere); None: the
     # environment's DIB200_LARGE_PRODUCTS, else "auto".  One per process, like the switch above.

@@ -15,11 +15,16 @@ from ctypes import byref, c_float, c_int, c_longlong, c_void_p
 
 import torch
 
-# Rows up to which the package's own kernel is used; products of more rows go to the
-# library.  ``set_library_products(False)`` sends every product to the package's kernel,
-# whose order of summation does not depend on the number of rows: a token's bits are then
-# the same whatever else the step holds (the library's algorithm depends on the shape).
-OWN_KERNEL_ROWS = int(os.environ.get("DIB200_GEMM_MAX_ROWS", "128"))
+# Rows up to which the few-rows kernel (swap-AB, split of k) is used; products of more rows go
+# to the many-rows kernel or the library.  ``set_library_products(False)`` sends every product
+# to the few-rows kernel, whose order of summation does not depend on the number of rows: a
+# token's bits are then the same whatever else the step holds (the library's algorithm depends
+# on the shape).  64: the split of k is the decode step's (a function of the layer's sizes
+# alone), and its float32 partial sums grow with the rows: from 65 rows on they cost more than
+# the other kernels' few tiles do (0.6B sizes on B200: a prompt of 128 tokens 1.60 against
+# 1.95 ms, decode at batch 96 / 128 17,800 / 20,200 against 16,500 / 19,100 tokens a second;
+# batch 48 unchanged, and a line at 32 slower there).
+OWN_KERNEL_ROWS = int(os.environ.get("DIB200_GEMM_MAX_ROWS", "64"))
 MAX_ROWS = OWN_KERNEL_ROWS
 # DIB200_GATED=0/1 (read once): never / always the gate in the product's epilogue
 GATED = os.environ.get("DIB200_GATED")

@@ -127,7 +127,7 @@ def mixed(trace, requests, max_live=4, sizes=(11, 2, 17, 5, 2, 29, 3), tail=6, p
 
 
 def run_trace(model_dir, dtype, trace, out_dir, max_tokens=None, page_size=16, timeout=900,
-              user=None, cuda_graphs=False):
+              user=None, cuda_graphs=False, extra_env=None):
     """Run the trace through bin/trace_run; returns {step: float32 array [wanted, V]}."""
     out_dir = Path(out_dir)
     out_dir.mkdir(parents=True, exist_ok=True)
@@ -137,6 +137,7 @@ def run_trace(model_dir, dtype, trace, out_dir, max_tokens=None, page_size=16, t
     if cuda_graphs:
         cmd.append("--cuda-graphs")
     env = dict(os.environ)
+    env.update(extra_env or {})
     proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
     try:
         for rec in trace.steps:

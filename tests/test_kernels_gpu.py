@@ -193,22 +193,30 @@ def test_linear_fp32_row_does_not_depend_on_batch():
     (129, 152, 96), (300, 152, 96), (2048, 512, 256)])
 @pytest.mark.parametrize("cluster", ["1", "0"])
 def test_linear_bf16(m, n, k, cluster, switches):
-    """Rows up to 128 run the package's tcgen05 kernel (tails in N and K, split k,
-    one to four token tiles), more rows the library.  A split of k is added up by the
-    tile's cluster of CTAs (a finished tensor comes back) or left as partial products."""
+    """Few rows (up to ``gemm_bf16.MAX_ROWS``) run the package's swap-AB tcgen05 kernel (tails
+    in N and K, split k), more rows the library or the many-rows kernel.  A split of k is
+    added up by the tile's cluster of CTAs (a finished tensor comes back) or left as partial
+    products.  With the library switched off the few-rows kernel takes every row count (one
+    to many token tiles): the sizes above the line run on it too."""
     from deterministic_inference_b200.kernels import gemm_bf16
     switches.gemm(cluster=cluster)
     torch.manual_seed(8)
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (0.05 * torch.randn(n, k, device="cuda")).to(torch.bfloat16)
     want = x.float() @ w.float().T
-    got = ops().linear(x, w)
-    assert isinstance(got, ops().SplitSum) == (cluster == "0" and m <= 128
-                                               and gemm_bf16.plan(m, n, k, x.device)[2] > 1)
-    torch.testing.assert_close(ops().as_tensor(got).float(), want, atol=2e-2, rtol=2e-2)
-    got32 = ops().as_tensor(ops().linear(x, w, out_dtype=torch.float32))
-    assert got32.dtype == torch.float32
-    torch.testing.assert_close(got32, want, atol=1e-3, rtol=1e-3)
+    modes = [True] if m <= gemm_bf16.MAX_ROWS else [True, False]
+    try:
+        for library in modes:
+            gemm_bf16.set_library_products(library)
+            got = ops().linear(x, w)
+            assert isinstance(got, ops().SplitSum) == (cluster == "0" and m <= gemm_bf16.MAX_ROWS
+                                                       and gemm_bf16.plan(m, n, k, x.device)[2] > 1)
+            torch.testing.assert_close(ops().as_tensor(got).float(), want, atol=2e-2, rtol=2e-2)
+            got32 = ops().as_tensor(ops().linear(x, w, out_dtype=torch.float32))
+            assert got32.dtype == torch.float32
+            torch.testing.assert_close(got32, want, atol=1e-3, rtol=1e-3)
+    finally:
+        gemm_bf16.set_library_products(True)
     assert gemm_bf16.status() == 0
 
 
@@ -250,24 +258,29 @@ def test_cluster_sum_of_a_split_gives_the_bits_of_the_partials(m, n, k, splits, 
     distributed shared memory, once left as partial products that a reader adds in split
     order: the same bits, in bfloat16 and float32 outputs; and the gate after a cluster's
     sum gives what the gate kernel gives on the partials."""
+    from deterministic_inference_b200.kernels import gemm_bf16
     switches.gemm(splits=splits)
     torch.manual_seed(14)
     x = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     w = (0.05 * torch.randn(n, k, device="cuda")).to(torch.bfloat16)
     outs = {}
-    for cluster in ("1", "0"):
-        switches.gemm(cluster=cluster)
-        y = ops().linear(x, w)
-        assert isinstance(y, ops().SplitSum) == (cluster == "0")
-        outs[cluster] = (ops().as_tensor(y), ops().as_tensor(ops().linear(x, w, out_dtype=torch.float32)))
-    assert torch.equal(outs["1"][0], outs["0"][0]) and torch.equal(outs["1"][1], outs["0"][1])
-    if n % 128 == 0:
-        gated = {}
+    gemm_bf16.set_library_products(False)      # the few-rows kernel whatever the row count
+    try:
         for cluster in ("1", "0"):
             switches.gemm(cluster=cluster)
-            switches.gated("1" if cluster == "1" else "0")
-            gated[cluster] = ops().as_tensor(ops().gated_linear(x, w))
-        assert torch.equal(gated["1"], gated["0"])
+            y = ops().linear(x, w)
+            assert isinstance(y, ops().SplitSum) == (cluster == "0")
+            outs[cluster] = (ops().as_tensor(y), ops().as_tensor(ops().linear(x, w, out_dtype=torch.float32)))
+        assert torch.equal(outs["1"][0], outs["0"][0]) and torch.equal(outs["1"][1], outs["0"][1])
+        if n % 128 == 0:
+            gated = {}
+            for cluster in ("1", "0"):
+                switches.gemm(cluster=cluster)
+                switches.gated("1" if cluster == "1" else "0")
+                gated[cluster] = ops().as_tensor(ops().gated_linear(x, w))
+            assert torch.equal(gated["1"], gated["0"])
+    finally:
+        gemm_bf16.set_library_products(True)
 
 
 @pytest.mark.parametrize("m", [1, 8, 50])

@@ -149,7 +149,11 @@ def test_replay_with_captured_graphs(name, dtype, tiny_model_dirs, tmp_path):
     single tokens), and the mixed cutting on top; every row against the plain
     implementation, and the replayed run against a launched run of the same trace: equal
     bits (a captured step sizes its grids for the longest sequence its block-table width
-    allows, which must not change what a row adds up)."""
+    allows, which must not change what a row adds up).  A replayed step runs with its bucket's
+    row count and the launched run of this test with the step's own, so both runs keep every
+    matrix product on the few-rows kernel, whose sums do not depend on the row count (which
+    product kernel a row count selects is the one thing a bucket may change; the many-rows
+    kernels under graphs are compared in test_generate_gpu.py with lengths on bucket lines)."""
     cfg, w = plain_qwen3.read_model_dir(tiny_model_dirs[name])
     _, w64 = plain_qwen3.read_model_dir(tiny_model_dirs[name], torch.float64)
     n = 200 if name == "b" else 520
@@ -168,7 +172,8 @@ def test_replay_with_captured_graphs(name, dtype, tiny_model_dirs, tmp_path):
     outs = {}
     for graphs in (True, False):
         out = ru.run_trace(tiny_model_dirs[name], dtype, trace, tmp_path / f"out{int(graphs)}",
-                           page_size=page, cuda_graphs=graphs)
+                           page_size=page, cuda_graphs=graphs,
+                           extra_env={"DIB200_GEMM_MAX_ROWS": "1000000"})
         outs[graphs] = ru.read_rows(out, trace, cfg["vocab_size"])
     for key_pos, row in outs[True].items():
         assert torch.equal(row, outs[False][key_pos]), key_pos
