@@ -341,20 +341,23 @@ __device__ __forceinline__ void store_rows(unsigned src, const CUtensorMap* map_
                                            int lane, int row0, int n0, int half) {
   constexpr int PER_BLOCK = 128 / (int)sizeof(OutT);            // output values per row of a block
   constexpr int OUT_COLS = GATED ? BNL / 2 : BNL;               // output columns of a tile
-  constexpr int BLOCKS = OUT_COLS / 2 / PER_BLOCK;              // blocks of this warp's half
+  // a gated tile of 64 + 64 rows has one block of output columns: the first half's warps take it
+  constexpr bool ONE_HALF = GATED && OUT_COLS == PER_BLOCK;
+  constexpr int BLOCKS = ONE_HALF ? 1 : OUT_COLS / 2 / PER_BLOCK;   // blocks of this warp's half
+  if (ONE_HALF && half == 1) return;
 #pragma unroll 1
   for (int blk = 0; blk < BLOCKS; ++blk) {
-    const int col = half * (OUT_COLS / 2) + blk * PER_BLOCK;    // first output column of the block
+    const int col = (ONE_HALF ? 0 : half * (OUT_COLS / 2)) + blk * PER_BLOCK;    // first output column of the block
     // the store before this one must have read the staging block
     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     __syncwarp();
     if (GATED) {
-      // accumulator columns 0..127: gate, 128..255: up, of the same 128 features
+      // accumulator columns 0..BNL/2-1: gate, the other half: up, of the same features
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         unsigned g[32], u[32];
         tc_ld32(src + col + h * 32, g);
-        tc_ld32(src + 128 + col + h * 32, u);
+        tc_ld32(src + BNL / 2 + col + h * 32, u);
         tc_wait_ld();
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -406,7 +409,7 @@ __global__ void __launch_bounds__(THREADS, 1)
 gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                   const __grid_constant__ CUtensorMap map_out, int M, int N, int K, int m_tiles, int n_tiles,
                   const __grid_constant__ QkvEpilogue qk) {
-  static_assert(!GATED || BNL == 256, "the gated epilogue pairs 128 gate rows with 128 up rows");
+  // (gated: a tile holds BNL / 2 gate rows and the BNL / 2 up rows of the same features)
   using TL = Tile<BNL, QKV>;
   constexpr int B_BYTES = TL::B_BYTES, STAGE_BYTES = TL::STAGE_BYTES, STAGES = TL::STAGES;
   extern __shared__ unsigned char smem_raw[];
@@ -468,7 +471,7 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           const int n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
           unsigned char* b = smem + (c % STAGES) * STAGE_BYTES + A_BYTES;
           tma_load_2d(b, &map_w, kb * BK, n0, &full[c % STAGES]);
-          if (BNL == 256)
+          if (BNL == 256 || GATED)     // (the weight map's boxes are 128 rows, or BNL / 2 for a gated tile)
             tma_load_2d(b + B_BYTES / 2, &map_w, kb * BK, GATED ? N + n0 : n0 + 128, &full[c % STAGES]);
         };
         auto load_x = [&](int c) {
@@ -529,18 +532,22 @@ gemm_large_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++local) {
       const int buf = local & 1;
       const int m0 = (t % m_tiles) * BM, n0 = (t / m_tiles) * (GATED ? BNL / 2 : BNL);
+      // (QKV tiles of 128 columns are one head: the warps of the second half have no part in them)
+      const bool works = !(QKV && BNL == 128 && half == 1);
       QkvRows rows;
-      if (QKV) qkv_rows_prepare(rows, lane, m0 + quarter * 32, n0, half, qk);
+      if (QKV && works) qkv_rows_prepare(rows, lane, m0 + quarter * 32, n0, half, qk);
       bool got = ok && mbar_wait(&acc_full[buf], (local >> 1) & 1);
       got = __all_sync(0xffffffffu, got);     // tcgen05.ld below is warp-wide
       if (!got) { ok = false; break; }
       tc_fence_after();
-      if (QKV)
-        store_rows_qkv(tmem + buf * BNL + lane_base, epi_stage + (warp - EPI_WARP0) * 2 * EPI_STAGE_BYTES, lane, half, qk, rows,
-                       &map_out, m0 + quarter * 32);
-      else
+      if (QKV) {
+        if (works)
+          store_rows_qkv(tmem + buf * BNL + lane_base, epi_stage + (warp - EPI_WARP0) * 2 * EPI_STAGE_BYTES, lane, half, qk,
+                         rows, &map_out, m0 + quarter * 32);
+      } else {
         store_rows<OutT, GATED, BNL>(tmem + buf * BNL + lane_base, &map_out, epi_stage + (warp - EPI_WARP0) * EPI_STAGE_BYTES,
                                      lane, m0 + quarter * 32, n0, half);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);
@@ -831,7 +838,7 @@ template <typename OutT, bool GATED, int BNL, bool QKV = false>
 int launch_large(const void* x, const void* w, void* out, int M, int N, int K, int sm_count,
                  cudaStream_t st, const QkvEpilogue& qk = QkvEpilogue{}) {
   CUtensorMap mx, mw, mo;
-  if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, GATED ? 2ll * N : (long long)N, K, 128) ||
+  if (!make_map(&mx, x, M, K, BM) || !make_map(&mw, w, GATED ? 2ll * N : (long long)N, K, GATED ? BNL / 2 : 128) ||
       !make_out_map<OutT>(&mo, out, M, QKV ? (long long)qk.Hq * 128 : (long long)N))
     return DIB_LAUNCH_FAILED;
   const int m_tiles = (M + BM - 1) / BM;
@@ -902,13 +909,14 @@ int& forced_shape() {
 // A function of the sizes and the SM count alone (the order in which a row's k is added up
 // is the same for all three, so the choice never changes a bit of the result).  The pair of
 // CTAs where its tiles of 256 x 256 keep two thirds of the SMs busy or more; else tiles of
-// 128 x 256, or of 128 x 128 where those would be fewer than the SMs.
+// 128 x 256, or of 128 x 128 where twice as many tiles still get an SM each (two rounds of
+// half tiles are no shorter than one round of whole ones).
 int tile_shape(int M, int n_rows, int sm_count) {
   if (forced_shape() >= 0) return forced_shape();
   const long long pair_tiles = (long long)((M + 2 * BM - 1) / (2 * BM)) * ((n_rows + 255) / 256);
   if (sm_count >= 2 && 3 * pair_tiles >= sm_count) return 2;
   const long long tiles256 = (long long)((M + BM - 1) / BM) * ((n_rows + 255) / 256);
-  return tiles256 < sm_count && n_rows > 128 ? 0 : 1;
+  return 2 * tiles256 <= sm_count && n_rows > 128 ? 0 : 1;
 }
 
 }  // namespace
@@ -955,9 +963,10 @@ int dib_gemm_bf16_large_gated(const void* x, const void* w, void* out, int M, in
   if (K < 8 || K % 8 != 0 || I % 8 != 0 || sm_count < 1) return DIB_BAD_SIZE;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(out)) % 16 != 0)
     return DIB_BAD_ALIGN;
-  return tile_shape(M, 2 * I, sm_count) == 2
-             ? launch_pair<__nv_bfloat16, true, 256>(x, w, out, M, I, K, sm_count, st)
-             : launch_large<__nv_bfloat16, true, 256>(x, w, out, M, I, K, sm_count, st);
+  const int shape = tile_shape(M, 2 * I, sm_count);
+  if (shape == 2) return launch_pair<__nv_bfloat16, true, 256>(x, w, out, M, I, K, sm_count, st);
+  if (shape == 0) return launch_large<__nv_bfloat16, true, 128>(x, w, out, M, I, K, sm_count, st);
+  return launch_large<__nv_bfloat16, true, 256>(x, w, out, M, I, K, sm_count, st);
 }
 
 // The fused q/k/v projection of a prompt portion: x [M, K] times w [(Hq + 2 Hkv) * 128, K]^T,
@@ -980,9 +989,12 @@ int dib_gemm_bf16_large_qkv(const void* x, const void* w, void* q_out, int M, in
   qk.positions = positions; qk.slot_mapping = slot_mapping; qk.cache = (__nv_bfloat16*)cache;
   qk.q_out = (__nv_bfloat16*)q_out;
   qk.num_pages = num_pages; qk.page_size = page_size; qk.Hq = Hq; qk.Hkv = Hkv; qk.M = M;
-  return tile_shape(M, N, sm_count) == 2
-             ? launch_pair<__nv_bfloat16, false, 256, true>(x, w, q_out, M, N, K, sm_count, st, qk)
-             : launch_large<__nv_bfloat16, false, 256, true>(x, w, q_out, M, N, K, sm_count, st, qk);
+  // (tiles of one head where tiles of two would be fewer than the SMs: a prompt portion of up to
+  // about a thousand tokens)
+  const int shape = tile_shape(M, N, sm_count);
+  if (shape == 2) return launch_pair<__nv_bfloat16, false, 256, true>(x, w, q_out, M, N, K, sm_count, st, qk);
+  if (shape == 0) return launch_large<__nv_bfloat16, false, 128, true>(x, w, q_out, M, N, K, sm_count, st, qk);
+  return launch_large<__nv_bfloat16, false, 256, true>(x, w, q_out, M, N, K, sm_count, st, qk);
 }
 
 }  // extern "C"

@@ -959,7 +959,7 @@ def test_gated_product_many_rows_gives_the_bits_of_product_and_gate(m, i, k):
     two = ops().silu_mul(gemm_bf16.linear_large(x, w, torch.bfloat16))
     assert fused is not None and torch.equal(fused, two)
     try:
-        for shape in (1, 2):      # one CTA on 128 tokens; a pair of CTAs on 256
+        for shape in (0, 1, 2):   # one CTA on 128 tokens and 64 + 64 or 128 + 128 weight rows; a pair of CTAs on 256
             gemm_bf16.force_large_shape(shape)
             assert torch.equal(gemm_bf16.gated_linear_large(x, w), fused), shape
     finally:
@@ -976,7 +976,7 @@ def test_gated_product_many_rows_gives_the_bits_of_product_and_gate(m, i, k):
 def test_qkv_projection_with_the_norms_in_its_epilogue_gives_the_bits_of_the_two_kernels(t, hq, hkv, k, page_size,
                                                                                          norm, rope):
     """The fused q/k/v projection of many bfloat16 rows whose epilogue norms q and k, rotates them
-    and writes k and v to the cache (one kernel, on one CTA a tile and on a pair of CTAs),
+    and writes k and v to the cache (one kernel; tiles of one head and of two on one CTA, of two on a pair of CTAs),
     against the same product followed by the q/k kernel: the same q rows and the same cache,
     bit for bit; with and without norm weights and a rotation, an odd number of heads (the
     last tile's second half lies beyond them), token counts and depths off the tile's sizes,
@@ -1003,7 +1003,7 @@ def test_qkv_projection_with_the_norms_in_its_epilogue_gives_the_bits_of_the_two
     want_q = o.qk_norm_rope_cache(gemm_bf16.linear_large(x, w, torch.bfloat16), hq, hkv, d, qn, kn, 1e-6, table,
                                   positions, want_cache, slots, page_size)
     try:
-        for shape in (1, 2):
+        for shape in (0, 1, 2):
             gemm_bf16.force_large_shape(shape)
             cache = torch.full_like(want_cache, 7.0)
             q = gemm_bf16.qkv_large(x, w, hq, hkv, qn, kn, 1e-6, table, positions, cache, slots, page_size)
