@@ -23,7 +23,7 @@ import torch
 # alone), and its float32 partial sums grow with the rows: from 65 rows on they cost more than
 # the other kernels' few tiles do (0.6B sizes on B200: a prompt of 128 tokens 1.60 against
 # 1.95 ms, decode at batch 96 / 128 17,800 / 20,200 against 16,500 / 19,100 tokens a second;
-# batch 48 unchanged, and a line at 32 slower there).
+# batch 48 unchanged; a line at 48 is 3 % slower at batch 56 and 64, one at 32 slower at 48).
 OWN_KERNEL_ROWS = int(os.environ.get("DIB200_GEMM_MAX_ROWS", "64"))
 MAX_ROWS = OWN_KERNEL_ROWS
 # DIB200_GATED=0/1 (read once): never / always the gate in the product's epilogue
